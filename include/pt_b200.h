@@ -1,0 +1,176 @@
+/*
+ * C ABI of the sm_100a (B200) low-precision GEMM path: quantize / dequantize,
+ * dense and grouped FP8 / MXFP8 / MXFP4 GEMMs.
+ *
+ * This is the boundary a host binding talks to.  It replaces the operators the
+ * reference registers in TORCH_LIBRARY(primus_turbo_cpp_extension, ...)
+ * (csrc/pytorch/bindings_pytorch.cpp:15-135) and the Python-level custom ops
+ * primus_turbo::gemm_fp8_impl / grouped_gemm_fp8_impl / ... that wrap its Triton and
+ * FlyDSL kernels (primus_turbo/pytorch/kernels/gemm/gemm_fp8_impl.py:518-593,
+ * primus_turbo/pytorch/kernels/grouped_gemm/grouped_gemm_fp8_impl.py:888-1030).
+ *
+ * Conventions
+ *  - every pointer is a DEVICE pointer unless its comment says "host";
+ *  - the caller allocates every output and every workspace (the reference's ops allocate
+ *    with at::empty; here the binding does that and passes the pointers);
+ *  - `stream` is a cudaStream_t passed as void*; all work is enqueued on it, nothing
+ *    synchronises the device;
+ *  - every function returns 0 on success or a negative pt_status; pt_last_error() gives
+ *    the message of the last failure on the calling thread (the reference throws
+ *    std::runtime_error through PRIMUS_TURBO_CHECK, csrc/include/primus_turbo/macros.h:71-84);
+ *  - inputs are never written; outputs may be left unwritten only where stated.
+ */
+#ifndef PT_B200_H_
+#define PT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum { PT_OK = 0, PT_ERR_INVALID = -1, PT_ERR_CUDA = -2, PT_ERR_UNSUPPORTED = -3, PT_ERR_TIMEOUT = -4 } pt_status;
+
+/* source / output element types */
+typedef enum { PT_BF16 = 0, PT_F16 = 1, PT_F32 = 2 } pt_dtype;
+/* quantized element formats: e4m3fn, e5m2 (1 byte each), e2m1 (two per byte, element 2j in the low nibble) */
+typedef enum { PT_E4M3 = 0, PT_E5M2 = 1, PT_E2M1 = 2 } pt_format;
+/* scaling granularity, in the order of ScalingGranularity (primus_turbo/pytorch/core/low_precision.py:123-132),
+ * counted from 0 (the Python enum counts from 1) */
+typedef enum { PT_TENSORWISE = 0, PT_ROWWISE = 1, PT_BLOCKWISE = 2, PT_MX_BLOCKWISE = 3 } pt_granularity;
+
+const char *pt_last_error(void);
+/* Library / device sanity: returns the number of SMs of the current device, or a negative status. */
+int pt_device_sm_count(void);
+
+/* ------------------------------------------------------------------ tensorwise / rowwise FP8 */
+
+/* Bytes of scratch pt_quantize_fp8_tensorwise needs (holds the running amax). */
+size_t pt_quantize_fp8_tensorwise_workspace_bytes(void);
+
+/* q = fp8(clamp(x * scale, +-qmax)), scale = qmax / max(amax(|x|), 1e-12), *scale_inv = 1 / scale.
+ * x: n contiguous elements of x_dtype.  scale_opt: optional device float; when given it is used as
+ * `scale` and no amax is taken.  workspace: >= pt_quantize_fp8_tensorwise_workspace_bytes() bytes.
+ * Replaces quantize_fp8_tensorwise (csrc/pytorch/quantization/quantization.cpp:44-90). */
+int pt_quantize_fp8_tensorwise(const void *x, int x_dtype, int64_t n, int fmt, void *q, float *scale_inv,
+                               const float *scale_opt, void *workspace, size_t workspace_bytes, void *stream);
+
+/* x viewed as [B, M, N] with the scaled axis being M when axis_is_last == 0 (scale_inv is [B, 1, N]) or
+ * N when axis_is_last != 0 (pass B = 1, M = outer rows; scale_inv is [M, 1]).  scale_opt as above, same
+ * shape as scale_inv.  workspace: B*N floats when axis_is_last == 0 and scale_opt is null, else unused.
+ * Replaces quantize_fp8_rowwise (quantization.cpp:110-208). */
+int pt_quantize_fp8_rowwise(const void *x, int x_dtype, int64_t B, int64_t M, int64_t N, int axis_is_last, int fmt,
+                            void *q, float *scale_inv, const float *scale_opt, void *workspace,
+                            size_t workspace_bytes, void *stream);
+
+/* y = float(q) * scale_inv, cast to y_dtype.  Scale broadcast is described by [B, M, N] as above:
+ * tensorwise: B = M = 1 and scale_kind = 0; per-row (axis last): scale_kind = 1; per-column: scale_kind = 2.
+ * Replaces dequantize_fp8_tensorwise / dequantize_fp8_rowwise (quantization.cpp:211-330). */
+int pt_dequantize_fp8(const void *q, int fmt, const float *scale_inv, int scale_kind, int64_t B, int64_t M,
+                      int64_t N, void *y, int y_dtype, void *stream);
+
+/* ------------------------------------------------------------------ 128-blockwise FP8 */
+
+/* 1 x 128 (row) and / or 128 x 1 (col) block scales of x [M, N]; eps 1e-4; stored scale is 1/scale.
+ * q_row [M, N], s_row [M, ceil(N/128)]; q_col [M, N] (NOT transposed), s_col [ceil(M/128), N].
+ * Pass null for the direction that is not wanted.
+ * Replaces quant_fp8_blockwise_impl / quant_fp8_blockwise_dual_impl
+ * (primus_turbo/pytorch/kernels/quantization/quantization_impl.py:81-125,236-281). */
+int pt_quantize_fp8_blockwise(const void *x, int x_dtype, int64_t M, int64_t N, int fmt, void *q_row, float *s_row,
+                              void *q_col, float *s_col, void *stream);
+
+/* One scale per 128 x 128 tile of w [B, M, N]; s [B, ceil(M/128), ceil(N/128)].
+ * Replaces quantize_fp8_blockwise_for_weight (bindings_pytorch.cpp:40, quantization_blockwise.cu:248-346). */
+int pt_quantize_fp8_blockwise_weight(const void *w, int x_dtype, int64_t B, int64_t M, int64_t N, int fmt, void *q,
+                                     float *s, void *stream);
+
+/* Grouped row + segment-padded column quantization of x [M, N] whose rows are split into G groups.
+ * group_offs / padded_offs: int64 [G+1] exclusive prefix sums of the group lengths and of the lengths
+ * rounded up to 128.  q_row [M, N]; s_row [ceil(N/128), M] (transposed); q_col [m_alloc, N] and
+ * s_col [m_alloc/128, N] with m_alloc = M + G*128; rows at or past padded_offs[G] are not written.
+ * Replaces quantize_fp8_blockwise_segment_m_row_col (bindings_pytorch.cpp:38, quantization_blockwise.cu:60-232). */
+int pt_quantize_fp8_blockwise_segment_m(const void *x, int x_dtype, int64_t M, int64_t N, int G,
+                                        const int64_t *group_offs, const int64_t *padded_offs, int fmt, void *q_row,
+                                        float *s_row, void *q_col, float *s_col, void *stream);
+
+/* y = float(q) * s with the block scale layouts above: kind 0 = row (s [M, ceil(N/128)]),
+ * 1 = col (s [ceil(M/128), N]), 2 = weight tiles (s [ceil(M/128), ceil(N/128)]); B batches.
+ * Replaces dequant_fp8_blockwise_impl / dequant_fp8_blockwise_for_weight_impl (quantization_impl.py:146-233). */
+int pt_dequantize_fp8_blockwise(const void *q, int fmt, const float *s, int kind, int64_t B, int64_t M, int64_t N,
+                                void *y, int y_dtype, void *stream);
+
+/* ------------------------------------------------------------------ group offsets */
+
+/* offs[0] = 0, offs[i+1] = sum_{j<=i} lens[j]; int64, G <= 4096.
+ * Replaces grouped_gemm_compute_offs (bindings_pytorch.cpp:134, compute_group_offs.cu:15-32). */
+int pt_compute_group_offs(const int64_t *lens, int G, int64_t *offs, void *stream);
+/* plens[i] = ceil_to(lens[i], align); poffs = their exclusive prefix sums
+ * (quantization_blockwise.cu:18-36, quantization_mxfp8.cu:2025-2039). */
+int pt_compute_padded_group_offs(const int64_t *lens, int G, int64_t align, int64_t *plens, int64_t *poffs,
+                                 void *stream);
+
+/* ------------------------------------------------------------------ MX (32-element blocks, ue8m0 scales) */
+
+/* flags for pt_quantize_mx */
+#define PT_MX_ROW 1u        /* produce the row-wise copy  (blocks along N) */
+#define PT_MX_COL 2u        /* produce the col-wise, transposed copy (blocks along M) */
+#define PT_MX_ROW_2D 4u     /* row copy uses one scale per 32 x 32 tile */
+#define PT_MX_COL_2D 8u     /* col copy uses one scale per 32 x 32 tile */
+#define PT_MX_ROW_RHT 16u   /* e2m1 only: 16-point Hadamard along the quantized axis before amax */
+#define PT_MX_COL_RHT 32u
+
+/* x [G, M, N] (G = 1 for 2-D), bf16 / fp16, N % 32 == 0.  M_pad = ceil128(M), N_pad = ceil128(N).
+ * fmt e4m3 / e5m2: q_row [G, M, N_pad], s_row [G, M, N_pad/32]; q_col [G, N, M_pad], s_col [G, N, M_pad/32].
+ * fmt e2m1: data rows are half as long (two codes per byte).  Pad columns hold zeros (scale byte 0).
+ * Replaces quantize_mxfp8 / quantize_mxfp8_dual / quantize_mxfp4 / quantize_mxfp4_dual with shuffle off
+ * (bindings_pytorch.cpp:52-93; csrc/pytorch/quantization/quantization.cpp:511-969). */
+int pt_quantize_mx(const void *x, int x_dtype, int64_t G, int64_t M, int64_t N, int fmt, unsigned flags,
+                   void *q_row, uint8_t *s_row, void *q_col, uint8_t *s_col, void *stream);
+
+/* y [rows, cols] = decode(q [rows, cols_stored]) * 2^(s - 127); cols <= cols_stored (the stored row length in
+ * elements, a multiple of 32); s [rows, cols_stored/32].  When transpose_out != 0 y is written as [cols, rows]
+ * (col-wise inputs are returned re-transposed, quantization.cpp:332-358).
+ * Replaces dequantize_mxfp8 / dequantize_mxfp4 (bindings_pytorch.cpp:58,88). */
+int pt_dequantize_mx(const void *q, int fmt, const uint8_t *s, int64_t rows, int64_t cols, int64_t cols_stored,
+                     int transpose_out, void *y, int y_dtype, void *stream);
+
+/* ------------------------------------------------------------------ transpose */
+/* y [N, M] = x [M, N]^T for 1-, 2- or 4-byte elements (bindings_pytorch.cpp:44, csrc/kernels/transpose/transpose_2d.cu). */
+int pt_transpose_2d(const void *x, int64_t M, int64_t N, int elem_bytes, void *y, void *stream);
+
+/* ------------------------------------------------------------------ FP8 / MXFP8 GEMM (tcgen05, TMEM accumulators) */
+
+/* C [M, N] (row-major, c_dtype) = A [M, K] . B [N, K]^T, both operands K-major FP8 bytes ("NT").  Other
+ * layouts of the reference's (trans_a, trans_b, trans_c) are reached by swapping operands (trans_c) or by
+ * handing in the transposed copy (pt_transpose_2d) as the reference itself does for its NT-only back ends
+ * (primus_turbo/pytorch/ops/gemm_fp8.py:44-50,126-149).
+ *   granularity PT_TENSORWISE:   a_scale, b_scale = device float[1] (scale_inv);  C = acc * a_scale * b_scale
+ *   granularity PT_ROWWISE:      a_scale float[M], b_scale float[N];               C = acc * a_scale[m] * b_scale[n]
+ *   granularity PT_MX_BLOCKWISE: a_scale uint8 [M, K/32], b_scale uint8 [N, K/32] (ue8m0, raw row-major as the
+ *                                quantizer writes them); K is the padded length (multiple of 128)
+ * a_fmt / b_fmt: PT_E4M3 or PT_E5M2 (may differ: HYBRID).  beta: 0, or 1 to accumulate into C.
+ * block_n: 0 = default tile width, else 128 / 240 / 256.  status: optional device int that receives
+ * PT_ERR_TIMEOUT if a bounded wait inside the kernel expires (it is never written otherwise).
+ * Replaces primus_turbo::gemm_fp8_impl / gemm_fp8_accum_impl (primus_turbo/pytorch/kernels/gemm/gemm_fp8_impl.py:518-593)
+ * and the vendor ops hipblaslt_gemm_fp8 / ck_gemm_fp8 / turbo_gemm_fp8 (csrc/pytorch/bindings_pytorch.cpp:20-31). */
+int pt_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const void *b, const void *b_scale, int b_fmt, void *c,
+                int c_dtype, int granularity, int64_t M, int64_t N, int64_t K, float beta, int block_n, int *status,
+                void *stream);
+
+/* Grouped form: rows are split into G groups, group g multiplies B[g] ([G, N, K] contiguous).
+ * group_offs_write int64 [G+1]: first C row of each group (tight); group length = difference.
+ * group_offs_read  int64 [G+1] or null: first A row of each group when A (and its scales) were written in a
+ * padded layout (MX grouped quantizers); null = same as group_offs_write.
+ * a_rows: rows of the A buffer; c_rows: rows of C covered by the groups.  Rows of C at or past
+ * group_offs_write[G] are not written.  max_ctas: 0 = one CTA per SM, else an upper bound (the reference's num_cu).
+ * Replaces primus_turbo::grouped_gemm_fp8_impl (primus_turbo/pytorch/kernels/grouped_gemm/grouped_gemm_fp8_impl.py:888-930). */
+int pt_grouped_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const void *b, const void *b_scale, int b_fmt,
+                        void *c, int c_dtype, int granularity, int64_t a_rows, int64_t c_rows, int64_t N, int64_t K,
+                        const int64_t *group_offs_read, const int64_t *group_offs_write, int G, float beta, int block_n,
+                        int max_ctas, int *status, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PT_B200_H_ */

@@ -1,0 +1,125 @@
+// Shared device / host helpers for the sm_100a low-precision GEMM path.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/pt_b200.h"
+
+namespace ptb {
+
+// ---------------------------------------------------------------- error reporting
+// Records a message for pt_last_error() and returns `code`.
+int set_error(int code, const char *fmt, ...);
+
+#define PT_REQUIRE(cond, ...)                                                                      \
+    do {                                                                                           \
+        if (!(cond)) return ::ptb::set_error(PT_ERR_INVALID, __VA_ARGS__);                         \
+    } while (0)
+
+#define PT_CUDA_OK(expr)                                                                           \
+    do {                                                                                           \
+        cudaError_t _e = (expr);                                                                   \
+        if (_e != cudaSuccess)                                                                     \
+            return ::ptb::set_error(PT_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                   \
+                                    cudaGetErrorString(_e), __FILE__, __LINE__);                   \
+    } while (0)
+
+#define PT_LAUNCH_OK() PT_CUDA_OK(cudaGetLastError())
+
+int sm_count();  // cached multiprocessor count of the current device
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+inline int64_t ceil_to(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
+
+// ---------------------------------------------------------------- element access
+template <typename T> struct Src;
+template <> struct Src<__nv_bfloat16> {
+    static __device__ __forceinline__ float to_f32(uint16_t b) { return __uint_as_float((uint32_t) b << 16); }
+};
+template <> struct Src<__half> {
+    static __device__ __forceinline__ float to_f32(uint16_t b) { return __half2float(__ushort_as_half(b)); }
+};
+
+// Loads 8 consecutive elements starting at p (16-byte aligned for 2-byte types, 32 for fp32).
+template <typename T> __device__ __forceinline__ void load8(const T *p, float (&v)[8]) {
+    const uint4 r = __ldg(reinterpret_cast<const uint4 *>(p));
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i]     = Src<T>::to_f32((uint16_t) (w[i] & 0xFFFF));
+        v[2 * i + 1] = Src<T>::to_f32((uint16_t) (w[i] >> 16));
+    }
+}
+template <> __device__ __forceinline__ void load8<float>(const float *p, float (&v)[8]) {
+    const float4 a = __ldg(reinterpret_cast<const float4 *>(p));
+    const float4 b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <typename T> __device__ __forceinline__ float load1(const T *p) {
+    return Src<T>::to_f32(*reinterpret_cast<const uint16_t *>(p));
+}
+template <> __device__ __forceinline__ float load1<float>(const float *p) { return *p; }
+
+// ---------------------------------------------------------------- fp32 -> fp8 / fp4 (RNE, saturate to finite)
+// Two floats to two codes; `lo` lands in the low byte (lower address).
+template <int FMT> __device__ __forceinline__ uint16_t cvt2_fp8(float lo, float hi) {
+    uint16_t r;
+    if constexpr (FMT == PT_E4M3)
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    else
+        asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+template <int FMT> __device__ __forceinline__ uint32_t cvt4_fp8(float a, float b, float c, float d) {
+    return (uint32_t) cvt2_fp8<FMT>(a, b) | ((uint32_t) cvt2_fp8<FMT>(c, d) << 16);
+}
+template <int FMT> __device__ __forceinline__ uint8_t cvt1_fp8(float a) {
+    return (uint8_t) (cvt2_fp8<FMT>(a, 0.f) & 0xFF);
+}
+// Two floats to one byte of e2m1 codes; `lo` in the low nibble.
+__device__ __forceinline__ uint8_t cvt2_e2m1(float lo, float hi) {
+    uint16_t r;
+    asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u16.u8 %0, t; }" : "=h"(r) : "f"(hi), "f"(lo));
+    return (uint8_t) r;
+}
+
+template <int FMT> struct FmtMax;
+template <> struct FmtMax<PT_E4M3> { static constexpr float value = 448.f; };
+template <> struct FmtMax<PT_E5M2> { static constexpr float value = 57344.f; };
+
+// y = fmax(fmin(x * scale, qmax), -qmax)
+template <int FMT> __device__ __forceinline__ float scale_clamp(float x, float scale) {
+    return fmaxf(fminf(x * scale, FmtMax<FMT>::value), -FmtMax<FMT>::value);
+}
+// scale = qmax / fmax(amax, eps), a true (correctly rounded) division
+template <int FMT> __device__ __forceinline__ float scale_from_amax(float amax, float eps) {
+    return __fdiv_rn(FmtMax<FMT>::value, fmaxf(amax, eps));
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+    return __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(v)));  // v >= 0
+}
+
+// ---------------------------------------------------------------- dispatch helpers (host)
+#define PT_SWITCH_SRC(dtype, T, ...)                                                               \
+    switch (dtype) {                                                                               \
+    case PT_BF16: { using T = __nv_bfloat16; __VA_ARGS__; } break;                                 \
+    case PT_F16: { using T = __half; __VA_ARGS__; } break;                                         \
+    case PT_F32: { using T = float; __VA_ARGS__; } break;                                          \
+    default: return ::ptb::set_error(PT_ERR_INVALID, "unsupported source dtype %d", (int) dtype);  \
+    }
+
+#define PT_SWITCH_FP8(fmt, F, ...)                                                                 \
+    switch (fmt) {                                                                                 \
+    case PT_E4M3: { constexpr int F = PT_E4M3; __VA_ARGS__; } break;                               \
+    case PT_E5M2: { constexpr int F = PT_E5M2; __VA_ARGS__; } break;                               \
+    default: return ::ptb::set_error(PT_ERR_INVALID, "unsupported fp8 format %d", (int) fmt);      \
+    }
+
+inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+template <typename T> constexpr size_t vec8_align() { return sizeof(T) == 4 ? 16 : 16; }
+
+}  // namespace ptb

@@ -1,0 +1,526 @@
+// Dense and grouped FP8 / MXFP8 GEMM for sm_100a:  C[m, n] = sum_k A[m, k] * B[n, k]  (both operands
+// K-major, "NT"), fp32 accumulation in tensor memory.
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0      TMA producer: A (128 x 128 B) and B (BLOCK_N x 128 B) tiles, 128-byte swizzle, into a ring
+//   warp 1      MMA issuer (one elected lane): tcgen05.mma kind::f8f6f4 or kind::mxf8f6f4.block_scale;
+//               owns the TMEM allocation
+//   warps 2-5   MX only: bring the raw row-major ue8m0 scales [rows, K/32] into the 32 x 16 B block layout
+//               tcgen05.cp expects, one 128-row block per 128-K step
+//   warps 6-9   epilogue: TMEM -> registers -> (scales) -> staging in shared memory -> coalesced global stores
+// The accumulator is double buffered in TMEM when 2 * BLOCK_N (+ scale columns) fits in 512 columns, so the
+// epilogue of tile i overlaps the main loop of tile i + 1.
+//
+// Scaling modes (reference semantics: primus_turbo/triton/gemm/gemm_fp8_kernel.py:167-169,231,447-565;
+// MX: hardware block scaling as in csrc/pytorch/gemm/hipblaslt_gemm.cpp:127-135):
+//   TENSORWISE   C = acc * (sa[0] * sb[0])
+//   ROWWISE      C = acc * sa[m] * sb[n]
+//   MX_BLOCKWISE C = sum over 32-element K blocks of (a * 2^(sfa-127)) * (b * 2^(sfb-127))
+// Grouped form: rows of A / C are split into G groups (group g uses B[g]); tiles never cross a group.
+#include <algorithm>
+#include <mutex>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace ptb {
+using namespace sm100;
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 128;  // bytes == fp8 elements per stage row
+constexpr int UMMA_K = 32;    // fp8 elements per tcgen05.mma
+constexpr int kNumSfWarps = 4;
+constexpr int kNumEpiWarps = 4;
+constexpr int kGemmThreads = 32 * (2 + kNumSfWarps + kNumEpiWarps);
+constexpr int kSfWarp0 = 2;
+constexpr int kEpiWarp0 = 2 + kNumSfWarps;
+constexpr int kStagePitchMax = 128 + 16;  // staging row pitch (bytes) of the epilogue, fp32 worst case
+constexpr int kMaxGroups = 1024;
+
+enum GemmMode { GEMM_TENSOR = 0, GEMM_ROW = 1, GEMM_MX = 3 };
+
+struct GemmParams {
+    int64_t M;             // rows of A / C (all groups)
+    int N, K;              // K in elements, contraction length the tensor maps cover
+    void *C;
+    int64_t ldc;           // elements
+    int c_dtype;
+    int vec_store_ok;
+    float beta;            // 0 or 1 (C += ...)
+    const float *sa, *sb;  // fp32 scales (tensorwise / rowwise)
+    const uint8_t *sfa, *sfb;  // ue8m0 scales (MX), row pitch sf_ld bytes
+    int64_t sf_ld;
+    int a_fmt, b_fmt;      // 0 = e4m3, 1 = e5m2
+    // grouping: null offsets = one group covering [0, M)
+    const int64_t *offs_read;   // [G+1] first A row of each group (layout A was written in)
+    const int64_t *offs_write;  // [G+1] first C row of each group; group length = difference
+    int G;
+    int64_t b_group_rows;       // rows between consecutive B[g] (N for [G, N, K])
+    int *status;                // device int: set to a PT_ERR_* code on a bounded-wait expiry
+};
+
+template <int BLOCK_N, bool MX> struct GemmCfg {
+    static constexpr int kSfbBlocks = (BLOCK_N + 127) / 128;
+    static constexpr int kSfCols = MX ? 4 + 4 * kSfbBlocks : 0;
+    static constexpr int kAccStages = (2 * BLOCK_N + kSfCols <= 512) ? 2 : 1;
+    static constexpr int kTmemColsNeeded = kAccStages * BLOCK_N + kSfCols;
+    static constexpr int kTmemCols = kTmemColsNeeded <= 32 ? 32 : kTmemColsNeeded <= 64 ? 64 : kTmemColsNeeded <= 128 ? 128
+                                     : kTmemColsNeeded <= 256 ? 256 : 512;
+    static constexpr int kABytes = BLOCK_M * BLOCK_K;
+    static constexpr int kBBytes = BLOCK_N * BLOCK_K;
+    static constexpr int kSfBytes = MX ? 512 * (1 + kSfbBlocks) : 0;
+    static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
+    static constexpr int kEpiBytes = kNumEpiWarps * 32 * kStagePitchMax;
+    static constexpr int kBarBytes = 1024;
+    static constexpr int kSmemBudget = 227 * 1024 - 1024 /* alignment slack */ - 4608 /* static shared: tile table */;
+    static constexpr int kStages = std::min(8, (kSmemBudget - kEpiBytes - kBarBytes) / kStageBytes);
+    static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarBytes + 1024;
+    static_assert(kStages >= 3, "not enough shared memory for a 3-stage ring");
+    static_assert(BLOCK_N % 16 == 0 && BLOCK_N >= 16 && BLOCK_N <= 256, "invalid UMMA N");
+    static_assert(kBBytes % 1024 == 0, "B stage must keep 1024-byte alignment");
+};
+
+// Tile walk shared by every role: tiles are numbered group by group, rows (m) fastest inside a group.
+struct TileWalk {
+    const int *tile_start;  // shared memory [G+1]
+    int G, num_n_blocks;
+    int g;
+    __device__ __forceinline__ bool locate(int t, int &g_out, int &m_blk, int &n_blk) {
+        if (t >= tile_start[G]) return false;
+        while (t >= tile_start[g + 1]) ++g;
+        const int local = t - tile_start[g];
+        const int m_blocks = (tile_start[g + 1] - tile_start[g]) / num_n_blocks;
+        g_out = g;
+        m_blk = local % m_blocks;
+        n_blk = local / m_blocks;
+        return true;
+    }
+};
+
+template <typename OutT> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+template <int BLOCK_N, int MODE>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
+    constexpr bool MX = MODE == GEMM_MX;
+    using Cfg = GemmCfg<BLOCK_N, MX>;
+    constexpr int kStages = Cfg::kStages;
+    constexpr int kAccStages = Cfg::kAccStages;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *smem_a = smem;
+    uint8_t *smem_b = smem_a + kStages * Cfg::kABytes;
+    uint8_t *smem_sf = smem_b + kStages * Cfg::kBBytes;
+    uint8_t *smem_epi = smem_sf + kStages * Cfg::kSfBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_epi + Cfg::kEpiBytes);
+    uint64_t *full_bar = bars;                        // [kStages]
+    uint64_t *empty_bar = bars + kStages;             // [kStages]
+    uint64_t *tmem_full_bar = bars + 2 * kStages;     // [kAccStages]
+    uint64_t *tmem_empty_bar = tmem_full_bar + kAccStages;
+    uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(tmem_empty_bar + kAccStages);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_base_slot + 1);
+    __shared__ int s_tile_start[kMaxGroups + 1];
+
+    const int warp = threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+    const int num_n_blocks = (p.N + BLOCK_N - 1) / BLOCK_N;
+    const int num_k_blocks = (p.K + BLOCK_K - 1) / BLOCK_K;
+    const int G = p.G;
+
+    // ---- prologue: tile table, barriers, TMEM
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        s_tile_start[0] = 0;
+        for (int g = 0; g < G; ++g) {
+            const int64_t len = p.offs_write ? (p.offs_write[g + 1] - p.offs_write[g]) : p.M;
+            acc += (int) ((len + BLOCK_M - 1) / BLOCK_M) * num_n_blocks;
+            s_tile_start[g + 1] = acc;
+        }
+        *abort_flag = 0;
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full_bar[s], MX ? 1 + kNumSfWarps * 32 : 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int s = 0; s < kAccStages; ++s) {
+            mbar_init(&tmem_full_bar[s], 1);
+            mbar_init(&tmem_empty_bar[s], kNumEpiWarps);
+        }
+        fence_barrier_init();
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_base_slot, Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_base_slot;
+    const uint32_t tmem_sfa = tmem_base + kAccStages * BLOCK_N;
+    const uint32_t tmem_sfb = tmem_sfa + 4;
+
+    TileWalk walk{s_tile_start, G, num_n_blocks, 0};
+    int gi, m_blk, n_blk;
+    bool ok = true;
+
+    if (warp == 0) {
+        // ================================================================ TMA producer
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0;
+            for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
+                const int64_t a_row0 = (p.offs_read ? p.offs_read[gi] : 0) + (int64_t) m_blk * BLOCK_M;
+                const int64_t b_row0 = (int64_t) gi * p.b_group_rows + (int64_t) n_blk * BLOCK_N;
+                for (int kb = 0; kb < num_k_blocks; ++kb) {
+                    if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
+                    mbar_arrive_expect_tx(&full_bar[stage], Cfg::kABytes + Cfg::kBBytes);
+                    tma_load_2d(smem_a + stage * Cfg::kABytes, &tmap_a, &full_bar[stage], kb * BLOCK_K, (int) a_row0);
+                    tma_load_2d(smem_b + stage * Cfg::kBBytes, &tmap_b, &full_bar[stage], kb * BLOCK_K, (int) b_row0);
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================================================================ MMA issuer
+        if (elect_one()) {
+            constexpr uint32_t kIdescPlainShape = 0;
+            (void) kIdescPlainShape;
+            const uint32_t idesc = MX ? idesc_block_scaled(p.a_fmt, p.b_fmt, BLOCK_M, BLOCK_N)
+                                      : idesc_f8(p.a_fmt, p.b_fmt, BLOCK_M, BLOCK_N);
+            uint32_t stage = 0, phase = 0, acc_stage = 0, acc_phase = 0;
+            for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
+                if (!(ok = mbar_wait(&tmem_empty_bar[acc_stage], acc_phase ^ 1, abort_flag))) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc_stage * BLOCK_N;
+                for (int kb = 0; kb < num_k_blocks; ++kb) {
+                    if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
+                    tc_fence_after_sync();
+                    if constexpr (MX) {
+                        const uint32_t sf_addr = smem_u32(smem_sf + stage * Cfg::kSfBytes);
+                        tc_cp_sf(tmem_sfa, smem_desc_sf(sf_addr));
+#pragma unroll
+                        for (int j = 0; j < Cfg::kSfbBlocks; ++j) tc_cp_sf(tmem_sfb + 4 * j, smem_desc_sf(sf_addr + 512 * (1 + j)));
+                    }
+                    const uint64_t a_desc = smem_desc_sw128(smem_u32(smem_a + stage * Cfg::kABytes));
+                    const uint64_t b_desc = smem_desc_sw128(smem_u32(smem_b + stage * Cfg::kBBytes));
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        const uint64_t adv = (uint64_t) ((k * UMMA_K) >> 4);
+                        const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+                        if constexpr (MX)
+                            mma_mxf8(d_tmem, a_desc + adv, b_desc + adv, idesc_sf_ids(idesc, k, k), tmem_sfa, tmem_sfb, accumulate);
+                        else
+                            mma_f8(d_tmem, a_desc + adv, b_desc + adv, idesc, accumulate);
+                    }
+                    tc_commit(&empty_bar[stage]);  // frees the ring slot once these MMAs have read it
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                tc_commit(&tmem_full_bar[acc_stage]);
+                if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1; }
+            }
+        }
+    } else if (warp < kEpiWarp0) {
+        // ================================================================ scale-factor loaders (MX only)
+        if constexpr (MX) {
+            const int r = (warp - kSfWarp0) * 32 + lane;  // 0..127: row inside a 128-row block
+            const int slot = (r & 31) * 16 + (r >> 5) * 4;  // byte offset inside the 32 x 16 B block
+            uint32_t stage = 0, phase = 0;
+            for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
+                const int64_t a_row0 = (p.offs_read ? p.offs_read[gi] : 0) + (int64_t) m_blk * BLOCK_M;
+                const int64_t a_rows_end = p.offs_read ? p.offs_read[G] : p.M;
+                const int64_t b_row0 = (int64_t) gi * p.b_group_rows + (int64_t) n_blk * BLOCK_N;
+                const int64_t b_rows_end = (int64_t) G * p.b_group_rows;
+                const bool a_ok = a_row0 + r < a_rows_end;
+                const uint8_t *pa = p.sfa + (a_row0 + r) * p.sf_ld;
+                const uint8_t *pb[Cfg::kSfbBlocks];
+                bool b_ok[Cfg::kSfbBlocks];
+#pragma unroll
+                for (int j = 0; j < Cfg::kSfbBlocks; ++j) {
+                    b_ok[j] = (128 * j + r < BLOCK_N) && (b_row0 + 128 * j + r < b_rows_end);
+                    pb[j] = p.sfb + (b_row0 + 128 * j + r) * p.sf_ld;
+                }
+                // scales of 4 consecutive K blocks are fetched together (one step ahead of their use)
+                for (int kb0 = 0; kb0 < num_k_blocks && ok; kb0 += 4) {
+                    uint32_t wa[4], wb[Cfg::kSfbBlocks][4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const bool in = kb0 + u < num_k_blocks;
+                        wa[u] = (in && a_ok) ? __ldg(reinterpret_cast<const uint32_t *>(pa) + kb0 + u) : 0u;
+#pragma unroll
+                        for (int j = 0; j < Cfg::kSfbBlocks; ++j)
+                            wb[j][u] = (in && b_ok[j]) ? __ldg(reinterpret_cast<const uint32_t *>(pb[j]) + kb0 + u) : 0u;
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (kb0 + u >= num_k_blocks) break;
+                        if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
+                        uint8_t *sf = smem_sf + stage * Cfg::kSfBytes;
+                        *reinterpret_cast<uint32_t *>(sf + slot) = wa[u];
+#pragma unroll
+                        for (int j = 0; j < Cfg::kSfbBlocks; ++j) *reinterpret_cast<uint32_t *>(sf + 512 * (1 + j) + slot) = wb[j][u];
+                        fence_proxy_async_smem();  // generic-proxy stores must be visible to tcgen05.cp
+                        mbar_arrive(&full_bar[stage]);
+                        if (++stage == kStages) { stage = 0; phase ^= 1; }
+                    }
+                }
+            }
+        }
+    } else {
+        // ================================================================ epilogue
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        uint8_t *stg = smem_epi + (warp - kEpiWarp0) * 32 * kStagePitchMax;
+        const int esize = p.c_dtype == PT_F32 ? 4 : 2;
+        const int pitch = 32 * esize + 16;
+        const int lanes_per_row = (32 * esize) / 16;      // 4 (16-bit) or 8 (fp32)
+        const int rows_per_pass = 32 / lanes_per_row;     // 8 or 4
+        uint32_t acc_stage = 0, acc_phase = 0;
+        for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
+            const int64_t c_row_base = (p.offs_write ? p.offs_write[gi] : 0);
+            const int64_t c_row_end = p.offs_write ? p.offs_write[gi + 1] : p.M;
+            const int64_t tile_row0 = c_row_base + (int64_t) m_blk * BLOCK_M + q * 32;
+            const int n0 = n_blk * BLOCK_N;
+            if (!(ok = mbar_wait(&tmem_full_bar[acc_stage], acc_phase, abort_flag))) break;
+            tc_fence_after_sync();
+            const uint32_t taddr = tmem_base + ((uint32_t) (q * 32) << 16) + acc_stage * BLOCK_N;
+            float row_scale = 1.f;
+            if (MODE == GEMM_TENSOR) row_scale = __ldg(p.sa) * __ldg(p.sb);
+            if (MODE == GEMM_ROW) row_scale = (tile_row0 + lane < c_row_end) ? __ldg(p.sa + tile_row0 + lane) : 0.f;
+#pragma unroll 1
+            constexpr int kChunks = (BLOCK_N + 31) / 32;  // a last partial chunk reads past the tile; masked below
+            const int n_end = min(p.N, n0 + BLOCK_N);
+            for (int c = 0; c < kChunks; ++c) {
+                uint32_t r[32];
+                tmem_ld32(taddr + c * 32, r);
+                tmem_ld_wait();
+                if (c == kChunks - 1) {
+                    // whole accumulator is in registers / staged: hand the TMEM buffer back to the MMA warp
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&tmem_empty_bar[acc_stage]);
+                }
+                const int col0 = n0 + c * 32;
+                float f[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]) * row_scale;
+                if (MODE == GEMM_ROW) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) f[i] *= (col0 + i < n_end) ? __ldg(p.sb + (int64_t) gi * p.b_group_rows + col0 + i) : 0.f;
+                }
+                // stage this thread's row
+                uint8_t *my = stg + lane * pitch;
+                if (esize == 4) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        *reinterpret_cast<float4 *>(my + 16 * i) = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+                } else if (p.c_dtype == PT_BF16) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        *reinterpret_cast<uint4 *>(my + 16 * i) =
+                            make_uint4(pack2<__nv_bfloat16>(f[8 * i], f[8 * i + 1]), pack2<__nv_bfloat16>(f[8 * i + 2], f[8 * i + 3]),
+                                       pack2<__nv_bfloat16>(f[8 * i + 4], f[8 * i + 5]), pack2<__nv_bfloat16>(f[8 * i + 6], f[8 * i + 7]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        *reinterpret_cast<uint4 *>(my + 16 * i) =
+                            make_uint4(pack2<__half>(f[8 * i], f[8 * i + 1]), pack2<__half>(f[8 * i + 2], f[8 * i + 3]),
+                                       pack2<__half>(f[8 * i + 4], f[8 * i + 5]), pack2<__half>(f[8 * i + 6], f[8 * i + 7]));
+                }
+                __syncwarp();
+                // coalesced write-out: lanes_per_row lanes cover one staged row
+                const int sub = lane % lanes_per_row;
+                const int elems16 = 16 / esize;
+#pragma unroll 1
+                for (int pass = 0; pass < 32; pass += rows_per_pass) {
+                    const int rr = pass + lane / lanes_per_row;
+                    const int64_t grow = tile_row0 + rr;
+                    const int gcol = col0 + sub * elems16;
+                    if (grow < c_row_end && gcol < n_end) {
+                        const uint4 val = *reinterpret_cast<const uint4 *>(stg + rr * pitch + sub * 16);
+                        uint8_t *dst = reinterpret_cast<uint8_t *>(p.C) + (grow * p.ldc + gcol) * esize;
+                        if (p.vec_store_ok && gcol + elems16 <= n_end && p.beta == 0.f) {
+                            *reinterpret_cast<uint4 *>(dst) = val;
+                        } else {
+                            const uint8_t *src = reinterpret_cast<const uint8_t *>(&val);
+                            for (int e = 0; e < elems16 && gcol + e < n_end; ++e) {
+                                if (esize == 4) {
+                                    float nv = reinterpret_cast<const float *>(src)[e];
+                                    if (p.beta != 0.f) nv += reinterpret_cast<float *>(dst)[e];
+                                    reinterpret_cast<float *>(dst)[e] = nv;
+                                } else if (p.c_dtype == PT_BF16) {
+                                    __nv_bfloat16 nv = reinterpret_cast<const __nv_bfloat16 *>(src)[e];
+                                    if (p.beta != 0.f) nv = __float2bfloat16_rn(__bfloat162float(nv) + __bfloat162float(reinterpret_cast<__nv_bfloat16 *>(dst)[e]));
+                                    reinterpret_cast<__nv_bfloat16 *>(dst)[e] = nv;
+                                } else {
+                                    __half nv = reinterpret_cast<const __half *>(src)[e];
+                                    if (p.beta != 0.f) nv = __float2half_rn(__half2float(nv) + __half2float(reinterpret_cast<__half *>(dst)[e]));
+                                    reinterpret_cast<__half *>(dst)[e] = nv;
+                                }
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+            if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1; }
+        }
+    }
+
+    // ---- teardown
+    if (!ok || *abort_flag) {
+        if (p.status && lane == 0) atomicExch(p.status, (int) PT_ERR_TIMEOUT);
+        __nanosleep(200000);  // let any TMA copy still in flight land before the shared memory is released
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// 2-D byte tensor [rows, row_bytes] (pitch `pitch_bytes`), box = 128 bytes x box_rows, 128-byte swizzle.
+static int make_tmap_bytes(CUtensorMap *m, const void *base, int64_t rows, int64_t row_bytes, int64_t pitch_bytes, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return set_error(PT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    PT_REQUIRE(aligned(base, 16) && pitch_bytes % 16 == 0, "GEMM operand base / row pitch must be 16-byte aligned");
+    cuuint64_t dims[2] = {(cuuint64_t) row_bytes, (cuuint64_t) rows};
+    cuuint64_t strides[1] = {(cuuint64_t) pitch_bytes};
+    cuuint32_t box[2] = {128u, (cuuint32_t) box_rows};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(PT_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int) r);
+    return PT_OK;
+}
+
+template <int BLOCK_N, int MODE>
+static int launch_gemm(const void *a, int64_t a_rows, const void *b, int64_t b_rows, const GemmParams &p, int max_ctas,
+                       int64_t max_tiles, cudaStream_t st) {
+    using Cfg = GemmCfg<BLOCK_N, MODE == GEMM_MX>;
+    CUtensorMap ta, tb;
+    int rc;
+    if ((rc = make_tmap_bytes(&ta, a, a_rows, p.K, p.K, BLOCK_M)) != PT_OK) return rc;
+    if ((rc = make_tmap_bytes(&tb, b, b_rows, p.K, p.K, BLOCK_N)) != PT_OK) return rc;
+    auto kern = gemm_fp8_kernel<BLOCK_N, MODE>;
+    static bool attr_set = false;  // per instantiation
+    if (!attr_set) {
+        PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        attr_set = true;
+    }
+    int grid = (int) std::min<int64_t>(max_tiles, sm_count());
+    if (max_ctas > 0) grid = std::min(grid, max_ctas);
+    if (grid <= 0) return PT_OK;
+    kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ta, tb, p);
+    PT_LAUNCH_OK();
+    return PT_OK;
+}
+
+template <int MODE>
+static int dispatch_block_n(int block_n, const void *a, int64_t a_rows, const void *b, int64_t b_rows, const GemmParams &p,
+                            int max_ctas, cudaStream_t st) {
+    // upper bound on tiles: every group may add one partial row block
+    const int64_t m_blocks_bound = ceil_div(p.M, BLOCK_M) + (p.offs_write ? p.G : 0);
+    if (block_n == 0) block_n = p.N <= 128 ? 128 : (MODE == GEMM_MX ? 240 : 256);
+    const int64_t tiles = m_blocks_bound * ceil_div(p.N, block_n);
+    switch (block_n) {
+    case 128: return launch_gemm<128, MODE>(a, a_rows, b, b_rows, p, max_ctas, tiles, st);
+    case 240: return launch_gemm<240, MODE>(a, a_rows, b, b_rows, p, max_ctas, tiles, st);
+    case 256: return launch_gemm<256, MODE>(a, a_rows, b, b_rows, p, max_ctas, tiles, st);
+    default: return set_error(PT_ERR_INVALID, "GEMM: BLOCK_N %d is not built (128, 240, 256)", block_n);
+    }
+}
+
+int gemm_fp8_host(const void *a, const void *a_scale, int a_fmt, const void *b, const void *b_scale, int b_fmt, void *c,
+                  int c_dtype, int64_t ldc, int granularity, int64_t M, int64_t N, int64_t K, float beta,
+                  const int64_t *offs_read, const int64_t *offs_write, int G, int64_t a_rows_total, int block_n,
+                  int max_ctas, int *status, void *stream) {
+    PT_REQUIRE(M >= 0 && N >= 0 && K >= 0 && G >= 1 && G <= kMaxGroups, "GEMM: bad shape (M=%lld N=%lld K=%lld G=%d)",
+               (long long) M, (long long) N, (long long) K, G);
+    PT_REQUIRE(a_fmt == PT_E4M3 || a_fmt == PT_E5M2, "GEMM: A format must be e4m3 or e5m2");
+    PT_REQUIRE(b_fmt == PT_E4M3 || b_fmt == PT_E5M2, "GEMM: B format must be e4m3 or e5m2");
+    PT_REQUIRE(c_dtype == PT_BF16 || c_dtype == PT_F16 || c_dtype == PT_F32, "GEMM: bad output dtype");
+    PT_REQUIRE(beta == 0.f || beta == 1.f, "GEMM: beta must be 0 or 1");
+    PT_REQUIRE((offs_read == nullptr) == (offs_write == nullptr) || offs_write, "GEMM: write offsets required with read offsets");
+    if (M == 0 || N == 0) return PT_OK;
+    PT_REQUIRE(K > 0 && K % 16 == 0, "GEMM: K must be a positive multiple of 16 (got %lld)", (long long) K);
+    PT_REQUIRE(a && b && c && a_scale && b_scale, "GEMM: null pointer");
+    PT_REQUIRE(N < (1 << 30) && K < (1 << 30) && a_rows_total < (1ll << 31) && (int64_t) G * N < (1ll << 31),
+               "GEMM: extent exceeds 32-bit tile coordinates");
+    GemmParams p{};
+    p.M = M; p.N = (int) N; p.K = (int) K; p.C = c; p.ldc = ldc; p.c_dtype = c_dtype; p.beta = beta;
+    const int esize = c_dtype == PT_F32 ? 4 : 2;
+    p.vec_store_ok = aligned(c, 16) && (ldc * esize) % 16 == 0;
+    p.a_fmt = a_fmt; p.b_fmt = b_fmt;
+    p.offs_read = offs_read ? offs_read : offs_write; p.offs_write = offs_write; p.G = G; p.b_group_rows = N;
+    p.status = status;
+    cudaStream_t st = (cudaStream_t) stream;
+    const int64_t b_rows = (int64_t) G * N;
+    switch (granularity) {
+    case PT_TENSORWISE:
+        p.sa = (const float *) a_scale; p.sb = (const float *) b_scale;
+        return dispatch_block_n<GEMM_TENSOR>(block_n, a, a_rows_total, b, b_rows, p, max_ctas, st);
+    case PT_ROWWISE:
+        p.sa = (const float *) a_scale; p.sb = (const float *) b_scale;
+        return dispatch_block_n<GEMM_ROW>(block_n, a, a_rows_total, b, b_rows, p, max_ctas, st);
+    case PT_MX_BLOCKWISE:
+        PT_REQUIRE(K % 128 == 0, "MX GEMM: K must be padded to a multiple of 128 (got %lld)", (long long) K);
+        p.sfa = (const uint8_t *) a_scale; p.sfb = (const uint8_t *) b_scale; p.sf_ld = K / 32;
+        PT_REQUIRE(aligned(a_scale, 4) && aligned(b_scale, 4), "MX GEMM: scale pointers must be 4-byte aligned");
+        return dispatch_block_n<GEMM_MX>(block_n, a, a_rows_total, b, b_rows, p, max_ctas, st);
+    default:
+        return set_error(PT_ERR_UNSUPPORTED, "GEMM: granularity %d is not handled by this kernel", granularity);
+    }
+}
+
+}  // namespace ptb
+
+using namespace ptb;
+
+extern "C" {
+
+int pt_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const void *b, const void *b_scale, int b_fmt, void *c,
+                int c_dtype, int granularity, int64_t M, int64_t N, int64_t K, float beta, int block_n, int *status,
+                void *stream) {
+    return gemm_fp8_host(a, a_scale, a_fmt, b, b_scale, b_fmt, c, c_dtype, N, granularity, M, N, K, beta, nullptr, nullptr,
+                         1, M, block_n, 0, status, stream);
+}
+
+int pt_grouped_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const void *b, const void *b_scale, int b_fmt,
+                        void *c, int c_dtype, int granularity, int64_t a_rows, int64_t c_rows, int64_t N, int64_t K,
+                        const int64_t *group_offs_read, const int64_t *group_offs_write, int G, float beta, int block_n,
+                        int max_ctas, int *status, void *stream) {
+    PT_REQUIRE(group_offs_write, "grouped GEMM: group offsets required");
+    return gemm_fp8_host(a, a_scale, a_fmt, b, b_scale, b_fmt, c, c_dtype, N, granularity, c_rows, N, K, beta,
+                         group_offs_read, group_offs_write, G, a_rows, block_n, max_ctas, status, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,371 @@
+// 128-blockwise FP8 quantization: one CTA per 128 x 128 tile, the tile held in registers so that the
+// row-wise (1 x 128), column-wise (128 x 1), dual, per-tile (weight) and grouped segment-M variants all
+// read their input exactly once.
+//
+// Arithmetic follows primus_turbo/triton/quantization/quant_blockwise.py:11-18 and
+// csrc/kernels/quantization/quantization_blockwise.cu:60-334 of the reference:
+//   scale = qmax / fmaxf(amax, 1e-4f); q = fp8_rne(clamp(x * scale, +-qmax)); stored scale = 1.0f / scale.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace ptb {
+
+constexpr int kBlk = 128;
+constexpr int kTileThreads = 256;
+constexpr int kPack = 8;
+constexpr int kLanesPerRow = kBlk / kPack;             // 16
+constexpr int kRowsPerRound = kTileThreads / kLanesPerRow;  // 16
+constexpr int kRounds = kBlk / kRowsPerRound;          // 8
+constexpr float kEpsBlock = 1e-4f;
+
+enum TileMode { MODE_ROW = 1, MODE_COL = 2, MODE_DUAL = 3, MODE_WEIGHT = 4, MODE_SEGMENT = 7 };
+
+template <typename T>
+__device__ __forceinline__ void load_row8(const T *row_ptr, int64_t gn, int64_t N, bool valid, bool vec_ok,
+                                          float (&v)[kPack]) {
+    if (valid && vec_ok && gn + kPack <= N) {
+        load8(row_ptr + gn, v);
+    } else {
+#pragma unroll
+        for (int i = 0; i < kPack; ++i) v[i] = (valid && gn + i < N) ? load1(row_ptr + gn + i) : 0.f;
+    }
+}
+
+template <int FMT>
+__device__ __forceinline__ void store_row8(uint8_t *row_ptr, int64_t gn, int64_t N, bool vec_ok, const float (&v)[kPack]) {
+    if (vec_ok && gn + kPack <= N) {
+        uint2 o;
+        o.x = cvt4_fp8<FMT>(v[0], v[1], v[2], v[3]);
+        o.y = cvt4_fp8<FMT>(v[4], v[5], v[6], v[7]);
+        *reinterpret_cast<uint2 *>(row_ptr + gn) = o;
+    } else {
+#pragma unroll
+        for (int i = 0; i < kPack; ++i)
+            if (gn + i < N) row_ptr[gn + i] = cvt1_fp8<FMT>(v[i]);
+    }
+}
+
+struct SegmentArgs {
+    const int64_t *group_offs;
+    const int64_t *padded_offs;
+    int num_groups;
+};
+
+// grid: (N tiles, M tiles, batch). For MODE_SEGMENT the M tiles run over the padded row space.
+template <typename T, int FMT, int MODE>
+__global__ void __launch_bounds__(kTileThreads)
+    blockwise_tile_kernel(const T *__restrict__ x, int64_t M, int64_t N, int vec_ok, uint8_t *__restrict__ q_row,
+                          float *__restrict__ s_row, uint8_t *__restrict__ q_col, float *__restrict__ s_col,
+                          SegmentArgs seg) {
+    constexpr bool kRow = (MODE & 1) != 0 && MODE != MODE_WEIGHT;
+    constexpr bool kCol = (MODE & 2) != 0 && MODE != MODE_WEIGHT;
+    constexpr bool kSeg = MODE == MODE_SEGMENT;
+    constexpr bool kWeight = MODE == MODE_WEIGHT;
+
+    const int tid = threadIdx.x;
+    const int lane16 = tid % kLanesPerRow;
+    const int row_base = tid / kLanesPerRow;
+    const int64_t col_blk = blockIdx.x;
+    const int64_t pid_m = blockIdx.y;
+    const int64_t batch = blockIdx.z;
+    const int64_t n_blocks = (N + kBlk - 1) / kBlk;
+    const int64_t m_blocks = (M + kBlk - 1) / kBlk;
+    const int64_t gn = col_blk * kBlk + lane16 * kPack;
+
+    x += batch * M * N;
+
+    // row mapping: plain tiles start at pid_m * 128; segment tiles live in padded row space
+    int64_t in_row0 = pid_m * kBlk, in_lo = 0, in_hi = M, out_row0 = pid_m * kBlk;
+    if constexpr (kSeg) {
+        const int64_t m_padded = seg.padded_offs[seg.num_groups];
+        if (out_row0 >= m_padded) return;
+        int lo = 0, hi = seg.num_groups - 1;  // last group g with padded_offs[g] <= out_row0 (empty groups skipped)
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (seg.padded_offs[mid] <= out_row0) lo = mid; else hi = mid - 1;
+        }
+        in_lo = seg.group_offs[lo];
+        in_hi = min(seg.group_offs[lo + 1], M);
+        in_row0 = in_lo + (out_row0 - seg.padded_offs[lo]);
+    }
+
+    __shared__ float s_part[kRowsPerRound][kBlk];
+    __shared__ float s_scale[kBlk];
+
+    float vals[kRounds][kPack];
+    float col_amax[kPack];
+#pragma unroll
+    for (int i = 0; i < kPack; ++i) col_amax[i] = 0.f;
+    float tile_amax = 0.f;
+
+#pragma unroll
+    for (int r = 0; r < kRounds; ++r) {
+        const int local_m = row_base + r * kRowsPerRound;
+        const int64_t in_m = in_row0 + local_m;
+        const bool valid = in_m >= in_lo && in_m < in_hi;
+        load_row8(x + in_m * N, gn, N, valid, vec_ok != 0, vals[r]);
+        float row_amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < kPack; ++i) {
+            const float av = fabsf(vals[r][i]);
+            row_amax = fmaxf(row_amax, av);
+            col_amax[i] = fmaxf(col_amax[i], av);
+        }
+        if constexpr (kWeight) tile_amax = fmaxf(tile_amax, row_amax);
+        if constexpr (kRow) {
+#pragma unroll
+            for (int off = kLanesPerRow >> 1; off > 0; off >>= 1)
+                row_amax = fmaxf(row_amax, __shfl_xor_sync(0xffffffffu, row_amax, off, kLanesPerRow));
+            const float scale = scale_from_amax<FMT>(row_amax, kEpsBlock);
+            if (valid) {
+                float o[kPack];
+#pragma unroll
+                for (int i = 0; i < kPack; ++i) o[i] = scale_clamp<FMT>(vals[r][i], scale);
+                store_row8<FMT>(q_row + (batch * M + in_m) * N, gn, N, vec_ok != 0, o);
+                if (lane16 == 0) {
+                    const float inv = __fdiv_rn(1.0f, scale);
+                    if constexpr (kSeg) s_row[col_blk * M + in_m] = inv;  // transposed [N blocks, M]
+                    else s_row[(batch * M + in_m) * n_blocks + col_blk] = inv;
+                }
+            }
+        }
+    }
+
+    if constexpr (kWeight) {
+        tile_amax = warp_max(tile_amax);
+        if ((tid & 31) == 0) s_part[0][tid >> 5] = tile_amax;
+        __syncthreads();
+        float m = 0.f;
+#pragma unroll
+        for (int w = 0; w < kTileThreads / 32; ++w) m = fmaxf(m, s_part[0][w]);
+        const float scale = scale_from_amax<FMT>(m, kEpsBlock);
+        if (tid == 0) s_row[(batch * m_blocks + pid_m) * n_blocks + col_blk] = __fdiv_rn(1.0f, scale);
+#pragma unroll
+        for (int r = 0; r < kRounds; ++r) {
+            const int64_t in_m = in_row0 + row_base + r * kRowsPerRound;
+            if (in_m < M) {
+                float o[kPack];
+#pragma unroll
+                for (int i = 0; i < kPack; ++i) o[i] = scale_clamp<FMT>(vals[r][i], scale);
+                store_row8<FMT>(q_row + (batch * M + in_m) * N, gn, N, vec_ok != 0, o);
+            }
+        }
+    }
+
+    if constexpr (kCol) {
+#pragma unroll
+        for (int i = 0; i < kPack; ++i) s_part[row_base][lane16 * kPack + i] = col_amax[i];
+        __syncthreads();
+        if (tid < kBlk) {
+            float m = 0.f;
+#pragma unroll
+            for (int rs = 0; rs < kRowsPerRound; ++rs) m = fmaxf(m, s_part[rs][tid]);
+            const float scale = scale_from_amax<FMT>(m, kEpsBlock);
+            s_scale[tid] = scale;
+            const int64_t c = col_blk * kBlk + tid;
+            if (c < N) s_col[(batch * (kSeg ? 0 : m_blocks) + pid_m) * N + c] = __fdiv_rn(1.0f, scale);
+        }
+        __syncthreads();
+        float sc[kPack];
+#pragma unroll
+        for (int i = 0; i < kPack; ++i) sc[i] = s_scale[lane16 * kPack + i];
+        const int64_t out_rows = kSeg ? seg.padded_offs[seg.num_groups] : M;
+#pragma unroll
+        for (int r = 0; r < kRounds; ++r) {
+            const int64_t out_m = out_row0 + row_base + r * kRowsPerRound;
+            if (out_m < out_rows) {
+                float o[kPack];
+#pragma unroll
+                for (int i = 0; i < kPack; ++i) o[i] = scale_clamp<FMT>(vals[r][i], sc[i]);  // invalid rows hold 0
+                store_row8<FMT>(q_col + (batch * (kSeg ? 0 : M) + out_m) * N, gn, N, vec_ok != 0, o);
+            }
+        }
+    }
+}
+
+// y = float(q) * s for the three block-scale layouts
+template <typename T, int FMT>
+__global__ void __launch_bounds__(256) dequant_blockwise_kernel(const uint8_t *__restrict__ q,
+                                                               const float *__restrict__ s, int kind, int64_t M,
+                                                               int64_t N, int64_t total, T *__restrict__ y);
+
+template <int FMT> __device__ __forceinline__ float decode8(uint8_t c) {
+    if constexpr (FMT == PT_E5M2) return __half2float(__ushort_as_half((uint16_t) c << 8));
+    // e4m3fn -> float: sign | exp(4) | man(3), bias 7
+    const uint32_t sign = (uint32_t) (c & 0x80) << 24;
+    const uint32_t e = (c >> 3) & 0xF, m = c & 7;
+    if (e == 0) return __uint_as_float(sign | __float_as_uint((float) m * 0.001953125f));  // m * 2^-9
+    if (e == 15 && m == 7) return __uint_as_float(sign | 0x7FC00000u);
+    return __uint_as_float(sign | ((e + 120) << 23) | (m << 20));
+}
+template <typename T> __device__ __forceinline__ void put(T *p, float v);
+template <> __device__ __forceinline__ void put<float>(float *p, float v) { *p = v; }
+template <> __device__ __forceinline__ void put<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ void put<__half>(__half *p, float v) { *p = __float2half_rn(v); }
+
+template <typename T, int FMT>
+__global__ void __launch_bounds__(256) dequant_blockwise_kernel(const uint8_t *__restrict__ q,
+                                                               const float *__restrict__ s, int kind, int64_t M,
+                                                               int64_t N, int64_t total, T *__restrict__ y) {
+    const int64_t nb = (N + kBlk - 1) / kBlk, mb = (M + kBlk - 1) / kBlk;
+    const int64_t stride = (int64_t) gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t b = i / (M * N), rem = i % (M * N), m = rem / N, n = rem % N;
+        int64_t si;
+        if (kind == 0) si = (b * M + m) * nb + n / kBlk;
+        else if (kind == 1) si = (b * mb + m / kBlk) * N + n;
+        else si = (b * mb + m / kBlk) * nb + n / kBlk;
+        put(y + i, decode8<FMT>(q[i]) * __ldg(s + si));
+    }
+}
+
+// offs[i+1] = sum_{j<=i} ceil_to(lens[j], align); one block, G <= 4096
+__global__ void __launch_bounds__(1024) group_offs_kernel(const int64_t *__restrict__ lens, int G, int64_t align,
+                                                          int64_t *__restrict__ plens, int64_t *__restrict__ offs) {
+    __shared__ int64_t s[1024];
+    __shared__ int64_t carry;
+    if (threadIdx.x == 0) { carry = 0; offs[0] = 0; }
+    __syncthreads();
+    for (int base = 0; base < G; base += 1024) {
+        const int i = base + threadIdx.x;
+        int64_t v = 0;
+        if (i < G) {
+            v = lens[i];
+            if (align > 1) v = (v + align - 1) / align * align;
+            if (plens) plens[i] = v;
+        }
+        s[threadIdx.x] = v;
+        __syncthreads();
+        for (int d = 1; d < 1024; d <<= 1) {
+            const int64_t t = threadIdx.x >= d ? s[threadIdx.x - d] : 0;
+            __syncthreads();
+            s[threadIdx.x] += t;
+            __syncthreads();
+        }
+        if (i < G) offs[i + 1] = carry + s[threadIdx.x];
+        __syncthreads();
+        if (threadIdx.x == 1023) carry += s[1023];
+        __syncthreads();
+    }
+}
+
+// tiled transpose of 1/2/4-byte elements
+template <typename E>
+__global__ void __launch_bounds__(256) transpose_kernel(const E *__restrict__ x, int64_t M, int64_t N, E *__restrict__ y) {
+    __shared__ E tile[64][64 + (sizeof(E) == 1 ? 4 : (sizeof(E) == 2 ? 2 : 1))];
+    const int64_t m0 = (int64_t) blockIdx.y * 64, n0 = (int64_t) blockIdx.x * 64;
+    const int tx = threadIdx.x % 64, ty = threadIdx.x / 64;
+    for (int r = ty; r < 64; r += 4)
+        if (m0 + r < M && n0 + tx < N) tile[r][tx] = x[(m0 + r) * N + n0 + tx];
+    __syncthreads();
+    for (int r = ty; r < 64; r += 4)
+        if (n0 + r < N && m0 + tx < M) y[(n0 + r) * M + m0 + tx] = tile[tx][r];
+}
+
+}  // namespace ptb
+
+using namespace ptb;
+
+template <int MODE>
+static int launch_tile(const void *x, int x_dtype, int64_t B, int64_t m_tiles, int64_t M, int64_t N, int fmt,
+                       void *q_row, float *s_row, void *q_col, float *s_col, SegmentArgs seg, void *stream) {
+    PT_REQUIRE(B <= 65535 && m_tiles <= 65535, "blockwise: too many tiles along M or batch");
+    dim3 grid((unsigned) ceil_div(N, kBlk), (unsigned) m_tiles, (unsigned) B);
+    PT_SWITCH_SRC(x_dtype, T, {
+        const int vec_ok = aligned(x, 16) && (N % 8 == 0) && (!q_row || aligned(q_row, 8)) && (!q_col || aligned(q_col, 8));
+        PT_SWITCH_FP8(fmt, F, {
+            blockwise_tile_kernel<T, F, MODE><<<grid, kTileThreads, 0, (cudaStream_t) stream>>>(
+                (const T *) x, M, N, vec_ok, (uint8_t *) q_row, s_row, (uint8_t *) q_col, s_col, seg);
+        });
+        PT_LAUNCH_OK();
+    });
+    return PT_OK;
+}
+
+extern "C" {
+
+int pt_quantize_fp8_blockwise(const void *x, int x_dtype, int64_t M, int64_t N, int fmt, void *q_row, float *s_row,
+                              void *q_col, float *s_col, void *stream) {
+    PT_REQUIRE(M >= 0 && N >= 0, "blockwise: negative shape");
+    const bool row = q_row != nullptr, col = q_col != nullptr;
+    PT_REQUIRE(row || col, "blockwise: no output requested");
+    PT_REQUIRE((!row || s_row) && (!col || s_col), "blockwise: missing scale output");
+    if (M * N == 0) return PT_OK;
+    PT_REQUIRE(x, "blockwise: null input");
+    SegmentArgs seg{nullptr, nullptr, 0};
+    const int64_t mt = ceil_div(M, kBlk);
+    if (row && col) return launch_tile<MODE_DUAL>(x, x_dtype, 1, mt, M, N, fmt, q_row, s_row, q_col, s_col, seg, stream);
+    if (row) return launch_tile<MODE_ROW>(x, x_dtype, 1, mt, M, N, fmt, q_row, s_row, nullptr, nullptr, seg, stream);
+    return launch_tile<MODE_COL>(x, x_dtype, 1, mt, M, N, fmt, nullptr, nullptr, q_col, s_col, seg, stream);
+}
+
+int pt_quantize_fp8_blockwise_weight(const void *w, int x_dtype, int64_t B, int64_t M, int64_t N, int fmt, void *q,
+                                     float *s, void *stream) {
+    PT_REQUIRE(B >= 0 && M >= 0 && N >= 0, "blockwise weight: negative shape");
+    if (B * M * N == 0) return PT_OK;
+    PT_REQUIRE(w && q && s, "blockwise weight: null pointer");
+    SegmentArgs seg{nullptr, nullptr, 0};
+    return launch_tile<MODE_WEIGHT>(w, x_dtype, B, ceil_div(M, kBlk), M, N, fmt, q, s, nullptr, nullptr, seg, stream);
+}
+
+int pt_quantize_fp8_blockwise_segment_m(const void *x, int x_dtype, int64_t M, int64_t N, int G,
+                                        const int64_t *group_offs, const int64_t *padded_offs, int fmt, void *q_row,
+                                        float *s_row, void *q_col, float *s_col, void *stream) {
+    PT_REQUIRE(M >= 0 && N >= 0 && G >= 1, "segment-M: bad shape");
+    PT_REQUIRE(group_offs && padded_offs && q_row && s_row && q_col && s_col, "segment-M: null pointer");
+    if (N == 0) return PT_OK;
+    SegmentArgs seg{group_offs, padded_offs, G};
+    const int64_t m_alloc = M + (int64_t) G * kBlk;
+    return launch_tile<MODE_SEGMENT>(x, x_dtype, 1, ceil_div(m_alloc, kBlk), M, N, fmt, q_row, s_row, q_col, s_col, seg,
+                                     stream);
+}
+
+int pt_dequantize_fp8_blockwise(const void *q, int fmt, const float *s, int kind, int64_t B, int64_t M, int64_t N,
+                                void *y, int y_dtype, void *stream) {
+    const int64_t total = B * M * N;
+    PT_REQUIRE(total >= 0 && kind >= 0 && kind <= 2, "blockwise dequantize: bad arguments");
+    if (total == 0) return PT_OK;
+    PT_REQUIRE(q && s && y, "blockwise dequantize: null pointer");
+    const int blocks = (int) std::min<int64_t>(ceil_div(total, 256), (int64_t) sm_count() * 16);
+    PT_SWITCH_SRC(y_dtype, T, {
+        PT_SWITCH_FP8(fmt, F, {
+            dequant_blockwise_kernel<T, F><<<blocks, 256, 0, (cudaStream_t) stream>>>((const uint8_t *) q, s, kind, M, N,
+                                                                                      total, (T *) y);
+        });
+        PT_LAUNCH_OK();
+    });
+    return PT_OK;
+}
+
+int pt_compute_group_offs(const int64_t *lens, int G, int64_t *offs, void *stream) {
+    PT_REQUIRE(lens && offs && G >= 0 && G <= 4096, "group offsets: bad arguments");
+    group_offs_kernel<<<1, 1024, 0, (cudaStream_t) stream>>>(lens, G, 1, nullptr, offs);
+    PT_LAUNCH_OK();
+    return PT_OK;
+}
+
+int pt_compute_padded_group_offs(const int64_t *lens, int G, int64_t align, int64_t *plens, int64_t *poffs,
+                                 void *stream) {
+    PT_REQUIRE(lens && poffs && G >= 0 && G <= 4096 && align >= 1, "padded group offsets: bad arguments");
+    group_offs_kernel<<<1, 1024, 0, (cudaStream_t) stream>>>(lens, G, align, plens, poffs);
+    PT_LAUNCH_OK();
+    return PT_OK;
+}
+
+int pt_transpose_2d(const void *x, int64_t M, int64_t N, int elem_bytes, void *y, void *stream) {
+    PT_REQUIRE(M >= 0 && N >= 0, "transpose: negative shape");
+    if (M * N == 0) return PT_OK;
+    PT_REQUIRE(x && y, "transpose: null pointer");
+    PT_REQUIRE(ceil_div(M, 64) <= 65535, "transpose: M too large");
+    dim3 grid((unsigned) ceil_div(N, 64), (unsigned) ceil_div(M, 64));
+    cudaStream_t st = (cudaStream_t) stream;
+    if (elem_bytes == 1) transpose_kernel<uint8_t><<<grid, 256, 0, st>>>((const uint8_t *) x, M, N, (uint8_t *) y);
+    else if (elem_bytes == 2) transpose_kernel<uint16_t><<<grid, 256, 0, st>>>((const uint16_t *) x, M, N, (uint16_t *) y);
+    else if (elem_bytes == 4) transpose_kernel<uint32_t><<<grid, 256, 0, st>>>((const uint32_t *) x, M, N, (uint32_t *) y);
+    else return set_error(PT_ERR_INVALID, "transpose: element size %d not supported", elem_bytes);
+    PT_LAUNCH_OK();
+    return PT_OK;
+}
+
+}  // extern "C"

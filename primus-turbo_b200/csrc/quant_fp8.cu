@@ -1,0 +1,363 @@
+// Tensorwise and rowwise FP8 quantize / dequantize: HBM-bound streaming kernels.
+//
+// Arithmetic follows csrc/include/primus_turbo/device/quant_utils.cuh:33-74 of the reference:
+//   scale = qmax / fmax(amax, 1e-12f), scale_inv = 1.0f / scale,
+//   q = fp8_rne(fmax(fmin(float(x) * scale, qmax), -qmax)).
+#include <cuda_fp8.h>
+#include <stdarg.h>
+#include <algorithm>
+#include <stdio.h>
+
+#include "common.cuh"
+
+namespace ptb {
+
+// ------------------------------------------------------------------------------------------------
+// error plumbing
+static thread_local char g_err[512] = "";
+int set_error(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+constexpr int kThreads = 256;
+constexpr float kEpsTensor = 1e-12f;
+
+// ------------------------------------------------------------------------------------------------
+// amax over a flat array: 8-element vectors, 4 in flight per thread, one atomicMax per block.
+// Non-negative floats order like their bit patterns, so the running maximum is kept as uint32.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) amax_flat_kernel(const T *__restrict__ x, int64_t n, int vec_ok,
+                                                             unsigned *__restrict__ amax_bits) {
+    float m = 0.f;
+    const int64_t tid = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t nthreads = (int64_t) gridDim.x * blockDim.x;
+    int64_t done = 0;
+    if (vec_ok) {
+        const int64_t nvec = n / 8;
+        int64_t i = tid;
+        for (; i + 3 * nthreads < nvec; i += 4 * nthreads) {
+            float v[4][8];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) load8(x + (i + u * nthreads) * 8, v[u]);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int k = 0; k < 8; ++k) m = fmaxf(m, fabsf(v[u][k]));
+        }
+        for (; i < nvec; i += nthreads) {
+            float v[8];
+            load8(x + i * 8, v);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) m = fmaxf(m, fabsf(v[k]));
+        }
+        done = nvec * 8;
+    }
+    for (int64_t i = done + tid; i < n; i += nthreads) m = fmaxf(m, fabsf(load1(x + i)));
+
+    m = warp_max(m);
+    __shared__ float s[kThreads / 32];
+    if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float w = threadIdx.x < kThreads / 32 ? s[threadIdx.x] : 0.f;
+        w = warp_max(w);
+        if (threadIdx.x == 0) atomicMax(amax_bits, __float_as_uint(w));
+    }
+}
+
+// Flat cast with one scale read from device memory. 16 elements per thread per step.
+template <typename T, int FMT>
+__global__ void __launch_bounds__(kThreads)
+    cast_flat_kernel(const T *__restrict__ x, int64_t n, int vec_ok, const unsigned *__restrict__ amax_bits,
+                     const float *__restrict__ scale_opt, uint8_t *__restrict__ q, float *__restrict__ scale_inv) {
+    float scale;
+    if (scale_opt != nullptr) scale = __ldg(scale_opt);
+    else scale = scale_from_amax<FMT>(__uint_as_float(*amax_bits), kEpsTensor);
+    const int64_t tid = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t nthreads = (int64_t) gridDim.x * blockDim.x;
+    if (tid == 0) *scale_inv = __fdiv_rn(1.0f, scale);
+    int64_t done = 0;
+    if (vec_ok) {
+        const int64_t nvec = n / 16;
+        for (int64_t i = tid; i < nvec; i += nthreads) {
+            float a[8], b[8];
+            load8(x + i * 16, a);
+            load8(x + i * 16 + 8, b);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                a[k] = scale_clamp<FMT>(a[k], scale);
+                b[k] = scale_clamp<FMT>(b[k], scale);
+            }
+            uint4 o;
+            o.x = cvt4_fp8<FMT>(a[0], a[1], a[2], a[3]);
+            o.y = cvt4_fp8<FMT>(a[4], a[5], a[6], a[7]);
+            o.z = cvt4_fp8<FMT>(b[0], b[1], b[2], b[3]);
+            o.w = cvt4_fp8<FMT>(b[4], b[5], b[6], b[7]);
+            *reinterpret_cast<uint4 *>(q + i * 16) = o;
+        }
+        done = nvec * 16;
+    }
+    for (int64_t i = done + tid; i < n; i += nthreads) q[i] = cvt1_fp8<FMT>(scale_clamp<FMT>(load1(x + i), scale));
+}
+
+// ------------------------------------------------------------------------------------------------
+// Row-major rowwise: one block per row; the row is read twice (second read hits L1/L2).
+template <typename T, int FMT>
+__global__ void __launch_bounds__(kThreads)
+    rowwise_last_axis_kernel(const T *__restrict__ x, int64_t rows, int64_t len, int vec_ok,
+                             const float *__restrict__ scale_opt, uint8_t *__restrict__ q,
+                             float *__restrict__ scale_inv) {
+    __shared__ float s[kThreads / 32];
+    __shared__ float s_scale;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T *xr = x + row * len;
+        uint8_t *qr = q + row * len;
+        float scale;
+        if (scale_opt != nullptr) {
+            scale = __ldg(scale_opt + row);
+        } else {
+            float m = 0.f;
+            int64_t done = 0;
+            if (vec_ok) {
+                const int64_t nvec = len / 8;
+                for (int64_t i = threadIdx.x; i < nvec; i += kThreads) {
+                    float v[8];
+                    load8(xr + i * 8, v);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) m = fmaxf(m, fabsf(v[k]));
+                }
+                done = nvec * 8;
+            }
+            for (int64_t i = done + threadIdx.x; i < len; i += kThreads) m = fmaxf(m, fabsf(load1(xr + i)));
+            m = warp_max(m);
+            if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = m;
+            __syncthreads();
+            if (threadIdx.x < 32) {
+                float w = threadIdx.x < kThreads / 32 ? s[threadIdx.x] : 0.f;
+                w = warp_max(w);
+                if (threadIdx.x == 0) s_scale = scale_from_amax<FMT>(w, kEpsTensor);
+            }
+            __syncthreads();
+            scale = s_scale;
+        }
+        if (threadIdx.x == 0) scale_inv[row] = __fdiv_rn(1.0f, scale);
+        int64_t done = 0;
+        if (vec_ok) {
+            const int64_t nvec = len / 8;
+            for (int64_t i = threadIdx.x; i < nvec; i += kThreads) {
+                float v[8];
+                load8(xr + i * 8, v);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[k] = scale_clamp<FMT>(v[k], scale);
+                uint2 o;
+                o.x = cvt4_fp8<FMT>(v[0], v[1], v[2], v[3]);
+                o.y = cvt4_fp8<FMT>(v[4], v[5], v[6], v[7]);
+                *reinterpret_cast<uint2 *>(qr + i * 8) = o;
+            }
+            done = nvec * 8;
+        }
+        for (int64_t i = done + threadIdx.x; i < len; i += kThreads)
+            qr[i] = cvt1_fp8<FMT>(scale_clamp<FMT>(load1(xr + i), scale));
+        __syncthreads();  // s / s_scale are reused by the next row
+    }
+}
+
+// Column amax of x [B, M, N]: each block owns a (b, 64-row, 256-column) tile and folds it into
+// amax_bits [B, N] with atomicMax.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    amax_cols_kernel(const T *__restrict__ x, int64_t M, int64_t N, unsigned *__restrict__ amax_bits) {
+    const int64_t b = blockIdx.z;
+    const int64_t col = (int64_t) blockIdx.x * kThreads + threadIdx.x;
+    if (col >= N) return;
+    const int64_t r0 = (int64_t) blockIdx.y * 64;
+    const int64_t r1 = min(M, r0 + 64);
+    const T *p = x + (b * M) * N + col;
+    float m = 0.f;
+    for (int64_t r = r0; r < r1; ++r) m = fmaxf(m, fabsf(load1(p + r * N)));
+    atomicMax(amax_bits + b * N + col, __float_as_uint(m));
+}
+
+// Cast of x [B, M, N] with one scale per (b, column). 8 columns per thread when aligned.
+template <typename T, int FMT>
+__global__ void __launch_bounds__(kThreads)
+    cast_cols_kernel(const T *__restrict__ x, int64_t M, int64_t N, int vec_ok, const unsigned *__restrict__ amax_bits,
+                     const float *__restrict__ scale_opt, uint8_t *__restrict__ q, float *__restrict__ scale_inv) {
+    const int64_t b = blockIdx.z;
+    const int64_t r0 = (int64_t) blockIdx.y * 32;
+    const int64_t r1 = min(M, r0 + 32);
+    const int W = vec_ok ? 8 : 1;
+    const int64_t c0 = ((int64_t) blockIdx.x * kThreads + threadIdx.x) * W;
+    if (c0 >= N) return;
+    float sc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        if (k < W) {
+            sc[k] = scale_opt ? __ldg(scale_opt + b * N + c0 + k)
+                              : scale_from_amax<FMT>(__uint_as_float(amax_bits[b * N + c0 + k]), kEpsTensor);
+            if (blockIdx.y == 0) scale_inv[b * N + c0 + k] = __fdiv_rn(1.0f, sc[k]);
+        }
+    }
+    for (int64_t r = r0; r < r1; ++r) {
+        const int64_t off = (b * M + r) * N + c0;
+        if (vec_ok) {
+            float v[8];
+            load8(x + off, v);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = scale_clamp<FMT>(v[k], sc[k]);
+            uint2 o;
+            o.x = cvt4_fp8<FMT>(v[0], v[1], v[2], v[3]);
+            o.y = cvt4_fp8<FMT>(v[4], v[5], v[6], v[7]);
+            *reinterpret_cast<uint2 *>(q + off) = o;
+        } else {
+            q[off] = cvt1_fp8<FMT>(scale_clamp<FMT>(load1(x + off), sc[0]));
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// dequantize: y = float(q) * scale_inv
+template <int FMT> __device__ __forceinline__ float decode_fp8(uint8_t c) {
+    if constexpr (FMT == PT_E4M3) {
+        __half_raw h = __nv_cvt_fp8_to_halfraw(c, __NV_E4M3);
+        return __half2float(__half(h));
+    } else {
+        return __half2float(__ushort_as_half((uint16_t) c << 8));  // e5m2 is the top byte of fp16
+    }
+}
+template <typename T> __device__ __forceinline__ void store1(T *p, float v);
+template <> __device__ __forceinline__ void store1<float>(float *p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store1<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ void store1<__half>(__half *p, float v) { *p = __float2half_rn(v); }
+
+template <typename T, int FMT>
+__global__ void __launch_bounds__(kThreads) dequant_kernel(const uint8_t *__restrict__ q, const float *__restrict__ s,
+                                                           int kind, int64_t M, int64_t N, int64_t total,
+                                                           T *__restrict__ y) {
+    const int64_t stride = (int64_t) gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        int64_t si = 0;
+        if (kind == 1) si = i / N;                             // per row
+        else if (kind == 2) si = (i / (M * N)) * N + (i % N);  // per (batch, column)
+        store1(y + i, decode_fp8<FMT>(q[i]) * __ldg(s + si));
+    }
+}
+
+}  // namespace ptb
+
+using namespace ptb;
+
+extern "C" {
+
+const char *pt_last_error(void) { return ptb::g_err; }
+
+int pt_device_sm_count(void) {
+    int dev = 0, n = 0;
+    PT_CUDA_OK(cudaGetDevice(&dev));
+    PT_CUDA_OK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    return n;
+}
+
+size_t pt_quantize_fp8_tensorwise_workspace_bytes(void) { return 256; }
+
+int pt_quantize_fp8_tensorwise(const void *x, int x_dtype, int64_t n, int fmt, void *q, float *scale_inv,
+                               const float *scale_opt, void *workspace, size_t workspace_bytes, void *stream) {
+    PT_REQUIRE(n >= 0 && (n == 0 || (x && q)) && scale_inv, "tensorwise: null pointer or negative size");
+    PT_REQUIRE(scale_opt || (workspace && workspace_bytes >= 4), "tensorwise: workspace of >= 4 bytes required");
+    cudaStream_t st = (cudaStream_t) stream;
+    unsigned *amax = (unsigned *) workspace;
+    const int64_t max_blocks = (int64_t) sm_count() * 8;
+    PT_SWITCH_SRC(x_dtype, T, {
+        const int vec_ok = aligned(x, sizeof(T) == 4 ? 16 : 16) && aligned(q, 16);
+        if (!scale_opt) {
+            PT_CUDA_OK(cudaMemsetAsync(amax, 0, 4, st));
+            const int blocks = (int) std::max<int64_t>(1, std::min(max_blocks, ceil_div(n, (int64_t) kThreads * 32)));
+            amax_flat_kernel<T><<<blocks, kThreads, 0, st>>>((const T *) x, n, vec_ok, amax);
+            PT_LAUNCH_OK();
+        }
+        const int blocks = (int) std::max<int64_t>(1, std::min(max_blocks * 2, ceil_div(n, (int64_t) kThreads * 16)));
+        PT_SWITCH_FP8(fmt, F, {
+            cast_flat_kernel<T, F><<<blocks, kThreads, 0, st>>>((const T *) x, n, vec_ok, amax, scale_opt,
+                                                                 (uint8_t *) q, scale_inv);
+        });
+        PT_LAUNCH_OK();
+    });
+    return PT_OK;
+}
+
+int pt_quantize_fp8_rowwise(const void *x, int x_dtype, int64_t B, int64_t M, int64_t N, int axis_is_last, int fmt,
+                            void *q, float *scale_inv, const float *scale_opt, void *workspace,
+                            size_t workspace_bytes, void *stream) {
+    PT_REQUIRE(B >= 0 && M >= 0 && N >= 0 && scale_inv, "rowwise: bad shape or null scale_inv");
+    if (B * M * N == 0) return PT_OK;
+    PT_REQUIRE(x && q, "rowwise: null pointer");
+    cudaStream_t st = (cudaStream_t) stream;
+    if (axis_is_last) {
+        const int64_t rows = B * M;
+        PT_SWITCH_SRC(x_dtype, T, {
+            const int vec_ok = aligned(x, 16) && aligned(q, 8) && (N % 8 == 0);
+            const int blocks = (int) std::min<int64_t>(rows, (int64_t) sm_count() * 16);
+            PT_SWITCH_FP8(fmt, F, {
+                rowwise_last_axis_kernel<T, F><<<blocks, kThreads, 0, st>>>((const T *) x, rows, N, vec_ok, scale_opt,
+                                                                            (uint8_t *) q, scale_inv);
+            });
+            PT_LAUNCH_OK();
+        });
+        return PT_OK;
+    }
+    PT_REQUIRE(B <= 65535, "rowwise: batch too large");
+    unsigned *amax = (unsigned *) workspace;
+    if (!scale_opt) {
+        PT_REQUIRE(workspace && workspace_bytes >= (size_t) (B * N) * 4, "rowwise: workspace of B*N floats required");
+        PT_CUDA_OK(cudaMemsetAsync(amax, 0, (size_t) (B * N) * 4, st));
+    }
+    PT_SWITCH_SRC(x_dtype, T, {
+        if (!scale_opt) {
+            dim3 grid((unsigned) ceil_div(N, kThreads), (unsigned) ceil_div(M, 64), (unsigned) B);
+            amax_cols_kernel<T><<<grid, kThreads, 0, st>>>((const T *) x, M, N, amax);
+            PT_LAUNCH_OK();
+        }
+        const int vec_ok = aligned(x, 16) && aligned(q, 8) && (N % 8 == 0);
+        dim3 grid((unsigned) ceil_div(N, kThreads * (vec_ok ? 8 : 1)), (unsigned) ceil_div(M, 32), (unsigned) B);
+        PT_SWITCH_FP8(fmt, F, {
+            cast_cols_kernel<T, F><<<grid, kThreads, 0, st>>>((const T *) x, M, N, vec_ok, amax, scale_opt,
+                                                              (uint8_t *) q, scale_inv);
+        });
+        PT_LAUNCH_OK();
+    });
+    return PT_OK;
+}
+
+int pt_dequantize_fp8(const void *q, int fmt, const float *scale_inv, int scale_kind, int64_t B, int64_t M, int64_t N,
+                      void *y, int y_dtype, void *stream) {
+    const int64_t total = B * M * N;
+    PT_REQUIRE(total >= 0 && scale_kind >= 0 && scale_kind <= 2, "dequantize: bad arguments");
+    if (total == 0) return PT_OK;
+    PT_REQUIRE(q && y && scale_inv, "dequantize: null pointer");
+    const int blocks = (int) std::min<int64_t>(ceil_div(total, kThreads), (int64_t) sm_count() * 16);
+    PT_SWITCH_SRC(y_dtype, T, {
+        PT_SWITCH_FP8(fmt, F, {
+            dequant_kernel<T, F><<<blocks, kThreads, 0, (cudaStream_t) stream>>>((const uint8_t *) q, scale_inv,
+                                                                                 scale_kind, M, N, total, (T *) y);
+        });
+        PT_LAUNCH_OK();
+    });
+    return PT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,380 @@
+// MX (32-element block, ue8m0 scale) quantization to e4m3 / e5m2 / e2m1 and the matching dequantize.
+//
+// One CTA owns a 128 (rows) x 64 (cols) tile of the bf16 / fp16 input.  The row-wise copy is produced
+// straight from the registers the tile was loaded into (4 lanes x 8 elements per 32-block, amax by
+// warp shuffle); the col-wise (transposed) copy is produced from a shared-memory image of the tile,
+// one thread per (column, 32-row band).  The input is read from HBM once for both copies.
+//
+// Arithmetic follows csrc/kernels/quantization/quantization_mxfp8.cu:68-214 and
+// quantization_mxfp4.cu:91-227 of the reference:
+//   e    = (((bits(amax) + (1 << (22 - mbits))) >> 23) & 0x1FF) - 127 - emax_target, clamped to [-127, 128]
+//   byte = e + 127, scale = 2^e
+//   fp8:  q = rne(clamp(v, +-qmax * scale) / scale)        fp4: q = rne_sat(v / scale)
+// A block whose scale byte is 0 (every |v| < 2^-118 or so) is written as zeros.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace ptb {
+
+constexpr int kTileM = 128;
+constexpr int kTileN = 64;
+constexpr int kMxThreads = 256;
+constexpr int kSmemStride = kTileN + 2;  // halfwords; keeps 4-byte alignment of pairs
+
+template <int FMT> struct MxParams;
+template <> struct MxParams<PT_E4M3> { static constexpr int mbits = 3, target = 8; static constexpr float qmax = 448.f; };
+template <> struct MxParams<PT_E5M2> { static constexpr int mbits = 2, target = 15; static constexpr float qmax = 57344.f; };
+template <> struct MxParams<PT_E2M1> { static constexpr int mbits = 1, target = 2; static constexpr float qmax = 6.f; };
+
+struct MxScale {
+    uint8_t byte;
+    float native;  // 2^e as the reference builds it: (byte << 23) reinterpret; 0.0f for byte 0
+    float inv;     // 2^-e, exact
+};
+
+template <int FMT> __device__ __forceinline__ MxScale mx_scale(float amax, bool zero_is_one) {
+    const uint32_t bits = __float_as_uint(amax);
+    int e = (int) (((bits + (1u << (22 - MxParams<FMT>::mbits))) >> 23) & 0x1FFu) - 127 - MxParams<FMT>::target;
+    e = max(-127, min(128, e));
+    MxScale s;
+    if (zero_is_one && amax == 0.f) e = 0;  // grouped kernels: an all-zero block gets scale 1.0 (byte 127)
+    s.byte = (uint8_t) (e + 127);
+    s.native = __uint_as_float((uint32_t) s.byte << 23);
+    if (e >= -126 && e <= 126) s.inv = __uint_as_float((uint32_t) (127 - e) << 23);
+    else if (e == 127) s.inv = __uint_as_float(0x00400000u);  // 2^-127
+    else s.inv = 0.f;                                         // byte 0 (data forced to 0) or byte 255
+    return s;
+}
+
+// 8 scaled values -> 8 codes packed into 8 bytes (fp8) or 4 bytes (fp4)
+template <int FMT> __device__ __forceinline__ uint2 mx_encode8(const float (&v)[8], const MxScale &s) {
+    uint2 o = make_uint2(0u, 0u);
+    if (s.byte == 0) return o;
+    float t[8];
+    if constexpr (FMT == PT_E2M1) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t[i] = v[i] * s.inv;
+        o.x = (uint32_t) cvt2_e2m1(t[0], t[1]) | ((uint32_t) cvt2_e2m1(t[2], t[3]) << 8) |
+              ((uint32_t) cvt2_e2m1(t[4], t[5]) << 16) | ((uint32_t) cvt2_e2m1(t[6], t[7]) << 24);
+    } else {
+        const float lim = MxParams<FMT>::qmax * s.native;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t[i] = fminf(fmaxf(v[i], -lim), lim) * s.inv;
+        o.x = cvt4_fp8<FMT>(t[0], t[1], t[2], t[3]);
+        o.y = cvt4_fp8<FMT>(t[4], t[5], t[6], t[7]);
+    }
+    return o;
+}
+
+// 16-point Hadamard over v[0..15] (four runs of 4), operation order of quantization_mxfp4.cu:91-136
+__device__ __forceinline__ void rht16(float *v) {
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        float *p = v + 4 * t;
+        const float a0 = p[0] + p[1], a1 = p[0] - p[1], a2 = p[2] + p[3], a3 = p[2] - p[3];
+        p[0] = a0 + a2; p[2] = a0 - a2; p[1] = a1 + a3; p[3] = a1 - a3;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {  // partner = run xor 1: odd run takes (partner - own), even (partner + own)
+        const float r0 = v[i], r1 = v[4 + i], r2 = v[8 + i], r3 = v[12 + i];
+        v[i] = r1 + r0; v[4 + i] = r0 - r1; v[8 + i] = r3 + r2; v[12 + i] = r2 - r3;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {  // partner = run xor 2
+        const float r0 = v[i], r1 = v[4 + i], r2 = v[8 + i], r3 = v[12 + i];
+        v[i] = (r2 + r0) * 0.25f; v[4 + i] = (r3 + r1) * 0.25f;
+        v[8 + i] = (r0 - r2) * 0.25f; v[12 + i] = (r1 - r3) * 0.25f;
+    }
+}
+
+struct MxArgs {
+    const void *x;
+    int64_t M, N, M_pad, N_pad;
+    uint8_t *q_row, *s_row, *q_col, *s_col;
+    int64_t x_gstride, qrow_gstride, srow_gstride, qcol_gstride, scol_gstride;  // per batch entry, in elements/bytes
+};
+
+// grid: (N_pad / 64, M_pad / 128, G)
+template <typename T, int FMT, bool ROW, bool COL, bool ROW2D, bool COL2D, bool ROWRHT, bool COLRHT>
+__global__ void __launch_bounds__(kMxThreads) mx_quant_kernel(MxArgs a) {
+    constexpr bool kFp4 = FMT == PT_E2M1;
+    constexpr bool kNeed2D = (ROW && ROW2D) || (COL && COL2D);
+    __shared__ __align__(16) uint16_t s_tile[COL ? kTileM : 1][kSmemStride];
+    __shared__ unsigned s_amax2d[4][2];
+
+    const int tid = threadIdx.x;
+    const int64_t g = blockIdx.z;
+    const int64_t m0 = (int64_t) blockIdx.y * kTileM;
+    const int64_t n0 = (int64_t) blockIdx.x * kTileN;
+    const T *x = reinterpret_cast<const T *>(a.x) + g * a.x_gstride;
+
+    if constexpr (kNeed2D) {
+        if (tid < 8) s_amax2d[tid >> 1][tid & 1] = 0u;
+        __syncthreads();
+    }
+
+    // ---- load: iteration i covers rows 32 i .. 32 i + 31 (8 lanes x 8 elements per row)
+    const int cvec = tid & 7;
+    const int rsub = tid >> 3;
+    const int64_t gn = n0 + cvec * 8;
+    float v[4][8];
+    float amax4[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int64_t gm = m0 + 32 * i + rsub;
+        uint32_t w[4] = {0u, 0u, 0u, 0u};
+        if (gm < a.M && gn < a.N) {
+            const uint4 r = __ldg(reinterpret_cast<const uint4 *>(x + gm * a.N + gn));
+            w[0] = r.x; w[1] = r.y; w[2] = r.z; w[3] = r.w;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            v[i][2 * k] = Src<T>::to_f32((uint16_t) (w[k] & 0xFFFF));
+            v[i][2 * k + 1] = Src<T>::to_f32((uint16_t) (w[k] >> 16));
+        }
+        if constexpr (COL) {
+            // keep the raw 16-bit pattern; re-expanded exactly when read back
+            uint32_t *dst = reinterpret_cast<uint32_t *>(&s_tile[32 * i + rsub][cvec * 8]);
+            dst[0] = w[0]; dst[1] = w[1]; dst[2] = w[2]; dst[3] = w[3];
+        }
+        if constexpr (kNeed2D) {
+            float m = 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) m = fmaxf(m, fabsf(v[i][k]));
+            amax4[i] = m;
+        }
+    }
+    if constexpr (kNeed2D) {
+        // 32 x 32 tile amax: (band i, column half c) collects lanes with cvec / 4 == c
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float m = amax4[i];
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+            if ((tid & 27) == 0) atomicMax(&s_amax2d[i][(tid >> 2) & 1], __float_as_uint(m));
+        }
+    }
+    if constexpr (COL || kNeed2D) __syncthreads();
+
+    // ---- row-wise copy from registers
+    if constexpr (ROW) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int64_t gm = m0 + 32 * i + rsub;
+            float t[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) t[k] = v[i][k];
+            if constexpr (ROWRHT) {
+                // a 16-group spans two lanes: runs 0,1 in the even lane, runs 2,3 in the odd lane
+                float full[16];
+                const bool odd = cvec & 1;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const float other = __shfl_xor_sync(0xffffffffu, t[k], 1);
+                    full[k] = odd ? other : t[k];
+                    full[8 + k] = odd ? t[k] : other;
+                }
+                rht16(full);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) t[k] = odd ? full[8 + k] : full[k];
+            }
+            float m;
+            if constexpr (ROW2D) {
+                m = __uint_as_float(s_amax2d[i][cvec >> 2]);
+            } else {
+                m = 0.f;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) m = fmaxf(m, fabsf(t[k]));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+            }
+            const MxScale s = mx_scale<FMT>(m, false);
+            const uint2 o = mx_encode8<FMT>(t, s);
+            if (gm < a.M && gn < a.N_pad) {
+                uint8_t *qr = a.q_row + g * a.qrow_gstride;
+                if constexpr (kFp4) *reinterpret_cast<uint32_t *>(qr + (gm * a.N_pad + gn) / 2) = o.x;
+                else *reinterpret_cast<uint2 *>(qr + gm * a.N_pad + gn) = o;
+                if ((cvec & 3) == 0) (a.s_row + g * a.srow_gstride)[gm * (a.N_pad / 32) + gn / 32] = s.byte;
+            }
+        }
+    }
+
+    // ---- col-wise (transposed) copy from shared memory: thread = (column tid % 64, band tid / 64)
+    if constexpr (COL) {
+        const int col = tid & 63;
+        const int band = tid >> 6;
+        const int64_t gc = n0 + col;
+        if (gc < a.N) {
+            float c[32];
+#pragma unroll
+            for (int r = 0; r < 32; ++r) c[r] = Src<T>::to_f32(s_tile[band * 32 + r][col]);
+            if constexpr (COLRHT) { rht16(c); rht16(c + 16); }
+            float m;
+            if constexpr (COL2D) {
+                m = __uint_as_float(s_amax2d[band][col >> 5]);
+            } else {
+                m = 0.f;
+#pragma unroll
+                for (int r = 0; r < 32; ++r) m = fmaxf(m, fabsf(c[r]));
+            }
+            const MxScale s = mx_scale<FMT>(m, false);
+            const int64_t gm = m0 + band * 32;
+            uint8_t *qc = a.q_col + g * a.qcol_gstride;
+            uint32_t w[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float t[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) t[k] = c[8 * j + k];
+                const uint2 o = mx_encode8<FMT>(t, s);
+                if constexpr (kFp4) w[j] = o.x; else { w[2 * j] = o.x; w[2 * j + 1] = o.y; }
+            }
+            if constexpr (kFp4) {
+                *reinterpret_cast<uint4 *>(qc + (gc * a.M_pad + gm) / 2) = make_uint4(w[0], w[1], w[2], w[3]);
+            } else {
+                uint4 *dst = reinterpret_cast<uint4 *>(qc + gc * a.M_pad + gm);
+                dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            }
+            (a.s_col + g * a.scol_gstride)[gc * (a.M_pad / 32) + gm / 32] = s.byte;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ dequantize
+template <typename T> __device__ __forceinline__ void put_out(T *p, float v);
+template <> __device__ __forceinline__ void put_out<float>(float *p, float v) { *p = v; }
+template <> __device__ __forceinline__ void put_out<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ void put_out<__half>(__half *p, float v) { *p = __float2half_rn(v); }
+
+__device__ __forceinline__ float decode_code(int fmt, uint8_t c) {
+    if (fmt == PT_E5M2) return __half2float(__ushort_as_half((uint16_t) c << 8));
+    if (fmt == PT_E4M3) {
+        const uint32_t sign = (uint32_t) (c & 0x80) << 24, e = (c >> 3) & 0xF, m = c & 7;
+        if (e == 0) return __uint_as_float(sign | __float_as_uint((float) m * 0.001953125f));
+        if (e == 15 && m == 7) return __uint_as_float(sign | 0x7FC00000u);
+        return __uint_as_float(sign | ((e + 120) << 23) | (m << 20));
+    }
+    const float tab[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+    const float mag = tab[c & 7];
+    return (c & 8) ? -mag : mag;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) mx_dequant_kernel(const uint8_t *__restrict__ q, int fmt,
+                                                        const uint8_t *__restrict__ s, int64_t rows, int64_t cols,
+                                                        int64_t cols_stored, int transpose_out, T *__restrict__ y) {
+    const int64_t total = rows * cols;
+    const int64_t stride = (int64_t) gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t r = i / cols, c = i % cols;
+        uint8_t code;
+        if (fmt == PT_E2M1) {
+            const uint8_t b = q[(r * cols_stored + c) >> 1];
+            code = (c & 1) ? (b >> 4) : (b & 0xF);
+        } else {
+            code = q[r * cols_stored + c];
+        }
+        const int sb = s[r * (cols_stored / 32) + c / 32];
+        const float sc = __uint_as_float(sb == 255 ? 0x7FC00000u : (sb == 0 ? 0x00400000u : (uint32_t) sb << 23));
+        const float val = decode_code(fmt, code) * sc;
+        put_out(y + (transpose_out ? c * rows + r : i), val);
+    }
+}
+
+template <typename T, int FMT>
+static int launch_mx(const MxArgs &a, int64_t G, unsigned flags, cudaStream_t st) {
+    dim3 grid((unsigned) (a.N_pad / kTileN), (unsigned) (a.M_pad / kTileM), (unsigned) G);
+    const bool row = flags & PT_MX_ROW, col = flags & PT_MX_COL;
+    const bool r2d = flags & PT_MX_ROW_2D, c2d = flags & PT_MX_COL_2D;
+    const bool rrht = flags & PT_MX_ROW_RHT, crht = flags & PT_MX_COL_RHT;
+#define PT_MX_CASE(R, C, R2, C2, RR, CR)                                                                   \
+    if (row == R && col == C && (!R || r2d == R2) && (!C || c2d == C2) && (!R || rrht == RR) && (!C || crht == CR)) { \
+        mx_quant_kernel<T, FMT, R, C, R2, C2, RR, CR><<<grid, kMxThreads, 0, st>>>(a);                     \
+        PT_LAUNCH_OK();                                                                                    \
+        return PT_OK;                                                                                      \
+    }
+    if constexpr (FMT == PT_E2M1) {
+        PT_MX_CASE(true, false, false, false, false, false)
+        PT_MX_CASE(true, false, true, false, false, false)
+        PT_MX_CASE(true, false, false, false, true, false)
+        PT_MX_CASE(false, true, false, false, false, false)
+        PT_MX_CASE(false, true, false, true, false, false)
+        PT_MX_CASE(false, true, false, false, false, true)
+        PT_MX_CASE(true, true, false, false, false, false)
+        PT_MX_CASE(true, true, true, true, false, false)
+        PT_MX_CASE(true, true, false, false, false, true)
+        PT_MX_CASE(true, true, false, false, true, true)
+        PT_MX_CASE(true, true, false, false, true, false)
+    } else {
+        PT_MX_CASE(true, false, false, false, false, false)
+        PT_MX_CASE(true, false, true, false, false, false)
+        PT_MX_CASE(false, true, false, false, false, false)
+        PT_MX_CASE(false, true, false, true, false, false)
+        PT_MX_CASE(true, true, false, false, false, false)
+        PT_MX_CASE(true, true, true, true, false, false)
+        PT_MX_CASE(true, true, true, false, false, false)
+        PT_MX_CASE(true, true, false, true, false, false)
+    }
+#undef PT_MX_CASE
+    return set_error(PT_ERR_UNSUPPORTED, "MX quantize: flag combination 0x%x is not built for this format", flags);
+}
+
+}  // namespace ptb
+
+using namespace ptb;
+
+extern "C" {
+
+int pt_quantize_mx(const void *x, int x_dtype, int64_t G, int64_t M, int64_t N, int fmt, unsigned flags, void *q_row,
+                   uint8_t *s_row, void *q_col, uint8_t *s_col, void *stream) {
+    PT_REQUIRE(G >= 1 && M >= 0 && N >= 0, "MX quantize: bad shape");
+    PT_REQUIRE(N % 32 == 0, "MX quantize: N must be divisible by 32 (got %lld)", (long long) N);
+    PT_REQUIRE(x_dtype == PT_BF16 || x_dtype == PT_F16, "MX quantize: input must be bf16 or fp16");
+    PT_REQUIRE(flags & (PT_MX_ROW | PT_MX_COL), "MX quantize: no output requested");
+    PT_REQUIRE(!(flags & PT_MX_ROW) || (q_row && s_row), "MX quantize: row outputs missing");
+    PT_REQUIRE(!(flags & PT_MX_COL) || (q_col && s_col), "MX quantize: col outputs missing");
+    PT_REQUIRE(fmt == PT_E2M1 || !(flags & (PT_MX_ROW_RHT | PT_MX_COL_RHT)), "MX quantize: RHT is an e2m1 option");
+    if (M == 0 || N == 0) return PT_OK;
+    PT_REQUIRE(x && aligned(x, 16), "MX quantize: input must be 16-byte aligned");
+    PT_REQUIRE(G <= 65535, "MX quantize: batch too large");
+    MxArgs a;
+    a.x = x; a.M = M; a.N = N; a.M_pad = ceil_to(M, 128); a.N_pad = ceil_to(N, 128);
+    PT_REQUIRE(a.M_pad / kTileM <= 65535, "MX quantize: M too large");
+    a.q_row = (uint8_t *) q_row; a.s_row = s_row; a.q_col = (uint8_t *) q_col; a.s_col = s_col;
+    const int div = fmt == PT_E2M1 ? 2 : 1;
+    a.x_gstride = M * N;
+    a.qrow_gstride = M * a.N_pad / div; a.srow_gstride = M * (a.N_pad / 32);
+    a.qcol_gstride = N * a.M_pad / div; a.scol_gstride = N * (a.M_pad / 32);
+    cudaStream_t st = (cudaStream_t) stream;
+    if (x_dtype == PT_BF16) {
+        if (fmt == PT_E4M3) return launch_mx<__nv_bfloat16, PT_E4M3>(a, G, flags, st);
+        if (fmt == PT_E5M2) return launch_mx<__nv_bfloat16, PT_E5M2>(a, G, flags, st);
+        if (fmt == PT_E2M1) return launch_mx<__nv_bfloat16, PT_E2M1>(a, G, flags, st);
+    } else {
+        if (fmt == PT_E4M3) return launch_mx<__half, PT_E4M3>(a, G, flags, st);
+        if (fmt == PT_E5M2) return launch_mx<__half, PT_E5M2>(a, G, flags, st);
+        if (fmt == PT_E2M1) return launch_mx<__half, PT_E2M1>(a, G, flags, st);
+    }
+    return set_error(PT_ERR_INVALID, "MX quantize: unknown format %d", fmt);
+}
+
+int pt_dequantize_mx(const void *q, int fmt, const uint8_t *s, int64_t rows, int64_t cols, int64_t cols_stored,
+                     int transpose_out, void *y, int y_dtype, void *stream) {
+    PT_REQUIRE(rows >= 0 && cols >= 0 && cols <= cols_stored && cols_stored % 32 == 0, "MX dequantize: bad shape");
+    PT_REQUIRE(fmt == PT_E4M3 || fmt == PT_E5M2 || fmt == PT_E2M1, "MX dequantize: unknown format %d", fmt);
+    if (rows * cols == 0) return PT_OK;
+    PT_REQUIRE(q && s && y, "MX dequantize: null pointer");
+    const int blocks = (int) std::min<int64_t>(ceil_div(rows * cols, 256), (int64_t) sm_count() * 16);
+    PT_SWITCH_SRC(y_dtype, T, {
+        mx_dequant_kernel<T><<<blocks, 256, 0, (cudaStream_t) stream>>>((const uint8_t *) q, fmt, s, rows, cols,
+                                                                        cols_stored, transpose_out, (T *) y);
+        PT_LAUNCH_OK();
+    });
+    return PT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,6 @@
+"""primus_turbo.pytorch: the operator surface of the low-precision GEMM path."""
+from .. import _clib
+
+_clib.load()  # fail at import, loudly, when the CUDA library is absent
+
+from .core.low_precision import float4_e2m1fn_x2, float8_e4m3, float8_e5m2  # noqa: E402,F401

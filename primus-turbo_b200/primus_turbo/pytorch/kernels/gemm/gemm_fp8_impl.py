@@ -1,0 +1,74 @@
+"""FP8 / MXFP8 dense GEMM over the C ABI.
+
+Same call shape as primus_turbo::gemm_fp8_impl / gemm_fp8_accum_impl of the reference
+(primus_turbo/pytorch/kernels/gemm/gemm_fp8_impl.py:518-593).  The CUDA kernel computes
+C = A . B^T with both operands K-major; the other (trans_a, trans_b, trans_c) combinations are
+mapped onto it by swapping the operands (trans_c) or by transposing the FP8 bytes first, which is
+what the reference does for its NT-only back ends (primus_turbo/pytorch/ops/gemm_fp8.py:44-50).
+"""
+import torch
+
+from ...core.low_precision import ScalingGranularity
+from .. import _native as nv
+from ..quantization.quantization_impl import transpose_2d
+
+_GRAN = {ScalingGranularity.TENSORWISE: nv.PT_TENSORWISE, ScalingGranularity.ROWWISE: nv.PT_ROWWISE,
+         ScalingGranularity.BLOCKWISE: nv.PT_BLOCKWISE, ScalingGranularity.MX_BLOCKWISE: nv.PT_MX_BLOCKWISE}
+
+
+def _as_gran(granularity):
+    return granularity if isinstance(granularity, ScalingGranularity) else ScalingGranularity(int(granularity))
+
+
+def _k_major(x, trans):
+    """Returns x laid out [rows, K]: x itself when it already is, else the transposed bytes."""
+    return transpose_2d(x) if trans else x.contiguous()
+
+
+def _launch(a_km, a_s, b_km, b_s, out, gran, beta, block_n=0):
+    M, K = a_km.shape
+    N = b_km.shape[0]
+    assert b_km.shape[1] == K, f"contraction mismatch: {a_km.shape} vs {b_km.shape}"
+    st = nv.status_word(out.device)
+    with torch.cuda.device(out.device):
+        nv.check(nv.lib().pt_gemm_fp8(nv.ptr(a_km), nv.ptr(a_s), nv.fmt_code(a_km.dtype), nv.ptr(b_km), nv.ptr(b_s),
+                                       nv.fmt_code(b_km.dtype), nv.ptr(out), nv.src_code(out.dtype), _GRAN[gran], M, N, K,
+                                       float(beta), block_n, nv.ptr(st), nv.stream(out.device)), "gemm_fp8")
+    return out
+
+
+def _gemm(a, a_scale_inv, trans_a, b, b_scale_inv, trans_b, out_dtype, trans_c, granularity, out=None, block_n=0):
+    nv.require_cuda(a, b, a_scale_inv, b_scale_inv)
+    assert a.dim() == 2 and b.dim() == 2, "Only 2D tensors are supported"
+    gran = _as_gran(granularity)
+    if gran == ScalingGranularity.MX_BLOCKWISE:
+        assert not trans_a and trans_b, "MX GEMM takes K-major operands only (trans_a=False, trans_b=True)"
+    a_km = _k_major(a, trans_a)            # [M, K]
+    b_km = _k_major(b, not trans_b)        # [N, K]
+    a_s = a_scale_inv.contiguous()
+    b_s = b_scale_inv.contiguous()
+    if gran in (ScalingGranularity.TENSORWISE, ScalingGranularity.ROWWISE):
+        a_s, b_s = a_s.to(torch.float32).reshape(-1), b_s.to(torch.float32).reshape(-1)
+        if gran == ScalingGranularity.ROWWISE:
+            assert a_s.numel() == a_km.shape[0] and b_s.numel() == b_km.shape[0], "rowwise scales must match M and N"
+    M, N = a_km.shape[0], b_km.shape[0]
+    beta = 0.0
+    if out is not None:
+        beta = 1.0
+        assert out.is_contiguous() and tuple(out.shape) == ((N, M) if trans_c else (M, N))
+    else:
+        out = torch.empty((N, M) if trans_c else (M, N), dtype=out_dtype, device=a.device)
+    if trans_c:
+        return _launch(b_km, b_s, a_km, a_s, out, gran, beta, block_n)
+    return _launch(a_km, a_s, b_km, b_s, out, gran, beta, block_n)
+
+
+def gemm_fp8_impl(a, a_scale_inv, trans_a, b, b_scale_inv, trans_b, out_dtype, trans_c, granularity,
+                  default_backend=0, block_n=0):
+    """C = op(A) . op(B) (optionally transposed). `default_backend` is accepted and ignored: there is one back end."""
+    return _gemm(a, a_scale_inv, trans_a, b, b_scale_inv, trans_b, out_dtype, trans_c, granularity, None, block_n)
+
+
+def gemm_fp8_accum_impl(a, a_scale_inv, trans_a, b, b_scale_inv, trans_b, out, trans_c, granularity, default_backend=0):
+    """out += op(A) . op(B); `out` is modified in place and returned."""
+    return _gemm(a, a_scale_inv, trans_a, b, b_scale_inv, trans_b, out.dtype, trans_c, granularity, out)

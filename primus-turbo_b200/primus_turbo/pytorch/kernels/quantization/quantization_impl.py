@@ -1,0 +1,334 @@
+"""Quantize / dequantize entry points over the C ABI.
+
+Function names, arguments and return layouts follow
+primus_turbo/pytorch/kernels/quantization/quantization_impl.py of the reference; each call lands in
+one extern "C" function of libpt_b200.so.
+"""
+from typing import Optional, Tuple
+
+import torch
+
+from ...core.low_precision import ScalingRecipe
+from .. import _native as nv
+
+BLOCK = 128
+MX_BLOCK = 32
+MX_ALIGN = 128
+
+
+def ceil_div(a, b):
+    return (a + b - 1) // b
+
+
+def _ws(device):
+    return torch.empty(64, dtype=torch.int32, device=device)
+
+
+# ------------------------------------------------------------------------------ tensorwise / rowwise
+def quantize_fp8_tensorwise_impl(x: torch.Tensor, out_dtype: torch.dtype,
+                                 scale: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    nv.require_cuda(x, scale)
+    x = x.contiguous()
+    q = torch.empty_like(x, dtype=out_dtype)
+    scale_inv = torch.empty((), dtype=torch.float32, device=x.device)
+    ws = _ws(x.device)
+    if scale is not None:
+        assert scale.numel() == 1, "tensorwise scale must be scalar tensor"
+        scale = scale.to(torch.float32).contiguous()
+    with torch.cuda.device(x.device):
+        nv.check(nv.lib().pt_quantize_fp8_tensorwise(nv.ptr(x), nv.src_code(x.dtype), x.numel(), nv.fmt_code(out_dtype),
+                                                      nv.ptr(q), nv.ptr(scale_inv), nv.ptr(scale), nv.ptr(ws),
+                                                      ws.numel() * 4, nv.stream(x.device)), "quantize_fp8_tensorwise")
+    return q, scale_inv
+
+
+def quantize_fp8_rowwise_impl(x: torch.Tensor, out_dtype: torch.dtype, axis: int,
+                              scale: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    nv.require_cuda(x, scale)
+    assert x.is_contiguous(), "The x tensor must be contiguous."
+    axis = axis if axis >= 0 else x.dim() + axis
+    assert 0 <= axis < x.dim()
+    shape = list(x.shape)
+    scale_shape = list(shape)
+    scale_shape[axis] = 1
+    q = torch.empty_like(x, dtype=out_dtype)
+    scale_inv = torch.empty(scale_shape, dtype=torch.float32, device=x.device)
+    last = axis == x.dim() - 1
+    if last:
+        B, M, N = 1, x.numel() // max(shape[axis], 1), shape[axis]
+    else:
+        B = 1
+        for s in shape[:axis]:
+            B *= s
+        M = shape[axis]
+        N = 1
+        for s in shape[axis + 1:]:
+            N *= s
+    ws = None
+    if not last and scale is None:
+        ws = torch.empty(max(B * N, 1), dtype=torch.int32, device=x.device)
+    if scale is not None:
+        assert list(scale.shape) == scale_shape
+        scale = scale.to(torch.float32).contiguous()
+    with torch.cuda.device(x.device):
+        nv.check(nv.lib().pt_quantize_fp8_rowwise(nv.ptr(x), nv.src_code(x.dtype), B, M, N, int(last),
+                                                   nv.fmt_code(out_dtype), nv.ptr(q), nv.ptr(scale_inv), nv.ptr(scale),
+                                                   nv.ptr(ws), 0 if ws is None else ws.numel() * 4,
+                                                   nv.stream(x.device)), "quantize_fp8_rowwise")
+    return q, scale_inv
+
+
+def dequantize_fp8_tensorwise_impl(x: torch.Tensor, out_dtype: torch.dtype, scale_inv: torch.Tensor):
+    nv.require_cuda(x, scale_inv)
+    x = x.contiguous()
+    y = torch.empty_like(x, dtype=out_dtype)
+    with torch.cuda.device(x.device):
+        nv.check(nv.lib().pt_dequantize_fp8(nv.ptr(x), nv.fmt_code(x.dtype), nv.ptr(scale_inv.contiguous()), 0, 1, 1,
+                                             x.numel(), nv.ptr(y), nv.src_code(out_dtype), nv.stream(x.device)),
+                 "dequantize_fp8_tensorwise")
+    return y
+
+
+def dequantize_fp8_rowwise_impl(x: torch.Tensor, out_dtype: torch.dtype, axis: int, scale_inv: torch.Tensor):
+    nv.require_cuda(x, scale_inv)
+    assert x.is_contiguous(), "The x tensor must be contiguous."
+    assert scale_inv.is_contiguous(), "The scale_inv tensor must be contiguous."
+    axis = axis if axis >= 0 else x.dim() + axis
+    shape = list(x.shape)
+    y = torch.empty_like(x, dtype=out_dtype)
+    if axis == x.dim() - 1:
+        kind, B, M, N = 1, 1, x.numel() // max(shape[axis], 1), shape[axis]
+    else:
+        kind, B = 2, 1
+        for s in shape[:axis]:
+            B *= s
+        M, N = shape[axis], 1
+        for s in shape[axis + 1:]:
+            N *= s
+    with torch.cuda.device(x.device):
+        nv.check(nv.lib().pt_dequantize_fp8(nv.ptr(x), nv.fmt_code(x.dtype), nv.ptr(scale_inv), kind, B, M, N,
+                                             nv.ptr(y), nv.src_code(out_dtype), nv.stream(x.device)),
+                 "dequantize_fp8_rowwise")
+    return y
+
+
+# ------------------------------------------------------------------------------ 128-blockwise
+def quant_fp8_blockwise_impl(x: torch.Tensor, dtype: torch.dtype, axis: int,
+                             block_size: int = 128) -> Tuple[torch.Tensor, torch.Tensor]:
+    nv.require_cuda(x)
+    assert x.is_contiguous() and x.dim() == 2, "Input must be 2D and contiguous"
+    assert axis in (-2, -1, 0, 1), f"axis must be 0 or 1 (or -1, -2), got {axis}"
+    assert block_size == BLOCK, "block_size must be 128"
+    axis = axis % 2
+    M, N = x.shape
+    q = torch.empty((M, N), dtype=dtype, device=x.device)
+    s = torch.empty((M, ceil_div(N, BLOCK)) if axis == 1 else (ceil_div(M, BLOCK), N), dtype=torch.float32,
+                    device=x.device)
+    args = (nv.ptr(q), nv.ptr(s), None, None) if axis == 1 else (None, None, nv.ptr(q), nv.ptr(s))
+    with torch.cuda.device(x.device):
+        nv.check(nv.lib().pt_quantize_fp8_blockwise(nv.ptr(x), nv.src_code(x.dtype), M, N, nv.fmt_code(dtype), *args,
+                                                     nv.stream(x.device)), "quant_fp8_blockwise")
+    return q, s
+
+
+def quant_fp8_blockwise_dual_impl(x: torch.Tensor, dtype: torch.dtype, block_size: int = 128):
+    """(q_row, s_row [M, N/128], q_col [M, N] not transposed, s_col [M/128, N]) from one read of x."""
+    nv.require_cuda(x)
+    assert x.is_contiguous() and x.dim() == 2, "Input must be 2D and contiguous"
+    assert block_size == BLOCK, "block_size must be 128"
+    M, N = x.shape
+    q_row = torch.empty((M, N), dtype=dtype, device=x.device)
+    q_col = torch.empty((M, N), dtype=dtype, device=x.device)
+    s_row = torch.empty((M, ceil_div(N, BLOCK)), dtype=torch.float32, device=x.device)
+    s_col = torch.empty((ceil_div(M, BLOCK), N), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        nv.check(nv.lib().pt_quantize_fp8_blockwise(nv.ptr(x), nv.src_code(x.dtype), M, N, nv.fmt_code(dtype),
+                                                     nv.ptr(q_row), nv.ptr(s_row), nv.ptr(q_col), nv.ptr(s_col),
+                                                     nv.stream(x.device)), "quant_fp8_blockwise_dual")
+    return q_row, s_row, q_col, s_col
+
+
+def quant_fp8_blockwise_for_weight_impl(w: torch.Tensor, dtype: torch.dtype, block_size: int = 128):
+    nv.require_cuda(w)
+    assert w.dim() in (2, 3), "Weight must be 2D or 3D"
+    assert block_size == BLOCK, "block_size must be 128"
+    w = w.contiguous()
+    B = 1 if w.dim() == 2 else w.shape[0]
+    M, N = w.shape[-2:]
+    q = torch.empty_like(w, dtype=dtype)
+    sshape = (ceil_div(M, BLOCK), ceil_div(N, BLOCK))
+    s = torch.empty(sshape if w.dim() == 2 else (B,) + sshape, dtype=torch.float32, device=w.device)
+    with torch.cuda.device(w.device):
+        nv.check(nv.lib().pt_quantize_fp8_blockwise_weight(nv.ptr(w), nv.src_code(w.dtype), B, M, N, nv.fmt_code(dtype),
+                                                            nv.ptr(q), nv.ptr(s), nv.stream(w.device)),
+                 "quant_fp8_blockwise_for_weight")
+    return q, s
+
+
+def compute_padded_group_offs(group_lens: torch.Tensor, align: int):
+    nv.require_cuda(group_lens)
+    G = group_lens.numel()
+    lens = group_lens.to(torch.int64).contiguous()
+    plens = torch.empty(G, dtype=torch.int64, device=lens.device)
+    poffs = torch.empty(G + 1, dtype=torch.int64, device=lens.device)
+    with torch.cuda.device(lens.device):
+        nv.check(nv.lib().pt_compute_padded_group_offs(nv.ptr(lens), G, align, nv.ptr(plens), nv.ptr(poffs),
+                                                        nv.stream(lens.device)), "compute_padded_group_offs")
+    return plens, poffs
+
+
+def quant_fp8_blockwise_segment_m_row_col_impl(x: torch.Tensor, dtype: torch.dtype, block_size: int,
+                                               group_lens: torch.Tensor, group_offs: torch.Tensor,
+                                               gemm_other_dim: Optional[int] = None):
+    """Returns (x_row, x_col_padded, scales_row [N/128, M], scales_col_padded, padded_lens, padded_offs)."""
+    nv.require_cuda(x, group_lens, group_offs)
+    assert x.is_contiguous() and x.dim() == 2, "Input must be 2D and contiguous"
+    assert block_size == BLOCK, "block_size must be 128"
+    M, N = x.shape
+    G = group_lens.numel()
+    plens, poffs = compute_padded_group_offs(group_lens, BLOCK)
+    m_alloc = M + G * BLOCK
+    x_row = torch.empty((M, N), dtype=dtype, device=x.device)
+    x_col = torch.empty((m_alloc, N), dtype=dtype, device=x.device)
+    s_row = torch.empty((ceil_div(N, BLOCK), M), dtype=torch.float32, device=x.device)
+    s_col = torch.empty((m_alloc // BLOCK, N), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        nv.check(nv.lib().pt_quantize_fp8_blockwise_segment_m(
+            nv.ptr(x), nv.src_code(x.dtype), M, N, G, nv.ptr(group_offs.to(torch.int64).contiguous()), nv.ptr(poffs),
+            nv.fmt_code(dtype), nv.ptr(x_row), nv.ptr(s_row), nv.ptr(x_col), nv.ptr(s_col), nv.stream(x.device)),
+            "quant_fp8_blockwise_segment_m_row_col")
+    return x_row, x_col, s_row, s_col, plens, poffs
+
+
+def _dequant_blockwise(x, scales, out_dtype, kind):
+    nv.require_cuda(x, scales)
+    x = x.contiguous()
+    B = 1 if x.dim() == 2 else x.shape[0]
+    M, N = x.shape[-2:]
+    y = torch.empty_like(x, dtype=out_dtype)
+    with torch.cuda.device(x.device):
+        nv.check(nv.lib().pt_dequantize_fp8_blockwise(nv.ptr(x), nv.fmt_code(x.dtype), nv.ptr(scales.contiguous()), kind,
+                                                       B, M, N, nv.ptr(y), nv.src_code(out_dtype), nv.stream(x.device)),
+                 "dequant_fp8_blockwise")
+    return y
+
+
+def dequant_fp8_blockwise_impl(x: torch.Tensor, scales: torch.Tensor, out_dtype: torch.dtype, axis: int,
+                               block_size: int = 128):
+    assert block_size == BLOCK
+    return _dequant_blockwise(x, scales, out_dtype, 0 if axis % 2 == 1 else 1)
+
+
+def dequant_fp8_blockwise_for_weight_impl(x: torch.Tensor, scales: torch.Tensor, out_dtype: torch.dtype,
+                                          block_size: int = 128):
+    assert block_size == BLOCK
+    return _dequant_blockwise(x, scales, out_dtype, 2)
+
+
+# ------------------------------------------------------------------------------ MX
+def _mx_quant(x, out_dtype, want_row, want_col, row_recipe, col_recipe):
+    nv.require_cuda(x)
+    for r in (row_recipe, col_recipe):
+        if r is not None and (r.shuffle_scale or r.shuffle_out):
+            raise NotImplementedError("pre-shuffled (AITER) MX layouts are not provided on B200")
+        if r is not None and r.use_sr:
+            raise NotImplementedError("stochastic rounding is not provided on B200")
+    x = x.contiguous()
+    fmt = nv.fmt_code(out_dtype)
+    fp4 = fmt == nv.PT_E2M1
+    G = 1 if x.dim() == 2 else x.shape[0]
+    M, N = x.shape[-2:]
+    M_pad, N_pad = ceil_div(M, MX_ALIGN) * MX_ALIGN, ceil_div(N, MX_ALIGN) * MX_ALIGN
+    lead = () if x.dim() == 2 else (G,)
+    div = 2 if fp4 else 1
+    flags = 0
+    q_row = s_row = q_col = s_col = None
+    if want_row:
+        flags |= nv.PT_MX_ROW | (nv.PT_MX_ROW_2D if row_recipe.use_2d_block else 0) | (nv.PT_MX_ROW_RHT if row_recipe.use_rht else 0)
+        q_row = torch.empty(lead + (M, N_pad // div), dtype=torch.uint8, device=x.device)
+        s_row = torch.empty(lead + (M, N_pad // MX_BLOCK), dtype=torch.uint8, device=x.device)
+    if want_col:
+        flags |= nv.PT_MX_COL | (nv.PT_MX_COL_2D if col_recipe.use_2d_block else 0) | (nv.PT_MX_COL_RHT if col_recipe.use_rht else 0)
+        q_col = torch.empty(lead + (N, M_pad // div), dtype=torch.uint8, device=x.device)
+        s_col = torch.empty(lead + (N, M_pad // MX_BLOCK), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        nv.check(nv.lib().pt_quantize_mx(nv.ptr(x), nv.src_code(x.dtype), G, M, N, fmt, flags, nv.ptr(q_row), nv.ptr(s_row),
+                                          nv.ptr(q_col), nv.ptr(s_col), nv.stream(x.device)), "quantize_mx")
+    view = lambda t: None if t is None else t.view(out_dtype)
+    sview = lambda t: None if t is None else t.view(torch.float8_e8m0fnu)
+    return view(q_row), sview(s_row), view(q_col), sview(s_col)
+
+
+def _quantize_mx_impl(x, out_dtype, axis, block_size, with_trans, scaling_recipe, scaling_recipe_for_trans):
+    assert block_size == MX_BLOCK, f"The block size must be {MX_BLOCK} for MX quantization"
+    scaling_recipe = ScalingRecipe() if scaling_recipe is None else scaling_recipe
+    if with_trans:
+        assert axis is None, "The axis must be None when with_trans is True."
+        scaling_recipe_for_trans = ScalingRecipe() if scaling_recipe_for_trans is None else scaling_recipe_for_trans
+        return _mx_quant(x, out_dtype, True, True, scaling_recipe, scaling_recipe_for_trans)
+    if x.ndim == 2:
+        assert axis in (0, 1), "The axis must be 0 or 1 when with_trans is False and x is 2D."
+        rowwise = axis == 1
+    elif x.ndim == 3:
+        assert axis in (1, 2), "The axis must be 1 or 2 when with_trans is False and x is 3D."
+        rowwise = axis == 2
+    else:
+        raise ValueError(f"The input tensor must be 2D or 3D but got {x.ndim}D.")
+    q_row, s_row, q_col, s_col = _mx_quant(x, out_dtype, rowwise, not rowwise, scaling_recipe, scaling_recipe)
+    return (q_row, s_row) if rowwise else (q_col, s_col)
+
+
+def quantize_mxfp8_impl(x, out_dtype, axis, block_size, with_trans=False, scaling_recipe=None,
+                        scaling_recipe_for_trans=None):
+    return _quantize_mx_impl(x, out_dtype, axis, block_size, with_trans, scaling_recipe, scaling_recipe_for_trans)
+
+
+def quantize_mxfp4_impl(x, out_dtype, axis, block_size, with_trans=False, scaling_recipe=None,
+                        scaling_recipe_for_trans=None):
+    return _quantize_mx_impl(x, out_dtype, axis, block_size, with_trans, scaling_recipe, scaling_recipe_for_trans)
+
+
+def _dequantize_mx(x, out_dtype, axis, scale_inv, orig_shape=None):
+    """x: row-wise [R, C_pad(/2)] data (axis = last) or col-wise transposed data (axis = first, 2-D).
+    Returns the dequantized tensor in the ORIGINAL orientation (col-wise inputs are re-transposed)."""
+    nv.require_cuda(x, scale_inv)
+    fmt = nv.fmt_code(x.dtype)
+    xb = x.contiguous().view(torch.uint8)
+    sb = scale_inv.contiguous().view(torch.uint8)
+    lead = xb.shape[:-2]
+    rows, stored = xb.shape[-2], xb.shape[-1] * (2 if fmt == nv.PT_E2M1 else 1)
+    transpose = axis in (0, -2) if x.dim() == 2 else axis in (1, -2)
+    cols = stored
+    if orig_shape is not None:
+        cols = orig_shape[-2] if transpose else orig_shape[-1]
+    outs = []
+    xs = xb.reshape(-1, rows, xb.shape[-1])
+    ss = sb.reshape(-1, rows, sb.shape[-1])
+    for g in range(xs.shape[0]):
+        y = torch.empty((cols, rows) if transpose else (rows, cols), dtype=out_dtype, device=x.device)
+        with torch.cuda.device(x.device):
+            nv.check(nv.lib().pt_dequantize_mx(nv.ptr(xs[g]), fmt, nv.ptr(ss[g]), rows, cols, stored, int(transpose),
+                                                nv.ptr(y), nv.src_code(out_dtype), nv.stream(x.device)), "dequantize_mx")
+        outs.append(y)
+    return outs[0] if not lead else torch.stack(outs).reshape(*lead, *outs[0].shape)
+
+
+def dequantize_mxfp8_impl(x, out_dtype, axis, block_size, scale_inv, scaling_recipe=None, orig_shape=None):
+    assert block_size == MX_BLOCK
+    return _dequantize_mx(x, out_dtype, axis, scale_inv, orig_shape)
+
+
+def dequantize_mxfp4_impl(x, out_dtype, axis, block_size, scale_inv, scaling_recipe=None, orig_shape=None):
+    assert block_size == MX_BLOCK
+    return _dequantize_mx(x, out_dtype, axis, scale_inv, orig_shape)
+
+
+def transpose_2d(x: torch.Tensor) -> torch.Tensor:
+    nv.require_cuda(x)
+    assert x.dim() == 2
+    x = x.contiguous()
+    y = torch.empty((x.shape[1], x.shape[0]), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        nv.check(nv.lib().pt_transpose_2d(nv.ptr(x), x.shape[0], x.shape[1], x.element_size(), nv.ptr(y),
+                                           nv.stream(x.device)), "transpose_2d")
+    return y

@@ -1,0 +1,131 @@
+"""Dense FP8 / MXFP8 GEMM through the C ABI against the fp32-dequantized matmul of the oracle.
+Tolerance (stated by the task): relative Frobenius error <= 1e-2 for FP8; the reference's own SNR
+gates against the unquantized product (tests/pytorch/ops/test_gemm_fp8.py:101-114) are checked too."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import gemm as og
+from oracle import quant as oq
+from tests._util import f32, fmt_of, make, u8
+
+pytestmark = pytest.mark.gpu
+
+FP8_TOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def mods():
+    from primus_turbo.pytorch.core.low_precision import ScalingGranularity, ScalingRecipe
+    from primus_turbo.pytorch.kernels import _native as nv
+    from primus_turbo.pytorch.kernels.gemm import gemm_fp8_impl as gi
+    from primus_turbo.pytorch.kernels.quantization import quantization_impl as qi
+    return qi, gi, nv, ScalingGranularity, ScalingRecipe
+
+
+def _ref(qa, sa, qb, sb, fa, fb):
+    return og.gemm_nt(oq.dequantize_fp8(qa, sa, fa), oq.dequantize_fp8(qb, sb, fb))
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 512, 256), (255, 520, 576), (507, 1024, 2048), (1000, 264, 144)])
+@pytest.mark.parametrize("fa,fb", [(torch.float8_e4m3fn, torch.float8_e4m3fn), (torch.float8_e5m2, torch.float8_e4m3fn)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_tensorwise_nt(mods, M, N, K, fa, fb, out_dtype):
+    qi, gi, nv, SG, _ = mods
+    a, b = make((M, K), torch.bfloat16, 21), make((N, K), torch.bfloat16, 22)
+    qa, sa = qi.quantize_fp8_tensorwise_impl(a, fa)
+    qb, sb = qi.quantize_fp8_tensorwise_impl(b, fb)
+    c = gi.gemm_fp8_impl(qa, sa, False, qb, sb, True, out_dtype, False, SG.TENSORWISE)
+    nv.check_status(c.device)
+    ref = _ref(u8(qa), f32(sa), u8(qb), f32(sb), fmt_of(fa), fmt_of(fb))
+    err = og.rel_frobenius(f32(c), ref)
+    assert err <= (FP8_TOL if out_dtype == torch.bfloat16 else 1e-5), err
+    if fa == torch.float8_e4m3fn:
+        assert og.snr_db(f32(c), f32(a) @ f32(b).T) > 25
+
+
+@pytest.mark.parametrize("block_n", [128, 240, 256])
+def test_tile_widths_agree(mods, block_n):
+    qi, gi, nv, SG, _ = mods
+    a, b = make((384, 512), torch.bfloat16, 23), make((1000, 512), torch.bfloat16, 24)
+    qa, sa = qi.quantize_fp8_tensorwise_impl(a, torch.float8_e4m3fn)
+    qb, sb = qi.quantize_fp8_tensorwise_impl(b, torch.float8_e4m3fn)
+    c = gi.gemm_fp8_impl(qa, sa, False, qb, sb, True, torch.float32, False, SG.TENSORWISE, block_n=block_n)
+    nv.check_status(c.device)
+    ref = _ref(u8(qa), f32(sa), u8(qb), f32(sb), "e4m3", "e4m3")
+    assert og.rel_frobenius(f32(c), ref) <= 1e-5
+
+
+@pytest.mark.parametrize("trans_a,trans_b,trans_c", [(False, False, False), (True, False, False), (False, True, True),
+                                                     (True, True, False), (False, False, True)])
+def test_tensorwise_layouts(mods, trans_a, trans_b, trans_c):
+    qi, gi, nv, SG, _ = mods
+    M, N, K = 256, 384, 512
+    a = make((K, M) if trans_a else (M, K), torch.bfloat16, 25)
+    b = make((N, K) if trans_b else (K, N), torch.bfloat16, 26)
+    qa, sa = qi.quantize_fp8_tensorwise_impl(a, torch.float8_e4m3fn)
+    qb, sb = qi.quantize_fp8_tensorwise_impl(b, torch.float8_e4m3fn)
+    c = gi.gemm_fp8_impl(qa, sa, trans_a, qb, sb, trans_b, torch.float32, trans_c, SG.TENSORWISE)
+    nv.check_status(c.device)
+    da = oq.dequantize_fp8(u8(qa), f32(sa), "e4m3")
+    db = oq.dequantize_fp8(u8(qb), f32(sb), "e4m3")
+    ref = (da.T if trans_a else da) @ (db.T if trans_b else db)
+    ref = ref.T if trans_c else ref
+    assert og.rel_frobenius(f32(c), ref) <= 1e-5
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 256), (255, 520, 576), (512, 4096, 1024)])
+def test_rowwise_nt(mods, M, N, K):
+    qi, gi, nv, SG, _ = mods
+    a, b = make((M, K), torch.bfloat16, 27, "outlier"), make((N, K), torch.bfloat16, 28, "weight")
+    qa, sa = qi.quantize_fp8_rowwise_impl(a, torch.float8_e4m3fn, -1)
+    qb, sb = qi.quantize_fp8_rowwise_impl(b, torch.float8_e4m3fn, -1)
+    c = gi.gemm_fp8_impl(qa, sa, False, qb, sb, True, torch.bfloat16, False, SG.ROWWISE)
+    nv.check_status(c.device)
+    ref = _ref(u8(qa), f32(sa), u8(qb), f32(sb), "e4m3", "e4m3")
+    assert og.rel_frobenius(f32(c), ref) <= FP8_TOL
+    assert og.snr_db(f32(c), f32(a) @ f32(b).T) > 25
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 512, 256), (255, 520, 576), (507, 1000, 2048), (2048, 4096, 1024)])
+@pytest.mark.parametrize("fa,fb", [(torch.float8_e4m3fn, torch.float8_e4m3fn), (torch.float8_e5m2, torch.float8_e4m3fn)])
+@pytest.mark.parametrize("block_n", [0, 128, 256])
+def test_mx_nt(mods, M, N, K, fa, fb, block_n):
+    qi, gi, nv, SG, SR = mods
+    a, b = make((M, K), torch.bfloat16, 29, "outlier"), make((N, K), torch.bfloat16, 30, "weight")
+    qa, sa = qi.quantize_mxfp8_impl(a, fa, 1, 32)
+    qb, sb = qi.quantize_mxfp8_impl(b, fb, 1, 32, scaling_recipe=SR(use_2d_block=True))
+    c = gi.gemm_fp8_impl(qa, sa, False, qb, sb, True, torch.float32, False, SG.MX_BLOCKWISE, block_n=block_n)
+    nv.check_status(c.device)
+    ref = og.gemm_nt(oq.dequantize_mx(u8(qa), u8(sa), fmt_of(fa)), oq.dequantize_mx(u8(qb), u8(sb), fmt_of(fb)))
+    err = og.rel_frobenius(f32(c), ref)
+    assert err <= 1e-5, err   # products and power-of-two scales are exact; only fp32 summation order differs
+    cb = gi.gemm_fp8_impl(qa, sa, False, qb, sb, True, torch.bfloat16, False, SG.MX_BLOCKWISE, block_n=block_n)
+    assert og.rel_frobenius(f32(cb), ref) <= FP8_TOL
+    if fa == torch.float8_e4m3fn:
+        assert og.snr_db(f32(cb), f32(a) @ f32(b).T) > 25
+
+
+def test_mx_deterministic(mods):
+    # tests/pytorch/ops/test_gemm_fp8.py:190-200 of the reference: repeated runs are bit-identical
+    qi, gi, nv, SG, _ = mods
+    a, b = make((512, 1024), torch.bfloat16, 31), make((768, 1024), torch.bfloat16, 32)
+    qa, sa = qi.quantize_mxfp8_impl(a, torch.float8_e4m3fn, 1, 32)
+    qb, sb = qi.quantize_mxfp8_impl(b, torch.float8_e4m3fn, 1, 32)
+    first = gi.gemm_fp8_impl(qa, sa, False, qb, sb, True, torch.bfloat16, False, SG.MX_BLOCKWISE)
+    for _ in range(9):
+        again = gi.gemm_fp8_impl(qa, sa, False, qb, sb, True, torch.bfloat16, False, SG.MX_BLOCKWISE)
+        assert torch.equal(first, again)
+    nv.check_status(first.device)
+
+
+def test_accumulate_into_out(mods):
+    qi, gi, nv, SG, _ = mods
+    a, b = make((256, 256), torch.bfloat16, 33), make((384, 256), torch.bfloat16, 34)
+    qa, sa = qi.quantize_fp8_tensorwise_impl(a, torch.float8_e4m3fn)
+    qb, sb = qi.quantize_fp8_tensorwise_impl(b, torch.float8_e4m3fn)
+    out = torch.ones(256, 384, dtype=torch.float32, device="cuda")
+    gi.gemm_fp8_accum_impl(qa, sa, False, qb, sb, True, out, False, SG.TENSORWISE)
+    nv.check_status(out.device)
+    ref = _ref(u8(qa), f32(sa), u8(qb), f32(sb), "e4m3", "e4m3") + 1.0
+    assert og.rel_frobenius(f32(out), ref) <= 1e-5
