@@ -150,13 +150,20 @@ int pt_transpose_2d(const void *x, int64_t M, int64_t N, int elem_bytes, void *y
  *   granularity PT_MX_BLOCKWISE: a_scale uint8 [M, K/32], b_scale uint8 [N, K/32] (ue8m0, raw row-major as the
  *                                quantizer writes them); K is the padded length (multiple of 128)
  * a_fmt / b_fmt: PT_E4M3 or PT_E5M2 (may differ: HYBRID).  beta: 0, or 1 to accumulate into C.
- * block_n: 0 = default tile width, else 128 / 240 / 256.  status: optional device int that receives
+ * block_n: 0 = default tile width, else 128 / 240 / 256.  workspace: device scratch of at least
+ * pt_gemm_fp8_workspace_bytes(...) bytes, 16-byte aligned (may be null when that is 0).  status: optional device int that receives
  * PT_ERR_TIMEOUT if a bounded wait inside the kernel expires (it is never written otherwise).
  * Replaces primus_turbo::gemm_fp8_impl / gemm_fp8_accum_impl (primus_turbo/pytorch/kernels/gemm/gemm_fp8_impl.py:518-593)
  * and the vendor ops hipblaslt_gemm_fp8 / ck_gemm_fp8 / turbo_gemm_fp8 (csrc/pytorch/bindings_pytorch.cpp:20-31). */
 int pt_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const void *b, const void *b_scale, int b_fmt, void *c,
-                int c_dtype, int granularity, int64_t M, int64_t N, int64_t K, float beta, int block_n, int *status,
-                void *stream);
+                int c_dtype, int granularity, int64_t M, int64_t N, int64_t K, float beta, int block_n, void *workspace,
+                size_t workspace_bytes, int *status, void *stream);
+
+/* Scratch bytes pt_gemm_fp8 / pt_grouped_gemm_fp8 need: 0 except for PT_MX_BLOCKWISE, where the raw scales are
+ * re-tiled into the block layout of the tensor core's scale copy before the GEMM (the reference's back ends also
+ * pre-shuffle the raw scales right before their kernels, primus_turbo/pytorch/ops/gemm_fp8.py:577-579).
+ * c_rows: rows of C; grouped: nonzero for the grouped entry point; block_n as passed to the GEMM. */
+size_t pt_gemm_fp8_workspace_bytes(int granularity, int64_t c_rows, int64_t N, int64_t K, int G, int grouped, int block_n);
 
 /* Grouped form: rows are split into G groups, group g multiplies B[g] ([G, N, K] contiguous).
  * group_offs_write int64 [G+1]: first C row of each group (tight); group length = difference.
@@ -168,7 +175,26 @@ int pt_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const void *b, co
 int pt_grouped_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const void *b, const void *b_scale, int b_fmt,
                         void *c, int c_dtype, int granularity, int64_t a_rows, int64_t c_rows, int64_t N, int64_t K,
                         const int64_t *group_offs_read, const int64_t *group_offs_write, int G, float beta, int block_n,
-                        int max_ctas, int *status, void *stream);
+                        int max_ctas, void *workspace, size_t workspace_bytes, int *status, void *stream);
+
+/* FP8 GEMM with fp32 128-block scales along K (BLOCKWISE granularity), dense (G = 1, offsets null) or grouped:
+ *   C[m, n] = sum_kb ( sum_{k in kb} A[m, k] B[n, k] ) * sa(m, kb) * sb(n, kb),   kb = 128-wide K block.
+ * A [a_rows, K] and B [G, N, K] are K-major FP8 bytes.  Each scale operand is read in place through
+ *   s(row, kb) = base[(row >> shift) * row_stride + kb * kb_stride]   (+ g * sb_group_stride for B),
+ * shift 0 = one scale per row, 7 = one per 128 rows, which covers every layout the reference's quantizers
+ * emit: [M, K/128] (shift 0, K/128, 1); transposed [K/128, M] (0, 1, M); column scales of a transposed
+ * operand [Kc/128, R] (0, 1, R); 128 x 128 weight tiles [N/128, K/128] (7, K/128, 1) or, for the transposed
+ * weight, (7, 1, R/128).  Group offsets as in pt_grouped_gemm_fp8.
+ * Replaces the BLOCKWISE branch of primus_turbo::gemm_fp8_impl, primus_turbo::grouped_gemm_fp8_impl and, with
+ * per-group K segments handled by the caller, grouped_gemm_fp8_variable_k_impl
+ * (primus_turbo/triton/gemm/gemm_fp8_kernel.py:872-1013,
+ *  primus_turbo/triton/grouped_gemm/grouped_gemm_fp8_kernel.py:1407-1556). */
+int pt_grouped_gemm_fp8_blockwise(const void *a, int a_fmt, const float *sa, int sa_shift, int64_t sa_row_stride,
+                                  int64_t sa_kb_stride, const void *b, int b_fmt, const float *sb, int sb_shift,
+                                  int64_t sb_row_stride, int64_t sb_kb_stride, int64_t sb_group_stride, void *c, int c_dtype,
+                                  int64_t a_rows, int64_t c_rows, int64_t N, int64_t K, const int64_t *group_offs_read,
+                                  const int64_t *group_offs_write, int G, float beta, int max_ctas, int *status,
+                                  void *stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,78 @@
+// Pieces shared by the tcgen05 GEMM kernels: tile geometry, the group-aware tile walk, output packing
+// and the host-side construction of TMA tensor maps.
+#pragma once
+#include <mutex>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace ptb {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 128;  // bytes == fp8 elements per stage row
+constexpr int UMMA_K = 32;    // fp8 elements per tcgen05.mma
+constexpr int kMaxGroups = 1024;
+
+// Tile walk shared by every role: tiles are numbered group by group, rows (m) fastest inside a group.
+struct TileWalk {
+    const int *tile_start;  // shared memory [G+1]
+    int G, num_n_blocks;
+    int g;
+    __device__ __forceinline__ bool locate(int t, int &g_out, int &m_blk, int &n_blk) {
+        if (t >= tile_start[G]) return false;
+        while (t >= tile_start[g + 1]) ++g;
+        const int local = t - tile_start[g];
+        const int m_blocks = (tile_start[g + 1] - tile_start[g]) / num_n_blocks;
+        g_out = g;
+        m_blk = local % m_blocks;
+        n_blk = local / m_blocks;
+        return true;
+    }
+};
+
+template <typename OutT> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// 2-D byte tensor [rows, row_bytes] (pitch `pitch_bytes`), box = 128 bytes x box_rows, 128-byte swizzle.
+inline int make_tmap_bytes(CUtensorMap *m, const void *base, int64_t rows, int64_t row_bytes, int64_t pitch_bytes, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return set_error(PT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    PT_REQUIRE(aligned(base, 16) && pitch_bytes % 16 == 0, "GEMM operand base / row pitch must be 16-byte aligned");
+    cuuint64_t dims[2] = {(cuuint64_t) row_bytes, (cuuint64_t) rows};
+    cuuint64_t strides[1] = {(cuuint64_t) pitch_bytes};
+    cuuint32_t box[2] = {128u, (cuuint32_t) box_rows};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(PT_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int) r);
+    return PT_OK;
+}
+
+
+}  // namespace ptb

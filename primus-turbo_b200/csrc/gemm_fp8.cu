@@ -5,9 +5,11 @@
 //   warp 0      TMA producer: A (128 x 128 B) and B (BLOCK_N x 128 B) tiles, 128-byte swizzle, into a ring
 //   warp 1      MMA issuer (one elected lane): tcgen05.mma kind::f8f6f4 or kind::mxf8f6f4.block_scale;
 //               owns the TMEM allocation
-//   warps 2-5   MX only: bring the raw row-major ue8m0 scales [rows, K/32] into the 32 x 16 B block layout
-//               tcgen05.cp expects, one 128-row block per 128-K step
-//   warps 6-9   epilogue: TMEM -> registers -> (scales) -> staging in shared memory -> coalesced global stores
+//   warps 2-5   epilogue: TMEM -> registers -> (scales) -> staging in shared memory -> coalesced global stores
+// MX scales: the quantizers emit raw row-major ue8m0 bytes [rows, K/32]; a small pre-pass (sf_retile_kernel)
+// re-tiles them per 128-row block and 128-K step into the 32 x 16-byte block layout tcgen05.cp expects, so the
+// producer can fetch each block with one bulk copy next to the operand tiles (gathering them with ordinary loads
+// inside the GEMM cost 20 % of its throughput).
 // The accumulator is double buffered in TMEM when 2 * BLOCK_N (+ scale columns) fits in 512 columns, so the
 // epilogue of tile i overlaps the main loop of tile i + 1.
 //
@@ -22,20 +24,15 @@
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
+#include "gemm_common.cuh"
 
 namespace ptb {
 using namespace sm100;
 
-constexpr int BLOCK_M = 128;
-constexpr int BLOCK_K = 128;  // bytes == fp8 elements per stage row
-constexpr int UMMA_K = 32;    // fp8 elements per tcgen05.mma
-constexpr int kNumSfWarps = 4;
 constexpr int kNumEpiWarps = 4;
-constexpr int kGemmThreads = 32 * (2 + kNumSfWarps + kNumEpiWarps);
-constexpr int kSfWarp0 = 2;
-constexpr int kEpiWarp0 = 2 + kNumSfWarps;
+constexpr int kGemmThreads = 32 * (2 + kNumEpiWarps);
+constexpr int kEpiWarp0 = 2;
 constexpr int kStagePitchMax = 128 + 16;  // staging row pitch (bytes) of the epilogue, fp32 worst case
-constexpr int kMaxGroups = 1024;
 
 enum GemmMode { GEMM_TENSOR = 0, GEMM_ROW = 1, GEMM_MX = 3 };
 
@@ -48,8 +45,7 @@ struct GemmParams {
     int vec_store_ok;
     float beta;            // 0 or 1 (C += ...)
     const float *sa, *sb;  // fp32 scales (tensorwise / rowwise)
-    const uint8_t *sfa, *sfb;  // ue8m0 scales (MX), row pitch sf_ld bytes
-    int64_t sf_ld;
+    const uint8_t *sfa_tiled, *sfb_tiled;  // MX scales re-tiled by sf_retile_kernel: 512-byte blocks [row block][K step]
     int a_fmt, b_fmt;      // 0 = e4m3, 1 = e5m2
     // grouping: null offsets = one group covering [0, M)
     const int64_t *offs_read;   // [G+1] first A row of each group (layout A was written in)
@@ -61,7 +57,8 @@ struct GemmParams {
 
 template <int BLOCK_N, bool MX> struct GemmCfg {
     static constexpr int kSfbBlocks = (BLOCK_N + 127) / 128;
-    static constexpr int kSfCols = MX ? 4 + 4 * kSfbBlocks : 0;
+    static constexpr int kSfColsOne = 4 + 4 * kSfbBlocks;       // SFA block + SFB blocks of one K step
+    static constexpr int kSfCols = MX ? 2 * kSfColsOne : 0;         // double buffered so tcgen05.cp of step i+1 need not wait for step i
     static constexpr int kAccStages = (2 * BLOCK_N + kSfCols <= 512) ? 2 : 1;
     static constexpr int kTmemColsNeeded = kAccStages * BLOCK_N + kSfCols;
     static constexpr int kTmemCols = kTmemColsNeeded <= 32 ? 32 : kTmemColsNeeded <= 64 ? 64 : kTmemColsNeeded <= 128 ? 128
@@ -80,31 +77,74 @@ template <int BLOCK_N, bool MX> struct GemmCfg {
     static_assert(kBBytes % 1024 == 0, "B stage must keep 1024-byte alignment");
 };
 
-// Tile walk shared by every role: tiles are numbered group by group, rows (m) fastest inside a group.
-struct TileWalk {
-    const int *tile_start;  // shared memory [G+1]
-    int G, num_n_blocks;
-    int g;
-    __device__ __forceinline__ bool locate(int t, int &g_out, int &m_blk, int &n_blk) {
-        if (t >= tile_start[G]) return false;
-        while (t >= tile_start[g + 1]) ++g;
-        const int local = t - tile_start[g];
-        const int m_blocks = (tile_start[g + 1] - tile_start[g]) / num_n_blocks;
-        g_out = g;
-        m_blk = local % m_blocks;
-        n_blk = local / m_blocks;
-        return true;
-    }
+
+// ------------------------------------------------------------------------------------------------ scale re-tiling
+// Raw ue8m0 scales [rows, K/32] -> 512-byte blocks dst[(rb * num_kb + kb) * 512 + (r % 32) * 16 + (r / 32) * 4 + i],
+// r = row inside row block rb, i = which 32-wide slice of K step kb.  Row blocks follow the GEMM's tiles:
+//   A side (is_b == 0): group by group, block m of group g starts at offs_read[g] + 128 m;
+//   B side (is_b == 1): tile (g, n) has `sfb_blocks` blocks starting at g * b_group_rows + n * block_n + 128 j.
+struct RetileArgs {
+    const uint8_t *src;
+    uint8_t *dst;
+    int64_t src_rows, sf_ld;  // rows of src, bytes per row (K / 32)
+    int num_kb, is_b;
+    const int64_t *offs_read, *offs_write;
+    int G;
+    int64_t M;
+    int block_n, sfb_blocks, num_n_blocks;
+    int64_t b_group_rows;
+    int64_t num_row_blocks;  // upper bound
 };
 
-template <typename OutT> __device__ __forceinline__ uint32_t pack2(float a, float b);
-template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t *>(&h);
-}
-template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
-    __half2 h = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t *>(&h);
+__global__ void __launch_bounds__(128) sf_retile_kernel(RetileArgs a) {
+    __shared__ uint32_t s_words[128][33];
+    __shared__ int s_start[kMaxGroups + 1];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (!a.is_b) {
+        if (tid == 0) {
+            int acc = 0;
+            s_start[0] = 0;
+            for (int g = 0; g < a.G; ++g) {
+                const int64_t len = a.offs_write ? (a.offs_write[g + 1] - a.offs_write[g]) : a.M;
+                acc += (int) ((len + BLOCK_M - 1) / BLOCK_M);
+                s_start[g + 1] = acc;
+            }
+        }
+        __syncthreads();
+    }
+    const int kb0 = blockIdx.y * 32;
+    const int nkb = min(32, a.num_kb - kb0);
+    int g = 0;
+    for (int64_t rb = blockIdx.x; rb < a.num_row_blocks; rb += gridDim.x) {
+        int64_t row_start;
+        int rows_in_block = 128;
+        if (a.is_b) {
+            const int64_t tile = rb / a.sfb_blocks;
+            const int j = (int) (rb % a.sfb_blocks);
+            const int64_t gg = tile / a.num_n_blocks, n_blk = tile % a.num_n_blocks;
+            row_start = gg * a.b_group_rows + n_blk * a.block_n + 128 * j;
+            rows_in_block = min(128, a.block_n - 128 * j);
+        } else {
+            if (rb >= s_start[a.G]) break;
+            while (rb >= s_start[g + 1]) ++g;
+            row_start = (a.offs_read ? a.offs_read[g] : 0) + (rb - s_start[g]) * 128;
+        }
+        // coalesced read: one warp per row, lane = K step
+        for (int r = warp; r < 128; r += 4) {
+            const int64_t row = row_start + r;
+            uint32_t w = 0;
+            if (r < rows_in_block && row < a.src_rows && lane < nkb)
+                w = __ldg(reinterpret_cast<const uint32_t *>(a.src + row * a.sf_ld) + kb0 + lane);
+            s_words[r][lane] = w;
+        }
+        __syncthreads();
+        // each warp writes whole 512-byte blocks: lane l carries rows l, l+32, l+64, l+96
+        for (int kb = warp; kb < nkb; kb += 4) {
+            const uint4 v = make_uint4(s_words[lane][kb], s_words[lane + 32][kb], s_words[lane + 64][kb], s_words[lane + 96][kb]);
+            *reinterpret_cast<uint4 *>(a.dst + (rb * a.num_kb + kb0 + kb) * 512 + lane * 16) = v;
+        }
+        __syncthreads();
+    }
 }
 
 template <int BLOCK_N, int MODE>
@@ -147,7 +187,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         *abort_flag = 0;
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(&full_bar[s], MX ? 1 + kNumSfWarps * 32 : 1);
+            mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
         for (int s = 0; s < kAccStages; ++s) {
@@ -180,11 +220,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
                 const int64_t a_row0 = (p.offs_read ? p.offs_read[gi] : 0) + (int64_t) m_blk * BLOCK_M;
                 const int64_t b_row0 = (int64_t) gi * p.b_group_rows + (int64_t) n_blk * BLOCK_N;
+                // scale blocks of this tile: A row block = running count of 128-row blocks over the groups
+                const uint8_t *sfa_blk = nullptr, *sfb_blk = nullptr;
+                if constexpr (MX) {
+                    const int64_t a_rb = s_tile_start[gi] / num_n_blocks + m_blk;
+                    const int64_t b_rb = ((int64_t) gi * num_n_blocks + n_blk) * Cfg::kSfbBlocks;
+                    sfa_blk = p.sfa_tiled + a_rb * num_k_blocks * 512;
+                    sfb_blk = p.sfb_tiled + b_rb * num_k_blocks * 512;
+                }
                 for (int kb = 0; kb < num_k_blocks; ++kb) {
                     if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
-                    mbar_arrive_expect_tx(&full_bar[stage], Cfg::kABytes + Cfg::kBBytes);
+                    mbar_arrive_expect_tx(&full_bar[stage], Cfg::kABytes + Cfg::kBBytes + Cfg::kSfBytes);
                     tma_load_2d(smem_a + stage * Cfg::kABytes, &tmap_a, &full_bar[stage], kb * BLOCK_K, (int) a_row0);
                     tma_load_2d(smem_b + stage * Cfg::kBBytes, &tmap_b, &full_bar[stage], kb * BLOCK_K, (int) b_row0);
+                    if constexpr (MX) {
+                        uint8_t *sf = smem_sf + stage * Cfg::kSfBytes;
+                        bulk_load(sf, sfa_blk + (int64_t) kb * 512, 512, &full_bar[stage]);
+#pragma unroll
+                        for (int j = 0; j < Cfg::kSfbBlocks; ++j)
+                            bulk_load(sf + 512 * (1 + j), sfb_blk + ((int64_t) j * num_k_blocks + kb) * 512, 512, &full_bar[stage]);
+                    }
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
             }
@@ -196,7 +251,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             (void) kIdescPlainShape;
             const uint32_t idesc = MX ? idesc_block_scaled(p.a_fmt, p.b_fmt, BLOCK_M, BLOCK_N)
                                       : idesc_f8(p.a_fmt, p.b_fmt, BLOCK_M, BLOCK_N);
-            uint32_t stage = 0, phase = 0, acc_stage = 0, acc_phase = 0;
+            uint32_t stage = 0, phase = 0, acc_stage = 0, acc_phase = 0, sf_buf = 0;
             for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
                 if (!(ok = mbar_wait(&tmem_empty_bar[acc_stage], acc_phase ^ 1, abort_flag))) break;
                 tc_fence_after_sync();
@@ -204,11 +259,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 for (int kb = 0; kb < num_k_blocks; ++kb) {
                     if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
                     tc_fence_after_sync();
+                    const uint32_t sfa_cur = tmem_sfa + sf_buf * Cfg::kSfColsOne;
+                    const uint32_t sfb_cur = tmem_sfb + sf_buf * Cfg::kSfColsOne;
                     if constexpr (MX) {
                         const uint32_t sf_addr = smem_u32(smem_sf + stage * Cfg::kSfBytes);
-                        tc_cp_sf(tmem_sfa, smem_desc_sf(sf_addr));
+                        tc_cp_sf(sfa_cur, smem_desc_sf(sf_addr));
 #pragma unroll
-                        for (int j = 0; j < Cfg::kSfbBlocks; ++j) tc_cp_sf(tmem_sfb + 4 * j, smem_desc_sf(sf_addr + 512 * (1 + j)));
+                        for (int j = 0; j < Cfg::kSfbBlocks; ++j) tc_cp_sf(sfb_cur + 4 * j, smem_desc_sf(sf_addr + 512 * (1 + j)));
+                        sf_buf ^= 1;
                     }
                     const uint64_t a_desc = smem_desc_sw128(smem_u32(smem_a + stage * Cfg::kABytes));
                     const uint64_t b_desc = smem_desc_sw128(smem_u32(smem_b + stage * Cfg::kBBytes));
@@ -217,7 +275,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                         const uint64_t adv = (uint64_t) ((k * UMMA_K) >> 4);
                         const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
                         if constexpr (MX)
-                            mma_mxf8(d_tmem, a_desc + adv, b_desc + adv, idesc_sf_ids(idesc, k, k), tmem_sfa, tmem_sfb, accumulate);
+                            mma_mxf8(d_tmem, a_desc + adv, b_desc + adv, idesc_sf_ids(idesc, k, k), sfa_cur, sfb_cur, accumulate);
                         else
                             mma_f8(d_tmem, a_desc + adv, b_desc + adv, idesc, accumulate);
                     }
@@ -227,52 +285,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 if (!ok) break;
                 tc_commit(&tmem_full_bar[acc_stage]);
                 if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1; }
-            }
-        }
-    } else if (warp < kEpiWarp0) {
-        // ================================================================ scale-factor loaders (MX only)
-        if constexpr (MX) {
-            const int r = (warp - kSfWarp0) * 32 + lane;  // 0..127: row inside a 128-row block
-            const int slot = (r & 31) * 16 + (r >> 5) * 4;  // byte offset inside the 32 x 16 B block
-            uint32_t stage = 0, phase = 0;
-            for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
-                const int64_t a_row0 = (p.offs_read ? p.offs_read[gi] : 0) + (int64_t) m_blk * BLOCK_M;
-                const int64_t a_rows_end = p.offs_read ? p.offs_read[G] : p.M;
-                const int64_t b_row0 = (int64_t) gi * p.b_group_rows + (int64_t) n_blk * BLOCK_N;
-                const int64_t b_rows_end = (int64_t) G * p.b_group_rows;
-                const bool a_ok = a_row0 + r < a_rows_end;
-                const uint8_t *pa = p.sfa + (a_row0 + r) * p.sf_ld;
-                const uint8_t *pb[Cfg::kSfbBlocks];
-                bool b_ok[Cfg::kSfbBlocks];
-#pragma unroll
-                for (int j = 0; j < Cfg::kSfbBlocks; ++j) {
-                    b_ok[j] = (128 * j + r < BLOCK_N) && (b_row0 + 128 * j + r < b_rows_end);
-                    pb[j] = p.sfb + (b_row0 + 128 * j + r) * p.sf_ld;
-                }
-                // scales of 4 consecutive K blocks are fetched together (one step ahead of their use)
-                for (int kb0 = 0; kb0 < num_k_blocks && ok; kb0 += 4) {
-                    uint32_t wa[4], wb[Cfg::kSfbBlocks][4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const bool in = kb0 + u < num_k_blocks;
-                        wa[u] = (in && a_ok) ? __ldg(reinterpret_cast<const uint32_t *>(pa) + kb0 + u) : 0u;
-#pragma unroll
-                        for (int j = 0; j < Cfg::kSfbBlocks; ++j)
-                            wb[j][u] = (in && b_ok[j]) ? __ldg(reinterpret_cast<const uint32_t *>(pb[j]) + kb0 + u) : 0u;
-                    }
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        if (kb0 + u >= num_k_blocks) break;
-                        if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
-                        uint8_t *sf = smem_sf + stage * Cfg::kSfBytes;
-                        *reinterpret_cast<uint32_t *>(sf + slot) = wa[u];
-#pragma unroll
-                        for (int j = 0; j < Cfg::kSfbBlocks; ++j) *reinterpret_cast<uint32_t *>(sf + 512 * (1 + j) + slot) = wb[j][u];
-                        fence_proxy_async_smem();  // generic-proxy stores must be visible to tcgen05.cp
-                        mbar_arrive(&full_bar[stage]);
-                        if (++stage == kStages) { stage = 0; phase ^= 1; }
-                    }
-                }
             }
         }
     } else {
@@ -389,43 +401,47 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 }
 
 // ------------------------------------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+struct MxScales {
+    const uint8_t *sfa, *sfb;  // raw [rows, K/32]
+    void *workspace;
+    size_t workspace_bytes;
+};
 
-static EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    return fn;
-}
-
-// 2-D byte tensor [rows, row_bytes] (pitch `pitch_bytes`), box = 128 bytes x box_rows, 128-byte swizzle.
-static int make_tmap_bytes(CUtensorMap *m, const void *base, int64_t rows, int64_t row_bytes, int64_t pitch_bytes, int box_rows) {
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (!fn) return set_error(PT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-    PT_REQUIRE(aligned(base, 16) && pitch_bytes % 16 == 0, "GEMM operand base / row pitch must be 16-byte aligned");
-    cuuint64_t dims[2] = {(cuuint64_t) row_bytes, (cuuint64_t) rows};
-    cuuint64_t strides[1] = {(cuuint64_t) pitch_bytes};
-    cuuint32_t box[2] = {128u, (cuuint32_t) box_rows};
-    cuuint32_t estr[2] = {1u, 1u};
-    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return set_error(PT_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int) r);
-    return PT_OK;
+static size_t mx_workspace_bytes(int64_t c_rows, int64_t N, int64_t K, int G, bool grouped, int block_n) {
+    const int64_t num_kb = ceil_div(K, BLOCK_K);
+    const int64_t ra = ceil_div(c_rows, BLOCK_M) + (grouped ? G : 0);
+    const int64_t rb = (int64_t) G * ceil_div(N, block_n) * ceil_div(block_n, 128);
+    return (size_t) ((ra + rb) * num_kb * 512);
 }
 
 template <int BLOCK_N, int MODE>
-static int launch_gemm(const void *a, int64_t a_rows, const void *b, int64_t b_rows, const GemmParams &p, int max_ctas,
-                       int64_t max_tiles, cudaStream_t st) {
+static int launch_gemm(const void *a, int64_t a_rows, const void *b, int64_t b_rows, GemmParams p, const MxScales &mx,
+                       int max_ctas, int64_t max_tiles, cudaStream_t st) {
     using Cfg = GemmCfg<BLOCK_N, MODE == GEMM_MX>;
+    if constexpr (MODE == GEMM_MX) {
+        const bool grouped = p.offs_write != nullptr;
+        const size_t need = mx_workspace_bytes(p.M, p.N, p.K, p.G, grouped, BLOCK_N);
+        PT_REQUIRE(mx.workspace && mx.workspace_bytes >= need && aligned(mx.workspace, 16),
+                   "MX GEMM: workspace of %zu bytes (16-byte aligned) required, got %zu", need, mx.workspace_bytes);
+        const int num_kb = (int) ceil_div(p.K, BLOCK_K);
+        RetileArgs ra{};
+        ra.src = mx.sfa; ra.dst = (uint8_t *) mx.workspace; ra.src_rows = a_rows; ra.sf_ld = p.K / 32; ra.num_kb = num_kb;
+        ra.is_b = 0; ra.offs_read = p.offs_read; ra.offs_write = p.offs_write; ra.G = p.G; ra.M = p.M;
+        ra.num_row_blocks = ceil_div(p.M, BLOCK_M) + (grouped ? p.G : 0);
+        RetileArgs rb = ra;
+        rb.src = mx.sfb; rb.dst = ra.dst + ra.num_row_blocks * num_kb * 512; rb.src_rows = b_rows; rb.is_b = 1;
+        rb.block_n = BLOCK_N; rb.sfb_blocks = Cfg::kSfbBlocks; rb.num_n_blocks = (int) ceil_div(p.N, BLOCK_N);
+        rb.b_group_rows = p.b_group_rows; rb.num_row_blocks = (int64_t) p.G * rb.num_n_blocks * Cfg::kSfbBlocks;
+        const int max_blocks = sm_count() * 8;
+        dim3 ga((unsigned) std::min<int64_t>(ra.num_row_blocks, max_blocks), (unsigned) ceil_div(num_kb, 32));
+        dim3 gb((unsigned) std::min<int64_t>(rb.num_row_blocks, max_blocks), (unsigned) ceil_div(num_kb, 32));
+        sf_retile_kernel<<<ga, 128, 0, st>>>(ra);
+        PT_LAUNCH_OK();
+        sf_retile_kernel<<<gb, 128, 0, st>>>(rb);
+        PT_LAUNCH_OK();
+        p.sfa_tiled = ra.dst;
+        p.sfb_tiled = rb.dst;
+    }
     CUtensorMap ta, tb;
     int rc;
     if ((rc = make_tmap_bytes(&ta, a, a_rows, p.K, p.K, BLOCK_M)) != PT_OK) return rc;
@@ -444,17 +460,19 @@ static int launch_gemm(const void *a, int64_t a_rows, const void *b, int64_t b_r
     return PT_OK;
 }
 
+static int default_block_n(int mode, int64_t N) { return N <= 128 ? 128 : (mode == GEMM_MX ? 240 : 256); }
+
 template <int MODE>
 static int dispatch_block_n(int block_n, const void *a, int64_t a_rows, const void *b, int64_t b_rows, const GemmParams &p,
-                            int max_ctas, cudaStream_t st) {
+                            const MxScales &mx, int max_ctas, cudaStream_t st) {
     // upper bound on tiles: every group may add one partial row block
     const int64_t m_blocks_bound = ceil_div(p.M, BLOCK_M) + (p.offs_write ? p.G : 0);
-    if (block_n == 0) block_n = p.N <= 128 ? 128 : (MODE == GEMM_MX ? 240 : 256);
+    if (block_n == 0) block_n = default_block_n(MODE, p.N);
     const int64_t tiles = m_blocks_bound * ceil_div(p.N, block_n);
     switch (block_n) {
-    case 128: return launch_gemm<128, MODE>(a, a_rows, b, b_rows, p, max_ctas, tiles, st);
-    case 240: return launch_gemm<240, MODE>(a, a_rows, b, b_rows, p, max_ctas, tiles, st);
-    case 256: return launch_gemm<256, MODE>(a, a_rows, b, b_rows, p, max_ctas, tiles, st);
+    case 128: return launch_gemm<128, MODE>(a, a_rows, b, b_rows, p, mx, max_ctas, tiles, st);
+    case 240: return launch_gemm<240, MODE>(a, a_rows, b, b_rows, p, mx, max_ctas, tiles, st);
+    case 256: return launch_gemm<256, MODE>(a, a_rows, b, b_rows, p, mx, max_ctas, tiles, st);
     default: return set_error(PT_ERR_INVALID, "GEMM: BLOCK_N %d is not built (128, 240, 256)", block_n);
     }
 }
@@ -462,7 +480,7 @@ static int dispatch_block_n(int block_n, const void *a, int64_t a_rows, const vo
 int gemm_fp8_host(const void *a, const void *a_scale, int a_fmt, const void *b, const void *b_scale, int b_fmt, void *c,
                   int c_dtype, int64_t ldc, int granularity, int64_t M, int64_t N, int64_t K, float beta,
                   const int64_t *offs_read, const int64_t *offs_write, int G, int64_t a_rows_total, int block_n,
-                  int max_ctas, int *status, void *stream) {
+                  int max_ctas, void *workspace, size_t workspace_bytes, int *status, void *stream) {
     PT_REQUIRE(M >= 0 && N >= 0 && K >= 0 && G >= 1 && G <= kMaxGroups, "GEMM: bad shape (M=%lld N=%lld K=%lld G=%d)",
                (long long) M, (long long) N, (long long) K, G);
     PT_REQUIRE(a_fmt == PT_E4M3 || a_fmt == PT_E5M2, "GEMM: A format must be e4m3 or e5m2");
@@ -484,18 +502,19 @@ int gemm_fp8_host(const void *a, const void *a_scale, int a_fmt, const void *b, 
     p.status = status;
     cudaStream_t st = (cudaStream_t) stream;
     const int64_t b_rows = (int64_t) G * N;
+    MxScales mx{nullptr, nullptr, workspace, workspace_bytes};
     switch (granularity) {
     case PT_TENSORWISE:
         p.sa = (const float *) a_scale; p.sb = (const float *) b_scale;
-        return dispatch_block_n<GEMM_TENSOR>(block_n, a, a_rows_total, b, b_rows, p, max_ctas, st);
+        return dispatch_block_n<GEMM_TENSOR>(block_n, a, a_rows_total, b, b_rows, p, mx, max_ctas, st);
     case PT_ROWWISE:
         p.sa = (const float *) a_scale; p.sb = (const float *) b_scale;
-        return dispatch_block_n<GEMM_ROW>(block_n, a, a_rows_total, b, b_rows, p, max_ctas, st);
+        return dispatch_block_n<GEMM_ROW>(block_n, a, a_rows_total, b, b_rows, p, mx, max_ctas, st);
     case PT_MX_BLOCKWISE:
         PT_REQUIRE(K % 128 == 0, "MX GEMM: K must be padded to a multiple of 128 (got %lld)", (long long) K);
-        p.sfa = (const uint8_t *) a_scale; p.sfb = (const uint8_t *) b_scale; p.sf_ld = K / 32;
+        mx.sfa = (const uint8_t *) a_scale; mx.sfb = (const uint8_t *) b_scale;
         PT_REQUIRE(aligned(a_scale, 4) && aligned(b_scale, 4), "MX GEMM: scale pointers must be 4-byte aligned");
-        return dispatch_block_n<GEMM_MX>(block_n, a, a_rows_total, b, b_rows, p, max_ctas, st);
+        return dispatch_block_n<GEMM_MX>(block_n, a, a_rows_total, b, b_rows, p, mx, max_ctas, st);
     default:
         return set_error(PT_ERR_UNSUPPORTED, "GEMM: granularity %d is not handled by this kernel", granularity);
     }
@@ -507,20 +526,27 @@ using namespace ptb;
 
 extern "C" {
 
+size_t pt_gemm_fp8_workspace_bytes(int granularity, int64_t c_rows, int64_t N, int64_t K, int G, int grouped, int block_n) {
+    if (granularity != PT_MX_BLOCKWISE || c_rows <= 0 || N <= 0 || K <= 0 || G < 1) return 0;
+    if (block_n == 0) block_n = default_block_n(GEMM_MX, N);
+    return mx_workspace_bytes(c_rows, N, K, G, grouped != 0, block_n);
+}
+
 int pt_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const void *b, const void *b_scale, int b_fmt, void *c,
-                int c_dtype, int granularity, int64_t M, int64_t N, int64_t K, float beta, int block_n, int *status,
-                void *stream) {
+                int c_dtype, int granularity, int64_t M, int64_t N, int64_t K, float beta, int block_n, void *workspace,
+                size_t workspace_bytes, int *status, void *stream) {
     return gemm_fp8_host(a, a_scale, a_fmt, b, b_scale, b_fmt, c, c_dtype, N, granularity, M, N, K, beta, nullptr, nullptr,
-                         1, M, block_n, 0, status, stream);
+                         1, M, block_n, 0, workspace, workspace_bytes, status, stream);
 }
 
 int pt_grouped_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const void *b, const void *b_scale, int b_fmt,
                         void *c, int c_dtype, int granularity, int64_t a_rows, int64_t c_rows, int64_t N, int64_t K,
                         const int64_t *group_offs_read, const int64_t *group_offs_write, int G, float beta, int block_n,
-                        int max_ctas, int *status, void *stream) {
+                        int max_ctas, void *workspace, size_t workspace_bytes, int *status, void *stream) {
     PT_REQUIRE(group_offs_write, "grouped GEMM: group offsets required");
     return gemm_fp8_host(a, a_scale, a_fmt, b, b_scale, b_fmt, c, c_dtype, N, granularity, c_rows, N, K, beta,
-                         group_offs_read, group_offs_write, G, a_rows, block_n, max_ctas, status, stream);
+                         group_offs_read, group_offs_write, G, a_rows, block_n, max_ctas, workspace, workspace_bytes, status,
+                         stream);
 }
 
 }  // extern "C"

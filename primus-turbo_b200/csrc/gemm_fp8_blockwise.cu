@@ -1,0 +1,340 @@
+// FP8 GEMM with fp32 block scales (128-element blocks along K), dense and grouped:
+//   C[m, n] = sum over K blocks kb of ( sum_{k in kb} A[m, k] * B[n, k] ) * sa(m, kb) * sb(n, kb)
+// which is the accumulation order of the reference kernel
+// (primus_turbo/triton/gemm/gemm_fp8_kernel.py:872-1013; grouped:
+// primus_turbo/triton/grouped_gemm/grouped_gemm_fp8_kernel.py:1407-1556, 1661-1802).
+//
+// The tensor core has no fp32 block scaling, so accumulation is done on two levels: tcgen05.mma sums one
+// 128-wide K block into a TMEM buffer (two buffers, ping-pong), and eight "promotion" warps read each finished
+// block out of TMEM, multiply by the two scales and add into fp32 register accumulators while the tensor core
+// is already working on the next block.  Tile 128 x 256: each promotion warp owns 32 rows x 128 columns.
+//
+//   warp 0       TMA producer (A 128 x 128 B, B 256 x 128 B per stage, 128-byte swizzle)
+//   warp 1       MMA issuer, owns TMEM (512 columns = 2 partial buffers x 256)
+//   warps 2-9    promotion + epilogue
+//
+// Scales are addressed through a small descriptor so that every layout the reference produces is read in
+// place: s(row, kb) = base[(row >> shift) * row_stride + kb * kb_stride]  (shift 0: per row, shift 7: per 128 rows).
+#include <algorithm>
+
+#include "gemm_common.cuh"
+
+namespace ptb {
+using namespace sm100;
+
+constexpr int BW_BLOCK_N = 256;
+constexpr int kBwPromoWarps = 8;
+constexpr int kBwThreads = 32 * (2 + kBwPromoWarps);
+constexpr int kBwStagePitch = 64 + 16;  // staging row: 32 x 16-bit or 16 x fp32 columns, padded
+constexpr int kBwABytes = BLOCK_M * BLOCK_K;
+constexpr int kBwBBytes = BW_BLOCK_N * BLOCK_K;
+constexpr int kBwStages = 4;
+constexpr int kBwEpiBytes = kBwPromoWarps * 32 * kBwStagePitch;
+constexpr int kBwSmemBytes = kBwStages * (kBwABytes + kBwBBytes) + kBwEpiBytes + 1024 + 1024;
+
+struct ScaleDesc {
+    const float *base;
+    int shift;            // 0: one scale per row, 7: one per 128 rows
+    int64_t row_stride;   // elements
+    int64_t kb_stride;    // elements between consecutive K blocks
+    int64_t group_stride; // elements between groups (B side of grouped GEMMs), else 0
+};
+
+struct BwParams {
+    int64_t M;
+    int N, K;
+    void *C;
+    int64_t ldc;
+    int c_dtype, vec_store_ok;
+    float beta;
+    ScaleDesc sa, sb;
+    int a_fmt, b_fmt;
+    const int64_t *offs_read, *offs_write;
+    int G;
+    int64_t b_group_rows;
+    int64_t a_rows_total;
+    int *status;
+};
+
+// Writes one warp's 32 x 128 fp32 accumulators (one row per lane) to C through a padded staging buffer so
+// that global stores are 64-byte row segments; rows / columns outside the group or the matrix are skipped.
+template <typename OutT>
+__device__ __forceinline__ void bw_store_tile(const float (&acc)[128], uint8_t *stg, int lane, int64_t tile_row0,
+                                              int64_t c_row_end, int n0, int n_end, const BwParams &p) {
+    constexpr int esize = sizeof(OutT);
+    constexpr int cols = 64 / esize;  // columns per staged row: 32 (16-bit) or 16 (fp32)
+    constexpr int elems16 = 16 / esize;
+    uint8_t *my = stg + lane * kBwStagePitch;
+    const int sub = lane & 3;
+#pragma unroll
+    for (int c = 0; c < 128 / cols; ++c) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if constexpr (esize == 4) {
+                *reinterpret_cast<float4 *>(my + 16 * i) =
+                    make_float4(acc[c * 16 + 4 * i], acc[c * 16 + 4 * i + 1], acc[c * 16 + 4 * i + 2], acc[c * 16 + 4 * i + 3]);
+            } else {
+                const float *f = &acc[c * 32 + 8 * i];
+                *reinterpret_cast<uint4 *>(my + 16 * i) =
+                    make_uint4(pack2<OutT>(f[0], f[1]), pack2<OutT>(f[2], f[3]), pack2<OutT>(f[4], f[5]), pack2<OutT>(f[6], f[7]));
+            }
+        }
+        __syncwarp();
+#pragma unroll 1
+        for (int pass = 0; pass < 32; pass += 8) {
+            const int rr = pass + (lane >> 2);
+            const int64_t grow = tile_row0 + rr;
+            const int gcol = n0 + c * cols + sub * elems16;
+            if (grow < c_row_end && gcol < n_end) {
+                const uint4 val = *reinterpret_cast<const uint4 *>(stg + rr * kBwStagePitch + sub * 16);
+                OutT *dst = reinterpret_cast<OutT *>(p.C) + grow * p.ldc + gcol;
+                if (p.vec_store_ok && gcol + elems16 <= n_end && p.beta == 0.f) {
+                    *reinterpret_cast<uint4 *>(dst) = val;
+                } else {
+                    const OutT *src = reinterpret_cast<const OutT *>(&val);
+                    for (int e = 0; e < elems16 && gcol + e < n_end; ++e) {
+                        float nv = static_cast<float>(src[e]);
+                        if (p.beta != 0.f) nv += static_cast<float>(dst[e]);
+                        dst[e] = static_cast<OutT>(nv);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+}
+
+__global__ void __launch_bounds__(kBwThreads, 1)
+    gemm_fp8_blockwise_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, BwParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *smem_a = smem;
+    uint8_t *smem_b = smem_a + kBwStages * kBwABytes;
+    uint8_t *smem_epi = smem_b + kBwStages * kBwBBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_epi + kBwEpiBytes);
+    uint64_t *full_bar = bars;
+    uint64_t *empty_bar = bars + kBwStages;
+    uint64_t *part_full_bar = bars + 2 * kBwStages;  // [2]
+    uint64_t *part_empty_bar = part_full_bar + 2;    // [2]
+    uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(part_empty_bar + 2);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_base_slot + 1);
+    __shared__ int s_tile_start[kMaxGroups + 1];
+
+    const int warp = threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+    const int num_n_blocks = (p.N + BW_BLOCK_N - 1) / BW_BLOCK_N;
+    const int num_k_blocks = (p.K + BLOCK_K - 1) / BLOCK_K;
+    const int G = p.G;
+
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        s_tile_start[0] = 0;
+        for (int g = 0; g < G; ++g) {
+            const int64_t len = p.offs_write ? (p.offs_write[g + 1] - p.offs_write[g]) : p.M;
+            acc += (int) ((len + BLOCK_M - 1) / BLOCK_M) * num_n_blocks;
+            s_tile_start[g + 1] = acc;
+        }
+        *abort_flag = 0;
+        for (int s = 0; s < kBwStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&part_full_bar[s], 1);
+            mbar_init(&part_empty_bar[s], kBwPromoWarps);
+        }
+        fence_barrier_init();
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_base_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    TileWalk walk{s_tile_start, G, num_n_blocks, 0};
+    int gi, m_blk, n_blk;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0;
+            for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
+                const int64_t a_row0 = (p.offs_read ? p.offs_read[gi] : 0) + (int64_t) m_blk * BLOCK_M;
+                const int64_t b_row0 = (int64_t) gi * p.b_group_rows + (int64_t) n_blk * BW_BLOCK_N;
+                for (int kb = 0; kb < num_k_blocks; ++kb) {
+                    if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
+                    mbar_arrive_expect_tx(&full_bar[stage], kBwABytes + kBwBBytes);
+                    tma_load_2d(smem_a + stage * kBwABytes, &tmap_a, &full_bar[stage], kb * BLOCK_K, (int) a_row0);
+                    tma_load_2d(smem_b + stage * kBwBBytes, &tmap_b, &full_bar[stage], kb * BLOCK_K, (int) b_row0);
+                    if (++stage == kBwStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            const uint32_t idesc = idesc_f8(p.a_fmt, p.b_fmt, BLOCK_M, BW_BLOCK_N);
+            uint32_t stage = 0, phase = 0, pb = 0, pphase = 0;
+            for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
+                for (int kb = 0; kb < num_k_blocks; ++kb) {
+                    if (!(ok = mbar_wait(&part_empty_bar[pb], pphase ^ 1, abort_flag))) break;
+                    if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
+                    tc_fence_after_sync();
+                    const uint32_t d_tmem = tmem_base + pb * BW_BLOCK_N;
+                    const uint64_t a_desc = smem_desc_sw128(smem_u32(smem_a + stage * kBwABytes));
+                    const uint64_t b_desc = smem_desc_sw128(smem_u32(smem_b + stage * kBwBBytes));
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        const uint64_t adv = (uint64_t) ((k * UMMA_K) >> 4);
+                        mma_f8(d_tmem, a_desc + adv, b_desc + adv, idesc, k > 0 ? 1u : 0u);
+                    }
+                    tc_commit(&empty_bar[stage]);
+                    tc_commit(&part_full_bar[pb]);
+                    if (++stage == kBwStages) { stage = 0; phase ^= 1; }
+                    if (++pb == 2) { pb = 0; pphase ^= 1; }
+                }
+                if (!ok) break;
+            }
+        }
+    } else {
+        // ================================================================ promotion + epilogue
+        const int pw = warp - 2;
+        const int q = warp & 3;       // TMEM lane quarter of this warp
+        const int half = pw >> 2;     // which 128 columns of the 256-wide tile
+        uint8_t *stg = smem_epi + pw * 32 * kBwStagePitch;
+        uint32_t pb = 0, pphase = 0;
+        for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
+            const int64_t c_row_base = (p.offs_write ? p.offs_write[gi] : 0);
+            const int64_t c_row_end = p.offs_write ? p.offs_write[gi + 1] : p.M;
+            const int64_t a_row_base = (p.offs_read ? p.offs_read[gi] : 0);
+            const int row_in_tile = q * 32 + lane;
+            const int64_t my_c_row = c_row_base + (int64_t) m_blk * BLOCK_M + row_in_tile;
+            const int64_t my_a_row = a_row_base + (int64_t) m_blk * BLOCK_M + row_in_tile;
+            const bool row_ok = my_c_row < c_row_end;
+            const int n0 = n_blk * BW_BLOCK_N + half * 128;
+            const int n_end = min(p.N, n0 + 128);
+            const float *sa_ptr = p.sa.base + (my_a_row >> p.sa.shift) * p.sa.row_stride;
+            const float *sb_base = p.sb.base + (int64_t) gi * p.sb.group_stride;
+            const bool sb_uniform = p.sb.shift == 7;
+            const float *sb_uni_ptr = sb_base + (int64_t) (n0 >> 7) * p.sb.row_stride;
+            const bool sb_uni_ok = n0 < p.N;
+
+            float acc[128];
+#pragma unroll
+            for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+
+            float sa_next = row_ok ? __ldg(sa_ptr) : 0.f;
+            float sbu_next = (sb_uniform && sb_uni_ok) ? __ldg(sb_uni_ptr) : 0.f;
+            for (int kb = 0; kb < num_k_blocks; ++kb) {
+                const float sa_cur = sa_next, sbu_cur = sbu_next;
+                if (kb + 1 < num_k_blocks) {
+                    sa_next = row_ok ? __ldg(sa_ptr + (int64_t) (kb + 1) * p.sa.kb_stride) : 0.f;
+                    sbu_next = (sb_uniform && sb_uni_ok) ? __ldg(sb_uni_ptr + (int64_t) (kb + 1) * p.sb.kb_stride) : 0.f;
+                }
+                if (!(ok = mbar_wait(&part_full_bar[pb], pphase, abort_flag))) break;
+                tc_fence_after_sync();
+                const uint32_t taddr = tmem_base + ((uint32_t) (q * 32) << 16) + pb * BW_BLOCK_N + half * 128;
+                if (sb_uniform) {
+                    const float sc = sa_cur * sbu_cur;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t r[32];
+                        tmem_ld32(taddr + c * 32, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), sc, acc[c * 32 + i]);
+                    }
+                } else {
+                    const float *sbk = sb_base + (int64_t) kb * p.sb.kb_stride;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t r[32];
+                        tmem_ld32(taddr + c * 32, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int n = n0 + c * 32 + i;
+                            const float sbv = n < n_end ? __ldg(sbk + (int64_t) n * p.sb.row_stride) : 0.f;
+                            acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), sa_cur * sbv, acc[c * 32 + i]);
+                        }
+                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&part_empty_bar[pb]);
+                if (++pb == 2) { pb = 0; pphase ^= 1; }
+            }
+            if (!ok) break;
+
+            // ---- write-out through the per-warp staging buffer
+            const int64_t tile_row0 = c_row_base + (int64_t) m_blk * BLOCK_M + q * 32;
+            if (p.c_dtype == PT_F32) bw_store_tile<float>(acc, stg, lane, tile_row0, c_row_end, n0, n_end, p);
+            else if (p.c_dtype == PT_BF16) bw_store_tile<__nv_bfloat16>(acc, stg, lane, tile_row0, c_row_end, n0, n_end, p);
+            else bw_store_tile<__half>(acc, stg, lane, tile_row0, c_row_end, n0, n_end, p);
+        }
+    }
+
+    if (!ok || *abort_flag) {
+        if (p.status && lane == 0) atomicExch(p.status, (int) PT_ERR_TIMEOUT);
+        __nanosleep(200000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+}  // namespace ptb
+
+using namespace ptb;
+
+extern "C" {
+
+int pt_grouped_gemm_fp8_blockwise(const void *a, int a_fmt, const float *sa, int sa_shift, int64_t sa_row_stride,
+                                  int64_t sa_kb_stride, const void *b, int b_fmt, const float *sb, int sb_shift,
+                                  int64_t sb_row_stride, int64_t sb_kb_stride, int64_t sb_group_stride, void *c, int c_dtype,
+                                  int64_t a_rows, int64_t c_rows, int64_t N, int64_t K, const int64_t *group_offs_read,
+                                  const int64_t *group_offs_write, int G, float beta, int max_ctas, int *status,
+                                  void *stream) {
+    PT_REQUIRE(c_rows >= 0 && N >= 0 && K >= 0 && G >= 1 && G <= kMaxGroups, "blockwise GEMM: bad shape");
+    PT_REQUIRE((a_fmt == PT_E4M3 || a_fmt == PT_E5M2) && (b_fmt == PT_E4M3 || b_fmt == PT_E5M2), "blockwise GEMM: operands must be e4m3 / e5m2");
+    PT_REQUIRE(c_dtype == PT_BF16 || c_dtype == PT_F16 || c_dtype == PT_F32, "blockwise GEMM: bad output dtype");
+    PT_REQUIRE((sa_shift == 0 || sa_shift == 7) && (sb_shift == 0 || sb_shift == 7), "blockwise GEMM: scale granularity must be 1 or 128 rows");
+    PT_REQUIRE(beta == 0.f || beta == 1.f, "blockwise GEMM: beta must be 0 or 1");
+    if (c_rows == 0 || N == 0) return PT_OK;
+    PT_REQUIRE(K > 0 && K % 16 == 0, "blockwise GEMM: K must be a positive multiple of 16 (got %lld)", (long long) K);
+    PT_REQUIRE(a && b && c && sa && sb, "blockwise GEMM: null pointer");
+    PT_REQUIRE(N < (1 << 30) && K < (1 << 30) && a_rows < (1ll << 31) && (int64_t) G * N < (1ll << 31), "blockwise GEMM: extent exceeds 32-bit tile coordinates");
+    BwParams p{};
+    p.M = c_rows; p.N = (int) N; p.K = (int) K; p.C = c; p.ldc = N; p.c_dtype = c_dtype; p.beta = beta;
+    const int esize = c_dtype == PT_F32 ? 4 : 2;
+    p.vec_store_ok = aligned(c, 16) && (N * esize) % 16 == 0;
+    p.sa = ScaleDesc{sa, sa_shift, sa_row_stride, sa_kb_stride, 0};
+    p.sb = ScaleDesc{sb, sb_shift, sb_row_stride, sb_kb_stride, sb_group_stride};
+    p.a_fmt = a_fmt; p.b_fmt = b_fmt;
+    p.offs_write = group_offs_write; p.offs_read = group_offs_read ? group_offs_read : group_offs_write;
+    p.G = G; p.b_group_rows = N; p.a_rows_total = a_rows; p.status = status;
+    CUtensorMap ta, tb;
+    int rc;
+    if ((rc = make_tmap_bytes(&ta, a, a_rows, K, K, BLOCK_M)) != PT_OK) return rc;
+    if ((rc = make_tmap_bytes(&tb, b, (int64_t) G * N, K, K, BW_BLOCK_N)) != PT_OK) return rc;
+    static bool attr_set = false;
+    if (!attr_set) {
+        PT_CUDA_OK(cudaFuncSetAttribute(gemm_fp8_blockwise_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwSmemBytes));
+        attr_set = true;
+    }
+    const int64_t tiles = (ceil_div(c_rows, BLOCK_M) + (group_offs_write ? G : 0)) * ceil_div(N, BW_BLOCK_N);
+    int grid = (int) std::min<int64_t>(tiles, sm_count());
+    if (max_ctas > 0) grid = std::min(grid, max_ctas);
+    gemm_fp8_blockwise_kernel<<<grid, kBwThreads, kBwSmemBytes, (cudaStream_t) stream>>>(ta, tb, p);
+    PT_LAUNCH_OK();
+    return PT_OK;
+}
+
+}  // extern "C"

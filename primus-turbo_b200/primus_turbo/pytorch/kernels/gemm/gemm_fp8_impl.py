@@ -21,8 +21,53 @@ def _as_gran(granularity):
 
 
 def _k_major(x, trans):
-    """Returns x laid out [rows, K]: x itself when it already is, else the transposed bytes."""
-    return transpose_2d(x) if trans else x.contiguous()
+    """Returns x laid out [rows, K] with K a multiple of 16 bytes (a TMA row pitch requirement): x itself when
+    it already is, else the transposed bytes; a ragged contraction length is zero padded."""
+    if not trans:
+        x = x.contiguous()
+        K = x.shape[1]
+        if K % 16 == 0:
+            return x
+        y = torch.zeros((x.shape[0], (K + 15) // 16 * 16), dtype=torch.uint8, device=x.device)
+        y[:, :K] = x.view(torch.uint8)
+        return y.view(x.dtype)
+    K = x.shape[0]
+    if K % 16 == 0:
+        return transpose_2d(x)
+    y = torch.zeros((x.shape[1], (K + 15) // 16 * 16), dtype=torch.uint8, device=x.device)
+    y[:, :K] = x.view(torch.uint8).t()
+    return y.view(x.dtype)
+
+
+def _block_scale_desc(scale, rows, kc, source_transposed):
+    """(shift, row_stride, kb_stride) that reads `scale` for a K-major operand of `rows` rows and contraction
+    length `kc`, given whether the operand's source tensor was stored contraction-major (transposed)."""
+    kb = (kc + 127) // 128
+    rb = (rows + 127) // 128
+    s0, s1 = scale.shape
+    if not source_transposed:           # source [rows, kc]
+        assert s1 == kb, f"blockwise scale shape {tuple(scale.shape)} does not match contraction {kc}"
+        if s0 == rows:
+            return 0, s1, 1
+        assert s0 == rb, f"blockwise scale shape {tuple(scale.shape)} does not match {rows} rows"
+        return 7, s1, 1
+    assert s0 == kb, f"blockwise scale shape {tuple(scale.shape)} does not match contraction {kc}"
+    if s1 == rows:                      # source [kc, rows], one scale per (K block, row)
+        return 0, 1, s1
+    assert s1 == rb, f"blockwise scale shape {tuple(scale.shape)} does not match {rows} rows"
+    return 7, 1, s1
+
+
+def _launch_blockwise(a_km, a_desc, a_s, b_km, b_desc, b_s, out, beta, kc):
+    M, N = a_km.shape[0], b_km.shape[0]
+    K = a_km.shape[1]
+    st = nv.status_word(out.device)
+    with torch.cuda.device(out.device):
+        nv.check(nv.lib().pt_grouped_gemm_fp8_blockwise(
+            nv.ptr(a_km), nv.fmt_code(a_km.dtype), nv.ptr(a_s), *a_desc, nv.ptr(b_km), nv.fmt_code(b_km.dtype), nv.ptr(b_s),
+            *b_desc, 0, nv.ptr(out), nv.src_code(out.dtype), M, M, N, K, None, None, 1, float(beta), 0, nv.ptr(st),
+            nv.stream(out.device)), "gemm_fp8_blockwise")
+    return out
 
 
 def _launch(a_km, a_s, b_km, b_s, out, gran, beta, block_n=0):
@@ -30,10 +75,13 @@ def _launch(a_km, a_s, b_km, b_s, out, gran, beta, block_n=0):
     N = b_km.shape[0]
     assert b_km.shape[1] == K, f"contraction mismatch: {a_km.shape} vs {b_km.shape}"
     st = nv.status_word(out.device)
+    ws_bytes = nv.lib().pt_gemm_fp8_workspace_bytes(_GRAN[gran], M, N, K, 1, 0, block_n)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=out.device) if ws_bytes else None
     with torch.cuda.device(out.device):
         nv.check(nv.lib().pt_gemm_fp8(nv.ptr(a_km), nv.ptr(a_s), nv.fmt_code(a_km.dtype), nv.ptr(b_km), nv.ptr(b_s),
                                        nv.fmt_code(b_km.dtype), nv.ptr(out), nv.src_code(out.dtype), _GRAN[gran], M, N, K,
-                                       float(beta), block_n, nv.ptr(st), nv.stream(out.device)), "gemm_fp8")
+                                       float(beta), block_n, nv.ptr(ws), ws_bytes, nv.ptr(st), nv.stream(out.device)),
+                 "gemm_fp8")
     return out
 
 
@@ -41,6 +89,22 @@ def _gemm(a, a_scale_inv, trans_a, b, b_scale_inv, trans_b, out_dtype, trans_c, 
     nv.require_cuda(a, b, a_scale_inv, b_scale_inv)
     assert a.dim() == 2 and b.dim() == 2, "Only 2D tensors are supported"
     gran = _as_gran(granularity)
+    if gran == ScalingGranularity.BLOCKWISE:
+        M = a.shape[1] if trans_a else a.shape[0]
+        N = b.shape[0] if trans_b else b.shape[1]
+        kc = a.shape[0] if trans_a else a.shape[1]
+        a_s, b_s = a_scale_inv.to(torch.float32).contiguous(), b_scale_inv.to(torch.float32).contiguous()
+        a_desc = _block_scale_desc(a_s, M, kc, trans_a)
+        b_desc = _block_scale_desc(b_s, N, kc, not trans_b)
+        a_km, b_km = _k_major(a, trans_a), _k_major(b, not trans_b)
+        beta = 0.0
+        if out is not None:
+            beta = 1.0
+        else:
+            out = torch.empty((N, M) if trans_c else (M, N), dtype=out_dtype, device=a.device)
+        if trans_c:
+            return _launch_blockwise(b_km, b_desc, b_s, a_km, a_desc, a_s, out, beta, kc)
+        return _launch_blockwise(a_km, a_desc, a_s, b_km, b_desc, b_s, out, beta, kc)
     if gran == ScalingGranularity.MX_BLOCKWISE:
         assert not trans_a and trans_b, "MX GEMM takes K-major operands only (trans_a=False, trans_b=True)"
     a_km = _k_major(a, trans_a)            # [M, K]

@@ -1,0 +1,2 @@
+from .gemm_fp8 import *  # noqa: F401,F403
+from .quantization import *  # noqa: F401,F403

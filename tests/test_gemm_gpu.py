@@ -129,3 +129,37 @@ def test_accumulate_into_out(mods):
     nv.check_status(out.device)
     ref = _ref(u8(qa), f32(sa), u8(qb), f32(sb), "e4m3", "e4m3") + 1.0
     assert og.rel_frobenius(f32(out), ref) <= 1e-5
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (256, 512, 384), (255, 520, 576), (1024, 1024, 2048)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_blockwise_fwd_dgrad_wgrad(mods, M, N, K, out_dtype):
+    """The three GEMMs of the blockwise path (primus_turbo/pytorch/ops/gemm_fp8.py:429-553 of the reference):
+    forward NT, dgrad NN against the 128x128-scaled weight, wgrad TN from the column-scaled copies."""
+    qi, gi, nv, SG, _ = mods
+    f8, f5 = torch.float8_e4m3fn, torch.float8_e5m2
+    a = make((M, K), torch.bfloat16, 41, "outlier")
+    w = make((N, K), torch.bfloat16, 42, "weight")
+    g = make((M, N), torch.bfloat16, 43, "small")
+    a_row, a_rs, a_col, a_cs = qi.quant_fp8_blockwise_dual_impl(a, f8)
+    w_q, w_s = qi.quant_fp8_blockwise_for_weight_impl(w, f8)
+    g_row, g_rs, g_col, g_cs = qi.quant_fp8_blockwise_dual_impl(g, f5)
+    tol = FP8_TOL if out_dtype == torch.bfloat16 else 1e-5
+    da_row = oq.dequantize_fp8_blockwise(u8(a_row), f32(a_rs), "e4m3", 1)
+    da_col = oq.dequantize_fp8_blockwise(u8(a_col), f32(a_cs), "e4m3", 0)
+    dw = oq.dequantize_fp8_blockwise_weight(u8(w_q), f32(w_s), "e4m3")
+    dg_row = oq.dequantize_fp8_blockwise(u8(g_row), f32(g_rs), "e5m2", 1)
+    dg_col = oq.dequantize_fp8_blockwise(u8(g_col), f32(g_cs), "e5m2", 0)
+    # forward: [M,K] x [N,K]^T
+    c = gi.gemm_fp8_impl(a_row, a_rs, False, w_q, w_s, True, out_dtype, False, SG.BLOCKWISE)
+    nv.check_status(c.device)
+    assert og.rel_frobenius(f32(c), og.gemm_nt(da_row, dw)) <= tol
+    # dgrad: [M,N] x [N,K]
+    da = gi.gemm_fp8_impl(g_row, g_rs, False, w_q, w_s, False, out_dtype, False, SG.BLOCKWISE)
+    nv.check_status(c.device)
+    assert og.rel_frobenius(f32(da), dg_row @ dw) <= tol
+    # wgrad: a_col^T [K,M] x g_col [M,N] -> [K,N], returned transposed as [N,K]
+    dwg = gi.gemm_fp8_impl(a_col, a_cs, True, g_col, g_cs, False, out_dtype, True, SG.BLOCKWISE)
+    nv.check_status(c.device)
+    assert dwg.shape == (N, K)
+    assert og.rel_frobenius(f32(dwg), (da_col.T @ dg_col).T) <= tol
