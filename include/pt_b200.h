@@ -64,6 +64,19 @@ int pt_quantize_fp8_rowwise(const void *x, int x_dtype, int64_t B, int64_t M, in
                             void *q, float *scale_inv, const float *scale_opt, void *workspace,
                             size_t workspace_bytes, void *stream);
 
+/* The column-scaled form of pt_quantize_fp8_rowwise (x viewed as [B, M, N], one scale per (b, n), scale_inv
+ * [B, 1, N]) for callers that cannot hand over scratch memory because they cannot allocate any: a host runtime
+ * that gave all of the GPU's memory to its own arena at start-up, or code that runs in a phase where calls into
+ * the driver's allocator are not permitted.  The per-column maxima are kept in an array built into the library
+ * (256 KiB on every GPU that loads it, until the process exits), so B * N may not exceed 65536 columns; larger
+ * inputs are refused with PT_ERR_INVALID and belong to pt_quantize_fp8_rowwise.  Results are identical to
+ * pt_quantize_fp8_rowwise(axis_is_last = 0, scale_opt = null).  The first call on each device looks up the
+ * array's device address (make that call before starting a stream capture).  All calls share the one array:
+ * two calls whose kernels overlap on the GPU (different streams) race; calls on one stream are safe.
+ * This entry point has no counterpart in the reference. */
+int pt_quantize_fp8_colscale_noalloc(const void *x, int x_dtype, int64_t B, int64_t M, int64_t N, int fmt, void *q,
+                                     float *scale_inv, void *stream);
+
 /* y = float(q) * scale_inv, cast to y_dtype.  Scale broadcast is described by [B, M, N] as above:
  * tensorwise: B = M = 1 and scale_kind = 0; per-row (axis last): scale_kind = 1; per-column: scale_kind = 2.
  * Replaces dequantize_fp8_tensorwise / dequantize_fp8_rowwise (quantization.cpp:211-330). */

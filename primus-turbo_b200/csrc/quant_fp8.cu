@@ -6,6 +6,7 @@
 #include <cuda_fp8.h>
 #include <stdarg.h>
 #include <algorithm>
+#include <mutex>
 #include <stdio.h>
 
 #include "common.cuh"
@@ -258,6 +259,31 @@ __global__ void __launch_bounds__(kThreads) dequant_kernel(const uint8_t *__rest
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Scratch for pt_quantize_fp8_colscale_noalloc: the per-column running amax lives in this fixed array
+// instead of caller-provided memory.  Every GPU that loads the library holds these 256 KiB until exit.
+constexpr int64_t kNoAllocMaxColumns = 65536;
+static __device__ __align__(256) unsigned g_noalloc_amax[kNoAllocMaxColumns];
+
+// In host code `g_noalloc_amax` is only a stand-in for the symbol, not a device address; the address a
+// kernel can use is looked up once per device (with that device current) and cached.
+static int noalloc_scratch(unsigned **out) {
+    static std::mutex mu;
+    static unsigned *cached[64] = {nullptr};
+    int dev = 0;
+    PT_CUDA_OK(cudaGetDevice(&dev));
+    PT_REQUIRE(dev >= 0 && dev < 64, "no-alloc quantize: device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == nullptr) {
+        void *p = nullptr;
+        PT_CUDA_OK(cudaGetSymbolAddress(&p, g_noalloc_amax));
+        PT_REQUIRE(p != nullptr, "no-alloc quantize: the scratch symbol has no address on device %d", dev);
+        cached[dev] = static_cast<unsigned *>(p);
+    }
+    *out = cached[dev];
+    return PT_OK;
+}
+
 }  // namespace ptb
 
 using namespace ptb;
@@ -354,6 +380,36 @@ int pt_dequantize_fp8(const void *q, int fmt, const float *scale_inv, int scale_
         PT_SWITCH_FP8(fmt, F, {
             dequant_kernel<T, F><<<blocks, kThreads, 0, (cudaStream_t) stream>>>((const uint8_t *) q, scale_inv,
                                                                                  scale_kind, M, N, total, (T *) y);
+        });
+        PT_LAUNCH_OK();
+    });
+    return PT_OK;
+}
+
+int pt_quantize_fp8_colscale_noalloc(const void *x, int x_dtype, int64_t B, int64_t M, int64_t N, int fmt, void *q,
+                                     float *scale_inv, void *stream) {
+    PT_REQUIRE(B >= 0 && M >= 0 && N >= 0 && scale_inv, "no-alloc quantize: bad shape or null scale_inv");
+    PT_REQUIRE(B * N <= kNoAllocMaxColumns,
+               "no-alloc quantize: B * N = %lld columns exceed the built-in scratch of %lld; use pt_quantize_fp8_rowwise "
+               "with a caller-provided workspace", (long long) (B * N), (long long) kNoAllocMaxColumns);
+    if (B * M * N == 0) return PT_OK;
+    PT_REQUIRE(x && q, "no-alloc quantize: null pointer");
+    PT_REQUIRE(B <= 65535, "no-alloc quantize: batch too large");
+    unsigned *amax = nullptr;
+    int rc = noalloc_scratch(&amax);  // first call on a device resolves the scratch address
+    if (rc != PT_OK) return rc;
+    cudaStream_t st = (cudaStream_t) stream;
+    // the array keeps the previous call's maxima: start this call's columns from zero
+    PT_CUDA_OK(cudaMemsetAsync(amax, 0, (size_t) (B * N) * sizeof(unsigned), st));
+    PT_SWITCH_SRC(x_dtype, T, {
+        dim3 grid_a((unsigned) ceil_div(N, kThreads), (unsigned) ceil_div(M, 64), (unsigned) B);
+        amax_cols_kernel<T><<<grid_a, kThreads, 0, st>>>((const T *) x, M, N, amax);
+        PT_LAUNCH_OK();
+        const int vec_ok = aligned(x, 16) && aligned(q, 8) && (N % 8 == 0);
+        dim3 grid_c((unsigned) ceil_div(N, kThreads * (vec_ok ? 8 : 1)), (unsigned) ceil_div(M, 32), (unsigned) B);
+        PT_SWITCH_FP8(fmt, F, {
+            cast_cols_kernel<T, F><<<grid_c, kThreads, 0, st>>>((const T *) x, M, N, vec_ok, amax, nullptr, (uint8_t *) q,
+                                                                scale_inv);
         });
         PT_LAUNCH_OK();
     });

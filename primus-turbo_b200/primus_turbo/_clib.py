@@ -21,6 +21,8 @@ SIGNATURES = {
                                            c_size_t, c_void_p]),
     "pt_quantize_fp8_rowwise": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p,
                                         c_void_p, c_void_p, c_size_t, c_void_p]),
+    "pt_quantize_fp8_colscale_noalloc": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p,
+                                                 c_void_p]),
     "pt_dequantize_fp8": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int, c_void_p]),
     "pt_quantize_fp8_blockwise": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p,
                                           c_void_p, c_void_p]),
