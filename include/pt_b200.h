@@ -190,24 +190,31 @@ int pt_grouped_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const voi
                         const int64_t *group_offs_read, const int64_t *group_offs_write, int G, float beta, int block_n,
                         int max_ctas, void *workspace, size_t workspace_bytes, int *status, void *stream);
 
-/* FP8 GEMM with fp32 128-block scales along K (BLOCKWISE granularity), dense (G = 1, offsets null) or grouped:
- *   C[m, n] = sum_kb ( sum_{k in kb} A[m, k] B[n, k] ) * sa(m, kb) * sb(n, kb),   kb = 128-wide K block.
- * A [a_rows, K] and B [G, N, K] are K-major FP8 bytes.  Each scale operand is read in place through
+/* FP8 GEMM with fp32 128-block scales along the contraction (BLOCKWISE granularity): dense (G = 1, offsets null),
+ * grouped by rows, or grouped with a per-group contraction range ("variable K", the grouped wgrad):
+ *   C[m, n] = sum_kb ( sum_{k in kb} A[m, k] B[n, k] ) * sa(m, kb) * sb(n, kb),   kb = 128-wide block of k.
+ * Operands are FP8 bytes, each either K-major (a_mn = 0: memory [rows, K]) or MN-major (a_mn = 1: memory [K, rows],
+ * the layout of an operand whose contraction runs over its stored rows); *_mem_rows x *_mem_cols is the 2-D
+ * extent of the buffer as stored (row pitch = *_mem_cols bytes, a multiple of 16).  MN-major operands make the
+ * reference's NN (dgrad) and TN (wgrad) GEMMs run on the stored tensors without transposed copies.
+ * Each scale operand is read in place through
  *   s(row, kb) = base[(row >> shift) * row_stride + kb * kb_stride]   (+ g * sb_group_stride for B),
- * shift 0 = one scale per row, 7 = one per 128 rows, which covers every layout the reference's quantizers
- * emit: [M, K/128] (shift 0, K/128, 1); transposed [K/128, M] (0, 1, M); column scales of a transposed
- * operand [Kc/128, R] (0, 1, R); 128 x 128 weight tiles [N/128, K/128] (7, K/128, 1) or, for the transposed
- * weight, (7, 1, R/128).  Group offsets as in pt_grouped_gemm_fp8.
- * Replaces the BLOCKWISE branch of primus_turbo::gemm_fp8_impl, primus_turbo::grouped_gemm_fp8_impl and, with
- * per-group K segments handled by the caller, grouped_gemm_fp8_variable_k_impl
- * (primus_turbo/triton/gemm/gemm_fp8_kernel.py:872-1013,
- *  primus_turbo/triton/grouped_gemm/grouped_gemm_fp8_kernel.py:1407-1556). */
-int pt_grouped_gemm_fp8_blockwise(const void *a, int a_fmt, const float *sa, int sa_shift, int64_t sa_row_stride,
-                                  int64_t sa_kb_stride, const void *b, int b_fmt, const float *sb, int sb_shift,
-                                  int64_t sb_row_stride, int64_t sb_kb_stride, int64_t sb_group_stride, void *c, int c_dtype,
-                                  int64_t a_rows, int64_t c_rows, int64_t N, int64_t K, const int64_t *group_offs_read,
-                                  const int64_t *group_offs_write, int G, float beta, int max_ctas, int *status,
-                                  void *stream);
+ * shift 0 = one scale per row, 7 = one per 128 rows; this covers every layout the reference's quantizers emit:
+ * [M, K/128] (0, K/128, 1); transposed [K/128, M] (0, 1, M); column scales [Kc/128, R] of a token-major operand
+ * (0, 1, R); 128 x 128 weight tiles [N/128, K/128] (7, K/128, 1) or, read across, (7, 1, R/128).
+ * Row grouping: group_offs_write / group_offs_read as in pt_grouped_gemm_fp8; B is [G, N, K] (K-major) or
+ * [G, K, N] (MN-major, K % 128 == 0).
+ * Variable K: k_offs int64 [G+1] (multiples of 128) gives the contraction rows of group g; both operands MN-major
+ * ([total_k, c_rows] and [total_k, N]); C is [G, c_rows, N]; a group with an empty range yields zeros.
+ * Replaces the BLOCKWISE branches of primus_turbo::gemm_fp8_impl, primus_turbo::grouped_gemm_fp8_impl and
+ * primus_turbo::grouped_gemm_fp8_variable_k_impl (primus_turbo/triton/gemm/gemm_fp8_kernel.py:872-1013,
+ * primus_turbo/triton/grouped_gemm/grouped_gemm_fp8_kernel.py:1407-1556,1661-1802). */
+int pt_grouped_gemm_fp8_blockwise(const void *a, int a_fmt, int a_mn, int64_t a_mem_rows, int64_t a_mem_cols, const float *sa,
+                                  int sa_shift, int64_t sa_row_stride, int64_t sa_kb_stride, const void *b, int b_fmt, int b_mn,
+                                  int64_t b_mem_rows, int64_t b_mem_cols, const float *sb, int sb_shift, int64_t sb_row_stride,
+                                  int64_t sb_kb_stride, int64_t sb_group_stride, void *c, int c_dtype, int64_t c_rows, int64_t N,
+                                  int64_t K, const int64_t *group_offs_read, const int64_t *group_offs_write,
+                                  const int64_t *k_offs, int G, float beta, int max_ctas, int *status, void *stream);
 
 #ifdef __cplusplus
 }

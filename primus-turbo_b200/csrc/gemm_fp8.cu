@@ -32,7 +32,7 @@ using namespace sm100;
 constexpr int kNumEpiWarps = 4;
 constexpr int kGemmThreads = 32 * (2 + kNumEpiWarps);
 constexpr int kEpiWarp0 = 2;
-constexpr int kStagePitchMax = 128 + 16;  // staging row pitch (bytes) of the epilogue, fp32 worst case
+constexpr int kStagePitchMax = 128;  // staging row pitch (bytes) of the epilogue, fp32 worst case
 
 enum GemmMode { GEMM_TENSOR = 0, GEMM_ROW = 1, GEMM_MX = 3 };
 
@@ -53,6 +53,7 @@ struct GemmParams {
     int G;
     int64_t b_group_rows;       // rows between consecutive B[g] (N for [G, N, K])
     int *status;                // device int: set to a PT_ERR_* code on a bounded-wait expiry
+    int raster_m;               // row blocks per raster band
 };
 
 template <int BLOCK_N, bool MX> struct GemmCfg {
@@ -209,7 +210,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const uint32_t tmem_sfa = tmem_base + kAccStages * BLOCK_N;
     const uint32_t tmem_sfb = tmem_sfa + 4;
 
-    TileWalk walk{s_tile_start, G, num_n_blocks, 0};
+    TileWalk walk{s_tile_start, G, num_n_blocks, 0, p.raster_m};
     int gi, m_blk, n_blk;
     bool ok = true;
 
@@ -292,7 +293,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const int q = warp & 3;  // TMEM lane quarter this warp may read
         uint8_t *stg = smem_epi + (warp - kEpiWarp0) * 32 * kStagePitchMax;
         const int esize = p.c_dtype == PT_F32 ? 4 : 2;
-        const int pitch = 32 * esize + 16;
+        const int pitch = 32 * esize;  // unpadded rows; 16-byte chunks are XOR-swizzled by row so that neither the
+                                       // row-per-lane writes nor the row-segment reads conflict on banks
         const int lanes_per_row = (32 * esize) / 16;      // 4 (16-bit) or 8 (fp32)
         const int rows_per_pass = 32 / lanes_per_row;     // 8 or 4
         uint32_t acc_stage = 0, acc_phase = 0;
@@ -330,20 +332,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 }
                 // stage this thread's row
                 uint8_t *my = stg + lane * pitch;
+                const int wsw = esize == 4 ? (lane & 7) : ((lane >> 1) & 3);  // chunk swizzle of this lane's row
                 if (esize == 4) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
-                        *reinterpret_cast<float4 *>(my + 16 * i) = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+                        *reinterpret_cast<float4 *>(my + 16 * (i ^ wsw)) = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
                 } else if (p.c_dtype == PT_BF16) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
-                        *reinterpret_cast<uint4 *>(my + 16 * i) =
+                        *reinterpret_cast<uint4 *>(my + 16 * (i ^ wsw)) =
                             make_uint4(pack2<__nv_bfloat16>(f[8 * i], f[8 * i + 1]), pack2<__nv_bfloat16>(f[8 * i + 2], f[8 * i + 3]),
                                        pack2<__nv_bfloat16>(f[8 * i + 4], f[8 * i + 5]), pack2<__nv_bfloat16>(f[8 * i + 6], f[8 * i + 7]));
                 } else {
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
-                        *reinterpret_cast<uint4 *>(my + 16 * i) =
+                        *reinterpret_cast<uint4 *>(my + 16 * (i ^ wsw)) =
                             make_uint4(pack2<__half>(f[8 * i], f[8 * i + 1]), pack2<__half>(f[8 * i + 2], f[8 * i + 3]),
                                        pack2<__half>(f[8 * i + 4], f[8 * i + 5]), pack2<__half>(f[8 * i + 6], f[8 * i + 7]));
                 }
@@ -357,7 +360,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     const int64_t grow = tile_row0 + rr;
                     const int gcol = col0 + sub * elems16;
                     if (grow < c_row_end && gcol < n_end) {
-                        const uint4 val = *reinterpret_cast<const uint4 *>(stg + rr * pitch + sub * 16);
+                        const int rsw = esize == 4 ? (rr & 7) : ((rr >> 1) & 3);
+                        const uint4 val = *reinterpret_cast<const uint4 *>(stg + rr * pitch + (sub ^ rsw) * 16);
                         uint8_t *dst = reinterpret_cast<uint8_t *>(p.C) + (grow * p.ldc + gcol) * esize;
                         if (p.vec_store_ok && gcol + elems16 <= n_end && p.beta == 0.f) {
                             *reinterpret_cast<uint4 *>(dst) = val;
@@ -500,6 +504,7 @@ int gemm_fp8_host(const void *a, const void *a_scale, int a_fmt, const void *b, 
     p.a_fmt = a_fmt; p.b_fmt = b_fmt;
     p.offs_read = offs_read ? offs_read : offs_write; p.offs_write = offs_write; p.G = G; p.b_group_rows = N;
     p.status = status;
+    p.raster_m = raster_rows(a_rows_total, K);
     cudaStream_t st = (cudaStream_t) stream;
     const int64_t b_rows = (int64_t) G * N;
     MxScales mx{nullptr, nullptr, workspace, workspace_bytes};

@@ -9,9 +9,18 @@
 // block out of TMEM, multiply by the two scales and add into fp32 register accumulators while the tensor core
 // is already working on the next block.  Tile 128 x 256: each promotion warp owns 32 rows x 128 columns.
 //
-//   warp 0       TMA producer (A 128 x 128 B, B 256 x 128 B per stage, 128-byte swizzle)
+//   warp 0       TMA producer (A 128 x 128 B, B 256 x 128 B per stage, 128-byte swizzle; B column-scale slabs)
 //   warp 1       MMA issuer, owns TMEM (512 columns = 2 partial buffers x 256)
-//   warps 2-9    promotion + epilogue
+//   warps 2-3    idle (they complete the first warpgroup, which hands its registers over with setmaxnreg)
+//   warps 4-11   promotion + epilogue, 232 registers each (128 fp32 accumulators per thread)
+//
+// Operand layouts: each operand may be K-major ([rows, K], the contraction index contiguous) or MN-major
+// ([K, rows], the row index contiguous), selected per operand in the instruction descriptor.  MN-major tiles are
+// loaded as 128-byte x 128-row TMA boxes and described to the tensor core with SBO = 1024 bytes (eight contraction
+// rows) and LBO = 16 KiB (next 128-wide box); this is what lets dgrad (weight stored [N, K], contraction over N)
+// and wgrad (both operands stored token-major, contraction over tokens) run without transposed copies.
+// Variable-K form (grouped wgrad): every group g produces a full [rows_a, N] output block from the contraction
+// range [koffs[g], koffs[g+1]) of both (MN-major) operands.
 //
 // Scales are addressed through a small descriptor so that every layout the reference produces is read in
 // place: s(row, kb) = base[(row >> shift) * row_stride + kb * kb_stride]  (shift 0: per row, shift 7: per 128 rows).
@@ -24,13 +33,16 @@ using namespace sm100;
 
 constexpr int BW_BLOCK_N = 256;
 constexpr int kBwPromoWarps = 8;
-constexpr int kBwThreads = 32 * (2 + kBwPromoWarps);
-constexpr int kBwStagePitch = 64 + 16;  // staging row: 32 x 16-bit or 16 x fp32 columns, padded
+constexpr int kBwPromoWarp0 = 4;  // warps 0-3 form the first warpgroup: producer, MMA issuer, two idle warps
+constexpr int kBwThreads = 32 * (kBwPromoWarp0 + kBwPromoWarps);
+constexpr int kBwSlabRing = 8;    // ring of per-K-step B column-scale slabs (256 floats each)
+constexpr int kBwSlabBytes = BW_BLOCK_N * 4;
+constexpr int kBwStagePitch = 64;  // staging row: 32 x 16-bit or 16 x fp32 columns; 16-byte chunks XOR-swizzled by row
 constexpr int kBwABytes = BLOCK_M * BLOCK_K;
 constexpr int kBwBBytes = BW_BLOCK_N * BLOCK_K;
 constexpr int kBwStages = 4;
 constexpr int kBwEpiBytes = kBwPromoWarps * 32 * kBwStagePitch;
-constexpr int kBwSmemBytes = kBwStages * (kBwABytes + kBwBBytes) + kBwEpiBytes + 1024 + 1024;
+constexpr int kBwSmemBytes = kBwStages * (kBwABytes + kBwBBytes) + kBwEpiBytes + kBwSlabRing * kBwSlabBytes + 1024 + 1024;
 
 struct ScaleDesc {
     const float *base;
@@ -54,6 +66,11 @@ struct BwParams {
     int64_t b_group_rows;
     int64_t a_rows_total;
     int *status;
+    int raster_m;
+    int a_mn, b_mn;            // operand is MN-major (stored [contraction, rows])
+    int sb_slab;               // B scales are per column and contiguous along the columns: staged through shared memory
+    const int64_t *koffs;      // variable-K: contraction row range of each group (multiples of 128), else null
+    int64_t b_group_kstride;   // MN-major B of a grouped GEMM: contraction rows per group
 };
 
 // Writes one warp's 32 x 128 fp32 accumulators (one row per lane) to C through a padded staging buffer so
@@ -66,16 +83,17 @@ __device__ __forceinline__ void bw_store_tile(const float (&acc)[128], uint8_t *
     constexpr int elems16 = 16 / esize;
     uint8_t *my = stg + lane * kBwStagePitch;
     const int sub = lane & 3;
+    const int wsw = (lane >> 1) & 3;  // chunk swizzle of this lane's row: conflict-free writes and reads
 #pragma unroll
     for (int c = 0; c < 128 / cols; ++c) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             if constexpr (esize == 4) {
-                *reinterpret_cast<float4 *>(my + 16 * i) =
+                *reinterpret_cast<float4 *>(my + 16 * (i ^ wsw)) =
                     make_float4(acc[c * 16 + 4 * i], acc[c * 16 + 4 * i + 1], acc[c * 16 + 4 * i + 2], acc[c * 16 + 4 * i + 3]);
             } else {
                 const float *f = &acc[c * 32 + 8 * i];
-                *reinterpret_cast<uint4 *>(my + 16 * i) =
+                *reinterpret_cast<uint4 *>(my + 16 * (i ^ wsw)) =
                     make_uint4(pack2<OutT>(f[0], f[1]), pack2<OutT>(f[2], f[3]), pack2<OutT>(f[4], f[5]), pack2<OutT>(f[6], f[7]));
             }
         }
@@ -86,7 +104,7 @@ __device__ __forceinline__ void bw_store_tile(const float (&acc)[128], uint8_t *
             const int64_t grow = tile_row0 + rr;
             const int gcol = n0 + c * cols + sub * elems16;
             if (grow < c_row_end && gcol < n_end) {
-                const uint4 val = *reinterpret_cast<const uint4 *>(stg + rr * kBwStagePitch + sub * 16);
+                const uint4 val = *reinterpret_cast<const uint4 *>(stg + rr * kBwStagePitch + (sub ^ ((rr >> 1) & 3)) * 16);
                 OutT *dst = reinterpret_cast<OutT *>(p.C) + grow * p.ldc + gcol;
                 if (p.vec_store_ok && gcol + elems16 <= n_end && p.beta == 0.f) {
                     *reinterpret_cast<uint4 *>(dst) = val;
@@ -111,12 +129,14 @@ __global__ void __launch_bounds__(kBwThreads, 1)
     uint8_t *smem_a = smem;
     uint8_t *smem_b = smem_a + kBwStages * kBwABytes;
     uint8_t *smem_epi = smem_b + kBwStages * kBwBBytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_epi + kBwEpiBytes);
+    float *smem_slab = reinterpret_cast<float *>(smem_epi + kBwEpiBytes);  // [kBwSlabRing][256] B column scales
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_epi + kBwEpiBytes + kBwSlabRing * kBwSlabBytes);
     uint64_t *full_bar = bars;
     uint64_t *empty_bar = bars + kBwStages;
     uint64_t *part_full_bar = bars + 2 * kBwStages;  // [2]
     uint64_t *part_empty_bar = part_full_bar + 2;    // [2]
-    uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(part_empty_bar + 2);
+    uint64_t *slab_full_bar = part_empty_bar + 2;    // [kBwSlabRing]
+    uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(slab_full_bar + kBwSlabRing);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_base_slot + 1);
     __shared__ int s_tile_start[kMaxGroups + 1];
 
@@ -130,7 +150,7 @@ __global__ void __launch_bounds__(kBwThreads, 1)
         int acc = 0;
         s_tile_start[0] = 0;
         for (int g = 0; g < G; ++g) {
-            const int64_t len = p.offs_write ? (p.offs_write[g + 1] - p.offs_write[g]) : p.M;
+            const int64_t len = p.koffs ? p.M : (p.offs_write ? (p.offs_write[g + 1] - p.offs_write[g]) : p.M);
             acc += (int) ((len + BLOCK_M - 1) / BLOCK_M) * num_n_blocks;
             s_tile_start[g + 1] = acc;
         }
@@ -143,6 +163,7 @@ __global__ void __launch_bounds__(kBwThreads, 1)
             mbar_init(&part_full_bar[s], 1);
             mbar_init(&part_empty_bar[s], kBwPromoWarps);
         }
+        for (int s = 0; s < kBwSlabRing; ++s) mbar_init(&slab_full_bar[s], 1);
         fence_barrier_init();
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
@@ -156,42 +177,86 @@ __global__ void __launch_bounds__(kBwThreads, 1)
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_base_slot;
 
-    TileWalk walk{s_tile_start, G, num_n_blocks, 0};
+    TileWalk walk{s_tile_start, G, num_n_blocks, 0, p.raster_m};
     int gi, m_blk, n_blk;
     bool ok = true;
 
+    // K steps of group g: all of K, or the group's contraction range in the variable-K form
+    auto k_range = [&](int g, int &kb_begin, int &kb_count) {
+        if (p.koffs) {
+            kb_begin = (int) (p.koffs[g] / BLOCK_K);
+            kb_count = (int) ((p.koffs[g + 1] - p.koffs[g]) / BLOCK_K);
+        } else {
+            kb_begin = 0;
+            kb_count = num_k_blocks;
+        }
+    };
+
+    if (warp < kBwPromoWarp0) {
+    // the first warpgroup (producer, MMA issuer, two idle warps) gives registers to the promotion warps
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0) {
+        // ================================================================ TMA producer
         if (elect_one()) {
-            uint32_t stage = 0, phase = 0;
+            uint32_t stage = 0, phase = 0, step = 0;
             for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
-                const int64_t a_row0 = (p.offs_read ? p.offs_read[gi] : 0) + (int64_t) m_blk * BLOCK_M;
-                const int64_t b_row0 = (int64_t) gi * p.b_group_rows + (int64_t) n_blk * BW_BLOCK_N;
-                for (int kb = 0; kb < num_k_blocks; ++kb) {
+                const int64_t a_row0 = (p.koffs ? 0 : (p.offs_read ? p.offs_read[gi] : 0)) + (int64_t) m_blk * BLOCK_M;
+                const int64_t b_row0 = (p.koffs ? 0 : (int64_t) gi * p.b_group_rows) + (int64_t) n_blk * BW_BLOCK_N;
+                int kb_begin, kb_count;
+                k_range(gi, kb_begin, kb_count);
+                const int n0 = n_blk * BW_BLOCK_N;
+                const int slab_cols = min(BW_BLOCK_N, p.N - n0);
+                for (int kb = 0; kb < kb_count; ++kb, ++step) {
                     if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
                     mbar_arrive_expect_tx(&full_bar[stage], kBwABytes + kBwBBytes);
-                    tma_load_2d(smem_a + stage * kBwABytes, &tmap_a, &full_bar[stage], kb * BLOCK_K, (int) a_row0);
-                    tma_load_2d(smem_b + stage * kBwBBytes, &tmap_b, &full_bar[stage], kb * BLOCK_K, (int) b_row0);
+                    const int k0 = (kb_begin + kb) * BLOCK_K;
+                    uint8_t *sa = smem_a + stage * kBwABytes, *sb = smem_b + stage * kBwBBytes;
+                    if (p.a_mn) tma_load_2d(sa, &tmap_a, &full_bar[stage], (int) a_row0, k0);
+                    else tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, (int) a_row0);
+                    if (p.b_mn) {
+                        // two 128-wide boxes; contraction rows of group g start at g * b_group_kstride
+                        const int kr = (int) ((p.koffs ? 0 : (int64_t) gi * p.b_group_kstride) + k0);
+                        tma_load_2d(sb, &tmap_b, &full_bar[stage], n0, kr);
+                        tma_load_2d(sb + kBwBBytes / 2, &tmap_b, &full_bar[stage], n0 + 128, kr);
+                    } else {
+                        tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, (int) b_row0);
+                    }
+                    if (p.sb_slab) {
+                        // per-column B scales of this K step: one contiguous run of `slab_cols` floats.  Ring slot
+                        // step % 8 is free: the producer runs at most 4 stages + 2 partial buffers ahead of the readers.
+                        const uint32_t slot = step % kBwSlabRing;
+                        const float *src = p.sb.base + (int64_t) gi * p.sb.group_stride + (int64_t) (kb_begin + kb) * p.sb.kb_stride + n0;
+                        mbar_arrive_expect_tx(&slab_full_bar[slot], (uint32_t) slab_cols * 4);
+                        bulk_load(smem_slab + slot * (kBwSlabBytes / 4), src, (uint32_t) slab_cols * 4, &slab_full_bar[slot]);
+                    }
                     if (++stage == kBwStages) { stage = 0; phase ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
+        // ================================================================ MMA issuer
         if (elect_one()) {
-            const uint32_t idesc = idesc_f8(p.a_fmt, p.b_fmt, BLOCK_M, BW_BLOCK_N);
+            const uint32_t idesc = idesc_f8(p.a_fmt, p.b_fmt, BLOCK_M, BW_BLOCK_N) | ((uint32_t) (p.a_mn != 0) << 15) |
+                                   ((uint32_t) (p.b_mn != 0) << 16);
             uint32_t stage = 0, phase = 0, pb = 0, pphase = 0;
             for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
-                for (int kb = 0; kb < num_k_blocks; ++kb) {
+                int kb_begin, kb_count;
+                k_range(gi, kb_begin, kb_count);
+                for (int kb = 0; kb < kb_count; ++kb) {
                     if (!(ok = mbar_wait(&part_empty_bar[pb], pphase ^ 1, abort_flag))) break;
                     if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + pb * BW_BLOCK_N;
-                    const uint64_t a_desc = smem_desc_sw128(smem_u32(smem_a + stage * kBwABytes));
-                    const uint64_t b_desc = smem_desc_sw128(smem_u32(smem_b + stage * kBwBBytes));
+                    const uint32_t a_addr = smem_u32(smem_a + stage * kBwABytes), b_addr = smem_u32(smem_b + stage * kBwBBytes);
+                    const uint64_t a_desc = p.a_mn ? smem_desc_sw128_mn(a_addr, 16384) : smem_desc_sw128(a_addr);
+                    const uint64_t b_desc = p.b_mn ? smem_desc_sw128_mn(b_addr, 16384) : smem_desc_sw128(b_addr);
+                    // one instruction consumes 32 contraction indices: 32 bytes along a K-major row, or 32 rows of
+                    // 128 bytes in an MN-major tile
+                    const uint64_t a_step = p.a_mn ? (uint64_t) ((UMMA_K * 128) >> 4) : (uint64_t) (UMMA_K >> 4);
+                    const uint64_t b_step = p.b_mn ? (uint64_t) ((UMMA_K * 128) >> 4) : (uint64_t) (UMMA_K >> 4);
 #pragma unroll
-                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-                        const uint64_t adv = (uint64_t) ((k * UMMA_K) >> 4);
-                        mma_f8(d_tmem, a_desc + adv, b_desc + adv, idesc, k > 0 ? 1u : 0u);
-                    }
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                        mma_f8(d_tmem, a_desc + k * a_step, b_desc + k * b_step, idesc, k > 0 ? 1u : 0u);
                     tc_commit(&empty_bar[stage]);
                     tc_commit(&part_full_bar[pb]);
                     if (++stage == kBwStages) { stage = 0; phase ^= 1; }
@@ -200,25 +265,29 @@ __global__ void __launch_bounds__(kBwThreads, 1)
                 if (!ok) break;
             }
         }
+    }
     } else {
         // ================================================================ promotion + epilogue
-        const int pw = warp - 2;
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        const int pw = warp - kBwPromoWarp0;
         const int q = warp & 3;       // TMEM lane quarter of this warp
         const int half = pw >> 2;     // which 128 columns of the 256-wide tile
         uint8_t *stg = smem_epi + pw * 32 * kBwStagePitch;
-        uint32_t pb = 0, pphase = 0;
+        uint32_t pb = 0, pphase = 0, step = 0;
         for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
-            const int64_t c_row_base = (p.offs_write ? p.offs_write[gi] : 0);
-            const int64_t c_row_end = p.offs_write ? p.offs_write[gi + 1] : p.M;
-            const int64_t a_row_base = (p.offs_read ? p.offs_read[gi] : 0);
+            const int64_t c_row_base = p.koffs ? (int64_t) gi * p.M : (p.offs_write ? p.offs_write[gi] : 0);
+            const int64_t c_row_end = p.koffs ? c_row_base + p.M : (p.offs_write ? p.offs_write[gi + 1] : p.M);
+            const int64_t a_row_base = p.koffs ? 0 : (p.offs_read ? p.offs_read[gi] : 0);
+            int kb_begin, kb_count;
+            k_range(gi, kb_begin, kb_count);
             const int row_in_tile = q * 32 + lane;
             const int64_t my_c_row = c_row_base + (int64_t) m_blk * BLOCK_M + row_in_tile;
             const int64_t my_a_row = a_row_base + (int64_t) m_blk * BLOCK_M + row_in_tile;
             const bool row_ok = my_c_row < c_row_end;
             const int n0 = n_blk * BW_BLOCK_N + half * 128;
             const int n_end = min(p.N, n0 + 128);
-            const float *sa_ptr = p.sa.base + (my_a_row >> p.sa.shift) * p.sa.row_stride;
-            const float *sb_base = p.sb.base + (int64_t) gi * p.sb.group_stride;
+            const float *sa_ptr = p.sa.base + (my_a_row >> p.sa.shift) * p.sa.row_stride + (int64_t) kb_begin * p.sa.kb_stride;
+            const float *sb_base = p.sb.base + (int64_t) gi * p.sb.group_stride + (int64_t) kb_begin * p.sb.kb_stride;
             const bool sb_uniform = p.sb.shift == 7;
             const float *sb_uni_ptr = sb_base + (int64_t) (n0 >> 7) * p.sb.row_stride;
             const bool sb_uni_ok = n0 < p.N;
@@ -227,39 +296,68 @@ __global__ void __launch_bounds__(kBwThreads, 1)
 #pragma unroll
             for (int i = 0; i < 128; ++i) acc[i] = 0.f;
 
-            float sa_next = row_ok ? __ldg(sa_ptr) : 0.f;
-            float sbu_next = (sb_uniform && sb_uni_ok) ? __ldg(sb_uni_ptr) : 0.f;
-            for (int kb = 0; kb < num_k_blocks; ++kb) {
+            float sa_next = (row_ok && kb_count > 0) ? __ldg(sa_ptr) : 0.f;
+            float sbu_next = (sb_uniform && sb_uni_ok && kb_count > 0) ? __ldg(sb_uni_ptr) : 0.f;
+            for (int kb = 0; kb < kb_count; ++kb, ++step) {
                 const float sa_cur = sa_next, sbu_cur = sbu_next;
-                if (kb + 1 < num_k_blocks) {
+                if (kb + 1 < kb_count) {
                     sa_next = row_ok ? __ldg(sa_ptr + (int64_t) (kb + 1) * p.sa.kb_stride) : 0.f;
                     sbu_next = (sb_uniform && sb_uni_ok) ? __ldg(sb_uni_ptr + (int64_t) (kb + 1) * p.sb.kb_stride) : 0.f;
                 }
                 if (!(ok = mbar_wait(&part_full_bar[pb], pphase, abort_flag))) break;
                 tc_fence_after_sync();
                 const uint32_t taddr = tmem_base + ((uint32_t) (q * 32) << 16) + pb * BW_BLOCK_N + half * 128;
+                // TMEM reads are issued one chunk ahead of the FMAs that consume them
+                uint32_t r0[32], r1[32];
+                tmem_ld32(taddr, r0);
                 if (sb_uniform) {
                     const float sc = sa_cur * sbu_cur;
+                    tmem_ld_wait();
+                    tmem_ld32(taddr + 32, r1);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[i] = fmaf(__uint_as_float(r0[i]), sc, acc[i]);
+                    tmem_ld_wait();
+                    tmem_ld32(taddr + 64, r0);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(__uint_as_float(r1[i]), sc, acc[32 + i]);
+                    tmem_ld_wait();
+                    tmem_ld32(taddr + 96, r1);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(__uint_as_float(r0[i]), sc, acc[64 + i]);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(__uint_as_float(r1[i]), sc, acc[96 + i]);
+                } else if (p.sb_slab) {
+                    const uint32_t slot = step % kBwSlabRing;
+                    if (!(ok = mbar_wait(&slab_full_bar[slot], (step / kBwSlabRing) & 1u, abort_flag))) break;
+                    const float4 *sl = reinterpret_cast<const float4 *>(smem_slab + slot * (kBwSlabBytes / 4) + half * 128);
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
-                        uint32_t r[32];
-                        tmem_ld32(taddr + c * 32, r);
+                        uint32_t(&r)[32] = (c & 1) ? r1 : r0;
                         tmem_ld_wait();
+                        if (c < 3) tmem_ld32(taddr + 32 * (c + 1), (c & 1) ? r0 : r1);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), sc, acc[c * 32 + i]);
+                        for (int i = 0; i < 8; ++i) {
+                            const float4 sv = sl[c * 8 + i];  // same address in every lane: a broadcast read
+                            acc[c * 32 + 4 * i + 0] = fmaf(__uint_as_float(r[4 * i + 0]) * sv.x, sa_cur, acc[c * 32 + 4 * i + 0]);
+                            acc[c * 32 + 4 * i + 1] = fmaf(__uint_as_float(r[4 * i + 1]) * sv.y, sa_cur, acc[c * 32 + 4 * i + 1]);
+                            acc[c * 32 + 4 * i + 2] = fmaf(__uint_as_float(r[4 * i + 2]) * sv.z, sa_cur, acc[c * 32 + 4 * i + 2]);
+                            acc[c * 32 + 4 * i + 3] = fmaf(__uint_as_float(r[4 * i + 3]) * sv.w, sa_cur, acc[c * 32 + 4 * i + 3]);
+                        }
                     }
                 } else {
+                    // general per-row B scales read from global memory (no reference path needs this to be fast)
                     const float *sbk = sb_base + (int64_t) kb * p.sb.kb_stride;
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
-                        uint32_t r[32];
-                        tmem_ld32(taddr + c * 32, r);
+                        uint32_t(&r)[32] = (c & 1) ? r1 : r0;
                         tmem_ld_wait();
+                        if (c < 3) tmem_ld32(taddr + 32 * (c + 1), (c & 1) ? r0 : r1);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
                             const int n = n0 + c * 32 + i;
-                            const float sbv = n < n_end ? __ldg(sbk + (int64_t) n * p.sb.row_stride) : 0.f;
-                            acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), sa_cur * sbv, acc[c * 32 + i]);
+                            const float sbv = n < n_end ? __ldg(sbk + (int64_t) (n >> p.sb.shift) * p.sb.row_stride) : 0.f;
+                            acc[c * 32 + i] = fmaf(__uint_as_float(r[i]) * sbv, sa_cur, acc[c * 32 + i]);
                         }
                     }
                 }
@@ -296,21 +394,27 @@ using namespace ptb;
 
 extern "C" {
 
-int pt_grouped_gemm_fp8_blockwise(const void *a, int a_fmt, const float *sa, int sa_shift, int64_t sa_row_stride,
-                                  int64_t sa_kb_stride, const void *b, int b_fmt, const float *sb, int sb_shift,
-                                  int64_t sb_row_stride, int64_t sb_kb_stride, int64_t sb_group_stride, void *c, int c_dtype,
-                                  int64_t a_rows, int64_t c_rows, int64_t N, int64_t K, const int64_t *group_offs_read,
-                                  const int64_t *group_offs_write, int G, float beta, int max_ctas, int *status,
-                                  void *stream) {
+int pt_grouped_gemm_fp8_blockwise(const void *a, int a_fmt, int a_mn, int64_t a_mem_rows, int64_t a_mem_cols, const float *sa,
+                                  int sa_shift, int64_t sa_row_stride, int64_t sa_kb_stride, const void *b, int b_fmt, int b_mn,
+                                  int64_t b_mem_rows, int64_t b_mem_cols, const float *sb, int sb_shift, int64_t sb_row_stride,
+                                  int64_t sb_kb_stride, int64_t sb_group_stride, void *c, int c_dtype, int64_t c_rows, int64_t N,
+                                  int64_t K, const int64_t *group_offs_read, const int64_t *group_offs_write,
+                                  const int64_t *k_offs, int G, float beta, int max_ctas, int *status, void *stream) {
     PT_REQUIRE(c_rows >= 0 && N >= 0 && K >= 0 && G >= 1 && G <= kMaxGroups, "blockwise GEMM: bad shape");
     PT_REQUIRE((a_fmt == PT_E4M3 || a_fmt == PT_E5M2) && (b_fmt == PT_E4M3 || b_fmt == PT_E5M2), "blockwise GEMM: operands must be e4m3 / e5m2");
     PT_REQUIRE(c_dtype == PT_BF16 || c_dtype == PT_F16 || c_dtype == PT_F32, "blockwise GEMM: bad output dtype");
     PT_REQUIRE((sa_shift == 0 || sa_shift == 7) && (sb_shift == 0 || sb_shift == 7), "blockwise GEMM: scale granularity must be 1 or 128 rows");
     PT_REQUIRE(beta == 0.f || beta == 1.f, "blockwise GEMM: beta must be 0 or 1");
+    PT_REQUIRE(!k_offs || (a_mn && b_mn && !group_offs_read && !group_offs_write),
+               "blockwise GEMM: the variable-K form takes MN-major operands and no row offsets");
     if (c_rows == 0 || N == 0) return PT_OK;
-    PT_REQUIRE(K > 0 && K % 16 == 0, "blockwise GEMM: K must be a positive multiple of 16 (got %lld)", (long long) K);
+    PT_REQUIRE(k_offs || (K > 0 && (K % 16 == 0 || (a_mn && b_mn))), "blockwise GEMM: K must be a positive multiple of 16 (got %lld)", (long long) K);
     PT_REQUIRE(a && b && c && sa && sb, "blockwise GEMM: null pointer");
-    PT_REQUIRE(N < (1 << 30) && K < (1 << 30) && a_rows < (1ll << 31) && (int64_t) G * N < (1ll << 31), "blockwise GEMM: extent exceeds 32-bit tile coordinates");
+    PT_REQUIRE(a_mem_cols % 16 == 0 && b_mem_cols % 16 == 0, "blockwise GEMM: operand row pitch must be a multiple of 16 bytes");
+    PT_REQUIRE(N < (1 << 30) && K < (1 << 30) && a_mem_rows < (1ll << 31) && b_mem_rows < (1ll << 31) && a_mem_cols < (1ll << 31) &&
+                   b_mem_cols < (1ll << 31), "blockwise GEMM: extent exceeds 32-bit tile coordinates");
+    PT_REQUIRE(!(b_mn && G > 1 && !k_offs) || K % BLOCK_K == 0,
+               "blockwise GEMM: an MN-major grouped B needs a contraction length that is a multiple of 128");
     BwParams p{};
     p.M = c_rows; p.N = (int) N; p.K = (int) K; p.C = c; p.ldc = N; p.c_dtype = c_dtype; p.beta = beta;
     const int esize = c_dtype == PT_F32 ? 4 : 2;
@@ -319,17 +423,22 @@ int pt_grouped_gemm_fp8_blockwise(const void *a, int a_fmt, const float *sa, int
     p.sb = ScaleDesc{sb, sb_shift, sb_row_stride, sb_kb_stride, sb_group_stride};
     p.a_fmt = a_fmt; p.b_fmt = b_fmt;
     p.offs_write = group_offs_write; p.offs_read = group_offs_read ? group_offs_read : group_offs_write;
-    p.G = G; p.b_group_rows = N; p.a_rows_total = a_rows; p.status = status;
+    p.G = G; p.b_group_rows = N; p.a_rows_total = a_mem_rows; p.status = status;
+    p.a_mn = a_mn; p.b_mn = b_mn; p.koffs = k_offs; p.b_group_kstride = K;
+    p.sb_slab = sb_shift == 0 && sb_row_stride == 1 && sb_kb_stride % 4 == 0 && sb_group_stride % 4 == 0 && N % 4 == 0 && aligned(sb, 16);
+    p.raster_m = raster_rows(a_mn ? a_mem_cols : a_mem_rows, a_mn ? a_mem_rows : a_mem_cols);
     CUtensorMap ta, tb;
     int rc;
-    if ((rc = make_tmap_bytes(&ta, a, a_rows, K, K, BLOCK_M)) != PT_OK) return rc;
-    if ((rc = make_tmap_bytes(&tb, b, (int64_t) G * N, K, K, BW_BLOCK_N)) != PT_OK) return rc;
+    // K-major: box = 128 contraction bytes x tile rows; MN-major: box = 128 row indices x 128 contraction rows
+    if ((rc = make_tmap_bytes(&ta, a, a_mem_rows, a_mem_cols, a_mem_cols, a_mn ? BLOCK_K : BLOCK_M)) != PT_OK) return rc;
+    if ((rc = make_tmap_bytes(&tb, b, b_mem_rows, b_mem_cols, b_mem_cols, b_mn ? BLOCK_K : BW_BLOCK_N)) != PT_OK) return rc;
     static bool attr_set = false;
     if (!attr_set) {
         PT_CUDA_OK(cudaFuncSetAttribute(gemm_fp8_blockwise_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwSmemBytes));
         attr_set = true;
     }
-    const int64_t tiles = (ceil_div(c_rows, BLOCK_M) + (group_offs_write ? G : 0)) * ceil_div(N, BW_BLOCK_N);
+    const int64_t m_blocks = k_offs ? (int64_t) G * ceil_div(c_rows, BLOCK_M) : ceil_div(c_rows, BLOCK_M) + (group_offs_write ? G : 0);
+    const int64_t tiles = m_blocks * ceil_div(N, BW_BLOCK_N);
     int grid = (int) std::min<int64_t>(tiles, sm_count());
     if (max_ctas > 0) grid = std::min(grid, max_ctas);
     gemm_fp8_blockwise_kernel<<<grid, kBwThreads, kBwSmemBytes, (cudaStream_t) stream>>>(ta, tb, p);

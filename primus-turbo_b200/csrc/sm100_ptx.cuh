@@ -116,6 +116,18 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
     d |= (uint64_t) 2 << 61;                       // SWIZZLE_128B
     return d;
 }
+// MN-major operand tile with the 128-byte swizzle: rows of the tile are contraction indices, each 128 bytes =
+// 128 consecutive row (M / N) indices; 8 contraction rows form a 1024-byte group (stride byte offset); the next
+// 128 row indices start `mn_chunk_bytes` further (leading byte offset).
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t smem_addr, uint32_t mn_chunk_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t) ((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t) ((mn_chunk_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t) (1024 >> 4) << 32;
+    d |= (uint64_t) 1 << 46;
+    d |= (uint64_t) 2 << 61;
+    return d;
+}
 // Descriptor of a 32 x 16-byte scale-factor block for tcgen05.cp (no swizzle, 8-row groups 128 bytes apart).
 __device__ __forceinline__ uint64_t smem_desc_sf(uint32_t smem_addr) {
     uint64_t d = 0;

@@ -44,9 +44,10 @@ SIGNATURES = {
     "pt_grouped_gemm_fp8": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
                                     c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int, c_float, c_int, c_int,
                                     c_void_p, c_size_t, c_void_p, c_void_p]),
-    "pt_grouped_gemm_fp8_blockwise": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_void_p,
-                                              c_int, c_int64, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64, c_int64,
-                                              c_int64, c_void_p, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p]),
+    "pt_grouped_gemm_fp8_blockwise": (c_int, [c_void_p, c_int, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64,
+                                              c_void_p, c_int, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64,
+                                              c_int64, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p,
+                                              c_void_p, c_int, c_float, c_int, c_void_p, c_void_p]),
 }
 
 _lib = None

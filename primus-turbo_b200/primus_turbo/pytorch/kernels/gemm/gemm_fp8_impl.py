@@ -58,14 +58,32 @@ def _block_scale_desc(scale, rows, kc, source_transposed):
     return 7, 1, s1
 
 
-def _launch_blockwise(a_km, a_desc, a_s, b_km, b_desc, b_s, out, beta, kc):
-    M, N = a_km.shape[0], b_km.shape[0]
-    K = a_km.shape[1]
+def _bw_operand(x, trans_to_kmajor):
+    """(tensor, mn_major, mem_rows, mem_cols): a K-major operand is used as stored; one stored contraction-major is
+    used as stored too (MN-major) when its row pitch allows, else transposed into a zero-padded K-major copy."""
+    x = x.contiguous()
+    if not trans_to_kmajor:
+        xk = _k_major(x, False)
+        return xk, 0, xk.shape[0], xk.shape[1]
+    if x.shape[1] % 16 == 0:
+        return x, 1, x.shape[0], x.shape[1]
+    xk = _k_major(x, True)
+    return xk, 0, xk.shape[0], xk.shape[1]
+
+
+def _launch_blockwise(a_op, a_desc, a_s, b_op, b_desc, b_s, out, beta, M, N, kc):
+    a_t, a_mn, a_r, a_c = a_op
+    b_t, b_mn, b_r, b_c = b_op
+    K = kc if (a_mn and b_mn) else (a_t.shape[1] if not a_mn else (b_t.shape[1] if not b_mn else kc))
+    if not (a_mn and b_mn):
+        # a K-major operand may carry zero padding up to a multiple of 16; the other side must agree on K
+        K = max(K, kc)
     st = nv.status_word(out.device)
     with torch.cuda.device(out.device):
         nv.check(nv.lib().pt_grouped_gemm_fp8_blockwise(
-            nv.ptr(a_km), nv.fmt_code(a_km.dtype), nv.ptr(a_s), *a_desc, nv.ptr(b_km), nv.fmt_code(b_km.dtype), nv.ptr(b_s),
-            *b_desc, 0, nv.ptr(out), nv.src_code(out.dtype), M, M, N, K, None, None, 1, float(beta), 0, nv.ptr(st),
+            nv.ptr(a_t), nv.fmt_code(a_t.dtype), a_mn, a_r, a_c, nv.ptr(a_s), *a_desc,
+            nv.ptr(b_t), nv.fmt_code(b_t.dtype), b_mn, b_r, b_c, nv.ptr(b_s), *b_desc, 0,
+            nv.ptr(out), nv.src_code(out.dtype), M, N, K, None, None, None, 1, float(beta), 0, nv.ptr(st),
             nv.stream(out.device)), "gemm_fp8_blockwise")
     return out
 
@@ -96,15 +114,19 @@ def _gemm(a, a_scale_inv, trans_a, b, b_scale_inv, trans_b, out_dtype, trans_c, 
         a_s, b_s = a_scale_inv.to(torch.float32).contiguous(), b_scale_inv.to(torch.float32).contiguous()
         a_desc = _block_scale_desc(a_s, M, kc, trans_a)
         b_desc = _block_scale_desc(b_s, N, kc, not trans_b)
-        a_km, b_km = _k_major(a, trans_a), _k_major(b, not trans_b)
+        a_op, b_op = _bw_operand(a, trans_a), _bw_operand(b, not trans_b)
+        if (a_op[1] == 0) != (b_op[1] == 0) and kc % 16 != 0:
+            # a ragged contraction cannot mix a padded K-major copy with an MN-major operand read in place
+            a_op = (_k_major(a, trans_a), 0) + tuple(_k_major(a, trans_a).shape)
+            b_op = (_k_major(b, not trans_b), 0) + tuple(_k_major(b, not trans_b).shape)
         beta = 0.0
         if out is not None:
             beta = 1.0
         else:
             out = torch.empty((N, M) if trans_c else (M, N), dtype=out_dtype, device=a.device)
         if trans_c:
-            return _launch_blockwise(b_km, b_desc, b_s, a_km, a_desc, a_s, out, beta, kc)
-        return _launch_blockwise(a_km, a_desc, a_s, b_km, b_desc, b_s, out, beta, kc)
+            return _launch_blockwise(b_op, b_desc, b_s, a_op, a_desc, a_s, out, beta, N, M, kc)
+        return _launch_blockwise(a_op, a_desc, a_s, b_op, b_desc, b_s, out, beta, M, N, kc)
     if gran == ScalingGranularity.MX_BLOCKWISE:
         assert not trans_a and trans_b, "MX GEMM takes K-major operands only (trans_a=False, trans_b=True)"
     a_km = _k_major(a, trans_a)            # [M, K]
