@@ -141,6 +141,19 @@ int pt_compute_padded_group_offs(const int64_t *lens, int G, int64_t align, int6
 int pt_quantize_mx(const void *x, int x_dtype, int64_t G, int64_t M, int64_t N, int fmt, unsigned flags,
                    void *q_row, uint8_t *s_row, void *q_col, uint8_t *s_col, void *stream);
 
+/* Grouped form for x [M, N] whose rows are split into G groups (int64 offsets [G+1] on the device).
+ * The col-wise copy lives in the 128-padded row space: q_col [N, col_alloc(/2)], s_col [N, col_alloc/32] with
+ * col_alloc = ceil128(M + G*128); group g occupies columns padded_offs_col[g] .. padded_offs_col[g+1], zero padded.
+ * The row-wise copy puts row i of group g at row padded_offs_row[g] + i of q_row [rows_alloc, N_pad(/2)],
+ * s_row [rows_alloc, N_pad/32] (fp8: groups padded to 32 rows, rows_alloc = ceil32(M + G*32); fp4: pass the tight
+ * offsets, rows_alloc = M); pad rows and anything at or past the last padded offset are not written.
+ * An all-zero block gets scale byte 127.  Flags as in pt_quantize_mx without the 2-D options.
+ * Replaces grouped_quantize_mxfp8(_dual) / grouped_quantize_mxfp4(_dual) (bindings_pytorch.cpp:61-70,79-93;
+ * csrc/pytorch/quantization/quantization.cpp:971-1378). */
+int pt_grouped_quantize_mx(const void *x, int x_dtype, int64_t M, int64_t N, int G, const int64_t *group_offs,
+                           const int64_t *padded_offs_row, const int64_t *padded_offs_col, int fmt, unsigned flags, void *q_row,
+                           uint8_t *s_row, void *q_col, uint8_t *s_col, int64_t col_alloc, void *stream);
+
 /* y [rows, cols] = decode(q [rows, cols_stored]) * 2^(s - 127); cols <= cols_stored (the stored row length in
  * elements, a multiple of 32); s [rows, cols_stored/32].  When transpose_out != 0 y is written as [cols, rows]
  * (col-wise inputs are returned re-transposed, quantization.cpp:332-358).
@@ -175,7 +188,8 @@ int pt_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const void *b, co
 /* Scratch bytes pt_gemm_fp8 / pt_grouped_gemm_fp8 need: 0 except for PT_MX_BLOCKWISE, where the raw scales are
  * re-tiled into the block layout of the tensor core's scale copy before the GEMM (the reference's back ends also
  * pre-shuffle the raw scales right before their kernels, primus_turbo/pytorch/ops/gemm_fp8.py:577-579).
- * c_rows: rows of C; grouped: nonzero for the grouped entry point; block_n as passed to the GEMM. */
+ * c_rows: rows of C (per group for the variable-K form); grouped: 0 = pt_gemm_fp8, 1 = pt_grouped_gemm_fp8,
+ * 2 = pt_grouped_gemm_fp8_variable_k; block_n as passed to the GEMM. */
 size_t pt_gemm_fp8_workspace_bytes(int granularity, int64_t c_rows, int64_t N, int64_t K, int G, int grouped, int block_n);
 
 /* Grouped form: rows are split into G groups, group g multiplies B[g] ([G, N, K] contiguous).
@@ -189,6 +203,17 @@ int pt_grouped_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const voi
                         void *c, int c_dtype, int granularity, int64_t a_rows, int64_t c_rows, int64_t N, int64_t K,
                         const int64_t *group_offs_read, const int64_t *group_offs_write, int G, float beta, int block_n,
                         int max_ctas, void *workspace, size_t workspace_bytes, int *status, void *stream);
+
+/* Variable-K grouped GEMM (the grouped wgrad): C [G, M, N], C[g] = A[:, k_offs[g]:k_offs[g+1]] . B[:, same range]^T with
+ * A [M, K_total] and B [N, K_total] K-major and shared by all groups; k_offs int64 [G+1], multiples of 128 (the
+ * 128-padded per-group token segments the grouped quantizers produce).  A group with an empty range yields zeros.
+ * Scales: PT_TENSORWISE scalars; PT_ROWWISE a_scale [G, M], b_scale [G, N]; PT_MX_BLOCKWISE raw ue8m0 [rows, K_total/32].
+ * Replaces primus_turbo::grouped_gemm_fp8_variable_k_impl / _accum_impl
+ * (primus_turbo/pytorch/kernels/grouped_gemm/grouped_gemm_fp8_impl.py:936-1030). */
+int pt_grouped_gemm_fp8_variable_k(const void *a, const void *a_scale, int a_fmt, const void *b, const void *b_scale, int b_fmt,
+                                   void *c, int c_dtype, int granularity, int64_t M, int64_t N, int64_t K_total,
+                                   const int64_t *k_offs, int G, float beta, int block_n, int max_ctas, void *workspace,
+                                   size_t workspace_bytes, int *status, void *stream);
 
 /* FP8 GEMM with fp32 128-block scales along the contraction (BLOCKWISE granularity): dense (G = 1, offsets null),
  * grouped by rows, or grouped with a per-group contraction range ("variable K", the grouped wgrad):

@@ -52,6 +52,8 @@ struct GemmParams {
     const int64_t *offs_write;  // [G+1] first C row of each group; group length = difference
     int G;
     int64_t b_group_rows;       // rows between consecutive B[g] (N for [G, N, K])
+    const int64_t *koffs;       // variable-K form: contraction range [koffs[g], koffs[g+1]) of group g (multiples of 128);
+                                // every group then yields a full [M, N] block of C (C is [G, M, N]), A and B are shared
     int *status;                // device int: set to a PT_ERR_* code on a bounded-wait expiry
     int raster_m;               // row blocks per raster band
 };
@@ -182,7 +184,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         int acc = 0;
         s_tile_start[0] = 0;
         for (int g = 0; g < G; ++g) {
-            const int64_t len = p.offs_write ? (p.offs_write[g + 1] - p.offs_write[g]) : p.M;
+            const int64_t len = (p.offs_write && !p.koffs) ? (p.offs_write[g + 1] - p.offs_write[g]) : p.M;
             acc += (int) ((len + BLOCK_M - 1) / BLOCK_M) * num_n_blocks;
             s_tile_start[g + 1] = acc;
         }
@@ -213,27 +215,38 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     TileWalk walk{s_tile_start, G, num_n_blocks, 0, p.raster_m};
     int gi, m_blk, n_blk;
     bool ok = true;
+    auto k_range = [&](int g, int &kb_begin, int &kb_count) {
+        if (p.koffs) {
+            kb_begin = (int) (p.koffs[g] / BLOCK_K);
+            kb_count = (int) ((p.koffs[g + 1] - p.koffs[g]) / BLOCK_K);
+        } else {
+            kb_begin = 0;
+            kb_count = num_k_blocks;
+        }
+    };
 
     if (warp == 0) {
         // ================================================================ TMA producer
         if (elect_one()) {
             uint32_t stage = 0, phase = 0;
             for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
-                const int64_t a_row0 = (p.offs_read ? p.offs_read[gi] : 0) + (int64_t) m_blk * BLOCK_M;
-                const int64_t b_row0 = (int64_t) gi * p.b_group_rows + (int64_t) n_blk * BLOCK_N;
+                const int64_t a_row0 = ((p.offs_read && !p.koffs) ? p.offs_read[gi] : 0) + (int64_t) m_blk * BLOCK_M;
+                const int64_t b_row0 = (p.koffs ? 0 : (int64_t) gi * p.b_group_rows) + (int64_t) n_blk * BLOCK_N;
+                int kb_begin, kb_count;
+                k_range(gi, kb_begin, kb_count);
                 // scale blocks of this tile: A row block = running count of 128-row blocks over the groups
                 const uint8_t *sfa_blk = nullptr, *sfb_blk = nullptr;
                 if constexpr (MX) {
-                    const int64_t a_rb = s_tile_start[gi] / num_n_blocks + m_blk;
-                    const int64_t b_rb = ((int64_t) gi * num_n_blocks + n_blk) * Cfg::kSfbBlocks;
-                    sfa_blk = p.sfa_tiled + a_rb * num_k_blocks * 512;
-                    sfb_blk = p.sfb_tiled + b_rb * num_k_blocks * 512;
+                    const int64_t a_rb = p.koffs ? m_blk : s_tile_start[gi] / num_n_blocks + m_blk;
+                    const int64_t b_rb = ((p.koffs ? 0 : (int64_t) gi * num_n_blocks) + n_blk) * Cfg::kSfbBlocks;
+                    sfa_blk = p.sfa_tiled + (a_rb * num_k_blocks + kb_begin) * 512;
+                    sfb_blk = p.sfb_tiled + (b_rb * num_k_blocks + kb_begin) * 512;
                 }
-                for (int kb = 0; kb < num_k_blocks; ++kb) {
+                for (int kb = 0; kb < kb_count; ++kb) {
                     if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
                     mbar_arrive_expect_tx(&full_bar[stage], Cfg::kABytes + Cfg::kBBytes + Cfg::kSfBytes);
-                    tma_load_2d(smem_a + stage * Cfg::kABytes, &tmap_a, &full_bar[stage], kb * BLOCK_K, (int) a_row0);
-                    tma_load_2d(smem_b + stage * Cfg::kBBytes, &tmap_b, &full_bar[stage], kb * BLOCK_K, (int) b_row0);
+                    tma_load_2d(smem_a + stage * Cfg::kABytes, &tmap_a, &full_bar[stage], (kb_begin + kb) * BLOCK_K, (int) a_row0);
+                    tma_load_2d(smem_b + stage * Cfg::kBBytes, &tmap_b, &full_bar[stage], (kb_begin + kb) * BLOCK_K, (int) b_row0);
                     if constexpr (MX) {
                         uint8_t *sf = smem_sf + stage * Cfg::kSfBytes;
                         bulk_load(sf, sfa_blk + (int64_t) kb * 512, 512, &full_bar[stage]);
@@ -254,10 +267,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                                       : idesc_f8(p.a_fmt, p.b_fmt, BLOCK_M, BLOCK_N);
             uint32_t stage = 0, phase = 0, acc_stage = 0, acc_phase = 0, sf_buf = 0;
             for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
+                int kb_begin, kb_count;
+                k_range(gi, kb_begin, kb_count);
+                if (kb_count == 0) continue;  // empty contraction range: the epilogue writes zeros on its own
                 if (!(ok = mbar_wait(&tmem_empty_bar[acc_stage], acc_phase ^ 1, abort_flag))) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc_stage * BLOCK_N;
-                for (int kb = 0; kb < num_k_blocks; ++kb) {
+                for (int kb = 0; kb < kb_count; ++kb) {
                     if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
                     tc_fence_after_sync();
                     const uint32_t sfa_cur = tmem_sfa + sf_buf * Cfg::kSfColsOne;
@@ -299,24 +315,32 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const int rows_per_pass = 32 / lanes_per_row;     // 8 or 4
         uint32_t acc_stage = 0, acc_phase = 0;
         for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
-            const int64_t c_row_base = (p.offs_write ? p.offs_write[gi] : 0);
-            const int64_t c_row_end = p.offs_write ? p.offs_write[gi + 1] : p.M;
+            const int64_t c_row_base = p.koffs ? (int64_t) gi * p.M : (p.offs_write ? p.offs_write[gi] : 0);
+            const int64_t c_row_end = p.koffs ? c_row_base + p.M : (p.offs_write ? p.offs_write[gi + 1] : p.M);
+            int kb_begin, kb_count;
+            k_range(gi, kb_begin, kb_count);
+            const bool have_acc = kb_count > 0;
             const int64_t tile_row0 = c_row_base + (int64_t) m_blk * BLOCK_M + q * 32;
             const int n0 = n_blk * BLOCK_N;
-            if (!(ok = mbar_wait(&tmem_full_bar[acc_stage], acc_phase, abort_flag))) break;
+            if (have_acc && !(ok = mbar_wait(&tmem_full_bar[acc_stage], acc_phase, abort_flag))) break;
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t) (q * 32) << 16) + acc_stage * BLOCK_N;
             float row_scale = 1.f;
             if (MODE == GEMM_TENSOR) row_scale = __ldg(p.sa) * __ldg(p.sb);
             if (MODE == GEMM_ROW) row_scale = (tile_row0 + lane < c_row_end) ? __ldg(p.sa + tile_row0 + lane) : 0.f;
-#pragma unroll 1
             constexpr int kChunks = (BLOCK_N + 31) / 32;  // a last partial chunk reads past the tile; masked below
             const int n_end = min(p.N, n0 + BLOCK_N);
+#pragma unroll 1
             for (int c = 0; c < kChunks; ++c) {
                 uint32_t r[32];
-                tmem_ld32(taddr + c * 32, r);
-                tmem_ld_wait();
-                if (c == kChunks - 1) {
+                if (have_acc) {
+                    tmem_ld32(taddr + c * 32, r);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = 0u;
+                }
+                if (have_acc && c == kChunks - 1) {
                     // whole accumulator is in registers / staged: hand the TMEM buffer back to the MMA warp
                     tc_fence_before_sync();
                     __syncwarp();
@@ -387,7 +411,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 }
                 __syncwarp();
             }
-            if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1; }
+            if (have_acc && ++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1; }
         }
     }
 
@@ -423,19 +447,21 @@ static int launch_gemm(const void *a, int64_t a_rows, const void *b, int64_t b_r
                        int max_ctas, int64_t max_tiles, cudaStream_t st) {
     using Cfg = GemmCfg<BLOCK_N, MODE == GEMM_MX>;
     if constexpr (MODE == GEMM_MX) {
-        const bool grouped = p.offs_write != nullptr;
-        const size_t need = mx_workspace_bytes(p.M, p.N, p.K, p.G, grouped, BLOCK_N);
+        const bool grouped = p.offs_write != nullptr && !p.koffs;
+        const int sf_groups = p.koffs ? 1 : p.G;  // variable-K: one shared A and one shared B
+        const size_t need = mx_workspace_bytes(p.M, p.N, p.K, sf_groups, grouped, BLOCK_N);
         PT_REQUIRE(mx.workspace && mx.workspace_bytes >= need && aligned(mx.workspace, 16),
                    "MX GEMM: workspace of %zu bytes (16-byte aligned) required, got %zu", need, mx.workspace_bytes);
         const int num_kb = (int) ceil_div(p.K, BLOCK_K);
         RetileArgs ra{};
         ra.src = mx.sfa; ra.dst = (uint8_t *) mx.workspace; ra.src_rows = a_rows; ra.sf_ld = p.K / 32; ra.num_kb = num_kb;
-        ra.is_b = 0; ra.offs_read = p.offs_read; ra.offs_write = p.offs_write; ra.G = p.G; ra.M = p.M;
+        ra.is_b = 0; ra.offs_read = grouped ? p.offs_read : nullptr; ra.offs_write = grouped ? p.offs_write : nullptr;
+        ra.G = sf_groups; ra.M = p.M;
         ra.num_row_blocks = ceil_div(p.M, BLOCK_M) + (grouped ? p.G : 0);
         RetileArgs rb = ra;
         rb.src = mx.sfb; rb.dst = ra.dst + ra.num_row_blocks * num_kb * 512; rb.src_rows = b_rows; rb.is_b = 1;
         rb.block_n = BLOCK_N; rb.sfb_blocks = Cfg::kSfbBlocks; rb.num_n_blocks = (int) ceil_div(p.N, BLOCK_N);
-        rb.b_group_rows = p.b_group_rows; rb.num_row_blocks = (int64_t) p.G * rb.num_n_blocks * Cfg::kSfbBlocks;
+        rb.b_group_rows = p.b_group_rows; rb.G = sf_groups; rb.num_row_blocks = (int64_t) sf_groups * rb.num_n_blocks * Cfg::kSfbBlocks;
         const int max_blocks = sm_count() * 8;
         dim3 ga((unsigned) std::min<int64_t>(ra.num_row_blocks, max_blocks), (unsigned) ceil_div(num_kb, 32));
         dim3 gb((unsigned) std::min<int64_t>(rb.num_row_blocks, max_blocks), (unsigned) ceil_div(num_kb, 32));
@@ -470,7 +496,7 @@ template <int MODE>
 static int dispatch_block_n(int block_n, const void *a, int64_t a_rows, const void *b, int64_t b_rows, const GemmParams &p,
                             const MxScales &mx, int max_ctas, cudaStream_t st) {
     // upper bound on tiles: every group may add one partial row block
-    const int64_t m_blocks_bound = ceil_div(p.M, BLOCK_M) + (p.offs_write ? p.G : 0);
+    const int64_t m_blocks_bound = p.koffs ? (int64_t) p.G * ceil_div(p.M, BLOCK_M) : ceil_div(p.M, BLOCK_M) + (p.offs_write ? p.G : 0);
     if (block_n == 0) block_n = default_block_n(MODE, p.N);
     const int64_t tiles = m_blocks_bound * ceil_div(p.N, block_n);
     switch (block_n) {
@@ -483,8 +509,8 @@ static int dispatch_block_n(int block_n, const void *a, int64_t a_rows, const vo
 
 int gemm_fp8_host(const void *a, const void *a_scale, int a_fmt, const void *b, const void *b_scale, int b_fmt, void *c,
                   int c_dtype, int64_t ldc, int granularity, int64_t M, int64_t N, int64_t K, float beta,
-                  const int64_t *offs_read, const int64_t *offs_write, int G, int64_t a_rows_total, int block_n,
-                  int max_ctas, void *workspace, size_t workspace_bytes, int *status, void *stream) {
+                  const int64_t *offs_read, const int64_t *offs_write, const int64_t *k_offs, int G, int64_t a_rows_total,
+                  int block_n, int max_ctas, void *workspace, size_t workspace_bytes, int *status, void *stream) {
     PT_REQUIRE(M >= 0 && N >= 0 && K >= 0 && G >= 1 && G <= kMaxGroups, "GEMM: bad shape (M=%lld N=%lld K=%lld G=%d)",
                (long long) M, (long long) N, (long long) K, G);
     PT_REQUIRE(a_fmt == PT_E4M3 || a_fmt == PT_E5M2, "GEMM: A format must be e4m3 or e5m2");
@@ -503,10 +529,12 @@ int gemm_fp8_host(const void *a, const void *a_scale, int a_fmt, const void *b, 
     p.vec_store_ok = aligned(c, 16) && (ldc * esize) % 16 == 0;
     p.a_fmt = a_fmt; p.b_fmt = b_fmt;
     p.offs_read = offs_read ? offs_read : offs_write; p.offs_write = offs_write; p.G = G; p.b_group_rows = N;
+    p.koffs = k_offs;
+    PT_REQUIRE(!k_offs || (!offs_read && !offs_write), "GEMM: the variable-K form takes no row offsets");
     p.status = status;
     p.raster_m = raster_rows(a_rows_total, K);
     cudaStream_t st = (cudaStream_t) stream;
-    const int64_t b_rows = (int64_t) G * N;
+    const int64_t b_rows = k_offs ? N : (int64_t) G * N;
     MxScales mx{nullptr, nullptr, workspace, workspace_bytes};
     switch (granularity) {
     case PT_TENSORWISE:
@@ -534,6 +562,7 @@ extern "C" {
 size_t pt_gemm_fp8_workspace_bytes(int granularity, int64_t c_rows, int64_t N, int64_t K, int G, int grouped, int block_n) {
     if (granularity != PT_MX_BLOCKWISE || c_rows <= 0 || N <= 0 || K <= 0 || G < 1) return 0;
     if (block_n == 0) block_n = default_block_n(GEMM_MX, N);
+    if (grouped == 2) return mx_workspace_bytes(c_rows, N, K, 1, false, block_n);  // variable-K: shared A and B
     return mx_workspace_bytes(c_rows, N, K, G, grouped != 0, block_n);
 }
 
@@ -541,7 +570,7 @@ int pt_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const void *b, co
                 int c_dtype, int granularity, int64_t M, int64_t N, int64_t K, float beta, int block_n, void *workspace,
                 size_t workspace_bytes, int *status, void *stream) {
     return gemm_fp8_host(a, a_scale, a_fmt, b, b_scale, b_fmt, c, c_dtype, N, granularity, M, N, K, beta, nullptr, nullptr,
-                         1, M, block_n, 0, workspace, workspace_bytes, status, stream);
+                         nullptr, 1, M, block_n, 0, workspace, workspace_bytes, status, stream);
 }
 
 int pt_grouped_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const void *b, const void *b_scale, int b_fmt,
@@ -550,8 +579,17 @@ int pt_grouped_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const voi
                         int max_ctas, void *workspace, size_t workspace_bytes, int *status, void *stream) {
     PT_REQUIRE(group_offs_write, "grouped GEMM: group offsets required");
     return gemm_fp8_host(a, a_scale, a_fmt, b, b_scale, b_fmt, c, c_dtype, N, granularity, c_rows, N, K, beta,
-                         group_offs_read, group_offs_write, G, a_rows, block_n, max_ctas, workspace, workspace_bytes, status,
-                         stream);
+                         group_offs_read, group_offs_write, nullptr, G, a_rows, block_n, max_ctas, workspace, workspace_bytes,
+                         status, stream);
+}
+
+int pt_grouped_gemm_fp8_variable_k(const void *a, const void *a_scale, int a_fmt, const void *b, const void *b_scale, int b_fmt,
+                                   void *c, int c_dtype, int granularity, int64_t M, int64_t N, int64_t K_total,
+                                   const int64_t *k_offs, int G, float beta, int block_n, int max_ctas, void *workspace,
+                                   size_t workspace_bytes, int *status, void *stream) {
+    PT_REQUIRE(k_offs, "variable-K GEMM: contraction offsets required");
+    return gemm_fp8_host(a, a_scale, a_fmt, b, b_scale, b_fmt, c, c_dtype, N, granularity, M, N, K_total, beta, nullptr, nullptr,
+                         k_offs, G, M, block_n, max_ctas, workspace, workspace_bytes, status, stream);
 }
 
 }  // extern "C"

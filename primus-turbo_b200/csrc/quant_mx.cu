@@ -93,10 +93,17 @@ struct MxArgs {
     int64_t M, N, M_pad, N_pad;
     uint8_t *q_row, *s_row, *q_col, *s_col;
     int64_t x_gstride, qrow_gstride, srow_gstride, qcol_gstride, scol_gstride;  // per batch entry, in elements/bytes
+    // grouped form: rows of x are split into groups; the tile grid runs over the 128-padded row space
+    const int64_t *group_offs, *poffs_row, *poffs_col;
+    int num_groups;
 };
 
-// grid: (N_pad / 64, M_pad / 128, G)
-template <typename T, int FMT, bool ROW, bool COL, bool ROW2D, bool COL2D, bool ROWRHT, bool COLRHT>
+// grid: (N_pad / 64, M_pad / 128, G); GROUPED: (N_pad / 64, (M + groups * 128) / 128, 1)
+// GROUPED (csrc/kernels/quantization/quantization_mxfp8.cu:979-1709 of the reference): every 128-row tile of the
+// 128-padded row space belongs to one group; rows past the group's end read as zero; the col-wise copy is written
+// in that padded space, the row-wise copy at the group's own (32-padded for fp8, tight for fp4) offset, real rows
+// only; an all-zero block gets scale byte 127.
+template <typename T, int FMT, bool ROW, bool COL, bool ROW2D, bool COL2D, bool ROWRHT, bool COLRHT, bool GROUPED = false>
 __global__ void __launch_bounds__(kMxThreads) mx_quant_kernel(MxArgs a) {
     constexpr bool kFp4 = FMT == PT_E2M1;
     constexpr bool kNeed2D = (ROW && ROW2D) || (COL && COL2D);
@@ -105,9 +112,22 @@ __global__ void __launch_bounds__(kMxThreads) mx_quant_kernel(MxArgs a) {
 
     const int tid = threadIdx.x;
     const int64_t g = blockIdx.z;
-    const int64_t m0 = (int64_t) blockIdx.y * kTileM;
+    const int64_t m0 = (int64_t) blockIdx.y * kTileM;  // tile origin: input rows, or padded rows when GROUPED
     const int64_t n0 = (int64_t) blockIdx.x * kTileN;
     const T *x = reinterpret_cast<const T *>(a.x) + g * a.x_gstride;
+    int64_t in_row0 = m0, in_end = a.M, row_out0 = m0;
+    if constexpr (GROUPED) {
+        if (m0 >= a.poffs_col[a.num_groups]) return;
+        int lo = 0, hi = a.num_groups - 1;  // last group whose padded start is <= m0 (empty groups are skipped)
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (a.poffs_col[mid] <= m0) lo = mid; else hi = mid - 1;
+        }
+        const int64_t into = m0 - a.poffs_col[lo];
+        in_row0 = a.group_offs[lo] + into;
+        in_end = min(a.group_offs[lo + 1], a.M);
+        row_out0 = a.poffs_row[lo] + into;
+    }
 
     if constexpr (kNeed2D) {
         if (tid < 8) s_amax2d[tid >> 1][tid & 1] = 0u;
@@ -122,9 +142,9 @@ __global__ void __launch_bounds__(kMxThreads) mx_quant_kernel(MxArgs a) {
     float amax4[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const int64_t gm = m0 + 32 * i + rsub;
+        const int64_t gm = in_row0 + 32 * i + rsub;
         uint32_t w[4] = {0u, 0u, 0u, 0u};
-        if (gm < a.M && gn < a.N) {
+        if (gm < in_end && gn < a.N) {
             const uint4 r = __ldg(reinterpret_cast<const uint4 *>(x + gm * a.N + gn));
             w[0] = r.x; w[1] = r.y; w[2] = r.z; w[3] = r.w;
         }
@@ -163,7 +183,8 @@ __global__ void __launch_bounds__(kMxThreads) mx_quant_kernel(MxArgs a) {
     if constexpr (ROW) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const int64_t gm = m0 + 32 * i + rsub;
+            const int64_t gm = in_row0 + 32 * i + rsub;  // input row
+            const int64_t go = row_out0 + 32 * i + rsub; // row of the row-wise copy
             float t[8];
 #pragma unroll
             for (int k = 0; k < 8; ++k) t[k] = v[i][k];
@@ -191,13 +212,13 @@ __global__ void __launch_bounds__(kMxThreads) mx_quant_kernel(MxArgs a) {
                 m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
                 m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
             }
-            const MxScale s = mx_scale<FMT>(m, false);
+            const MxScale s = mx_scale<FMT>(m, GROUPED);
             const uint2 o = mx_encode8<FMT>(t, s);
-            if (gm < a.M && gn < a.N_pad) {
+            if (gm < in_end && gn < a.N_pad) {
                 uint8_t *qr = a.q_row + g * a.qrow_gstride;
-                if constexpr (kFp4) *reinterpret_cast<uint32_t *>(qr + (gm * a.N_pad + gn) / 2) = o.x;
-                else *reinterpret_cast<uint2 *>(qr + gm * a.N_pad + gn) = o;
-                if ((cvec & 3) == 0) (a.s_row + g * a.srow_gstride)[gm * (a.N_pad / 32) + gn / 32] = s.byte;
+                if constexpr (kFp4) *reinterpret_cast<uint32_t *>(qr + (go * a.N_pad + gn) / 2) = o.x;
+                else *reinterpret_cast<uint2 *>(qr + go * a.N_pad + gn) = o;
+                if ((cvec & 3) == 0) (a.s_row + g * a.srow_gstride)[go * (a.N_pad / 32) + gn / 32] = s.byte;
             }
         }
     }
@@ -220,7 +241,7 @@ __global__ void __launch_bounds__(kMxThreads) mx_quant_kernel(MxArgs a) {
 #pragma unroll
                 for (int r = 0; r < 32; ++r) m = fmaxf(m, fabsf(c[r]));
             }
-            const MxScale s = mx_scale<FMT>(m, false);
+            const MxScale s = mx_scale<FMT>(m, GROUPED);
             const int64_t gm = m0 + band * 32;
             uint8_t *qc = a.q_col + g * a.qcol_gstride;
             uint32_t w[8];
@@ -323,11 +344,69 @@ static int launch_mx(const MxArgs &a, int64_t G, unsigned flags, cudaStream_t st
     return set_error(PT_ERR_UNSUPPORTED, "MX quantize: flag combination 0x%x is not built for this format", flags);
 }
 
+template <typename T, int FMT>
+static int launch_mx_grouped(const MxArgs &a, int64_t m_alloc, unsigned flags, cudaStream_t st) {
+    dim3 grid((unsigned) (a.N_pad / kTileN), (unsigned) (m_alloc / kTileM), 1u);
+    const bool row = flags & PT_MX_ROW, col = flags & PT_MX_COL;
+    const bool rrht = flags & PT_MX_ROW_RHT, crht = flags & PT_MX_COL_RHT;
+#define PT_MXG_CASE(R, C, RR, CR)                                                                     \
+    if (row == R && col == C && (!R || rrht == RR) && (!C || crht == CR)) {                          \
+        mx_quant_kernel<T, FMT, R, C, false, false, RR, CR, true><<<grid, kMxThreads, 0, st>>>(a);   \
+        PT_LAUNCH_OK();                                                                               \
+        return PT_OK;                                                                                 \
+    }
+    PT_MXG_CASE(true, false, false, false)
+    PT_MXG_CASE(false, true, false, false)
+    PT_MXG_CASE(true, true, false, false)
+    if constexpr (FMT == PT_E2M1) {
+        PT_MXG_CASE(false, true, false, true)
+        PT_MXG_CASE(true, true, false, true)
+        PT_MXG_CASE(true, true, true, true)
+        PT_MXG_CASE(true, false, true, false)
+    }
+#undef PT_MXG_CASE
+    return set_error(PT_ERR_UNSUPPORTED, "grouped MX quantize: flag combination 0x%x is not built", flags);
+}
+
 }  // namespace ptb
 
 using namespace ptb;
 
 extern "C" {
+
+int pt_grouped_quantize_mx(const void *x, int x_dtype, int64_t M, int64_t N, int G, const int64_t *group_offs,
+                           const int64_t *padded_offs_row, const int64_t *padded_offs_col, int fmt, unsigned flags, void *q_row,
+                           uint8_t *s_row, void *q_col, uint8_t *s_col, int64_t col_alloc, void *stream) {
+    PT_REQUIRE(M >= 0 && N >= 0 && G >= 1, "grouped MX quantize: bad shape");
+    PT_REQUIRE(N % 32 == 0, "grouped MX quantize: N must be divisible by 32 (got %lld)", (long long) N);
+    PT_REQUIRE(x_dtype == PT_BF16 || x_dtype == PT_F16, "grouped MX quantize: input must be bf16 or fp16");
+    PT_REQUIRE(flags & (PT_MX_ROW | PT_MX_COL), "grouped MX quantize: no output requested");
+    PT_REQUIRE(!(flags & (PT_MX_ROW_2D | PT_MX_COL_2D)), "grouped MX quantize: 2-D block scales are a weight option, not a grouped one");
+    PT_REQUIRE(group_offs && padded_offs_col, "grouped MX quantize: group offsets required");
+    PT_REQUIRE(!(flags & PT_MX_ROW) || (q_row && s_row && padded_offs_row), "grouped MX quantize: row outputs missing");
+    PT_REQUIRE(!(flags & PT_MX_COL) || (q_col && s_col), "grouped MX quantize: col outputs missing");
+    PT_REQUIRE(col_alloc % 128 == 0 && col_alloc >= M, "grouped MX quantize: col_alloc must be the 128-multiple width of the col-wise buffers");
+    PT_REQUIRE(fmt == PT_E2M1 || !(flags & (PT_MX_ROW_RHT | PT_MX_COL_RHT)), "grouped MX quantize: RHT is an e2m1 option");
+    if (N == 0) return PT_OK;
+    PT_REQUIRE(x == nullptr ? M == 0 : aligned(x, 16), "grouped MX quantize: input must be 16-byte aligned");
+    MxArgs a{};
+    a.x = x; a.M = M; a.N = N; a.M_pad = col_alloc; a.N_pad = ceil_to(N, 128);
+    a.q_row = (uint8_t *) q_row; a.s_row = s_row; a.q_col = (uint8_t *) q_col; a.s_col = s_col;
+    a.group_offs = group_offs; a.poffs_row = padded_offs_row; a.poffs_col = padded_offs_col; a.num_groups = G;
+    const int64_t m_alloc = ceil_to(M + (int64_t) G * 128, 128);  // upper bound of the padded row space
+    PT_REQUIRE(m_alloc / kTileM <= 65535, "grouped MX quantize: too many rows");
+    cudaStream_t st = (cudaStream_t) stream;
+    if (x_dtype == PT_BF16) {
+        if (fmt == PT_E4M3) return launch_mx_grouped<__nv_bfloat16, PT_E4M3>(a, m_alloc, flags, st);
+        if (fmt == PT_E5M2) return launch_mx_grouped<__nv_bfloat16, PT_E5M2>(a, m_alloc, flags, st);
+        if (fmt == PT_E2M1) return launch_mx_grouped<__nv_bfloat16, PT_E2M1>(a, m_alloc, flags, st);
+    } else {
+        if (fmt == PT_E4M3) return launch_mx_grouped<__half, PT_E4M3>(a, m_alloc, flags, st);
+        if (fmt == PT_E5M2) return launch_mx_grouped<__half, PT_E5M2>(a, m_alloc, flags, st);
+        if (fmt == PT_E2M1) return launch_mx_grouped<__half, PT_E2M1>(a, m_alloc, flags, st);
+    }
+    return set_error(PT_ERR_INVALID, "grouped MX quantize: unknown format %d", fmt);
+}
 
 int pt_quantize_mx(const void *x, int x_dtype, int64_t G, int64_t M, int64_t N, int fmt, unsigned flags, void *q_row,
                    uint8_t *s_row, void *q_col, uint8_t *s_col, void *stream) {
@@ -341,7 +420,7 @@ int pt_quantize_mx(const void *x, int x_dtype, int64_t G, int64_t M, int64_t N, 
     if (M == 0 || N == 0) return PT_OK;
     PT_REQUIRE(x && aligned(x, 16), "MX quantize: input must be 16-byte aligned");
     PT_REQUIRE(G <= 65535, "MX quantize: batch too large");
-    MxArgs a;
+    MxArgs a{};
     a.x = x; a.M = M; a.N = N; a.M_pad = ceil_to(M, 128); a.N_pad = ceil_to(N, 128);
     PT_REQUIRE(a.M_pad / kTileM <= 65535, "MX quantize: M too large");
     a.q_row = (uint8_t *) q_row; a.s_row = s_row; a.q_col = (uint8_t *) q_col; a.s_col = s_col;

@@ -36,6 +36,8 @@ SIGNATURES = {
     "pt_compute_padded_group_offs": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
     "pt_quantize_mx": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_uint, c_void_p, c_void_p, c_void_p,
                                c_void_p, c_void_p]),
+    "pt_grouped_quantize_mx": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int, c_uint,
+                                       c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "pt_dequantize_mx": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_int, c_void_p]),
     "pt_transpose_2d": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "pt_gemm_fp8": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int64,
@@ -44,6 +46,9 @@ SIGNATURES = {
     "pt_grouped_gemm_fp8": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
                                     c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int, c_float, c_int, c_int,
                                     c_void_p, c_size_t, c_void_p, c_void_p]),
+    "pt_grouped_gemm_fp8_variable_k": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                                               c_int64, c_int64, c_int64, c_void_p, c_int, c_float, c_int, c_int, c_void_p,
+                                               c_size_t, c_void_p, c_void_p]),
     "pt_grouped_gemm_fp8_blockwise": (c_int, [c_void_p, c_int, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64,
                                               c_void_p, c_int, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64,
                                               c_int64, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p,

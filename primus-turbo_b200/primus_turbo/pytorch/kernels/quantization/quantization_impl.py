@@ -332,3 +332,81 @@ def transpose_2d(x: torch.Tensor) -> torch.Tensor:
         nv.check(nv.lib().pt_transpose_2d(nv.ptr(x), x.shape[0], x.shape[1], x.element_size(), nv.ptr(y),
                                            nv.stream(x.device)), "transpose_2d")
     return y
+
+
+# ------------------------------------------------------------------------------ grouped MX
+MX_GROUP_ROW_ALIGN = 32   # fp8 row-wise copy: each group padded to 32 rows (quantization.cpp:1098 of the reference)
+MX_GROUP_COL_ALIGN = 128  # col-wise copy: each group padded to 128 rows
+
+
+def _grouped_mx_quant(x, out_dtype, group_lens, group_offs, want_row, want_col, row_recipe, col_recipe):
+    nv.require_cuda(x, group_lens, group_offs)
+    for r in (row_recipe, col_recipe):
+        if r is not None and (r.shuffle_scale or r.shuffle_out or r.use_sr):
+            raise NotImplementedError("pre-shuffled layouts and stochastic rounding are not provided on B200")
+        if r is not None and r.use_2d_block:
+            raise NotImplementedError("2-D block scales are a weight option; grouped activations use 1-D blocks")
+    assert x.dim() == 2, "Input must be 2D"
+    x = x.contiguous()
+    fmt = nv.fmt_code(out_dtype)
+    fp4 = fmt == nv.PT_E2M1
+    M, N = x.shape
+    G = group_lens.numel()
+    lens = group_lens.to(torch.int64).contiguous()
+    offs = group_offs.to(torch.int64).contiguous()
+    N_pad = ceil_div(N, MX_ALIGN) * MX_ALIGN
+    div = 2 if fp4 else 1
+    row_align = 1 if fp4 else MX_GROUP_ROW_ALIGN
+    if fp4:
+        plens_row, poffs_row = lens, offs
+        rows_alloc = M
+    else:
+        plens_row, poffs_row = compute_padded_group_offs(lens, row_align)
+        rows_alloc = ceil_div(M + G * row_align, row_align) * row_align
+    plens_col, poffs_col = compute_padded_group_offs(lens, MX_GROUP_COL_ALIGN)
+    col_alloc = ceil_div(M + G * MX_GROUP_COL_ALIGN, MX_GROUP_COL_ALIGN) * MX_GROUP_COL_ALIGN
+    flags = 0
+    q_row = s_row = q_col = s_col = None
+    if want_row:
+        flags |= nv.PT_MX_ROW | (nv.PT_MX_ROW_RHT if row_recipe.use_rht else 0)
+        q_row = torch.empty((rows_alloc, N_pad // div), dtype=torch.uint8, device=x.device)
+        s_row = torch.empty((rows_alloc, N_pad // MX_BLOCK), dtype=torch.uint8, device=x.device)
+    if want_col:
+        flags |= nv.PT_MX_COL | (nv.PT_MX_COL_RHT if col_recipe.use_rht else 0)
+        q_col = torch.empty((N, col_alloc // div), dtype=torch.uint8, device=x.device)
+        s_col = torch.empty((N, col_alloc // MX_BLOCK), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        nv.check(nv.lib().pt_grouped_quantize_mx(nv.ptr(x), nv.src_code(x.dtype), M, N, G, nv.ptr(offs), nv.ptr(poffs_row),
+                                                  nv.ptr(poffs_col), fmt, flags, nv.ptr(q_row), nv.ptr(s_row), nv.ptr(q_col),
+                                                  nv.ptr(s_col), col_alloc, nv.stream(x.device)), "grouped_quantize_mx")
+    view = lambda t: None if t is None else t.view(out_dtype)
+    sview = lambda t: None if t is None else t.view(torch.float8_e8m0fnu)
+    return (view(q_row), sview(s_row), view(q_col), sview(s_col), plens_row, poffs_row, plens_col, poffs_col)
+
+
+def _grouped_quantize_mx_impl(x, out_dtype, axis, block_size, group_lens, group_offs, with_trans, scaling_recipe,
+                              scaling_recipe_for_trans):
+    assert block_size == MX_BLOCK, f"The block size must be {MX_BLOCK} for MX quantization"
+    scaling_recipe = ScalingRecipe() if scaling_recipe is None else scaling_recipe
+    if with_trans:
+        scaling_recipe_for_trans = ScalingRecipe() if scaling_recipe_for_trans is None else scaling_recipe_for_trans
+        return _grouped_mx_quant(x, out_dtype, group_lens, group_offs, True, True, scaling_recipe, scaling_recipe_for_trans)
+    assert axis in (0, 1), "The axis must be 0 or 1 when with_trans is False."
+    q_row, s_row, q_col, s_col, lr, orow, lc, ocol = _grouped_mx_quant(x, out_dtype, group_lens, group_offs, axis == 1,
+                                                                       axis == 0, scaling_recipe, scaling_recipe)
+    return (q_row, s_row, lr, orow) if axis == 1 else (q_col, s_col, lc, ocol)
+
+
+def grouped_quantize_mxfp8_impl(x, out_dtype, axis, block_size, group_lens, group_offs, with_trans=False,
+                                scaling_recipe=None, scaling_recipe_for_trans=None):
+    """(q, s, lens_padded, offs_padded), or with_trans: (q_row, s_row, q_col, s_col, lens_pad_row, offs_pad_row,
+    lens_pad_col, offs_pad_col).  Row copy: groups padded to 32 rows; col copy (transposed): groups padded to 128."""
+    return _grouped_quantize_mx_impl(x, out_dtype, axis, block_size, group_lens, group_offs, with_trans, scaling_recipe,
+                                     scaling_recipe_for_trans)
+
+
+def grouped_quantize_mxfp4_impl(x, out_dtype, axis, block_size, group_lens, group_offs, with_trans=False,
+                                scaling_recipe=None, scaling_recipe_for_trans=None):
+    """As the fp8 form with packed e2m1; the row copy is tight (row i = input row i)."""
+    return _grouped_quantize_mx_impl(x, out_dtype, axis, block_size, group_lens, group_offs, with_trans, scaling_recipe,
+                                     scaling_recipe_for_trans)

@@ -1,2 +1,3 @@
 from .gemm_fp8 import *  # noqa: F401,F403
+from .grouped_gemm_fp8 import *  # noqa: F401,F403
 from .quantization import *  # noqa: F401,F403
