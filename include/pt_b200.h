@@ -215,6 +215,23 @@ int pt_grouped_gemm_fp8_variable_k(const void *a, const void *a_scale, int a_fmt
                                    const int64_t *k_offs, int G, float beta, int block_n, int max_ctas, void *workspace,
                                    size_t workspace_bytes, int *status, void *stream);
 
+/* MXFP4 (packed e2m1, 32-element blocks, ue8m0 scales) forms of the three MX GEMMs above, on
+ * tcgen05.mma kind::mxf4.block_scale: a [M, K/2] bytes, a_scale [M, K/32]; b [N, K/2], b_scale [N, K/32]; K is the
+ * padded element count (multiple of 128).  Variable-K offsets count elements and are multiples of 256.
+ * Replace primus_turbo::gemm_fp4_impl / gemm_fp4_accum_impl (primus_turbo/pytorch/kernels/gemm/gemm_fp4_impl.py:340-441)
+ * and primus_turbo::grouped_gemm_fp4_impl / _variable_k_impl / _variable_k_accum_impl
+ * (primus_turbo/pytorch/kernels/grouped_gemm/grouped_gemm_fp4_impl.py:430-). */
+int pt_gemm_fp4(const void *a, const void *a_scale, const void *b, const void *b_scale, void *c, int c_dtype, int64_t M, int64_t N,
+                int64_t K, float beta, int block_n, void *workspace, size_t workspace_bytes, int *status, void *stream);
+int pt_grouped_gemm_fp4(const void *a, const void *a_scale, const void *b, const void *b_scale, void *c, int c_dtype, int64_t a_rows,
+                        int64_t c_rows, int64_t N, int64_t K, const int64_t *group_offs_read, const int64_t *group_offs_write, int G,
+                        float beta, int block_n, int max_ctas, void *workspace, size_t workspace_bytes, int *status, void *stream);
+int pt_grouped_gemm_fp4_variable_k(const void *a, const void *a_scale, const void *b, const void *b_scale, void *c, int c_dtype,
+                                   int64_t M, int64_t N, int64_t K_total, const int64_t *k_offs, int G, float beta, int block_n,
+                                   int max_ctas, void *workspace, size_t workspace_bytes, int *status, void *stream);
+/* Scratch bytes of the FP4 GEMMs (grouped: 0 dense, 1 grouped, 2 variable-K), cf. pt_gemm_fp8_workspace_bytes. */
+size_t pt_gemm_fp4_workspace_bytes(int64_t c_rows, int64_t N, int64_t K, int G, int grouped, int block_n);
+
 /* FP8 GEMM with fp32 128-block scales along the contraction (BLOCKWISE granularity): dense (G = 1, offsets null),
  * grouped by rows, or grouped with a per-group contraction range ("variable K", the grouped wgrad):
  *   C[m, n] = sum_kb ( sum_{k in kb} A[m, k] B[n, k] ) * sa(m, kb) * sb(n, kb),   kb = 128-wide block of k.

@@ -34,7 +34,8 @@ constexpr int kGemmThreads = 32 * (2 + kNumEpiWarps);
 constexpr int kEpiWarp0 = 2;
 constexpr int kStagePitchMax = 128;  // staging row pitch (bytes) of the epilogue, fp32 worst case
 
-enum GemmMode { GEMM_TENSOR = 0, GEMM_ROW = 1, GEMM_MX = 3 };
+enum GemmMode { GEMM_TENSOR = 0, GEMM_ROW = 1, GEMM_MX = 3, GEMM_MXF4 = 4 };
+constexpr bool mode_is_mx(int m) { return m == GEMM_MX || m == GEMM_MXF4; }
 
 struct GemmParams {
     int64_t M;             // rows of A / C (all groups)
@@ -58,17 +59,21 @@ struct GemmParams {
     int raster_m;               // row blocks per raster band
 };
 
-template <int BLOCK_N, bool MX> struct GemmCfg {
+// F4: packed e2m1 operands.  A 128-byte stage row then holds 256 elements = two 128-element scale blocks, so every
+// scale quantity per stage doubles (kSfPerStage) and one tcgen05.mma consumes 64 elements with two scales per row.
+template <int BLOCK_N, bool MX, bool F4 = false> struct GemmCfg {
     static constexpr int kSfbBlocks = (BLOCK_N + 127) / 128;
-    static constexpr int kSfColsOne = 4 + 4 * kSfbBlocks;       // SFA block + SFB blocks of one K step
-    static constexpr int kSfCols = MX ? 2 * kSfColsOne : 0;         // double buffered so tcgen05.cp of step i+1 need not wait for step i
+    static constexpr int kSfPerStage = F4 ? 2 : 1;
+    static constexpr int kSfColsHalf = 4 + 4 * kSfbBlocks;          // SFA block + SFB blocks of one 128-element scale block
+    static constexpr int kSfColsOne = kSfColsHalf * kSfPerStage;    // ... of one stage
+    static constexpr int kSfCols = MX ? (F4 ? 1 : 2) * kSfColsOne : 0;  // fp8: double buffered (it fits); fp4: single
     static constexpr int kAccStages = (2 * BLOCK_N + kSfCols <= 512) ? 2 : 1;
     static constexpr int kTmemColsNeeded = kAccStages * BLOCK_N + kSfCols;
     static constexpr int kTmemCols = kTmemColsNeeded <= 32 ? 32 : kTmemColsNeeded <= 64 ? 64 : kTmemColsNeeded <= 128 ? 128
                                      : kTmemColsNeeded <= 256 ? 256 : 512;
     static constexpr int kABytes = BLOCK_M * BLOCK_K;
     static constexpr int kBBytes = BLOCK_N * BLOCK_K;
-    static constexpr int kSfBytes = MX ? 512 * (1 + kSfbBlocks) : 0;
+    static constexpr int kSfBytes = MX ? 512 * (1 + kSfbBlocks) * kSfPerStage : 0;
     static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
     static constexpr int kEpiBytes = kNumEpiWarps * 32 * kStagePitchMax;
     static constexpr int kBarBytes = 1024;
@@ -90,7 +95,7 @@ struct RetileArgs {
     const uint8_t *src;
     uint8_t *dst;
     int64_t src_rows, sf_ld;  // rows of src, bytes per row (K / 32)
-    int num_kb, is_b;
+    int num_kb, is_b;         // num_kb: 512-byte blocks to produce per row block (those past sf_ld / 4 are zero)
     const int64_t *offs_read, *offs_write;
     int G;
     int64_t M;
@@ -136,7 +141,7 @@ __global__ void __launch_bounds__(128) sf_retile_kernel(RetileArgs a) {
         for (int r = warp; r < 128; r += 4) {
             const int64_t row = row_start + r;
             uint32_t w = 0;
-            if (r < rows_in_block && row < a.src_rows && lane < nkb)
+            if (r < rows_in_block && row < a.src_rows && lane < nkb && (kb0 + lane) * 4 < a.sf_ld)
                 w = __ldg(reinterpret_cast<const uint32_t *>(a.src + row * a.sf_ld) + kb0 + lane);
             s_words[r][lane] = w;
         }
@@ -153,8 +158,10 @@ __global__ void __launch_bounds__(128) sf_retile_kernel(RetileArgs a) {
 template <int BLOCK_N, int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
-    constexpr bool MX = MODE == GEMM_MX;
-    using Cfg = GemmCfg<BLOCK_N, MX>;
+    constexpr bool MX = mode_is_mx(MODE);
+    constexpr bool F4 = MODE == GEMM_MXF4;
+    using Cfg = GemmCfg<BLOCK_N, MX, F4>;
+    constexpr int kSfP = Cfg::kSfPerStage;
     constexpr int kStages = Cfg::kStages;
     constexpr int kAccStages = Cfg::kAccStages;
 
@@ -216,9 +223,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     int gi, m_blk, n_blk;
     bool ok = true;
     auto k_range = [&](int g, int &kb_begin, int &kb_count) {
-        if (p.koffs) {
-            kb_begin = (int) (p.koffs[g] / BLOCK_K);
-            kb_count = (int) ((p.koffs[g + 1] - p.koffs[g]) / BLOCK_K);
+        if (p.koffs) {  // offsets count elements; a stage holds 128 (fp8) or 256 (packed fp4) of them
+            constexpr int kElemsPerStage = F4 ? 2 * BLOCK_K : BLOCK_K;
+            kb_begin = (int) (p.koffs[g] / kElemsPerStage);
+            kb_count = (int) ((p.koffs[g + 1] - p.koffs[g]) / kElemsPerStage);
         } else {
             kb_begin = 0;
             kb_count = num_k_blocks;
@@ -239,8 +247,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 if constexpr (MX) {
                     const int64_t a_rb = p.koffs ? m_blk : s_tile_start[gi] / num_n_blocks + m_blk;
                     const int64_t b_rb = ((p.koffs ? 0 : (int64_t) gi * num_n_blocks) + n_blk) * Cfg::kSfbBlocks;
-                    sfa_blk = p.sfa_tiled + (a_rb * num_k_blocks + kb_begin) * 512;
-                    sfb_blk = p.sfb_tiled + (b_rb * num_k_blocks + kb_begin) * 512;
+                    sfa_blk = p.sfa_tiled + (a_rb * num_k_blocks + kb_begin) * kSfP * 512;
+                    sfb_blk = p.sfb_tiled + (b_rb * num_k_blocks + kb_begin) * kSfP * 512;
                 }
                 for (int kb = 0; kb < kb_count; ++kb) {
                     if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
@@ -248,11 +256,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     tma_load_2d(smem_a + stage * Cfg::kABytes, &tmap_a, &full_bar[stage], (kb_begin + kb) * BLOCK_K, (int) a_row0);
                     tma_load_2d(smem_b + stage * Cfg::kBBytes, &tmap_b, &full_bar[stage], (kb_begin + kb) * BLOCK_K, (int) b_row0);
                     if constexpr (MX) {
+                        // per stage: kSfP consecutive 512-byte blocks of A (one copy), and of each 128-row block of B
                         uint8_t *sf = smem_sf + stage * Cfg::kSfBytes;
-                        bulk_load(sf, sfa_blk + (int64_t) kb * 512, 512, &full_bar[stage]);
+                        bulk_load(sf, sfa_blk + (int64_t) kb * kSfP * 512, kSfP * 512, &full_bar[stage]);
 #pragma unroll
                         for (int j = 0; j < Cfg::kSfbBlocks; ++j)
-                            bulk_load(sf + 512 * (1 + j), sfb_blk + ((int64_t) j * num_k_blocks + kb) * 512, 512, &full_bar[stage]);
+                            bulk_load(sf + kSfP * 512 * (1 + j), sfb_blk + ((int64_t) j * num_k_blocks + kb) * kSfP * 512, kSfP * 512,
+                                      &full_bar[stage]);
                     }
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
@@ -263,8 +273,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (elect_one()) {
             constexpr uint32_t kIdescPlainShape = 0;
             (void) kIdescPlainShape;
-            const uint32_t idesc = MX ? idesc_block_scaled(p.a_fmt, p.b_fmt, BLOCK_M, BLOCK_N)
-                                      : idesc_f8(p.a_fmt, p.b_fmt, BLOCK_M, BLOCK_N);
+            const uint32_t idesc = F4 ? idesc_block_scaled(1, 1, BLOCK_M, BLOCK_N)   // kind::mxf4: format code 1 = e2m1
+                                   : MX ? idesc_block_scaled(p.a_fmt, p.b_fmt, BLOCK_M, BLOCK_N)
+                                        : idesc_f8(p.a_fmt, p.b_fmt, BLOCK_M, BLOCK_N);
             uint32_t stage = 0, phase = 0, acc_stage = 0, acc_phase = 0, sf_buf = 0;
             for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
                 int kb_begin, kb_count;
@@ -279,11 +290,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     const uint32_t sfa_cur = tmem_sfa + sf_buf * Cfg::kSfColsOne;
                     const uint32_t sfb_cur = tmem_sfb + sf_buf * Cfg::kSfColsOne;
                     if constexpr (MX) {
+                        // shared memory per stage: [A: kSfP blocks][B block 0: kSfP blocks][B block 1: ...];
+                        // TMEM per stage: for each scale block h: [A 4 cols][B 4 cols per 128 rows]
                         const uint32_t sf_addr = smem_u32(smem_sf + stage * Cfg::kSfBytes);
-                        tc_cp_sf(sfa_cur, smem_desc_sf(sf_addr));
 #pragma unroll
-                        for (int j = 0; j < Cfg::kSfbBlocks; ++j) tc_cp_sf(sfb_cur + 4 * j, smem_desc_sf(sf_addr + 512 * (1 + j)));
-                        sf_buf ^= 1;
+                        for (int h = 0; h < kSfP; ++h) {
+                            tc_cp_sf(sfa_cur + h * Cfg::kSfColsHalf, smem_desc_sf(sf_addr + 512 * h));
+#pragma unroll
+                            for (int j = 0; j < Cfg::kSfbBlocks; ++j)
+                                tc_cp_sf(sfb_cur + h * Cfg::kSfColsHalf + 4 * j, smem_desc_sf(sf_addr + kSfP * 512 * (1 + j) + 512 * h));
+                        }
+                        if constexpr (!F4) sf_buf ^= 1;
                     }
                     const uint64_t a_desc = smem_desc_sw128(smem_u32(smem_a + stage * Cfg::kABytes));
                     const uint64_t b_desc = smem_desc_sw128(smem_u32(smem_b + stage * Cfg::kBBytes));
@@ -291,7 +308,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
                         const uint64_t adv = (uint64_t) ((k * UMMA_K) >> 4);
                         const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-                        if constexpr (MX)
+                        if constexpr (F4)  // 64 elements, two scales per row: scale block k / 2, bytes (k % 2) * 2 .. +1
+                            mma_mxf4(d_tmem, a_desc + adv, b_desc + adv, idesc_sf_ids(idesc, (k & 1) * 2, (k & 1) * 2),
+                                     sfa_cur + (k >> 1) * Cfg::kSfColsHalf, sfb_cur + (k >> 1) * Cfg::kSfColsHalf, accumulate);
+                        else if constexpr (MX)
                             mma_mxf8(d_tmem, a_desc + adv, b_desc + adv, idesc_sf_ids(idesc, k, k), sfa_cur, sfb_cur, accumulate);
                         else
                             mma_f8(d_tmem, a_desc + adv, b_desc + adv, idesc, accumulate);
@@ -431,6 +451,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 // ------------------------------------------------------------------------------------------------ host side
 struct MxScales {
     const uint8_t *sfa, *sfb;  // raw [rows, K/32]
+    int64_t sf_ld;             // bytes per scale row
     void *workspace;
     size_t workspace_bytes;
 };
@@ -445,16 +466,16 @@ static size_t mx_workspace_bytes(int64_t c_rows, int64_t N, int64_t K, int G, bo
 template <int BLOCK_N, int MODE>
 static int launch_gemm(const void *a, int64_t a_rows, const void *b, int64_t b_rows, GemmParams p, const MxScales &mx,
                        int max_ctas, int64_t max_tiles, cudaStream_t st) {
-    using Cfg = GemmCfg<BLOCK_N, MODE == GEMM_MX>;
-    if constexpr (MODE == GEMM_MX) {
+    using Cfg = GemmCfg<BLOCK_N, mode_is_mx(MODE), MODE == GEMM_MXF4>;
+    if constexpr (mode_is_mx(MODE)) {
         const bool grouped = p.offs_write != nullptr && !p.koffs;
         const int sf_groups = p.koffs ? 1 : p.G;  // variable-K: one shared A and one shared B
-        const size_t need = mx_workspace_bytes(p.M, p.N, p.K, sf_groups, grouped, BLOCK_N);
+        const size_t need = mx_workspace_bytes(p.M, p.N, p.K, sf_groups, grouped, BLOCK_N) * Cfg::kSfPerStage;
         PT_REQUIRE(mx.workspace && mx.workspace_bytes >= need && aligned(mx.workspace, 16),
                    "MX GEMM: workspace of %zu bytes (16-byte aligned) required, got %zu", need, mx.workspace_bytes);
-        const int num_kb = (int) ceil_div(p.K, BLOCK_K);
+        const int num_kb = (int) ceil_div(p.K, BLOCK_K) * Cfg::kSfPerStage;  // scale blocks per row block
         RetileArgs ra{};
-        ra.src = mx.sfa; ra.dst = (uint8_t *) mx.workspace; ra.src_rows = a_rows; ra.sf_ld = p.K / 32; ra.num_kb = num_kb;
+        ra.src = mx.sfa; ra.dst = (uint8_t *) mx.workspace; ra.src_rows = a_rows; ra.sf_ld = mx.sf_ld; ra.num_kb = num_kb;
         ra.is_b = 0; ra.offs_read = grouped ? p.offs_read : nullptr; ra.offs_write = grouped ? p.offs_write : nullptr;
         ra.G = sf_groups; ra.M = p.M;
         ra.num_row_blocks = ceil_div(p.M, BLOCK_M) + (grouped ? p.G : 0);
@@ -490,7 +511,7 @@ static int launch_gemm(const void *a, int64_t a_rows, const void *b, int64_t b_r
     return PT_OK;
 }
 
-static int default_block_n(int mode, int64_t N) { return N <= 128 ? 128 : (mode == GEMM_MX ? 240 : 256); }
+static int default_block_n(int mode, int64_t N) { return N <= 128 ? 128 : (mode_is_mx(mode) ? 240 : 256); }
 
 template <int MODE>
 static int dispatch_block_n(int block_n, const void *a, int64_t a_rows, const void *b, int64_t b_rows, const GemmParams &p,
@@ -513,8 +534,11 @@ int gemm_fp8_host(const void *a, const void *a_scale, int a_fmt, const void *b, 
                   int block_n, int max_ctas, void *workspace, size_t workspace_bytes, int *status, void *stream) {
     PT_REQUIRE(M >= 0 && N >= 0 && K >= 0 && G >= 1 && G <= kMaxGroups, "GEMM: bad shape (M=%lld N=%lld K=%lld G=%d)",
                (long long) M, (long long) N, (long long) K, G);
-    PT_REQUIRE(a_fmt == PT_E4M3 || a_fmt == PT_E5M2, "GEMM: A format must be e4m3 or e5m2");
-    PT_REQUIRE(b_fmt == PT_E4M3 || b_fmt == PT_E5M2, "GEMM: B format must be e4m3 or e5m2");
+    const bool fp4 = a_fmt == PT_E2M1 || b_fmt == PT_E2M1;
+    PT_REQUIRE(!fp4 || (a_fmt == PT_E2M1 && b_fmt == PT_E2M1 && granularity == PT_MX_BLOCKWISE),
+               "GEMM: e2m1 operands go together and take MX_BLOCKWISE scales");
+    PT_REQUIRE(fp4 || a_fmt == PT_E4M3 || a_fmt == PT_E5M2, "GEMM: A format must be e4m3, e5m2 or e2m1");
+    PT_REQUIRE(fp4 || b_fmt == PT_E4M3 || b_fmt == PT_E5M2, "GEMM: B format must be e4m3, e5m2 or e2m1");
     PT_REQUIRE(c_dtype == PT_BF16 || c_dtype == PT_F16 || c_dtype == PT_F32, "GEMM: bad output dtype");
     PT_REQUIRE(beta == 0.f || beta == 1.f, "GEMM: beta must be 0 or 1");
     PT_REQUIRE((offs_read == nullptr) == (offs_write == nullptr) || offs_write, "GEMM: write offsets required with read offsets");
@@ -535,7 +559,7 @@ int gemm_fp8_host(const void *a, const void *a_scale, int a_fmt, const void *b, 
     p.raster_m = raster_rows(a_rows_total, K);
     cudaStream_t st = (cudaStream_t) stream;
     const int64_t b_rows = k_offs ? N : (int64_t) G * N;
-    MxScales mx{nullptr, nullptr, workspace, workspace_bytes};
+    MxScales mx{nullptr, nullptr, 0, workspace, workspace_bytes};
     switch (granularity) {
     case PT_TENSORWISE:
         p.sa = (const float *) a_scale; p.sb = (const float *) b_scale;
@@ -545,8 +569,13 @@ int gemm_fp8_host(const void *a, const void *a_scale, int a_fmt, const void *b, 
         return dispatch_block_n<GEMM_ROW>(block_n, a, a_rows_total, b, b_rows, p, mx, max_ctas, st);
     case PT_MX_BLOCKWISE:
         PT_REQUIRE(K % 128 == 0, "MX GEMM: K must be padded to a multiple of 128 (got %lld)", (long long) K);
-        mx.sfa = (const uint8_t *) a_scale; mx.sfb = (const uint8_t *) b_scale;
+        mx.sfa = (const uint8_t *) a_scale; mx.sfb = (const uint8_t *) b_scale; mx.sf_ld = K / 32;
         PT_REQUIRE(aligned(a_scale, 4) && aligned(b_scale, 4), "MX GEMM: scale pointers must be 4-byte aligned");
+        if (a_fmt == PT_E2M1) {
+            // packed e2m1: the kernel's contraction extent is in bytes (two elements each)
+            p.K = (int) (K / 2);
+            return dispatch_block_n<GEMM_MXF4>(block_n, a, a_rows_total, b, b_rows, p, mx, max_ctas, st);
+        }
         return dispatch_block_n<GEMM_MX>(block_n, a, a_rows_total, b, b_rows, p, mx, max_ctas, st);
     default:
         return set_error(PT_ERR_UNSUPPORTED, "GEMM: granularity %d is not handled by this kernel", granularity);
@@ -558,6 +587,14 @@ int gemm_fp8_host(const void *a, const void *a_scale, int a_fmt, const void *b, 
 using namespace ptb;
 
 extern "C" {
+
+size_t pt_gemm_fp4_workspace_bytes(int64_t c_rows, int64_t N, int64_t K, int G, int grouped, int block_n) {
+    if (c_rows <= 0 || N <= 0 || K <= 0 || G < 1) return 0;
+    if (block_n == 0) block_n = default_block_n(GEMM_MXF4, N);
+    // K / 2 bytes per row -> ceil(K / 256) stages, two 512-byte scale blocks each
+    if (grouped == 2) return 2 * mx_workspace_bytes(c_rows, N, K / 2, 1, false, block_n);
+    return 2 * mx_workspace_bytes(c_rows, N, K / 2, G, grouped != 0, block_n);
+}
 
 size_t pt_gemm_fp8_workspace_bytes(int granularity, int64_t c_rows, int64_t N, int64_t K, int G, int grouped, int block_n) {
     if (granularity != PT_MX_BLOCKWISE || c_rows <= 0 || N <= 0 || K <= 0 || G < 1) return 0;
@@ -581,6 +618,29 @@ int pt_grouped_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const voi
     return gemm_fp8_host(a, a_scale, a_fmt, b, b_scale, b_fmt, c, c_dtype, N, granularity, c_rows, N, K, beta,
                          group_offs_read, group_offs_write, nullptr, G, a_rows, block_n, max_ctas, workspace, workspace_bytes,
                          status, stream);
+}
+
+int pt_gemm_fp4(const void *a, const void *a_scale, const void *b, const void *b_scale, void *c, int c_dtype, int64_t M, int64_t N,
+                int64_t K, float beta, int block_n, void *workspace, size_t workspace_bytes, int *status, void *stream) {
+    return gemm_fp8_host(a, a_scale, PT_E2M1, b, b_scale, PT_E2M1, c, c_dtype, N, PT_MX_BLOCKWISE, M, N, K, beta, nullptr, nullptr,
+                         nullptr, 1, M, block_n, 0, workspace, workspace_bytes, status, stream);
+}
+
+int pt_grouped_gemm_fp4(const void *a, const void *a_scale, const void *b, const void *b_scale, void *c, int c_dtype, int64_t a_rows,
+                        int64_t c_rows, int64_t N, int64_t K, const int64_t *group_offs_read, const int64_t *group_offs_write, int G,
+                        float beta, int block_n, int max_ctas, void *workspace, size_t workspace_bytes, int *status, void *stream) {
+    PT_REQUIRE(group_offs_write, "grouped FP4 GEMM: group offsets required");
+    return gemm_fp8_host(a, a_scale, PT_E2M1, b, b_scale, PT_E2M1, c, c_dtype, N, PT_MX_BLOCKWISE, c_rows, N, K, beta,
+                         group_offs_read, group_offs_write, nullptr, G, a_rows, block_n, max_ctas, workspace, workspace_bytes,
+                         status, stream);
+}
+
+int pt_grouped_gemm_fp4_variable_k(const void *a, const void *a_scale, const void *b, const void *b_scale, void *c, int c_dtype,
+                                   int64_t M, int64_t N, int64_t K_total, const int64_t *k_offs, int G, float beta, int block_n,
+                                   int max_ctas, void *workspace, size_t workspace_bytes, int *status, void *stream) {
+    PT_REQUIRE(k_offs, "variable-K FP4 GEMM: contraction offsets required");
+    return gemm_fp8_host(a, a_scale, PT_E2M1, b, b_scale, PT_E2M1, c, c_dtype, N, PT_MX_BLOCKWISE, M, N, K_total, beta, nullptr,
+                         nullptr, k_offs, G, M, block_n, max_ctas, workspace, workspace_bytes, status, stream);
 }
 
 int pt_grouped_gemm_fp8_variable_k(const void *a, const void *a_scale, int a_fmt, const void *b, const void *b_scale, int b_fmt,

@@ -346,7 +346,7 @@ static int launch_mx(const MxArgs &a, int64_t G, unsigned flags, cudaStream_t st
 
 template <typename T, int FMT>
 static int launch_mx_grouped(const MxArgs &a, int64_t m_alloc, unsigned flags, cudaStream_t st) {
-    dim3 grid((unsigned) (a.N_pad / kTileN), (unsigned) (m_alloc / kTileM), 1u);
+    dim3 grid((unsigned) (a.N_pad / kTileN), (unsigned) (m_alloc / kTileM), 1u);  // tiles past padded_offs_col[G] return at once
     const bool row = flags & PT_MX_ROW, col = flags & PT_MX_COL;
     const bool rrht = flags & PT_MX_ROW_RHT, crht = flags & PT_MX_COL_RHT;
 #define PT_MXG_CASE(R, C, RR, CR)                                                                     \
@@ -393,7 +393,7 @@ int pt_grouped_quantize_mx(const void *x, int x_dtype, int64_t M, int64_t N, int
     a.x = x; a.M = M; a.N = N; a.M_pad = col_alloc; a.N_pad = ceil_to(N, 128);
     a.q_row = (uint8_t *) q_row; a.s_row = s_row; a.q_col = (uint8_t *) q_col; a.s_col = s_col;
     a.group_offs = group_offs; a.poffs_row = padded_offs_row; a.poffs_col = padded_offs_col; a.num_groups = G;
-    const int64_t m_alloc = ceil_to(M + (int64_t) G * 128, 128);  // upper bound of the padded row space
+    const int64_t m_alloc = col_alloc;  // the padded row space never exceeds the width the caller allocated for it
     PT_REQUIRE(m_alloc / kTileM <= 65535, "grouped MX quantize: too many rows");
     cudaStream_t st = (cudaStream_t) stream;
     if (x_dtype == PT_BF16) {

@@ -363,8 +363,10 @@ def _grouped_mx_quant(x, out_dtype, group_lens, group_offs, want_row, want_col, 
     else:
         plens_row, poffs_row = compute_padded_group_offs(lens, row_align)
         rows_alloc = ceil_div(M + G * row_align, row_align) * row_align
-    plens_col, poffs_col = compute_padded_group_offs(lens, MX_GROUP_COL_ALIGN)
-    col_alloc = ceil_div(M + G * MX_GROUP_COL_ALIGN, MX_GROUP_COL_ALIGN) * MX_GROUP_COL_ALIGN
+    # fp4: a GEMM stage spans 256 elements of the contraction, so token segments are padded to 256
+    col_align = 2 * MX_GROUP_COL_ALIGN if fp4 else MX_GROUP_COL_ALIGN
+    plens_col, poffs_col = compute_padded_group_offs(lens, col_align)
+    col_alloc = ceil_div(M + G * col_align, col_align) * col_align
     flags = 0
     q_row = s_row = q_col = s_col = None
     if want_row:

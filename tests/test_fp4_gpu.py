@@ -1,0 +1,129 @@
+"""MXFP4 GEMMs (tcgen05 kind::mxf4.block_scale): against the fp32 matmul of the dequantized operands (stated tolerance:
+relative Frobenius error <= 5e-2; with fp32 output the only difference is summation order) and the reference's SNR
+gates against the unquantized product: > 10 dB dense (tests/pytorch/ops/test_gemm_fp4.py:120), > 8 dB grouped
+(tests/pytorch/ops/test_grouped_gemm_fp4.py:55-57)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import gemm as og
+from oracle import quant as oq
+from tests._util import f32, make, u8
+
+pytestmark = pytest.mark.gpu
+F4 = torch.float4_e2m1fn_x2
+
+
+def snr(x, ref):
+    x, ref = x.float(), ref.float()
+    return float(10 * torch.log10(ref.pow(2).sum() / (x - ref).pow(2).sum().clamp_min(1e-30)))
+
+
+@pytest.fixture(scope="module")
+def m():
+    import primus_turbo.pytorch as turbo
+    from primus_turbo.pytorch.core.low_precision import ScalingRecipe
+    from primus_turbo.pytorch.kernels import _native as nv
+    from primus_turbo.pytorch.kernels.gemm import gemm_fp4_impl as g4
+    from primus_turbo.pytorch.kernels.grouped_gemm import grouped_gemm_fp4_impl as gg4
+    from primus_turbo.pytorch.kernels.quantization import quantization_impl as qi
+    return dict(turbo=turbo, nv=nv, g4=g4, gg4=gg4, qi=qi, SR=ScalingRecipe)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 256), (256, 512, 384), (255, 520, 576), (1024, 2048, 1024), (512, 240, 128)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_fp4_dense(m, M, N, K, out_dtype):
+    qi, g4, nv, SR = m["qi"], m["g4"], m["nv"], m["SR"]
+    a, b = make((M, K), torch.bfloat16, 61, "outlier"), make((N, K), torch.bfloat16, 62, "weight")
+    qa, sa = qi.quantize_mxfp4_impl(a, F4, 1, 32)
+    qb, sb = qi.quantize_mxfp4_impl(b, F4, 1, 32, scaling_recipe=SR(use_2d_block=True))
+    c = g4.gemm_fp4_impl(qa, sa, False, qb, sb, True, out_dtype, False)
+    nv.check_status(c.device)
+    ref = og.gemm_nt(oq.dequantize_mx(u8(qa), u8(sa), "e2m1"), oq.dequantize_mx(u8(qb), u8(sb), "e2m1"))
+    err = og.rel_frobenius(f32(c), ref)
+    assert err <= (1e-5 if out_dtype == torch.float32 else 5e-2), err
+    assert og.snr_db(f32(c), f32(a) @ f32(b).T) > 10
+
+
+def test_gemm_fp4_accumulate_and_transposed_output(m):
+    qi, g4, nv = m["qi"], m["g4"], m["nv"]
+    a, b = make((256, 256), torch.bfloat16, 63), make((384, 256), torch.bfloat16, 64)
+    qa, sa = qi.quantize_mxfp4_impl(a, F4, 1, 32)
+    qb, sb = qi.quantize_mxfp4_impl(b, F4, 1, 32)
+    ref = og.gemm_nt(oq.dequantize_mx(u8(qa), u8(sa), "e2m1"), oq.dequantize_mx(u8(qb), u8(sb), "e2m1"))
+    out = torch.ones(256, 384, dtype=torch.float32, device="cuda")
+    g4.gemm_fp4_accum_impl(qa, sa, False, qb, sb, True, out, False)
+    ct = g4.gemm_fp4_impl(qa, sa, False, qb, sb, True, torch.float32, True)
+    nv.check_status(out.device)
+    assert og.rel_frobenius(f32(out), ref + 1.0) <= 1e-5
+    assert og.rel_frobenius(f32(ct), ref.T) <= 1e-5
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 256), (512, 2048, 1024), (255, 512, 576)])
+def test_gemm_fp4_op_fwd_bwd(m, M, N, K):
+    turbo = m["turbo"]
+    torch.manual_seed(5)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    a_ref, b_ref = a.detach().clone().requires_grad_(), b.detach().clone().requires_grad_()
+    out = turbo.ops.gemm_fp4(a, b, trans_b=True)
+    ref = a_ref @ b_ref.t()
+    g = torch.randn_like(ref)
+    out.backward(g)
+    ref.backward(g)
+    assert snr(out.detach(), ref.detach()) > 10
+    assert snr(a.grad, a_ref.grad) > 10
+    assert snr(b.grad, b_ref.grad) > 10
+
+
+@pytest.mark.parametrize("lens", [[128, 256, 64], [100, 0, 300, 29], [512] * 8])
+def test_grouped_gemm_fp4_kernels(m, lens):
+    qi, gg4, nv, SR = m["qi"], m["gg4"], m["nv"], m["SR"]
+    lens_t = torch.tensor(lens, dtype=torch.int64, device="cuda")
+    offs = torch.zeros(len(lens) + 1, dtype=torch.int64, device="cuda")
+    offs[1:] = torch.cumsum(lens_t, 0)
+    G, M, K, N = len(lens), int(sum(lens)), 256, 320
+    a = make((M, K), torch.bfloat16, 65, "outlier")
+    w = make((G, N, K), torch.bfloat16, 66, "weight")
+    a_row, a_s_row, a_col, a_s_col, _, orow, lcol, ocol = qi.grouped_quantize_mxfp4_impl(a, F4, None, 32, lens_t, offs, with_trans=True)
+    w_row, w_s_row = qi.quantize_mxfp4_impl(w, F4, 2, 32, scaling_recipe=SR(use_2d_block=True))
+    out = gg4.grouped_gemm_fp4_impl(a_row, w_row, a_s_row, w_s_row, lens_t, orow, out_dtype=torch.float32, group_offs_out=offs)
+    nv.check_status(out.device)
+    da = oq.dequantize_mx(u8(a_row), u8(a_s_row), "e2m1")
+    dw = np.stack([oq.dequantize_mx(u8(w_row)[g], u8(w_s_row)[g], "e2m1") for g in range(G)])
+    assert og.rel_frobenius(f32(out), og.grouped_gemm_nt(da, dw, np.array(lens))) <= 1e-5
+    # variable-K over the 256-padded token segments
+    go = make((M, N), torch.bfloat16, 67)
+    g_row, g_s_row, g_col, g_s_col, _, _, lcol, ocol = qi.grouped_quantize_mxfp4_impl(go, F4, None, 32, lens_t, offs, with_trans=True)
+    wg = gg4.grouped_gemm_fp4_variable_k_impl(g_col, a_col, g_s_col, a_s_col, lcol, ocol, torch.float32)
+    nv.check_status(out.device)
+    tot = int(ocol[-1])
+    dgc = oq.dequantize_mx(u8(g_col)[:, :tot // 2], u8(g_s_col)[:, :tot // 32], "e2m1")
+    dac = oq.dequantize_mx(u8(a_col)[:, :tot // 2], u8(a_s_col)[:, :tot // 32], "e2m1")
+    refw = og.grouped_gemm_variable_k(dgc.T, dac.T, lcol.cpu().numpy())
+    assert wg.shape == (G, N, K)
+    assert og.rel_frobenius(f32(wg), refw) <= 1e-5
+
+
+@pytest.mark.parametrize("lens", [[128, 256, 64], [100, 0, 300, 29], [512] * 8])
+def test_grouped_gemm_fp4_op(m, lens):
+    turbo = m["turbo"]
+    torch.manual_seed(6)
+    lens_t = torch.tensor(lens, dtype=torch.int64, device="cuda")
+    offs = [0] + list(np.cumsum(lens))
+    G, M, K, N = len(lens), int(sum(lens)), 512, 384
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    b = torch.randn(G, N, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    a_ref, b_ref = a.detach().clone().requires_grad_(), b.detach().clone().requires_grad_()
+    out = turbo.ops.grouped_gemm_fp4(a, b, lens_t, trans_b=True)
+    ref = torch.cat([a_ref[offs[g]:offs[g + 1]].float() @ b_ref[g].float().t() for g in range(G)]).to(torch.bfloat16)
+    go = torch.randn_like(ref)
+    out.backward(go)
+    ref.backward(go)
+    assert snr(out.detach(), ref.detach()) > 8
+    assert snr(a.grad, a_ref.grad) > 8
+    for g, n in enumerate(lens):
+        if n == 0:
+            assert float(b.grad[g].abs().max()) == 0.0
+        elif n >= 64:
+            assert snr(b.grad[g], b_ref.grad[g]) > 8

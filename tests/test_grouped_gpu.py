@@ -49,7 +49,8 @@ def test_grouped_mx_quantize(mods, dtype, lens):
     q_row, s_row, q_col, s_col, lr, orow, lc, ocol = impl(x, dtype, None, 32, lens_t, offs, with_trans=True)
     row_align = 1 if fmt == "e2m1" else 32
     wq_r, ws_r, wl_r, wo_r = oq.quantize_mx_grouped(f32(x), fmt, np.array(lens), 1, row_align=row_align)
-    wq_c, ws_c, wl_c, wo_c = oq.quantize_mx_grouped(f32(x), fmt, np.array(lens), 0)
+    col_align = 256 if fmt == "e2m1" else 128   # fp4: one GEMM stage spans 256 contraction elements
+    wq_c, ws_c, wl_c, wo_c = oq.quantize_mx_grouped(f32(x), fmt, np.array(lens), 0, col_align=col_align)
     assert np.array_equal(orow.cpu().numpy(), wo_r) and np.array_equal(ocol.cpu().numpy(), wo_c)
     assert np.array_equal(lr.cpu().numpy(), wl_r) and np.array_equal(lc.cpu().numpy(), wl_c)
     gq_r, gs_r, gq_c, gs_c = u8(q_row), u8(s_row), u8(q_col), u8(s_col)
