@@ -294,7 +294,7 @@ def main():
         "e2e": {"value": None if args.no_e2e else world * flops / (e2e_ms / 1e3) / 1e12, "unit": "TFLOPS",
                 "h2d_bytes_per_step": a_host.numel() * 2 + w_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
                 "ms_per_step": e2e_ms},
-        "gpu_launches": 3 * args.steps,
+        "gpu_launches": 5 * args.steps,  # per step: 2 dual quantize, 2 scale re-tile, 1 GEMM
     }
     if world == 1 and not args.no_cpu_baseline:
         cb = cpu_baseline(M, N, K, seed)

@@ -14,6 +14,8 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "gemm_common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace ptb {
 
@@ -58,9 +60,10 @@ template <int FMT> __device__ __forceinline__ uint2 mx_encode8(const float (&v)[
         o.x = (uint32_t) cvt2_e2m1(t[0], t[1]) | ((uint32_t) cvt2_e2m1(t[2], t[3]) << 8) |
               ((uint32_t) cvt2_e2m1(t[4], t[5]) << 16) | ((uint32_t) cvt2_e2m1(t[6], t[7]) << 24);
     } else {
-        const float lim = MxParams<FMT>::qmax * s.native;
+        // the reference clamps to +-qmax * scale first; the saturating convert below does the same for every
+        // non-NaN input (a NaN converts to the NaN code instead of -qmax)
 #pragma unroll
-        for (int i = 0; i < 8; ++i) t[i] = fminf(fmaxf(v[i], -lim), lim) * s.inv;
+        for (int i = 0; i < 8; ++i) t[i] = v[i] * s.inv;
         o.x = cvt4_fp8<FMT>(t[0], t[1], t[2], t[3]);
         o.y = cvt4_fp8<FMT>(t[4], t[5], t[6], t[7]);
     }
@@ -265,6 +268,222 @@ __global__ void __launch_bounds__(kMxThreads) mx_quant_kernel(MxArgs a) {
     }
 }
 
+// ------------------------------------------------------------------------------------------------ TMA-pipelined form
+// Same arithmetic and outputs as mx_quant_kernel for the non-grouped case, restructured so that input loads are
+// always in flight: persistent CTAs (three per SM), one producer thread streaming 128 x 64 tiles into a four-stage
+// shared-memory ring with cp.async.bulk.tensor (3-D map [G, M, N]; rows past M and columns past N arrive as zeros),
+// eight consumer warps quantizing one tile while the next three are on their way.  The first form issues its loads,
+// waits, computes and stores in sequence inside each CTA and reached 44 % of the copy bandwidth; it stays in use
+// for the grouped layout, whose row masking a plain TMA box cannot express.
+constexpr int kQStages = 4;
+constexpr int kQCtasPerSm = 3;
+constexpr int kQTileBytes = kTileM * kTileN * 2;
+constexpr int kQConsumerWarps = 8;
+constexpr int kQThreads = 32 * (1 + kQConsumerWarps);
+constexpr int kQSmemBytes = kQStages * kQTileBytes + 1024 + 1024;
+
+__device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *m, uint64_t *bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(sm100::smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(sm100::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+// 32 scaled values -> 32 fp8 codes (8 words) or 32 fp4 codes (4 words).  The reference's soft clamp to +-qmax*scale
+// is subsumed by the saturating convert (identical bytes for every non-NaN input; a NaN converts to the NaN code).
+template <int FMT> __device__ __forceinline__ void mx_encode32(const float (&v)[32], const MxScale &s, uint32_t (&w)[8]) {
+    if (s.byte == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = 0u;
+        return;
+    }
+    if constexpr (FMT == PT_E2M1) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float *t = &v[8 * i];
+            w[i] = (uint32_t) cvt2_e2m1(t[0] * s.inv, t[1] * s.inv) | ((uint32_t) cvt2_e2m1(t[2] * s.inv, t[3] * s.inv) << 8) |
+                   ((uint32_t) cvt2_e2m1(t[4] * s.inv, t[5] * s.inv) << 16) | ((uint32_t) cvt2_e2m1(t[6] * s.inv, t[7] * s.inv) << 24);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            w[i] = cvt4_fp8<FMT>(v[4 * i] * s.inv, v[4 * i + 1] * s.inv, v[4 * i + 2] * s.inv, v[4 * i + 3] * s.inv);
+    }
+}
+
+// Shared-memory tile as TMA writes it with the 128-byte swizzle: 128 rows of 128 bytes, the 16-byte chunk c of
+// row r stored at chunk position c ^ (r % 8).
+template <typename T> struct SwizzledTile {
+    const uint8_t *base;
+    __device__ __forceinline__ uint4 chunk(int row, int c) const {
+        return *reinterpret_cast<const uint4 *>(base + row * 128 + ((c ^ (row & 7)) << 4));
+    }
+    __device__ __forceinline__ uint32_t pair(int row, int col_pair) const {  // elements 2*col_pair, 2*col_pair + 1
+        const int c = col_pair >> 2;
+        return *reinterpret_cast<const uint32_t *>(base + row * 128 + ((c ^ (row & 7)) << 4) + ((col_pair & 3) << 2));
+    }
+};
+
+template <typename T, int FMT, bool ROW, bool COL, bool ROW2D, bool COL2D, bool ROWRHT, bool COLRHT>
+__global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
+    mx_quant_tma_kernel(const __grid_constant__ CUtensorMap tmap, MxArgs a, int tiles_n, int tiles_m, int64_t total_tiles, int *status) {
+    using namespace sm100;
+    constexpr bool kFp4 = FMT == PT_E2M1;
+    constexpr bool kNeed2D = (ROW && ROW2D) || (COL && COL2D);
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + kQStages * kQTileBytes);
+    uint64_t *empty_bar = full_bar + kQStages;
+    __shared__ unsigned s_amax2d[3][4][2];
+    __shared__ int s_abort;
+    volatile int *abort_flag = &s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < kQStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], kQConsumerWarps);
+        }
+        fence_barrier_init();
+        prefetch_tmap(&tmap);
+    }
+    if (threadIdx.x < 24) (&s_amax2d[0][0][0])[threadIdx.x] = 0u;
+    __syncthreads();
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            // 32-bit tile arithmetic: 64-bit divisions cost more instructions than quantizing the tile
+            const uint32_t per_g = (uint32_t) tiles_n * (uint32_t) tiles_m;
+            for (uint32_t t = blockIdx.x; t < (uint32_t) total_tiles; t += gridDim.x) {
+                const uint32_t g = t / per_g, rem = t - g * per_g;
+                const int tm = (int) (rem / (uint32_t) tiles_n), tn = (int) (rem - (uint32_t) tm * tiles_n);
+                if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
+                mbar_arrive_expect_tx(&full_bar[stage], kQTileBytes);
+                tma_load_3d(smem + stage * kQTileBytes, &tmap, &full_bar[stage], tn * kTileN, tm * kTileM, (int) g);
+                if (++stage == kQStages) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else {
+        const int tid = threadIdx.x - 32;
+        // row-wise work item: one 32-element block per thread (row tid / 2, block tid % 2)
+        const int r_row = tid >> 1, r_blk = tid & 1;
+        // col-wise work item: two adjacent columns x 16 rows per thread; lanes 2i, 2i+1 share a 32-row block
+        const int cw = warp - 1;
+        const int c_half = lane & 1, c_pair = ((cw & 1) << 4) | (lane >> 1), c_band = cw >> 1;
+        uint32_t stage = 0, phase = 0, tile_count = 0;
+        const uint32_t per_g = (uint32_t) tiles_n * (uint32_t) tiles_m;
+        for (uint32_t t = blockIdx.x; t < (uint32_t) total_tiles; t += gridDim.x, ++tile_count) {
+            const uint32_t gq = t / per_g, rem = t - gq * per_g;
+            const int tm = (int) (rem / (uint32_t) tiles_n), tn = (int) (rem - (uint32_t) tm * tiles_n);
+            const int64_t g = gq;
+            const int64_t m0 = (int64_t) tm * kTileM, n0 = (int64_t) tn * kTileN;
+            if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
+            const SwizzledTile<T> tile{smem + stage * kQTileBytes};
+            unsigned(*amax2d)[2] = s_amax2d[tile_count % 3];
+
+            // ---- this thread's row block: 64 bytes = chunks 4 * r_blk .. + 3 of row r_row
+            float rv[32];
+            float r_amax = 0.f;
+            if constexpr (ROW || kNeed2D) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint4 q = tile.chunk(r_row, 4 * r_blk + j);
+                    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        rv[8 * j + 2 * k] = Src<T>::to_f32((uint16_t) (w[k] & 0xFFFF));
+                        rv[8 * j + 2 * k + 1] = Src<T>::to_f32((uint16_t) (w[k] >> 16));
+                    }
+                }
+                if constexpr (ROW && ROWRHT) { rht16(rv); rht16(rv + 16); }
+#pragma unroll
+                for (int k = 0; k < 32; ++k) r_amax = fmaxf(r_amax, fabsf(rv[k]));
+            }
+            if constexpr (kNeed2D) {
+                // 32 x 32 tile maxima through shared memory (of the untransformed values; RHT and 2-D are never combined).
+                // The buffer of the tile after next is cleared here: every consumer has passed the previous tile's barrier.
+                if (tid < 8) (&s_amax2d[(tile_count + 1) % 3][0][0])[tid] = 0u;
+                float m = r_amax;  // lanes of a warp: 16 rows x 2 blocks; reduce over the rows (lane bits 1..4)
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+                if (lane < 2) atomicMax(&amax2d[r_row >> 5][r_blk], __float_as_uint(m));
+                asm volatile("bar.sync 1, %0;" ::"n"(kQConsumerWarps * 32));
+            }
+
+            if constexpr (ROW) {
+                const int64_t gm = m0 + r_row, gn = n0 + 32 * r_blk;
+                const float m = ROW2D ? __uint_as_float(amax2d[r_row >> 5][r_blk]) : r_amax;
+                const MxScale sc = mx_scale<FMT>(m, false);
+                uint32_t w[8];
+                mx_encode32<FMT>(rv, sc, w);
+                if (gm < a.M && gn < a.N_pad) {
+                    uint8_t *qr = a.q_row + g * a.qrow_gstride;
+                    if constexpr (kFp4) {
+                        *reinterpret_cast<uint4 *>(qr + (gm * a.N_pad + gn) / 2) = make_uint4(w[0], w[1], w[2], w[3]);
+                    } else {
+                        uint4 *dst = reinterpret_cast<uint4 *>(qr + gm * a.N_pad + gn);
+                        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                    }
+                    (a.s_row + g * a.srow_gstride)[gm * (a.N_pad / 32) + gn / 32] = sc.byte;
+                }
+            }
+
+            if constexpr (COL) {
+                // columns 2 c_pair, 2 c_pair + 1; rows c_band * 32 + c_half * 16 .. + 15
+                float c0[16], c1[16];
+#pragma unroll
+                for (int r = 0; r < 16; ++r) {
+                    const uint32_t w = tile.pair(c_band * 32 + c_half * 16 + r, c_pair);
+                    c0[r] = Src<T>::to_f32((uint16_t) (w & 0xFFFF));
+                    c1[r] = Src<T>::to_f32((uint16_t) (w >> 16));
+                }
+                if constexpr (COLRHT) { rht16(c0); rht16(c1); }
+                float m0c = 0.f, m1c = 0.f;
+                if constexpr (COL2D) {
+                    m0c = m1c = __uint_as_float(amax2d[c_band][c_pair >> 4]);
+                } else {
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) { m0c = fmaxf(m0c, fabsf(c0[r])); m1c = fmaxf(m1c, fabsf(c1[r])); }
+                    m0c = fmaxf(m0c, __shfl_xor_sync(0xffffffffu, m0c, 1));
+                    m1c = fmaxf(m1c, __shfl_xor_sync(0xffffffffu, m1c, 1));
+                }
+                const MxScale s0 = mx_scale<FMT>(m0c, false), s1 = mx_scale<FMT>(m1c, false);
+                const int64_t gc = n0 + 2 * c_pair;
+                const int64_t gm = m0 + c_band * 32 + c_half * 16;
+                if (gc < a.N) {  // N is a multiple of 32: both columns are in or out together
+                    uint8_t *qc = a.q_col + g * a.qcol_gstride;
+                    uint8_t *scl = a.s_col + g * a.scol_gstride;
+#pragma unroll
+                    for (int cc = 0; cc < 2; ++cc) {
+                        const float(&cv)[16] = cc ? c1 : c0;
+                        const MxScale &sc = cc ? s1 : s0;
+                        float t0[8], t1[8];
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) { t0[k] = cv[k]; t1[k] = cv[8 + k]; }
+                        const uint2 o0 = mx_encode8<FMT>(t0, sc), o1 = mx_encode8<FMT>(t1, sc);
+                        if constexpr (kFp4) *reinterpret_cast<uint2 *>(qc + ((gc + cc) * a.M_pad + gm) / 2) = make_uint2(o0.x, o1.x);
+                        else *reinterpret_cast<uint4 *>(qc + (gc + cc) * a.M_pad + gm) = make_uint4(o0.x, o0.y, o1.x, o1.y);
+                        if (c_half == 0) scl[(gc + cc) * (a.M_pad / 32) + gm / 32] = sc.byte;
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[stage]);  // this warp no longer reads the stage
+            if (++stage == kQStages) { stage = 0; phase ^= 1; }
+        }
+    }
+    if (!ok || *abort_flag) {
+        if (status && lane == 0) atomicExch(status, (int) PT_ERR_TIMEOUT);
+        __nanosleep(100000);  // let a copy still in flight land before the shared memory is released
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ dequantize
 template <typename T> __device__ __forceinline__ void put_out(T *p, float v);
 template <> __device__ __forceinline__ void put_out<float>(float *p, float v) { *p = v; }
@@ -306,15 +525,52 @@ __global__ void __launch_bounds__(256) mx_dequant_kernel(const uint8_t *__restri
     }
 }
 
+// 3-D tensor map over x [G, M, N] (16-bit elements), box 64 x 128 x 1, 128-byte swizzle
+static int make_tmap_x(CUtensorMap *m, const void *base, int64_t G, int64_t M, int64_t N) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return set_error(PT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[3] = {(cuuint64_t) N, (cuuint64_t) M, (cuuint64_t) G};
+    cuuint64_t strides[2] = {(cuuint64_t) N * 2, (cuuint64_t) M * N * 2};
+    cuuint32_t box[3] = {(cuuint32_t) kTileN, (cuuint32_t) kTileM, 1u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(PT_ERR_CUDA, "cuTensorMapEncodeTiled (quantize input) failed with code %d", (int) r);
+    return PT_OK;
+}
+
 template <typename T, int FMT>
 static int launch_mx(const MxArgs &a, int64_t G, unsigned flags, cudaStream_t st) {
     dim3 grid((unsigned) (a.N_pad / kTileN), (unsigned) (a.M_pad / kTileM), (unsigned) G);
+    // TMA needs a 16-byte row pitch; N % 32 == 0 guarantees it for 16-bit elements
+    const bool use_tma = getenv("PT_MX_QUANT_NO_TMA") == nullptr;
+    CUtensorMap tmap;
+    const int tiles_n = (int) (a.N_pad / kTileN), tiles_m = (int) (a.M_pad / kTileM);
+    const int64_t total_tiles = (int64_t) tiles_n * tiles_m * G;
+    int tma_grid = 0;
+    if (use_tma) {
+        int rc = make_tmap_x(&tmap, a.x, G, a.M, a.N);
+        if (rc != PT_OK) return rc;
+        PT_REQUIRE(total_tiles < (1ll << 31), "MX quantize: too many tiles");
+        tma_grid = (int) std::min<int64_t>(total_tiles, (int64_t) sm_count() * kQCtasPerSm);
+    }
     const bool row = flags & PT_MX_ROW, col = flags & PT_MX_COL;
     const bool r2d = flags & PT_MX_ROW_2D, c2d = flags & PT_MX_COL_2D;
     const bool rrht = flags & PT_MX_ROW_RHT, crht = flags & PT_MX_COL_RHT;
 #define PT_MX_CASE(R, C, R2, C2, RR, CR)                                                                   \
     if (row == R && col == C && (!R || r2d == R2) && (!C || c2d == C2) && (!R || rrht == RR) && (!C || crht == CR)) { \
-        mx_quant_kernel<T, FMT, R, C, R2, C2, RR, CR><<<grid, kMxThreads, 0, st>>>(a);                     \
+        if (use_tma) {                                                                                     \
+            auto kern = mx_quant_tma_kernel<T, FMT, R, C, R2, C2, RR, CR>;                                 \
+            static bool attr_set = false;                                                                  \
+            if (!attr_set) {                                                                               \
+                PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kQSmemBytes)); \
+                attr_set = true;                                                                           \
+            }                                                                                              \
+            kern<<<tma_grid, kQThreads, kQSmemBytes, st>>>(tmap, a, tiles_n, tiles_m, total_tiles, nullptr); \
+        } else {                                                                                           \
+            mx_quant_kernel<T, FMT, R, C, R2, C2, RR, CR><<<grid, kMxThreads, 0, st>>>(a);                 \
+        }                                                                                                  \
         PT_LAUNCH_OK();                                                                                    \
         return PT_OK;                                                                                      \
     }
