@@ -11,7 +11,7 @@
 //
 //   warp 0       TMA producer (A 128 x 128 B, B 256 x 128 B per stage, 128-byte swizzle; B column-scale slabs)
 //   warp 1       MMA issuer, owns TMEM (512 columns = 2 partial buffers x 256)
-//   warps 2-3    idle (they complete the first warpgroup, which hands its registers over with setmaxnreg)
+//   warps 2-3    scale loaders: stage the fp32 scales of each K step into a shared-memory ring (cp.async)
 //   warps 4-11   promotion + epilogue, 232 registers each (128 fp32 accumulators per thread)
 //
 // Operand layouts: each operand may be K-major ([rows, K], the contraction index contiguous) or MN-major
@@ -33,16 +33,18 @@ using namespace sm100;
 
 constexpr int BW_BLOCK_N = 256;
 constexpr int kBwPromoWarps = 8;
-constexpr int kBwPromoWarp0 = 4;  // warps 0-3 form the first warpgroup: producer, MMA issuer, two idle warps
+constexpr int kBwPromoWarp0 = 4;  // warps 0-3 form the first warpgroup: producer, MMA issuer, two scale loaders
 constexpr int kBwThreads = 32 * (kBwPromoWarp0 + kBwPromoWarps);
 constexpr int kBwSlabRing = 8;    // ring of per-K-step B column-scale slabs (256 floats each)
 constexpr int kBwSlabBytes = BW_BLOCK_N * 4;
+constexpr int kBwScaleSlot = 136;  // floats per scale-ring slot: 128 A row scales, 2 B tile scales, padding
 constexpr int kBwStagePitch = 64;  // staging row: 32 x 16-bit or 16 x fp32 columns; 16-byte chunks XOR-swizzled by row
 constexpr int kBwABytes = BLOCK_M * BLOCK_K;
 constexpr int kBwBBytes = BW_BLOCK_N * BLOCK_K;
 constexpr int kBwStages = 4;
 constexpr int kBwEpiBytes = kBwPromoWarps * 32 * kBwStagePitch;
-constexpr int kBwSmemBytes = kBwStages * (kBwABytes + kBwBBytes) + kBwEpiBytes + kBwSlabRing * kBwSlabBytes + 1024 + 1024;
+constexpr int kBwSmemBytes =
+    kBwStages * (kBwABytes + kBwBBytes) + kBwEpiBytes + kBwSlabRing * (kBwSlabBytes + kBwScaleSlot * 4) + 1024 + 1024;
 
 struct ScaleDesc {
     const float *base;
@@ -130,13 +132,16 @@ __global__ void __launch_bounds__(kBwThreads, 1)
     uint8_t *smem_b = smem_a + kBwStages * kBwABytes;
     uint8_t *smem_epi = smem_b + kBwStages * kBwBBytes;
     float *smem_slab = reinterpret_cast<float *>(smem_epi + kBwEpiBytes);  // [kBwSlabRing][256] B column scales
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_epi + kBwEpiBytes + kBwSlabRing * kBwSlabBytes);
+    float *smem_scale = smem_slab + kBwSlabRing * (kBwSlabBytes / 4);      // [kBwSlabRing][kBwScaleSlot] row / tile scales
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_scale + kBwSlabRing * kBwScaleSlot);
     uint64_t *full_bar = bars;
     uint64_t *empty_bar = bars + kBwStages;
     uint64_t *part_full_bar = bars + 2 * kBwStages;  // [2]
     uint64_t *part_empty_bar = part_full_bar + 2;    // [2]
     uint64_t *slab_full_bar = part_empty_bar + 2;    // [kBwSlabRing]
-    uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(slab_full_bar + kBwSlabRing);
+    uint64_t *scale_full_bar = slab_full_bar + kBwSlabRing;    // [kBwSlabRing]
+    uint64_t *scale_empty_bar = scale_full_bar + kBwSlabRing;  // [kBwSlabRing]
+    uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(scale_empty_bar + kBwSlabRing);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_base_slot + 1);
     __shared__ int s_tile_start[kMaxGroups + 1];
 
@@ -163,7 +168,11 @@ __global__ void __launch_bounds__(kBwThreads, 1)
             mbar_init(&part_full_bar[s], 1);
             mbar_init(&part_empty_bar[s], kBwPromoWarps);
         }
-        for (int s = 0; s < kBwSlabRing; ++s) mbar_init(&slab_full_bar[s], 1);
+        for (int s = 0; s < kBwSlabRing; ++s) {
+            mbar_init(&slab_full_bar[s], 1);
+            mbar_init(&scale_full_bar[s], 64);  // one deferred arrival per loader thread
+            mbar_init(&scale_empty_bar[s], kBwPromoWarps);
+        }
         fence_barrier_init();
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
@@ -193,7 +202,7 @@ __global__ void __launch_bounds__(kBwThreads, 1)
     };
 
     if (warp < kBwPromoWarp0) {
-    // the first warpgroup (producer, MMA issuer, two idle warps) gives registers to the promotion warps
+    // the first warpgroup (producer, MMA issuer, scale loaders) gives registers to the promotion warps
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0) {
         // ================================================================ TMA producer
@@ -231,6 +240,34 @@ __global__ void __launch_bounds__(kBwThreads, 1)
                     }
                     if (++stage == kBwStages) { stage = 0; phase ^= 1; }
                 }
+            }
+        }
+    } else if (warp >= 2) {
+        // ================================================================ scale loader (warps 2-3)
+        // Stages the fp32 scales of each K step into an 8-slot ring with asynchronous 4-byte copies: two A rows
+        // per thread, and the two per-tile B scales.  The promotion warps then read their scales from shared
+        // memory and never wait on a global load.  A slot is reused once all promotion warps have released it.
+        const int lt = threadIdx.x - 64;  // 0..63
+        const bool sb_uniform = p.sb.shift == 7;
+        const int64_t sa_last = p.a_rows_total - 1;
+        uint32_t step = 0;
+        for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
+            const int64_t a_row0 = (p.koffs ? 0 : (p.offs_read ? p.offs_read[gi] : 0)) + (int64_t) m_blk * BLOCK_M;
+            int kb_begin, kb_count;
+            k_range(gi, kb_begin, kb_count);
+            // rows past the end of the operand are never stored; their scale reads are clamped to the last row
+            const float *src0 = p.sa.base + (min(a_row0 + lt, sa_last) >> p.sa.shift) * p.sa.row_stride + (int64_t) kb_begin * p.sa.kb_stride;
+            const float *src1 = p.sa.base + (min(a_row0 + lt + 64, sa_last) >> p.sa.shift) * p.sa.row_stride + (int64_t) kb_begin * p.sa.kb_stride;
+            const int nb = min(n_blk * BW_BLOCK_N + 128 * (lt & 1), p.N - 1) >> 7;
+            const float *srcb = p.sb.base + (int64_t) gi * p.sb.group_stride + (int64_t) kb_begin * p.sb.kb_stride + (int64_t) nb * p.sb.row_stride;
+            for (int kb = 0; kb < kb_count; ++kb, ++step) {
+                const uint32_t slot = step % kBwSlabRing;
+                if (!(ok = mbar_wait(&scale_empty_bar[slot], ((step / kBwSlabRing) & 1u) ^ 1u, abort_flag))) break;
+                float *slot_ptr = smem_scale + slot * kBwScaleSlot;
+                cp_async_4(slot_ptr + lt, src0 + (int64_t) kb * p.sa.kb_stride);
+                cp_async_4(slot_ptr + lt + 64, src1 + (int64_t) kb * p.sa.kb_stride);
+                if (sb_uniform && lt < 2) cp_async_4(slot_ptr + 128 + lt, srcb + (int64_t) kb * p.sb.kb_stride);
+                cp_async_arrive_noinc(&scale_full_bar[slot]);
             }
         }
     } else if (warp == 1) {
@@ -286,24 +323,20 @@ __global__ void __launch_bounds__(kBwThreads, 1)
             const bool row_ok = my_c_row < c_row_end;
             const int n0 = n_blk * BW_BLOCK_N + half * 128;
             const int n_end = min(p.N, n0 + 128);
-            const float *sa_ptr = p.sa.base + (my_a_row >> p.sa.shift) * p.sa.row_stride + (int64_t) kb_begin * p.sa.kb_stride;
             const float *sb_base = p.sb.base + (int64_t) gi * p.sb.group_stride + (int64_t) kb_begin * p.sb.kb_stride;
             const bool sb_uniform = p.sb.shift == 7;
-            const float *sb_uni_ptr = sb_base + (int64_t) (n0 >> 7) * p.sb.row_stride;
-            const bool sb_uni_ok = n0 < p.N;
 
             float acc[128];
 #pragma unroll
             for (int i = 0; i < 128; ++i) acc[i] = 0.f;
 
-            float sa_next = (row_ok && kb_count > 0) ? __ldg(sa_ptr) : 0.f;
-            float sbu_next = (sb_uniform && sb_uni_ok && kb_count > 0) ? __ldg(sb_uni_ptr) : 0.f;
             for (int kb = 0; kb < kb_count; ++kb, ++step) {
-                const float sa_cur = sa_next, sbu_cur = sbu_next;
-                if (kb + 1 < kb_count) {
-                    sa_next = row_ok ? __ldg(sa_ptr + (int64_t) (kb + 1) * p.sa.kb_stride) : 0.f;
-                    sbu_next = (sb_uniform && sb_uni_ok) ? __ldg(sb_uni_ptr + (int64_t) (kb + 1) * p.sb.kb_stride) : 0.f;
-                }
+                // scales of this K step were staged by the producer warp several steps ago
+                if (!(ok = mbar_wait(&scale_full_bar[step % kBwSlabRing], (step / kBwSlabRing) & 1u, abort_flag))) break;
+                const float *sc_slot = smem_scale + (step % kBwSlabRing) * kBwScaleSlot;
+                const float sa_cur = sc_slot[row_in_tile], sbu_cur = sc_slot[128 + half];
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&scale_empty_bar[step % kBwSlabRing]);
                 if (!(ok = mbar_wait(&part_full_bar[pb], pphase, abort_flag))) break;
                 tc_fence_after_sync();
                 const uint32_t taddr = tmem_base + ((uint32_t) (q * 32) << 16) + pb * BW_BLOCK_N + half * 128;
@@ -423,7 +456,8 @@ int pt_grouped_gemm_fp8_blockwise(const void *a, int a_fmt, int a_mn, int64_t a_
     p.sb = ScaleDesc{sb, sb_shift, sb_row_stride, sb_kb_stride, sb_group_stride};
     p.a_fmt = a_fmt; p.b_fmt = b_fmt;
     p.offs_write = group_offs_write; p.offs_read = group_offs_read ? group_offs_read : group_offs_write;
-    p.G = G; p.b_group_rows = N; p.a_rows_total = a_mem_rows; p.status = status;
+    p.G = G; p.b_group_rows = N; p.a_rows_total = a_mn ? a_mem_cols : a_mem_rows;
+    if (!group_offs_read) p.a_rows_total = std::min<int64_t>(p.a_rows_total, c_rows);  // rows that have scales p.status = status;
     p.a_mn = a_mn; p.b_mn = b_mn; p.koffs = k_offs; p.b_group_kstride = K;
     p.sb_slab = sb_shift == 0 && sb_row_stride == 1 && sb_kb_stride % 4 == 0 && sb_group_stride % 4 == 0 && N % 4 == 0 && aligned(sb, 16);
     p.raster_m = raster_rows(a_mn ? a_mem_cols : a_mem_rows, a_mn ? a_mem_rows : a_mem_cols);

@@ -71,6 +71,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     }
 }
 
+// 4-byte asynchronous copy global -> shared (non-bulk); completion is observed through
+// cp_async_arrive_noinc on an mbarrier whose expected count includes the issuing thread.
+__device__ __forceinline__ void cp_async_4(void *smem_dst, const void *gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)) : "memory");
+}
+// The barrier receives one arrival from this thread once all of its earlier cp.async copies have landed.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t *bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 // ------------------------------------------------------------------ proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
