@@ -41,8 +41,9 @@ constexpr int kBwScaleSlot = 136;  // floats per scale-ring slot: 128 A row scal
 constexpr int kBwStagePitch = 64;  // staging row: 32 x 16-bit or 16 x fp32 columns; 16-byte chunks XOR-swizzled by row
 constexpr int kBwABytes = BLOCK_M * BLOCK_K;
 constexpr int kBwBBytes = BW_BLOCK_N * BLOCK_K;
-constexpr int kBwStages = 4;
-constexpr int kBwEpiBytes = kBwPromoWarps * 32 * kBwStagePitch;
+constexpr int kBwStages = 3;
+constexpr int kBwEpiWarpBytes = 8192;  // per promotion warp: two 32-row x 128-byte boxes of the bulk-store path
+constexpr int kBwEpiBytes = kBwPromoWarps * kBwEpiWarpBytes;
 constexpr int kBwSmemBytes =
     kBwStages * (kBwABytes + kBwBBytes) + kBwEpiBytes + kBwSlabRing * (kBwSlabBytes + kBwScaleSlot * 4) + 1024 + 1024;
 
@@ -60,6 +61,8 @@ struct BwParams {
     void *C;
     int64_t ldc;
     int c_dtype, vec_store_ok;
+    int c_tma;                 // C has a tensor map: whole 32-row blocks leave through bulk tensor stores
+    int64_t c_rows_total;
     float beta;
     ScaleDesc sa, sb;
     int a_fmt, b_fmt;
@@ -124,8 +127,54 @@ __device__ __forceinline__ void bw_store_tile(const float (&acc)[128], uint8_t *
     }
 }
 
+// Write-out of one warp's 32 x 128 block through bulk tensor stores: the block is converted into 128-byte-swizzled
+// boxes of 32 rows x 128 bytes in the warp's staging area, and one lane hands them to the TMA unit, which clips
+// rows / columns beyond the matrix.  The warp does not wait for the stores; the staging area is reclaimed at the
+// next write-out (bulk_wait_read_all).
+template <typename OutT>
+__device__ __forceinline__ void bw_store_tile_bulk(const float (&acc)[128], uint8_t *stg, int lane, int64_t tile_row0, int n0,
+                                                   int N, const CUtensorMap *tmap_c) {
+    constexpr int esize = sizeof(OutT);
+    constexpr int box_cols = 128 / esize;        // 64 (16-bit) or 32 (fp32) columns per box
+    constexpr int rounds = 128 / (2 * box_cols);  // two boxes fit the staging area: 1 round (16-bit), 2 rounds (fp32)
+    uint8_t *my = stg + lane * 128;
+#pragma unroll
+    for (int rd = 0; rd < rounds; ++rd) {
+        if (lane == 0) bulk_wait_read_all();
+        __syncwarp();
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float *f = &acc[(rd * 2 + b) * box_cols + j * (16 / esize)];
+                uint4 v;
+                if constexpr (esize == 4) v = make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+                else v = make_uint4(pack2<OutT>(f[0], f[1]), pack2<OutT>(f[2], f[3]), pack2<OutT>(f[4], f[5]), pack2<OutT>(f[6], f[7]));
+                *reinterpret_cast<uint4 *>(my + b * 4096 + ((j ^ (lane & 7)) * 16)) = v;
+            }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+                if (n0 + (rd * 2 + b) * box_cols < N)  // boxes that start past the last column are dropped
+                    tma_store_2d(tmap_c, stg + b * 4096, (n0 + (rd * 2 + b) * box_cols) * esize, (int) tile_row0);
+            bulk_commit_group();
+        }
+    }
+}
+
+// SBM selects how the B scales reach the promotion warps (one kernel per mode keeps each K loop small):
+//   SB_TILE   one scale per 128 columns (weights quantised in 128 x 128 blocks): staged with the A scales
+//   SB_SLAB   one scale per column, contiguous along the columns: 256-float slabs through shared memory
+//   SB_GLOBAL any other per-row layout, read from global memory
+enum { SB_TILE = 0, SB_SLAB = 1, SB_GLOBAL = 2 };
+
+template <int SBM, typename OutT>
 __global__ void __launch_bounds__(kBwThreads, 1)
-    gemm_fp8_blockwise_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, BwParams p) {
+    gemm_fp8_blockwise_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                              const __grid_constant__ CUtensorMap tmap_c, BwParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *smem_a = smem;
@@ -171,7 +220,7 @@ __global__ void __launch_bounds__(kBwThreads, 1)
         for (int s = 0; s < kBwSlabRing; ++s) {
             mbar_init(&slab_full_bar[s], 1);
             mbar_init(&scale_full_bar[s], 64);  // one deferred arrival per loader thread
-            mbar_init(&scale_empty_bar[s], kBwPromoWarps);
+            mbar_init(&scale_empty_bar[s], 1);  // released by the MMA issuer on behalf of the promotion warps
         }
         fence_barrier_init();
         prefetch_tmap(&tmap_a);
@@ -230,7 +279,7 @@ __global__ void __launch_bounds__(kBwThreads, 1)
                     } else {
                         tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, (int) b_row0);
                     }
-                    if (p.sb_slab) {
+                    if constexpr (SBM == SB_SLAB) {
                         // per-column B scales of this K step: one contiguous run of `slab_cols` floats.  Ring slot
                         // step % 8 is free: the producer runs at most 4 stages + 2 partial buffers ahead of the readers.
                         const uint32_t slot = step % kBwSlabRing;
@@ -246,9 +295,9 @@ __global__ void __launch_bounds__(kBwThreads, 1)
         // ================================================================ scale loader (warps 2-3)
         // Stages the fp32 scales of each K step into an 8-slot ring with asynchronous 4-byte copies: two A rows
         // per thread, and the two per-tile B scales.  The promotion warps then read their scales from shared
-        // memory and never wait on a global load.  A slot is reused once all promotion warps have released it.
+        // memory and never wait on a global load.  A slot is refilled once the MMA issuer has released it.
         const int lt = threadIdx.x - 64;  // 0..63
-        const bool sb_uniform = p.sb.shift == 7;
+        constexpr bool sb_uniform = SBM == SB_TILE;
         const int64_t sa_last = p.a_rows_total - 1;
         uint32_t step = 0;
         for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
@@ -275,18 +324,22 @@ __global__ void __launch_bounds__(kBwThreads, 1)
         if (elect_one()) {
             const uint32_t idesc = idesc_f8(p.a_fmt, p.b_fmt, BLOCK_M, BW_BLOCK_N) | ((uint32_t) (p.a_mn != 0) << 15) |
                                    ((uint32_t) (p.b_mn != 0) << 16);
-            uint32_t stage = 0, phase = 0, pb = 0, pphase = 0;
+            uint32_t stage = 0, phase = 0, pb = 0, pphase = 0, step = 0;
             for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
                 int kb_begin, kb_count;
                 k_range(gi, kb_begin, kb_count);
-                for (int kb = 0; kb < kb_count; ++kb) {
-                    if (!(ok = mbar_wait(&part_empty_bar[pb], pphase ^ 1, abort_flag))) break;
+                for (int kb = 0; kb < kb_count; ++kb, ++step) {
+                    // The partial sum of this step is only announced once its scales have landed, so the promotion
+                    // warps need no barrier of their own for the scale ring.  Operands and scales arrive long before
+                    // the partial buffer is handed back; waiting for the buffer last keeps that hand-over short.
+                    if (!(ok = mbar_wait(&scale_full_bar[step % kBwSlabRing], (step / kBwSlabRing) & 1u, abort_flag))) break;
                     if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
-                    tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + pb * BW_BLOCK_N;
                     const uint32_t a_addr = smem_u32(smem_a + stage * kBwABytes), b_addr = smem_u32(smem_b + stage * kBwBBytes);
                     const uint64_t a_desc = p.a_mn ? smem_desc_sw128_mn(a_addr, 16384) : smem_desc_sw128(a_addr);
                     const uint64_t b_desc = p.b_mn ? smem_desc_sw128_mn(b_addr, 16384) : smem_desc_sw128(b_addr);
+                    if (!(ok = mbar_wait(&part_empty_bar[pb], pphase ^ 1, abort_flag))) break;
+                    tc_fence_after_sync();
                     // one instruction consumes 32 contraction indices: 32 bytes along a K-major row, or 32 rows of
                     // 128 bytes in an MN-major tile
                     const uint64_t a_step = p.a_mn ? (uint64_t) ((UMMA_K * 128) >> 4) : (uint64_t) (UMMA_K >> 4);
@@ -296,6 +349,8 @@ __global__ void __launch_bounds__(kBwThreads, 1)
                         mma_f8(d_tmem, a_desc + k * a_step, b_desc + k * b_step, idesc, k > 0 ? 1u : 0u);
                     tc_commit(&empty_bar[stage]);
                     tc_commit(&part_full_bar[pb]);
+                    // the promotion warps are done with step - 2 (its buffer was just reused): its scale slot is free
+                    if (step >= 2) mbar_arrive(&scale_empty_bar[(step - 2) % kBwSlabRing]);
                     if (++stage == kBwStages) { stage = 0; phase ^= 1; }
                     if (++pb == 2) { pb = 0; pphase ^= 1; }
                 }
@@ -309,7 +364,7 @@ __global__ void __launch_bounds__(kBwThreads, 1)
         const int pw = warp - kBwPromoWarp0;
         const int q = warp & 3;       // TMEM lane quarter of this warp
         const int half = pw >> 2;     // which 128 columns of the 256-wide tile
-        uint8_t *stg = smem_epi + pw * 32 * kBwStagePitch;
+        uint8_t *stg = smem_epi + pw * kBwEpiWarpBytes;
         uint32_t pb = 0, pphase = 0, step = 0;
         for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
             const int64_t c_row_base = p.koffs ? (int64_t) gi * p.M : (p.offs_write ? p.offs_write[gi] : 0);
@@ -324,43 +379,44 @@ __global__ void __launch_bounds__(kBwThreads, 1)
             const int n0 = n_blk * BW_BLOCK_N + half * 128;
             const int n_end = min(p.N, n0 + 128);
             const float *sb_base = p.sb.base + (int64_t) gi * p.sb.group_stride + (int64_t) kb_begin * p.sb.kb_stride;
-            const bool sb_uniform = p.sb.shift == 7;
+            constexpr bool sb_uniform = SBM == SB_TILE;
 
             float acc[128];
 #pragma unroll
             for (int i = 0; i < 128; ++i) acc[i] = 0.f;
 
             for (int kb = 0; kb < kb_count; ++kb, ++step) {
-                // scales of this K step were staged by the producer warp several steps ago
-                if (!(ok = mbar_wait(&scale_full_bar[step % kBwSlabRing], (step / kBwSlabRing) & 1u, abort_flag))) break;
-                const float *sc_slot = smem_scale + (step % kBwSlabRing) * kBwScaleSlot;
-                const float sa_cur = sc_slot[row_in_tile], sbu_cur = sc_slot[128 + half];
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&scale_empty_bar[step % kBwSlabRing]);
                 if (!(ok = mbar_wait(&part_full_bar[pb], pphase, abort_flag))) break;
                 tc_fence_after_sync();
                 const uint32_t taddr = tmem_base + ((uint32_t) (q * 32) << 16) + pb * BW_BLOCK_N + half * 128;
                 // TMEM reads are issued one chunk ahead of the FMAs that consume them
                 uint32_t r0[32], r1[32];
                 tmem_ld32(taddr, r0);
-                if (sb_uniform) {
+                // the scales of this K step landed in the ring before the partial sum was announced
+                const float *sc_slot = smem_scale + (step % kBwSlabRing) * kBwScaleSlot;
+                const float sa_cur = sc_slot[row_in_tile], sbu_cur = sc_slot[128 + half];
+                if constexpr (sb_uniform) {
+                    // one scale for the whole 32 x 128 block of this warp.  Two TMEM loads are kept in flight, so the
+                    // step has two load latencies on its critical path instead of four; the partial buffer goes back
+                    // to the MMA issuer as soon as the last load has landed.
                     const float sc = sa_cur * sbu_cur;
-                    tmem_ld_wait();
                     tmem_ld32(taddr + 32, r1);
+                    tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) acc[i] = fmaf(__uint_as_float(r0[i]), sc, acc[i]);
-                    tmem_ld_wait();
                     tmem_ld32(taddr + 64, r0);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(__uint_as_float(r1[i]), sc, acc[32 + i]);
-                    tmem_ld_wait();
                     tmem_ld32(taddr + 96, r1);
+                    tmem_ld_wait();
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&part_empty_bar[pb]);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(__uint_as_float(r0[i]), sc, acc[64 + i]);
-                    tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(__uint_as_float(r1[i]), sc, acc[96 + i]);
-                } else if (p.sb_slab) {
+                } else if constexpr (SBM == SB_SLAB) {
                     const uint32_t slot = step % kBwSlabRing;
                     if (!(ok = mbar_wait(&slab_full_bar[slot], (step / kBwSlabRing) & 1u, abort_flag))) break;
                     const float4 *sl = reinterpret_cast<const float4 *>(smem_slab + slot * (kBwSlabBytes / 4) + half * 128);
@@ -394,19 +450,30 @@ __global__ void __launch_bounds__(kBwThreads, 1)
                         }
                     }
                 }
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&part_empty_bar[pb]);
+                if constexpr (!sb_uniform) {
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&part_empty_bar[pb]);
+                }
                 if (++pb == 2) { pb = 0; pphase ^= 1; }
             }
             if (!ok) break;
 
             // ---- write-out through the per-warp staging buffer
             const int64_t tile_row0 = c_row_base + (int64_t) m_blk * BLOCK_M + q * 32;
-            if (p.c_dtype == PT_F32) bw_store_tile<float>(acc, stg, lane, tile_row0, c_row_end, n0, n_end, p);
-            else if (p.c_dtype == PT_BF16) bw_store_tile<__nv_bfloat16>(acc, stg, lane, tile_row0, c_row_end, n0, n_end, p);
-            else bw_store_tile<__half>(acc, stg, lane, tile_row0, c_row_end, n0, n_end, p);
+            // whole blocks (or blocks cut only by the end of the matrix, which the TMA unit clips) take the bulk path
+            if (p.c_tma && tile_row0 < c_row_end && n0 < p.N && (tile_row0 + 32 <= c_row_end || c_row_end == p.c_rows_total)) {
+                bw_store_tile_bulk<OutT>(acc, stg, lane, tile_row0, n0, p.N, &tmap_c);
+                continue;
+            }
+            if (p.c_tma) {  // the staging area may still be read by an earlier bulk store
+                if (lane == 0) bulk_wait_read_all();
+                __syncwarp();
+            }
+            bw_store_tile<OutT>(acc, stg, lane, tile_row0, c_row_end, n0, n_end, p);
         }
+        // bulk stores still in flight read this CTA's shared memory
+        if (p.c_tma && lane == 0) bulk_wait_all();
     }
 
     if (!ok || *abort_flag) {
@@ -419,6 +486,17 @@ __global__ void __launch_bounds__(kBwThreads, 1)
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, 512);
     }
+}
+
+// Raises the dynamic shared-memory limit of one kernel instantiation (on every call: it is a cheap host-side
+// attribute write and keeps the limit right on every device of the process) and launches it.
+template <typename Kernel>
+static int bw_launch(Kernel kernel, int grid, cudaStream_t stream, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc,
+                     const BwParams &p) {
+    PT_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwSmemBytes));
+    kernel<<<grid, kBwThreads, kBwSmemBytes, stream>>>(ta, tb, tc, p);
+    PT_LAUNCH_OK();
+    return PT_OK;
 }
 
 }  // namespace ptb
@@ -466,18 +544,29 @@ int pt_grouped_gemm_fp8_blockwise(const void *a, int a_fmt, int a_mn, int64_t a_
     // K-major: box = 128 contraction bytes x tile rows; MN-major: box = 128 row indices x 128 contraction rows
     if ((rc = make_tmap_bytes(&ta, a, a_mem_rows, a_mem_cols, a_mem_cols, a_mn ? BLOCK_K : BLOCK_M)) != PT_OK) return rc;
     if ((rc = make_tmap_bytes(&tb, b, b_mem_rows, b_mem_cols, b_mem_cols, b_mn ? BLOCK_K : BW_BLOCK_N)) != PT_OK) return rc;
-    static bool attr_set = false;
-    if (!attr_set) {
-        PT_CUDA_OK(cudaFuncSetAttribute(gemm_fp8_blockwise_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwSmemBytes));
-        attr_set = true;
-    }
     const int64_t m_blocks = k_offs ? (int64_t) G * ceil_div(c_rows, BLOCK_M) : ceil_div(c_rows, BLOCK_M) + (group_offs_write ? G : 0);
     const int64_t tiles = m_blocks * ceil_div(N, BW_BLOCK_N);
     int grid = (int) std::min<int64_t>(tiles, sm_count());
     if (max_ctas > 0) grid = std::min(grid, max_ctas);
-    gemm_fp8_blockwise_kernel<<<grid, kBwThreads, kBwSmemBytes, (cudaStream_t) stream>>>(ta, tb, p);
-    PT_LAUNCH_OK();
-    return PT_OK;
+    // C as a byte tensor of 128-byte x 32-row boxes for the bulk-store write-out
+    CUtensorMap tc{};
+    p.c_rows_total = k_offs ? (int64_t) G * c_rows : c_rows;
+    p.c_tma = p.vec_store_ok && beta == 0.f && N * esize < (1ll << 31) && p.c_rows_total < (1ll << 31);
+    if (p.c_tma && (rc = make_tmap_bytes(&tc, c, p.c_rows_total, N * esize, N * esize, 32)) != PT_OK) return rc;
+    const int sbm = sb_shift == 7 ? SB_TILE : (p.sb_slab ? SB_SLAB : SB_GLOBAL);
+#define PT_BW_CASE(SBM_, T_)                                                                                         \
+    return bw_launch(gemm_fp8_blockwise_kernel<SBM_, T_>, grid, (cudaStream_t) stream, ta, tb, tc, p)
+#define PT_BW_DTYPE(SBM_)                                                                                            \
+    do {                                                                                                             \
+        if (c_dtype == PT_F32) PT_BW_CASE(SBM_, float);                                                              \
+        if (c_dtype == PT_BF16) PT_BW_CASE(SBM_, __nv_bfloat16);                                                     \
+        PT_BW_CASE(SBM_, __half);                                                                                    \
+    } while (0)
+    if (sbm == SB_TILE) PT_BW_DTYPE(SB_TILE);
+    if (sbm == SB_SLAB) PT_BW_DTYPE(SB_SLAB);
+    PT_BW_DTYPE(SB_GLOBAL);
+#undef PT_BW_DTYPE
+#undef PT_BW_CASE
 }
 
 }  // extern "C"

@@ -71,6 +71,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     }
 }
 
+// 2-D tiled store shared -> global (bulk-group completion).  Issued by one thread after the writers of the
+// shared tile have executed fence_proxy_async_smem() and synchronised with it.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, const void *smem_src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(reinterpret_cast<uint64_t>(m)),
+                 "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all bulk groups of this thread have finished reading their shared-memory source
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all bulk groups of this thread are complete
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // 4-byte asynchronous copy global -> shared (non-bulk); completion is observed through
 // cp_async_arrive_noinc on an mbarrier whose expected count includes the issuing thread.
 __device__ __forceinline__ void cp_async_4(void *smem_dst, const void *gsrc) {
