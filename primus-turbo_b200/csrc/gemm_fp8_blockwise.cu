@@ -329,10 +329,12 @@ __global__ void __launch_bounds__(kBwThreads, 1)
                 int kb_begin, kb_count;
                 k_range(gi, kb_begin, kb_count);
                 for (int kb = 0; kb < kb_count; ++kb, ++step) {
-                    // The partial sum of this step is only announced once its scales have landed, so the promotion
-                    // warps need no barrier of their own for the scale ring.  Operands and scales arrive long before
+                    // The partial sum of this step is only announced once its scales (and B slab) have landed, so the
+                    // promotion warps need no barrier of their own for the scale rings.  Operands and scales arrive long before
                     // the partial buffer is handed back; waiting for the buffer last keeps that hand-over short.
                     if (!(ok = mbar_wait(&scale_full_bar[step % kBwSlabRing], (step / kBwSlabRing) & 1u, abort_flag))) break;
+                    if constexpr (SBM == SB_SLAB)
+                        if (!(ok = mbar_wait(&slab_full_bar[step % kBwSlabRing], (step / kBwSlabRing) & 1u, abort_flag))) break;
                     if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
                     const uint32_t d_tmem = tmem_base + pb * BW_BLOCK_N;
                     const uint32_t a_addr = smem_u32(smem_a + stage * kBwABytes), b_addr = smem_u32(smem_b + stage * kBwBBytes);
@@ -395,36 +397,16 @@ __global__ void __launch_bounds__(kBwThreads, 1)
                 // the scales of this K step landed in the ring before the partial sum was announced
                 const float *sc_slot = smem_scale + (step % kBwSlabRing) * kBwScaleSlot;
                 const float sa_cur = sc_slot[row_in_tile], sbu_cur = sc_slot[128 + half];
-                if constexpr (sb_uniform) {
-                    // one scale for the whole 32 x 128 block of this warp.  Two TMEM loads are kept in flight, so the
-                    // step has two load latencies on its critical path instead of four; the partial buffer goes back
-                    // to the MMA issuer as soon as the last load has landed.
-                    const float sc = sa_cur * sbu_cur;
-                    tmem_ld32(taddr + 32, r1);
-                    tmem_ld_wait();
+                // acc[32 c ..] += partial chunk c * scales
+                auto add_chunk = [&](int c, const uint32_t(&r)[32]) {
+                    if constexpr (sb_uniform) {
+                        const float sc = sa_cur * sbu_cur;  // one scale for the whole 32 x 128 block of this warp
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) acc[i] = fmaf(__uint_as_float(r0[i]), sc, acc[i]);
-                    tmem_ld32(taddr + 64, r0);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(__uint_as_float(r1[i]), sc, acc[32 + i]);
-                    tmem_ld32(taddr + 96, r1);
-                    tmem_ld_wait();
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&part_empty_bar[pb]);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(__uint_as_float(r0[i]), sc, acc[64 + i]);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(__uint_as_float(r1[i]), sc, acc[96 + i]);
-                } else if constexpr (SBM == SB_SLAB) {
-                    const uint32_t slot = step % kBwSlabRing;
-                    if (!(ok = mbar_wait(&slab_full_bar[slot], (step / kBwSlabRing) & 1u, abort_flag))) break;
-                    const float4 *sl = reinterpret_cast<const float4 *>(smem_slab + slot * (kBwSlabBytes / 4) + half * 128);
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t(&r)[32] = (c & 1) ? r1 : r0;
-                        tmem_ld_wait();
-                        if (c < 3) tmem_ld32(taddr + 32 * (c + 1), (c & 1) ? r0 : r1);
+                        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), sc, acc[c * 32 + i]);
+                    } else if constexpr (SBM == SB_SLAB) {
+                        // the slab of this K step landed before the partial sum was announced (see the MMA issuer)
+                        const float4 *sl =
+                            reinterpret_cast<const float4 *>(smem_slab + (step % kBwSlabRing) * (kBwSlabBytes / 4) + half * 128);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const float4 sv = sl[c * 8 + i];  // same address in every lane: a broadcast read
@@ -433,15 +415,9 @@ __global__ void __launch_bounds__(kBwThreads, 1)
                             acc[c * 32 + 4 * i + 2] = fmaf(__uint_as_float(r[4 * i + 2]) * sv.z, sa_cur, acc[c * 32 + 4 * i + 2]);
                             acc[c * 32 + 4 * i + 3] = fmaf(__uint_as_float(r[4 * i + 3]) * sv.w, sa_cur, acc[c * 32 + 4 * i + 3]);
                         }
-                    }
-                } else {
-                    // general per-row B scales read from global memory (no reference path needs this to be fast)
-                    const float *sbk = sb_base + (int64_t) kb * p.sb.kb_stride;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t(&r)[32] = (c & 1) ? r1 : r0;
-                        tmem_ld_wait();
-                        if (c < 3) tmem_ld32(taddr + 32 * (c + 1), (c & 1) ? r0 : r1);
+                    } else {
+                        // general per-row B scales read from global memory (no reference path needs this to be fast)
+                        const float *sbk = sb_base + (int64_t) kb * p.sb.kb_stride;
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
                             const int n = n0 + c * 32 + i;
@@ -449,12 +425,21 @@ __global__ void __launch_bounds__(kBwThreads, 1)
                             acc[c * 32 + i] = fmaf(__uint_as_float(r[i]) * sbv, sa_cur, acc[c * 32 + i]);
                         }
                     }
-                }
-                if constexpr (!sb_uniform) {
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&part_empty_bar[pb]);
-                }
+                };
+                // Two TMEM loads are kept in flight, so the step has two load latencies on its critical path instead
+                // of four; the partial buffer goes back to the MMA issuer as soon as the last load has landed.
+                tmem_ld32(taddr + 32, r1);
+                tmem_ld_wait();
+                add_chunk(0, r0);
+                tmem_ld32(taddr + 64, r0);
+                add_chunk(1, r1);
+                tmem_ld32(taddr + 96, r1);
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&part_empty_bar[pb]);
+                add_chunk(2, r0);
+                add_chunk(3, r1);
                 if (++pb == 2) { pb = 0; pphase ^= 1; }
             }
             if (!ok) break;
