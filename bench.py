@@ -167,6 +167,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--granularity", default="mx", choices=["mx", "blockwise", "tensorwise", "rowwise", "mxfp4"],
+                    help="scaling recipe of the linear forward; the headline metric is 'mx' (the others print the same "
+                         "line for their own kernels and skip the CPU leg)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (used when profiling)")
     args = ap.parse_args()
@@ -174,6 +177,9 @@ def main():
     M, N, K, seed = WORKLOADS[args.workload]
 
     if args.impl == "reference":
+        if args.granularity != "mx":
+            print(json.dumps({"impl": "reference", "unavailable": "the CPU port covers the MX_BLOCKWISE headline workload only"}))
+            return
         run_reference(args, M, N, K, seed, args.workload)
         return
 
@@ -191,10 +197,22 @@ def main():
                                                          ScalingRecipe)
     from primus_turbo.pytorch.kernels import _native as nv
     from primus_turbo.pytorch.kernels.gemm.gemm_fp8_impl import gemm_fp8_impl
+    from primus_turbo.pytorch.kernels.gemm.gemm_fp4_impl import gemm_fp4_impl
+    from primus_turbo.pytorch.kernels.quantization import quantization_impl as qi
     from primus_turbo.pytorch.kernels.quantization.quantization_impl import quantize_mxfp8_impl
 
-    cfg = Float8QuantConfig(format=Format.E4M3, granularity=ScalingGranularity.MX_BLOCKWISE, scale_dtype=ScaleDtype.E8M0,
-                            block_size=32)
+    if args.granularity == "mxfp4":
+        from primus_turbo.pytorch.core.low_precision import Float4QuantConfig
+        cfg, public_op = Float4QuantConfig(), turbo.ops.gemm_fp4
+    elif args.granularity == "mx":
+        cfg = Float8QuantConfig(format=Format.E4M3, granularity=ScalingGranularity.MX_BLOCKWISE, scale_dtype=ScaleDtype.E8M0,
+                                block_size=32)
+        public_op = turbo.ops.gemm_fp8
+    else:
+        gran = {"blockwise": ScalingGranularity.BLOCKWISE, "tensorwise": ScalingGranularity.TENSORWISE,
+                "rowwise": ScalingGranularity.ROWWISE}[args.granularity]
+        cfg = Float8QuantConfig(format=Format.E4M3, granularity=gran, block_size=128 if args.granularity == "blockwise" else None)
+        public_op = turbo.ops.gemm_fp8
     # weak scaling: every rank owns one N-shard of a layer that is `world` times as wide (its own weight shard),
     # the activation is replicated; no collective on the data path (outputs stay column-sharded).
     a_host, w_host = make_inputs(M, N, K, seed + 1000 * rank, "cuda")
@@ -205,13 +223,39 @@ def main():
     plain, two_d = ScalingRecipe(), ScalingRecipe(use_2d_block=True)
     gemm_events = []
 
+    G = ScalingGranularity
+    # per recipe: (quantize both operands the way the reference's forward does, GEMM on the quantized operands,
+    #              launches of this library per step, name of the dominant kernel)
+    if args.granularity == "mx":
+        quant = lambda: (quantize_mxfp8_impl(a, f8, None, 32, True, plain, plain)[:2],
+                         quantize_mxfp8_impl(w, f8, None, 32, True, two_d, two_d)[:2])
+        gemm = lambda qa, qw: gemm_fp8_impl(qa[0], qa[1], False, qw[0], qw[1], True, torch.bfloat16, False, G.MX_BLOCKWISE)
+        launches, kernel_name = 5, "gemm_fp8_kernel<MX>"  # 2 dual quantize, 2 scale re-tile, 1 GEMM
+    elif args.granularity == "mxfp4":
+        fp4 = torch.float4_e2m1fn_x2
+        quant = lambda: (qi.quantize_mxfp4_impl(a, fp4, None, 32, True, plain, plain)[:2],
+                         qi.quantize_mxfp4_impl(w, fp4, None, 32, True, two_d, two_d)[:2])
+        gemm = lambda qa, qw: gemm_fp4_impl(qa[0], qa[1], False, qw[0], qw[1], True, torch.bfloat16, False, G.MX_BLOCKWISE)
+        launches, kernel_name = 5, "gemm_fp8_kernel<MXF4>"
+    elif args.granularity == "blockwise":
+        quant = lambda: (qi.quant_fp8_blockwise_impl(a, f8, 1), qi.quant_fp8_blockwise_for_weight_impl(w, f8))
+        gemm = lambda qa, qw: gemm_fp8_impl(qa[0], qa[1], False, qw[0], qw[1], True, torch.bfloat16, False, G.BLOCKWISE)
+        launches, kernel_name = 3, "gemm_fp8_blockwise_kernel<SB_TILE>"
+    else:
+        gran = G.TENSORWISE if args.granularity == "tensorwise" else G.ROWWISE
+        if gran == G.TENSORWISE:
+            quant = lambda: (qi.quantize_fp8_tensorwise_impl(a, f8), qi.quantize_fp8_tensorwise_impl(w, f8))
+        else:
+            quant = lambda: (qi.quantize_fp8_rowwise_impl(a, f8, -1), qi.quantize_fp8_rowwise_impl(w, f8, -1))
+        gemm = lambda qa, qw: gemm_fp8_impl(qa[0], qa[1], False, qw[0], qw[1], True, torch.bfloat16, False, gran)
+        launches, kernel_name = (5 if gran == G.TENSORWISE else 3), f"gemm_fp8_kernel<{args.granularity.upper()}>"
+
     def step(record=False):
-        a_row, a_rs, _a_col, _a_cs = quantize_mxfp8_impl(a, f8, None, 32, True, plain, plain)
-        w_row, w_rs, _w_col, _w_cs = quantize_mxfp8_impl(w, f8, None, 32, True, two_d, two_d)
+        qa, qw = quant()
         if record:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-        out = gemm_fp8_impl(a_row, a_rs, False, w_row, w_rs, True, torch.bfloat16, False, ScalingGranularity.MX_BLOCKWISE)
+        out = gemm(qa, qw)
         if record:
             e1.record()
             gemm_events.append((e0, e1))
@@ -247,7 +291,7 @@ def main():
     def e2e_step():
         a_d = a_host.to(dev, non_blocking=True)
         w_d = w_host.to(dev, non_blocking=True)
-        y = turbo.ops.gemm_fp8(a_d, w_d, trans_b=True, out_dtype=torch.bfloat16, config=cfg)
+        y = public_op(a_d, w_d, trans_b=True, out_dtype=torch.bfloat16, config=cfg)
         out_host.copy_(y, non_blocking=True)
 
     with torch.no_grad():
@@ -278,25 +322,33 @@ def main():
     peaks = measured_peaks()
     fp8_peak = 2.0 * peaks["bf16_sustained"]  # kernels timed inside a long step: sustained figure; fp8 = 2 x bf16
     achieved = flops / (gemm_ms / 1e3) / 1e12
+    if args.granularity == "mxfp4":
+        fp8_peak *= 2.0  # fp4 = 2 x fp8 = 4 x bf16
+    recipe = {"mx": ("MXFP8 linear forward (dual quantize x2 + GEMM) throughput", "MX_BLOCKWISE", "E4M3", "fp8_e4m3 (fp32 accumulate)"),
+              "mxfp4": ("MXFP4 linear forward (dual quantize x2 + GEMM) throughput", "MX_BLOCKWISE", "E2M1_X2", "fp4_e2m1 (fp32 accumulate)"),
+              "blockwise": ("FP8 blockwise linear forward (quantize x2 + GEMM) throughput", "BLOCKWISE", "E4M3", "fp8_e4m3 (fp32 accumulate)"),
+              "tensorwise": ("FP8 tensorwise linear forward (quantize x2 + GEMM) throughput", "TENSORWISE", "E4M3", "fp8_e4m3 (fp32 accumulate)"),
+              "rowwise": ("FP8 rowwise linear forward (quantize x2 + GEMM) throughput", "ROWWISE", "E4M3", "fp8_e4m3 (fp32 accumulate)")}[args.granularity]
     result = {
-        "metric": "MXFP8 linear forward (dual quantize x2 + GEMM) throughput", "value": world * flops / (ms_per_step / 1e3) / 1e12,
+        "metric": recipe[0], "value": world * flops / (ms_per_step / 1e3) / 1e12,
         "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": recipe[3],
         "data": "synthetic",
-        "config": {"workload": args.workload, "M": M, "N": N, "K": K, "granularity": "MX_BLOCKWISE", "format": "E4M3",
+        "config": {"workload": args.workload, "M": M, "N": N, "K": K, "granularity": recipe[1], "format": recipe[2],
                    "out_dtype": "bf16", "per_gpu_shard": f"activation replicated, weight shard [{N}x{K}] per GPU",
                    "l2": "inputs 184 MB per step exceed the 126 MB L2; no flush between iterations"},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
-                     "traffic": GEMM_DRAM_TRAFFIC.get(args.workload), "kernel": "gemm_fp8_kernel<MX>",
-                     "peak_source": f"2 x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS.json",
-                     "gemm_ms_per_launch": gemm_ms, "frac_of_nominal_4500": achieved / 4500.0},
+                     "traffic": GEMM_DRAM_TRAFFIC.get(args.workload) if args.granularity == "mx" else None, "kernel": kernel_name,
+                     "peak_source": f"{'4' if args.granularity == 'mxfp4' else '2'} x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS.json",
+                     "gemm_ms_per_launch": gemm_ms,
+                     "frac_of_nominal": achieved / (9000.0 if args.granularity == "mxfp4" else 4500.0)},
         "clocks": clocks,
         "e2e": {"value": None if args.no_e2e else world * flops / (e2e_ms / 1e3) / 1e12, "unit": "TFLOPS",
                 "h2d_bytes_per_step": a_host.numel() * 2 + w_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
-                "ms_per_step": e2e_ms},
-        "gpu_launches": 5 * args.steps,  # per step: 2 dual quantize, 2 scale re-tile, 1 GEMM
+                "ms_per_step": None if args.no_e2e else e2e_ms},
+        "gpu_launches": launches * args.steps,
     }
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and args.granularity == "mx":
         cb = cpu_baseline(M, N, K, seed)
         cb.pop("seconds")
         result["cpu_baseline"] = cb
