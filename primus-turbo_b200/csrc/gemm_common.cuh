@@ -90,4 +90,21 @@ inline int make_tmap_bytes(CUtensorMap *m, const void *base, int64_t rows, int64
 }
 
 
+// 3-D tensor map over a [G, M, N] array of 16-bit elements, box = 64 columns (128 bytes) x box_rows x 1,
+// 128-byte swizzle; out-of-range rows / columns read as zero.
+inline int make_tmap_u16_3d(CUtensorMap *m, const void *base, int64_t G, int64_t M, int64_t N, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return set_error(PT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    PT_REQUIRE(aligned(base, 16) && (N * 2) % 16 == 0, "tensor map: base / row pitch must be 16-byte aligned");
+    cuuint64_t dims[3] = {(cuuint64_t) N, (cuuint64_t) M, (cuuint64_t) G};
+    cuuint64_t strides[2] = {(cuuint64_t) N * 2, (cuuint64_t) M * N * 2};
+    cuuint32_t box[3] = {64u, (cuuint32_t) box_rows, 1u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(PT_ERR_CUDA, "cuTensorMapEncodeTiled (16-bit 3-D) failed with code %d", (int) r);
+    return PT_OK;
+}
+
 }  // namespace ptb

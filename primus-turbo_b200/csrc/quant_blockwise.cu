@@ -6,8 +6,11 @@
 // csrc/kernels/quantization/quantization_blockwise.cu:60-334 of the reference:
 //   scale = qmax / fmaxf(amax, 1e-4f); q = fp8_rne(clamp(x * scale, +-qmax)); stored scale = 1.0f / scale.
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
+#include "gemm_common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace ptb {
 
@@ -184,6 +187,271 @@ __global__ void __launch_bounds__(kTileThreads)
     }
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// Persistent, TMA-pipelined form of the tile kernel for 16-bit inputs with N % 16 == 0.
+//
+// One producer warp streams 128 x 128 tiles (two 128-row x 128-byte boxes of a 3-D tensor map, 128-byte swizzle)
+// through a ring of shared-memory stages; eight consumer warps quantize a tile while the next ones are in flight.
+//   row pass   8 lanes share one row: each lane owns 16 consecutive elements (two 16-byte chunks), the 128-wide
+//              row amax is three shuffles, and a warp store writes four full 128-byte output rows
+//   col pass   a warp owns 16 rows, a lane four adjacent columns; the 128-row column amax goes through a 2 KiB
+//              shared-memory exchange (one named barrier per tile), and a warp store writes one 128-byte row
+// amax is taken on packed 16-bit pairs (two elements per instruction); the scale / clamp / convert arithmetic is
+// the same as in blockwise_tile_kernel, so both forms produce identical bytes.
+constexpr int kBqStages = 3;
+constexpr int kBqCtasPerSm = 2;
+constexpr int kBqTileBytes = kBlk * kBlk * 2;
+constexpr int kBqConsumerWarps = 8;
+constexpr int kBqThreads = 32 * (1 + kBqConsumerWarps);
+constexpr int kBqSmemBytes = kBqStages * kBqTileBytes + 1024 + 256;
+
+template <typename T> __device__ __forceinline__ uint32_t absmax2(uint32_t m, uint32_t w);
+template <> __device__ __forceinline__ uint32_t absmax2<__nv_bfloat16>(uint32_t m, uint32_t w) {
+    w &= 0x7FFF7FFFu;
+    __nv_bfloat162 r = __hmax2(*reinterpret_cast<__nv_bfloat162 *>(&m), *reinterpret_cast<__nv_bfloat162 *>(&w));
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+template <> __device__ __forceinline__ uint32_t absmax2<__half>(uint32_t m, uint32_t w) {
+    w &= 0x7FFF7FFFu;
+    __half2 r = __hmax2(*reinterpret_cast<__half2 *>(&m), *reinterpret_cast<__half2 *>(&w));
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+template <typename T> __device__ __forceinline__ float lo_f32(uint32_t w) { return Src<T>::to_f32((uint16_t) (w & 0xFFFF)); }
+template <typename T> __device__ __forceinline__ float hi_f32(uint32_t w) { return Src<T>::to_f32((uint16_t) (w >> 16)); }
+
+struct BqArgs {
+    int64_t M, N;
+    int tiles_n, tiles_m;      // tiles per row of tiles / per matrix (segment: over the padded row space)
+    int64_t total_tiles;
+    uint8_t *q_row, *q_col;
+    float *s_row, *s_col;
+    SegmentArgs seg;
+};
+
+template <typename T, int FMT, int MODE>
+__global__ void __launch_bounds__(kBqThreads, kBqCtasPerSm)
+    blockwise_tma_kernel(const __grid_constant__ CUtensorMap tmap, BqArgs a) {
+    using namespace sm100;
+    constexpr bool kRow = (MODE & 1) != 0 && MODE != MODE_WEIGHT;
+    constexpr bool kCol = (MODE & 2) != 0 && MODE != MODE_WEIGHT;
+    constexpr bool kSeg = MODE == MODE_SEGMENT;
+    constexpr bool kWeight = MODE == MODE_WEIGHT;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + kBqStages * kBqTileBytes);
+    uint64_t *empty_bar = full_bar + kBqStages;
+    __shared__ uint2 s_cmax[2][kBqConsumerWarps][32];  // packed column maxima of each 16-row band
+    __shared__ float s_wmax[2][kBqConsumerWarps];
+    __shared__ int s_abort;
+    volatile int *abort_flag = &s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < kBqStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], kBqConsumerWarps);
+        }
+        fence_barrier_init();
+        prefetch_tmap(&tmap);
+    }
+    __syncthreads();
+    bool ok = true;
+    const uint32_t per_b = (uint32_t) a.tiles_n * (uint32_t) a.tiles_m;
+    const int64_t m_blocks = (a.M + kBlk - 1) / kBlk;
+    const int64_t n_blocks = a.tiles_n;
+    const int64_t m_padded = kSeg ? a.seg.padded_offs[a.seg.num_groups] : 0;
+
+    // tile t -> batch, row block (segment: block of the padded row space), column block; and for the segment form
+    // the input rows it covers: [in_row0, in_row0 + n_valid), written at padded rows out_row0 ...
+    auto locate = [&](uint32_t t, int64_t &batch, int64_t &pid_m, int64_t &col_blk, int64_t &in_row0, int &n_valid) -> bool {
+        const uint32_t b = t / per_b, rem = t - b * per_b;
+        const uint32_t tm = rem / (uint32_t) a.tiles_n;
+        batch = b; pid_m = tm; col_blk = rem - tm * (uint32_t) a.tiles_n;
+        in_row0 = pid_m * kBlk;
+        n_valid = kBlk;
+        if constexpr (kSeg) {
+            const int64_t out_row0 = pid_m * kBlk;
+            if (out_row0 >= m_padded) return false;
+            int lo = 0, hi = a.seg.num_groups - 1;  // last group g with padded_offs[g] <= out_row0 (empty groups skipped)
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (a.seg.padded_offs[mid] <= out_row0) lo = mid; else hi = mid - 1;
+            }
+            in_row0 = a.seg.group_offs[lo] + (out_row0 - a.seg.padded_offs[lo]);
+            const int64_t in_hi = min(a.seg.group_offs[lo + 1], a.M);
+            n_valid = (int) max((int64_t) 0, min((int64_t) kBlk, in_hi - in_row0));
+        }
+        return true;
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            for (uint32_t t = blockIdx.x; t < (uint32_t) a.total_tiles; t += gridDim.x) {
+                int64_t batch, pid_m, col_blk, in_row0;
+                int n_valid;
+                if (!locate(t, batch, pid_m, col_blk, in_row0, n_valid)) continue;
+                if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
+                mbar_arrive_expect_tx(&full_bar[stage], kBqTileBytes);
+                uint8_t *dst = smem + stage * kBqTileBytes;
+                tma_load_3d(dst, &tmap, &full_bar[stage], (int) (col_blk * kBlk), (int) in_row0, (int) batch);
+                tma_load_3d(dst + kBqTileBytes / 2, &tmap, &full_bar[stage], (int) (col_blk * kBlk + 64), (int) in_row0, (int) batch);
+                if (++stage == kBqStages) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else {
+        const int cw = warp - 1;
+        // row pass: 8 lanes per row; lane l8 owns elements [16 l8, 16 l8 + 16) = chunks 2m, 2m + 1 of box l8 / 4.
+        // Lanes of box 0 read their even chunk first, lanes of box 1 their odd chunk: the eight 16-byte reads of a
+        // row then fall on eight different swizzled chunk positions (the two boxes share banks).
+        const int l8 = lane & 7, r_box = l8 >> 2, r_m = l8 & 3, r_sub = lane >> 3;
+        // col pass: lane = column quad of the 128-wide tile row, warp = band of 16 rows
+        const int c_box = lane >> 4, c_chunk = (lane & 15) >> 1, c_off = (lane & 1) << 3;
+        uint32_t stage = 0, phase = 0, tile_count = 0;
+        for (uint32_t t = blockIdx.x; t < (uint32_t) a.total_tiles; t += gridDim.x) {
+            int64_t batch, pid_m, col_blk, in_row0;
+            int n_valid;
+            if (!locate(t, batch, pid_m, col_blk, in_row0, n_valid)) continue;
+            if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
+            const uint8_t *tile = smem + stage * kBqTileBytes;
+            const int buf = tile_count & 1;
+            ++tile_count;
+            const int64_t n0 = col_blk * kBlk;
+            const int64_t out_row0 = pid_m * kBlk;
+
+            // ---- loads: everything this thread needs from the tile goes to registers, then the stage is released
+            uint4 rc[4][2];  // row pass / weight: 4 rows x 2 chunks
+            if constexpr (kRow || kWeight) {
+#pragma unroll
+                for (int it = 0; it < 4; ++it) {
+                    const int row = cw * 16 + it * 4 + r_sub;
+                    const uint8_t *rp = tile + r_box * (kBqTileBytes / 2) + row * 128;
+                    const int first = 2 * r_m + r_box, second = 2 * r_m + (r_box ^ 1);
+                    const uint4 x0 = *reinterpret_cast<const uint4 *>(rp + ((first ^ (row & 7)) << 4));
+                    const uint4 x1 = *reinterpret_cast<const uint4 *>(rp + ((second ^ (row & 7)) << 4));
+                    rc[it][0] = r_box ? x1 : x0;  // chunk 2m
+                    rc[it][1] = r_box ? x0 : x1;  // chunk 2m + 1
+                }
+            }
+            uint2 cc[16];  // col pass: 16 rows x 4 columns
+            if constexpr (kCol) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int row = cw * 16 + i;
+                    cc[i] = *reinterpret_cast<const uint2 *>(tile + c_box * (kBqTileBytes / 2) + row * 128 +
+                                                             ((c_chunk ^ (row & 7)) << 4) + c_off);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[stage]);  // this warp no longer reads the stage
+            if (++stage == kBqStages) { stage = 0; phase ^= 1; }
+
+            // ---- column maxima (and the tile maximum of the weight form) go through shared memory
+            if constexpr (kCol) {
+                uint32_t m01 = 0u, m23 = 0u;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    if (!kSeg || cw * 16 + i < n_valid) {  // rows past the group end belong to the next group
+                        m01 = absmax2<T>(m01, cc[i].x);
+                        m23 = absmax2<T>(m23, cc[i].y);
+                    }
+                }
+                s_cmax[buf][cw][lane] = make_uint2(m01, m23);
+            }
+            float w_amax = 0.f;
+            if constexpr (kWeight) {
+                uint32_t m = 0u;
+#pragma unroll
+                for (int it = 0; it < 4; ++it) {
+                    const uint32_t w[8] = {rc[it][0].x, rc[it][0].y, rc[it][0].z, rc[it][0].w, rc[it][1].x, rc[it][1].y, rc[it][1].z, rc[it][1].w};
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) m = absmax2<T>(m, w[k]);
+                }
+                w_amax = warp_max(fmaxf(lo_f32<T>(m), hi_f32<T>(m)));
+                if (lane == 0) s_wmax[buf][cw] = w_amax;
+            }
+            if constexpr (kCol || kWeight) asm volatile("bar.sync 1, %0;" ::"n"(kBqConsumerWarps * 32) : "memory");
+
+            // ---- row pass
+            if constexpr (kRow || kWeight) {
+                float w_scale = 0.f;
+                if constexpr (kWeight) {
+                    float m = 0.f;
+#pragma unroll
+                    for (int w = 0; w < kBqConsumerWarps; ++w) m = fmaxf(m, s_wmax[buf][w]);
+                    w_scale = scale_from_amax<FMT>(m, kEpsBlock);
+                    if (cw == 0 && lane == 0) a.s_row[(batch * m_blocks + pid_m) * n_blocks + col_blk] = __fdiv_rn(1.0f, w_scale);
+                }
+#pragma unroll
+                for (int it = 0; it < 4; ++it) {
+                    const int row = cw * 16 + it * 4 + r_sub;
+                    const uint32_t w[8] = {rc[it][0].x, rc[it][0].y, rc[it][0].z, rc[it][0].w, rc[it][1].x, rc[it][1].y, rc[it][1].z, rc[it][1].w};
+                    float scale = w_scale;
+                    if constexpr (kRow) {
+                        uint32_t m = 0u;
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) m = absmax2<T>(m, w[k]);
+                        float am = fmaxf(lo_f32<T>(m), hi_f32<T>(m));
+                        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+                        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+                        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 4));
+                        scale = scale_from_amax<FMT>(am, kEpsBlock);
+                    }
+                    const int64_t in_m = in_row0 + row;
+                    const int64_t gn = n0 + l8 * 16;
+                    if (row < n_valid && in_m < a.M && gn < a.N) {
+                        uint32_t o[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            o[k] = cvt4_fp8<FMT>(scale_clamp<FMT>(lo_f32<T>(w[2 * k]), scale), scale_clamp<FMT>(hi_f32<T>(w[2 * k]), scale),
+                                                 scale_clamp<FMT>(lo_f32<T>(w[2 * k + 1]), scale), scale_clamp<FMT>(hi_f32<T>(w[2 * k + 1]), scale));
+                        *reinterpret_cast<uint4 *>(a.q_row + (batch * a.M + in_m) * a.N + gn) = make_uint4(o[0], o[1], o[2], o[3]);
+                        if (kRow && l8 == 0) {
+                            const float inv = __fdiv_rn(1.0f, scale);
+                            if constexpr (kSeg) a.s_row[col_blk * a.M + in_m] = inv;  // transposed [N blocks, M]
+                            else a.s_row[(batch * a.M + in_m) * n_blocks + col_blk] = inv;
+                        }
+                    }
+                }
+            }
+
+            // ---- col pass
+            if constexpr (kCol) {
+                uint32_t m01 = 0u, m23 = 0u;
+#pragma unroll
+                for (int w = 0; w < kBqConsumerWarps; ++w) {
+                    const uint2 v = s_cmax[buf][w][lane];
+                    m01 = absmax2<T>(m01, v.x);
+                    m23 = absmax2<T>(m23, v.y);
+                }
+                const float sc0 = scale_from_amax<FMT>(lo_f32<T>(m01), kEpsBlock), sc1 = scale_from_amax<FMT>(hi_f32<T>(m01), kEpsBlock);
+                const float sc2 = scale_from_amax<FMT>(lo_f32<T>(m23), kEpsBlock), sc3 = scale_from_amax<FMT>(hi_f32<T>(m23), kEpsBlock);
+                const int64_t gc = n0 + 4 * lane;
+                if (gc < a.N) {
+                    if (cw == 0)
+                        *reinterpret_cast<float4 *>(a.s_col + (batch * (kSeg ? 0 : m_blocks) + pid_m) * a.N + gc) =
+                            make_float4(__fdiv_rn(1.0f, sc0), __fdiv_rn(1.0f, sc1), __fdiv_rn(1.0f, sc2), __fdiv_rn(1.0f, sc3));
+                    const int64_t out_rows = kSeg ? m_padded : a.M;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int row = cw * 16 + i;
+                        const int64_t out_m = out_row0 + row;
+                        if (out_m < out_rows) {
+                            const bool live = !kSeg || row < n_valid;  // padding rows of a group are written as zeros
+                            const uint32_t x01 = live ? cc[i].x : 0u, x23 = live ? cc[i].y : 0u;
+                            const uint32_t o = cvt4_fp8<FMT>(scale_clamp<FMT>(lo_f32<T>(x01), sc0), scale_clamp<FMT>(hi_f32<T>(x01), sc1),
+                                                             scale_clamp<FMT>(lo_f32<T>(x23), sc2), scale_clamp<FMT>(hi_f32<T>(x23), sc3));
+                            *reinterpret_cast<uint32_t *>(a.q_col + (batch * (kSeg ? 0 : a.M) + out_m) * a.N + gc) = o;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (!ok || *abort_flag) __nanosleep(100000);  // let a copy still in flight land before the shared memory is released
+}
+
 // y = float(q) * s for the three block-scale layouts
 template <typename T, int FMT>
 __global__ void __launch_bounds__(256) dequant_blockwise_kernel(const uint8_t *__restrict__ q,
@@ -272,6 +540,28 @@ static int launch_tile(const void *x, int x_dtype, int64_t B, int64_t m_tiles, i
                        void *q_row, float *s_row, void *q_col, float *s_col, SegmentArgs seg, void *stream) {
     PT_REQUIRE(B <= 65535 && m_tiles <= 65535, "blockwise: too many tiles along M or batch");
     dim3 grid((unsigned) ceil_div(N, kBlk), (unsigned) m_tiles, (unsigned) B);
+    const int64_t tiles_n = ceil_div(N, kBlk), total_tiles = tiles_n * m_tiles * B;
+    // persistent TMA form: 16-bit input, 16-byte vectors on every output row
+    const bool tma_ok = x_dtype != PT_F32 && N % 16 == 0 && aligned(x, 16) && (!q_row || aligned(q_row, 16)) &&
+                        (!q_col || aligned(q_col, 16)) && (!s_col || aligned(s_col, 16)) && M < (1ll << 31) && N < (1ll << 31) &&
+                        total_tiles < (1ll << 31) && getenv("PT_BW_QUANT_NO_TMA") == nullptr;
+    if (tma_ok) {
+        CUtensorMap tmap;
+        int rc = make_tmap_u16_3d(&tmap, x, B, M, N, kBlk);
+        if (rc != PT_OK) return rc;
+        BqArgs a{M, N, (int) tiles_n, (int) m_tiles, total_tiles, (uint8_t *) q_row, (uint8_t *) q_col, s_row, s_col, seg};
+        const int tma_grid = (int) std::min<int64_t>(total_tiles, (int64_t) sm_count() * kBqCtasPerSm);
+#define PT_BQ_LAUNCH(T_)                                                                                           \
+        PT_SWITCH_FP8(fmt, F, {                                                                                    \
+            auto kern = blockwise_tma_kernel<T_, F, MODE>;                                                         \
+            PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBqSmemBytes));     \
+            kern<<<tma_grid, kBqThreads, kBqSmemBytes, (cudaStream_t) stream>>>(tmap, a);                          \
+        })
+        if (x_dtype == PT_BF16) { PT_BQ_LAUNCH(__nv_bfloat16); } else { PT_BQ_LAUNCH(__half); }
+#undef PT_BQ_LAUNCH
+        PT_LAUNCH_OK();
+        return PT_OK;
+    }
     PT_SWITCH_SRC(x_dtype, T, {
         const int vec_ok = aligned(x, 16) && (N % 8 == 0) && (!q_row || aligned(q_row, 8)) && (!q_col || aligned(q_col, 8));
         PT_SWITCH_FP8(fmt, F, {

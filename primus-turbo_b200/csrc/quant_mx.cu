@@ -282,13 +282,6 @@ constexpr int kQConsumerWarps = 8;
 constexpr int kQThreads = 32 * (1 + kQConsumerWarps);
 constexpr int kQSmemBytes = kQStages * kQTileBytes + 1024 + 1024;
 
-__device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *m, uint64_t *bar, int c0, int c1, int c2) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(sm100::smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(sm100::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
-        : "memory");
-}
-
 // 32 scaled values -> 32 fp8 codes (8 words) or 32 fp4 codes (4 words).  The reference's soft clamp to +-qmax*scale
 // is subsumed by the saturating convert (identical bytes for every non-NaN input; a NaN converts to the NaN code).
 template <int FMT> __device__ __forceinline__ void mx_encode32(const float (&v)[32], const MxScale &s, uint32_t (&w)[8]) {
@@ -362,7 +355,7 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
                 const int tm = (int) (rem / (uint32_t) tiles_n), tn = (int) (rem - (uint32_t) tm * tiles_n);
                 if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
                 mbar_arrive_expect_tx(&full_bar[stage], kQTileBytes);
-                tma_load_3d(smem + stage * kQTileBytes, &tmap, &full_bar[stage], tn * kTileN, tm * kTileM, (int) g);
+                sm100::tma_load_3d(smem + stage * kQTileBytes, &tmap, &full_bar[stage], tn * kTileN, tm * kTileM, (int) g);
                 if (++stage == kQStages) { stage = 0; phase ^= 1; }
             }
         }
