@@ -63,6 +63,22 @@ template <typename T> __device__ __forceinline__ float load1(const T *p) {
 }
 template <> __device__ __forceinline__ float load1<float>(const float *p) { return *p; }
 
+// ---------------------------------------------------------------- packed 16-bit helpers
+// m = max(m, |w|) on both 16-bit halves of a word holding two bf16 / fp16 elements (a NaN half is ignored, as by fmaxf)
+template <typename T> __device__ __forceinline__ uint32_t absmax2(uint32_t m, uint32_t w);
+template <> __device__ __forceinline__ uint32_t absmax2<__nv_bfloat16>(uint32_t m, uint32_t w) {
+    w &= 0x7FFF7FFFu;
+    __nv_bfloat162 r = __hmax2(*reinterpret_cast<__nv_bfloat162 *>(&m), *reinterpret_cast<__nv_bfloat162 *>(&w));
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+template <> __device__ __forceinline__ uint32_t absmax2<__half>(uint32_t m, uint32_t w) {
+    w &= 0x7FFF7FFFu;
+    __half2 r = __hmax2(*reinterpret_cast<__half2 *>(&m), *reinterpret_cast<__half2 *>(&w));
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+template <typename T> __device__ __forceinline__ float lo_f32(uint32_t w) { return Src<T>::to_f32((uint16_t) (w & 0xFFFF)); }
+template <typename T> __device__ __forceinline__ float hi_f32(uint32_t w) { return Src<T>::to_f32((uint16_t) (w >> 16)); }
+
 // ---------------------------------------------------------------- fp32 -> fp8 / fp4 (RNE, saturate to finite)
 // Two floats to two codes; `lo` lands in the low byte (lower address).
 template <int FMT> __device__ __forceinline__ uint16_t cvt2_fp8(float lo, float hi) {

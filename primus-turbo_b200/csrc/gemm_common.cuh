@@ -70,6 +70,14 @@ inline EncodeTiledFn encode_tiled_fn() {
             qres == cudaDriverEntryPointSuccess)
             fn = reinterpret_cast<EncodeTiledFn>(p);
     });
+    // The driver call needs a context bound to the calling thread.  A thread that has made no runtime call yet
+    // (autograd's backward threads reach the quantizers this way) has none: cudaFree(nullptr) binds the device's
+    // primary context; once per thread.
+    thread_local bool bound = false;
+    if (!bound) {
+        cudaFree(nullptr);
+        bound = true;
+    }
     return fn;
 }
 

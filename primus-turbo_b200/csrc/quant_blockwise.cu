@@ -205,20 +205,6 @@ constexpr int kBqConsumerWarps = 8;
 constexpr int kBqThreads = 32 * (1 + kBqConsumerWarps);
 constexpr int kBqSmemBytes = kBqStages * kBqTileBytes + 1024 + 256;
 
-template <typename T> __device__ __forceinline__ uint32_t absmax2(uint32_t m, uint32_t w);
-template <> __device__ __forceinline__ uint32_t absmax2<__nv_bfloat16>(uint32_t m, uint32_t w) {
-    w &= 0x7FFF7FFFu;
-    __nv_bfloat162 r = __hmax2(*reinterpret_cast<__nv_bfloat162 *>(&m), *reinterpret_cast<__nv_bfloat162 *>(&w));
-    return *reinterpret_cast<uint32_t *>(&r);
-}
-template <> __device__ __forceinline__ uint32_t absmax2<__half>(uint32_t m, uint32_t w) {
-    w &= 0x7FFF7FFFu;
-    __half2 r = __hmax2(*reinterpret_cast<__half2 *>(&m), *reinterpret_cast<__half2 *>(&w));
-    return *reinterpret_cast<uint32_t *>(&r);
-}
-template <typename T> __device__ __forceinline__ float lo_f32(uint32_t w) { return Src<T>::to_f32((uint16_t) (w & 0xFFFF)); }
-template <typename T> __device__ __forceinline__ float hi_f32(uint32_t w) { return Src<T>::to_f32((uint16_t) (w >> 16)); }
-
 struct BqArgs {
     int64_t M, N;
     int tiles_n, tiles_m;      // tiles per row of tiles / per matrix (segment: over the padded row space)

@@ -381,6 +381,7 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
             float rv[32];
             float r_amax = 0.f;
             if constexpr (ROW || kNeed2D) {
+                uint32_t pm = 0u;  // packed |max| of the 16 words: two elements per instruction
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const uint4 q = tile.chunk(r_row, 4 * r_blk + j);
@@ -389,11 +390,16 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
                     for (int k = 0; k < 4; ++k) {
                         rv[8 * j + 2 * k] = Src<T>::to_f32((uint16_t) (w[k] & 0xFFFF));
                         rv[8 * j + 2 * k + 1] = Src<T>::to_f32((uint16_t) (w[k] >> 16));
+                        pm = absmax2<T>(pm, w[k]);
                     }
                 }
-                if constexpr (ROW && ROWRHT) { rht16(rv); rht16(rv + 16); }
+                if constexpr (ROW && ROWRHT) {  // the scale follows the transformed values
+                    rht16(rv); rht16(rv + 16);
 #pragma unroll
-                for (int k = 0; k < 32; ++k) r_amax = fmaxf(r_amax, fabsf(rv[k]));
+                    for (int k = 0; k < 32; ++k) r_amax = fmaxf(r_amax, fabsf(rv[k]));
+                } else {
+                    r_amax = fmaxf(lo_f32<T>(pm), hi_f32<T>(pm));
+                }
             }
             if constexpr (kNeed2D) {
                 // 32 x 32 tile maxima through shared memory (of the untransformed values; RHT and 2-D are never combined).
@@ -430,19 +436,26 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
             if constexpr (COL) {
                 // columns 2 c_pair, 2 c_pair + 1; rows c_band * 32 + c_half * 16 .. + 15
                 float c0[16], c1[16];
+                uint32_t pmc = 0u;  // packed |max| of (column 2 c_pair, column 2 c_pair + 1)
 #pragma unroll
                 for (int r = 0; r < 16; ++r) {
                     const uint32_t w = tile.pair(c_band * 32 + c_half * 16 + r, c_pair);
                     c0[r] = Src<T>::to_f32((uint16_t) (w & 0xFFFF));
                     c1[r] = Src<T>::to_f32((uint16_t) (w >> 16));
+                    pmc = absmax2<T>(pmc, w);
                 }
                 if constexpr (COLRHT) { rht16(c0); rht16(c1); }
                 float m0c = 0.f, m1c = 0.f;
                 if constexpr (COL2D) {
                     m0c = m1c = __uint_as_float(amax2d[c_band][c_pair >> 4]);
                 } else {
+                    if constexpr (COLRHT) {
 #pragma unroll
-                    for (int r = 0; r < 16; ++r) { m0c = fmaxf(m0c, fabsf(c0[r])); m1c = fmaxf(m1c, fabsf(c1[r])); }
+                        for (int r = 0; r < 16; ++r) { m0c = fmaxf(m0c, fabsf(c0[r])); m1c = fmaxf(m1c, fabsf(c1[r])); }
+                    } else {
+                        m0c = lo_f32<T>(pmc);
+                        m1c = hi_f32<T>(pmc);
+                    }
                     m0c = fmaxf(m0c, __shfl_xor_sync(0xffffffffu, m0c, 1));
                     m1c = fmaxf(m1c, __shfl_xor_sync(0xffffffffu, m1c, 1));
                 }
