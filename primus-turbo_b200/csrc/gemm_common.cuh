@@ -98,6 +98,22 @@ inline int make_tmap_bytes(CUtensorMap *m, const void *base, int64_t rows, int64
 }
 
 
+// 2-D byte tensor of 128-byte lines without swizzle, box = 128 bytes x box_lines (bulk fetch of small contiguous blocks)
+inline int make_tmap_lines(CUtensorMap *m, const void *base, int64_t lines, int box_lines) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return set_error(PT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    PT_REQUIRE(aligned(base, 128), "line tensor map: base must be 128-byte aligned");
+    cuuint64_t dims[2] = {128u, (cuuint64_t) lines};
+    cuuint64_t strides[1] = {128u};
+    cuuint32_t box[2] = {128u, (cuuint32_t) box_lines};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(PT_ERR_CUDA, "cuTensorMapEncodeTiled (lines) failed with code %d", (int) r);
+    return PT_OK;
+}
+
 // 3-D tensor map over a [G, M, N] array of 16-bit elements, box = 64 columns (128 bytes) x box_rows x 1,
 // 128-byte swizzle; out-of-range rows / columns read as zero.
 inline int make_tmap_u16_3d(CUtensorMap *m, const void *base, int64_t G, int64_t M, int64_t N, int box_rows) {

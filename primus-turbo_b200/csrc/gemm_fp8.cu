@@ -20,6 +20,7 @@
 //   MX_BLOCKWISE C = sum over 32-element K blocks of (a * 2^(sfa-127)) * (b * 2^(sfb-127))
 // Grouped form: rows of A / C are split into G groups (group g uses B[g]); tiles never cross a group.
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -57,6 +58,7 @@ struct GemmParams {
                                 // every group then yields a full [M, N] block of C (C is [G, M, N]), A and B are shared
     int *status;                // device int: set to a PT_ERR_* code on a bounded-wait expiry
     int raster_m;               // row blocks per raster band
+    int64_t sfb_line0;          // CTA-pair MX kernel: first 128-byte line of the re-tiled B scales in the scale buffer
 };
 
 // F4: packed e2m1 operands.  A 128-byte stage row then holds 256 elements = two 128-element scale blocks, so every
@@ -152,6 +154,105 @@ __global__ void __launch_bounds__(128) sf_retile_kernel(RetileArgs a) {
             *reinterpret_cast<uint4 *>(a.dst + (rb * a.num_kb + kb0 + kb) * 512 + lane * 16) = v;
         }
         __syncthreads();
+    }
+}
+
+// Write-out of one epilogue warp's 32 x BLOCK_N block of a tile: TMEM -> registers -> scales -> XOR-swizzled staging
+// rows in shared memory -> coalesced row-segment stores, masked at the end of the group / matrix.  `release` hands the
+// accumulator buffer back to the MMA issuer as soon as its last chunk is in registers.
+template <int BLOCK_N, int MODE, typename Release>
+__device__ __forceinline__ void epilogue_store_block(const GemmParams &p, uint32_t taddr, bool have_acc, int64_t tile_row0,
+                                                     int64_t c_row_end, int n0, int gi, uint8_t *stg, int lane, Release release) {
+    const int esize = p.c_dtype == PT_F32 ? 4 : 2;
+    const int pitch = 32 * esize;  // unpadded rows; 16-byte chunks are XOR-swizzled by row so that neither the
+                                   // row-per-lane writes nor the row-segment reads conflict on banks
+    const int lanes_per_row = (32 * esize) / 16;      // 4 (16-bit) or 8 (fp32)
+    const int rows_per_pass = 32 / lanes_per_row;     // 8 or 4
+    float row_scale = 1.f;
+    if (MODE == GEMM_TENSOR) row_scale = __ldg(p.sa) * __ldg(p.sb);
+    if (MODE == GEMM_ROW) row_scale = (tile_row0 + lane < c_row_end) ? __ldg(p.sa + tile_row0 + lane) : 0.f;
+    constexpr int kChunks = (BLOCK_N + 31) / 32;  // a last partial chunk reads past the tile; masked below
+    const int n_end = min(p.N, n0 + BLOCK_N);
+#pragma unroll 1
+    for (int c = 0; c < kChunks; ++c) {
+        uint32_t r[32];
+        if (have_acc) {
+            tmem_ld32(taddr + c * 32, r);
+            tmem_ld_wait();
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+        if (have_acc && c == kChunks - 1) {
+            // whole accumulator is in registers / staged: hand the TMEM buffer back to the MMA warp
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) release();
+        }
+        const int col0 = n0 + c * 32;
+        float f[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]) * row_scale;
+        if (MODE == GEMM_ROW) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] *= (col0 + i < n_end) ? __ldg(p.sb + (int64_t) gi * p.b_group_rows + col0 + i) : 0.f;
+        }
+        // stage this thread's row
+        uint8_t *my = stg + lane * pitch;
+        const int wsw = esize == 4 ? (lane & 7) : ((lane >> 1) & 3);  // chunk swizzle of this lane's row
+        if (esize == 4) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                *reinterpret_cast<float4 *>(my + 16 * (i ^ wsw)) = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+        } else if (p.c_dtype == PT_BF16) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                *reinterpret_cast<uint4 *>(my + 16 * (i ^ wsw)) =
+                    make_uint4(pack2<__nv_bfloat16>(f[8 * i], f[8 * i + 1]), pack2<__nv_bfloat16>(f[8 * i + 2], f[8 * i + 3]),
+                               pack2<__nv_bfloat16>(f[8 * i + 4], f[8 * i + 5]), pack2<__nv_bfloat16>(f[8 * i + 6], f[8 * i + 7]));
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                *reinterpret_cast<uint4 *>(my + 16 * (i ^ wsw)) =
+                    make_uint4(pack2<__half>(f[8 * i], f[8 * i + 1]), pack2<__half>(f[8 * i + 2], f[8 * i + 3]),
+                               pack2<__half>(f[8 * i + 4], f[8 * i + 5]), pack2<__half>(f[8 * i + 6], f[8 * i + 7]));
+        }
+        __syncwarp();
+        // coalesced write-out: lanes_per_row lanes cover one staged row
+        const int sub = lane % lanes_per_row;
+        const int elems16 = 16 / esize;
+#pragma unroll 1
+        for (int pass = 0; pass < 32; pass += rows_per_pass) {
+            const int rr = pass + lane / lanes_per_row;
+            const int64_t grow = tile_row0 + rr;
+            const int gcol = col0 + sub * elems16;
+            if (grow < c_row_end && gcol < n_end) {
+                const int rsw = esize == 4 ? (rr & 7) : ((rr >> 1) & 3);
+                const uint4 val = *reinterpret_cast<const uint4 *>(stg + rr * pitch + (sub ^ rsw) * 16);
+                uint8_t *dst = reinterpret_cast<uint8_t *>(p.C) + (grow * p.ldc + gcol) * esize;
+                if (p.vec_store_ok && gcol + elems16 <= n_end && p.beta == 0.f) {
+                    *reinterpret_cast<uint4 *>(dst) = val;
+                } else {
+                    const uint8_t *src = reinterpret_cast<const uint8_t *>(&val);
+                    for (int e = 0; e < elems16 && gcol + e < n_end; ++e) {
+                        if (esize == 4) {
+                            float nv = reinterpret_cast<const float *>(src)[e];
+                            if (p.beta != 0.f) nv += reinterpret_cast<float *>(dst)[e];
+                            reinterpret_cast<float *>(dst)[e] = nv;
+                        } else if (p.c_dtype == PT_BF16) {
+                            __nv_bfloat16 nv = reinterpret_cast<const __nv_bfloat16 *>(src)[e];
+                            if (p.beta != 0.f) nv = __float2bfloat16_rn(__bfloat162float(nv) + __bfloat162float(reinterpret_cast<__nv_bfloat16 *>(dst)[e]));
+                            reinterpret_cast<__nv_bfloat16 *>(dst)[e] = nv;
+                        } else {
+                            __half nv = reinterpret_cast<const __half *>(src)[e];
+                            if (p.beta != 0.f) nv = __float2half_rn(__half2float(nv) + __half2float(reinterpret_cast<__half *>(dst)[e]));
+                            reinterpret_cast<__half *>(dst)[e] = nv;
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
     }
 }
 
@@ -328,11 +429,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // ================================================================ epilogue
         const int q = warp & 3;  // TMEM lane quarter this warp may read
         uint8_t *stg = smem_epi + (warp - kEpiWarp0) * 32 * kStagePitchMax;
-        const int esize = p.c_dtype == PT_F32 ? 4 : 2;
-        const int pitch = 32 * esize;  // unpadded rows; 16-byte chunks are XOR-swizzled by row so that neither the
-                                       // row-per-lane writes nor the row-segment reads conflict on banks
-        const int lanes_per_row = (32 * esize) / 16;      // 4 (16-bit) or 8 (fp32)
-        const int rows_per_pass = 32 / lanes_per_row;     // 8 or 4
         uint32_t acc_stage = 0, acc_phase = 0;
         for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
             const int64_t c_row_base = p.koffs ? (int64_t) gi * p.M : (p.offs_write ? p.offs_write[gi] : 0);
@@ -345,92 +441,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             if (have_acc && !(ok = mbar_wait(&tmem_full_bar[acc_stage], acc_phase, abort_flag))) break;
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t) (q * 32) << 16) + acc_stage * BLOCK_N;
-            float row_scale = 1.f;
-            if (MODE == GEMM_TENSOR) row_scale = __ldg(p.sa) * __ldg(p.sb);
-            if (MODE == GEMM_ROW) row_scale = (tile_row0 + lane < c_row_end) ? __ldg(p.sa + tile_row0 + lane) : 0.f;
-            constexpr int kChunks = (BLOCK_N + 31) / 32;  // a last partial chunk reads past the tile; masked below
-            const int n_end = min(p.N, n0 + BLOCK_N);
-#pragma unroll 1
-            for (int c = 0; c < kChunks; ++c) {
-                uint32_t r[32];
-                if (have_acc) {
-                    tmem_ld32(taddr + c * 32, r);
-                    tmem_ld_wait();
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) r[i] = 0u;
-                }
-                if (have_acc && c == kChunks - 1) {
-                    // whole accumulator is in registers / staged: hand the TMEM buffer back to the MMA warp
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&tmem_empty_bar[acc_stage]);
-                }
-                const int col0 = n0 + c * 32;
-                float f[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]) * row_scale;
-                if (MODE == GEMM_ROW) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) f[i] *= (col0 + i < n_end) ? __ldg(p.sb + (int64_t) gi * p.b_group_rows + col0 + i) : 0.f;
-                }
-                // stage this thread's row
-                uint8_t *my = stg + lane * pitch;
-                const int wsw = esize == 4 ? (lane & 7) : ((lane >> 1) & 3);  // chunk swizzle of this lane's row
-                if (esize == 4) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        *reinterpret_cast<float4 *>(my + 16 * (i ^ wsw)) = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
-                } else if (p.c_dtype == PT_BF16) {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        *reinterpret_cast<uint4 *>(my + 16 * (i ^ wsw)) =
-                            make_uint4(pack2<__nv_bfloat16>(f[8 * i], f[8 * i + 1]), pack2<__nv_bfloat16>(f[8 * i + 2], f[8 * i + 3]),
-                                       pack2<__nv_bfloat16>(f[8 * i + 4], f[8 * i + 5]), pack2<__nv_bfloat16>(f[8 * i + 6], f[8 * i + 7]));
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        *reinterpret_cast<uint4 *>(my + 16 * (i ^ wsw)) =
-                            make_uint4(pack2<__half>(f[8 * i], f[8 * i + 1]), pack2<__half>(f[8 * i + 2], f[8 * i + 3]),
-                                       pack2<__half>(f[8 * i + 4], f[8 * i + 5]), pack2<__half>(f[8 * i + 6], f[8 * i + 7]));
-                }
-                __syncwarp();
-                // coalesced write-out: lanes_per_row lanes cover one staged row
-                const int sub = lane % lanes_per_row;
-                const int elems16 = 16 / esize;
-#pragma unroll 1
-                for (int pass = 0; pass < 32; pass += rows_per_pass) {
-                    const int rr = pass + lane / lanes_per_row;
-                    const int64_t grow = tile_row0 + rr;
-                    const int gcol = col0 + sub * elems16;
-                    if (grow < c_row_end && gcol < n_end) {
-                        const int rsw = esize == 4 ? (rr & 7) : ((rr >> 1) & 3);
-                        const uint4 val = *reinterpret_cast<const uint4 *>(stg + rr * pitch + (sub ^ rsw) * 16);
-                        uint8_t *dst = reinterpret_cast<uint8_t *>(p.C) + (grow * p.ldc + gcol) * esize;
-                        if (p.vec_store_ok && gcol + elems16 <= n_end && p.beta == 0.f) {
-                            *reinterpret_cast<uint4 *>(dst) = val;
-                        } else {
-                            const uint8_t *src = reinterpret_cast<const uint8_t *>(&val);
-                            for (int e = 0; e < elems16 && gcol + e < n_end; ++e) {
-                                if (esize == 4) {
-                                    float nv = reinterpret_cast<const float *>(src)[e];
-                                    if (p.beta != 0.f) nv += reinterpret_cast<float *>(dst)[e];
-                                    reinterpret_cast<float *>(dst)[e] = nv;
-                                } else if (p.c_dtype == PT_BF16) {
-                                    __nv_bfloat16 nv = reinterpret_cast<const __nv_bfloat16 *>(src)[e];
-                                    if (p.beta != 0.f) nv = __float2bfloat16_rn(__bfloat162float(nv) + __bfloat162float(reinterpret_cast<__nv_bfloat16 *>(dst)[e]));
-                                    reinterpret_cast<__nv_bfloat16 *>(dst)[e] = nv;
-                                } else {
-                                    __half nv = reinterpret_cast<const __half *>(src)[e];
-                                    if (p.beta != 0.f) nv = __float2half_rn(__half2float(nv) + __half2float(reinterpret_cast<__half *>(dst)[e]));
-                                    reinterpret_cast<__half *>(dst)[e] = nv;
-                                }
-                            }
-                        }
-                    }
-                }
-                __syncwarp();
-            }
+            epilogue_store_block<BLOCK_N, MODE>(p, taddr, have_acc, tile_row0, c_row_end, n0, gi, stg, lane,
+                                                [&]() { mbar_arrive(&tmem_empty_bar[acc_stage]); });
             if (have_acc && ++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1; }
         }
     }
@@ -448,6 +460,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
 }
 
+}  // namespace ptb
+
+#include "gemm_fp8_pair.cuh"
+
+namespace ptb {
+
 // ------------------------------------------------------------------------------------------------ host side
 struct MxScales {
     const uint8_t *sfa, *sfb;  // raw [rows, K/32]
@@ -463,35 +481,45 @@ static size_t mx_workspace_bytes(int64_t c_rows, int64_t N, int64_t K, int G, bo
     return (size_t) ((ra + rb) * num_kb * 512);
 }
 
+// Re-tiles the raw MX scales of both operands into the workspace ([A row blocks][B tile blocks], 512-byte blocks) and
+// records where they are.  `block_n` is the tile width the B blocks follow.
+static int prepare_mx_scales(GemmParams &p, const MxScales &mx, int64_t a_rows, int64_t b_rows, int block_n, int sfb_blocks,
+                             int sf_per_stage, cudaStream_t st) {
+    const bool grouped = p.offs_write != nullptr && !p.koffs;
+    const int sf_groups = p.koffs ? 1 : p.G;  // variable-K: one shared A and one shared B
+    const size_t need = mx_workspace_bytes(p.M, p.N, p.K, sf_groups, grouped, block_n) * sf_per_stage;
+    PT_REQUIRE(mx.workspace && mx.workspace_bytes >= need && aligned(mx.workspace, 16),
+               "MX GEMM: workspace of %zu bytes (16-byte aligned) required, got %zu", need, mx.workspace_bytes);
+    const int num_kb = (int) ceil_div(p.K, BLOCK_K) * sf_per_stage;  // scale blocks per row block
+    RetileArgs ra{};
+    ra.src = mx.sfa; ra.dst = (uint8_t *) mx.workspace; ra.src_rows = a_rows; ra.sf_ld = mx.sf_ld; ra.num_kb = num_kb;
+    ra.is_b = 0; ra.offs_read = grouped ? p.offs_read : nullptr; ra.offs_write = grouped ? p.offs_write : nullptr;
+    ra.G = sf_groups; ra.M = p.M;
+    ra.num_row_blocks = ceil_div(p.M, BLOCK_M) + (grouped ? p.G : 0);
+    RetileArgs rb = ra;
+    rb.src = mx.sfb; rb.dst = ra.dst + ra.num_row_blocks * num_kb * 512; rb.src_rows = b_rows; rb.is_b = 1;
+    rb.block_n = block_n; rb.sfb_blocks = sfb_blocks; rb.num_n_blocks = (int) ceil_div(p.N, block_n);
+    rb.b_group_rows = p.b_group_rows; rb.G = sf_groups; rb.num_row_blocks = (int64_t) sf_groups * rb.num_n_blocks * sfb_blocks;
+    const int max_blocks = sm_count() * 8;
+    dim3 ga((unsigned) std::min<int64_t>(ra.num_row_blocks, max_blocks), (unsigned) ceil_div(num_kb, 32));
+    dim3 gb((unsigned) std::min<int64_t>(rb.num_row_blocks, max_blocks), (unsigned) ceil_div(num_kb, 32));
+    sf_retile_kernel<<<ga, 128, 0, st>>>(ra);
+    PT_LAUNCH_OK();
+    sf_retile_kernel<<<gb, 128, 0, st>>>(rb);
+    PT_LAUNCH_OK();
+    p.sfa_tiled = ra.dst;
+    p.sfb_tiled = rb.dst;
+    p.sfb_line0 = (rb.dst - ra.dst) / 128;
+    return PT_OK;
+}
+
 template <int BLOCK_N, int MODE>
 static int launch_gemm(const void *a, int64_t a_rows, const void *b, int64_t b_rows, GemmParams p, const MxScales &mx,
                        int max_ctas, int64_t max_tiles, cudaStream_t st) {
     using Cfg = GemmCfg<BLOCK_N, mode_is_mx(MODE), MODE == GEMM_MXF4>;
     if constexpr (mode_is_mx(MODE)) {
-        const bool grouped = p.offs_write != nullptr && !p.koffs;
-        const int sf_groups = p.koffs ? 1 : p.G;  // variable-K: one shared A and one shared B
-        const size_t need = mx_workspace_bytes(p.M, p.N, p.K, sf_groups, grouped, BLOCK_N) * Cfg::kSfPerStage;
-        PT_REQUIRE(mx.workspace && mx.workspace_bytes >= need && aligned(mx.workspace, 16),
-                   "MX GEMM: workspace of %zu bytes (16-byte aligned) required, got %zu", need, mx.workspace_bytes);
-        const int num_kb = (int) ceil_div(p.K, BLOCK_K) * Cfg::kSfPerStage;  // scale blocks per row block
-        RetileArgs ra{};
-        ra.src = mx.sfa; ra.dst = (uint8_t *) mx.workspace; ra.src_rows = a_rows; ra.sf_ld = mx.sf_ld; ra.num_kb = num_kb;
-        ra.is_b = 0; ra.offs_read = grouped ? p.offs_read : nullptr; ra.offs_write = grouped ? p.offs_write : nullptr;
-        ra.G = sf_groups; ra.M = p.M;
-        ra.num_row_blocks = ceil_div(p.M, BLOCK_M) + (grouped ? p.G : 0);
-        RetileArgs rb = ra;
-        rb.src = mx.sfb; rb.dst = ra.dst + ra.num_row_blocks * num_kb * 512; rb.src_rows = b_rows; rb.is_b = 1;
-        rb.block_n = BLOCK_N; rb.sfb_blocks = Cfg::kSfbBlocks; rb.num_n_blocks = (int) ceil_div(p.N, BLOCK_N);
-        rb.b_group_rows = p.b_group_rows; rb.G = sf_groups; rb.num_row_blocks = (int64_t) sf_groups * rb.num_n_blocks * Cfg::kSfbBlocks;
-        const int max_blocks = sm_count() * 8;
-        dim3 ga((unsigned) std::min<int64_t>(ra.num_row_blocks, max_blocks), (unsigned) ceil_div(num_kb, 32));
-        dim3 gb((unsigned) std::min<int64_t>(rb.num_row_blocks, max_blocks), (unsigned) ceil_div(num_kb, 32));
-        sf_retile_kernel<<<ga, 128, 0, st>>>(ra);
-        PT_LAUNCH_OK();
-        sf_retile_kernel<<<gb, 128, 0, st>>>(rb);
-        PT_LAUNCH_OK();
-        p.sfa_tiled = ra.dst;
-        p.sfb_tiled = rb.dst;
+        int rc0 = prepare_mx_scales(p, mx, a_rows, b_rows, BLOCK_N, Cfg::kSfbBlocks, Cfg::kSfPerStage, st);
+        if (rc0 != PT_OK) return rc0;
     }
     CUtensorMap ta, tb;
     int rc;
@@ -511,6 +539,57 @@ static int launch_gemm(const void *a, int64_t a_rows, const void *b, int64_t b_r
     return PT_OK;
 }
 
+// CTA-pair launch (dense problems only): grid = 2 x min(tiles, co-resident clusters)
+template <int BLOCK_N, int MODE>
+static int launch_gemm_pair(const void *a, int64_t a_rows, const void *b, int64_t b_rows, GemmParams p, const MxScales &mx,
+                            cudaStream_t st) {
+    using Cfg = PairCfg<BLOCK_N, MODE == GEMM_MX>;
+    CUtensorMap ta, tb, tsf;
+    int rc;
+    if constexpr (MODE == GEMM_MX) {
+        if ((rc = prepare_mx_scales(p, mx, a_rows, b_rows, BLOCK_N, Cfg::kSfbBlocks, 1, st)) != PT_OK) return rc;
+        const int64_t lines = (int64_t) mx_workspace_bytes(p.M, p.N, p.K, 1, false, BLOCK_N) / 128;
+        if ((rc = make_tmap_lines(&tsf, p.sfa_tiled, lines, 4)) != PT_OK) return rc;
+    }
+    if ((rc = make_tmap_bytes(&ta, a, a_rows, p.K, p.K, BLOCK_M)) != PT_OK) return rc;
+    if ((rc = make_tmap_bytes(&tb, b, b_rows, p.K, p.K, Cfg::kHalfN)) != PT_OK) return rc;
+    if constexpr (MODE != GEMM_MX) tsf = ta;
+    auto kern = gemm_fp8_pair_kernel<BLOCK_N, MODE>;
+    PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    const int64_t tiles = ceil_div(p.M, 2 * BLOCK_M) * ceil_div(p.N, BLOCK_N);
+    static int max_clusters = 0;  // co-resident pairs of this device (one device per process in this library's use)
+    if (max_clusters == 0) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(2 * (unsigned) sm_count());
+        cfg.blockDim = dim3(kGemmThreads);
+        cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr; cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, (const void *) kern, &cfg) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            n = sm_count() / 2;
+        }
+        max_clusters = n;
+    }
+    const int pairs = (int) std::min<int64_t>(tiles, max_clusters);
+    if (pairs <= 0) return PT_OK;
+    kern<<<2 * pairs, kGemmThreads, Cfg::kSmemBytes, st>>>(ta, tb, tsf, p);
+    PT_LAUNCH_OK();
+    return PT_OK;
+}
+
+static bool pair_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("PT_GEMM_PAIR");
+        v = e ? atoi(e) : 0;
+    }
+    return v != 0;
+}
+
 static int default_block_n(int mode, int64_t N) { return N <= 128 ? 128 : (mode_is_mx(mode) ? 240 : 256); }
 
 template <int MODE>
@@ -518,6 +597,18 @@ static int dispatch_block_n(int block_n, const void *a, int64_t a_rows, const vo
                             const MxScales &mx, int max_ctas, cudaStream_t st) {
     // upper bound on tiles: every group may add one partial row block
     const int64_t m_blocks_bound = p.koffs ? (int64_t) p.G * ceil_div(p.M, BLOCK_M) : ceil_div(p.M, BLOCK_M) + (p.offs_write ? p.G : 0);
+    if constexpr (MODE == GEMM_TENSOR || MODE == GEMM_ROW || MODE == GEMM_MX) {
+        // large dense problems run on CTA pairs (256-row tiles, half of the B tile per CTA)
+        const bool dense = !p.offs_write && !p.koffs && p.G == 1 && p.beta == 0.f;
+        if (dense && block_n == 0 && pair_enabled() && p.M >= 1024 && p.N >= 512 && (MODE != GEMM_MX || aligned(mx.workspace, 128))) {
+            if constexpr (MODE == GEMM_MX) {
+                if (mx.workspace_bytes >= mx_workspace_bytes(p.M, p.N, p.K, 1, false, 224))
+                    return launch_gemm_pair<224, MODE>(a, a_rows, b, b_rows, p, mx, st);
+            } else {
+                return launch_gemm_pair<256, MODE>(a, a_rows, b, b_rows, p, mx, st);
+            }
+        }
+    }
     if (block_n == 0) block_n = default_block_n(MODE, p.N);
     const int64_t tiles = m_blocks_bound * ceil_div(p.N, block_n);
     switch (block_n) {
@@ -598,9 +689,12 @@ size_t pt_gemm_fp4_workspace_bytes(int64_t c_rows, int64_t N, int64_t K, int G, 
 
 size_t pt_gemm_fp8_workspace_bytes(int granularity, int64_t c_rows, int64_t N, int64_t K, int G, int grouped, int block_n) {
     if (granularity != PT_MX_BLOCKWISE || c_rows <= 0 || N <= 0 || K <= 0 || G < 1) return 0;
+    const bool auto_n = block_n == 0;
     if (block_n == 0) block_n = default_block_n(GEMM_MX, N);
     if (grouped == 2) return mx_workspace_bytes(c_rows, N, K, 1, false, block_n);  // variable-K: shared A and B
-    return mx_workspace_bytes(c_rows, N, K, G, grouped != 0, block_n);
+    size_t need = mx_workspace_bytes(c_rows, N, K, G, grouped != 0, block_n);
+    if (auto_n && !grouped && G == 1) need = std::max(need, mx_workspace_bytes(c_rows, N, K, 1, false, 224));  // CTA-pair tiles
+    return need;
 }
 
 int pt_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const void *b, const void *b_scale, int b_fmt, void *c,

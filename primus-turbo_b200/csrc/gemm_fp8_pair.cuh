@@ -1,0 +1,215 @@
+// Dense FP8 / MXFP8 GEMM on CTA pairs (tcgen05 cta_group::2): a cluster of two CTAs computes one 256 x BLOCK_N tile.
+// Included by gemm_fp8.cu (uses its GemmParams, GemmMode and epilogue_store_block).
+//
+// Why pairs: with one CTA per tile every tcgen05.mma reads its whole A (128 x 32 B) and B (BLOCK_N x 32 B) slice from
+// that CTA's shared memory while TMA writes the next stages into it, and the 128 B/clk shared-memory port, not the
+// tensor core, bounds the main loop.  In a pair each CTA stores only half of the B tile, so per CTA and K step the
+// shared-memory traffic drops from 48 KB + 48 KB to 32 KB + 32 KB at the same number of MMA cycles.
+//
+//   both CTAs    warp 0: TMA producer for its own A rows and its own half of the B rows; every copy counts its bytes
+//                on the leader's (rank 0) full barrier
+//   leader       warp 1: issues the cta_group::2 MMAs; tcgen05.commit multicasts the arrivals to both CTAs
+//                (stage free -> both producers, accumulator full -> both epilogues)
+//   both CTAs    warps 2-5: epilogue of the CTA's own 128 accumulator rows; hand the TMEM buffer back by arriving on
+//                the leader's barrier
+// No TMA multicast is used.  Every wait is bounded exactly as in the single-CTA kernel.
+#pragma once
+
+namespace ptb {
+
+template <int BLOCK_N, bool MX> struct PairCfg {
+    static constexpr int kHalfN = BLOCK_N / 2;
+    static constexpr int kSfbBlocks = (BLOCK_N + 127) / 128;
+    static constexpr int kSfColsOne = 4 + 4 * kSfbBlocks;
+    static constexpr int kSfCols = MX ? 2 * kSfColsOne : 0;  // double buffered
+    static constexpr int kAccStages = (2 * BLOCK_N + kSfCols <= 512) ? 2 : 1;
+    static constexpr int kTmemCols = 512;
+    static constexpr int kABytes = BLOCK_M * BLOCK_K;
+    static constexpr int kBBytes = kHalfN * BLOCK_K;
+    static constexpr int kSfBytes = MX ? 512 * (1 + kSfbBlocks) : 0;  // own A block + every B block of the tile
+    static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
+    static constexpr int kEpiBytes = kNumEpiWarps * 32 * kStagePitchMax;
+    static constexpr int kBarBytes = 1024;
+    static constexpr int kSmemBudget = 227 * 1024 - 1024 - 256;
+    static constexpr int kStages = std::min(8, (kSmemBudget - kEpiBytes - kBarBytes) / kStageBytes);
+    static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarBytes + 1024;
+    static_assert(kStages >= 3, "not enough shared memory for a 3-stage ring");
+    static_assert(BLOCK_N % 32 == 0 && BLOCK_N <= 256, "pair tile: N must be a multiple of 32 (16 B-tile rows per CTA)");
+    static_assert(kBBytes % 1024 == 0, "B stage must keep 1024-byte alignment");
+    static_assert(kAccStages * BLOCK_N + kSfCols <= 512, "accumulators and scales do not fit the tensor memory");
+};
+
+template <int BLOCK_N, int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                         const __grid_constant__ CUtensorMap tmap_sf, GemmParams p) {
+    constexpr bool MX = MODE == GEMM_MX;
+    using Cfg = PairCfg<BLOCK_N, MX>;
+    constexpr int kStages = Cfg::kStages;
+    constexpr int kAccStages = Cfg::kAccStages;
+    constexpr int kTileM = 2 * BLOCK_M;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *smem_a = smem;
+    uint8_t *smem_b = smem_a + kStages * Cfg::kABytes;
+    uint8_t *smem_sf = smem_b + kStages * Cfg::kBBytes;
+    uint8_t *smem_epi = smem_sf + kStages * Cfg::kSfBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_epi + Cfg::kEpiBytes);
+    uint64_t *full_bar = bars;                     // [kStages]    used in the leader: bytes of both CTAs
+    uint64_t *empty_bar = bars + kStages;          // [kStages]    one multicast commit arrival per use, in each CTA
+    uint64_t *tmem_full_bar = bars + 2 * kStages;  // [kAccStages] one multicast commit arrival per tile, in each CTA
+    uint64_t *tmem_empty_bar = tmem_full_bar + kAccStages;  // used in the leader: epilogue warps of both CTAs
+    uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(tmem_empty_bar + kAccStages);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_base_slot + 1);
+
+    const int warp = threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+    const uint32_t rank = cluster_ctarank();
+    const int num_n_blocks = (p.N + BLOCK_N - 1) / BLOCK_N;
+    const int num_m_blocks = (int) ((p.M + kTileM - 1) / kTileM);
+    const int num_k_blocks = (p.K + BLOCK_K - 1) / BLOCK_K;
+    const int num_tiles = num_m_blocks * num_n_blocks;
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int s = 0; s < kAccStages; ++s) {
+            mbar_init(&tmem_full_bar[s], 1);
+            mbar_init(&tmem_empty_bar[s], 2 * kNumEpiWarps);
+        }
+        fence_barrier_init();
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+        if constexpr (MX) prefetch_tmap(&tmap_sf);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_base_slot, Cfg::kTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    __syncwarp();
+    cluster_sync_all();  // barriers of both CTAs are initialised before any remote arrival or copy
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_base_slot;
+    const uint32_t tmem_sfa = tmem_base + kAccStages * BLOCK_N;
+    const uint32_t tmem_sfb = tmem_sfa + 4;
+
+    // tile t -> (m_blk, n_blk): bands of raster_m row blocks, rows fastest inside a band
+    auto locate = [&](int t, int &m_blk, int &n_blk) {
+        const int band_h = max(1, p.raster_m / 2);
+        const int per_band = band_h * num_n_blocks;
+        const int band = t / per_band, first_m = band * band_h;
+        const int rows = min(band_h, num_m_blocks - first_m);
+        const int in_band = t - band * per_band;
+        m_blk = first_m + in_band % rows;
+        n_blk = in_band / rows;
+    };
+    bool ok = true;
+    int m_blk, n_blk;
+
+    if (warp == 0) {
+        // ================================================================ TMA producer (both CTAs)
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0;
+            for (int t = pair; ok && t < num_tiles; t += num_pairs) {
+                locate(t, m_blk, n_blk);
+                const int a_row0 = m_blk * kTileM + (int) rank * BLOCK_M;
+                const int b_row0 = n_blk * BLOCK_N + (int) rank * Cfg::kHalfN;
+                // 512-byte scale blocks as rows of four 128-byte lines: A block of this CTA's rows, all B blocks of the tile
+                const int64_t sfa_line0 = ((int64_t) (2 * m_blk + (int) rank) * num_k_blocks) * 4;
+                const int64_t sfb_line0 = p.sfb_line0 + ((int64_t) n_blk * Cfg::kSfbBlocks * num_k_blocks) * 4;
+                for (int kb = 0; kb < num_k_blocks; ++kb) {
+                    if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
+                    const uint32_t full_leader = map_to_rank(&full_bar[stage], 0);
+                    if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
+                    tma_load_2d_pair(smem_a + stage * Cfg::kABytes, &tmap_a, full_leader, kb * BLOCK_K, a_row0);
+                    tma_load_2d_pair(smem_b + stage * Cfg::kBBytes, &tmap_b, full_leader, kb * BLOCK_K, b_row0);
+                    if constexpr (MX) {
+                        uint8_t *sf = smem_sf + stage * Cfg::kSfBytes;
+                        tma_load_2d_pair(sf, &tmap_sf, full_leader, 0, (int) (sfa_line0 + 4 * kb));
+#pragma unroll
+                        for (int j = 0; j < Cfg::kSfbBlocks; ++j)
+                            tma_load_2d_pair(sf + 512 * (1 + j), &tmap_sf, full_leader, 0,
+                                             (int) (sfb_line0 + ((int64_t) j * num_k_blocks + kb) * 4));
+                    }
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================================================================ MMA issuer (leader CTA only)
+        if (rank == 0 && elect_one()) {
+            const uint32_t idesc = MX ? idesc_block_scaled(p.a_fmt, p.b_fmt, kTileM, BLOCK_N) : idesc_f8(p.a_fmt, p.b_fmt, kTileM, BLOCK_N);
+            uint32_t stage = 0, phase = 0, acc_stage = 0, acc_phase = 0, sf_buf = 0;
+            for (int t = pair; ok && t < num_tiles; t += num_pairs) {
+                if (!(ok = mbar_wait(&tmem_empty_bar[acc_stage], acc_phase ^ 1, abort_flag))) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc_stage * BLOCK_N;
+                for (int kb = 0; kb < num_k_blocks; ++kb) {
+                    if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
+                    tc_fence_after_sync();
+                    const uint32_t sfa_cur = tmem_sfa + sf_buf * Cfg::kSfColsOne;
+                    const uint32_t sfb_cur = tmem_sfb + sf_buf * Cfg::kSfColsOne;
+                    if constexpr (MX) {
+                        const uint32_t sf_addr = smem_u32(smem_sf + stage * Cfg::kSfBytes);
+                        tc_cp_sf_pair(sfa_cur, smem_desc_sf(sf_addr));
+#pragma unroll
+                        for (int j = 0; j < Cfg::kSfbBlocks; ++j) tc_cp_sf_pair(sfb_cur + 4 * j, smem_desc_sf(sf_addr + 512 * (1 + j)));
+                        sf_buf ^= 1;
+                    }
+                    const uint64_t a_desc = smem_desc_sw128(smem_u32(smem_a + stage * Cfg::kABytes));
+                    const uint64_t b_desc = smem_desc_sw128(smem_u32(smem_b + stage * Cfg::kBBytes));
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        const uint64_t adv = (uint64_t) ((k * UMMA_K) >> 4);
+                        const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+                        if constexpr (MX) mma_mxf8_pair(d_tmem, a_desc + adv, b_desc + adv, idesc_sf_ids(idesc, k, k), sfa_cur, sfb_cur, accumulate);
+                        else mma_f8_pair(d_tmem, a_desc + adv, b_desc + adv, idesc, accumulate);
+                    }
+                    tc_commit_pair(&empty_bar[stage], 3);  // frees the ring slot in both CTAs
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                tc_commit_pair(&tmem_full_bar[acc_stage], 3);
+                if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        // ================================================================ epilogue (both CTAs, own 128 rows)
+        const int q = warp & 3;
+        uint8_t *stg = smem_epi + (warp - kEpiWarp0) * 32 * kStagePitchMax;
+        uint32_t acc_stage = 0, acc_phase = 0;
+        for (int t = pair; ok && t < num_tiles; t += num_pairs) {
+            locate(t, m_blk, n_blk);
+            const int64_t tile_row0 = (int64_t) m_blk * kTileM + (int64_t) rank * BLOCK_M + q * 32;
+            const int n0 = n_blk * BLOCK_N;
+            if (!(ok = mbar_wait(&tmem_full_bar[acc_stage], acc_phase, abort_flag))) break;
+            tc_fence_after_sync();
+            const uint32_t taddr = tmem_base + ((uint32_t) (q * 32) << 16) + acc_stage * BLOCK_N;
+            const uint32_t release_addr = map_to_rank(&tmem_empty_bar[acc_stage], 0);
+            epilogue_store_block<BLOCK_N, MODE>(p, taddr, true, tile_row0, p.M, n0, 0, stg, lane,
+                                                [&]() { mbar_arrive_cluster(release_addr); });
+            if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1; }
+        }
+    }
+
+    // ---- teardown: both CTAs leave together (the leader's MMAs read the peer's shared and tensor memory)
+    if (!ok || *abort_flag) {
+        if (p.status && lane == 0) atomicExch(p.status, (int) PT_ERR_TIMEOUT);
+        __nanosleep(200000);
+    }
+    tc_fence_before_sync();
+    __syncwarp();  // the cluster barrier is warp-aligned: role branches above may have split the warp
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+}  // namespace ptb
