@@ -543,17 +543,17 @@ static int launch_gemm(const void *a, int64_t a_rows, const void *b, int64_t b_r
 template <int BLOCK_N, int MODE>
 static int launch_gemm_pair(const void *a, int64_t a_rows, const void *b, int64_t b_rows, GemmParams p, const MxScales &mx,
                             cudaStream_t st) {
-    using Cfg = PairCfg<BLOCK_N, MODE == GEMM_MX>;
+    using Cfg = PairCfg<BLOCK_N, mode_is_mx(MODE), MODE == GEMM_MXF4>;
     CUtensorMap ta, tb, tsf;
     int rc;
-    if constexpr (MODE == GEMM_MX) {
-        if ((rc = prepare_mx_scales(p, mx, a_rows, b_rows, BLOCK_N, Cfg::kSfbBlocks, 1, st)) != PT_OK) return rc;
-        const int64_t lines = (int64_t) mx_workspace_bytes(p.M, p.N, p.K, 1, false, BLOCK_N) / 128;
-        if ((rc = make_tmap_lines(&tsf, p.sfa_tiled, lines, 4)) != PT_OK) return rc;
+    if constexpr (mode_is_mx(MODE)) {
+        if ((rc = prepare_mx_scales(p, mx, a_rows, b_rows, BLOCK_N, Cfg::kSfbBlocks, Cfg::kSfPerStage, st)) != PT_OK) return rc;
+        const int64_t lines = (int64_t) mx_workspace_bytes(p.M, p.N, p.K, 1, false, BLOCK_N) * Cfg::kSfPerStage / 128;
+        if ((rc = make_tmap_lines(&tsf, p.sfa_tiled, lines, 4 * Cfg::kSfPerStage)) != PT_OK) return rc;
     }
     if ((rc = make_tmap_bytes(&ta, a, a_rows, p.K, p.K, BLOCK_M)) != PT_OK) return rc;
     if ((rc = make_tmap_bytes(&tb, b, b_rows, p.K, p.K, Cfg::kHalfN)) != PT_OK) return rc;
-    if constexpr (MODE != GEMM_MX) tsf = ta;
+    if constexpr (!mode_is_mx(MODE)) tsf = ta;
     auto kern = gemm_fp8_pair_kernel<BLOCK_N, MODE>;
     PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     const int64_t tiles = ceil_div(p.M, 2 * BLOCK_M) * ceil_div(p.N, BLOCK_N);
@@ -584,8 +584,8 @@ static int launch_gemm_pair(const void *a, int64_t a_rows, const void *b, int64_
 static bool pair_enabled() {
     static int v = -1;
     if (v < 0) {
-        const char *e = getenv("PT_GEMM_PAIR");
-        v = e ? atoi(e) : 0;
+        const char *e = getenv("PT_GEMM_PAIR");  // PT_GEMM_PAIR=0 keeps every problem on the single-CTA kernel
+        v = e ? atoi(e) : 1;
     }
     return v != 0;
 }
@@ -597,12 +597,13 @@ static int dispatch_block_n(int block_n, const void *a, int64_t a_rows, const vo
                             const MxScales &mx, int max_ctas, cudaStream_t st) {
     // upper bound on tiles: every group may add one partial row block
     const int64_t m_blocks_bound = p.koffs ? (int64_t) p.G * ceil_div(p.M, BLOCK_M) : ceil_div(p.M, BLOCK_M) + (p.offs_write ? p.G : 0);
-    if constexpr (MODE == GEMM_TENSOR || MODE == GEMM_ROW || MODE == GEMM_MX) {
+    {
         // large dense problems run on CTA pairs (256-row tiles, half of the B tile per CTA)
         const bool dense = !p.offs_write && !p.koffs && p.G == 1 && p.beta == 0.f;
-        if (dense && block_n == 0 && pair_enabled() && p.M >= 1024 && p.N >= 512 && (MODE != GEMM_MX || aligned(mx.workspace, 128))) {
-            if constexpr (MODE == GEMM_MX) {
-                if (mx.workspace_bytes >= mx_workspace_bytes(p.M, p.N, p.K, 1, false, 224))
+        if (dense && block_n == 0 && pair_enabled() && p.M >= 1024 && p.N >= 512 && p.M * (int64_t) p.N >= (int64_t) 4096 * 4096 && (!mode_is_mx(MODE) || aligned(mx.workspace, 128))) {
+            if constexpr (mode_is_mx(MODE)) {
+                constexpr int kSfP = MODE == GEMM_MXF4 ? 2 : 1;
+                if (mx.workspace_bytes >= mx_workspace_bytes(p.M, p.N, p.K, 1, false, 224) * kSfP)
                     return launch_gemm_pair<224, MODE>(a, a_rows, b, b_rows, p, mx, st);
             } else {
                 return launch_gemm_pair<256, MODE>(a, a_rows, b, b_rows, p, mx, st);
@@ -681,10 +682,13 @@ extern "C" {
 
 size_t pt_gemm_fp4_workspace_bytes(int64_t c_rows, int64_t N, int64_t K, int G, int grouped, int block_n) {
     if (c_rows <= 0 || N <= 0 || K <= 0 || G < 1) return 0;
+    const bool auto_n = block_n == 0;
     if (block_n == 0) block_n = default_block_n(GEMM_MXF4, N);
     // K / 2 bytes per row -> ceil(K / 256) stages, two 512-byte scale blocks each
     if (grouped == 2) return 2 * mx_workspace_bytes(c_rows, N, K / 2, 1, false, block_n);
-    return 2 * mx_workspace_bytes(c_rows, N, K / 2, G, grouped != 0, block_n);
+    size_t need = 2 * mx_workspace_bytes(c_rows, N, K / 2, G, grouped != 0, block_n);
+    if (auto_n && !grouped && G == 1) need = std::max(need, 2 * mx_workspace_bytes(c_rows, N, K / 2, 1, false, 224));  // CTA-pair tiles
+    return need;
 }
 
 size_t pt_gemm_fp8_workspace_bytes(int granularity, int64_t c_rows, int64_t N, int64_t K, int G, int grouped, int block_n) {

@@ -17,16 +17,19 @@
 
 namespace ptb {
 
-template <int BLOCK_N, bool MX> struct PairCfg {
+// F4: packed e2m1 operands, 256 elements per 128-byte stage row = two 128-element scale blocks per stage (kSfPerStage)
+template <int BLOCK_N, bool MX, bool F4 = false> struct PairCfg {
     static constexpr int kHalfN = BLOCK_N / 2;
     static constexpr int kSfbBlocks = (BLOCK_N + 127) / 128;
-    static constexpr int kSfColsOne = 4 + 4 * kSfbBlocks;
-    static constexpr int kSfCols = MX ? 2 * kSfColsOne : 0;  // double buffered
+    static constexpr int kSfPerStage = F4 ? 2 : 1;
+    static constexpr int kSfColsHalf = 4 + 4 * kSfbBlocks;        // SFA block + SFB blocks of one 128-element scale block
+    static constexpr int kSfColsOne = kSfColsHalf * kSfPerStage;  // ... of one stage
+    static constexpr int kSfCols = MX ? 2 * kSfColsOne : 0;       // double buffered
     static constexpr int kAccStages = (2 * BLOCK_N + kSfCols <= 512) ? 2 : 1;
     static constexpr int kTmemCols = 512;
     static constexpr int kABytes = BLOCK_M * BLOCK_K;
     static constexpr int kBBytes = kHalfN * BLOCK_K;
-    static constexpr int kSfBytes = MX ? 512 * (1 + kSfbBlocks) : 0;  // own A block + every B block of the tile
+    static constexpr int kSfBytes = MX ? 512 * (1 + kSfbBlocks) * kSfPerStage : 0;  // own A blocks + every B block of the tile
     static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
     static constexpr int kEpiBytes = kNumEpiWarps * 32 * kStagePitchMax;
     static constexpr int kBarBytes = 1024;
@@ -43,8 +46,10 @@ template <int BLOCK_N, int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_sf, GemmParams p) {
-    constexpr bool MX = MODE == GEMM_MX;
-    using Cfg = PairCfg<BLOCK_N, MX>;
+    constexpr bool MX = mode_is_mx(MODE);
+    constexpr bool F4 = MODE == GEMM_MXF4;
+    using Cfg = PairCfg<BLOCK_N, MX, F4>;
+    constexpr int kSfP = Cfg::kSfPerStage;
     constexpr int kStages = Cfg::kStages;
     constexpr int kAccStages = Cfg::kAccStages;
     constexpr int kTileM = 2 * BLOCK_M;
@@ -121,8 +126,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                 const int a_row0 = m_blk * kTileM + (int) rank * BLOCK_M;
                 const int b_row0 = n_blk * BLOCK_N + (int) rank * Cfg::kHalfN;
                 // 512-byte scale blocks as rows of four 128-byte lines: A block of this CTA's rows, all B blocks of the tile
-                const int64_t sfa_line0 = ((int64_t) (2 * m_blk + (int) rank) * num_k_blocks) * 4;
-                const int64_t sfb_line0 = p.sfb_line0 + ((int64_t) n_blk * Cfg::kSfbBlocks * num_k_blocks) * 4;
+                // (kSfP blocks per K step; one box fetches the kSfP consecutive blocks of a step)
+                const int64_t sfa_line0 = ((int64_t) (2 * m_blk + (int) rank) * num_k_blocks) * kSfP * 4;
+                const int64_t sfb_line0 = p.sfb_line0 + ((int64_t) n_blk * Cfg::kSfbBlocks * num_k_blocks) * kSfP * 4;
                 for (int kb = 0; kb < num_k_blocks; ++kb) {
                     if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
                     const uint32_t full_leader = map_to_rank(&full_bar[stage], 0);
@@ -131,11 +137,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     tma_load_2d_pair(smem_b + stage * Cfg::kBBytes, &tmap_b, full_leader, kb * BLOCK_K, b_row0);
                     if constexpr (MX) {
                         uint8_t *sf = smem_sf + stage * Cfg::kSfBytes;
-                        tma_load_2d_pair(sf, &tmap_sf, full_leader, 0, (int) (sfa_line0 + 4 * kb));
+                        tma_load_2d_pair(sf, &tmap_sf, full_leader, 0, (int) (sfa_line0 + 4 * kSfP * kb));
 #pragma unroll
                         for (int j = 0; j < Cfg::kSfbBlocks; ++j)
-                            tma_load_2d_pair(sf + 512 * (1 + j), &tmap_sf, full_leader, 0,
-                                             (int) (sfb_line0 + ((int64_t) j * num_k_blocks + kb) * 4));
+                            tma_load_2d_pair(sf + kSfP * 512 * (1 + j), &tmap_sf, full_leader, 0,
+                                             (int) (sfb_line0 + ((int64_t) j * num_k_blocks + kb) * kSfP * 4));
                     }
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
@@ -144,7 +150,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     } else if (warp == 1) {
         // ================================================================ MMA issuer (leader CTA only)
         if (rank == 0 && elect_one()) {
-            const uint32_t idesc = MX ? idesc_block_scaled(p.a_fmt, p.b_fmt, kTileM, BLOCK_N) : idesc_f8(p.a_fmt, p.b_fmt, kTileM, BLOCK_N);
+            const uint32_t idesc = F4 ? idesc_block_scaled(1, 1, kTileM, BLOCK_N)  // kind::mxf4: format code 1 = e2m1
+                                   : MX ? idesc_block_scaled(p.a_fmt, p.b_fmt, kTileM, BLOCK_N)
+                                        : idesc_f8(p.a_fmt, p.b_fmt, kTileM, BLOCK_N);
             uint32_t stage = 0, phase = 0, acc_stage = 0, acc_phase = 0, sf_buf = 0;
             for (int t = pair; ok && t < num_tiles; t += num_pairs) {
                 if (!(ok = mbar_wait(&tmem_empty_bar[acc_stage], acc_phase ^ 1, abort_flag))) break;
@@ -157,9 +165,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     const uint32_t sfb_cur = tmem_sfb + sf_buf * Cfg::kSfColsOne;
                     if constexpr (MX) {
                         const uint32_t sf_addr = smem_u32(smem_sf + stage * Cfg::kSfBytes);
-                        tc_cp_sf_pair(sfa_cur, smem_desc_sf(sf_addr));
 #pragma unroll
-                        for (int j = 0; j < Cfg::kSfbBlocks; ++j) tc_cp_sf_pair(sfb_cur + 4 * j, smem_desc_sf(sf_addr + 512 * (1 + j)));
+                        for (int h = 0; h < kSfP; ++h) {
+                            tc_cp_sf_pair(sfa_cur + h * Cfg::kSfColsHalf, smem_desc_sf(sf_addr + 512 * h));
+#pragma unroll
+                            for (int j = 0; j < Cfg::kSfbBlocks; ++j)
+                                tc_cp_sf_pair(sfb_cur + h * Cfg::kSfColsHalf + 4 * j, smem_desc_sf(sf_addr + kSfP * 512 * (1 + j) + 512 * h));
+                        }
                         sf_buf ^= 1;
                     }
                     const uint64_t a_desc = smem_desc_sw128(smem_u32(smem_a + stage * Cfg::kABytes));
@@ -168,7 +180,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
                         const uint64_t adv = (uint64_t) ((k * UMMA_K) >> 4);
                         const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-                        if constexpr (MX) mma_mxf8_pair(d_tmem, a_desc + adv, b_desc + adv, idesc_sf_ids(idesc, k, k), sfa_cur, sfb_cur, accumulate);
+                        if constexpr (F4)  // 64 elements, two scales per row: scale block k / 2, bytes (k % 2) * 2 .. +1
+                            mma_mxf4_pair(d_tmem, a_desc + adv, b_desc + adv, idesc_sf_ids(idesc, (k & 1) * 2, (k & 1) * 2),
+                                          sfa_cur + (k >> 1) * Cfg::kSfColsHalf, sfb_cur + (k >> 1) * Cfg::kSfColsHalf, accumulate);
+                        else if constexpr (MX) mma_mxf8_pair(d_tmem, a_desc + adv, b_desc + adv, idesc_sf_ids(idesc, k, k), sfa_cur, sfb_cur, accumulate);
                         else mma_f8_pair(d_tmem, a_desc + adv, b_desc + adv, idesc, accumulate);
                     }
                     tc_commit_pair(&empty_bar[stage], 3);  // frees the ring slot in both CTAs

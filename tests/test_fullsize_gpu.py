@@ -158,6 +158,24 @@ def test_gemm_sampled_outputs_determinism_and_permutation(mods, operands, gran):
     assert torch.equal(cp, c[perm])
 
 
+def test_mxfp4_gemm_sampled_outputs(mods, operands):
+    """MXFP4 forward at the benchmark shape: sampled outputs against the dequantized operands (tolerance 5e-2 stated for
+    FP4; the products themselves are exact, so the bf16 rounding of the output dominates)."""
+    qi, _, nv, _, SR = mods
+    from primus_turbo.pytorch.kernels.gemm.gemm_fp4_impl import gemm_fp4_impl
+    a, w = operands
+    fp4 = torch.float4_e2m1fn_x2
+    qa, sa = qi.quantize_mxfp4_impl(a, fp4, 1, 32)
+    qw, sw = qi.quantize_mxfp4_impl(w, fp4, 1, 32)
+    c = gemm_fp4_impl(qa, sa, False, qw, sw, True, torch.bfloat16, False)
+    nv.check_status(c.device)
+    rows, cols = _rows(M, 64, 11), _rows(N, 64, 12)
+    qa8, qw8 = qa.view(torch.uint8), qw.view(torch.uint8)  # torch cannot index packed-fp4 tensors
+    ref = og.gemm_nt(oq.dequantize_mx(u8(qa8[rows]), u8(sa[rows]), "e2m1"), oq.dequantize_mx(u8(qw8[cols]), u8(sw[cols]), "e2m1"))
+    assert og.rel_frobenius(f32(c[rows][:, cols]), ref) <= 1e-2
+    assert torch.equal(c, gemm_fp4_impl(qa, sa, False, qw, sw, True, torch.bfloat16, False))
+
+
 def test_tensorwise_gemm_is_linear_in_the_scale(mods, operands):
     qi, gi, nv, SG, _ = mods
     a, w = operands
