@@ -285,24 +285,46 @@ def main():
     ms_total = t_begin.elapsed_time(t_end)
     gemm_ms = sum(e0.elapsed_time(e1) for e0, e1 in gemm_events) / len(gemm_events)
 
-    # end to end through the public operator, host buffers in and out
-    out_host = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    # End to end through the public operator, host buffers in and out.  Every step uploads its inputs from pinned host
+    # memory and downloads its result; uploads, compute and downloads run on three streams over two sets of device
+    # buffers, so step i + 1's upload overlaps step i's download (PCIe is full duplex) — all inside the timed region.
+    out_host = [torch.empty((M, N), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    a_dev = [torch.empty_like(a) for _ in range(2)]
+    w_dev = [torch.empty_like(w) for _ in range(2)]
+    main = torch.cuda.current_stream()
+    up, down = torch.cuda.Stream(), torch.cuda.Stream()
+    uploaded = [torch.cuda.Event() for _ in range(2)]
+    computed = [torch.cuda.Event() for _ in range(2)]
+    downloaded = [torch.cuda.Event() for _ in range(2)]
+    results = [None, None]
 
-    def e2e_step():
-        a_d = a_host.to(dev, non_blocking=True)
-        w_d = w_host.to(dev, non_blocking=True)
-        y = public_op(a_d, w_d, trans_b=True, out_dtype=torch.bfloat16, config=cfg)
-        out_host.copy_(y, non_blocking=True)
+    def e2e_step(i):
+        s = i & 1
+        with torch.cuda.stream(up):
+            up.wait_event(computed[s])        # the compute that read this input set two steps ago is done
+            a_dev[s].copy_(a_host, non_blocking=True)
+            w_dev[s].copy_(w_host, non_blocking=True)
+            uploaded[s].record(up)
+        main.wait_event(uploaded[s])
+        main.wait_event(downloaded[s])       # the result buffer of two steps ago has left the device
+        results[s] = public_op(a_dev[s], w_dev[s], trans_b=True, out_dtype=torch.bfloat16, config=cfg)
+        computed[s].record(main)
+        with torch.cuda.stream(down):
+            down.wait_event(computed[s])
+            out_host[s].copy_(results[s], non_blocking=True)
+            downloaded[s].record(down)
 
     with torch.no_grad():
-        for _ in range(0 if args.no_e2e else 3):
-            e2e_step()
+        for i in range(0 if args.no_e2e else 4):
+            e2e_step(i)
         barrier()
         e_begin, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        n_e2e = 0 if args.no_e2e else max(3, min(args.steps, 10))
+        n_e2e = 0 if args.no_e2e else max(4, min(args.steps, 12))
         e_begin.record()
-        for _ in range(n_e2e):
-            e2e_step()
+        for i in range(n_e2e):
+            e2e_step(i)
+        main.wait_stream(down)               # the last downloads are part of the measurement
+        main.wait_stream(up)
         e_end.record()
         barrier()
     e2e_ms = e_begin.elapsed_time(e_end) / n_e2e if n_e2e else float('nan')
@@ -344,7 +366,7 @@ def main():
                      "frac_of_nominal": achieved / (9000.0 if args.granularity == "mxfp4" else 4500.0)},
         "clocks": clocks,
         "e2e": {"value": None if args.no_e2e else world * flops / (e2e_ms / 1e3) / 1e12, "unit": "TFLOPS",
-                "h2d_bytes_per_step": a_host.numel() * 2 + w_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
+                "h2d_bytes_per_step": a_host.numel() * 2 + w_host.numel() * 2, "d2h_bytes_per_step": out_host[0].numel() * 2,
                 "ms_per_step": None if args.no_e2e else e2e_ms},
         "gpu_launches": launches * args.steps,
     }
