@@ -548,7 +548,8 @@ static int launch_gemm_pair(const void *a, int64_t a_rows, const void *b, int64_
     int rc;
     if constexpr (mode_is_mx(MODE)) {
         if ((rc = prepare_mx_scales(p, mx, a_rows, b_rows, BLOCK_N, Cfg::kSfbBlocks, Cfg::kSfPerStage, st)) != PT_OK) return rc;
-        const int64_t lines = (int64_t) mx_workspace_bytes(p.M, p.N, p.K, 1, false, BLOCK_N) * Cfg::kSfPerStage / 128;
+        const bool grouped = p.offs_write != nullptr && !p.koffs;
+        const int64_t lines = (int64_t) mx_workspace_bytes(p.M, p.N, p.K, p.koffs ? 1 : p.G, grouped, BLOCK_N) * Cfg::kSfPerStage / 128;
         if ((rc = make_tmap_lines(&tsf, p.sfa_tiled, lines, 4 * Cfg::kSfPerStage)) != PT_OK) return rc;
     }
     if ((rc = make_tmap_bytes(&ta, a, a_rows, p.K, p.K, BLOCK_M)) != PT_OK) return rc;
@@ -556,7 +557,9 @@ static int launch_gemm_pair(const void *a, int64_t a_rows, const void *b, int64_
     if constexpr (!mode_is_mx(MODE)) tsf = ta;
     auto kern = gemm_fp8_pair_kernel<BLOCK_N, MODE>;
     PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    const int64_t tiles = ceil_div(p.M, 2 * BLOCK_M) * ceil_div(p.N, BLOCK_N);
+    // upper bound on tiles: every group may add one partial 256-row tile
+    const int64_t m_tiles = p.koffs ? (int64_t) p.G * ceil_div(p.M, 2 * BLOCK_M) : ceil_div(p.M, 2 * BLOCK_M) + (p.offs_write ? p.G : 0);
+    const int64_t tiles = m_tiles * ceil_div(p.N, BLOCK_N);
     static int max_clusters = 0;  // co-resident pairs of this device (one device per process in this library's use)
     if (max_clusters == 0) {
         cudaLaunchConfig_t cfg{};
@@ -582,12 +585,8 @@ static int launch_gemm_pair(const void *a, int64_t a_rows, const void *b, int64_
 }
 
 static bool pair_enabled() {
-    static int v = -1;
-    if (v < 0) {
-        const char *e = getenv("PT_GEMM_PAIR");  // PT_GEMM_PAIR=0 keeps every problem on the single-CTA kernel
-        v = e ? atoi(e) : 1;
-    }
-    return v != 0;
+    const char *e = getenv("PT_GEMM_PAIR");  // PT_GEMM_PAIR=0 keeps every problem on the single-CTA kernel
+    return !e || atoi(e) != 0;
 }
 
 static int default_block_n(int mode, int64_t N) { return N <= 128 ? 128 : (mode_is_mx(mode) ? 240 : 256); }
@@ -598,12 +597,16 @@ static int dispatch_block_n(int block_n, const void *a, int64_t a_rows, const vo
     // upper bound on tiles: every group may add one partial row block
     const int64_t m_blocks_bound = p.koffs ? (int64_t) p.G * ceil_div(p.M, BLOCK_M) : ceil_div(p.M, BLOCK_M) + (p.offs_write ? p.G : 0);
     {
-        // large dense problems run on CTA pairs (256-row tiles, half of the B tile per CTA)
-        const bool dense = !p.offs_write && !p.koffs && p.G == 1 && p.beta == 0.f;
-        if (dense && block_n == 0 && pair_enabled() && p.M >= 1024 && p.N >= 512 && p.M * (int64_t) p.N >= (int64_t) 4096 * 4096 && (!mode_is_mx(MODE) || aligned(mx.workspace, 128))) {
+        // Large problems run on CTA pairs (256-row tiles, half of the B tile per CTA).  Group lengths live on the
+        // device; the average rows per group decide (short groups would waste up to 128 rows of work each).
+        const int64_t rows_per_group = p.koffs ? p.M : p.M / p.G;
+        const int64_t out_elems = (p.koffs ? (int64_t) p.G : 1) * p.M * (int64_t) p.N;
+        const bool grouped = p.offs_write != nullptr && !p.koffs;
+        if (block_n == 0 && max_ctas <= 0 && pair_enabled() && rows_per_group >= 1024 && p.N >= 512 &&
+            out_elems >= (int64_t) 4096 * 4096 && (!mode_is_mx(MODE) || aligned(mx.workspace, 128))) {
             if constexpr (mode_is_mx(MODE)) {
                 constexpr int kSfP = MODE == GEMM_MXF4 ? 2 : 1;
-                if (mx.workspace_bytes >= mx_workspace_bytes(p.M, p.N, p.K, 1, false, 224) * kSfP)
+                if (mx.workspace_bytes >= mx_workspace_bytes(p.M, p.N, p.K, p.koffs ? 1 : p.G, grouped, 224) * kSfP)
                     return launch_gemm_pair<224, MODE>(a, a_rows, b, b_rows, p, mx, st);
             } else {
                 return launch_gemm_pair<256, MODE>(a, a_rows, b, b_rows, p, mx, st);
@@ -685,9 +688,11 @@ size_t pt_gemm_fp4_workspace_bytes(int64_t c_rows, int64_t N, int64_t K, int G, 
     const bool auto_n = block_n == 0;
     if (block_n == 0) block_n = default_block_n(GEMM_MXF4, N);
     // K / 2 bytes per row -> ceil(K / 256) stages, two 512-byte scale blocks each
-    if (grouped == 2) return 2 * mx_workspace_bytes(c_rows, N, K / 2, 1, false, block_n);
+    if (grouped == 2)
+        return 2 * std::max(mx_workspace_bytes(c_rows, N, K / 2, 1, false, block_n),
+                            auto_n ? mx_workspace_bytes(c_rows, N, K / 2, 1, false, 224) : (size_t) 0);
     size_t need = 2 * mx_workspace_bytes(c_rows, N, K / 2, G, grouped != 0, block_n);
-    if (auto_n && !grouped && G == 1) need = std::max(need, 2 * mx_workspace_bytes(c_rows, N, K / 2, 1, false, 224));  // CTA-pair tiles
+    if (auto_n) need = std::max(need, 2 * mx_workspace_bytes(c_rows, N, K / 2, G, grouped != 0, 224));  // CTA-pair tiles
     return need;
 }
 
@@ -695,9 +700,10 @@ size_t pt_gemm_fp8_workspace_bytes(int granularity, int64_t c_rows, int64_t N, i
     if (granularity != PT_MX_BLOCKWISE || c_rows <= 0 || N <= 0 || K <= 0 || G < 1) return 0;
     const bool auto_n = block_n == 0;
     if (block_n == 0) block_n = default_block_n(GEMM_MX, N);
-    if (grouped == 2) return mx_workspace_bytes(c_rows, N, K, 1, false, block_n);  // variable-K: shared A and B
+    if (grouped == 2)  // variable-K: shared A and B
+        return std::max(mx_workspace_bytes(c_rows, N, K, 1, false, block_n), auto_n ? mx_workspace_bytes(c_rows, N, K, 1, false, 224) : (size_t) 0);
     size_t need = mx_workspace_bytes(c_rows, N, K, G, grouped != 0, block_n);
-    if (auto_n && !grouped && G == 1) need = std::max(need, mx_workspace_bytes(c_rows, N, K, 1, false, 224));  // CTA-pair tiles
+    if (auto_n) need = std::max(need, mx_workspace_bytes(c_rows, N, K, G, grouped != 0, 224));  // CTA-pair tiles
     return need;
 }
 

@@ -1,4 +1,5 @@
-// Dense FP8 / MXFP8 GEMM on CTA pairs (tcgen05 cta_group::2): a cluster of two CTAs computes one 256 x BLOCK_N tile.
+// FP8 / MXFP8 / MXFP4 GEMM on CTA pairs (tcgen05 cta_group::2): a cluster of two CTAs computes one 256 x BLOCK_N tile.
+// Dense, grouped (tiles never cross a group; 256-row tiles per group) and variable-K forms, as in gemm_fp8.cu.
 // Included by gemm_fp8.cu (uses its GemmParams, GemmMode and epilogue_store_block).
 //
 // Why pairs: with one CTA per tile every tcgen05.mma reads its whole A (128 x 32 B) and B (BLOCK_N x 32 B) slice from
@@ -33,7 +34,7 @@ template <int BLOCK_N, bool MX, bool F4 = false> struct PairCfg {
     static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
     static constexpr int kEpiBytes = kNumEpiWarps * 32 * kStagePitchMax;
     static constexpr int kBarBytes = 1024;
-    static constexpr int kSmemBudget = 227 * 1024 - 1024 - 256;
+    static constexpr int kSmemBudget = 227 * 1024 - 1024 /* alignment slack */ - 9216 /* static shared: group tables */;
     static constexpr int kStages = std::min(8, (kSmemBudget - kEpiBytes - kBarBytes) / kStageBytes);
     static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarBytes + 1024;
     static_assert(kStages >= 3, "not enough shared memory for a 3-stage ring");
@@ -67,17 +68,28 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     uint64_t *tmem_empty_bar = tmem_full_bar + kAccStages;  // used in the leader: epilogue warps of both CTAs
     uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(tmem_empty_bar + kAccStages);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_base_slot + 1);
+    __shared__ int s_tile_start[kMaxGroups + 1];    // running count of 256-row tiles (x column blocks) over the groups
+    __shared__ int s_blk128_start[kMaxGroups + 1];  // running count of 128-row blocks: index of a group's first A scale block
 
     const int warp = threadIdx.x / 32;
     const int lane = threadIdx.x % 32;
     const uint32_t rank = cluster_ctarank();
     const int num_n_blocks = (p.N + BLOCK_N - 1) / BLOCK_N;
-    const int num_m_blocks = (int) ((p.M + kTileM - 1) / kTileM);
     const int num_k_blocks = (p.K + BLOCK_K - 1) / BLOCK_K;
-    const int num_tiles = num_m_blocks * num_n_blocks;
+    const int G = p.G;
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
+        int tiles = 0, blks = 0;
+        s_tile_start[0] = 0;
+        s_blk128_start[0] = 0;
+        for (int g = 0; g < G; ++g) {
+            const int64_t len = (p.offs_write && !p.koffs) ? (p.offs_write[g + 1] - p.offs_write[g]) : p.M;
+            tiles += (int) ((len + kTileM - 1) / kTileM) * num_n_blocks;
+            blks += (int) ((len + BLOCK_M - 1) / BLOCK_M);
+            s_tile_start[g + 1] = tiles;
+            s_blk128_start[g + 1] = blks;
+        }
         *abort_flag = 0;
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full_bar[s], 1);
@@ -104,37 +116,43 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     const uint32_t tmem_sfa = tmem_base + kAccStages * BLOCK_N;
     const uint32_t tmem_sfb = tmem_sfa + 4;
 
-    // tile t -> (m_blk, n_blk): bands of raster_m row blocks, rows fastest inside a band
-    auto locate = [&](int t, int &m_blk, int &n_blk) {
-        const int band_h = max(1, p.raster_m / 2);
-        const int per_band = band_h * num_n_blocks;
-        const int band = t / per_band, first_m = band * band_h;
-        const int rows = min(band_h, num_m_blocks - first_m);
-        const int in_band = t - band * per_band;
-        m_blk = first_m + in_band % rows;
-        n_blk = in_band / rows;
-    };
+    TileWalk walk{s_tile_start, G, num_n_blocks, 0, max(1, p.raster_m / 2)};
     bool ok = true;
-    int m_blk, n_blk;
+    int gi, m_blk, n_blk;
+    auto k_range = [&](int g, int &kb_begin, int &kb_count) {
+        if (p.koffs) {  // offsets count elements; a stage holds 128 (fp8) or 256 (packed fp4) of them
+            constexpr int kElemsPerStage = F4 ? 2 * BLOCK_K : BLOCK_K;
+            kb_begin = (int) (p.koffs[g] / kElemsPerStage);
+            kb_count = (int) ((p.koffs[g + 1] - p.koffs[g]) / kElemsPerStage);
+        } else {
+            kb_begin = 0;
+            kb_count = num_k_blocks;
+        }
+    };
 
     if (warp == 0) {
         // ================================================================ TMA producer (both CTAs)
         if (elect_one()) {
             uint32_t stage = 0, phase = 0;
-            for (int t = pair; ok && t < num_tiles; t += num_pairs) {
-                locate(t, m_blk, n_blk);
-                const int a_row0 = m_blk * kTileM + (int) rank * BLOCK_M;
-                const int b_row0 = n_blk * BLOCK_N + (int) rank * Cfg::kHalfN;
+            for (int t = pair; ok && walk.locate(t, gi, m_blk, n_blk); t += num_pairs) {
+                const int a_row0 = (int) (((p.offs_read && !p.koffs) ? p.offs_read[gi] : 0) + (int64_t) m_blk * kTileM) + (int) rank * BLOCK_M;
+                const int b_row0 = (int) ((p.koffs ? 0 : (int64_t) gi * p.b_group_rows) + (int64_t) n_blk * BLOCK_N) + (int) rank * Cfg::kHalfN;
+                int kb_begin, kb_count;
+                k_range(gi, kb_begin, kb_count);
                 // 512-byte scale blocks as rows of four 128-byte lines: A block of this CTA's rows, all B blocks of the tile
-                // (kSfP blocks per K step; one box fetches the kSfP consecutive blocks of a step)
-                const int64_t sfa_line0 = ((int64_t) (2 * m_blk + (int) rank) * num_k_blocks) * kSfP * 4;
-                const int64_t sfb_line0 = p.sfb_line0 + ((int64_t) n_blk * Cfg::kSfbBlocks * num_k_blocks) * kSfP * 4;
-                for (int kb = 0; kb < num_k_blocks; ++kb) {
+                // (kSfP blocks per K step; one box fetches the kSfP consecutive blocks of a step).  A 256-row tile that
+                // ends a group with an odd number of 128-row blocks reads the next block's scales for rows that are
+                // never stored.
+                const int64_t a_rb = (p.koffs ? 0 : s_blk128_start[gi]) + 2 * m_blk + (int) rank;
+                const int64_t b_rb = ((p.koffs ? 0 : (int64_t) gi * num_n_blocks) + n_blk) * Cfg::kSfbBlocks;
+                const int64_t sfa_line0 = (a_rb * num_k_blocks + kb_begin) * kSfP * 4;
+                const int64_t sfb_line0 = p.sfb_line0 + (b_rb * num_k_blocks + kb_begin) * kSfP * 4;
+                for (int kb = 0; kb < kb_count; ++kb) {
                     if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
                     const uint32_t full_leader = map_to_rank(&full_bar[stage], 0);
                     if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
-                    tma_load_2d_pair(smem_a + stage * Cfg::kABytes, &tmap_a, full_leader, kb * BLOCK_K, a_row0);
-                    tma_load_2d_pair(smem_b + stage * Cfg::kBBytes, &tmap_b, full_leader, kb * BLOCK_K, b_row0);
+                    tma_load_2d_pair(smem_a + stage * Cfg::kABytes, &tmap_a, full_leader, (kb_begin + kb) * BLOCK_K, a_row0);
+                    tma_load_2d_pair(smem_b + stage * Cfg::kBBytes, &tmap_b, full_leader, (kb_begin + kb) * BLOCK_K, b_row0);
                     if constexpr (MX) {
                         uint8_t *sf = smem_sf + stage * Cfg::kSfBytes;
                         tma_load_2d_pair(sf, &tmap_sf, full_leader, 0, (int) (sfa_line0 + 4 * kSfP * kb));
@@ -154,11 +172,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                                    : MX ? idesc_block_scaled(p.a_fmt, p.b_fmt, kTileM, BLOCK_N)
                                         : idesc_f8(p.a_fmt, p.b_fmt, kTileM, BLOCK_N);
             uint32_t stage = 0, phase = 0, acc_stage = 0, acc_phase = 0, sf_buf = 0;
-            for (int t = pair; ok && t < num_tiles; t += num_pairs) {
+            for (int t = pair; ok && walk.locate(t, gi, m_blk, n_blk); t += num_pairs) {
+                int kb_begin, kb_count;
+                k_range(gi, kb_begin, kb_count);
+                if (kb_count == 0) continue;  // empty contraction range: the epilogues write zeros on their own
                 if (!(ok = mbar_wait(&tmem_empty_bar[acc_stage], acc_phase ^ 1, abort_flag))) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc_stage * BLOCK_N;
-                for (int kb = 0; kb < num_k_blocks; ++kb) {
+                for (int kb = 0; kb < kb_count; ++kb) {
                     if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
                     tc_fence_after_sync();
                     const uint32_t sfa_cur = tmem_sfa + sf_buf * Cfg::kSfColsOne;
@@ -199,17 +220,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         const int q = warp & 3;
         uint8_t *stg = smem_epi + (warp - kEpiWarp0) * 32 * kStagePitchMax;
         uint32_t acc_stage = 0, acc_phase = 0;
-        for (int t = pair; ok && t < num_tiles; t += num_pairs) {
-            locate(t, m_blk, n_blk);
-            const int64_t tile_row0 = (int64_t) m_blk * kTileM + (int64_t) rank * BLOCK_M + q * 32;
+        for (int t = pair; ok && walk.locate(t, gi, m_blk, n_blk); t += num_pairs) {
+            const int64_t c_row_base = p.koffs ? (int64_t) gi * p.M : (p.offs_write ? p.offs_write[gi] : 0);
+            const int64_t c_row_end = p.koffs ? c_row_base + p.M : (p.offs_write ? p.offs_write[gi + 1] : p.M);
+            int kb_begin, kb_count;
+            k_range(gi, kb_begin, kb_count);
+            const bool have_acc = kb_count > 0;
+            const int64_t tile_row0 = c_row_base + (int64_t) m_blk * kTileM + (int64_t) rank * BLOCK_M + q * 32;
             const int n0 = n_blk * BLOCK_N;
-            if (!(ok = mbar_wait(&tmem_full_bar[acc_stage], acc_phase, abort_flag))) break;
+            if (have_acc && !(ok = mbar_wait(&tmem_full_bar[acc_stage], acc_phase, abort_flag))) break;
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t) (q * 32) << 16) + acc_stage * BLOCK_N;
             const uint32_t release_addr = map_to_rank(&tmem_empty_bar[acc_stage], 0);
-            epilogue_store_block<BLOCK_N, MODE>(p, taddr, true, tile_row0, p.M, n0, 0, stg, lane,
+            epilogue_store_block<BLOCK_N, MODE>(p, taddr, have_acc, tile_row0, c_row_end, n0, gi, stg, lane,
                                                 [&]() { mbar_arrive_cluster(release_addr); });
-            if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1; }
+            if (have_acc && ++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1; }
         }
     }
 
