@@ -24,19 +24,29 @@ struct TileWalk {
     int G, num_n_blocks;
     int g;
     int kRasterM;
+    int cached_g = -1, cached_m_blocks = 0;  // row blocks of group `cached_g` (saves a division per tile)
     __device__ __forceinline__ bool locate(int t, int &g_out, int &m_blk, int &n_blk) {
         if (t >= tile_start[G]) return false;
         while (t >= tile_start[g + 1]) ++g;
         const int local = t - tile_start[g];
-        const int m_blocks = (tile_start[g + 1] - tile_start[g]) / num_n_blocks;
+        if (g != cached_g) {
+            cached_g = g;
+            cached_m_blocks = (tile_start[g + 1] - tile_start[g]) / num_n_blocks;
+        }
+        const int m_blocks = cached_m_blocks;
+        g_out = g;
+        if (kRasterM >= m_blocks) {  // one band over all row blocks of the group
+            n_blk = local / m_blocks;
+            m_blk = local - n_blk * m_blocks;
+            return true;
+        }
         const int per_band = kRasterM * num_n_blocks;
         const int band = local / per_band;
         const int first_m = band * kRasterM;
         const int band_rows = min(kRasterM, m_blocks - first_m);
         const int in_band = local - band * per_band;
-        g_out = g;
-        m_blk = first_m + in_band % band_rows;
         n_blk = in_band / band_rows;
+        m_blk = first_m + in_band - n_blk * band_rows;
         return true;
     }
 };
