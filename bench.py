@@ -28,7 +28,7 @@ for p in (ROOT, os.path.join(ROOT, "primus-turbo_b200")):
 import torch  # noqa: E402
 
 WORKLOADS = {
-    # name: (M, N, K, seed)  -- shapes of BASELINE.json configs; activations ~N(0,1) with 0.1% x50 outliers, weights ~N(0,0.02)
+    # name: (M, N, K, seed)  -- Llama-3 MLP / FFN shapes of the benchmark configurations; activations ~N(0,1) with 0.1% x50 outliers, weights ~N(0,0.02)
     "mxfp8_linear_fwd_llama3_8b_mlp": (8192, 14336, 4096, 1),
     "mxfp8_linear_fwd_llama3_70b_ffn": (16384, 28672, 8192, 2),
 }
