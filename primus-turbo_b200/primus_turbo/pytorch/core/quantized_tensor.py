@@ -1,9 +1,12 @@
-"""QuantizedTensor: quantized bytes + scale_inv + the metadata needed to check and undo the quantization.
+"""QuantizedTensor: a tensor wrapper subclass that carries quantized bytes + scale_inv + the metadata needed to
+check and undo the quantization.
 
-A light container with the fields and methods the GEMM operators use from the reference's
-QuantizedTensor (primus_turbo/pytorch/core/quantized_tensor.py:148-835): qdata, scale_inv,
-real_dtype (the quantized dtype), orig_dtype, granularity / axis / block_size / scaling_recipe,
-shape (the original, unpadded shape), quantize(), dequantize(), t().
+Same role and surface as the reference's QuantizedTensor (primus_turbo/pytorch/core/quantized_tensor.py:148-835):
+the wrapper reports the original (unpadded) shape and the original dtype, `qdata` / `scale_inv` hold the
+quantized payload, `real_dtype` is the quantized dtype, and the tensor flattens into its inner tensors + metadata
+for FSDP / torch.compile.  View-like operations are answered without dequantizing where the scales allow it
+(detach / alias / clone always; view / reshape when the scaled trailing dimensions are untouched; t / transpose
+for tensorwise scaling, whose single scale survives a transpose).
 """
 from typing import NamedTuple, Optional
 
@@ -18,40 +21,78 @@ def _norm_axis(axis, ndim):
     return axis if axis >= 0 else ndim + axis
 
 
-class QuantizedTensor:
-    def __init__(self, qdata, scale_inv, *, orig_dtype, orig_shape, granularity, axis=None, block_size=None,
-                 scaling_recipe=None):
-        self.qdata = qdata
-        self.scale_inv = scale_inv
-        self.orig_dtype = orig_dtype
-        self._shape = torch.Size(orig_shape)
-        self.granularity = granularity
-        self.axis = _norm_axis(axis, len(orig_shape))
-        self.block_size = block_size
-        self.scaling_recipe = scaling_recipe
+class QuantizedTensor(torch.Tensor):
+    @staticmethod
+    def __new__(cls, qdata, scale_inv, *, orig_dtype, orig_shape=None, granularity, axis=None, block_size=None,
+                scaling_recipe=None, group_lens=None, group_offs=None, requires_grad=False, shape=None,
+                dest_dtype=None, quantized_axis=None):
+        # `shape`, `dest_dtype`, `quantized_axis` are the reference's keyword names for orig_shape, the quantized
+        # dtype (always qdata.dtype here) and axis
+        orig_shape = torch.Size(orig_shape if orig_shape is not None else shape)
+        if axis is None:
+            axis = quantized_axis
+        assert dest_dtype is None or dest_dtype == qdata.dtype, "dest_dtype must be the dtype of the quantized data"
+        self = torch.Tensor._make_wrapper_subclass(cls, orig_shape, dtype=orig_dtype, layout=qdata.layout,
+                                                   device=qdata.device, requires_grad=requires_grad)
+        self._qdata, self._scale_inv = qdata, scale_inv
+        self._granularity = granularity
+        self._axis = _norm_axis(axis, len(orig_shape))
+        self._block_size = block_size
+        self._scaling_recipe = scaling_recipe
+        self._group_lens, self._group_offs = group_lens, group_offs
+        return self
 
-    # ---- metadata
+    def __init__(self, *args, **kwargs):
+        pass
+
+    # ---- payload and metadata
+    @property
+    def qdata(self):
+        return self._qdata
+
+    @property
+    def scale_inv(self):
+        return self._scale_inv
+
     @property
     def real_dtype(self):
-        return self.qdata.dtype
+        return self._qdata.dtype
 
     @property
-    def shape(self):
-        return self._shape
+    def orig_dtype(self):
+        return self.dtype
 
     @property
-    def dtype(self):
-        return self.orig_dtype
+    def granularity(self):
+        return self._granularity
 
     @property
-    def device(self):
-        return self.qdata.device
+    def axis(self):
+        return self._axis
 
-    def dim(self):
-        return len(self._shape)
+    quantized_axis = axis
 
-    def size(self, i=None):
-        return self._shape if i is None else self._shape[i]
+    @property
+    def block_size(self):
+        return self._block_size
+
+    @property
+    def scaling_recipe(self):
+        return self._scaling_recipe
+
+    @property
+    def group_lens(self):
+        return self._group_lens
+
+    @property
+    def group_offs(self):
+        return self._group_offs
+
+    def _like(self, qdata, scale_inv, shape, axis="same"):
+        return QuantizedTensor(qdata, scale_inv, orig_dtype=self.dtype, orig_shape=shape, granularity=self._granularity,
+                               axis=self._axis if axis == "same" else axis, block_size=self._block_size,
+                               scaling_recipe=self._scaling_recipe, group_lens=self._group_lens,
+                               group_offs=self._group_offs, requires_grad=False)
 
     # ---- construction
     @classmethod
@@ -61,44 +102,100 @@ class QuantizedTensor:
         if granularity == ScalingGranularity.MX_BLOCKWISE and block_size is None:
             block_size = 32
         fn = quantize_fp4 if is_fp4_dtype(dtype) else quantize_fp8
-        q, s = fn(x, dtype, granularity, block_size=block_size, axis=axis, scaling_recipe=scaling_recipe)
+        with torch.no_grad():
+            q, s = fn(x, dtype, granularity, block_size=block_size, axis=axis, scaling_recipe=scaling_recipe)
         return cls(q, s, orig_dtype=x.dtype, orig_shape=x.shape, granularity=granularity, axis=axis,
                    block_size=block_size, scaling_recipe=scaling_recipe)
 
     def dequantize(self, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         from ..ops.quantization import dequantize_fp4, dequantize_fp8
-        dtype = dtype or self.orig_dtype
-        fn = dequantize_fp4 if is_fp4_dtype(self.qdata.dtype) else dequantize_fp8
-        y = fn(self.qdata, dtype, self.granularity, block_size=self.block_size, axis=self.axis,
-               scale_inv=self.scale_inv, scaling_recipe=self.scaling_recipe)
-        if self.granularity == ScalingGranularity.MX_BLOCKWISE:  # drop the 128-padding
-            y = y[..., : self._shape[-2], : self._shape[-1]]
+        dtype = dtype or self.dtype
+        fn = dequantize_fp4 if is_fp4_dtype(self._qdata.dtype) else dequantize_fp8
+        with torch.no_grad():
+            y = fn(self._qdata, dtype, self._granularity, block_size=self._block_size, axis=self._axis,
+                   scale_inv=self._scale_inv, scaling_recipe=self._scaling_recipe)
+        if self._granularity == ScalingGranularity.MX_BLOCKWISE:  # drop the 128-padding
+            y = y[..., : self.shape[-2], : self.shape[-1]]
         return y
 
-    def t(self) -> "QuantizedTensor":
-        """Transposed view; only tensorwise scaling survives a transpose unchanged
-        (quantized_tensor.py:762-764 of the reference)."""
-        assert self.granularity == ScalingGranularity.TENSORWISE and self.qdata.dim() == 2, \
-            "t() is defined for 2-D tensorwise tensors"
-        return QuantizedTensor(self.qdata.t(), self.scale_inv, orig_dtype=self.orig_dtype,
-                               orig_shape=self._shape[::-1], granularity=self.granularity)
-
     def contiguous(self) -> "QuantizedTensor":
-        if self.qdata.is_contiguous():
+        """Materialises a lazily transposed payload (byte transpose on the device)."""
+        q = self._qdata
+        if q.is_contiguous():
             return self
         from ..kernels.quantization.quantization_impl import transpose_2d
-        q = self.qdata
-        if q.dim() == 2 and q.t().is_contiguous():
-            q = transpose_2d(q.t())  # byte transpose on the device
-        else:
-            q = q.contiguous()
-        return QuantizedTensor(q, self.scale_inv, orig_dtype=self.orig_dtype, orig_shape=self._shape,
-                               granularity=self.granularity, axis=self.axis, block_size=self.block_size,
-                               scaling_recipe=self.scaling_recipe)
+        q = transpose_2d(q.t()) if (q.dim() == 2 and q.t().is_contiguous()) else q.contiguous()
+        return self._like(q, self._scale_inv, self.shape)
 
-    def __repr__(self):
-        return (f"QuantizedTensor(shape={tuple(self._shape)}, real_dtype={self.real_dtype}, orig_dtype={self.orig_dtype}, "
-                f"granularity={self.granularity.name}, axis={self.axis}, block_size={self.block_size})")
+    # ---- flatten / unflatten (FSDP, torch.compile)
+    def __tensor_flatten__(self):
+        inner = ["_qdata", "_scale_inv"]
+        if self._group_lens is not None:
+            inner.append("_group_lens")
+        if self._group_offs is not None:
+            inner.append("_group_offs")
+        meta = dict(granularity=self._granularity, axis=self._axis, block_size=self._block_size,
+                    scaling_recipe=self._scaling_recipe, orig_dtype=self.dtype)
+        return inner, meta
+
+    @staticmethod
+    def __tensor_unflatten__(inner_tensors, meta, outer_size, outer_stride):
+        return QuantizedTensor(inner_tensors["_qdata"], inner_tensors["_scale_inv"], orig_dtype=meta["orig_dtype"],
+                               orig_shape=outer_size, granularity=meta["granularity"], axis=meta["axis"],
+                               block_size=meta["block_size"], scaling_recipe=meta["scaling_recipe"],
+                               group_lens=inner_tensors.get("_group_lens"), group_offs=inner_tensors.get("_group_offs"))
+
+    # ---- view-like operations that keep the quantization valid
+    def _reshaped(self, shape, op):
+        """view / reshape to `shape` when the scales stay attached to the same elements: tensorwise always; otherwise
+        the trailing dimensions the scales refer to (the last one for rowwise along the last axis, the last two for
+        every other case) must be unchanged, and the leading ones are regrouped alike on data and scales."""
+        shape = list(shape[0]) if len(shape) == 1 and isinstance(shape[0], (tuple, list, torch.Size)) else list(shape)
+        numel = self.numel()
+        if -1 in shape:
+            known = 1
+            for d in shape:
+                known *= d if d != -1 else 1
+            shape[shape.index(-1)] = numel // max(known, 1)
+        new_shape = torch.Size(shape)
+        q, s = self._qdata, self._scale_inv
+        if self._granularity == ScalingGranularity.TENSORWISE:
+            return self._like(op(q, new_shape), s, new_shape)
+        keep = 1 if (self._granularity == ScalingGranularity.ROWWISE and self._axis == self.dim() - 1) else 2
+        if len(new_shape) < keep or tuple(new_shape[-keep:]) != tuple(self.shape[-keep:]):
+            raise NotImplementedError(f"QuantizedTensor: cannot view {tuple(self.shape)} as {tuple(new_shape)} without "
+                                      f"dequantizing ({self._granularity.name} scales are tied to the trailing dimensions)")
+        lead = tuple(new_shape[:-keep])
+        axis = None if self._axis is None else len(new_shape) - (self.dim() - self._axis)
+        return self._like(op(q, lead + tuple(q.shape[-keep:])), op(s, lead + tuple(s.shape[-keep:])), new_shape, axis=axis)
+
+    @classmethod
+    def __torch_dispatch__(cls, func, types, args=(), kwargs=None):
+        aten = torch.ops.aten
+        t = args[0]
+        if func in (aten.detach.default, aten.alias.default):
+            return t._like(t._qdata.detach(), t._scale_inv.detach(), t.shape)
+        if func is aten.clone.default:
+            return t._like(t._qdata.clone(), t._scale_inv.clone(), t.shape)
+        if func in (aten.view.default, aten._unsafe_view.default):
+            return t._reshaped((args[1],), torch.Tensor.view)
+        if func is aten.reshape.default:
+            return t._reshaped((args[1],), torch.Tensor.reshape)
+        if func in (aten.t.default, aten.transpose.int):
+            d0, d1 = (0, 1) if func is aten.t.default else (args[1] % t.dim(), args[2] % t.dim())
+            if t._granularity != ScalingGranularity.TENSORWISE or t.dim() != 2:
+                raise NotImplementedError("QuantizedTensor: only 2-D tensorwise tensors transpose without requantizing "
+                                          "(quantized_tensor.py:762-764 of the reference)")
+            if d0 == d1:
+                return t
+            return t._like(t._qdata.t(), t._scale_inv, t.shape[::-1])   # lazy: .contiguous() moves the bytes
+        raise NotImplementedError(f"QuantizedTensor: {func} needs the values; call dequantize() first")
+
+    __torch_function__ = torch._C._disabled_torch_function_impl
+
+    def __repr__(self, *, tensor_contents=None):
+        return (f"QuantizedTensor(shape={tuple(self.shape)}, real_dtype={self.real_dtype}, orig_dtype={self.dtype}, "
+                f"granularity={self._granularity.name}, axis={self._axis}, block_size={self._block_size})")
 
 
 class QuantizedTensorPair(NamedTuple):
