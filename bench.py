@@ -230,13 +230,13 @@ def main():
         quant = lambda: (quantize_mxfp8_impl(a, f8, None, 32, True, plain, plain)[:2],
                          quantize_mxfp8_impl(w, f8, None, 32, True, two_d, two_d)[:2])
         gemm = lambda qa, qw: gemm_fp8_impl(qa[0], qa[1], False, qw[0], qw[1], True, torch.bfloat16, False, G.MX_BLOCKWISE)
-        launches, kernel_name = 5, "gemm_fp8_kernel<MX>"  # 2 dual quantize, 2 scale re-tile, 1 GEMM
+        launches, kernel_name = 4, "gemm_fp8_pair_kernel<MX>"  # 2 dual quantize, 1 scale re-tile, 1 GEMM
     elif args.granularity == "mxfp4":
         fp4 = torch.float4_e2m1fn_x2
         quant = lambda: (qi.quantize_mxfp4_impl(a, fp4, None, 32, True, plain, plain)[:2],
                          qi.quantize_mxfp4_impl(w, fp4, None, 32, True, two_d, two_d)[:2])
         gemm = lambda qa, qw: gemm_fp4_impl(qa[0], qa[1], False, qw[0], qw[1], True, torch.bfloat16, False, G.MX_BLOCKWISE)
-        launches, kernel_name = 5, "gemm_fp8_kernel<MXF4>"
+        launches, kernel_name = 4, "gemm_fp8_pair_kernel<MXF4>"
     elif args.granularity == "blockwise":
         quant = lambda: (qi.quant_fp8_blockwise_impl(a, f8, 1), qi.quant_fp8_blockwise_for_weight_impl(w, f8))
         gemm = lambda qa, qw: gemm_fp8_impl(qa[0], qa[1], False, qw[0], qw[1], True, torch.bfloat16, False, G.BLOCKWISE)

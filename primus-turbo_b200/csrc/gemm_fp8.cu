@@ -106,9 +106,14 @@ struct RetileArgs {
     int64_t num_row_blocks;  // upper bound
 };
 
-__global__ void __launch_bounds__(128) sf_retile_kernel(RetileArgs a) {
+// One launch re-tiles both operands: blocks [0, blocks_a) work on the A side, the rest on the B side.
+__global__ void __launch_bounds__(128) sf_retile_kernel(RetileArgs args_a, RetileArgs args_b, int blocks_a) {
     __shared__ uint32_t s_words[128][33];
     __shared__ int s_start[kMaxGroups + 1];
+    const bool side_b = (int) blockIdx.x >= blocks_a;
+    const RetileArgs &a = side_b ? args_b : args_a;
+    const int block_x = side_b ? (int) blockIdx.x - blocks_a : (int) blockIdx.x;
+    const int grid_x = side_b ? (int) gridDim.x - blocks_a : blocks_a;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (!a.is_b) {
         if (tid == 0) {
@@ -125,7 +130,7 @@ __global__ void __launch_bounds__(128) sf_retile_kernel(RetileArgs a) {
     const int kb0 = blockIdx.y * 32;
     const int nkb = min(32, a.num_kb - kb0);
     int g = 0;
-    for (int64_t rb = blockIdx.x; rb < a.num_row_blocks; rb += gridDim.x) {
+    for (int64_t rb = block_x; rb < a.num_row_blocks; rb += grid_x) {
         int64_t row_start;
         int rows_in_block = 128;
         if (a.is_b) {
@@ -159,10 +164,12 @@ __global__ void __launch_bounds__(128) sf_retile_kernel(RetileArgs a) {
 
 // Write-out of one epilogue warp's 32 x BLOCK_N block of a tile: TMEM -> registers -> scales -> XOR-swizzled staging
 // rows in shared memory -> coalesced row-segment stores, masked at the end of the group / matrix.  `release` hands the
-// accumulator buffer back to the MMA issuer as soon as its last chunk is in registers.
+// accumulator buffer back to the MMA issuer as soon as the warp's last chunk is in registers.  The warp handles the
+// 32-column chunks [c_begin, c_end) of the tile (all of them, or a share when several warps split a lane quarter).
 template <int BLOCK_N, int MODE, typename Release>
 __device__ __forceinline__ void epilogue_store_block(const GemmParams &p, uint32_t taddr, bool have_acc, int64_t tile_row0,
-                                                     int64_t c_row_end, int n0, int gi, uint8_t *stg, int lane, Release release) {
+                                                     int64_t c_row_end, int n0, int gi, uint8_t *stg, int lane, int c_begin,
+                                                     int c_end, Release release) {
     const int esize = p.c_dtype == PT_F32 ? 4 : 2;
     const int pitch = 32 * esize;  // unpadded rows; 16-byte chunks are XOR-swizzled by row so that neither the
                                    // row-per-lane writes nor the row-segment reads conflict on banks
@@ -171,10 +178,9 @@ __device__ __forceinline__ void epilogue_store_block(const GemmParams &p, uint32
     float row_scale = 1.f;
     if (MODE == GEMM_TENSOR) row_scale = __ldg(p.sa) * __ldg(p.sb);
     if (MODE == GEMM_ROW) row_scale = (tile_row0 + lane < c_row_end) ? __ldg(p.sa + tile_row0 + lane) : 0.f;
-    constexpr int kChunks = (BLOCK_N + 31) / 32;  // a last partial chunk reads past the tile; masked below
-    const int n_end = min(p.N, n0 + BLOCK_N);
+    const int n_end = min(p.N, n0 + BLOCK_N);  // a last partial chunk reads past the tile; masked below
 #pragma unroll 1
-    for (int c = 0; c < kChunks; ++c) {
+    for (int c = c_begin; c < c_end; ++c) {
         uint32_t r[32];
         if (have_acc) {
             tmem_ld32(taddr + c * 32, r);
@@ -183,7 +189,7 @@ __device__ __forceinline__ void epilogue_store_block(const GemmParams &p, uint32
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = 0u;
         }
-        if (have_acc && c == kChunks - 1) {
+        if (have_acc && c == c_end - 1) {
             // whole accumulator is in registers / staged: hand the TMEM buffer back to the MMA warp
             tc_fence_before_sync();
             __syncwarp();
@@ -441,7 +447,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             if (have_acc && !(ok = mbar_wait(&tmem_full_bar[acc_stage], acc_phase, abort_flag))) break;
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t) (q * 32) << 16) + acc_stage * BLOCK_N;
-            epilogue_store_block<BLOCK_N, MODE>(p, taddr, have_acc, tile_row0, c_row_end, n0, gi, stg, lane,
+            epilogue_store_block<BLOCK_N, MODE>(p, taddr, have_acc, tile_row0, c_row_end, n0, gi, stg, lane, 0, (BLOCK_N + 31) / 32,
                                                 [&]() { mbar_arrive(&tmem_empty_bar[acc_stage]); });
             if (have_acc && ++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1; }
         }
@@ -501,11 +507,10 @@ static int prepare_mx_scales(GemmParams &p, const MxScales &mx, int64_t a_rows, 
     rb.block_n = block_n; rb.sfb_blocks = sfb_blocks; rb.num_n_blocks = (int) ceil_div(p.N, block_n);
     rb.b_group_rows = p.b_group_rows; rb.G = sf_groups; rb.num_row_blocks = (int64_t) sf_groups * rb.num_n_blocks * sfb_blocks;
     const int max_blocks = sm_count() * 8;
-    dim3 ga((unsigned) std::min<int64_t>(ra.num_row_blocks, max_blocks), (unsigned) ceil_div(num_kb, 32));
-    dim3 gb((unsigned) std::min<int64_t>(rb.num_row_blocks, max_blocks), (unsigned) ceil_div(num_kb, 32));
-    sf_retile_kernel<<<ga, 128, 0, st>>>(ra);
-    PT_LAUNCH_OK();
-    sf_retile_kernel<<<gb, 128, 0, st>>>(rb);
+    const int blocks_a = (int) std::min<int64_t>(ra.num_row_blocks, max_blocks);
+    const int blocks_b = (int) std::min<int64_t>(rb.num_row_blocks, max_blocks);
+    dim3 grid((unsigned) (blocks_a + blocks_b), (unsigned) ceil_div(num_kb, 32));
+    sf_retile_kernel<<<grid, 128, 0, st>>>(ra, rb, blocks_a);
     PT_LAUNCH_OK();
     p.sfa_tiled = ra.dst;
     p.sfb_tiled = rb.dst;
@@ -564,7 +569,7 @@ static int launch_gemm_pair(const void *a, int64_t a_rows, const void *b, int64_
     if (max_clusters == 0) {
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(2 * (unsigned) sm_count());
-        cfg.blockDim = dim3(kGemmThreads);
+        cfg.blockDim = dim3(Cfg::kThreads);
         cfg.dynamicSmemBytes = Cfg::kSmemBytes;
         cudaLaunchAttribute attr{};
         attr.id = cudaLaunchAttributeClusterDimension;
@@ -579,7 +584,7 @@ static int launch_gemm_pair(const void *a, int64_t a_rows, const void *b, int64_
     }
     const int pairs = (int) std::min<int64_t>(tiles, max_clusters);
     if (pairs <= 0) return PT_OK;
-    kern<<<2 * pairs, kGemmThreads, Cfg::kSmemBytes, st>>>(ta, tb, tsf, p);
+    kern<<<2 * pairs, Cfg::kThreads, Cfg::kSmemBytes, st>>>(ta, tb, tsf, p);
     PT_LAUNCH_OK();
     return PT_OK;
 }

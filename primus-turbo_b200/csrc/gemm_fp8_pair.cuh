@@ -11,8 +11,10 @@
 //                on the leader's (rank 0) full barrier
 //   leader       warp 1: issues the cta_group::2 MMAs; tcgen05.commit multicasts the arrivals to both CTAs
 //                (stage free -> both producers, accumulator full -> both epilogues)
-//   both CTAs    warps 2-5: epilogue of the CTA's own 128 accumulator rows; hand the TMEM buffer back by arriving on
-//                the leader's barrier
+//   both CTAs    warps 2-5 (FP4: 2-9): epilogue of the CTA's own 128 accumulator rows.  FP4 uses two warps per TMEM
+//                lane quarter, each taking half of the columns: at FP4 rates and short K the write-out is as long as
+//                the main loop (grouped FP4 forward +5 %), while for FP8 the extra staging memory costs a pipeline
+//                stage.  They hand the TMEM buffer back by arriving on the leader's barrier
 // No TMA multicast is used.  Every wait is bounded exactly as in the single-CTA kernel.
 #pragma once
 
@@ -20,6 +22,8 @@ namespace ptb {
 
 // F4: packed e2m1 operands, 256 elements per 128-byte stage row = two 128-element scale blocks per stage (kSfPerStage)
 template <int BLOCK_N, bool MX, bool F4 = false> struct PairCfg {
+    static constexpr int kEpiWarps = F4 ? 8 : 4;
+    static constexpr int kThreads = 32 * (2 + kEpiWarps);
     static constexpr int kHalfN = BLOCK_N / 2;
     static constexpr int kSfbBlocks = (BLOCK_N + 127) / 128;
     static constexpr int kSfPerStage = F4 ? 2 : 1;
@@ -32,7 +36,7 @@ template <int BLOCK_N, bool MX, bool F4 = false> struct PairCfg {
     static constexpr int kBBytes = kHalfN * BLOCK_K;
     static constexpr int kSfBytes = MX ? 512 * (1 + kSfbBlocks) * kSfPerStage : 0;  // own A blocks + every B block of the tile
     static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
-    static constexpr int kEpiBytes = kNumEpiWarps * 32 * kStagePitchMax;
+    static constexpr int kEpiBytes = kEpiWarps * 32 * kStagePitchMax;
     static constexpr int kBarBytes = 1024;
     static constexpr int kSmemBudget = 227 * 1024 - 1024 /* alignment slack */ - 9216 /* static shared: group tables */;
     static constexpr int kStages = std::min(8, (kSmemBudget - kEpiBytes - kBarBytes) / kStageBytes);
@@ -44,7 +48,7 @@ template <int BLOCK_N, bool MX, bool F4 = false> struct PairCfg {
 };
 
 template <int BLOCK_N, int MODE>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((PairCfg<BLOCK_N, mode_is_mx(MODE), MODE == GEMM_MXF4>::kThreads), 1)
     gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_sf, GemmParams p) {
     constexpr bool MX = mode_is_mx(MODE);
@@ -97,7 +101,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         }
         for (int s = 0; s < kAccStages; ++s) {
             mbar_init(&tmem_full_bar[s], 1);
-            mbar_init(&tmem_empty_bar[s], 2 * kNumEpiWarps);
+            mbar_init(&tmem_empty_bar[s], 2 * Cfg::kEpiWarps);
         }
         fence_barrier_init();
         prefetch_tmap(&tmap_a);
@@ -217,7 +221,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         }
     } else {
         // ================================================================ epilogue (both CTAs, own 128 rows)
-        const int q = warp & 3;
+        const int q = warp & 3;                      // TMEM lane quarter this warp may read
+        const int half = (warp - kEpiWarp0) >> 2;    // with eight warps: which share of the tile's 32-column chunks
+        constexpr int kChunks = (BLOCK_N + 31) / 32;
+        const int c_begin = (Cfg::kEpiWarps == 8 && half) ? kChunks / 2 : 0;
+        const int c_end = (Cfg::kEpiWarps == 8 && !half) ? kChunks / 2 : kChunks;
         uint8_t *stg = smem_epi + (warp - kEpiWarp0) * 32 * kStagePitchMax;
         uint32_t acc_stage = 0, acc_phase = 0;
         for (int t = pair; ok && walk.locate(t, gi, m_blk, n_blk); t += num_pairs) {
@@ -232,7 +240,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t) (q * 32) << 16) + acc_stage * BLOCK_N;
             const uint32_t release_addr = map_to_rank(&tmem_empty_bar[acc_stage], 0);
-            epilogue_store_block<BLOCK_N, MODE>(p, taddr, have_acc, tile_row0, c_row_end, n0, gi, stg, lane,
+            epilogue_store_block<BLOCK_N, MODE>(p, taddr, have_acc, tile_row0, c_row_end, n0, gi, stg, lane, c_begin, c_end,
                                                 [&]() { mbar_arrive_cluster(release_addr); });
             if (have_acc && ++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1; }
         }
