@@ -165,6 +165,12 @@ int pt_dequantize_mx(const void *q, int fmt, const uint8_t *s, int64_t rows, int
 /* y [N, M] = x [M, N]^T for 1-, 2- or 4-byte elements (bindings_pytorch.cpp:44, csrc/kernels/transpose/transpose_2d.cu). */
 int pt_transpose_2d(const void *x, int64_t M, int64_t N, int elem_bytes, void *y, void *stream);
 
+/* Zero-fills rows [*first_row, rows) of a row-major buffer with `row_bytes` bytes per row (a multiple of 4, base 4-byte
+ * aligned); `first_row` is a device pointer, so no host synchronisation is needed.  The grouped GEMMs leave rows past the
+ * last group untouched; the reference returns zeros there (grouped_gemm_fp8_impl.py: output tail), so the caller
+ * clears that tail — and only it — with this call instead of a memset of the whole output. */
+int pt_zero_rows_from(void *buf, int64_t rows, int64_t row_bytes, const int64_t *first_row, void *stream);
+
 /* ------------------------------------------------------------------ FP8 / MXFP8 GEMM (tcgen05, TMEM accumulators) */
 
 /* C [M, N] (row-major, c_dtype) = A [M, K] . B [N, K]^T, both operands K-major FP8 bytes ("NT").  Other

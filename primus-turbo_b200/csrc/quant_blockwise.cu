@@ -504,6 +504,14 @@ __global__ void __launch_bounds__(1024) group_offs_kernel(const int64_t *__restr
     }
 }
 
+// zero-fill of rows [*first_row, rows), 4-byte words, grid-stride; nothing to do in the usual case *first_row == rows
+__global__ void __launch_bounds__(256) zero_rows_from_kernel(uint32_t *__restrict__ buf, int64_t rows, int64_t row_words,
+                                                            const int64_t *__restrict__ first_row) {
+    const int64_t begin = min(max(*first_row, (int64_t) 0), rows) * row_words, end = rows * row_words;
+    const int64_t stride = (int64_t) gridDim.x * blockDim.x;
+    for (int64_t i = begin + (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < end; i += stride) buf[i] = 0u;
+}
+
 // tiled transpose of 1/2/4-byte elements
 template <typename E>
 __global__ void __launch_bounds__(256) transpose_kernel(const E *__restrict__ x, int64_t M, int64_t N, E *__restrict__ y) {
@@ -625,6 +633,16 @@ int pt_compute_padded_group_offs(const int64_t *lens, int G, int64_t align, int6
                                  void *stream) {
     PT_REQUIRE(lens && poffs && G >= 0 && G <= 4096 && align >= 1, "padded group offsets: bad arguments");
     group_offs_kernel<<<1, 1024, 0, (cudaStream_t) stream>>>(lens, G, align, plens, poffs);
+    PT_LAUNCH_OK();
+    return PT_OK;
+}
+
+int pt_zero_rows_from(void *buf, int64_t rows, int64_t row_bytes, const int64_t *first_row, void *stream) {
+    PT_REQUIRE(rows >= 0 && row_bytes >= 0 && row_bytes % 4 == 0, "zero rows: bad extents");
+    if (rows == 0 || row_bytes == 0) return PT_OK;
+    PT_REQUIRE(buf && first_row && aligned(buf, 4), "zero rows: null or unaligned pointer");
+    // the tail is normally empty or a few rows: a small fixed grid is enough
+    zero_rows_from_kernel<<<sm_count() * 4, 256, 0, (cudaStream_t) stream>>>((uint32_t *) buf, rows, row_bytes / 4, first_row);
     PT_LAUNCH_OK();
     return PT_OK;
 }

@@ -281,6 +281,7 @@ constexpr int kQTileBytes = kTileM * kTileN * 2;
 constexpr int kQConsumerWarps = 8;
 constexpr int kQThreads = 32 * (1 + kQConsumerWarps);
 constexpr int kQSmemBytes = kQStages * kQTileBytes + 1024 + 1024;
+constexpr int kQMaxGroups = 256;  // grouped form: offset tables of up to this many groups are held in shared memory
 
 // 32 scaled values -> 32 fp8 codes (8 words) or 32 fp4 codes (4 words).  The reference's soft clamp to +-qmax*scale
 // is subsumed by the saturating convert (identical bytes for every non-NaN input; a NaN converts to the NaN code).
@@ -317,7 +318,10 @@ template <typename T> struct SwizzledTile {
     }
 };
 
-template <typename T, int FMT, bool ROW, bool COL, bool ROW2D, bool COL2D, bool ROWRHT, bool COLRHT>
+// GROUPED: the tile grid runs over the padded row space of the col-wise copy (see mx_quant_kernel): a tile maps to
+// rows [in_row0, in_row0 + n_valid) of one group, later rows of the fetched box belong to the next group and are
+// treated as zeros; the row-wise copy goes to the group's own row offset, real rows only.
+template <typename T, int FMT, bool ROW, bool COL, bool ROW2D, bool COL2D, bool ROWRHT, bool COLRHT, bool GROUPED = false>
 __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
     mx_quant_tma_kernel(const __grid_constant__ CUtensorMap tmap, MxArgs a, int tiles_n, int tiles_m, int64_t total_tiles, int *status) {
     using namespace sm100;
@@ -344,6 +348,34 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
     if (threadIdx.x < 24) (&s_amax2d[0][0][0])[threadIdx.x] = 0u;
     __syncthreads();
     bool ok = true;
+    // grouped: tile row block tm -> first input row, number of rows of the group in the tile, first row of the
+    // row-wise copy; false for tiles past the padded end
+    // (the three offset tables are copied to shared memory first: a search through global memory would cost each tile
+    // several dependent round trips)
+    __shared__ int s_gtab[GROUPED ? 3 * (kQMaxGroups + 1) : 1];
+    if constexpr (GROUPED) {
+        for (int i = threadIdx.x; i <= a.num_groups; i += blockDim.x) {
+            s_gtab[i] = (int) a.poffs_col[i];
+            s_gtab[(kQMaxGroups + 1) + i] = (int) a.group_offs[i];
+            s_gtab[2 * (kQMaxGroups + 1) + i] = (int) a.poffs_row[i];
+        }
+        __syncthreads();
+    }
+    auto locate_group = [&](int tm, int64_t &in_row0, int &n_valid, int64_t &row_out0) -> bool {
+        const int *pcol = s_gtab, *goffs = s_gtab + (kQMaxGroups + 1), *prow = s_gtab + 2 * (kQMaxGroups + 1);
+        const int m0 = tm * kTileM;
+        if (m0 >= pcol[a.num_groups]) return false;
+        int lo = 0, hi = a.num_groups - 1;  // last group whose padded start is <= m0 (empty groups are skipped)
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (pcol[mid] <= m0) lo = mid; else hi = mid - 1;
+        }
+        const int into = m0 - pcol[lo];
+        in_row0 = goffs[lo] + into;
+        n_valid = max(0, min(kTileM, min(goffs[lo + 1], (int) a.M) - (int) in_row0));
+        row_out0 = prow[lo] + into;
+        return true;
+    };
 
     if (warp == 0) {
         if (lane == 0) {
@@ -353,9 +385,13 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
             for (uint32_t t = blockIdx.x; t < (uint32_t) total_tiles; t += gridDim.x) {
                 const uint32_t g = t / per_g, rem = t - g * per_g;
                 const int tm = (int) (rem / (uint32_t) tiles_n), tn = (int) (rem - (uint32_t) tm * tiles_n);
+                int64_t in_row0 = (int64_t) tm * kTileM, row_out0 = 0;
+                int n_valid = kTileM;
+                if constexpr (GROUPED)
+                    if (!locate_group(tm, in_row0, n_valid, row_out0)) continue;
                 if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
                 mbar_arrive_expect_tx(&full_bar[stage], kQTileBytes);
-                sm100::tma_load_3d(smem + stage * kQTileBytes, &tmap, &full_bar[stage], tn * kTileN, tm * kTileM, (int) g);
+                sm100::tma_load_3d(smem + stage * kQTileBytes, &tmap, &full_bar[stage], tn * kTileN, (int) in_row0, (int) g);
                 if (++stage == kQStages) { stage = 0; phase ^= 1; }
             }
         }
@@ -368,11 +404,16 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
         const int c_half = lane & 1, c_pair = ((cw & 1) << 4) | (lane >> 1), c_band = cw >> 1;
         uint32_t stage = 0, phase = 0, tile_count = 0;
         const uint32_t per_g = (uint32_t) tiles_n * (uint32_t) tiles_m;
-        for (uint32_t t = blockIdx.x; t < (uint32_t) total_tiles; t += gridDim.x, ++tile_count) {
+        for (uint32_t t = blockIdx.x; t < (uint32_t) total_tiles; t += gridDim.x) {
             const uint32_t gq = t / per_g, rem = t - gq * per_g;
             const int tm = (int) (rem / (uint32_t) tiles_n), tn = (int) (rem - (uint32_t) tm * tiles_n);
             const int64_t g = gq;
             const int64_t m0 = (int64_t) tm * kTileM, n0 = (int64_t) tn * kTileN;
+            int64_t in_row0 = m0, row_out0 = m0;
+            int n_valid = kTileM;
+            if constexpr (GROUPED)
+                if (!locate_group(tm, in_row0, n_valid, row_out0)) continue;
+            ++tile_count;
             if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
             const SwizzledTile<T> tile{smem + stage * kQTileBytes};
             unsigned(*amax2d)[2] = s_amax2d[tile_count % 3];
@@ -415,12 +456,13 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
             }
 
             if constexpr (ROW) {
-                const int64_t gm = m0 + r_row, gn = n0 + 32 * r_blk;
+                // row of the row-wise copy: the input row, or the group's own offset in the grouped form
+                const int64_t gm = GROUPED ? row_out0 + r_row : m0 + r_row, gn = n0 + 32 * r_blk;
                 const float m = ROW2D ? __uint_as_float(amax2d[r_row >> 5][r_blk]) : r_amax;
-                const MxScale sc = mx_scale<FMT>(m, false);
+                const MxScale sc = mx_scale<FMT>(m, GROUPED);
                 uint32_t w[8];
                 mx_encode32<FMT>(rv, sc, w);
-                if (gm < a.M && gn < a.N_pad) {
+                if ((GROUPED ? r_row < n_valid : gm < a.M) && gn < a.N_pad) {
                     uint8_t *qr = a.q_row + g * a.qrow_gstride;
                     if constexpr (kFp4) {
                         *reinterpret_cast<uint4 *>(qr + (gm * a.N_pad + gn) / 2) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -439,7 +481,9 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
                 uint32_t pmc = 0u;  // packed |max| of (column 2 c_pair, column 2 c_pair + 1)
 #pragma unroll
                 for (int r = 0; r < 16; ++r) {
-                    const uint32_t w = tile.pair(c_band * 32 + c_half * 16 + r, c_pair);
+                    const int row = c_band * 32 + c_half * 16 + r;
+                    // grouped: rows past the group's end hold the next group's data and count as zeros
+                    const uint32_t w = (!GROUPED || row < n_valid) ? tile.pair(row, c_pair) : 0u;
                     c0[r] = Src<T>::to_f32((uint16_t) (w & 0xFFFF));
                     c1[r] = Src<T>::to_f32((uint16_t) (w >> 16));
                     pmc = absmax2<T>(pmc, w);
@@ -459,7 +503,7 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
                     m0c = fmaxf(m0c, __shfl_xor_sync(0xffffffffu, m0c, 1));
                     m1c = fmaxf(m1c, __shfl_xor_sync(0xffffffffu, m1c, 1));
                 }
-                const MxScale s0 = mx_scale<FMT>(m0c, false), s1 = mx_scale<FMT>(m1c, false);
+                const MxScale s0 = mx_scale<FMT>(m0c, GROUPED), s1 = mx_scale<FMT>(m1c, GROUPED);
                 const int64_t gc = n0 + 2 * c_pair;
                 const int64_t gm = m0 + c_band * 32 + c_half * 16;
                 if (gc < a.N) {  // N is a multiple of 32: both columns are in or out together
@@ -611,9 +655,28 @@ static int launch_mx_grouped(const MxArgs &a, int64_t m_alloc, unsigned flags, c
     dim3 grid((unsigned) (a.N_pad / kTileN), (unsigned) (m_alloc / kTileM), 1u);  // tiles past padded_offs_col[G] return at once
     const bool row = flags & PT_MX_ROW, col = flags & PT_MX_COL;
     const bool rrht = flags & PT_MX_ROW_RHT, crht = flags & PT_MX_COL_RHT;
+    // persistent TMA form: needs a 16-byte row pitch and base (N % 32 == 0 gives the pitch for 16-bit elements)
+    const bool use_tma = getenv("PT_MX_QUANT_NO_TMA") == nullptr && aligned(a.x, 16) && a.M < (1ll << 31) && m_alloc < (1ll << 31) &&
+                         a.num_groups <= kQMaxGroups;
+    CUtensorMap tmap;
+    const int tiles_n = (int) (a.N_pad / kTileN), tiles_m = (int) (m_alloc / kTileM);
+    const int64_t total_tiles = (int64_t) tiles_n * tiles_m;
+    int tma_grid = 0;
+    if (use_tma) {
+        int rc = make_tmap_x(&tmap, a.x, 1, a.M, a.N);
+        if (rc != PT_OK) return rc;
+        PT_REQUIRE(total_tiles < (1ll << 31), "grouped MX quantize: too many tiles");
+        tma_grid = (int) std::min<int64_t>(total_tiles, (int64_t) sm_count() * kQCtasPerSm);
+    }
 #define PT_MXG_CASE(R, C, RR, CR)                                                                     \
     if (row == R && col == C && (!R || rrht == RR) && (!C || crht == CR)) {                          \
-        mx_quant_kernel<T, FMT, R, C, false, false, RR, CR, true><<<grid, kMxThreads, 0, st>>>(a);   \
+        if (use_tma) {                                                                                \
+            auto kern = mx_quant_tma_kernel<T, FMT, R, C, false, false, RR, CR, true>;               \
+            PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kQSmemBytes)); \
+            kern<<<tma_grid, kQThreads, kQSmemBytes, st>>>(tmap, a, tiles_n, tiles_m, total_tiles, nullptr); \
+        } else {                                                                                      \
+            mx_quant_kernel<T, FMT, R, C, false, false, RR, CR, true><<<grid, kMxThreads, 0, st>>>(a); \
+        }                                                                                             \
         PT_LAUNCH_OK();                                                                               \
         return PT_OK;                                                                                 \
     }

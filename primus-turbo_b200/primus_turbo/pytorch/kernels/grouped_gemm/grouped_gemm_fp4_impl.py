@@ -19,7 +19,11 @@ def grouped_gemm_fp4_impl(a, b, a_scales, b_scales, group_lens, group_offs, tran
     K = a.view(torch.uint8).shape[1] * 2
     offs_read = group_offs.to(torch.int64).contiguous()
     offs_write = offs_read if group_offs_out is None else group_offs_out.to(torch.int64).contiguous()
-    out = torch.zeros((rows, N), dtype=out_dtype, device=a.device)
+    # rows past the last group stay zero: only that tail is cleared (its first row is read on the device)
+    out = torch.empty((rows, N), dtype=out_dtype, device=a.device)
+    with torch.cuda.device(a.device):
+        nv.check(nv.lib().pt_zero_rows_from(nv.ptr(out), rows, N * out.element_size(), nv.ptr(offs_write[G:]), nv.stream(a.device)),
+                 "zero_rows_from")
     lib = nv.lib()
     ws_bytes = lib.pt_gemm_fp4_workspace_bytes(rows, N, K, G, 1, 0)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)

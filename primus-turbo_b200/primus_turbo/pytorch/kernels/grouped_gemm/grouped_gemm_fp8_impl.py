@@ -39,7 +39,11 @@ def grouped_gemm_fp8_impl(a: torch.Tensor, b: torch.Tensor, a_scales: torch.Tens
     N = b.shape[1] if trans_b else b.shape[2]
     offs_read = group_offs.to(torch.int64).contiguous()
     offs_write = offs_read if group_offs_out is None else group_offs_out.to(torch.int64).contiguous()
-    out = torch.zeros((rows, N), dtype=out_dtype, device=a.device)  # rows no group owns stay zero
+    # rows past the last group stay zero: only that tail is cleared (its first row is read on the device)
+    out = torch.empty((rows, N), dtype=out_dtype, device=a.device)
+    with torch.cuda.device(a.device):
+        nv.check(nv.lib().pt_zero_rows_from(nv.ptr(out), rows, N * out.element_size(), nv.ptr(offs_write[G:]), nv.stream(a.device)),
+                 "zero_rows_from")
     st = nv.status_word(a.device)
     max_ctas = int(num_cu) if num_cu else 0
     lib = nv.lib()
