@@ -204,6 +204,7 @@ constexpr int kBqTileBytes = kBlk * kBlk * 2;
 constexpr int kBqConsumerWarps = 8;
 constexpr int kBqThreads = 32 * (1 + kBqConsumerWarps);
 constexpr int kBqSmemBytes = kBqStages * kBqTileBytes + 1024 + 256;
+constexpr int kBqMaxGroups = 256;  // segment form: offset tables of up to this many groups are held in shared memory
 
 struct BqArgs {
     int64_t M, N;
@@ -247,6 +248,16 @@ __global__ void __launch_bounds__(kBqThreads, kBqCtasPerSm)
     const int64_t m_blocks = (a.M + kBlk - 1) / kBlk;
     const int64_t n_blocks = a.tiles_n;
     const int64_t m_padded = kSeg ? a.seg.padded_offs[a.seg.num_groups] : 0;
+    // segment form: both offset tables are copied to shared memory first (a search through global memory would cost
+    // each tile several dependent round trips)
+    __shared__ int s_gtab[kSeg ? 2 * (kBqMaxGroups + 1) : 1];
+    if constexpr (kSeg) {
+        for (int i = threadIdx.x; i <= a.seg.num_groups; i += blockDim.x) {
+            s_gtab[i] = (int) a.seg.padded_offs[i];
+            s_gtab[(kBqMaxGroups + 1) + i] = (int) a.seg.group_offs[i];
+        }
+        __syncthreads();
+    }
 
     // tile t -> batch, row block (segment: block of the padded row space), column block; and for the segment form
     // the input rows it covers: [in_row0, in_row0 + n_valid), written at padded rows out_row0 ...
@@ -259,13 +270,14 @@ __global__ void __launch_bounds__(kBqThreads, kBqCtasPerSm)
         if constexpr (kSeg) {
             const int64_t out_row0 = pid_m * kBlk;
             if (out_row0 >= m_padded) return false;
+            const int *poffs = s_gtab, *goffs = s_gtab + (kBqMaxGroups + 1);
             int lo = 0, hi = a.seg.num_groups - 1;  // last group g with padded_offs[g] <= out_row0 (empty groups skipped)
             while (lo < hi) {
                 const int mid = (lo + hi + 1) >> 1;
-                if (a.seg.padded_offs[mid] <= out_row0) lo = mid; else hi = mid - 1;
+                if (poffs[mid] <= out_row0) lo = mid; else hi = mid - 1;
             }
-            in_row0 = a.seg.group_offs[lo] + (out_row0 - a.seg.padded_offs[lo]);
-            const int64_t in_hi = min(a.seg.group_offs[lo + 1], a.M);
+            in_row0 = goffs[lo] + (out_row0 - poffs[lo]);
+            const int64_t in_hi = min((int64_t) goffs[lo + 1], a.M);
             n_valid = (int) max((int64_t) 0, min((int64_t) kBlk, in_hi - in_row0));
         }
         return true;
@@ -538,7 +550,8 @@ static int launch_tile(const void *x, int x_dtype, int64_t B, int64_t m_tiles, i
     // persistent TMA form: 16-bit input, 16-byte vectors on every output row
     const bool tma_ok = x_dtype != PT_F32 && N % 16 == 0 && aligned(x, 16) && (!q_row || aligned(q_row, 16)) &&
                         (!q_col || aligned(q_col, 16)) && (!s_col || aligned(s_col, 16)) && M < (1ll << 31) && N < (1ll << 31) &&
-                        total_tiles < (1ll << 31) && getenv("PT_BW_QUANT_NO_TMA") == nullptr;
+                        total_tiles < (1ll << 31) && getenv("PT_BW_QUANT_NO_TMA") == nullptr &&
+                        seg.num_groups <= kBqMaxGroups && m_tiles * kBlk < (1ll << 31);
     if (tma_ok) {
         CUtensorMap tmap;
         int rc = make_tmap_u16_3d(&tmap, x, B, M, N, kBlk);
