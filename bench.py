@@ -34,8 +34,8 @@ WORKLOADS = {
 }
 DEFAULT_WORKLOAD = "mxfp8_linear_fwd_llama3_8b_mlp"
 # DRAM bytes (read + write) of one GEMM launch from the ncu capture summarised in
-# profiles/gemm_mxfp8_8192x14336x4096.md; null until that capture exists for the workload.
-GEMM_DRAM_TRAFFIC = {"mxfp8_linear_fwd_llama3_8b_mlp": 333.5e6}
+# profiles/gemm_mxfp8_pair_8192x14336x4096.md; null until that capture exists for the workload.
+GEMM_DRAM_TRAFFIC = {"mxfp8_linear_fwd_llama3_8b_mlp": 334.6e6}
 
 
 def measured_peaks():
