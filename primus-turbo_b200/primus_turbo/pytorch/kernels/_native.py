@@ -1,4 +1,5 @@
 """Glue between torch tensors and the C ABI: enum codes, pointer extraction, status checks."""
+import contextlib
 import ctypes
 
 import torch
@@ -38,6 +39,18 @@ def ptr(t):
 
 def stream(device=None):
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+_NO_GUARD = contextlib.nullcontext()
+
+
+def on_device(device):
+    """Context in which `device` is the current CUDA device; free when it already is (the usual case: one process
+    per GPU), a torch device guard otherwise."""
+    idx = device.index
+    if idx is None or idx == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(device)
 
 
 def require_cuda(*tensors):

@@ -79,7 +79,7 @@ def _launch_blockwise(a_op, a_desc, a_s, b_op, b_desc, b_s, out, beta, M, N, kc)
         # a K-major operand may carry zero padding up to a multiple of 16; the other side must agree on K
         K = max(K, kc)
     st = nv.status_word(out.device)
-    with torch.cuda.device(out.device):
+    with nv.on_device(out.device):
         nv.check(nv.lib().pt_grouped_gemm_fp8_blockwise(
             nv.ptr(a_t), nv.fmt_code(a_t.dtype), a_mn, a_r, a_c, nv.ptr(a_s), *a_desc,
             nv.ptr(b_t), nv.fmt_code(b_t.dtype), b_mn, b_r, b_c, nv.ptr(b_s), *b_desc, 0,
@@ -95,7 +95,7 @@ def _launch(a_km, a_s, b_km, b_s, out, gran, beta, block_n=0):
     st = nv.status_word(out.device)
     ws_bytes = nv.lib().pt_gemm_fp8_workspace_bytes(_GRAN[gran], M, N, K, 1, 0, block_n)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=out.device) if ws_bytes else None
-    with torch.cuda.device(out.device):
+    with nv.on_device(out.device):
         nv.check(nv.lib().pt_gemm_fp8(nv.ptr(a_km), nv.ptr(a_s), nv.fmt_code(a_km.dtype), nv.ptr(b_km), nv.ptr(b_s),
                                        nv.fmt_code(b_km.dtype), nv.ptr(out), nv.src_code(out.dtype), _GRAN[gran], M, N, K,
                                        float(beta), block_n, nv.ptr(ws), ws_bytes, nv.ptr(st), nv.stream(out.device)),

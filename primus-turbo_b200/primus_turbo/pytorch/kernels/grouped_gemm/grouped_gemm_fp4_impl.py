@@ -21,14 +21,14 @@ def grouped_gemm_fp4_impl(a, b, a_scales, b_scales, group_lens, group_offs, tran
     offs_write = offs_read if group_offs_out is None else group_offs_out.to(torch.int64).contiguous()
     # rows past the last group stay zero: only that tail is cleared (its first row is read on the device)
     out = torch.empty((rows, N), dtype=out_dtype, device=a.device)
-    with torch.cuda.device(a.device):
+    with nv.on_device(a.device):
         nv.check(nv.lib().pt_zero_rows_from(nv.ptr(out), rows, N * out.element_size(), nv.ptr(offs_write[G:]), nv.stream(a.device)),
                  "zero_rows_from")
     lib = nv.lib()
     ws_bytes = lib.pt_gemm_fp4_workspace_bytes(rows, N, K, G, 1, 0)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)
     st = nv.status_word(a.device)
-    with torch.cuda.device(a.device):
+    with nv.on_device(a.device):
         nv.check(lib.pt_grouped_gemm_fp4(nv.ptr(a), nv.ptr(a_scales.contiguous()), nv.ptr(b), nv.ptr(b_scales.contiguous()), nv.ptr(out),
                                          nv.src_code(out_dtype), rows, rows, N, K, nv.ptr(offs_read), nv.ptr(offs_write), G, 0.0, 0,
                                          int(num_cu) if num_cu else 0, nv.ptr(ws), ws_bytes, nv.ptr(st), nv.stream(a.device)),
@@ -52,7 +52,7 @@ def _variable_k(a, b, a_scales, b_scales, group_lens, group_offs, out_dtype, num
     ws_bytes = lib.pt_gemm_fp4_workspace_bytes(M, N, T, G, 2, 0)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)
     st = nv.status_word(a.device)
-    with torch.cuda.device(a.device):
+    with nv.on_device(a.device):
         nv.check(lib.pt_grouped_gemm_fp4_variable_k(nv.ptr(a), nv.ptr(a_scales.contiguous()), nv.ptr(b), nv.ptr(b_scales.contiguous()),
                                                     nv.ptr(out), nv.src_code(out.dtype), M, N, T, nv.ptr(k_offs), G, beta, 0,
                                                     int(num_cu) if num_cu else 0, nv.ptr(ws), ws_bytes, nv.ptr(st),

@@ -41,13 +41,13 @@ def grouped_gemm_fp8_impl(a: torch.Tensor, b: torch.Tensor, a_scales: torch.Tens
     offs_write = offs_read if group_offs_out is None else group_offs_out.to(torch.int64).contiguous()
     # rows past the last group stay zero: only that tail is cleared (its first row is read on the device)
     out = torch.empty((rows, N), dtype=out_dtype, device=a.device)
-    with torch.cuda.device(a.device):
+    with nv.on_device(a.device):
         nv.check(nv.lib().pt_zero_rows_from(nv.ptr(out), rows, N * out.element_size(), nv.ptr(offs_write[G:]), nv.stream(a.device)),
                  "zero_rows_from")
     st = nv.status_word(a.device)
     max_ctas = int(num_cu) if num_cu else 0
     lib = nv.lib()
-    with torch.cuda.device(a.device):
+    with nv.on_device(a.device):
         if gran == ScalingGranularity.BLOCKWISE:
             a_s = a_scales.to(torch.float32).contiguous()
             b_s = b_scales.to(torch.float32).contiguous()
@@ -96,7 +96,7 @@ def _variable_k(a, b, a_scales, b_scales, group_lens, group_offs, trans_a, trans
     max_ctas = int(num_cu) if num_cu else 0
     beta = 0.0 if out is None else 1.0
     lib = nv.lib()
-    with torch.cuda.device(a.device):
+    with nv.on_device(a.device):
         if gran == ScalingGranularity.BLOCKWISE:
             # a [T, Ka], b [T, Nb] token-major (T = padded tokens); C[g] = a[seg]^T . b[seg] -> [Ka, Nb] (or transposed)
             assert trans_a and not trans_b, "blockwise variable-K takes token-major operands (trans_a=True, trans_b=False)"

@@ -10,6 +10,6 @@ def group_offs_from_lens(group_lens: torch.Tensor) -> torch.Tensor:
     lens = group_lens.to(torch.int64).contiguous()
     G = lens.numel()
     offs = torch.empty(G + 1, dtype=torch.int64, device=lens.device)
-    with torch.cuda.device(lens.device):
+    with nv.on_device(lens.device):
         nv.check(nv.lib().pt_compute_group_offs(nv.ptr(lens), G, nv.ptr(offs), nv.stream(lens.device)), "compute_group_offs")
     return offs

@@ -35,7 +35,7 @@ def quantize_fp8_tensorwise_impl(x: torch.Tensor, out_dtype: torch.dtype,
     if scale is not None:
         assert scale.numel() == 1, "tensorwise scale must be scalar tensor"
         scale = scale.to(torch.float32).contiguous()
-    with torch.cuda.device(x.device):
+    with nv.on_device(x.device):
         nv.check(nv.lib().pt_quantize_fp8_tensorwise(nv.ptr(x), nv.src_code(x.dtype), x.numel(), nv.fmt_code(out_dtype),
                                                       nv.ptr(q), nv.ptr(scale_inv), nv.ptr(scale), nv.ptr(ws),
                                                       ws.numel() * 4, nv.stream(x.device)), "quantize_fp8_tensorwise")
@@ -70,7 +70,7 @@ def quantize_fp8_rowwise_impl(x: torch.Tensor, out_dtype: torch.dtype, axis: int
     if scale is not None:
         assert list(scale.shape) == scale_shape
         scale = scale.to(torch.float32).contiguous()
-    with torch.cuda.device(x.device):
+    with nv.on_device(x.device):
         nv.check(nv.lib().pt_quantize_fp8_rowwise(nv.ptr(x), nv.src_code(x.dtype), B, M, N, int(last),
                                                    nv.fmt_code(out_dtype), nv.ptr(q), nv.ptr(scale_inv), nv.ptr(scale),
                                                    nv.ptr(ws), 0 if ws is None else ws.numel() * 4,
@@ -82,7 +82,7 @@ def dequantize_fp8_tensorwise_impl(x: torch.Tensor, out_dtype: torch.dtype, scal
     nv.require_cuda(x, scale_inv)
     x = x.contiguous()
     y = torch.empty_like(x, dtype=out_dtype)
-    with torch.cuda.device(x.device):
+    with nv.on_device(x.device):
         nv.check(nv.lib().pt_dequantize_fp8(nv.ptr(x), nv.fmt_code(x.dtype), nv.ptr(scale_inv.contiguous()), 0, 1, 1,
                                              x.numel(), nv.ptr(y), nv.src_code(out_dtype), nv.stream(x.device)),
                  "dequantize_fp8_tensorwise")
@@ -105,7 +105,7 @@ def dequantize_fp8_rowwise_impl(x: torch.Tensor, out_dtype: torch.dtype, axis: i
         M, N = shape[axis], 1
         for s in shape[axis + 1:]:
             N *= s
-    with torch.cuda.device(x.device):
+    with nv.on_device(x.device):
         nv.check(nv.lib().pt_dequantize_fp8(nv.ptr(x), nv.fmt_code(x.dtype), nv.ptr(scale_inv), kind, B, M, N,
                                              nv.ptr(y), nv.src_code(out_dtype), nv.stream(x.device)),
                  "dequantize_fp8_rowwise")
@@ -125,7 +125,7 @@ def quant_fp8_blockwise_impl(x: torch.Tensor, dtype: torch.dtype, axis: int,
     s = torch.empty((M, ceil_div(N, BLOCK)) if axis == 1 else (ceil_div(M, BLOCK), N), dtype=torch.float32,
                     device=x.device)
     args = (nv.ptr(q), nv.ptr(s), None, None) if axis == 1 else (None, None, nv.ptr(q), nv.ptr(s))
-    with torch.cuda.device(x.device):
+    with nv.on_device(x.device):
         nv.check(nv.lib().pt_quantize_fp8_blockwise(nv.ptr(x), nv.src_code(x.dtype), M, N, nv.fmt_code(dtype), *args,
                                                      nv.stream(x.device)), "quant_fp8_blockwise")
     return q, s
@@ -141,7 +141,7 @@ def quant_fp8_blockwise_dual_impl(x: torch.Tensor, dtype: torch.dtype, block_siz
     q_col = torch.empty((M, N), dtype=dtype, device=x.device)
     s_row = torch.empty((M, ceil_div(N, BLOCK)), dtype=torch.float32, device=x.device)
     s_col = torch.empty((ceil_div(M, BLOCK), N), dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with nv.on_device(x.device):
         nv.check(nv.lib().pt_quantize_fp8_blockwise(nv.ptr(x), nv.src_code(x.dtype), M, N, nv.fmt_code(dtype),
                                                      nv.ptr(q_row), nv.ptr(s_row), nv.ptr(q_col), nv.ptr(s_col),
                                                      nv.stream(x.device)), "quant_fp8_blockwise_dual")
@@ -158,7 +158,7 @@ def quant_fp8_blockwise_for_weight_impl(w: torch.Tensor, dtype: torch.dtype, blo
     q = torch.empty_like(w, dtype=dtype)
     sshape = (ceil_div(M, BLOCK), ceil_div(N, BLOCK))
     s = torch.empty(sshape if w.dim() == 2 else (B,) + sshape, dtype=torch.float32, device=w.device)
-    with torch.cuda.device(w.device):
+    with nv.on_device(w.device):
         nv.check(nv.lib().pt_quantize_fp8_blockwise_weight(nv.ptr(w), nv.src_code(w.dtype), B, M, N, nv.fmt_code(dtype),
                                                             nv.ptr(q), nv.ptr(s), nv.stream(w.device)),
                  "quant_fp8_blockwise_for_weight")
@@ -171,7 +171,7 @@ def compute_padded_group_offs(group_lens: torch.Tensor, align: int):
     lens = group_lens.to(torch.int64).contiguous()
     plens = torch.empty(G, dtype=torch.int64, device=lens.device)
     poffs = torch.empty(G + 1, dtype=torch.int64, device=lens.device)
-    with torch.cuda.device(lens.device):
+    with nv.on_device(lens.device):
         nv.check(nv.lib().pt_compute_padded_group_offs(nv.ptr(lens), G, align, nv.ptr(plens), nv.ptr(poffs),
                                                         nv.stream(lens.device)), "compute_padded_group_offs")
     return plens, poffs
@@ -192,7 +192,7 @@ def quant_fp8_blockwise_segment_m_row_col_impl(x: torch.Tensor, dtype: torch.dty
     x_col = torch.empty((m_alloc, N), dtype=dtype, device=x.device)
     s_row = torch.empty((ceil_div(N, BLOCK), M), dtype=torch.float32, device=x.device)
     s_col = torch.empty((m_alloc // BLOCK, N), dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with nv.on_device(x.device):
         nv.check(nv.lib().pt_quantize_fp8_blockwise_segment_m(
             nv.ptr(x), nv.src_code(x.dtype), M, N, G, nv.ptr(group_offs.to(torch.int64).contiguous()), nv.ptr(poffs),
             nv.fmt_code(dtype), nv.ptr(x_row), nv.ptr(s_row), nv.ptr(x_col), nv.ptr(s_col), nv.stream(x.device)),
@@ -206,7 +206,7 @@ def _dequant_blockwise(x, scales, out_dtype, kind):
     B = 1 if x.dim() == 2 else x.shape[0]
     M, N = x.shape[-2:]
     y = torch.empty_like(x, dtype=out_dtype)
-    with torch.cuda.device(x.device):
+    with nv.on_device(x.device):
         nv.check(nv.lib().pt_dequantize_fp8_blockwise(nv.ptr(x), nv.fmt_code(x.dtype), nv.ptr(scales.contiguous()), kind,
                                                        B, M, N, nv.ptr(y), nv.src_code(out_dtype), nv.stream(x.device)),
                  "dequant_fp8_blockwise")
@@ -251,7 +251,7 @@ def _mx_quant(x, out_dtype, want_row, want_col, row_recipe, col_recipe):
         flags |= nv.PT_MX_COL | (nv.PT_MX_COL_2D if col_recipe.use_2d_block else 0) | (nv.PT_MX_COL_RHT if col_recipe.use_rht else 0)
         q_col = torch.empty(lead + (N, M_pad // div), dtype=torch.uint8, device=x.device)
         s_col = torch.empty(lead + (N, M_pad // MX_BLOCK), dtype=torch.uint8, device=x.device)
-    with torch.cuda.device(x.device):
+    with nv.on_device(x.device):
         nv.check(nv.lib().pt_quantize_mx(nv.ptr(x), nv.src_code(x.dtype), G, M, N, fmt, flags, nv.ptr(q_row), nv.ptr(s_row),
                                           nv.ptr(q_col), nv.ptr(s_col), nv.stream(x.device)), "quantize_mx")
     view = lambda t: None if t is None else t.view(out_dtype)
@@ -306,7 +306,7 @@ def _dequantize_mx(x, out_dtype, axis, scale_inv, orig_shape=None):
     ss = sb.reshape(-1, rows, sb.shape[-1])
     for g in range(xs.shape[0]):
         y = torch.empty((cols, rows) if transpose else (rows, cols), dtype=out_dtype, device=x.device)
-        with torch.cuda.device(x.device):
+        with nv.on_device(x.device):
             nv.check(nv.lib().pt_dequantize_mx(nv.ptr(xs[g]), fmt, nv.ptr(ss[g]), rows, cols, stored, int(transpose),
                                                 nv.ptr(y), nv.src_code(out_dtype), nv.stream(x.device)), "dequantize_mx")
         outs.append(y)
@@ -328,7 +328,7 @@ def transpose_2d(x: torch.Tensor) -> torch.Tensor:
     assert x.dim() == 2
     x = x.contiguous()
     y = torch.empty((x.shape[1], x.shape[0]), dtype=x.dtype, device=x.device)
-    with torch.cuda.device(x.device):
+    with nv.on_device(x.device):
         nv.check(nv.lib().pt_transpose_2d(nv.ptr(x), x.shape[0], x.shape[1], x.element_size(), nv.ptr(y),
                                            nv.stream(x.device)), "transpose_2d")
     return y
@@ -377,7 +377,7 @@ def _grouped_mx_quant(x, out_dtype, group_lens, group_offs, want_row, want_col, 
         flags |= nv.PT_MX_COL | (nv.PT_MX_COL_RHT if col_recipe.use_rht else 0)
         q_col = torch.empty((N, col_alloc // div), dtype=torch.uint8, device=x.device)
         s_col = torch.empty((N, col_alloc // MX_BLOCK), dtype=torch.uint8, device=x.device)
-    with torch.cuda.device(x.device):
+    with nv.on_device(x.device):
         nv.check(nv.lib().pt_grouped_quantize_mx(nv.ptr(x), nv.src_code(x.dtype), M, N, G, nv.ptr(offs), nv.ptr(poffs_row),
                                                   nv.ptr(poffs_col), fmt, flags, nv.ptr(q_row), nv.ptr(s_row), nv.ptr(q_col),
                                                   nv.ptr(s_col), col_alloc, nv.stream(x.device)), "grouped_quantize_mx")
