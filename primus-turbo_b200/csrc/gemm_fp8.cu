@@ -611,10 +611,13 @@ static int dispatch_block_n(int block_n, const void *a, int64_t a_rows, const vo
             out_elems >= (int64_t) 4096 * 4096 && (!mode_is_mx(MODE) || aligned(mx.workspace, 128))) {
             if constexpr (mode_is_mx(MODE)) {
                 constexpr int kSfP = MODE == GEMM_MXF4 ? 2 : 1;
-                if (mx.workspace_bytes >= mx_workspace_bytes(p.M, p.N, p.K, p.koffs ? 1 : p.G, grouped, 224) * kSfP)
-                    return launch_gemm_pair<224, MODE>(a, a_rows, b, b_rows, p, mx, st);
+                if (mx.workspace_bytes >= mx_workspace_bytes(p.M, p.N, p.K, p.koffs ? 1 : p.G, grouped, 224) * kSfP) {
+                    const int rc = launch_gemm_pair<224, MODE>(a, a_rows, b, b_rows, p, mx, st);
+                    if (rc != PT_ERR_CUDA) return rc;  // a device that cannot launch clusters falls through to single CTAs
+                }
             } else {
-                return launch_gemm_pair<256, MODE>(a, a_rows, b, b_rows, p, mx, st);
+                const int rc = launch_gemm_pair<256, MODE>(a, a_rows, b, b_rows, p, mx, st);
+                if (rc != PT_ERR_CUDA) return rc;
             }
         }
     }
