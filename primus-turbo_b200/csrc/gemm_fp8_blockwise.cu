@@ -78,6 +78,18 @@ struct BwParams {
     int64_t b_group_kstride;   // MN-major B of a grouped GEMM: contraction rows per group
 };
 
+// c (two adjacent fp32 accumulators viewed as one 64-bit register pair) += ((a0, a1) * (s0, s1)) * (t, t) with packed
+// fp32 instructions; each product and sum rounds like the scalar sequence fmaf(a * s, t, c).
+__device__ __forceinline__ void scaled_fma2(uint64_t &c, uint32_t a0, uint32_t a1, float s0, float s1, uint64_t t2) {
+    asm("{\n\t.reg .b64 aa, ss;\n\t"
+        "mov.b64 aa, {%1, %2};\n\t"
+        "mov.b64 ss, {%3, %4};\n\t"
+        "mul.rn.f32x2 aa, aa, ss;\n\t"
+        "fma.rn.f32x2 %0, aa, %5, %0;\n\t}"
+        : "+l"(c)
+        : "r"(a0), "r"(a1), "f"(s0), "f"(s1), "l"(t2));
+}
+
 // Writes one warp's 32 x 128 fp32 accumulators (one row per lane) to C through a padded staging buffer so
 // that global stores are 64-byte row segments; rows / columns outside the group or the matrix are skipped.
 template <typename OutT>
@@ -383,7 +395,7 @@ __global__ void __launch_bounds__(kBwThreads, 1)
             const float *sb_base = p.sb.base + (int64_t) gi * p.sb.group_stride + (int64_t) kb_begin * p.sb.kb_stride;
             constexpr bool sb_uniform = SBM == SB_TILE;
 
-            float acc[128];
+            __align__(8) float acc[128];
 #pragma unroll
             for (int i = 0; i < 128; ++i) acc[i] = 0.f;
 
@@ -407,13 +419,15 @@ __global__ void __launch_bounds__(kBwThreads, 1)
                         // the slab of this K step landed before the partial sum was announced (see the MMA issuer)
                         const float4 *sl =
                             reinterpret_cast<const float4 *>(smem_slab + (step % kBwSlabRing) * (kBwSlabBytes / 4) + half * 128);
+                        // two elements per instruction (mul.f32x2 / fma.f32x2): this path does two operations per
+                        // element and is bound by instruction issue
+                        uint64_t sa2;
+                        asm("mov.b64 %0, {%1, %1};" : "=l"(sa2) : "f"(sa_cur));
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const float4 sv = sl[c * 8 + i];  // same address in every lane: a broadcast read
-                            acc[c * 32 + 4 * i + 0] = fmaf(__uint_as_float(r[4 * i + 0]) * sv.x, sa_cur, acc[c * 32 + 4 * i + 0]);
-                            acc[c * 32 + 4 * i + 1] = fmaf(__uint_as_float(r[4 * i + 1]) * sv.y, sa_cur, acc[c * 32 + 4 * i + 1]);
-                            acc[c * 32 + 4 * i + 2] = fmaf(__uint_as_float(r[4 * i + 2]) * sv.z, sa_cur, acc[c * 32 + 4 * i + 2]);
-                            acc[c * 32 + 4 * i + 3] = fmaf(__uint_as_float(r[4 * i + 3]) * sv.w, sa_cur, acc[c * 32 + 4 * i + 3]);
+                            scaled_fma2(*reinterpret_cast<uint64_t *>(&acc[c * 32 + 4 * i + 0]), r[4 * i + 0], r[4 * i + 1], sv.x, sv.y, sa2);
+                            scaled_fma2(*reinterpret_cast<uint64_t *>(&acc[c * 32 + 4 * i + 2]), r[4 * i + 2], r[4 * i + 3], sv.z, sv.w, sa2);
                         }
                     } else {
                         // general per-row B scales read from global memory (no reference path needs this to be fast)
