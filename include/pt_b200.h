@@ -165,6 +165,20 @@ int pt_dequantize_mx(const void *q, int fmt, const uint8_t *s, int64_t rows, int
 /* y [N, M] = x [M, N]^T for 1-, 2- or 4-byte elements (bindings_pytorch.cpp:44, csrc/kernels/transpose/transpose_2d.cu). */
 int pt_transpose_2d(const void *x, int64_t M, int64_t N, int elem_bytes, void *y, void *stream);
 
+/* The same over a batch: y [B, N, M] = x [B, M, N] transposed per matrix (a [G, K, N] expert weight to [G, N, K]). */
+int pt_transpose_batched(const void *x, int64_t B, int64_t M, int64_t N, int elem_bytes, void *y, void *stream);
+
+/* Token-major to token-minor copy of a grouped byte operand for the variable-K GEMM: x [M, C] holds group g in rows
+ * group_offs[g] .. group_offs[g+1]; y [C, T] receives them as columns padded_offs[g] .. padded_offs[g] + len_g.  The rest
+ * of every segment (padded_offs are multiples of 128, see pt_compute_padded_group_offs) and all columns from
+ * padded_offs[G] on are written as zero bytes, so that they add nothing to the contraction.  T is a multiple of 64 and
+ * at least padded_offs[G]; both offset arrays are device int64 [G+1] (no host synchronisation).
+ * The reference's tensorwise / rowwise variable-K kernels read the token-major operands in place
+ * (primus_turbo/pytorch/kernels/grouped_gemm/grouped_gemm_fp8_impl.py:936-1030); pt_grouped_gemm_fp8_variable_k takes
+ * K-major operands, and this is the copy that produces them. */
+int pt_grouped_transpose_pad(const void *x, int64_t M, int64_t C, const int64_t *group_offs, const int64_t *padded_offs,
+                             int G, void *y, int64_t T, void *stream);
+
 /* Zero-fills rows [*first_row, rows) of a row-major buffer with `row_bytes` bytes per row (a multiple of 4, base 4-byte
  * aligned); `first_row` is a device pointer, so no host synchronisation is needed.  The grouped GEMMs leave rows past the
  * last group untouched; the reference returns zeros there (grouped_gemm_fp8_impl.py: output tail), so the caller

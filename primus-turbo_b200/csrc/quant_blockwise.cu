@@ -524,10 +524,12 @@ __global__ void __launch_bounds__(256) zero_rows_from_kernel(uint32_t *__restric
     for (int64_t i = begin + (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < end; i += stride) buf[i] = 0u;
 }
 
-// tiled transpose of 1/2/4-byte elements
+// tiled transpose of 1/2/4-byte elements; blockIdx.z walks a batch of [M, N] matrices
 template <typename E>
 __global__ void __launch_bounds__(256) transpose_kernel(const E *__restrict__ x, int64_t M, int64_t N, E *__restrict__ y) {
     __shared__ E tile[64][64 + (sizeof(E) == 1 ? 4 : (sizeof(E) == 2 ? 2 : 1))];
+    x += (int64_t) blockIdx.z * M * N;
+    y += (int64_t) blockIdx.z * M * N;
     const int64_t m0 = (int64_t) blockIdx.y * 64, n0 = (int64_t) blockIdx.x * 64;
     const int tx = threadIdx.x % 64, ty = threadIdx.x / 64;
     for (int r = ty; r < 64; r += 4)
@@ -535,6 +537,65 @@ __global__ void __launch_bounds__(256) transpose_kernel(const E *__restrict__ x,
     __syncthreads();
     for (int r = ty; r < 64; r += 4)
         if (n0 + r < N && m0 + tx < M) y[(n0 + r) * M + m0 + tx] = tile[tx][r];
+}
+
+// Grouped transpose with segment padding of a byte matrix: x [M, C] holds G groups of rows (group g = rows
+// offs[g] .. offs[g+1]); y [C, T] receives group g's rows as columns poffs[g] .. poffs[g] + len_g, the rest of each
+// 128-aligned segment and everything from poffs[G] on as zero bytes.  A block moves 64 padded columns x 64 source
+// columns; segments start on multiples of 128, so the 64 padded columns of a block belong to one group.
+// Shared-memory layout: row r keeps its four 16-byte chunks at chunk index (chunk ^ (r >> 4)), which spreads the
+// transposed byte reads of the four thread quarters over different banks.
+__global__ void __launch_bounds__(256)
+    grouped_transpose_pad_kernel(const uint8_t *__restrict__ x, int64_t C, int vec_ok, const int64_t *__restrict__ offs,
+                                 const int64_t *__restrict__ poffs, int G, uint8_t *__restrict__ y, int64_t T) {
+    __shared__ __align__(16) uint8_t tile[64][80];
+    __shared__ int64_t s_src;
+    __shared__ int s_valid;
+    const int64_t t0 = (int64_t) blockIdx.y * 64, c0 = (int64_t) blockIdx.x * 64;
+    if (threadIdx.x == 0) {
+        int valid = 0;
+        int64_t src = 0;
+        if (G > 0 && t0 < poffs[G]) {
+            int lo = 0, hi = G - 1;  // last group whose segment starts at or before t0
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (poffs[mid] <= t0) lo = mid;
+                else hi = mid - 1;
+            }
+            const int64_t in_seg = t0 - poffs[lo];
+            const int64_t left = offs[lo + 1] - offs[lo] - in_seg;
+            valid = (int) max((int64_t) 0, min((int64_t) 64, left));
+            src = offs[lo] + in_seg;
+        }
+        s_valid = valid;
+        s_src = src;
+    }
+    __syncthreads();
+    const int valid = s_valid;
+    const int r = threadIdx.x >> 2, part = threadIdx.x & 3;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < valid) {
+        const int64_t col = c0 + part * 16;
+        const uint8_t *p = x + (s_src + r) * C + col;
+        if (vec_ok && col + 16 <= C) {
+            v = *reinterpret_cast<const uint4 *>(p);
+        } else {
+            uint8_t b[16];
+#pragma unroll
+            for (int k = 0; k < 16; ++k) b[k] = col + k < C ? p[k] : (uint8_t) 0;
+            v = *reinterpret_cast<uint4 *>(b);
+        }
+    }
+    *reinterpret_cast<uint4 *>(&tile[r][(part ^ (r >> 4)) * 16]) = v;
+    __syncthreads();
+    const int c = threadIdx.x >> 2;  // output row inside the tile; this thread writes padded columns part*16 .. +15
+    if (c0 + c < C) {
+        __align__(16) uint8_t b[16];
+        const int pos = (((c >> 4) ^ part) << 4) | (c & 15);
+#pragma unroll
+        for (int k = 0; k < 16; ++k) b[k] = tile[part * 16 + k][pos];
+        *reinterpret_cast<uint4 *>(y + (c0 + c) * T + t0 + part * 16) = *reinterpret_cast<uint4 *>(b);
+    }
 }
 
 }  // namespace ptb
@@ -660,12 +721,31 @@ int pt_zero_rows_from(void *buf, int64_t rows, int64_t row_bytes, const int64_t 
     return PT_OK;
 }
 
+int pt_grouped_transpose_pad(const void *x, int64_t M, int64_t C, const int64_t *group_offs, const int64_t *padded_offs,
+                             int G, void *y, int64_t T, void *stream) {
+    PT_REQUIRE(M >= 0 && C >= 0 && T >= 0 && G >= 0, "grouped transpose: negative extent");
+    if (C == 0 || T == 0) return PT_OK;
+    PT_REQUIRE(y && group_offs && padded_offs && (x || M == 0), "grouped transpose: null pointer");
+    PT_REQUIRE(T % 64 == 0 && aligned(y, 16), "grouped transpose: the padded token count must be a multiple of 64 and y 16-byte aligned");
+    PT_REQUIRE(T / 64 <= 65535, "grouped transpose: too many tokens");
+    const int vec_ok = C % 16 == 0 && aligned(x, 16);
+    dim3 grid((unsigned) ceil_div(C, 64), (unsigned) (T / 64));
+    grouped_transpose_pad_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>((const uint8_t *) x, C, vec_ok, group_offs, padded_offs, G,
+                                                                          (uint8_t *) y, T);
+    PT_LAUNCH_OK();
+    return PT_OK;
+}
+
 int pt_transpose_2d(const void *x, int64_t M, int64_t N, int elem_bytes, void *y, void *stream) {
-    PT_REQUIRE(M >= 0 && N >= 0, "transpose: negative shape");
-    if (M * N == 0) return PT_OK;
+    return pt_transpose_batched(x, 1, M, N, elem_bytes, y, stream);
+}
+
+int pt_transpose_batched(const void *x, int64_t B, int64_t M, int64_t N, int elem_bytes, void *y, void *stream) {
+    PT_REQUIRE(B >= 0 && M >= 0 && N >= 0, "transpose: negative shape");
+    if (B * M * N == 0) return PT_OK;
     PT_REQUIRE(x && y, "transpose: null pointer");
-    PT_REQUIRE(ceil_div(M, 64) <= 65535, "transpose: M too large");
-    dim3 grid((unsigned) ceil_div(N, 64), (unsigned) ceil_div(M, 64));
+    PT_REQUIRE(ceil_div(M, 64) <= 65535 && B <= 65535, "transpose: M or batch too large");
+    dim3 grid((unsigned) ceil_div(N, 64), (unsigned) ceil_div(M, 64), (unsigned) B);
     cudaStream_t st = (cudaStream_t) stream;
     if (elem_bytes == 1) transpose_kernel<uint8_t><<<grid, 256, 0, st>>>((const uint8_t *) x, M, N, (uint8_t *) y);
     else if (elem_bytes == 2) transpose_kernel<uint16_t><<<grid, 256, 0, st>>>((const uint16_t *) x, M, N, (uint16_t *) y);

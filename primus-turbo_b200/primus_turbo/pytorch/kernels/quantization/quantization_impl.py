@@ -334,6 +334,36 @@ def transpose_2d(x: torch.Tensor) -> torch.Tensor:
     return y
 
 
+def transpose_batched(x: torch.Tensor) -> torch.Tensor:
+    """[B, M, N] -> [B, N, M] (contiguous), one launch for the whole batch."""
+    nv.require_cuda(x)
+    assert x.dim() == 3
+    x = x.contiguous()
+    B, M, N = x.shape
+    y = torch.empty((B, N, M), dtype=x.dtype, device=x.device)
+    with nv.on_device(x.device):
+        nv.check(nv.lib().pt_transpose_batched(nv.ptr(x), B, M, N, x.element_size(), nv.ptr(y), nv.stream(x.device)),
+                 "transpose_batched")
+    return y
+
+
+def grouped_transpose_pad(x: torch.Tensor, group_offs: torch.Tensor, padded_offs: torch.Tensor) -> torch.Tensor:
+    """x [M, C] of 1-byte elements, grouped along M -> [C, T] with each group's tokens in its 128-padded segment
+    (zero filled), T = round_up(M, 128) + 128 * G: an upper bound of padded_offs[-1] known without reading the device."""
+    nv.require_cuda(x, group_offs, padded_offs)
+    assert x.dim() == 2 and x.element_size() == 1
+    x = x.contiguous()
+    M, C = x.shape
+    G = group_offs.numel() - 1
+    T = ceil_div(M, BLOCK) * BLOCK + BLOCK * G
+    y = torch.empty((C, T), dtype=x.dtype, device=x.device)
+    with nv.on_device(x.device):
+        nv.check(nv.lib().pt_grouped_transpose_pad(nv.ptr(x), M, C, nv.ptr(group_offs.to(torch.int64).contiguous()),
+                                                    nv.ptr(padded_offs.to(torch.int64).contiguous()), G, nv.ptr(y), T,
+                                                    nv.stream(x.device)), "grouped_transpose_pad")
+    return y
+
+
 # ------------------------------------------------------------------------------ grouped MX
 MX_GROUP_ROW_ALIGN = 32   # fp8 row-wise copy: each group padded to 32 rows (quantization.cpp:1098 of the reference)
 MX_GROUP_COL_ALIGN = 128  # col-wise copy: each group padded to 128 rows

@@ -9,13 +9,13 @@ import torch
 
 from ..core.low_precision import Float8QuantConfig, ScalingGranularity, ScalingRecipe
 from ..core.quantized_tensor import QuantizedTensor, QuantizedTensorPair, check_quantized_tensor
-from ..kernels.gemm.gemm_fp8_impl import gemm_fp8_impl
 from ..kernels.grouped_gemm.grouped_gemm_fp8_impl import (grouped_gemm_fp8_impl, grouped_gemm_fp8_variable_k_accum_impl,
                                                           grouped_gemm_fp8_variable_k_impl)
 from ..kernels.grouped_gemm.grouped_gemm_utils import group_offs_from_lens
-from ..kernels.quantization.quantization_impl import (grouped_quantize_mxfp8_impl, quant_fp8_blockwise_for_weight_impl,
+from ..kernels.quantization.quantization_impl import (compute_padded_group_offs, grouped_quantize_mxfp8_impl,
+                                                      grouped_transpose_pad, quant_fp8_blockwise_for_weight_impl,
                                                       quant_fp8_blockwise_segment_m_row_col_impl, quantize_fp8_rowwise_impl,
-                                                      quantize_fp8_tensorwise_impl, quantize_mxfp8_impl)
+                                                      quantize_fp8_tensorwise_impl, quantize_mxfp8_impl, transpose_batched)
 from .utils import _get_dummy_wgrad, _get_fp8_dtype, _setup_fused_grad_accum
 
 __all__ = ["grouped_gemm_fp8"]
@@ -121,84 +121,116 @@ class FP8GroupedGemmMXFunc(torch.autograd.Function):
         return (grad_a, grad_b[:, :N, :K]) + (None,) * 9
 
 
-def _per_group_wgrad(a_q, a_s, g_q, g_s, group_lens, out_dtype, gran, trans_b, row_scales):
-    """Tensorwise / rowwise wgrad as one dense TN GEMM per group.  Reads group_lens on the host (one sync): the
-    variable-K kernel takes 128-padded token segments, which these two granularities do not produce."""
-    lens = group_lens.tolist()
-    outs, start = [], 0
-    for g, n in enumerate(lens):
-        sa = a_s[g] if row_scales else a_s
-        sg = g_s[g] if row_scales else g_s
-        if n == 0:
-            shape = (g_q.shape[1], a_q.shape[1]) if trans_b else (a_q.shape[1], g_q.shape[1])
-            outs.append(torch.zeros(shape, dtype=out_dtype, device=a_q.device))
-        else:
-            outs.append(gemm_fp8_impl(a_q[start:start + n], sa, True, g_q[start:start + n], sg, False, out_dtype, trans_b, gran))
-        start += n
-    return torch.stack(outs)
+def _token_minor_wgrad(a_q, a_s, g_q, g_s, group_lens, group_offs, trans_b, out_dtype, gran, num_cu, fuse, main_grad):
+    """Tensorwise / rowwise wgrad without a host round trip: both token-major FP8 operands are copied to the
+    [features, padded tokens] layout (each group's tokens in a zero-filled 128-aligned segment) and contracted by the
+    variable-K kernel.  a_q [M, K], g_q [M, N]; scales are scalars (tensorwise) or per column over all tokens
+    (rowwise, as the reference quantizes a grouped tensor along axis -2: primus_turbo/pytorch/core/quantized_tensor.py:309-324).
+    Returns grad_b as [G, N, K] (trans_b) or [G, K, N]."""
+    G = group_lens.numel()
+    plens, poffs = compute_padded_group_offs(group_lens, 128)
+    a_t = grouped_transpose_pad(a_q, group_offs, poffs)   # [K, T]
+    g_t = grouped_transpose_pad(g_q, group_offs, poffs)   # [N, T]
+    if gran == ScalingGranularity.ROWWISE:
+        a_s = a_s.reshape(1, -1).expand(G, -1).contiguous()
+        g_s = g_s.reshape(1, -1).expand(G, -1).contiguous()
+    # variable-K computes lhs . rhs^T per segment; trans_c swaps the operands: [G, N, K] = g_t . a_t^T, [G, K, N] the swap
+    return _variable_k(g_t, a_t, g_s, a_s, plens, poffs, False, False, not trans_b, out_dtype, gran, num_cu,
+                       inplace_add_to_out=fuse, out=main_grad)
 
 
 class FP8GroupedGemmTensorFunc(torch.autograd.Function):
+    """TENSORWISE: one scale per operand.  Follows FP8GroupedGemmTensorFunc of the reference
+    (primus_turbo/pytorch/ops/grouped_gemm_fp8.py:449-601)."""
+
     @staticmethod
     def forward(ctx, a, b, a_t, b_t, group_lens, group_offs, trans_b, out_dtype, config, num_cu, fuse_bgrad_accum_pattern=None):
-        assert fuse_bgrad_accum_pattern is None, "fused main_grad accumulation: use BLOCKWISE or MX_BLOCKWISE"
-        assert trans_b, "tensorwise grouped GEMM takes b as [G, N, K]"
+        fuse, main_grad = _setup_fused_grad_accum(b, fuse_bgrad_accum_pattern)
+        assert config.granularity == ScalingGranularity.TENSORWISE
         fwd = _get_fp8_dtype(config.format, True)
-        a_q, a_s = quantize_fp8_tensorwise_impl(a, fwd)
-        b_q, b_s = quantize_fp8_tensorwise_impl(b, fwd)
-        out = grouped_gemm_fp8_impl(a_q, b_q, a_s, b_s, group_lens, group_offs, False, True, out_dtype, config.granularity, num_cu)
+        if isinstance(a, QuantizedTensor):
+            check_quantized_tensor(a, config)
+            a_q, a_s = a.qdata, a.scale_inv
+        else:
+            a_q, a_s = quantize_fp8_tensorwise_impl(a.contiguous(), fwd)
+        if isinstance(b, QuantizedTensor):
+            check_quantized_tensor(b, config)
+            b_q, b_s = b.qdata, b.scale_inv
+        else:
+            b_q, b_s = quantize_fp8_tensorwise_impl(b.contiguous(), fwd)
+        b_km = b_q if trans_b else transpose_batched(b_q)                    # [G, N, K]
+        out = grouped_gemm_fp8_impl(a_q, b_km, a_s, b_s, group_lens, group_offs, False, True, out_dtype, config.granularity, num_cu)
         ctx.save_for_backward(a_q, a_s, b_q, b_s, group_lens, group_offs)
-        ctx.config, ctx.out_dtype, ctx.num_cu = config, out_dtype, num_cu
+        ctx.trans_b, ctx.config, ctx.out_dtype, ctx.num_cu = trans_b, config, out_dtype, num_cu
+        ctx.fuse, ctx.main_grad = fuse, main_grad
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        from ..kernels.quantization.quantization_impl import transpose_2d
         a_q, a_s, b_q, b_s, group_lens, group_offs = ctx.saved_tensors
         gran = ctx.config.granularity
         g_q, g_s = quantize_fp8_tensorwise_impl(grad_out.contiguous(), _get_fp8_dtype(ctx.config.format, False))
-        G, N, K = b_q.shape
-        b_t_q = torch.stack([transpose_2d(b_q[g]) for g in range(G)])  # [G, K, N]: dgrad contracts over N
-        grad_a = grouped_gemm_fp8_impl(g_q, b_t_q, g_s, b_s, group_lens, group_offs, False, True, ctx.out_dtype, gran, ctx.num_cu)
-        grad_b = _per_group_wgrad(a_q, a_s, g_q, g_s, group_lens, ctx.out_dtype, gran, True, False)
+        b_nm = transpose_batched(b_q) if ctx.trans_b else b_q                # [G, K, N]: dgrad contracts over N
+        grad_a = grouped_gemm_fp8_impl(g_q, b_nm, g_s, b_s, group_lens, group_offs, False, True, ctx.out_dtype, gran, ctx.num_cu)
+        grad_b = _token_minor_wgrad(a_q, a_s, g_q, g_s, group_lens, group_offs, ctx.trans_b, ctx.out_dtype, gran, ctx.num_cu,
+                                    ctx.fuse, ctx.main_grad)
         return (grad_a, grad_b) + (None,) * 9
 
 
 class FP8GroupedGemmRowFunc(torch.autograd.Function):
+    """ROWWISE: scales along the contraction axis of every GEMM.  Follows FP8GroupedGemmRowFunc of the reference
+    (primus_turbo/pytorch/ops/grouped_gemm_fp8.py:259-446): the copies scaled along the other axis, which backward
+    needs, are made in forward and saved as FP8, so the high-precision activation is not kept alive."""
+
     @staticmethod
     def forward(ctx, a, b, a_t, b_t, group_lens, group_offs, trans_b, out_dtype, config, num_cu, fuse_bgrad_accum_pattern=None):
-        assert fuse_bgrad_accum_pattern is None, "fused main_grad accumulation: use BLOCKWISE or MX_BLOCKWISE"
-        assert trans_b, "rowwise grouped GEMM takes b as [G, N, K]"
+        fuse, main_grad = _setup_fused_grad_accum(b, fuse_bgrad_accum_pattern)
+        assert config.granularity == ScalingGranularity.ROWWISE
         fwd = _get_fp8_dtype(config.format, True)
-        a_q, a_s = quantize_fp8_rowwise_impl(a, fwd, -1)
-        b_q, b_s = quantize_fp8_rowwise_impl(b, fwd, -1)                     # [G, N, 1]
-        out = grouped_gemm_fp8_impl(a_q, b_q, a_s, b_s, group_lens, group_offs, False, True, out_dtype, config.granularity, num_cu)
-        ctx.save_for_backward(a, b, group_lens, group_offs)
-        ctx.config, ctx.out_dtype, ctx.num_cu = config, out_dtype, num_cu
+        b_row_axis, b_col_axis = (-1, -2) if trans_b else (-2, -1)
+        if isinstance(a, QuantizedTensor):
+            check_quantized_tensor(a, config, axis=-1)
+            a_q, a_s = a.qdata, a.scale_inv
+            a_hp = None if a_t is not None else a.dequantize()
+        else:
+            a_hp = a.contiguous()
+            a_q, a_s = quantize_fp8_rowwise_impl(a_hp, fwd, -1)
+        if isinstance(b, QuantizedTensor):
+            check_quantized_tensor(b, config, axis=b_row_axis)
+            b_q, b_s = b.qdata, b.scale_inv
+            b_hp = None if b_t is not None else b.dequantize()
+        else:
+            b_hp = b.contiguous()
+            b_q, b_s = quantize_fp8_rowwise_impl(b_hp, fwd, b_row_axis)      # scales [G, N, 1] or [G, 1, N]
+        b_km = b_q if trans_b else transpose_batched(b_q)                    # [G, N, K]
+        out = grouped_gemm_fp8_impl(a_q, b_km, a_s, b_s, group_lens, group_offs, False, True, out_dtype, config.granularity, num_cu)
+        # copies scaled along the other axis: a per feature over all tokens, b per K
+        if a_t is not None:
+            a_c_q, a_c_s = a_t.qdata, a_t.scale_inv
+        else:
+            a_c_q, a_c_s = quantize_fp8_rowwise_impl(a_hp, fwd, -2)          # [M, K], scales [1, K]
+        if b_t is not None:
+            b_c_q, b_c_s = b_t.qdata, b_t.scale_inv
+        else:
+            b_c_q, b_c_s = quantize_fp8_rowwise_impl(b_hp, fwd, b_col_axis)  # scales [G, 1, K] or [G, K, 1]
+        b_nm = transpose_batched(b_c_q) if trans_b else b_c_q                # [G, K, N]: dgrad contracts over N
+        ctx.save_for_backward(a_c_q, a_c_s, b_nm, b_c_s, group_lens, group_offs)
+        ctx.trans_b, ctx.config, ctx.out_dtype, ctx.num_cu = trans_b, config, out_dtype, num_cu
+        ctx.fuse, ctx.main_grad = fuse, main_grad
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        a, b, group_lens, group_offs = ctx.saved_tensors
+        a_c_q, a_c_s, b_nm, b_c_s, group_lens, group_offs = ctx.saved_tensors
         gran = ctx.config.granularity
-        fwd, gdt = _get_fp8_dtype(ctx.config.format, True), _get_fp8_dtype(ctx.config.format, False)
+        gdt = _get_fp8_dtype(ctx.config.format, False)
         grad_out = grad_out.contiguous()
         g_q, g_s = quantize_fp8_rowwise_impl(grad_out, gdt, -1)
-        b_t = b.transpose(1, 2).contiguous()                                 # [G, K, N], scaled along N for dgrad
-        b_t_q, b_t_s = quantize_fp8_rowwise_impl(b_t, fwd, -1)
-        grad_a = grouped_gemm_fp8_impl(g_q, b_t_q, g_s, b_t_s, group_lens, group_offs, False, True, ctx.out_dtype, gran, ctx.num_cu)
-        # wgrad: per group, both operands scaled along the token axis
-        lens = group_lens.tolist()
-        outs, start = [], 0
-        for n in lens:
-            if n == 0:
-                outs.append(torch.zeros(b.shape[1:], dtype=ctx.out_dtype, device=b.device))
-            else:
-                a_q, a_s = quantize_fp8_rowwise_impl(a[start:start + n].contiguous(), fwd, 0)
-                gg_q, gg_s = quantize_fp8_rowwise_impl(grad_out[start:start + n].contiguous(), gdt, 0)
-                outs.append(gemm_fp8_impl(a_q, a_s, True, gg_q, gg_s, False, ctx.out_dtype, True, gran))
-            start += n
-        return (grad_a, torch.stack(outs)) + (None,) * 9
+        grad_a = grouped_gemm_fp8_impl(g_q, b_nm, g_s, b_c_s, group_lens, group_offs, False, True, ctx.out_dtype, gran, ctx.num_cu)
+        g_c_q, g_c_s = quantize_fp8_rowwise_impl(grad_out, gdt, -2)          # [M, N], scales [1, N]
+        grad_b = _token_minor_wgrad(a_c_q, a_c_s, g_c_q, g_c_s, group_lens, group_offs, ctx.trans_b, ctx.out_dtype, gran,
+                                    ctx.num_cu, ctx.fuse, ctx.main_grad)
+        return (grad_a, grad_b) + (None,) * 9
 
 
 @torch._dynamo.disable(recursive=True)

@@ -180,3 +180,96 @@ def test_grouped_gemm_fp8_op(mods, gran, fmt, lens):
             assert float(b.grad[g].abs().max()) == 0.0
         elif n >= 64:
             assert snr(b.grad[g], b_ref.grad[g]) > gate_b
+
+
+@pytest.mark.parametrize("lens", LENS + [[64, 192, 1, 127, 129]])
+@pytest.mark.parametrize("C", [64, 200, 4096 + 16])
+def test_grouped_transpose_pad_is_exact(mods, lens, C):
+    """Token-major -> [features, padded tokens] copy: every group's rows land in its 128-aligned segment, all other
+    bytes are zero."""
+    qi = mods["qi"]
+    lens_t, offs = _offs(lens)
+    M, G = int(sum(lens)), len(lens)
+    x = torch.randint(0, 256, (M, C), dtype=torch.uint8, device="cuda")
+    plens, poffs = qi.compute_padded_group_offs(lens_t, 128)
+    y = qi.grouped_transpose_pad(x, offs, poffs)
+    T = (M + 127) // 128 * 128 + 128 * G
+    assert tuple(y.shape) == (C, T)
+    want = torch.zeros((C, T), dtype=torch.uint8, device="cuda")
+    po = poffs.cpu().tolist()
+    o = offs.cpu().tolist()
+    for g, n in enumerate(lens):
+        assert po[g] % 128 == 0
+        want[:, po[g]:po[g] + n] = x[o[g]:o[g] + n].t()
+    assert torch.equal(y, want)
+
+
+@pytest.mark.parametrize("shape", [(1, 64, 64), (3, 100, 72), (8, 384, 512)])
+@pytest.mark.parametrize("dtype", [torch.uint8, torch.bfloat16, torch.float32])
+def test_transpose_batched(mods, shape, dtype):
+    qi = mods["qi"]
+    x = torch.randint(0, 200, shape, device="cuda").to(dtype)
+    assert torch.equal(qi.transpose_batched(x), x.transpose(1, 2).contiguous())
+
+
+@pytest.mark.parametrize("gran", ["TENSORWISE", "ROWWISE"])
+@pytest.mark.parametrize("trans_b", [True, False])
+@pytest.mark.parametrize("lens", [[100, 0, 300, 29], [512] * 4])
+def test_grouped_tensor_row_no_host_sync_and_layouts(mods, gran, trans_b, lens):
+    """Tensorwise / rowwise grouped GEMM, both weight layouts, forward and backward with host synchronisation
+    forbidden: group lengths are never read on the host."""
+    turbo = mods["turbo"]
+    torch.manual_seed(11)
+    lens_t, offs = _offs(lens)
+    G, M, K, N = len(lens), int(sum(lens)), 256, 384
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    b = torch.randn((G, N, K) if trans_b else (G, K, N), device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    a_ref, b_ref = a.detach().clone().requires_grad_(), b.detach().clone().requires_grad_()
+    go = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    cfg = _cfg(mods, gran, "E4M3")
+    torch.cuda.synchronize()
+    torch.cuda.set_sync_debug_mode("error")
+    try:
+        out = turbo.ops.grouped_gemm_fp8(a, b, lens_t, group_offs=offs, trans_b=trans_b, config=cfg)
+        out.backward(go)
+    finally:
+        torch.cuda.set_sync_debug_mode("default")
+    o = offs.cpu().tolist()
+    ref = torch.cat([a_ref[o[g]:o[g + 1]].float() @ (b_ref[g].float().t() if trans_b else b_ref[g].float())
+                     for g in range(G)]).to(torch.bfloat16)
+    ref.backward(go)
+    assert b.grad.shape == b_ref.grad.shape
+    assert snr(out.detach(), ref.detach()) > 25
+    assert snr(a.grad, a_ref.grad) > 25
+    for g, n in enumerate(lens):
+        if n == 0:
+            assert float(b.grad[g].abs().max()) == 0.0
+        elif n >= 64:
+            assert snr(b.grad[g], b_ref.grad[g]) > 25
+
+
+@pytest.mark.parametrize("gran", ["TENSORWISE", "ROWWISE"])
+def test_grouped_tensor_row_fused_main_grad(mods, gran):
+    """fuse_bgrad_accum_pattern='megatron': the wgrad is added into b.main_grad in place."""
+    turbo = mods["turbo"]
+    torch.manual_seed(12)
+    lens = [200, 56, 0, 256]
+    lens_t, offs = _offs(lens)
+    G, M, K, N = len(lens), int(sum(lens)), 256, 128
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    b = torch.randn(G, N, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    go = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    cfg = _cfg(mods, gran, "E4M3")
+    out = turbo.ops.grouped_gemm_fp8(a, b, lens_t, trans_b=True, config=cfg)
+    out.backward(go)
+    plain = b.grad.float().clone()
+    b2 = b.detach().clone().requires_grad_()
+    base = torch.randn(G, N, K, device="cuda", dtype=torch.float32)
+    b2.main_grad = base.clone()
+    b2.grad_added_to_main_grad = False
+    a2 = a.detach().clone().requires_grad_()
+    out2 = turbo.ops.grouped_gemm_fp8(a2, b2, lens_t, trans_b=True, config=cfg, fuse_bgrad_accum_pattern="megatron")
+    out2.backward(go)
+    assert b2.grad_added_to_main_grad
+    got = b2.main_grad - base
+    assert snr(got, plain) > 40   # same products, fp32 accumulate vs bf16 rounding of the plain path
