@@ -24,10 +24,11 @@ def _norm_axis(axis, ndim):
 class QuantizedTensor(torch.Tensor):
     @staticmethod
     def __new__(cls, qdata, scale_inv, *, orig_dtype, orig_shape=None, granularity, axis=None, block_size=None,
-                scaling_recipe=None, group_lens=None, group_offs=None, requires_grad=False, shape=None,
-                dest_dtype=None, quantized_axis=None):
+                scaling_recipe=None, group_lens=None, group_offs=None, orig_group_lens=None, orig_group_offs=None,
+                is_grouped_tensor=None, requires_grad=False, shape=None, dest_dtype=None, quantized_axis=None):
         # `shape`, `dest_dtype`, `quantized_axis` are the reference's keyword names for orig_shape, the quantized
-        # dtype (always qdata.dtype here) and axis
+        # dtype (always qdata.dtype here) and axis.  A grouped tensor (MoE activations, groups along dim 0) carries
+        # the tight group_lens / offs of the source (orig_*) and those of its padded payload (group_*).
         orig_shape = torch.Size(orig_shape if orig_shape is not None else shape)
         if axis is None:
             axis = quantized_axis
@@ -40,6 +41,8 @@ class QuantizedTensor(torch.Tensor):
         self._block_size = block_size
         self._scaling_recipe = scaling_recipe
         self._group_lens, self._group_offs = group_lens, group_offs
+        self._orig_group_lens, self._orig_group_offs = orig_group_lens, orig_group_offs
+        self._is_grouped_tensor = bool(is_grouped_tensor) if is_grouped_tensor is not None else group_lens is not None
         return self
 
     def __init__(self, *args, **kwargs):
@@ -88,33 +91,78 @@ class QuantizedTensor(torch.Tensor):
     def group_offs(self):
         return self._group_offs
 
+    @property
+    def orig_group_lens(self):
+        return self._orig_group_lens
+
+    @property
+    def orig_group_offs(self):
+        return self._orig_group_offs
+
+    @property
+    def is_grouped_tensor(self):
+        return self._is_grouped_tensor
+
     def _like(self, qdata, scale_inv, shape, axis="same"):
         return QuantizedTensor(qdata, scale_inv, orig_dtype=self.dtype, orig_shape=shape, granularity=self._granularity,
                                axis=self._axis if axis == "same" else axis, block_size=self._block_size,
                                scaling_recipe=self._scaling_recipe, group_lens=self._group_lens,
-                               group_offs=self._group_offs, requires_grad=False)
+                               group_offs=self._group_offs, orig_group_lens=self._orig_group_lens,
+                               orig_group_offs=self._orig_group_offs, is_grouped_tensor=self._is_grouped_tensor,
+                               requires_grad=False)
 
     # ---- construction
     @classmethod
     def quantize(cls, x: torch.Tensor, dtype: torch.dtype, granularity: ScalingGranularity, *, axis: Optional[int] = None,
-                 block_size: Optional[int] = None, scaling_recipe: Optional[ScalingRecipe] = None) -> "QuantizedTensor":
-        from ..ops.quantization import quantize_fp4, quantize_fp8
+                 block_size: Optional[int] = None, scaling_recipe: Optional[ScalingRecipe] = None,
+                 group_lens: Optional[torch.Tensor] = None) -> "QuantizedTensor":
+        """With `group_lens` (int64 on the device) x is a grouped tensor [total_m, N].  Tensorwise / rowwise treat it
+        as one tensor and only record the groups; MX quantizes group by group into the padded layout the grouped
+        GEMMs read (primus_turbo/pytorch/core/quantized_tensor.py:300-343 of the reference)."""
+        from ..ops.quantization import grouped_quantize_fp4, grouped_quantize_fp8, quantize_fp4, quantize_fp8
         if granularity == ScalingGranularity.MX_BLOCKWISE and block_size is None:
             block_size = 32
-        fn = quantize_fp4 if is_fp4_dtype(dtype) else quantize_fp8
+        fp4 = is_fp4_dtype(dtype)
+        grouped = group_lens is not None
+        meta = {}
         with torch.no_grad():
-            q, s = fn(x, dtype, granularity, block_size=block_size, axis=axis, scaling_recipe=scaling_recipe)
+            if grouped:
+                from ..kernels.grouped_gemm.grouped_gemm_utils import group_offs_from_lens
+                assert group_lens.is_cuda, "group_lens must be on CUDA"
+                offs = group_offs_from_lens(group_lens)
+                meta = dict(orig_group_lens=group_lens, orig_group_offs=offs, is_grouped_tensor=True)
+            if grouped and granularity not in (ScalingGranularity.TENSORWISE, ScalingGranularity.ROWWISE):
+                fn = grouped_quantize_fp4 if fp4 else grouped_quantize_fp8
+                q, s, plens, poffs = fn(x, dtype, granularity, group_lens, offs, block_size=block_size, axis=axis,
+                                        scaling_recipe=scaling_recipe)
+                meta.update(group_lens=plens, group_offs=poffs)
+            else:
+                fn = quantize_fp4 if fp4 else quantize_fp8
+                q, s = fn(x, dtype, granularity, block_size=block_size, axis=axis, scaling_recipe=scaling_recipe)
+                if grouped:
+                    meta.update(group_lens=group_lens, group_offs=offs)
         return cls(q, s, orig_dtype=x.dtype, orig_shape=x.shape, granularity=granularity, axis=axis,
-                   block_size=block_size, scaling_recipe=scaling_recipe)
+                   block_size=block_size, scaling_recipe=scaling_recipe, **meta)
 
     def dequantize(self, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        from ..ops.quantization import dequantize_fp4, dequantize_fp8
+        from ..ops.quantization import dequantize_fp4, dequantize_fp8, grouped_dequantize_fp4, grouped_dequantize_fp8
         dtype = dtype or self.dtype
-        fn = dequantize_fp4 if is_fp4_dtype(self._qdata.dtype) else dequantize_fp8
+        fp4 = is_fp4_dtype(self._qdata.dtype)
+        mx = self._granularity == ScalingGranularity.MX_BLOCKWISE
         with torch.no_grad():
-            y = fn(self._qdata, dtype, self._granularity, block_size=self._block_size, axis=self._axis,
-                   scale_inv=self._scale_inv, scaling_recipe=self._scaling_recipe)
-        if self._granularity == ScalingGranularity.MX_BLOCKWISE:  # drop the 128-padding
+            if self._is_grouped_tensor and mx and not fp4:
+                y = grouped_dequantize_fp8(self._qdata, dtype, self._granularity, self._orig_group_offs, self._group_offs,
+                                           block_size=self._block_size, axis=self._axis, scale_inv=self._scale_inv,
+                                           scaling_recipe=self._scaling_recipe, total_M=self.shape[0])
+            elif self._is_grouped_tensor and mx:
+                assert self._axis == self.dim() - 1, "grouped FP4 dequantization is row-wise only"
+                y = grouped_dequantize_fp4(self._qdata, dtype, self._granularity, block_size=self._block_size,
+                                           axis=self._axis, scale_inv=self._scale_inv, scaling_recipe=self._scaling_recipe)
+            else:
+                fn = dequantize_fp4 if fp4 else dequantize_fp8
+                y = fn(self._qdata, dtype, self._granularity, block_size=self._block_size, axis=self._axis,
+                       scale_inv=self._scale_inv, scaling_recipe=self._scaling_recipe)
+        if mx:  # drop the 128-padding
             y = y[..., : self.shape[-2], : self.shape[-1]]
         return y
 
@@ -134,8 +182,12 @@ class QuantizedTensor(torch.Tensor):
             inner.append("_group_lens")
         if self._group_offs is not None:
             inner.append("_group_offs")
+        if self._orig_group_lens is not None:
+            inner.append("_orig_group_lens")
+        if self._orig_group_offs is not None:
+            inner.append("_orig_group_offs")
         meta = dict(granularity=self._granularity, axis=self._axis, block_size=self._block_size,
-                    scaling_recipe=self._scaling_recipe, orig_dtype=self.dtype)
+                    scaling_recipe=self._scaling_recipe, orig_dtype=self.dtype, is_grouped_tensor=self._is_grouped_tensor)
         return inner, meta
 
     @staticmethod
@@ -143,7 +195,10 @@ class QuantizedTensor(torch.Tensor):
         return QuantizedTensor(inner_tensors["_qdata"], inner_tensors["_scale_inv"], orig_dtype=meta["orig_dtype"],
                                orig_shape=outer_size, granularity=meta["granularity"], axis=meta["axis"],
                                block_size=meta["block_size"], scaling_recipe=meta["scaling_recipe"],
-                               group_lens=inner_tensors.get("_group_lens"), group_offs=inner_tensors.get("_group_offs"))
+                               group_lens=inner_tensors.get("_group_lens"), group_offs=inner_tensors.get("_group_offs"),
+                               orig_group_lens=inner_tensors.get("_orig_group_lens"),
+                               orig_group_offs=inner_tensors.get("_orig_group_offs"),
+                               is_grouped_tensor=meta.get("is_grouped_tensor"))
 
     # ---- view-like operations that keep the quantization valid
     def _reshaped(self, shape, op):

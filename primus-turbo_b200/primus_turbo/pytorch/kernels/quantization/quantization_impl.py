@@ -442,3 +442,30 @@ def grouped_quantize_mxfp4_impl(x, out_dtype, axis, block_size, group_lens, grou
     """As the fp8 form with packed e2m1; the row copy is tight (row i = input row i)."""
     return _grouped_quantize_mx_impl(x, out_dtype, axis, block_size, group_lens, group_offs, with_trans, scaling_recipe,
                                      scaling_recipe_for_trans)
+
+
+def _tight_row_index(group_offs, group_offs_padded, total_M, device):
+    """For every row r of the tight (un-padded) layout, the row of the padded layout that holds it; built on the
+    device from the two offset arrays."""
+    offs = group_offs.to(torch.int64)
+    r = torch.arange(total_M, dtype=torch.int64, device=device)
+    g = torch.searchsorted(offs[1:].contiguous(), r, right=True).clamp_(max=offs.numel() - 2)
+    return group_offs_padded.to(torch.int64)[g] + (r - offs[g])
+
+
+def grouped_dequantize_mxfp8_impl(x: torch.Tensor, out_dtype: torch.dtype, axis: int, block_size: int, scale_inv: torch.Tensor,
+                                  group_offs: torch.Tensor, group_offs_padded: torch.Tensor,
+                                  total_M: Optional[int] = None) -> torch.Tensor:
+    """Undoes grouped_quantize_mxfp8_impl: x is the row-wise copy [M_pad, N] (axis 1) or the column-wise, transposed copy
+    [N, M_pad] (axis 0), both with per-group padded token segments at `group_offs_padded`; returns the tight
+    [total_M, N] tensor.  Same call shape as the reference (kernels/quantization/quantization_impl.py:838-865); like
+    there, total_M = None costs a host read of group_offs[-1]."""
+    nv.require_cuda(x, scale_inv, group_offs, group_offs_padded)
+    assert block_size == MX_BLOCK
+    assert x.dim() == 2 and scale_inv.dim() == 2 and axis in (0, 1)
+    assert out_dtype in (torch.float16, torch.bfloat16, torch.float32)
+    if total_M is None:
+        total_M = int(group_offs[-1].item())
+    padded = _dequantize_mx(x, out_dtype, axis, scale_inv)      # [M_pad, N(_pad)] in the original orientation
+    idx = _tight_row_index(group_offs, group_offs_padded, total_M, x.device)
+    return padded.index_select(0, idx)

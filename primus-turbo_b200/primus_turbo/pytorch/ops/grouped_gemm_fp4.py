@@ -5,7 +5,7 @@ from typing import Optional, Union
 import torch
 
 from ..core.low_precision import MXFP4_BLOCK_SIZE, Float4QuantConfig, ScalingGranularity, ScalingRecipe, float4_e2m1fn_x2
-from ..core.quantized_tensor import QuantizedTensor, QuantizedTensorPair
+from ..core.quantized_tensor import QuantizedTensor, QuantizedTensorPair, check_quantized_tensor
 from ..kernels.grouped_gemm.grouped_gemm_fp4_impl import (grouped_gemm_fp4_impl, grouped_gemm_fp4_variable_k_accum_impl,
                                                           grouped_gemm_fp4_variable_k_impl)
 from ..kernels.grouped_gemm.grouped_gemm_utils import group_offs_from_lens
@@ -23,18 +23,32 @@ class FP4GroupedGemmMXFunc(torch.autograd.Function):
         assert a.dim() == 2 and b.dim() == 3
         assert out_dtype in (torch.float16, torch.bfloat16)
         assert trans_b, "MXFP4 grouped GEMM only supports trans_b=True (NT layout)."
-        if isinstance(a, QuantizedTensor) or isinstance(b, QuantizedTensor):
-            raise NotImplementedError("pre-quantized grouped MXFP4 operands are not supported yet")
         N, K = int(b.shape[-2]), int(b.shape[-1])
         assert K % MXFP4_BLOCK_SIZE == 0, f"K must be a multiple of {MXFP4_BLOCK_SIZE} (got {K})."
         assert N % MXFP4_BLOCK_SIZE == 0, f"N must be a multiple of {MXFP4_BLOCK_SIZE} (got {N})."
         total_m = int(a.size(0))
-        a_row, a_row_s, a_col, a_col_s, _, offs_row, _, _ = grouped_quantize_mxfp4_impl(
-            a, float4_e2m1fn_x2, None, MXFP4_BLOCK_SIZE, group_lens, group_offs, with_trans=True,
-            scaling_recipe=ScalingRecipe(), scaling_recipe_for_trans=ScalingRecipe(use_rht=True))
-        two_d = ScalingRecipe(use_2d_block=True)
-        b_row, b_row_s, b_col, b_col_s = quantize_mxfp4_impl(b, float4_e2m1fn_x2, None, MXFP4_BLOCK_SIZE, with_trans=True,
-                                                             scaling_recipe=two_d, scaling_recipe_for_trans=two_d)
+        plain, rht, two_d = ScalingRecipe(), ScalingRecipe(use_rht=True), ScalingRecipe(use_2d_block=True)
+        if not isinstance(a, QuantizedTensor):
+            a_row, a_row_s, a_col, a_col_s, _, offs_row, _, _ = grouped_quantize_mxfp4_impl(
+                a, float4_e2m1fn_x2, None, MXFP4_BLOCK_SIZE, group_lens, group_offs, with_trans=True,
+                scaling_recipe=plain, scaling_recipe_for_trans=rht)
+        else:
+            # pre-quantized row-wise grouped activation; the column-wise (Hadamard-rotated) copy comes from a_t or from
+            # re-quantizing the dequantized values (ops/grouped_gemm_fp4.py:156-174 of the reference)
+            check_quantized_tensor(a, config, axis=-1, scaling_recipe=plain)
+            a_tq = a_t if a_t is not None else QuantizedTensor.quantize(
+                a.dequantize(), a.real_dtype, config.granularity, axis=-2, block_size=config.block_size, scaling_recipe=rht,
+                group_lens=group_lens)
+            a_row, a_row_s, a_col, a_col_s = a.qdata, a.scale_inv, a_tq.qdata, a_tq.scale_inv
+            offs_row = a.group_offs
+        if not isinstance(b, QuantizedTensor):
+            b_row, b_row_s, b_col, b_col_s = quantize_mxfp4_impl(b, float4_e2m1fn_x2, None, MXFP4_BLOCK_SIZE, with_trans=True,
+                                                                 scaling_recipe=two_d, scaling_recipe_for_trans=two_d)
+        else:
+            check_quantized_tensor(b, config, axis=-1, scaling_recipe=two_d)
+            b_tq = b_t if b_t is not None else QuantizedTensor.quantize(
+                b.dequantize(), b.real_dtype, config.granularity, axis=-2, block_size=config.block_size, scaling_recipe=two_d)
+            b_row, b_row_s, b_col, b_col_s = b.qdata, b.scale_inv, b_tq.qdata, b_tq.scale_inv
         out = grouped_gemm_fp4_impl(a_row, b_row, a_row_s, b_row_s, group_lens, offs_row, out_dtype=out_dtype, num_cu=num_cu,
                                     group_offs_out=group_offs)[:total_m]
         ctx.save_for_backward(a_col, a_col_s, b_col, b_col_s, group_lens, group_offs)

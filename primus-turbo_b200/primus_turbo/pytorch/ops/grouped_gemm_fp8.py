@@ -85,15 +85,30 @@ class FP8GroupedGemmMXFunc(torch.autograd.Function):
         assert config.granularity == ScalingGranularity.MX_BLOCKWISE
         assert a.dim() == 2 and b.dim() == 3
         assert trans_b, "MXFP8 grouped GEMM only supports trans_b=True (NT layout)."
-        if isinstance(a, QuantizedTensor) or isinstance(b, QuantizedTensor):
-            raise NotImplementedError("pre-quantized grouped MX operands are not supported yet")
         fp8_dtype = _get_fp8_dtype(config.format, True)
         bs = config.block_size
-        a_row, a_s_row, a_col, a_s_col, _, offs_pad_row, _, _ = grouped_quantize_mxfp8_impl(
-            a, fp8_dtype, None, bs, group_lens, group_offs, with_trans=True)
-        two_d = ScalingRecipe(use_2d_block=True)
-        b_row, b_s_row, b_col, b_s_col = quantize_mxfp8_impl(b, fp8_dtype, None, bs, with_trans=True, scaling_recipe=two_d,
-                                                             scaling_recipe_for_trans=two_d)
+        one_d, two_d = ScalingRecipe(), ScalingRecipe(use_2d_block=True)
+        if not isinstance(a, QuantizedTensor):
+            a_row, a_s_row, a_col, a_s_col, _, offs_pad_row, _, _ = grouped_quantize_mxfp8_impl(
+                a, fp8_dtype, None, bs, group_lens, group_offs, with_trans=True)
+        else:
+            # pre-quantized row-wise grouped activation; the column-wise copy comes from a_t or from re-quantizing
+            # the dequantized values, as the reference does (ops/grouped_gemm_fp8.py:663-687)
+            check_quantized_tensor(a, config, axis=-1, scaling_recipe=one_d)
+            assert a.is_grouped_tensor, "A QuantizedTensor input must be a grouped tensor"
+            a_tq = a_t if a_t is not None else QuantizedTensor.quantize(
+                a.dequantize(), a.real_dtype, config.granularity, axis=-2, block_size=bs, scaling_recipe=one_d,
+                group_lens=group_lens)
+            a_row, a_s_row, a_col, a_s_col = a.qdata, a.scale_inv, a_tq.qdata, a_tq.scale_inv
+            offs_pad_row = a.group_offs
+        if not isinstance(b, QuantizedTensor):
+            b_row, b_s_row, b_col, b_s_col = quantize_mxfp8_impl(b, fp8_dtype, None, bs, with_trans=True, scaling_recipe=two_d,
+                                                                 scaling_recipe_for_trans=two_d)
+        else:
+            check_quantized_tensor(b, config, axis=-1, scaling_recipe=two_d)
+            b_tq = b_t if b_t is not None else QuantizedTensor.quantize(
+                b.dequantize(), b.real_dtype, config.granularity, axis=-2, block_size=bs, scaling_recipe=two_d)
+            b_row, b_s_row, b_col, b_s_col = b.qdata, b.scale_inv, b_tq.qdata, b_tq.scale_inv
         total_m = int(a.size(0))
         out = grouped_gemm_fp8_impl(a_row, b_row, a_s_row, b_s_row, group_lens, offs_pad_row, False, True, out_dtype,
                                     ScalingGranularity.MX_BLOCKWISE, num_cu, group_offs_out=group_offs)[:total_m]

@@ -2,7 +2,9 @@
 
 Signatures and return layouts follow primus_turbo/pytorch/ops/quantization.py of the reference
 (quantize_fp8 :52, quantize_fp8_with_trans :103, dequantize_fp8 :225, quantize_fp4 :299,
-quantize_fp4_with_trans :446, dequantize_fp4 :486).
+quantize_fp4_with_trans :446, dequantize_fp4 :486; grouped forms: grouped_quantize_fp8 :144,
+grouped_quantize_fp8_with_trans :182, grouped_dequantize_fp8 :272, grouped_quantize_fp4 :340,
+grouped_quantize_fp4_with_trans :390, grouped_dequantize_fp4 :519).
 """
 from typing import Optional, Tuple
 
@@ -12,13 +14,16 @@ from ..core.low_precision import MXFP4_BLOCK_SIZE, MXFP8_BLOCK_SIZE, ScalingGran
 from ..kernels.quantization.quantization_impl import (dequant_fp8_blockwise_for_weight_impl, dequant_fp8_blockwise_impl,
                                                       dequantize_fp8_rowwise_impl, dequantize_fp8_tensorwise_impl,
                                                       dequantize_mxfp4_impl, dequantize_mxfp8_impl,
+                                                      grouped_dequantize_mxfp8_impl, grouped_quantize_mxfp4_impl,
+                                                      grouped_quantize_mxfp8_impl,
                                                       quant_fp8_blockwise_dual_impl, quant_fp8_blockwise_for_weight_impl,
                                                       quant_fp8_blockwise_impl, quantize_fp8_rowwise_impl,
                                                       quantize_fp8_tensorwise_impl, quantize_mxfp4_impl,
                                                       quantize_mxfp8_impl)
 
 __all__ = ["quantize_fp8", "quantize_fp8_with_trans", "dequantize_fp8", "quantize_fp4", "quantize_fp4_with_trans",
-           "dequantize_fp4"]
+           "dequantize_fp4", "grouped_quantize_fp8", "grouped_quantize_fp8_with_trans", "grouped_dequantize_fp8",
+           "grouped_quantize_fp4", "grouped_quantize_fp4_with_trans", "grouped_dequantize_fp4"]
 
 
 def _mx_axis(x, axis):
@@ -107,3 +112,78 @@ def dequantize_fp4(x: torch.Tensor, out_dtype: torch.dtype, granularity: Scaling
         raise NotImplementedError(f"Unknown granularity {granularity}")
     assert block_size == MXFP4_BLOCK_SIZE, f"The block size must be {MXFP4_BLOCK_SIZE} for MXFP4 quantization"
     return dequantize_mxfp4_impl(x, out_dtype, _mx_axis(x, axis), block_size, scale_inv)
+
+
+# ------------------------------------------------------------------------------ grouped (MoE activations)
+def grouped_quantize_fp8(x: torch.Tensor, out_dtype: torch.dtype, granularity: ScalingGranularity, group_lens: torch.Tensor,
+                         group_offs: torch.Tensor, *, block_size: Optional[int] = None, axis: Optional[int] = None,
+                         scaling_recipe: Optional[ScalingRecipe] = None):
+    """x [total_m, N] grouped along M.  Returns (data, scale_inv, group_lens_padded, group_offs_padded): the row-wise
+    copy (axis 1, groups padded to 32 rows) or the column-wise, transposed copy (axis 0, groups padded to 128)."""
+    if granularity == ScalingGranularity.MX_BLOCKWISE:
+        assert block_size == MXFP8_BLOCK_SIZE, f"The block size must be {MXFP8_BLOCK_SIZE} for MXFP8 quantization"
+        return grouped_quantize_mxfp8_impl(x, out_dtype, _mx_axis(x, axis), block_size, group_lens, group_offs, False,
+                                           scaling_recipe)
+    raise NotImplementedError(f"Unknown granularity {granularity}")
+
+
+def grouped_quantize_fp8_with_trans(x: torch.Tensor, out_dtype: torch.dtype, granularity: ScalingGranularity,
+                                    group_lens: torch.Tensor, group_offs: torch.Tensor, *, block_size: Optional[int] = None,
+                                    scaling_recipe: Optional[ScalingRecipe] = None,
+                                    scaling_recipe_for_trans: Optional[ScalingRecipe] = None):
+    """Both copies from one read of x: (x_row, scale_row, x_col, scale_col, group_lens_padded_row,
+    group_offs_padded_row, group_lens_padded_col, group_offs_padded_col)."""
+    if granularity == ScalingGranularity.MX_BLOCKWISE:
+        assert block_size == MXFP8_BLOCK_SIZE, f"The block size must be {MXFP8_BLOCK_SIZE} for MXFP8 quantization"
+        return grouped_quantize_mxfp8_impl(x, out_dtype, None, block_size, group_lens, group_offs, True, scaling_recipe,
+                                           scaling_recipe_for_trans)
+    raise NotImplementedError(f"Unknown granularity {granularity}")
+
+
+def grouped_dequantize_fp8(x: torch.Tensor, out_dtype: torch.dtype, granularity: ScalingGranularity, group_offs: torch.Tensor,
+                           group_offs_padded: torch.Tensor, *, block_size: Optional[int] = None, axis: Optional[int] = None,
+                           scale_inv: torch.Tensor, scaling_recipe: Optional[ScalingRecipe] = None,
+                           total_M: Optional[int] = None) -> torch.Tensor:
+    if granularity == ScalingGranularity.MX_BLOCKWISE:
+        assert block_size == MXFP8_BLOCK_SIZE, f"The block size must be {MXFP8_BLOCK_SIZE} for MXFP8 quantization"
+        return grouped_dequantize_mxfp8_impl(x, out_dtype, _mx_axis(x, axis), block_size, scale_inv, group_offs,
+                                             group_offs_padded, total_M)
+    raise NotImplementedError(f"Unknown granularity {granularity}")
+
+
+def grouped_quantize_fp4(x: torch.Tensor, out_dtype: torch.dtype, granularity: ScalingGranularity, group_lens: torch.Tensor,
+                         group_offs: torch.Tensor, *, block_size: Optional[int] = None, axis: Optional[int] = None,
+                         scaling_recipe: Optional[ScalingRecipe] = None):
+    """As grouped_quantize_fp8 with packed e2m1: the row-wise copy is tight (row i = input row i), the column-wise
+    copy pads each group's tokens for the variable-K GEMM."""
+    assert out_dtype == torch.float4_e2m1fn_x2, "The out_dtype must be float4_e2m1fn_x2 for MXFP4 quantization"
+    if granularity == ScalingGranularity.MX_BLOCKWISE:
+        assert block_size == MXFP4_BLOCK_SIZE, f"The block size must be {MXFP4_BLOCK_SIZE} for MXFP4 quantization"
+        assert x.ndim == 2, "grouped MXFP4 quantize expects a 2D packed-M tensor"
+        axis = _mx_axis(x, axis)
+        assert axis in (0, 1), "axis must be 0 (colwise) or 1 (rowwise) for grouped MXFP4"
+        return grouped_quantize_mxfp4_impl(x, out_dtype, axis, block_size, group_lens, group_offs, False, scaling_recipe)
+    raise NotImplementedError(f"Unknown granularity {granularity}")
+
+
+def grouped_quantize_fp4_with_trans(x: torch.Tensor, out_dtype: torch.dtype, granularity: ScalingGranularity,
+                                    group_lens: torch.Tensor, group_offs: torch.Tensor, *, block_size: Optional[int] = None,
+                                    scaling_recipe: Optional[ScalingRecipe] = None,
+                                    scaling_recipe_for_trans: Optional[ScalingRecipe] = None):
+    assert out_dtype == torch.float4_e2m1fn_x2, "The out_dtype must be float4_e2m1fn_x2 for MXFP4 quantization"
+    if granularity == ScalingGranularity.MX_BLOCKWISE:
+        assert block_size == MXFP4_BLOCK_SIZE, f"The block size must be {MXFP4_BLOCK_SIZE} for MXFP4 quantization"
+        assert x.ndim == 2, "grouped MXFP4 quantize expects a 2D packed-M tensor"
+        return grouped_quantize_mxfp4_impl(x, out_dtype, None, block_size, group_lens, group_offs, True, scaling_recipe,
+                                           scaling_recipe_for_trans)
+    raise NotImplementedError(f"Unknown granularity {granularity}")
+
+
+def grouped_dequantize_fp4(x: torch.Tensor, out_dtype: torch.dtype, granularity: ScalingGranularity, *,
+                           block_size: Optional[int] = None, axis: Optional[int] = None, scale_inv: torch.Tensor,
+                           scaling_recipe: Optional[ScalingRecipe] = None) -> torch.Tensor:
+    """Row-wise only: the grouped FP4 row copy is tight, so this is the plain dequantizer."""
+    if granularity == ScalingGranularity.MX_BLOCKWISE:
+        assert block_size == MXFP4_BLOCK_SIZE, f"The block size must be {MXFP4_BLOCK_SIZE} for MXFP4 quantization"
+        return dequantize_mxfp4_impl(x, out_dtype, _mx_axis(x, axis), block_size, scale_inv)
+    raise NotImplementedError(f"Unknown granularity {granularity}")

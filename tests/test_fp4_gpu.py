@@ -127,3 +127,34 @@ def test_grouped_gemm_fp4_op(m, lens):
             assert float(b.grad[g].abs().max()) == 0.0
         elif n >= 64:
             assert snr(b.grad[g], b_ref.grad[g]) > 8
+
+
+def test_grouped_gemm_fp4_prequantized_operands(m):
+    """grouped_gemm_fp4 with QuantizedTensor inputs: same forward bits as quantizing inside the operator; the
+    column-wise copies for backward are rebuilt from the dequantized values."""
+    from primus_turbo.pytorch.core.low_precision import ScalingGranularity, ScalingRecipe
+    from primus_turbo.pytorch.core.quantized_tensor import QuantizedTensor
+    turbo = m["turbo"]
+    torch.manual_seed(8)
+    lens = [200, 0, 312, 128]
+    lens_t = torch.tensor(lens, dtype=torch.int64, device="cuda")
+    offs = [0] + list(np.cumsum(lens))
+    G, M, K, N = len(lens), int(sum(lens)), 256, 384
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(G, N, K, device="cuda", dtype=torch.bfloat16)
+    plain = turbo.ops.grouped_gemm_fp4(a, b, lens_t, trans_b=True)
+    a_q = QuantizedTensor.quantize(a, torch.float4_e2m1fn_x2, ScalingGranularity.MX_BLOCKWISE, axis=-1, block_size=32,
+                                   scaling_recipe=ScalingRecipe(), group_lens=lens_t).requires_grad_()
+    b_q = QuantizedTensor.quantize(b, torch.float4_e2m1fn_x2, ScalingGranularity.MX_BLOCKWISE, axis=-1, block_size=32,
+                                   scaling_recipe=ScalingRecipe(use_2d_block=True)).requires_grad_()
+    out = turbo.ops.grouped_gemm_fp4(a_q, b_q, lens_t, trans_b=True)
+    assert torch.equal(out, plain)
+    go = torch.randn_like(out)
+    out.backward(go)
+    a_ref, b_ref = a.clone().requires_grad_(), b.clone().requires_grad_()
+    ref = torch.cat([a_ref[offs[g]:offs[g + 1]].float() @ b_ref[g].float().t() for g in range(G)]).to(torch.bfloat16)
+    ref.backward(go)
+    assert snr(a_q.grad, a_ref.grad) > 6
+    for g, n in enumerate(lens):
+        if n >= 64:
+            assert snr(b_q.grad[g], b_ref.grad[g]) > 6

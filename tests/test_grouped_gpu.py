@@ -273,3 +273,67 @@ def test_grouped_tensor_row_fused_main_grad(mods, gran):
     assert b2.grad_added_to_main_grad
     got = b2.main_grad - base
     assert snr(got, plain) > 40   # same products, fp32 accumulate vs bf16 rounding of the plain path
+
+
+@pytest.mark.parametrize("dtype", [torch.float8_e4m3fn, torch.float4_e2m1fn_x2])
+@pytest.mark.parametrize("lens", [[100, 0, 128, 29], [256, 256]])
+def test_grouped_quantized_tensor_roundtrip(mods, dtype, lens):
+    """QuantizedTensor.quantize(group_lens=...) produces the grouped payload of the grouped quantizers, and
+    dequantize() brings back the tight [total_m, N] tensor."""
+    from primus_turbo.pytorch.core.quantized_tensor import QuantizedTensor
+    qi, SG = mods["qi"], mods["SG"]
+    lens_t, offs = _offs(lens)
+    M, N = int(sum(lens)), 160
+    x = make((M, N), torch.bfloat16, 52, "normal")
+    impl = qi.grouped_quantize_mxfp4_impl if dtype == torch.float4_e2m1fn_x2 else qi.grouped_quantize_mxfp8_impl
+    axes = (-1,) if dtype == torch.float4_e2m1fn_x2 else (-1, -2)
+    for axis in axes:
+        qt = QuantizedTensor.quantize(x, dtype, SG.MX_BLOCKWISE, axis=axis, block_size=32, group_lens=lens_t)
+        assert qt.is_grouped_tensor and tuple(qt.shape) == (M, N)
+        q, s, plens, poffs = impl(x, dtype, 1 if axis == -1 else 0, 32, lens_t, offs, with_trans=False)
+        assert torch.equal(qt.group_offs, poffs) and torch.equal(qt.orig_group_offs, offs)
+        back = qt.dequantize()
+        assert tuple(back.shape) == (M, N)
+        step = 0.25 if dtype == torch.float4_e2m1fn_x2 else 0.0625   # half a mantissa step at the block's top binade, x2
+        blk = x.float().abs().amax().item()
+        assert float((back.float() - x.float()).abs().max()) <= 2 * step * blk
+        # group by group against the dense dequantizer on the same rows
+        o = offs.cpu().tolist()
+        for g, n in enumerate(lens):
+            if n == 0:
+                continue
+            seg = x[o[g]:o[g] + n].contiguous()
+            dense = QuantizedTensor.quantize(seg, dtype, SG.MX_BLOCKWISE, axis=axis, block_size=32).dequantize()
+            assert torch.equal(back[o[g]:o[g] + n], dense), f"group {g} axis {axis}"
+
+
+def test_grouped_mx_gemm_prequantized_operands(mods):
+    """grouped_gemm_fp8 (MX) with QuantizedTensor inputs: the forward is bit-identical to the path that quantizes
+    inside the operator; backward passes the same gates."""
+    from primus_turbo.pytorch.core.quantized_tensor import QuantizedTensor
+    turbo, SG, SR = mods["turbo"], mods["SG"], mods["SR"]
+    torch.manual_seed(5)
+    lens = [200, 0, 312, 128]
+    lens_t, offs = _offs(lens)
+    G, M, K, N = len(lens), int(sum(lens)), 256, 384
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    b = torch.randn(G, N, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    cfg = _cfg(mods, "MX_BLOCKWISE", "E4M3")
+    plain = turbo.ops.grouped_gemm_fp8(a, b, lens_t, trans_b=True, config=cfg)
+    a_q = QuantizedTensor.quantize(a.detach(), torch.float8_e4m3fn, SG.MX_BLOCKWISE, axis=-1, block_size=32, group_lens=lens_t)
+    b_q = QuantizedTensor.quantize(b.detach(), torch.float8_e4m3fn, SG.MX_BLOCKWISE, axis=-1, block_size=32,
+                                   scaling_recipe=SR(use_2d_block=True))
+    a_q.requires_grad_()
+    b_q.requires_grad_()
+    out = turbo.ops.grouped_gemm_fp8(a_q, b_q, lens_t, trans_b=True, config=cfg)
+    assert torch.equal(out, plain)
+    go = torch.randn_like(out)
+    out.backward(go)
+    o = offs.cpu().tolist()
+    a_ref, b_ref = a.detach().clone().requires_grad_(), b.detach().clone().requires_grad_()
+    ref = torch.cat([a_ref[o[g]:o[g + 1]].float() @ b_ref[g].float().t() for g in range(G)]).to(torch.bfloat16)
+    ref.backward(go)
+    assert snr(a_q.grad, a_ref.grad) > 20
+    for g, n in enumerate(lens):
+        if n >= 64:
+            assert snr(b_q.grad[g], b_ref.grad[g]) > 20
