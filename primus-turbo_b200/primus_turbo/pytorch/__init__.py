@@ -3,5 +3,5 @@ from .. import _clib
 
 _clib.load()  # fail at import, loudly, when the CUDA library is absent
 
-from . import ops  # noqa: E402,F401
+from . import modules, ops  # noqa: E402,F401
 from .core.low_precision import float4_e2m1fn_x2, float8_e4m3, float8_e5m2  # noqa: E402,F401

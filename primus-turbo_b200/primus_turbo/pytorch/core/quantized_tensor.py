@@ -8,7 +8,7 @@ for FSDP / torch.compile.  View-like operations are answered without dequantizin
 (detach / alias / clone always; view / reshape when the scaled trailing dimensions are untouched; t / transpose
 for tensorwise scaling, whose single scale survives a transpose).
 """
-from typing import NamedTuple, Optional
+from typing import NamedTuple, Optional, Tuple, Union
 
 import torch
 
@@ -273,3 +273,35 @@ def check_quantized_tensor(t: QuantizedTensor, config, axis: Optional[int] = Non
         raise ValueError(f"axis mismatch: tensor quantized along {t.axis}, GEMM needs {_norm_axis(axis, t.dim())}")
     if scaling_recipe is not None and (t.scaling_recipe or ScalingRecipe()) != scaling_recipe:
         raise ValueError(f"scaling recipe mismatch: tensor {t.scaling_recipe} vs required {scaling_recipe}")
+
+
+def create_quantized_weight(weight: torch.Tensor, dest_dtype: torch.dtype,
+                            quant_config: Union[Float4QuantConfig, Float8QuantConfig],
+                            need_weight_transpose_cache: bool = False) -> Tuple[QuantizedTensor, Optional[QuantizedTensor]]:
+    """Quantizes a weight ([N, K] or [G, N, K]) once so that GEMM calls can reuse it: returns (weight_q, weight_q_t) where
+    weight_q is what the forward GEMM reads and weight_q_t the copy backward needs (None unless asked for).  Same call as
+    create_quantized_weight of the reference (primus_turbo/pytorch/core/quantized_tensor.py:897-956): 2-D block scales
+    for BLOCKWISE / MX weights and FP4, plain scales otherwise.  weight_q_t per recipe: TENSORWISE the lazily transposed
+    view (2-D weights; the single scale survives a transpose); ROWWISE the weight scaled along its other axis in the
+    same layout, which is the operand FP8GemmRowFunction / FP8GroupedGemmRowFunc take as `b_t`; BLOCKWISE / MX the
+    quantization along axis -2."""
+    if isinstance(quant_config, Float4QuantConfig):
+        if getattr(quant_config, "use_preshuffle", False):
+            raise NotImplementedError("pre-shuffled weight layouts are not provided on B200")
+        recipe = ScalingRecipe(use_2d_block=True)
+    elif quant_config.granularity in (ScalingGranularity.BLOCKWISE, ScalingGranularity.MX_BLOCKWISE):
+        recipe = ScalingRecipe(use_2d_block=True)
+    else:
+        recipe = ScalingRecipe()
+    gran, bs = quant_config.granularity, quant_config.block_size
+    weight = weight.detach()
+    qw = QuantizedTensor.quantize(weight, dest_dtype, gran, axis=-1, block_size=bs, scaling_recipe=recipe)
+    qw_t = None
+    if need_weight_transpose_cache:
+        if gran == ScalingGranularity.TENSORWISE:
+            qw_t = qw.transpose(-2, -1) if weight.dim() == 2 else None
+        elif gran in (ScalingGranularity.ROWWISE, ScalingGranularity.BLOCKWISE, ScalingGranularity.MX_BLOCKWISE):
+            qw_t = QuantizedTensor.quantize(weight, dest_dtype, gran, axis=-2, block_size=bs, scaling_recipe=recipe)
+        else:
+            raise ValueError(f"Unsupported granularity: {gran}")
+    return qw, qw_t
