@@ -401,7 +401,19 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
         const int r_row = tid >> 1, r_blk = tid & 1;
         // col-wise work item: two adjacent columns x 16 rows per thread; lanes 2i, 2i+1 share a 32-row block
         const int cw = warp - 1;
-        const int c_half = lane & 1, c_pair = ((cw & 1) << 4) | (lane >> 1), c_band = cw >> 1;
+        // Two lane layouts.  kWide (no Hadamard transform): a warp owns four column pairs over all 128 rows, lane =
+        // (band, half, pair); the eight (band, half) lanes of a column store 8 x 16 = 128 contiguous bytes of the
+        // transposed output and its four scale bytes leave as one word.  Their rows are 16 apart (same swizzle phase,
+        // same banks), so lane group k = lane / 4 walks its 16 rows in the order r ^ k: eight different phases, no
+        // bank conflict; the bytes are put back in order after the convert.  Otherwise (the transform needs the rows in
+        // order): a warp owns 16 column pairs of one 32-row band, lanes 2i, 2i+1 hold its two halves.
+        constexpr bool kWide = !COLRHT;
+        const int c_k = kWide ? (lane >> 2) : 0;                            // row-order key
+        const int c_half = kWide ? ((lane >> 2) & 1) : (lane & 1);
+        const int c_band = kWide ? (lane >> 3) : (cw >> 1);
+        const int c_pair = kWide ? ((cw << 2) | (lane & 3)) : (((cw & 1) << 4) | (lane >> 1));
+        const int c_chunk = (c_pair >> 2) ^ c_k;
+        const uint32_t c_bsel = 0x3210u ^ (0x1111u * (uint32_t) (c_k & 1)) ^ (0x2222u * (uint32_t) ((c_k >> 1) & 1));
         uint32_t stage = 0, phase = 0, tile_count = 0;
         const uint32_t per_g = (uint32_t) tiles_n * (uint32_t) tiles_m;
         for (uint32_t t = blockIdx.x; t < (uint32_t) total_tiles; t += gridDim.x) {
@@ -467,9 +479,15 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
                     if constexpr (kFp4) {
                         *reinterpret_cast<uint4 *>(qr + (gm * a.N_pad + gn) / 2) = make_uint4(w[0], w[1], w[2], w[3]);
                     } else {
-                        uint4 *dst = reinterpret_cast<uint4 *>(qr + gm * a.N_pad + gn);
-                        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                        uint8_t *dst = qr + gm * a.N_pad + gn;
+                        if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+                            // one 32-byte store: lanes 2i, 2i+1 then cover a 64-byte row segment in one instruction
+                            asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(w[0]), "r"(w[1]),
+                                         "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+                        } else {
+                            reinterpret_cast<uint4 *>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                            reinterpret_cast<uint4 *>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                        }
                     }
                     (a.s_row + g * a.srow_gstride)[gm * (a.N_pad / 32) + gn / 32] = sc.byte;
                 }
@@ -479,11 +497,15 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
                 // columns 2 c_pair, 2 c_pair + 1; rows c_band * 32 + c_half * 16 .. + 15
                 float c0[16], c1[16];
                 uint32_t pmc = 0u;  // packed |max| of (column 2 c_pair, column 2 c_pair + 1)
+                const uint8_t *cbase = tile.base + (c_band * 32 + c_half * 16) * 128 + ((c_pair & 3) << 2);
 #pragma unroll
                 for (int r = 0; r < 16; ++r) {
-                    const int row = c_band * 32 + c_half * 16 + r;
+                    const int rr = r ^ c_k;  // row inside this thread's 16
+                    const int row = c_band * 32 + c_half * 16 + rr;
                     // grouped: rows past the group's end hold the next group's data and count as zeros
-                    const uint32_t w = (!GROUPED || row < n_valid) ? tile.pair(row, c_pair) : 0u;
+                    const uint32_t w = (!GROUPED || row < n_valid)
+                                           ? *reinterpret_cast<const uint32_t *>(cbase + rr * 128 + ((c_chunk ^ (r & 7)) << 4))
+                                           : 0u;
                     c0[r] = Src<T>::to_f32((uint16_t) (w & 0xFFFF));
                     c1[r] = Src<T>::to_f32((uint16_t) (w >> 16));
                     pmc = absmax2<T>(pmc, w);
@@ -500,8 +522,8 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
                         m0c = lo_f32<T>(pmc);
                         m1c = hi_f32<T>(pmc);
                     }
-                    m0c = fmaxf(m0c, __shfl_xor_sync(0xffffffffu, m0c, 1));
-                    m1c = fmaxf(m1c, __shfl_xor_sync(0xffffffffu, m1c, 1));
+                    m0c = fmaxf(m0c, __shfl_xor_sync(0xffffffffu, m0c, kWide ? 4 : 1));
+                    m1c = fmaxf(m1c, __shfl_xor_sync(0xffffffffu, m1c, kWide ? 4 : 1));
                 }
                 const MxScale s0 = mx_scale<FMT>(m0c, GROUPED), s1 = mx_scale<FMT>(m1c, GROUPED);
                 const int64_t gc = n0 + 2 * c_pair;
@@ -516,10 +538,35 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
                         float t0[8], t1[8];
 #pragma unroll
                         for (int k = 0; k < 8; ++k) { t0[k] = cv[k]; t1[k] = cv[8 + k]; }
-                        const uint2 o0 = mx_encode8<FMT>(t0, sc), o1 = mx_encode8<FMT>(t1, sc);
+                        uint2 o0 = mx_encode8<FMT>(t0, sc), o1 = mx_encode8<FMT>(t1, sc);
+                        if constexpr (kWide) {  // value r holds row r ^ k: undo the permutation on the codes
+                            if constexpr (kFp4) {   // 8 codes per word: nibble r of o?.x
+                                if (c_k & 1) {
+                                    o0.x = ((o0.x & 0x0F0F0F0Fu) << 4) | ((o0.x >> 4) & 0x0F0F0F0Fu);
+                                    o1.x = ((o1.x & 0x0F0F0F0Fu) << 4) | ((o1.x >> 4) & 0x0F0F0F0Fu);
+                                }
+                                const uint32_t sel = 0x3210u ^ (0x1111u * (uint32_t) ((c_k >> 1) & 1)) ^ (0x2222u * (uint32_t) ((c_k >> 2) & 1));
+                                o0.x = __byte_perm(o0.x, 0u, sel);
+                                o1.x = __byte_perm(o1.x, 0u, sel);
+                            } else {                // 4 codes per word: byte r % 4 of word r / 4
+                                const bool sw = c_k & 4;
+                                const uint32_t a0 = sw ? o0.y : o0.x, a1 = sw ? o0.x : o0.y;
+                                const uint32_t b0 = sw ? o1.y : o1.x, b1 = sw ? o1.x : o1.y;
+                                o0 = make_uint2(__byte_perm(a0, 0u, c_bsel), __byte_perm(a1, 0u, c_bsel));
+                                o1 = make_uint2(__byte_perm(b0, 0u, c_bsel), __byte_perm(b1, 0u, c_bsel));
+                            }
+                        }
                         if constexpr (kFp4) *reinterpret_cast<uint2 *>(qc + ((gc + cc) * a.M_pad + gm) / 2) = make_uint2(o0.x, o1.x);
                         else *reinterpret_cast<uint4 *>(qc + (gc + cc) * a.M_pad + gm) = make_uint4(o0.x, o0.y, o1.x, o1.y);
-                        if (c_half == 0) scl[(gc + cc) * (a.M_pad / 32) + gm / 32] = sc.byte;
+                        if constexpr (kWide) {
+                            // the four band scales of this column, gathered into the band-0 lane: one 4-byte store
+                            uint32_t sb = sc.byte;
+                            sb |= __shfl_down_sync(0xffffffffu, sb, 8) << 8;
+                            sb |= __shfl_down_sync(0xffffffffu, sb, 16) << 16;
+                            if (lane < 4) *reinterpret_cast<uint32_t *>(scl + (gc + cc) * (a.M_pad / 32) + m0 / 32) = sb;
+                        } else {
+                            if (c_half == 0) scl[(gc + cc) * (a.M_pad / 32) + gm / 32] = sc.byte;
+                        }
                     }
                 }
             }
