@@ -4,6 +4,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "../../include/pt_b200.h"
 
@@ -29,6 +30,24 @@ int set_error(int code, const char *fmt, ...);
 #define PT_LAUNCH_OK() PT_CUDA_OK(cudaGetLastError())
 
 int sm_count();  // cached multiprocessor count of the current device
+
+// Launch that may overlap the tail of the previous kernel on the stream (programmatic stream serialization): only for
+// kernels that call sm100::grid_dep_wait() before touching memory an earlier kernel produces or reads.
+// PT_NO_PDL=1 (read per call) launches the ordinary way, for A/B runs.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = getenv("PT_NO_PDL") == nullptr ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline int64_t ceil_to(int64_t a, int64_t b) { return ceil_div(a, b) * b; }

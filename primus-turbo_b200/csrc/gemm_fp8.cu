@@ -115,6 +115,8 @@ __global__ void __launch_bounds__(128) sf_retile_kernel(RetileArgs args_a, Retil
     const int block_x = side_b ? (int) blockIdx.x - blocks_a : (int) blockIdx.x;
     const int grid_x = side_b ? (int) gridDim.x - blocks_a : blocks_a;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    grid_dep_wait();    // the scales come from the quantizer launched just before
+    grid_dep_launch();  // the GEMM that follows may set up its barriers and TMEM meanwhile
     if (!a.is_b) {
         if (tid == 0) {
             int acc = 0;
@@ -293,7 +295,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int num_k_blocks = (p.K + BLOCK_K - 1) / BLOCK_K;
     const int G = p.G;
 
-    // ---- prologue: tile table, barriers, TMEM
+    // ---- prologue: barriers, TMEM, then (after the earlier kernels of the stream are done) the tile table
+    grid_dep_wait();
     if (threadIdx.x == 0) {
         int acc = 0;
         s_tile_start[0] = 0;
@@ -322,6 +325,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
+    grid_dep_launch();
     const uint32_t tmem_base = *tmem_base_slot;
     const uint32_t tmem_sfa = tmem_base + kAccStages * BLOCK_N;
     const uint32_t tmem_sfb = tmem_sfa + 4;
@@ -510,8 +514,7 @@ static int prepare_mx_scales(GemmParams &p, const MxScales &mx, int64_t a_rows, 
     const int blocks_a = (int) std::min<int64_t>(ra.num_row_blocks, max_blocks);
     const int blocks_b = (int) std::min<int64_t>(rb.num_row_blocks, max_blocks);
     dim3 grid((unsigned) (blocks_a + blocks_b), (unsigned) ceil_div(num_kb, 32));
-    sf_retile_kernel<<<grid, 128, 0, st>>>(ra, rb, blocks_a);
-    PT_LAUNCH_OK();
+    PT_CUDA_OK(launch_overlapped(sf_retile_kernel, grid, dim3(128), 0, st, ra, rb, blocks_a));
     p.sfa_tiled = ra.dst;
     p.sfb_tiled = rb.dst;
     p.sfb_line0 = (rb.dst - ra.dst) / 128;
@@ -539,8 +542,7 @@ static int launch_gemm(const void *a, int64_t a_rows, const void *b, int64_t b_r
     int grid = (int) std::min<int64_t>(max_tiles, sm_count());
     if (max_ctas > 0) grid = std::min(grid, max_ctas);
     if (grid <= 0) return PT_OK;
-    kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ta, tb, p);
-    PT_LAUNCH_OK();
+    PT_CUDA_OK(launch_overlapped(kern, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, st, ta, tb, p));
     return PT_OK;
 }
 
@@ -584,8 +586,7 @@ static int launch_gemm_pair(const void *a, int64_t a_rows, const void *b, int64_
     }
     const int pairs = (int) std::min<int64_t>(tiles, max_clusters);
     if (pairs <= 0) return PT_OK;
-    kern<<<2 * pairs, Cfg::kThreads, Cfg::kSmemBytes, st>>>(ta, tb, tsf, p);
-    PT_LAUNCH_OK();
+    PT_CUDA_OK(launch_overlapped(kern, dim3(2 * pairs), dim3(Cfg::kThreads), Cfg::kSmemBytes, st, ta, tb, tsf, p));
     return PT_OK;
 }
 

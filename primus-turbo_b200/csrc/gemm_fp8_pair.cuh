@@ -84,16 +84,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((PairCfg<BLOCK_N, mo
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
-        int tiles = 0, blks = 0;
-        s_tile_start[0] = 0;
-        s_blk128_start[0] = 0;
-        for (int g = 0; g < G; ++g) {
-            const int64_t len = (p.offs_write && !p.koffs) ? (p.offs_write[g + 1] - p.offs_write[g]) : p.M;
-            tiles += (int) ((len + kTileM - 1) / kTileM) * num_n_blocks;
-            blks += (int) ((len + BLOCK_M - 1) / BLOCK_M);
-            s_tile_start[g + 1] = tiles;
-            s_blk128_start[g + 1] = blks;
-        }
         *abort_flag = 0;
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full_bar[s], 1);
@@ -112,10 +102,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((PairCfg<BLOCK_N, mo
         tmem_alloc_pair(tmem_base_slot, Cfg::kTmemCols);
         tmem_relinquish_pair();
     }
+    // everything above is private to this launch; from here on memory written by earlier kernels is read
+    grid_dep_wait();
+    if (threadIdx.x == 0) {
+        int tiles = 0, blks = 0;
+        s_tile_start[0] = 0;
+        s_blk128_start[0] = 0;
+        for (int g = 0; g < G; ++g) {
+            const int64_t len = (p.offs_write && !p.koffs) ? (p.offs_write[g + 1] - p.offs_write[g]) : p.M;
+            tiles += (int) ((len + kTileM - 1) / kTileM) * num_n_blocks;
+            blks += (int) ((len + BLOCK_M - 1) / BLOCK_M);
+            s_tile_start[g + 1] = tiles;
+            s_blk128_start[g + 1] = blks;
+        }
+    }
     tc_fence_before_sync();
     __syncwarp();
     cluster_sync_all();  // barriers of both CTAs are initialised before any remote arrival or copy
     tc_fence_after_sync();
+    grid_dep_launch();
     const uint32_t tmem_base = *tmem_base_slot;
     const uint32_t tmem_sfa = tmem_base + kAccStages * BLOCK_N;
     const uint32_t tmem_sfb = tmem_sfa + 4;

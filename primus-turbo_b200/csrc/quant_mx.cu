@@ -347,6 +347,8 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
     }
     if (threadIdx.x < 24) (&s_amax2d[0][0][0])[threadIdx.x] = 0u;
     __syncthreads();
+    sm100::grid_dep_wait();    // the input may come from the previous kernel, and a GEMM before it may still read the outputs
+    sm100::grid_dep_launch();
     bool ok = true;
     // grouped: tile row block tm -> first input row, number of rows of the group in the tile, first row of the
     // row-wise copy; false for tiles past the padded end
@@ -664,7 +666,7 @@ static int launch_mx(const MxArgs &a, int64_t G, unsigned flags, cudaStream_t st
                 PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kQSmemBytes)); \
                 attr_set = true;                                                                           \
             }                                                                                              \
-            kern<<<tma_grid, kQThreads, kQSmemBytes, st>>>(tmap, a, tiles_n, tiles_m, total_tiles, nullptr); \
+            PT_CUDA_OK(launch_overlapped(kern, dim3(tma_grid), dim3(kQThreads), kQSmemBytes, st, tmap, a, tiles_n, tiles_m, total_tiles, (int *) nullptr)); \
         } else {                                                                                           \
             mx_quant_kernel<T, FMT, R, C, R2, C2, RR, CR><<<grid, kMxThreads, 0, st>>>(a);                 \
         }                                                                                                  \
@@ -720,7 +722,7 @@ static int launch_mx_grouped(const MxArgs &a, int64_t m_alloc, unsigned flags, c
         if (use_tma) {                                                                                \
             auto kern = mx_quant_tma_kernel<T, FMT, R, C, false, false, RR, CR, true>;               \
             PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kQSmemBytes)); \
-            kern<<<tma_grid, kQThreads, kQSmemBytes, st>>>(tmap, a, tiles_n, tiles_m, total_tiles, nullptr); \
+            PT_CUDA_OK(launch_overlapped(kern, dim3(tma_grid), dim3(kQThreads), kQSmemBytes, st, tmap, a, tiles_n, tiles_m, total_tiles, (int *) nullptr)); \
         } else {                                                                                      \
             mx_quant_kernel<T, FMT, R, C, false, false, RR, CR, true><<<grid, kMxThreads, 0, st>>>(a); \
         }                                                                                             \

@@ -80,6 +80,14 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *m
 }
 // 2-D tiled store shared -> global (bulk-group completion).  Issued by one thread after the writers of the
 // shared tile have executed fence_proxy_async_smem() and synchronised with it.
+// Programmatic dependent launch.  A kernel launched with programmatic stream serialization may become resident while
+// the previous kernel of the stream is still draining: grid_dep_wait() returns once every earlier grid has completed
+// and its writes are visible, and must run before the first access to memory an earlier kernel produces or still
+// reads.  grid_dep_launch() lets the next kernel of the stream start its own prologue.  Both are no-ops for a kernel
+// launched the ordinary way.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, const void *smem_src, int c0, int c1) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(reinterpret_cast<uint64_t>(m)),
                  "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
