@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(kTileThreads)
             if (valid) {
                 float o[kPack];
 #pragma unroll
-                for (int i = 0; i < kPack; ++i) o[i] = scale_clamp<FMT>(vals[r][i], scale);
+                for (int i = 0; i < kPack; ++i) o[i] = mul_sat<FMT>(vals[r][i], scale);
                 store_row8<FMT>(q_row + (batch * M + in_m) * N, gn, N, vec_ok != 0, o);
                 if (lane16 == 0) {
                     const float inv = __fdiv_rn(1.0f, scale);
@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(kTileThreads)
             if (in_m < M) {
                 float o[kPack];
 #pragma unroll
-                for (int i = 0; i < kPack; ++i) o[i] = scale_clamp<FMT>(vals[r][i], scale);
+                for (int i = 0; i < kPack; ++i) o[i] = mul_sat<FMT>(vals[r][i], scale);
                 store_row8<FMT>(q_row + (batch * M + in_m) * N, gn, N, vec_ok != 0, o);
             }
         }
@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(kTileThreads)
             if (out_m < out_rows) {
                 float o[kPack];
 #pragma unroll
-                for (int i = 0; i < kPack; ++i) o[i] = scale_clamp<FMT>(vals[r][i], sc[i]);  // invalid rows hold 0
+                for (int i = 0; i < kPack; ++i) o[i] = mul_sat<FMT>(vals[r][i], sc[i]);  // invalid rows hold 0
                 store_row8<FMT>(q_col + (batch * (kSeg ? 0 : M) + out_m) * N, gn, N, vec_ok != 0, o);
             }
         }
@@ -402,8 +402,8 @@ __global__ void __launch_bounds__(kBqThreads, kBqCtasPerSm)
                         uint32_t o[4];
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
-                            o[k] = cvt4_fp8<FMT>(scale_clamp<FMT>(lo_f32<T>(w[2 * k]), scale), scale_clamp<FMT>(hi_f32<T>(w[2 * k]), scale),
-                                                 scale_clamp<FMT>(lo_f32<T>(w[2 * k + 1]), scale), scale_clamp<FMT>(hi_f32<T>(w[2 * k + 1]), scale));
+                            o[k] = cvt4_fp8<FMT>(mul_sat<FMT>(lo_f32<T>(w[2 * k]), scale), mul_sat<FMT>(hi_f32<T>(w[2 * k]), scale),
+                                                 mul_sat<FMT>(lo_f32<T>(w[2 * k + 1]), scale), mul_sat<FMT>(hi_f32<T>(w[2 * k + 1]), scale));
                         *reinterpret_cast<uint4 *>(a.q_row + (batch * a.M + in_m) * a.N + gn) = make_uint4(o[0], o[1], o[2], o[3]);
                         if (kRow && l8 == 0) {
                             const float inv = __fdiv_rn(1.0f, scale);
@@ -438,8 +438,8 @@ __global__ void __launch_bounds__(kBqThreads, kBqCtasPerSm)
                         if (out_m < out_rows) {
                             const bool live = !kSeg || row < n_valid;  // padding rows of a group are written as zeros
                             const uint32_t x01 = live ? cc[i].x : 0u, x23 = live ? cc[i].y : 0u;
-                            const uint32_t o = cvt4_fp8<FMT>(scale_clamp<FMT>(lo_f32<T>(x01), sc0), scale_clamp<FMT>(hi_f32<T>(x01), sc1),
-                                                             scale_clamp<FMT>(lo_f32<T>(x23), sc2), scale_clamp<FMT>(hi_f32<T>(x23), sc3));
+                            const uint32_t o = cvt4_fp8<FMT>(mul_sat<FMT>(lo_f32<T>(x01), sc0), mul_sat<FMT>(hi_f32<T>(x01), sc1),
+                                                             mul_sat<FMT>(lo_f32<T>(x23), sc2), mul_sat<FMT>(hi_f32<T>(x23), sc3));
                             *reinterpret_cast<uint32_t *>(a.q_col + (batch * (kSeg ? 0 : a.M) + out_m) * a.N + gc) = o;
                         }
                     }

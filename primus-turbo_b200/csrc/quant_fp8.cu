@@ -2,7 +2,8 @@
 //
 // Arithmetic follows csrc/include/primus_turbo/device/quant_utils.cuh:33-74 of the reference:
 //   scale = qmax / fmax(amax, 1e-12f), scale_inv = 1.0f / scale,
-//   q = fp8_rne(fmax(fmin(float(x) * scale, qmax), -qmax)).
+//   q = fp8_rne(fmax(fmin(float(x) * scale, qmax), -qmax)),
+// the clamp being done by the saturating convert (mul_sat in common.cuh).
 #include <cuda_fp8.h>
 #include <stdarg.h>
 #include <algorithm>
@@ -101,8 +102,8 @@ __global__ void __launch_bounds__(kThreads)
             load8(x + i * 16 + 8, b);
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-                a[k] = scale_clamp<FMT>(a[k], scale);
-                b[k] = scale_clamp<FMT>(b[k], scale);
+                a[k] = mul_sat<FMT>(a[k], scale);
+                b[k] = mul_sat<FMT>(b[k], scale);
             }
             uint4 o;
             o.x = cvt4_fp8<FMT>(a[0], a[1], a[2], a[3]);
@@ -113,7 +114,7 @@ __global__ void __launch_bounds__(kThreads)
         }
         done = nvec * 16;
     }
-    for (int64_t i = done + tid; i < n; i += nthreads) q[i] = cvt1_fp8<FMT>(scale_clamp<FMT>(load1(x + i), scale));
+    for (int64_t i = done + tid; i < n; i += nthreads) q[i] = cvt1_fp8<FMT>(mul_sat<FMT>(load1(x + i), scale));
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -164,7 +165,7 @@ __global__ void __launch_bounds__(kThreads)
                 float v[8];
                 load8(xr + i * 8, v);
 #pragma unroll
-                for (int k = 0; k < 8; ++k) v[k] = scale_clamp<FMT>(v[k], scale);
+                for (int k = 0; k < 8; ++k) v[k] = mul_sat<FMT>(v[k], scale);
                 uint2 o;
                 o.x = cvt4_fp8<FMT>(v[0], v[1], v[2], v[3]);
                 o.y = cvt4_fp8<FMT>(v[4], v[5], v[6], v[7]);
@@ -173,7 +174,7 @@ __global__ void __launch_bounds__(kThreads)
             done = nvec * 8;
         }
         for (int64_t i = done + threadIdx.x; i < len; i += kThreads)
-            qr[i] = cvt1_fp8<FMT>(scale_clamp<FMT>(load1(xr + i), scale));
+            qr[i] = cvt1_fp8<FMT>(mul_sat<FMT>(load1(xr + i), scale));
         __syncthreads();  // s / s_scale are reused by the next row
     }
 }
@@ -220,13 +221,13 @@ __global__ void __launch_bounds__(kThreads)
             float v[8];
             load8(x + off, v);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) v[k] = scale_clamp<FMT>(v[k], sc[k]);
+            for (int k = 0; k < 8; ++k) v[k] = mul_sat<FMT>(v[k], sc[k]);
             uint2 o;
             o.x = cvt4_fp8<FMT>(v[0], v[1], v[2], v[3]);
             o.y = cvt4_fp8<FMT>(v[4], v[5], v[6], v[7]);
             *reinterpret_cast<uint2 *>(q + off) = o;
         } else {
-            q[off] = cvt1_fp8<FMT>(scale_clamp<FMT>(load1(x + off), sc[0]));
+            q[off] = cvt1_fp8<FMT>(mul_sat<FMT>(load1(x + off), sc[0]));
         }
     }
 }
