@@ -167,7 +167,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
-    ap.add_argument("--granularity", default="mx", choices=["mx", "blockwise", "tensorwise", "rowwise", "mxfp4"],
+    ap.add_argument("--granularity", default="mx", choices=["mx", "blockwise", "tensorwise", "rowwise", "mxfp4", "bf16"],
                     help="scaling recipe of the linear forward; the headline metric is 'mx' (the others print the same "
                          "line for their own kernels and skip the CPU leg)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -201,7 +201,9 @@ def main():
     from primus_turbo.pytorch.kernels.quantization import quantization_impl as qi
     from primus_turbo.pytorch.kernels.quantization.quantization_impl import quantize_mxfp8_impl
 
-    if args.granularity == "mxfp4":
+    if args.granularity == "bf16":
+        cfg, public_op = None, (lambda x, y, trans_b, out_dtype, config: turbo.ops.gemm(x, y, trans_b=trans_b, out_dtype=out_dtype))
+    elif args.granularity == "mxfp4":
         from primus_turbo.pytorch.core.low_precision import Float4QuantConfig
         cfg, public_op = Float4QuantConfig(), turbo.ops.gemm_fp4
     elif args.granularity == "mx":
@@ -237,6 +239,11 @@ def main():
                          qi.quantize_mxfp4_impl(w, fp4, None, 32, True, two_d, two_d)[:2])
         gemm = lambda qa, qw: gemm_fp4_impl(qa[0], qa[1], False, qw[0], qw[1], True, torch.bfloat16, False, G.MX_BLOCKWISE)
         launches, kernel_name = 4, "gemm_fp8_pair_kernel<MXF4>"
+    elif args.granularity == "bf16":
+        from primus_turbo.pytorch.kernels.gemm.gemm_impl import gemm_impl
+        quant = lambda: (a, w)   # nothing to quantize: the comparison line of the low-precision recipes
+        gemm = lambda qa, qw: gemm_impl(qa, False, qw, True, torch.bfloat16, False)
+        launches, kernel_name = 1, "gemm_fp8_pair_kernel<HP>"
     elif args.granularity == "blockwise":
         quant = lambda: (qi.quant_fp8_blockwise_impl(a, f8, 1), qi.quant_fp8_blockwise_for_weight_impl(w, f8))
         gemm = lambda qa, qw: gemm_fp8_impl(qa[0], qa[1], False, qw[0], qw[1], True, torch.bfloat16, False, G.BLOCKWISE)
@@ -346,11 +353,14 @@ def main():
     achieved = flops / (gemm_ms / 1e3) / 1e12
     if args.granularity == "mxfp4":
         fp8_peak *= 2.0  # fp4 = 2 x fp8 = 4 x bf16
+    if args.granularity == "bf16":
+        fp8_peak *= 0.5
     recipe = {"mx": ("MXFP8 linear forward (dual quantize x2 + GEMM) throughput", "MX_BLOCKWISE", "E4M3", "fp8_e4m3 (fp32 accumulate)"),
               "mxfp4": ("MXFP4 linear forward (dual quantize x2 + GEMM) throughput", "MX_BLOCKWISE", "E2M1_X2", "fp4_e2m1 (fp32 accumulate)"),
               "blockwise": ("FP8 blockwise linear forward (quantize x2 + GEMM) throughput", "BLOCKWISE", "E4M3", "fp8_e4m3 (fp32 accumulate)"),
               "tensorwise": ("FP8 tensorwise linear forward (quantize x2 + GEMM) throughput", "TENSORWISE", "E4M3", "fp8_e4m3 (fp32 accumulate)"),
-              "rowwise": ("FP8 rowwise linear forward (quantize x2 + GEMM) throughput", "ROWWISE", "E4M3", "fp8_e4m3 (fp32 accumulate)")}[args.granularity]
+              "rowwise": ("FP8 rowwise linear forward (quantize x2 + GEMM) throughput", "ROWWISE", "E4M3", "fp8_e4m3 (fp32 accumulate)"),
+              "bf16": ("BF16 linear forward (GEMM) throughput", "NONE", "BF16", "bf16 (fp32 accumulate)")}[args.granularity]
     result = {
         "metric": recipe[0], "value": world * flops / (ms_per_step / 1e3) / 1e12,
         "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
@@ -361,9 +371,9 @@ def main():
                    "l2": "inputs 184 MB per step exceed the 126 MB L2; no flush between iterations"},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
                      "traffic": GEMM_DRAM_TRAFFIC.get(args.workload) if args.granularity == "mx" else None, "kernel": kernel_name,
-                     "peak_source": f"{'4' if args.granularity == 'mxfp4' else '2'} x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS.json",
+                     "peak_source": f"{ {'mxfp4': '4', 'bf16': '1'}.get(args.granularity, '2') } x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS.json",
                      "gemm_ms_per_launch": gemm_ms,
-                     "frac_of_nominal": achieved / (9000.0 if args.granularity == "mxfp4" else 4500.0)},
+                     "frac_of_nominal": achieved / {"mxfp4": 9000.0, "bf16": 2250.0}.get(args.granularity, 4500.0)},
         "clocks": clocks,
         "e2e": {"value": None if args.no_e2e else world * flops / (e2e_ms / 1e3) / 1e12, "unit": "TFLOPS",
                 "h2d_bytes_per_step": a_host.numel() * 2 + w_host.numel() * 2, "d2h_bytes_per_step": out_host[0].numel() * 2,

@@ -168,16 +168,16 @@ int pt_transpose_2d(const void *x, int64_t M, int64_t N, int elem_bytes, void *y
 /* The same over a batch: y [B, N, M] = x [B, M, N] transposed per matrix (a [G, K, N] expert weight to [G, N, K]). */
 int pt_transpose_batched(const void *x, int64_t B, int64_t M, int64_t N, int elem_bytes, void *y, void *stream);
 
-/* Token-major to token-minor copy of a grouped byte operand for the variable-K GEMM: x [M, C] holds group g in rows
+/* Token-major to token-minor copy of a grouped operand (1- or 2-byte elements) for the variable-K GEMM: x [M, C] holds group g in rows
  * group_offs[g] .. group_offs[g+1]; y [C, T] receives them as columns padded_offs[g] .. padded_offs[g] + len_g.  The rest
  * of every segment (padded_offs are multiples of 128, see pt_compute_padded_group_offs) and all columns from
- * padded_offs[G] on are written as zero bytes, so that they add nothing to the contraction.  T is a multiple of 64 and
+ * padded_offs[G] on are written as zeros, so that they add nothing to the contraction.  T is a multiple of 64 and
  * at least padded_offs[G]; both offset arrays are device int64 [G+1] (no host synchronisation).
  * The reference's tensorwise / rowwise variable-K kernels read the token-major operands in place
  * (primus_turbo/pytorch/kernels/grouped_gemm/grouped_gemm_fp8_impl.py:936-1030); pt_grouped_gemm_fp8_variable_k takes
  * K-major operands, and this is the copy that produces them. */
-int pt_grouped_transpose_pad(const void *x, int64_t M, int64_t C, const int64_t *group_offs, const int64_t *padded_offs,
-                             int G, void *y, int64_t T, void *stream);
+int pt_grouped_transpose_pad(const void *x, int64_t M, int64_t C, int elem_bytes, const int64_t *group_offs,
+                             const int64_t *padded_offs, int G, void *y, int64_t T, void *stream);
 
 /* Zero-fills rows [*first_row, rows) of a row-major buffer with `row_bytes` bytes per row (a multiple of 4, base 4-byte
  * aligned); `first_row` is a device pointer, so no host synchronisation is needed.  The grouped GEMMs leave rows past the
@@ -234,6 +234,20 @@ int pt_grouped_gemm_fp8_variable_k(const void *a, const void *a_scale, int a_fmt
                                    void *c, int c_dtype, int granularity, int64_t M, int64_t N, int64_t K_total,
                                    const int64_t *k_offs, int G, float beta, int block_n, int max_ctas, void *workspace,
                                    size_t workspace_bytes, int *status, void *stream);
+
+/* fp16 / bf16 GEMMs on the same tcgen05 kernels (kind::f16, fp32 accumulate, no scales): C [M, N] = A [M, K] . B [N, K]^T,
+ * both operands K-major with K a multiple of 8; ab_dtype PT_BF16 or PT_F16; c_dtype any PT_* output type; beta 0 or 1.
+ * Grouped: A [a_rows, K] split by group_offs int64 [G+1] (device), B [G, N, K], rows of C past group_offs[G] are not
+ * written.  Variable-K: A [M, K_total], B [N, K_total], C [G, M, N], k_offs int64 [G+1] multiples of 64 elements.
+ * Replace primus_turbo::gemm_impl / gemm_accum_impl (primus_turbo/pytorch/kernels/gemm/gemm_impl.py) and
+ * primus_turbo::grouped_gemm_impl / grouped_gemm_variable_k_impl / _accum_impl
+ * (primus_turbo/pytorch/kernels/grouped_gemm/grouped_gemm_impl.py). */
+int pt_gemm(const void *a, const void *b, int ab_dtype, void *c, int c_dtype, int64_t M, int64_t N, int64_t K, float beta, int *status,
+            void *stream);
+int pt_grouped_gemm(const void *a, const void *b, int ab_dtype, void *c, int c_dtype, int64_t a_rows, int64_t N, int64_t K,
+                    const int64_t *group_offs, int G, float beta, int max_ctas, int *status, void *stream);
+int pt_grouped_gemm_variable_k(const void *a, const void *b, int ab_dtype, void *c, int c_dtype, int64_t M, int64_t N, int64_t K_total,
+                               const int64_t *k_offs, int G, float beta, int max_ctas, int *status, void *stream);
 
 /* MXFP4 (packed e2m1, 32-element blocks, ue8m0 scales) forms of the three MX GEMMs above, on
  * tcgen05.mma kind::mxf4.block_scale: a [M, K/2] bytes, a_scale [M, K/32]; b [N, K/2], b_scale [N, K/32]; K is the

@@ -35,7 +35,7 @@ constexpr int kGemmThreads = 32 * (2 + kNumEpiWarps);
 constexpr int kEpiWarp0 = 2;
 constexpr int kStagePitchMax = 128;  // staging row pitch (bytes) of the epilogue, fp32 worst case
 
-enum GemmMode { GEMM_TENSOR = 0, GEMM_ROW = 1, GEMM_MX = 3, GEMM_MXF4 = 4 };
+enum GemmMode { GEMM_TENSOR = 0, GEMM_ROW = 1, GEMM_MX = 3, GEMM_MXF4 = 4, GEMM_HP = 5 };  // HP: fp16 / bf16 operands, no scales
 constexpr bool mode_is_mx(int m) { return m == GEMM_MX || m == GEMM_MXF4; }
 
 struct GemmParams {
@@ -334,8 +334,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     int gi, m_blk, n_blk;
     bool ok = true;
     auto k_range = [&](int g, int &kb_begin, int &kb_count) {
-        if (p.koffs) {  // offsets count elements; a stage holds 128 (fp8) or 256 (packed fp4) of them
-            constexpr int kElemsPerStage = F4 ? 2 * BLOCK_K : BLOCK_K;
+        if (p.koffs) {  // offsets count elements; a stage holds 128 (fp8), 256 (packed fp4) or 64 (16-bit) of them
+            constexpr int kElemsPerStage = F4 ? 2 * BLOCK_K : (MODE == GEMM_HP ? BLOCK_K / 2 : BLOCK_K);
             kb_begin = (int) (p.koffs[g] / kElemsPerStage);
             kb_count = (int) ((p.koffs[g + 1] - p.koffs[g]) / kElemsPerStage);
         } else {
@@ -424,6 +424,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                                      sfa_cur + (k >> 1) * Cfg::kSfColsHalf, sfb_cur + (k >> 1) * Cfg::kSfColsHalf, accumulate);
                         else if constexpr (MX)
                             mma_mxf8(d_tmem, a_desc + adv, b_desc + adv, idesc_sf_ids(idesc, k, k), sfa_cur, sfb_cur, accumulate);
+                        else if constexpr (MODE == GEMM_HP)
+                            mma_f16(d_tmem, a_desc + adv, b_desc + adv, idesc, accumulate);
                         else
                             mma_f8(d_tmem, a_desc + adv, b_desc + adv, idesc, accumulate);
                     }
@@ -686,11 +688,56 @@ int gemm_fp8_host(const void *a, const void *a_scale, int a_fmt, const void *b, 
     }
 }
 
+// fp16 / bf16 operands on the same kernels (kind::f16, no scales): the kernels count the contraction in bytes
+int gemm_hp_host(const void *a, const void *b, int ab_dtype, void *c, int c_dtype, int64_t M, int64_t N, int64_t K, float beta,
+                 const int64_t *offs, const int64_t *k_offs, int G, int64_t a_rows_total, int max_ctas, int *status, void *stream) {
+    PT_REQUIRE(M >= 0 && N >= 0 && K >= 0 && G >= 1 && G <= kMaxGroups, "GEMM: bad shape (M=%lld N=%lld K=%lld G=%d)",
+               (long long) M, (long long) N, (long long) K, G);
+    PT_REQUIRE(ab_dtype == PT_BF16 || ab_dtype == PT_F16, "GEMM: operands must be bf16 or fp16");
+    PT_REQUIRE(c_dtype == PT_BF16 || c_dtype == PT_F16 || c_dtype == PT_F32, "GEMM: bad output dtype");
+    PT_REQUIRE(beta == 0.f || beta == 1.f, "GEMM: beta must be 0 or 1");
+    PT_REQUIRE(!k_offs || !offs, "GEMM: the variable-K form takes no row offsets");
+    if (M == 0 || N == 0) return PT_OK;
+    PT_REQUIRE(K > 0 && K % 8 == 0, "GEMM: K must be a positive multiple of 8 for 16-bit operands (got %lld)", (long long) K);
+    PT_REQUIRE(a && b && c, "GEMM: null pointer");
+    PT_REQUIRE(N < (1 << 30) && K < (1 << 29) && a_rows_total < (1ll << 31) && (int64_t) G * N < (1ll << 31),
+               "GEMM: extent exceeds 32-bit tile coordinates");
+    GemmParams p{};
+    p.M = M; p.N = (int) N; p.K = (int) (2 * K); p.C = c; p.ldc = N; p.c_dtype = c_dtype; p.beta = beta;
+    const int esize = c_dtype == PT_F32 ? 4 : 2;
+    p.vec_store_ok = aligned(c, 16) && (N * esize) % 16 == 0;
+    p.a_fmt = p.b_fmt = ab_dtype == PT_BF16 ? 1 : 0;
+    p.offs_read = offs; p.offs_write = offs; p.G = G; p.b_group_rows = N;
+    p.koffs = k_offs;
+    p.status = status;
+    p.raster_m = raster_rows(a_rows_total, 2 * K);
+    const int64_t b_rows = k_offs ? N : (int64_t) G * N;
+    MxScales mx{nullptr, nullptr, 0, nullptr, 0};
+    return dispatch_block_n<GEMM_HP>(0, a, a_rows_total, b, b_rows, p, mx, max_ctas, (cudaStream_t) stream);
+}
+
 }  // namespace ptb
 
 using namespace ptb;
 
 extern "C" {
+
+int pt_gemm(const void *a, const void *b, int ab_dtype, void *c, int c_dtype, int64_t M, int64_t N, int64_t K, float beta, int *status,
+            void *stream) {
+    return gemm_hp_host(a, b, ab_dtype, c, c_dtype, M, N, K, beta, nullptr, nullptr, 1, M, 0, status, stream);
+}
+
+int pt_grouped_gemm(const void *a, const void *b, int ab_dtype, void *c, int c_dtype, int64_t a_rows, int64_t N, int64_t K,
+                    const int64_t *group_offs, int G, float beta, int max_ctas, int *status, void *stream) {
+    PT_REQUIRE(group_offs, "grouped GEMM: group offsets required");
+    return gemm_hp_host(a, b, ab_dtype, c, c_dtype, a_rows, N, K, beta, group_offs, nullptr, G, a_rows, max_ctas, status, stream);
+}
+
+int pt_grouped_gemm_variable_k(const void *a, const void *b, int ab_dtype, void *c, int c_dtype, int64_t M, int64_t N, int64_t K_total,
+                               const int64_t *k_offs, int G, float beta, int max_ctas, int *status, void *stream) {
+    PT_REQUIRE(k_offs, "variable-K GEMM: contraction offsets required");
+    return gemm_hp_host(a, b, ab_dtype, c, c_dtype, M, N, K_total, beta, nullptr, k_offs, G, M, max_ctas, status, stream);
+}
 
 size_t pt_gemm_fp4_workspace_bytes(int64_t c_rows, int64_t N, int64_t K, int G, int grouped, int block_n) {
     if (c_rows <= 0 || N <= 0 || K <= 0 || G < 1) return 0;

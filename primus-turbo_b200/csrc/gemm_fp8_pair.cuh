@@ -129,8 +129,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((PairCfg<BLOCK_N, mo
     bool ok = true;
     int gi, m_blk, n_blk;
     auto k_range = [&](int g, int &kb_begin, int &kb_count) {
-        if (p.koffs) {  // offsets count elements; a stage holds 128 (fp8) or 256 (packed fp4) of them
-            constexpr int kElemsPerStage = F4 ? 2 * BLOCK_K : BLOCK_K;
+        if (p.koffs) {  // offsets count elements; a stage holds 128 (fp8), 256 (packed fp4) or 64 (16-bit) of them
+            constexpr int kElemsPerStage = F4 ? 2 * BLOCK_K : (MODE == GEMM_HP ? BLOCK_K / 2 : BLOCK_K);
             kb_begin = (int) (p.koffs[g] / kElemsPerStage);
             kb_count = (int) ((p.koffs[g + 1] - p.koffs[g]) / kElemsPerStage);
         } else {
@@ -214,6 +214,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((PairCfg<BLOCK_N, mo
                             mma_mxf4_pair(d_tmem, a_desc + adv, b_desc + adv, idesc_sf_ids(idesc, (k & 1) * 2, (k & 1) * 2),
                                           sfa_cur + (k >> 1) * Cfg::kSfColsHalf, sfb_cur + (k >> 1) * Cfg::kSfColsHalf, accumulate);
                         else if constexpr (MX) mma_mxf8_pair(d_tmem, a_desc + adv, b_desc + adv, idesc_sf_ids(idesc, k, k), sfa_cur, sfb_cur, accumulate);
+                        else if constexpr (MODE == GEMM_HP) mma_f16_pair(d_tmem, a_desc + adv, b_desc + adv, idesc, accumulate);
                         else mma_f8_pair(d_tmem, a_desc + adv, b_desc + adv, idesc, accumulate);
                     }
                     tc_commit_pair(&empty_bar[stage], 3);  // frees the ring slot in both CTAs

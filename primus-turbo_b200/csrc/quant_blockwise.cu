@@ -598,6 +598,42 @@ __global__ void __launch_bounds__(256)
     }
 }
 
+// The same for 2-byte elements (bf16 / fp16 operands of the 16-bit variable-K GEMM): 64 padded columns x 64 source
+// columns per block through a padded shared-memory tile.
+__global__ void __launch_bounds__(256)
+    grouped_transpose_pad16_kernel(const uint16_t *__restrict__ x, int64_t C, const int64_t *__restrict__ offs,
+                                   const int64_t *__restrict__ poffs, int G, uint16_t *__restrict__ y, int64_t T) {
+    __shared__ uint16_t tile[64][64 + 2];
+    __shared__ int64_t s_src;
+    __shared__ int s_valid;
+    const int64_t t0 = (int64_t) blockIdx.y * 64, c0 = (int64_t) blockIdx.x * 64;
+    if (threadIdx.x == 0) {
+        int valid = 0;
+        int64_t src = 0;
+        if (G > 0 && t0 < poffs[G]) {
+            int lo = 0, hi = G - 1;
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (poffs[mid] <= t0) lo = mid;
+                else hi = mid - 1;
+            }
+            const int64_t in_seg = t0 - poffs[lo];
+            valid = (int) max((int64_t) 0, min((int64_t) 64, offs[lo + 1] - offs[lo] - in_seg));
+            src = offs[lo] + in_seg;
+        }
+        s_valid = valid;
+        s_src = src;
+    }
+    __syncthreads();
+    const int valid = s_valid;
+    const int tx = threadIdx.x % 64, ty = threadIdx.x / 64;
+    for (int r = ty; r < 64; r += 4)
+        tile[r][tx] = (r < valid && c0 + tx < C) ? x[(s_src + r) * C + c0 + tx] : (uint16_t) 0;
+    __syncthreads();
+    for (int r = ty; r < 64; r += 4)
+        if (c0 + r < C) y[(c0 + r) * T + t0 + tx] = tile[tx][r];
+}
+
 }  // namespace ptb
 
 using namespace ptb;
@@ -721,15 +757,22 @@ int pt_zero_rows_from(void *buf, int64_t rows, int64_t row_bytes, const int64_t 
     return PT_OK;
 }
 
-int pt_grouped_transpose_pad(const void *x, int64_t M, int64_t C, const int64_t *group_offs, const int64_t *padded_offs,
-                             int G, void *y, int64_t T, void *stream) {
+int pt_grouped_transpose_pad(const void *x, int64_t M, int64_t C, int elem_bytes, const int64_t *group_offs,
+                             const int64_t *padded_offs, int G, void *y, int64_t T, void *stream) {
     PT_REQUIRE(M >= 0 && C >= 0 && T >= 0 && G >= 0, "grouped transpose: negative extent");
+    PT_REQUIRE(elem_bytes == 1 || elem_bytes == 2, "grouped transpose: 1- or 2-byte elements");
     if (C == 0 || T == 0) return PT_OK;
     PT_REQUIRE(y && group_offs && padded_offs && (x || M == 0), "grouped transpose: null pointer");
     PT_REQUIRE(T % 64 == 0 && aligned(y, 16), "grouped transpose: the padded token count must be a multiple of 64 and y 16-byte aligned");
     PT_REQUIRE(T / 64 <= 65535, "grouped transpose: too many tokens");
     const int vec_ok = C % 16 == 0 && aligned(x, 16);
     dim3 grid((unsigned) ceil_div(C, 64), (unsigned) (T / 64));
+    if (elem_bytes == 2) {
+        grouped_transpose_pad16_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>((const uint16_t *) x, C, group_offs, padded_offs, G,
+                                                                                (uint16_t *) y, T);
+        PT_LAUNCH_OK();
+        return PT_OK;
+    }
     grouped_transpose_pad_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>((const uint8_t *) x, C, vec_ok, group_offs, padded_offs, G,
                                                                           (uint8_t *) y, T);
     PT_LAUNCH_OK();

@@ -41,8 +41,13 @@ SIGNATURES = {
     "pt_dequantize_mx": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_int, c_void_p]),
     "pt_transpose_2d": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "pt_transpose_batched": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
-    "pt_grouped_transpose_pad": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p]),
+    "pt_grouped_transpose_pad": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p]),
     "pt_zero_rows_from": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
+    "pt_gemm": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p]),
+    "pt_grouped_gemm": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int, c_float,
+                                c_int, c_void_p, c_void_p]),
+    "pt_grouped_gemm_variable_k": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int,
+                                           c_float, c_int, c_void_p, c_void_p]),
     "pt_gemm_fp8": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int64,
                             c_int64, c_int64, c_float, c_int, c_void_p, c_size_t, c_void_p, c_void_p]),
     "pt_gemm_fp8_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int]),

@@ -348,17 +348,17 @@ def transpose_batched(x: torch.Tensor) -> torch.Tensor:
 
 
 def grouped_transpose_pad(x: torch.Tensor, group_offs: torch.Tensor, padded_offs: torch.Tensor) -> torch.Tensor:
-    """x [M, C] of 1-byte elements, grouped along M -> [C, T] with each group's tokens in its 128-padded segment
+    """x [M, C] of 1- or 2-byte elements, grouped along M -> [C, T] with each group's tokens in its 128-padded segment
     (zero filled), T = round_up(M, 128) + 128 * G: an upper bound of padded_offs[-1] known without reading the device."""
     nv.require_cuda(x, group_offs, padded_offs)
-    assert x.dim() == 2 and x.element_size() == 1
+    assert x.dim() == 2 and x.element_size() in (1, 2)
     x = x.contiguous()
     M, C = x.shape
     G = group_offs.numel() - 1
     T = ceil_div(M, BLOCK) * BLOCK + BLOCK * G
     y = torch.empty((C, T), dtype=x.dtype, device=x.device)
     with nv.on_device(x.device):
-        nv.check(nv.lib().pt_grouped_transpose_pad(nv.ptr(x), M, C, nv.ptr(group_offs.to(torch.int64).contiguous()),
+        nv.check(nv.lib().pt_grouped_transpose_pad(nv.ptr(x), M, C, x.element_size(), nv.ptr(group_offs.to(torch.int64).contiguous()),
                                                     nv.ptr(padded_offs.to(torch.int64).contiguous()), G, nv.ptr(y), T,
                                                     nv.stream(x.device)), "grouped_transpose_pad")
     return y
