@@ -83,18 +83,21 @@ template <typename T> __device__ __forceinline__ float load1(const T *p) {
 template <> __device__ __forceinline__ float load1<float>(const float *p) { return *p; }
 
 // ---------------------------------------------------------------- packed 16-bit helpers
-// m = max(m, |w|) on both 16-bit halves of a word holding two bf16 / fp16 elements (a NaN half is ignored, as by fmaxf)
+// Running |max| over words holding two bf16 / fp16 elements, one instruction per word: max.xorsign.abs takes the
+// magnitudes of both inputs itself (the sign it leaves in the result is meaningless and dropped by absmax2_done at
+// the end); a NaN half is ignored, as by fmaxf.
 template <typename T> __device__ __forceinline__ uint32_t absmax2(uint32_t m, uint32_t w);
 template <> __device__ __forceinline__ uint32_t absmax2<__nv_bfloat16>(uint32_t m, uint32_t w) {
-    w &= 0x7FFF7FFFu;
-    __nv_bfloat162 r = __hmax2(*reinterpret_cast<__nv_bfloat162 *>(&m), *reinterpret_cast<__nv_bfloat162 *>(&w));
-    return *reinterpret_cast<uint32_t *>(&r);
+    uint32_t r;
+    asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(m), "r"(w));
+    return r;
 }
 template <> __device__ __forceinline__ uint32_t absmax2<__half>(uint32_t m, uint32_t w) {
-    w &= 0x7FFF7FFFu;
-    __half2 r = __hmax2(*reinterpret_cast<__half2 *>(&m), *reinterpret_cast<__half2 *>(&w));
-    return *reinterpret_cast<uint32_t *>(&r);
+    uint32_t r;
+    asm("max.xorsign.abs.f16x2 %0, %1, %2;" : "=r"(r) : "r"(m), "r"(w));
+    return r;
 }
+__device__ __forceinline__ uint32_t absmax2_done(uint32_t m) { return m & 0x7FFF7FFFu; }
 template <typename T> __device__ __forceinline__ float lo_f32(uint32_t w) { return Src<T>::to_f32((uint16_t) (w & 0xFFFF)); }
 template <typename T> __device__ __forceinline__ float hi_f32(uint32_t w) { return Src<T>::to_f32((uint16_t) (w >> 16)); }
 

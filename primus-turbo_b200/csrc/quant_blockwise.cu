@@ -366,6 +366,7 @@ __global__ void __launch_bounds__(kBqThreads, kBqCtasPerSm)
 #pragma unroll
                     for (int k = 0; k < 8; ++k) m = absmax2<T>(m, w[k]);
                 }
+                m = absmax2_done(m);
                 w_amax = warp_max(fmaxf(lo_f32<T>(m), hi_f32<T>(m)));
                 if (lane == 0) s_wmax[buf][cw] = w_amax;
             }
@@ -390,6 +391,7 @@ __global__ void __launch_bounds__(kBqThreads, kBqCtasPerSm)
                         uint32_t m = 0u;
 #pragma unroll
                         for (int k = 0; k < 8; ++k) m = absmax2<T>(m, w[k]);
+                        m = absmax2_done(m);
                         float am = fmaxf(lo_f32<T>(m), hi_f32<T>(m));
                         am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
                         am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
@@ -423,6 +425,8 @@ __global__ void __launch_bounds__(kBqThreads, kBqCtasPerSm)
                     m01 = absmax2<T>(m01, v.x);
                     m23 = absmax2<T>(m23, v.y);
                 }
+                m01 = absmax2_done(m01);
+                m23 = absmax2_done(m23);
                 const float sc0 = scale_from_amax<FMT>(lo_f32<T>(m01), kEpsBlock), sc1 = scale_from_amax<FMT>(hi_f32<T>(m01), kEpsBlock);
                 const float sc2 = scale_from_amax<FMT>(lo_f32<T>(m23), kEpsBlock), sc3 = scale_from_amax<FMT>(hi_f32<T>(m23), kEpsBlock);
                 const int64_t gc = n0 + 4 * lane;

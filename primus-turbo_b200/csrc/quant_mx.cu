@@ -453,6 +453,7 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
 #pragma unroll
                     for (int k = 0; k < 32; ++k) r_amax = fmaxf(r_amax, fabsf(rv[k]));
                 } else {
+                    pm = absmax2_done(pm);
                     r_amax = fmaxf(lo_f32<T>(pm), hi_f32<T>(pm));
                 }
             }
@@ -521,6 +522,7 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
 #pragma unroll
                         for (int r = 0; r < 16; ++r) { m0c = fmaxf(m0c, fabsf(c0[r])); m1c = fmaxf(m1c, fabsf(c1[r])); }
                     } else {
+                        pmc = absmax2_done(pmc);
                         m0c = lo_f32<T>(pmc);
                         m1c = hi_f32<T>(pmc);
                     }
