@@ -31,6 +31,14 @@ int set_error(int code, const char *fmt, ...);
 
 int sm_count();  // cached multiprocessor count of the current device
 
+// Index of the current device for the small per-device caches below (function attributes and occupancy are
+// per-device state; a process may drive several GPUs).
+inline int current_device_slot() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    return dev;
+}
+
 // Launch that may overlap the tail of the previous kernel on the stream (programmatic stream serialization): only for
 // kernels that call sm100::grid_dep_wait() before touching memory an earlier kernel produces or reads.
 // PT_NO_PDL=1 (read per call) launches the ordinary way, for A/B runs.

@@ -536,10 +536,11 @@ static int launch_gemm(const void *a, int64_t a_rows, const void *b, int64_t b_r
     if ((rc = make_tmap_bytes(&ta, a, a_rows, p.K, p.K, BLOCK_M)) != PT_OK) return rc;
     if ((rc = make_tmap_bytes(&tb, b, b_rows, p.K, p.K, BLOCK_N)) != PT_OK) return rc;
     auto kern = gemm_fp8_kernel<BLOCK_N, MODE>;
-    static bool attr_set = false;  // per instantiation
-    if (!attr_set) {
+    static bool attr_set[64] = {};  // per instantiation and device
+    const int dev = current_device_slot();
+    if (!attr_set[dev]) {
         PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-        attr_set = true;
+        attr_set[dev] = true;
     }
     int grid = (int) std::min<int64_t>(max_tiles, sm_count());
     if (max_ctas > 0) grid = std::min(grid, max_ctas);
@@ -569,7 +570,8 @@ static int launch_gemm_pair(const void *a, int64_t a_rows, const void *b, int64_
     // upper bound on tiles: every group may add one partial 256-row tile
     const int64_t m_tiles = p.koffs ? (int64_t) p.G * ceil_div(p.M, 2 * BLOCK_M) : ceil_div(p.M, 2 * BLOCK_M) + (p.offs_write ? p.G : 0);
     const int64_t tiles = m_tiles * ceil_div(p.N, BLOCK_N);
-    static int max_clusters = 0;  // co-resident pairs of this device (one device per process in this library's use)
+    static int max_clusters_dev[64] = {};  // co-resident pairs, per instantiation and device
+    int &max_clusters = max_clusters_dev[current_device_slot()];
     if (max_clusters == 0) {
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(2 * (unsigned) sm_count());

@@ -663,7 +663,8 @@ static int launch_mx(const MxArgs &a, int64_t G, unsigned flags, cudaStream_t st
     if (row == R && col == C && (!R || r2d == R2) && (!C || c2d == C2) && (!R || rrht == RR) && (!C || crht == CR)) { \
         if (use_tma) {                                                                                     \
             auto kern = mx_quant_tma_kernel<T, FMT, R, C, R2, C2, RR, CR>;                                 \
-            static bool attr_set = false;                                                                  \
+            static bool attr_set_dev[64] = {};                                                             \
+            bool &attr_set = attr_set_dev[current_device_slot()];                                          \
             if (!attr_set) {                                                                               \
                 PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kQSmemBytes)); \
                 attr_set = true;                                                                           \
