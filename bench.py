@@ -292,6 +292,29 @@ def main():
     ms_total = t_begin.elapsed_time(t_end)
     gemm_ms = sum(e0.elapsed_time(e1) for e0, e1 in gemm_events) / len(gemm_events)
 
+    # N > 1: the same steps with the output columns of all ranks gathered on every rank (one NCCL all_gather per
+    # step, the collective of a column-parallel linear with gather_output); reported beside `value`, not in it.
+    gather_ms = 0.0
+    if world > 1:
+        import torch.distributed as dist
+        recv = torch.empty((world * N, M), dtype=torch.bfloat16, device=dev)   # row blocks of the gathered y^T
+
+        def gather_step():
+            out = step()
+            dist.all_gather_into_tensor(recv, out.t().contiguous())
+
+        for _ in range(3):
+            gather_step()
+        barrier()
+        g_begin, g_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g_begin.record()
+        for _ in range(args.steps):
+            gather_step()
+        g_end.record()
+        barrier()
+        gather_ms = g_begin.elapsed_time(g_end)
+        del recv
+
     # End to end through the public operator, host buffers in and out.  Every step uploads its inputs from pinned host
     # memory and downloads its result; uploads, compute and downloads run on three streams over two sets of device
     # buffers, so step i + 1's upload overlaps step i's download (PCIe is full duplex) — all inside the timed region.
@@ -336,11 +359,11 @@ def main():
         barrier()
     e2e_ms = e_begin.elapsed_time(e_end) / n_e2e if n_e2e else float('nan')
 
-    t = torch.tensor([ms_total, gemm_ms, e2e_ms], dtype=torch.float64, device=dev)
+    t = torch.tensor([ms_total, gemm_ms, e2e_ms, gather_ms], dtype=torch.float64, device=dev)
     if world > 1:
         import torch.distributed as dist
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, gemm_ms, e2e_ms = (float(v) for v in t.tolist())
+    ms_total, gemm_ms, e2e_ms, gather_ms = (float(v) for v in t.tolist())
     ms_per_step = ms_total / args.steps
     flops = 2.0 * M * N * K
     if rank != 0:
@@ -380,6 +403,11 @@ def main():
                 "ms_per_step": None if args.no_e2e else e2e_ms},
         "gpu_launches": launches * args.steps,
     }
+    if world > 1:
+        g_ms = gather_ms / args.steps
+        result["with_output_gather"] = {"value": world * flops / (g_ms / 1e3) / 1e12, "unit": "TFLOPS", "ms_per_step": g_ms,
+                                        "collective": f"NCCL all_gather of the [{M}x{N}] bf16 output shard, {world} ranks",
+                                        "gathered_bytes_per_rank": (world - 1) * M * N * 2}
     if world == 1 and not args.no_cpu_baseline and args.granularity == "mx":
         cb = cpu_baseline(M, N, K, seed)
         cb.pop("seconds")
