@@ -5,8 +5,6 @@ gradient-accumulation window and by every call in inference.  The cache is keyed
 (bumped by any in-place update, which is how optimizers write) and storage pointer; the cached QuantizedTensor is tied
 back to the parameter with an identity autograd node so that the weight gradient still reaches it.
 """
-from typing import Optional
-
 import torch
 
 from ..core.quantized_tensor import QuantizedTensor, QuantizedTensorPair, create_quantized_weight
