@@ -212,3 +212,47 @@ def test_errors_are_reported(qi):
         qi.quantize_mxfp8_impl(x, torch.float8_e4m3fn, 1, 32)
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
         qi.quantize_fp8_tensorwise_impl(x.cpu(), torch.float8_e4m3fn)
+
+
+@pytest.mark.parametrize("dtype", FP8)
+def test_nan_input_becomes_the_nan_code_and_leaves_the_rest_alone(qi, dtype):
+    """Documented difference from the reference: a NaN element does not take part in the amax (as there) and converts
+    to the format's NaN code (there: +qmax, through its fmin / fmax clamp); every other byte and every scale equals
+    the quantization of the same tensor with the NaN replaced by zero."""
+    x = make((256, 256), torch.bfloat16, 21, "normal")
+    x[3, 5] = float("nan")
+    clean = x.clone()
+    clean[3, 5] = 0
+    pairs = [
+        (qi.quantize_fp8_tensorwise_impl(x, dtype), qi.quantize_fp8_tensorwise_impl(clean, dtype)),
+        (qi.quantize_fp8_rowwise_impl(x, dtype, -1), qi.quantize_fp8_rowwise_impl(clean, dtype, -1)),
+        (qi.quant_fp8_blockwise_impl(x, dtype, 1), qi.quant_fp8_blockwise_impl(clean, dtype, 1)),
+        (qi.quant_fp8_blockwise_impl(x, dtype, 0), qi.quant_fp8_blockwise_impl(clean, dtype, 0)),
+        (qi.quantize_mxfp8_impl(x, dtype, 1, 32), qi.quantize_mxfp8_impl(clean, dtype, 1, 32)),
+    ]
+    for (q, s), (qc, sc) in pairs:
+        assert torch.equal(s.reshape(-1).view(torch.uint8), sc.reshape(-1).view(torch.uint8))
+        assert bool(torch.isnan(q[3, 5].float()))
+        qb, qcb = q.view(torch.uint8).clone(), qc.view(torch.uint8).clone()
+        qb[3, 5] = 0
+        qcb[3, 5] = 0
+        assert torch.equal(qb, qcb)
+
+
+def test_mx_row_copy_at_a_16_byte_aligned_output(qi):
+    """The row copy is written with 32-byte stores when its address allows and with 16-byte ones otherwise: an output
+    buffer that is only 16-byte aligned must receive the same bytes."""
+    from primus_turbo.pytorch.kernels import _native as nv
+    M, N = 256, 384
+    x = make((M, N), torch.bfloat16, 23, "normal")
+    q_ref, s_ref = qi.quantize_mxfp8_impl(x, torch.float8_e4m3fn, 1, 32)
+    raw = torch.zeros(M * N + 64, dtype=torch.uint8, device="cuda")
+    q_view = raw[16:16 + M * N]
+    assert q_view.data_ptr() % 32 == 16
+    s_row = torch.empty((M, N // 32), dtype=torch.uint8, device="cuda")
+    nv.check(nv.lib().pt_quantize_mx(nv.ptr(x), nv.src_code(x.dtype), 1, M, N, nv.fmt_code(torch.float8_e4m3fn), nv.PT_MX_ROW,
+                                      q_view.data_ptr(), nv.ptr(s_row), None, None, nv.stream(x.device)), "quantize_mx")
+    torch.cuda.synchronize()
+    assert torch.equal(q_view.view(M, N), q_ref.view(torch.uint8))
+    assert torch.equal(s_row, s_ref.view(torch.uint8))
+    assert int(raw[:16].max()) == 0 and int(raw[16 + M * N:].max()) == 0
