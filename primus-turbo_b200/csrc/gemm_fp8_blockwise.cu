@@ -25,6 +25,7 @@
 // Scales are addressed through a small descriptor so that every layout the reference produces is read in
 // place: s(row, kb) = base[(row >> shift) * row_stride + kb * kb_stride]  (shift 0: per row, shift 7: per 128 rows).
 #include <algorithm>
+#include <cstdio>
 
 #include "gemm_common.cuh"
 
@@ -487,6 +488,8 @@ __global__ void __launch_bounds__(kBwThreads, 1)
     }
 }
 
+#include "gemm_fp8_blockwise_pair.cuh"
+
 // Raises the dynamic shared-memory limit of one kernel instantiation (on every call: it is a cheap host-side
 // attribute write and keeps the limit right on every device of the process) and launches it.
 template <typename Kernel>
@@ -496,6 +499,50 @@ static int bw_launch(Kernel kernel, int grid, cudaStream_t stream, const CUtenso
     kernel<<<grid, kBwThreads, kBwSmemBytes, stream>>>(ta, tb, tc, p);
     PT_LAUNCH_OK();
     return PT_OK;
+}
+
+// CTA-pair launch: grid = 2 x min(tiles, co-resident clusters of this device).  PT_ERR_CUDA (clusters cannot be
+// launched here) sends the caller back to the single-CTA kernel.
+template <typename Kernel>
+static int bw_launch_pair(Kernel kernel, int64_t tiles, cudaStream_t stream, const CUtensorMap &ta, const CUtensorMap &tb,
+                          const CUtensorMap &tc, const BwParams &p) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwSmemBytes) != cudaSuccess) {
+        cudaGetLastError();
+        return PT_ERR_CUDA;
+    }
+    static int max_clusters_dev[64] = {};  // per instantiation and device
+    int &max_clusters = max_clusters_dev[current_device_slot()];
+    if (max_clusters == 0) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(2 * (unsigned) sm_count());
+        cfg.blockDim = dim3(kBwThreads);
+        cfg.dynamicSmemBytes = kBwSmemBytes;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr; cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, (const void *) kernel, &cfg) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            return PT_ERR_CUDA;
+        }
+        max_clusters = n;
+    }
+    const int pairs = (int) std::min<int64_t>(tiles, max_clusters);
+    if (pairs <= 0) return PT_OK;
+    kernel<<<2 * pairs, kBwThreads, kBwSmemBytes, stream>>>(ta, tb, tc, p);
+    if (cudaGetLastError() != cudaSuccess) return PT_ERR_CUDA;
+    return PT_OK;
+}
+
+// The CTA-pair form is correct but not faster than the single-CTA kernel yet (B200: 1965-2009 against 2077-2115
+// TFLOP/s on 8192 x 14336 x 4096 and 8192^3): it relieves shared memory, but the promotion warps set the pace in both
+// forms and the pair adds a cross-CTA hand-over of the partial-sum buffer per K step.  It therefore runs only when
+// PT_BW_GEMM_PAIR=1 (read per call); PT_GEMM_PAIR=0 switches it off together with the other pair kernels.
+static bool bw_pair_enabled() {
+    const char *on = getenv("PT_BW_GEMM_PAIR");
+    const char *all = getenv("PT_GEMM_PAIR");
+    return on && on[0] == '1' && !(all && all[0] == '0');
 }
 
 }  // namespace ptb
@@ -534,7 +581,8 @@ int pt_grouped_gemm_fp8_blockwise(const void *a, int a_fmt, int a_mn, int64_t a_
     p.a_fmt = a_fmt; p.b_fmt = b_fmt;
     p.offs_write = group_offs_write; p.offs_read = group_offs_read ? group_offs_read : group_offs_write;
     p.G = G; p.b_group_rows = N; p.a_rows_total = a_mn ? a_mem_cols : a_mem_rows;
-    if (!group_offs_read) p.a_rows_total = std::min<int64_t>(p.a_rows_total, c_rows);  // rows that have scales p.status = status;
+    if (!group_offs_read) p.a_rows_total = std::min<int64_t>(p.a_rows_total, c_rows);  // rows that have scales
+    p.status = status;
     p.a_mn = a_mn; p.b_mn = b_mn; p.koffs = k_offs; p.b_group_kstride = K;
     p.sb_slab = sb_shift == 0 && sb_row_stride == 1 && sb_kb_stride % 4 == 0 && sb_group_stride % 4 == 0 && N % 4 == 0 && aligned(sb, 16);
     p.raster_m = raster_rows(a_mn ? a_mem_cols : a_mem_rows, a_mn ? a_mem_rows : a_mem_cols);
@@ -553,6 +601,33 @@ int pt_grouped_gemm_fp8_blockwise(const void *a, int a_fmt, int a_mn, int64_t a_
     p.c_tma = p.vec_store_ok && beta == 0.f && N * esize < (1ll << 31) && p.c_rows_total < (1ll << 31);
     if (p.c_tma && (rc = make_tmap_bytes(&tc, c, p.c_rows_total, N * esize, N * esize, 32)) != PT_OK) return rc;
     const int sbm = sb_shift == 7 ? SB_TILE : (p.sb_slab ? SB_SLAB : SB_GLOBAL);
+    // Large problems run on CTA pairs (256-row tiles).  Group lengths live on the device: the average rows per group
+    // decide (short groups would waste up to 255 rows of work each).
+    {
+        const int64_t rows_per_group = k_offs ? c_rows : c_rows / G;
+        const int64_t out_elems = (k_offs ? (int64_t) G : 1) * c_rows * N;
+        if (max_ctas <= 0 && sbm != SB_GLOBAL && bw_pair_enabled() && rows_per_group >= 1024 && N >= 512 &&
+            out_elems >= (int64_t) 4096 * 4096) {
+            CUtensorMap tb_pair;
+            if ((rc = make_tmap_bytes(&tb_pair, b, b_mem_rows, b_mem_cols, b_mem_cols, b_mn ? BLOCK_K : BW_BLOCK_N / 2)) != PT_OK) return rc;
+            const int64_t m_tiles = k_offs ? (int64_t) G * ceil_div(c_rows, 2 * BLOCK_M) : ceil_div(c_rows, 2 * BLOCK_M) + (group_offs_write ? G : 0);
+            const int64_t pair_tiles = m_tiles * ceil_div(N, BW_BLOCK_N);
+            BwParams pp = p;
+            int prc = PT_ERR_CUDA;
+#define PT_BWP_CASE(SBM_, T_) prc = bw_launch_pair(gemm_fp8_blockwise_pair_kernel<SBM_, T_>, pair_tiles, (cudaStream_t) stream, ta, tb_pair, tc, pp)
+#define PT_BWP_DTYPE(SBM_)                                                                                           \
+            do {                                                                                                     \
+                if (c_dtype == PT_F32) PT_BWP_CASE(SBM_, float);                                                     \
+                else if (c_dtype == PT_BF16) PT_BWP_CASE(SBM_, __nv_bfloat16);                                       \
+                else PT_BWP_CASE(SBM_, __half);                                                                      \
+            } while (0)
+            if (sbm == SB_TILE) PT_BWP_DTYPE(SB_TILE);
+            else PT_BWP_DTYPE(SB_SLAB);
+#undef PT_BWP_DTYPE
+#undef PT_BWP_CASE
+            if (prc != PT_ERR_CUDA) return prc;  // a device that cannot launch clusters falls through to single CTAs
+        }
+    }
 #define PT_BW_CASE(SBM_, T_)                                                                                         \
     return bw_launch(gemm_fp8_blockwise_kernel<SBM_, T_>, grid, (cudaStream_t) stream, ta, tb, tc, p)
 #define PT_BW_DTYPE(SBM_)                                                                                            \

@@ -254,8 +254,11 @@ __device__ __forceinline__ uint32_t map_to_rank(const void *smem_ptr, uint32_t r
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(smem_ptr)), "r"(rank));
     return r;
 }
+// Arrival on a barrier of another CTA of the cluster (address from map_to_rank).  Default semantics (release at CTA
+// scope): a cluster-scope release costs a cluster-wide fence per arrival, which halved the CTA-pair blockwise kernel
+// (one hand-over per K step); the hand-overs made this way order tensor-memory reads, which tcgen05.fence covers.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // 2-D tiled load into this CTA's shared memory; the bytes are counted on the barrier at `bar_cluster_addr`, which may
 // live in the peer CTA.  No multicast: every CTA of the pair fetches its own tiles.

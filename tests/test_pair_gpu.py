@@ -30,18 +30,20 @@ def m():
 
 
 def _both(fn):
-    """fn() with the pair kernels and with the single-CTA kernels."""
-    old = os.environ.get("PT_GEMM_PAIR")
+    """fn() with the pair kernels and with the single-CTA kernels (the block-scaled pair kernel is opt-in)."""
+    old = {k: os.environ.get(k) for k in ("PT_GEMM_PAIR", "PT_BW_GEMM_PAIR")}
     try:
         os.environ["PT_GEMM_PAIR"] = "1"
+        os.environ["PT_BW_GEMM_PAIR"] = "1"
         pair = fn()
         os.environ["PT_GEMM_PAIR"] = "0"
         single = fn()
     finally:
-        if old is None:
-            os.environ.pop("PT_GEMM_PAIR", None)
-        else:
-            os.environ["PT_GEMM_PAIR"] = old
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
     torch.cuda.synchronize()
     return pair, single
 
@@ -127,3 +129,41 @@ def test_grouped_mxfp4_pair_matches_single(m):
     pair, single = _both(lambda: gg4.grouped_gemm_fp4_variable_k_impl(g_col, a_col, g_s_col, a_s_col, lcol, ocol, torch.float32))
     nv.check_status(pair.device)
     _close(pair, single)
+
+
+@pytest.mark.parametrize("M,N,K", [(4096, 4096, 1024), (4000, 4360, 640), (1024, 16384, 512)])
+def test_dense_blockwise_pair_matches_single(m, M, N, K):
+    """Block-scaled GEMM on CTA pairs: forward (K-major operands, 128 x 128 weight scales), dgrad (the weight read in
+    place as an MN-major operand) and wgrad (both operands MN-major, per-column scales) against the single-CTA kernel."""
+    qi, gi, SG = m["qi"], m["gi"], m["SG"]
+    a = make((M, K), torch.bfloat16, 61, "normal")
+    w = make((N, K), torch.bfloat16, 62, "normal")
+    g = make((M, N), torch.bfloat16, 63, "normal")
+    a_row, a_s_row, a_col, a_s_col = qi.quant_fp8_blockwise_dual_impl(a, F8, 128)
+    g_row, g_s_row, g_col, g_s_col = qi.quant_fp8_blockwise_dual_impl(g, F8, 128)
+    w_q, w_s = qi.quant_fp8_blockwise_for_weight_impl(w, F8)
+    fwd = _both(lambda: gi.gemm_fp8_impl(a_row, a_s_row, False, w_q, w_s, True, torch.bfloat16, False, SG.BLOCKWISE))
+    _close(*fwd)
+    dgrad = _both(lambda: gi.gemm_fp8_impl(g_row, g_s_row, False, w_q, w_s, False, torch.bfloat16, False, SG.BLOCKWISE))
+    _close(*dgrad)
+    wgrad = _both(lambda: gi.gemm_fp8_impl(g_col, g_s_col, True, a_col, a_s_col, False, torch.float32, False, SG.BLOCKWISE))
+    _close(*wgrad)
+
+
+def test_grouped_blockwise_pair_matches_single(m):
+    qi, ggi, SG = m["qi"], m["ggi"], m["SG"]
+    lens_t, offs = _offs(LENS)
+    M, K, N, G = sum(LENS), 512, 1024, len(LENS)
+    a = make((M, K), torch.bfloat16, 64, "normal")
+    w = make((G, N, K), torch.bfloat16, 65, "normal")
+    g = make((M, N), torch.bfloat16, 66, "normal")
+    a_row, a_col, a_s_row, a_s_col, vk_lens, vk_offs = qi.quant_fp8_blockwise_segment_m_row_col_impl(a, F8, 128, lens_t, offs)
+    g_row, g_col, g_s_row, g_s_col, _, _ = qi.quant_fp8_blockwise_segment_m_row_col_impl(g, F8, 128, lens_t, offs)
+    w_q, w_s = qi.quant_fp8_blockwise_for_weight_impl(w, F8)
+    fwd = _both(lambda: ggi.grouped_gemm_fp8_impl(a_row, w_q, a_s_row, w_s, lens_t, offs, False, True, torch.bfloat16, SG.BLOCKWISE))
+    _close(*fwd)
+    dgrad = _both(lambda: ggi.grouped_gemm_fp8_impl(g_row, w_q, g_s_row, w_s, lens_t, offs, False, False, torch.bfloat16, SG.BLOCKWISE))
+    _close(*dgrad)
+    wgrad = _both(lambda: ggi.grouped_gemm_fp8_variable_k_impl(a_col, g_col, a_s_col, g_s_col, vk_lens, vk_offs, True, False, True,
+                                                               torch.bfloat16, SG.BLOCKWISE))
+    _close(*wgrad)
