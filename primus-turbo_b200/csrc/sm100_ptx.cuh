@@ -57,13 +57,18 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitim
 // On a timeout the caller's CTA-wide abort flag is raised so every other waiter unwinds at once.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = globaltimer_ns();
+    // The clock is first read after 64 failed polls (a read of %globaltimer costs far more than a poll, and most
+    // waits end within a few polls); the limit counts from that first reading.
+    uint64_t t0 = 0;
     uint32_t spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 0x3F) == 0) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > kWaitLimitNs) {
                 *abort_flag = 1;
                 return false;
             }
@@ -78,8 +83,6 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *m
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
-// 2-D tiled store shared -> global (bulk-group completion).  Issued by one thread after the writers of the
-// shared tile have executed fence_proxy_async_smem() and synchronised with it.
 // Programmatic dependent launch.  A kernel launched with programmatic stream serialization may become resident while
 // the previous kernel of the stream is still draining: grid_dep_wait() returns once every earlier grid has completed
 // and its writes are visible, and must run before the first access to memory an earlier kernel produces or still
@@ -88,6 +91,8 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *m
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// 2-D tiled store shared -> global (bulk-group completion).  Issued by one thread after the writers of the
+// shared tile have executed fence_proxy_async_smem() and synchronised with it.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, const void *smem_src, int c0, int c1) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(reinterpret_cast<uint64_t>(m)),
                  "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
