@@ -4,6 +4,9 @@ A weight is unchanged between optimizer steps, so its quantized copies can be re
 gradient-accumulation window and by every call in inference.  The cache is keyed on the parameter's version counter
 (bumped by any in-place update, which is how optimizers write) and storage pointer; the cached QuantizedTensor is tied
 back to the parameter with an identity autograd node so that the weight gradient still reaches it.
+
+A write that goes around the version counter (`weight.data.add_(...)`, a raw pointer write from another library) is
+not seen: call `clear()` on the module's cache after such an update.
 """
 import torch
 
