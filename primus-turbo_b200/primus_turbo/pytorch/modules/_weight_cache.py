@@ -6,7 +6,7 @@ gradient-accumulation window and by every call in inference.  The cache is keyed
 back to the parameter with an identity autograd node so that the weight gradient still reaches it.
 
 A write that goes around the version counter (`weight.data.add_(...)`, a raw pointer write from another library) is
-not seen: call `clear()` on the module's cache after such an update.
+not seen: call the module's `clear_quantized_weight_cache()` after such an update.
 """
 import torch
 

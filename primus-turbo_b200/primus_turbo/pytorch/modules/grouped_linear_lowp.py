@@ -44,6 +44,10 @@ class _LowpGroupedLinear(nn.Module):
         return self._qcache.get(self.weight, self._dest_dtype(), self.config,
                                 need_transpose=grad and needs_transpose_copy(self.config))
 
+    def clear_quantized_weight_cache(self):
+        """Drops the cached quantized experts (needed only after a write that bypasses the parameter's version counter)."""
+        self._qcache.clear()
+
     def extra_repr(self) -> str:
         return (f"group_num={self.group_num}, in_features={self.in_features}, out_features={self.out_features}, "
                 f"config={self.config}")

@@ -34,6 +34,12 @@ class Float8Linear(torch.nn.Linear):
         return cache.get(self.weight, _get_fp8_dtype(self.config.format, True), self.config,
                          need_transpose=grad and needs_transpose_copy(self.config))
 
+    def clear_quantized_weight_cache(self):
+        """Drops the cached quantized weight (needed only after a write that bypasses the parameter's version counter)."""
+        cache = self.__dict__.get("_qcache")
+        if cache is not None:
+            cache.clear()
+
     def forward(self, x):
         flatten_shapes = x.shape[:-1]
         x_2d = x.reshape(-1, self.in_features)

@@ -105,6 +105,11 @@ def test_float8_linear_weight_cache(m, gran, monkeypatch):
     assert len(calls) == 2
     with torch.no_grad():   # inference: forward copy only
         assert torch.equal(plain(x), cached(x))
+        # a write around the version counter is invisible to the cache until it is cleared
+        cached.weight.data.mul_(2.0)
+        plain.weight.data.mul_(2.0)
+        cached.clear_quantized_weight_cache()
+        assert torch.equal(plain(x), cached(x))
 
 
 @pytest.mark.parametrize("gran", GRANS + ["FP4"])
