@@ -1,0 +1,336 @@
+"""Workloads of the five benchmark configurations and the per-configuration measurements `bench.py` prints
+beside its headline: quantizer GB/s, dense forward / dgrad / wgrad, grouped forward / dgrad / wgrad.
+
+Everything here calls the same `*_impl` functions the operators call (one extern "C" entry each).  Shapes:
+
+  C2  Llama-3-8B MLP      M=8192   K=4096  N=14336                      rowwise and 128-blockwise FP8
+  C3  Llama-3-70B FFN     M=16384  K=8192  N=28672                      MXFP8, forward + wgrad
+  C4  DeepSeek-V3 MoE     256 experts, 131072 rows, 7168 -> 4096 and 2048 -> 7168, Zipf(1.1) group lengths
+  C5  Mixtral-8x7B MoE    8 experts, 65536 rows, 4096 -> 14336, Dirichlet(0.3) group lengths, MXFP4
+
+The group-length generators are shared with tests/test_configs_gpu.py so that tests and measurements see the same
+ragged layouts.  Large operands are drawn with the device generator (seeded): 15 GB of weights do not fit a host
+generator's patience; the parity tests download the rows they compare.
+"""
+import statistics
+
+import numpy as np
+import torch
+
+C2 = dict(M=8192, K=4096, N=14336, seed=1)
+C3 = dict(M=16384, K=8192, N=28672, seed=2)
+C4 = dict(G=256, rows=131072, hidden=7168, inter2=4096, inter=2048, seed=3)
+C5 = dict(G=8, rows=65536, hidden=4096, ffn=14336, seed=4)
+
+
+# ---------------------------------------------------------------------------------------------- group lengths
+def zipf_group_lens(G=256, rows=131072, s=1.1, seed=3, empty=4):
+    """Multinomial(rows, p) with p_i proportional to (i + 1)^-s, randomly permuted; the `empty` least loaded experts
+    are emptied and their rows given to the most loaded one, so that the layout always has empty groups."""
+    rng = np.random.default_rng(seed)
+    p = np.arange(1, G + 1, dtype=np.float64) ** -s
+    p = p[rng.permutation(G)]
+    p /= p.sum()
+    lens = rng.multinomial(rows, p).astype(np.int64)
+    order = np.argsort(lens, kind="stable")
+    lens[order[-1]] += lens[order[:empty]].sum()
+    lens[order[:empty]] = 0
+    assert lens.sum() == rows
+    return lens
+
+
+def dirichlet_group_lens(G=8, rows=65536, alpha=0.3, seed=4):
+    """round(rows * Dirichlet(alpha)) with the remainder on the last group."""
+    rng = np.random.default_rng(seed)
+    frac = rng.dirichlet(alpha * np.ones(G))
+    lens = np.floor(frac * rows).astype(np.int64)
+    lens[-1] = rows - lens[:-1].sum()
+    assert lens.min() >= 0 and lens.sum() == rows
+    return lens
+
+
+def offsets_of(lens, device):
+    lens_t = torch.as_tensor(np.asarray(lens), dtype=torch.int64, device=device)
+    offs = torch.zeros(lens_t.numel() + 1, dtype=torch.int64, device=device)
+    offs[1:] = torch.cumsum(lens_t, 0)
+    return lens_t, offs
+
+
+def randn_bf16(shape, std, seed, device):
+    g = torch.Generator(device=device).manual_seed(seed)
+    x = torch.empty(shape, dtype=torch.bfloat16, device=device)
+    x.normal_(0.0, std, generator=g)
+    return x
+
+
+# ---------------------------------------------------------------------------------------------- timing
+def time_cuda(fn, iters=20, warmup=3):
+    """Median CUDA-event time of one call in ms (events on the current stream, one synchronise per call)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    return statistics.median(ts)
+
+
+def time_cuda_rotating(fns, iters=24, warmup=4):
+    """Median time of one call when the calls cycle through `fns` (same kernel, different input buffers whose sum
+    exceeds L2, so that no call finds its input cached); all calls of a round are timed back to back."""
+    n = len(fns)
+    for i in range(warmup):
+        fns[i % n]()
+    torch.cuda.synchronize()
+    ts = []
+    for r in range(max(3, iters // n)):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for f in fns:
+            f()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) / n)
+    return statistics.median(ts)
+
+
+def _tensor_rec(flops, ms, peaks, kind, kernel):
+    """TFLOP/s record of a GEMM timed alone in a short loop: the burst figure is the denominator (x2 for FP8, x4 for
+    FP4 over the measured bf16 GEMM), the sustained one is printed beside it."""
+    mult = {"fp8": 2.0, "fp4": 4.0, "bf16": 1.0}[kind]
+    tf = flops / (ms / 1e3) / 1e12
+    return {"ms": ms, "tflops": tf, "roofline": {"bound": "tensor", "achieved": tf, "peak": mult * peaks["bf16_burst"],
+            "frac": tf / (mult * peaks["bf16_burst"]), "frac_of_sustained": tf / (mult * peaks["bf16_sustained"]),
+            "frac_of_nominal": tf / (2250.0 * mult), "unit": "TFLOP/s", "kernel": kernel}}
+
+
+def _hbm_rec(nbytes, ms, peaks, kernel):
+    gbs = nbytes / (ms / 1e3) / 1e9
+    return {"ms": ms, "bytes": nbytes, "gbs": gbs, "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"],
+            "frac": gbs / peaks["hbm_gbs"], "unit": "GB/s", "kernel": kernel}}
+
+
+# ---------------------------------------------------------------------------------------------- quantizers
+def quantize_records(dev, peaks, copies=4):
+    """One entry per quantizer on the tensor its configuration gives it; algorithmic bytes = input + outputs + scales."""
+    from primus_turbo.pytorch.core.low_precision import ScalingRecipe as SR
+    from primus_turbo.pytorch.kernels.quantization import quantization_impl as qi
+    f8, f5, f4 = torch.float8_e4m3fn, torch.float8_e5m2, torch.float4_e2m1fn_x2
+    out = {}
+    M, K, N = C2["M"], C2["K"], C2["N"]
+
+    def act(seed):
+        x = randn_bf16((M, K), 1.0, seed, dev)
+        mask = torch.rand((M, K), device=dev, generator=torch.Generator(device=dev).manual_seed(seed + 100)) < 0.001
+        return torch.where(mask, x * 50, x)
+
+    acts = [act(10 + i) for i in range(copies)]
+    wts = [randn_bf16((N, K), 0.02, 20 + i, dev) for i in range(copies)]
+    two_d = SR(use_2d_block=True)
+
+    def run(name, fns, nbytes, kernel):
+        out[name] = _hbm_rec(nbytes, time_cuda_rotating(fns), peaks, kernel)
+
+    e, ew = M * K, N * K
+    run("tensorwise_act_8192x4096", [lambda x=x: qi.quantize_fp8_tensorwise_impl(x, f8) for x in acts], 2 * 2 * e + e + 4,
+        "amax_flat_kernel + cast_flat_kernel")
+    run("rowwise_act_8192x4096", [lambda x=x: qi.quantize_fp8_rowwise_impl(x, f8, -1) for x in acts], 3 * e + 4 * M,
+        "rowwise_last_axis_kernel")
+    run("rowwise_other_axis_act_8192x4096", [lambda x=x: qi.quantize_fp8_rowwise_impl(x, f8, -2) for x in acts], 5 * e + 4 * K,
+        "amax_cols_kernel + cast_cols_kernel")
+    run("blockwise_row_act_8192x4096", [lambda x=x: qi.quant_fp8_blockwise_impl(x, f8, 1) for x in acts], 3 * e + 4 * e // 128,
+        "blockwise_tma_kernel<ROW>")
+    run("blockwise_dual_act_8192x4096", [lambda x=x: qi.quant_fp8_blockwise_dual_impl(x, f8) for x in acts], 4 * e + 8 * e // 128,
+        "blockwise_tma_kernel<DUAL>")
+    run("blockwise_weight_14336x4096", [lambda w=w: qi.quant_fp8_blockwise_for_weight_impl(w, f8) for w in wts],
+        3 * ew + 4 * ew // 16384, "blockwise_tma_kernel<WEIGHT>")
+    run("mxfp8_row_act_8192x4096", [lambda x=x: qi.quantize_mxfp8_impl(x, f8, 1, 32) for x in acts], 3 * e + e // 32,
+        "mx_quant_tma_kernel<row>")
+    run("mxfp8_dual_act_8192x4096", [lambda x=x: qi.quantize_mxfp8_impl(x, f8, None, 32, True) for x in acts],
+        2 * e + 2 * (e + e // 32), "mx_quant_tma_kernel<row+col>")
+    run("mxfp8_dual_2d_weight_14336x4096", [lambda w=w: qi.quantize_mxfp8_impl(w, f8, None, 32, True, two_d, two_d) for w in wts],
+        2 * ew + 2 * (ew + ew // 32), "mx_quant_tma_kernel<row+col, 2-D>")
+    run("mxfp4_dual_act_8192x4096", [lambda x=x: qi.quantize_mxfp4_impl(x, f4, None, 32, True) for x in acts],
+        2 * e + 2 * (e // 2 + e // 32), "mx_quant_tma_kernel<e2m1, row+col>")
+    del wts
+    # C3: dual MX quantization of the 16384 x 8192 activation (the transposed copy feeds the wgrad)
+    a3 = [randn_bf16((C3["M"], C3["K"]), 1.0, 30 + i, dev) for i in range(2)]
+    e3 = C3["M"] * C3["K"]
+    run("mxfp8_dual_act_16384x8192", [lambda x=x: qi.quantize_mxfp8_impl(x, f8, None, 32, True) for x in a3],
+        2 * e3 + 2 * (e3 + e3 // 32), "mx_quant_tma_kernel<row+col>")
+    del a3
+    # C4: segment-M row + column quantization of 32768 of the routed rows (hidden 7168), Zipf lengths of 64 experts
+    lens = zipf_group_lens(64, 32768, seed=C4["seed"])
+    lens_t, offs = offsets_of(lens, dev)
+    xs = [randn_bf16((32768, C4["hidden"]), 1.0, 40 + i, dev) for i in range(2)]
+    e4 = 32768 * C4["hidden"]
+    e4_pad = int(((lens + 127) // 128 * 128).sum()) * C4["hidden"]
+    run("blockwise_segment_m_32768x7168_g64", [lambda x=x: qi.quant_fp8_blockwise_segment_m_row_col_impl(x, f8, 128, lens_t, offs) for x in xs],
+        2 * e4 + e4 + e4_pad + 4 * e4 // 128 + 4 * e4_pad // 128, "blockwise_tma_kernel<SEGMENT>")
+    del xs
+    # C5: grouped MXFP4 dual quantization (row copy plain, transposed copy with the 16-point Hadamard transform)
+    lens5 = dirichlet_group_lens(C5["G"], C5["rows"], seed=C5["seed"])
+    lens5_t, offs5 = offsets_of(lens5, dev)
+    x5 = [randn_bf16((C5["rows"], C5["hidden"]), 1.0, 50 + i, dev) for i in range(2)]
+    e5 = C5["rows"] * C5["hidden"]
+    e5_pad = int(((lens5 + 255) // 256 * 256).sum()) * C5["hidden"]
+    run("grouped_mxfp4_dual_rht_65536x4096_g8",
+        [lambda x=x: qi.grouped_quantize_mxfp4_impl(x, f4, None, 32, lens5_t, offs5, with_trans=True, scaling_recipe=SR(),
+                                                    scaling_recipe_for_trans=SR(use_rht=True)) for x in x5],
+        2 * e5 + (e5 // 2 + e5 // 32) + (e5_pad // 2 + e5_pad // 32), "mx_quant_tma_kernel<e2m1, row+col, RHT, grouped>")
+    run("grouped_mxfp8_dual_65536x4096_g8",
+        [lambda x=x: qi.grouped_quantize_mxfp8_impl(x, f8, None, 32, lens5_t, offs5, with_trans=True) for x in x5],
+        2 * e5 + 2 * (e5 + e5 // 32), "mx_quant_tma_kernel<row+col, grouped>")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------- dense C2 backward
+def dense_bwd_c2(dev, peaks):
+    """dgrad [8192 x 14336] -> [8192 x 4096] and wgrad -> [14336 x 4096] of the C2 linear, rowwise and blockwise,
+    e4m3 forward operands and e5m2 gradients, GEMM kernels timed on pre-quantized operands (quantizers have their own
+    records)."""
+    from primus_turbo.pytorch.core.low_precision import ScalingGranularity as SG, ScalingRecipe as SR
+    from primus_turbo.pytorch.kernels.gemm.gemm_fp8_impl import gemm_fp8_impl
+    from primus_turbo.pytorch.kernels.quantization import quantization_impl as qi
+    f8, f5 = torch.float8_e4m3fn, torch.float8_e5m2
+    M, K, N = C2["M"], C2["K"], C2["N"]
+    x = randn_bf16((M, K), 1.0, 61, dev)
+    w = randn_bf16((N, K), 0.02, 62, dev)
+    dy = randn_bf16((M, N), 1e-3, 63, dev)
+    flops = 2.0 * M * N * K
+    out = {}
+    # rowwise: dgrad = g(row scales) . w_t(col-axis scales);  wgrad = x_t^T . g_t  (scales along the tokens)
+    g_q, g_s = qi.quantize_fp8_rowwise_impl(dy, f5, -1)
+    wt_q, wt_s = qi.quantize_fp8_rowwise_impl(w, f8, -2)
+    out["rowwise_dgrad"] = _tensor_rec(flops, time_cuda(lambda: gemm_fp8_impl(g_q, g_s, False, wt_q, wt_s, False, torch.bfloat16, False, SG.ROWWISE)),
+                                       peaks, "fp8", "gemm_fp8_pair_kernel<ROW> (+ transposed weight copy)")
+    xt_q, xt_s = qi.quantize_fp8_rowwise_impl(x, f8, -2)
+    gt_q, gt_s = qi.quantize_fp8_rowwise_impl(dy, f5, -2)
+    out["rowwise_wgrad"] = _tensor_rec(flops, time_cuda(lambda: gemm_fp8_impl(xt_q, xt_s, True, gt_q, gt_s, False, torch.bfloat16, True, SG.ROWWISE)),
+                                       peaks, "fp8", "gemm_fp8_pair_kernel<ROW> (+ transposed operand copies)")
+    del g_q, wt_q, xt_q, gt_q
+    # blockwise: operands of the backward GEMMs are the forward's tensors read MN-major in place
+    _, _, a_col, a_col_s = qi.quant_fp8_blockwise_dual_impl(x, f8)
+    b_q, b_s = qi.quant_fp8_blockwise_for_weight_impl(w, f8)
+    g_row, g_row_s, g_col, g_col_s = qi.quant_fp8_blockwise_dual_impl(dy, f5)
+    out["blockwise_dgrad"] = _tensor_rec(flops, time_cuda(lambda: gemm_fp8_impl(g_row, g_row_s, False, b_q, b_s, False, torch.bfloat16, False, SG.BLOCKWISE)),
+                                         peaks, "fp8", "gemm_fp8_blockwise_kernel")
+    out["blockwise_wgrad"] = _tensor_rec(flops, time_cuda(lambda: gemm_fp8_impl(a_col, a_col_s, True, g_col, g_col_s, False, torch.bfloat16, True, SG.BLOCKWISE)),
+                                         peaks, "fp8", "gemm_fp8_blockwise_kernel")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------- C3 (MXFP8 70B FFN)
+def mx_c3(dev, peaks, n_lo=0, n_hi=None):
+    """Forward and wgrad of the 16384 x 28672 x 8192 MXFP8 linear restricted to output columns [n_lo, n_hi) (the whole
+    layer by default; one rank's shard in the N-sharded run).  The wgrad contracts the transposed MX copies."""
+    from primus_turbo.pytorch.core.low_precision import ScalingGranularity as SG, ScalingRecipe as SR
+    from primus_turbo.pytorch.kernels.gemm.gemm_fp8_impl import gemm_fp8_impl
+    from primus_turbo.pytorch.kernels.quantization import quantization_impl as qi
+    f8, f5 = torch.float8_e4m3fn, torch.float8_e5m2
+    M, K, N = C3["M"], C3["K"], C3["N"]
+    n_hi = N if n_hi is None else n_hi
+    n = n_hi - n_lo
+    x = randn_bf16((M, K), 1.0, 71, dev)
+    w = randn_bf16((N, K), 0.01, 72, dev)[n_lo:n_hi].contiguous()
+    dy = randn_bf16((M, n), 1e-3, 73 + n_lo, dev)
+    two_d = SR(use_2d_block=True)
+    a_row, a_row_s, a_col, a_col_s = qi.quantize_mxfp8_impl(x, f8, None, 32, True)
+    b_row, b_row_s, _, _ = qi.quantize_mxfp8_impl(w, f8, None, 32, True, two_d, two_d)
+    _, _, g_col, g_col_s = qi.quantize_mxfp8_impl(dy, f5, None, 32, True)
+    del x, w, dy
+    flops = 2.0 * M * n * K
+    out = {"columns": [n_lo, n_hi]}
+    out["fwd"] = _tensor_rec(flops, time_cuda(lambda: gemm_fp8_impl(a_row, a_row_s, False, b_row, b_row_s, True, torch.bfloat16, False, SG.MX_BLOCKWISE)),
+                             peaks, "fp8", "gemm_fp8_pair_kernel<MX>")
+    out["wgrad"] = _tensor_rec(flops, time_cuda(lambda: gemm_fp8_impl(g_col, g_col_s, False, a_col, a_col_s, True, torch.bfloat16, False, SG.MX_BLOCKWISE)),
+                               peaks, "fp8", "gemm_fp8_pair_kernel<MX>")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------- C4 (blockwise MoE)
+def grouped_blockwise_c4(dev, peaks, g_lo=0, g_hi=None, projections=("gate_up", "down"), iters=8):
+    """Blockwise-FP8 grouped forward / dgrad / wgrad over experts [g_lo, g_hi) of the 256 (all by default; one rank's
+    experts in the expert-sharded run) with the rows routed to them."""
+    from primus_turbo.pytorch.core.low_precision import ScalingGranularity as SG
+    from primus_turbo.pytorch.kernels.grouped_gemm import grouped_gemm_fp8_impl as ggi
+    from primus_turbo.pytorch.kernels.quantization import quantization_impl as qi
+    f8, f5 = torch.float8_e4m3fn, torch.float8_e5m2
+    lens_all = zipf_group_lens(C4["G"], C4["rows"], seed=C4["seed"])
+    g_hi = C4["G"] if g_hi is None else g_hi
+    lens = lens_all[g_lo:g_hi]
+    rows, G = int(lens.sum()), int(g_hi - g_lo)
+    lens_t, offs = offsets_of(lens, dev)
+    out = {"experts": [int(g_lo), int(g_hi)], "rows": rows, "empty_groups": int((lens == 0).sum()), "max_group": int(lens.max())}
+    shapes = {"gate_up": (C4["inter2"], C4["hidden"]), "down": (C4["hidden"], C4["inter"])}
+    for name in projections:
+        N, K = shapes[name]
+        x = randn_bf16((max(rows, 1), K), 1.0, 81 + g_lo, dev)[:rows]
+        dy = randn_bf16((max(rows, 1), N), 1e-3, 82 + g_lo, dev)[:rows]
+        w = randn_bf16((G, N, K), 0.02, 83 + g_lo, dev)
+        a_row, a_col, a_s_row, a_s_col, plens, poffs = qi.quant_fp8_blockwise_segment_m_row_col_impl(x, f8, 128, lens_t, offs)
+        w_q, w_s = qi.quant_fp8_blockwise_for_weight_impl(w, f8)
+        g_row, g_col, g_s_row, g_s_col, _, _ = qi.quant_fp8_blockwise_segment_m_row_col_impl(dy, f5, 128, lens_t, offs)
+        del x, dy, w
+        flops = 2.0 * rows * N * K
+        rec = {}
+        rec["fwd"] = _tensor_rec(flops, time_cuda(lambda: ggi.grouped_gemm_fp8_impl(a_row, w_q, a_s_row, w_s, lens_t, offs, False, True, torch.bfloat16, SG.BLOCKWISE), iters),
+                                 peaks, "fp8", "gemm_fp8_blockwise_kernel (grouped)")
+        rec["dgrad"] = _tensor_rec(flops, time_cuda(lambda: ggi.grouped_gemm_fp8_impl(g_row, w_q, g_s_row, w_s, lens_t, offs, False, False, torch.bfloat16, SG.BLOCKWISE), iters),
+                                   peaks, "fp8", "gemm_fp8_blockwise_kernel (grouped, MN-major weight)")
+        rec["wgrad"] = _tensor_rec(flops, time_cuda(lambda: ggi.grouped_gemm_fp8_variable_k_impl(a_col, g_col, a_s_col, g_s_col, plens, poffs, True, False, True, torch.bfloat16, SG.BLOCKWISE), max(3, iters // 2)),
+                                   peaks, "fp8", "gemm_fp8_blockwise_kernel (variable K)")
+        rec["wgrad"]["output_bytes"] = 2 * G * N * K
+        out[name] = rec
+        del a_row, a_col, w_q, g_row, g_col
+        torch.cuda.empty_cache()
+    return out
+
+
+# ---------------------------------------------------------------------------------------------- C5 (MXFP4 MoE)
+def grouped_mxfp4_c5(dev, peaks, lens=None, iters=8):
+    """MXFP4 grouped forward / dgrad / wgrad, 8 experts 4096 -> 14336; `lens` overrides the Dirichlet group lengths
+    (the tokens-per-expert sweep passes balanced ones)."""
+    from primus_turbo.pytorch.core.low_precision import ScalingRecipe as SR
+    from primus_turbo.pytorch.kernels.grouped_gemm import grouped_gemm_fp4_impl as gg4
+    from primus_turbo.pytorch.kernels.quantization import quantization_impl as qi
+    f4 = torch.float4_e2m1fn_x2
+    G, K, N = C5["G"], C5["hidden"], C5["ffn"]
+    lens = dirichlet_group_lens(G, C5["rows"], seed=C5["seed"]) if lens is None else np.asarray(lens, dtype=np.int64)
+    rows = int(lens.sum())
+    lens_t, offs = offsets_of(lens, dev)
+    x = randn_bf16((rows, K), 1.0, 91, dev)
+    dy = randn_bf16((rows, N), 1.0, 92, dev)
+    w = randn_bf16((G, N, K), 0.02, 93, dev)
+    rht = SR(use_rht=True)
+    two_d = SR(use_2d_block=True)
+    a_row, a_s_row, a_col, a_s_col, _, orow, lcol, ocol = qi.grouped_quantize_mxfp4_impl(x, f4, None, 32, lens_t, offs, with_trans=True,
+                                                                                         scaling_recipe=SR(), scaling_recipe_for_trans=rht)
+    w_row, w_s_row, w_col, w_s_col = qi.quantize_mxfp4_impl(w, f4, None, 32, with_trans=True, scaling_recipe=two_d, scaling_recipe_for_trans=two_d)
+    g_row, g_s_row, g_col, g_s_col, _, orow2, _, _ = qi.grouped_quantize_mxfp4_impl(dy, f4, None, 32, lens_t, offs, with_trans=True,
+                                                                                    scaling_recipe=SR(), scaling_recipe_for_trans=rht)
+    del x, dy, w
+    flops = 2.0 * rows * N * K
+    out = {"group_lens": [int(v) for v in lens]}
+    out["fwd"] = _tensor_rec(flops, time_cuda(lambda: gg4.grouped_gemm_fp4_impl(a_row, w_row, a_s_row, w_s_row, lens_t, orow, out_dtype=torch.bfloat16, group_offs_out=offs), iters),
+                             peaks, "fp4", "gemm_fp8_pair_kernel<MXF4> (grouped)")
+    out["dgrad"] = _tensor_rec(flops, time_cuda(lambda: gg4.grouped_gemm_fp4_impl(g_row, w_col, g_s_row, w_s_col, lens_t, orow2, out_dtype=torch.bfloat16, group_offs_out=offs), iters),
+                               peaks, "fp4", "gemm_fp8_pair_kernel<MXF4> (grouped)")
+    out["wgrad"] = _tensor_rec(flops, time_cuda(lambda: gg4.grouped_gemm_fp4_variable_k_impl(g_col, a_col, g_s_col, a_s_col, lcol, ocol, torch.bfloat16), iters),
+                               peaks, "fp4", "gemm_fp8_pair_kernel<MXF4> (variable K)")
+    return out
+
+
+def mxfp4_c5_sweep(dev, peaks, tokens_per_expert=(128, 512, 2048, 8192, 16384)):
+    """Forward TFLOP/s of the balanced tokens-per-expert sweep of C5."""
+    out = {}
+    for t in tokens_per_expert:
+        rec = grouped_mxfp4_c5(dev, peaks, lens=[t] * C5["G"], iters=6)
+        out[str(t)] = {"fwd_tflops": rec["fwd"]["tflops"], "dgrad_tflops": rec["dgrad"]["tflops"], "wgrad_tflops": rec["wgrad"]["tflops"]}
+        torch.cuda.empty_cache()
+    return out

@@ -17,11 +17,16 @@ Pinning status (what the restatement has been checked against):
   interpreter.
 * blockwise / tensorwise / rowwise GEMM semantics: pinned (to fp32 tolerance)
   against the reference's Triton GEMM kernels under the same interpreter.
-* MXFP8 / MXFP4 (ue8m0 scale, e4m3 / e5m2 / e2m1 conversion): the scale
-  computation is restated bit for bit from the kernel source; the final
-  fp32 -> fp8 / fp4 rounding is done in the reference by AMD CDNA4 convert
-  instructions whose tie rule is in no source file of the reference.  The
-  oracle assumes IEEE round-to-nearest-even then saturate-to-finite (the OCP
-  MX rule).  PARITY UNPINNED for that rounding step; the reference's own
-  round-trip tolerances are what is checked.
+* MXFP8 / MXFP4: the ue8m0 scale rule (compute_tile_scale) and the scale decode
+  (e8m0_to_scale) are pinned against the reference's own C++ functions compiled
+  on the host (oracle/build_ref.py -> oracle/_ref, vectors in
+  tests/golden/mx.npz: 36864 amax patterns x 3 formats, all 256 scale bytes);
+  the dequantizer against the reference's torch `_dequant_mxfp8`; the padded
+  row-wise / column-wise / batched layouts against `mxfp8_padded_ref` /
+  `mxfp4_padded_ref` of the reference's tests.  The final fp32 -> fp8 / fp4
+  rounding is done in the reference by AMD CDNA4 convert instructions whose
+  tie rule is in no source file of the reference; the oracle assumes IEEE
+  round-to-nearest-even then saturate-to-finite (the OCP MX rule).  PARITY
+  UNPINNED for that one step (the convert's tie rule); the reference's own
+  round-trip tolerances are what is checked there.
 """

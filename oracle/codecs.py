@@ -113,9 +113,10 @@ def e8m0_to_f32(byte) -> np.ndarray:
 
 
 def e8m0_decode(byte) -> np.ndarray:
-    """Dequantize-side value of a ue8m0 byte: exp2(byte - 127) (device/utils.cuh:124-126)."""
-    b = np.asarray(byte, dtype=np.int32)
-    return np.ldexp(np.float32(1.0), b - 127).astype(np.float32)
+    """Dequantize-side value of a ue8m0 byte: (byte << 23) reinterpreted as float32 (device/utils.cuh:124-126), i.e.
+    2^(byte - 127) for bytes 1..254, 0.0 for byte 0 and +inf for byte 255.  Pinned for all 256 bytes by
+    tests/golden/mx.npz (the reference's e8m0_to_scale compiled on the host)."""
+    return e8m0_to_f32(byte)
 
 
 def mx_scale_from_amax(amax, fmt: str):

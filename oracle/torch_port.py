@@ -39,17 +39,29 @@ def mx_dequantize_rows(q: torch.Tensor, byte: torch.Tensor) -> torch.Tensor:
     return (q.to(torch.float32).reshape(R, C // 32, 32) * s.unsqueeze(2)).reshape(R, C)
 
 
+def mx_weight_prepare(w: torch.Tensor, fmt: str = "e4m3") -> torch.Tensor:
+    """The weight half of the MX forward: dual (row + transposed col) quantization of w [N, K] with 2-D block scales;
+    returns the dequantized row-wise copy the GEMM consumes (the col-wise copy is what backward would read)."""
+    wf = w.float()
+    w_row = mx_quantize_rows(wf, fmt, use_2d_block=True)
+    _w_col = mx_quantize_rows(wf.t().contiguous(), fmt, use_2d_block=True)
+    return mx_dequantize_rows(*w_row)
+
+
+def mx_activation_forward(a: torch.Tensor, w_deq: torch.Tensor, fmt: str = "e4m3") -> torch.Tensor:
+    """The activation half: dual MX quantization of a [M, K], then dequant(a_row) . w_deq^T in fp32, returned as bf16.
+    Every part of it is linear in the number of activation rows."""
+    af = a.float()
+    a_row = mx_quantize_rows(af, fmt)
+    _a_col = mx_quantize_rows(af.t().contiguous(), fmt)
+    return (mx_dequantize_rows(*a_row) @ w_deq.t()).to(torch.bfloat16)
+
+
 def mx_linear_forward(a: torch.Tensor, w: torch.Tensor, fmt: str = "e4m3") -> torch.Tensor:
     """The reference's MX forward (primus_turbo/pytorch/ops/gemm_fp8.py:558-654) on the CPU: dual (row +
     transposed col) MX quantization of a [M, K] and of w [N, K] (2-D block scales), then
     out = dequant(a_row) . dequant(w_row)^T accumulated in fp32, returned as bf16."""
-    af, wf = a.float(), w.float()
-    a_row = mx_quantize_rows(af, fmt)
-    _a_col = mx_quantize_rows(af.t().contiguous(), fmt)
-    w_row = mx_quantize_rows(wf, fmt, use_2d_block=True)
-    _w_col = mx_quantize_rows(wf.t().contiguous(), fmt, use_2d_block=True)
-    out = mx_dequantize_rows(*a_row) @ mx_dequantize_rows(*w_row).t()
-    return out.to(torch.bfloat16)
+    return mx_activation_forward(a, mx_weight_prepare(w, fmt), fmt)
 
 
 def tensorwise_quantize(x: torch.Tensor, fmt: str):

@@ -136,11 +136,10 @@ template <int FMT> struct FmtMax;
 template <> struct FmtMax<PT_E4M3> { static constexpr float value = 448.f; };
 template <> struct FmtMax<PT_E5M2> { static constexpr float value = 57344.f; };
 
-// x * scale, to be fed to a saturating convert.  The reference clamps the product to +-qmax first
-// (fmax(fmin(x * scale, qmax), -qmax)); cvt.rn.satfinite does the same to every non-NaN product, so the two compare
-// instructions per element are left out (they were the largest share of the blockwise quantizer's ALU-pipe load).
-// The one difference: a NaN product, which the reference's fmin / fmax pair turns into +qmax, becomes the NaN code.
-template <int FMT> __device__ __forceinline__ float mul_sat(float x, float scale) { return x * scale; }
+// fmin(x * scale, qmax), to be fed to a saturating convert.  The reference clamps the product to +-qmax
+// (fmax(fmin(x * scale, qmax), -qmax)); cvt.rn.satfinite clamps every non-NaN product itself, so only the half of the
+// clamp that decides what a NaN becomes is kept: fmin(NaN, qmax) = qmax, as in the reference.
+template <int FMT> __device__ __forceinline__ float mul_sat(float x, float scale) { return fminf(x * scale, FmtMax<FMT>::value); }
 // scale = qmax / fmax(amax, eps), a true (correctly rounded) division
 template <int FMT> __device__ __forceinline__ float scale_from_amax(float amax, float eps) {
     return __fdiv_rn(FmtMax<FMT>::value, fmaxf(amax, eps));

@@ -9,7 +9,7 @@
 // quantization_mxfp4.cu:91-227 of the reference:
 //   e    = (((bits(amax) + (1 << (22 - mbits))) >> 23) & 0x1FF) - 127 - emax_target, clamped to [-127, 128]
 //   byte = e + 127, scale = 2^e
-//   fp8:  q = rne(clamp(v, +-qmax * scale) / scale)        fp4: q = rne_sat(v / scale)
+//   fp8:  q = rne(clamp(v, +-qmax * scale) / scale)  (a NaN becomes -qmax)        fp4: q = rne_sat(v / scale)
 // A block whose scale byte is 0 (every |v| < 2^-118 or so) is written as zeros.
 #include <algorithm>
 
@@ -60,10 +60,11 @@ template <int FMT> __device__ __forceinline__ uint2 mx_encode8(const float (&v)[
         o.x = (uint32_t) cvt2_e2m1(t[0], t[1]) | ((uint32_t) cvt2_e2m1(t[2], t[3]) << 8) |
               ((uint32_t) cvt2_e2m1(t[4], t[5]) << 16) | ((uint32_t) cvt2_e2m1(t[6], t[7]) << 24);
     } else {
-        // the reference clamps to +-qmax * scale first; the saturating convert below does the same for every
-        // non-NaN input (a NaN converts to the NaN code instead of -qmax)
+        // the reference clamps to +-qmax * scale first (fmin(fmax(v, -lim), lim)); the saturating convert below does
+        // that for every non-NaN input, so only the half that decides what a NaN becomes is kept: fmax(NaN, -lim) = -lim
+        const float nlim = -MxParams<FMT>::qmax * s.native;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) t[i] = v[i] * s.inv;
+        for (int i = 0; i < 8; ++i) t[i] = fmaxf(v[i], nlim) * s.inv;
         o.x = cvt4_fp8<FMT>(t[0], t[1], t[2], t[3]);
         o.y = cvt4_fp8<FMT>(t[4], t[5], t[6], t[7]);
     }
@@ -283,8 +284,8 @@ constexpr int kQThreads = 32 * (1 + kQConsumerWarps);
 constexpr int kQSmemBytes = kQStages * kQTileBytes + 1024 + 1024;
 constexpr int kQMaxGroups = 256;  // grouped form: offset tables of up to this many groups are held in shared memory
 
-// 32 scaled values -> 32 fp8 codes (8 words) or 32 fp4 codes (4 words).  The reference's soft clamp to +-qmax*scale
-// is subsumed by the saturating convert (identical bytes for every non-NaN input; a NaN converts to the NaN code).
+// 32 scaled values -> 32 fp8 codes (8 words) or 32 fp4 codes (4 words).  Of the reference's soft clamp to +-qmax*scale
+// only fmax(v, -lim) is kept (it sends a NaN to -qmax as the reference does); the saturating convert does the rest.
 template <int FMT> __device__ __forceinline__ void mx_encode32(const float (&v)[32], const MxScale &s, uint32_t (&w)[8]) {
     if (s.byte == 0) {
 #pragma unroll
@@ -299,9 +300,11 @@ template <int FMT> __device__ __forceinline__ void mx_encode32(const float (&v)[
                    ((uint32_t) cvt2_e2m1(t[4] * s.inv, t[5] * s.inv) << 16) | ((uint32_t) cvt2_e2m1(t[6] * s.inv, t[7] * s.inv) << 24);
         }
     } else {
+        const float nlim = -MxParams<FMT>::qmax * s.native;
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-            w[i] = cvt4_fp8<FMT>(v[4 * i] * s.inv, v[4 * i + 1] * s.inv, v[4 * i + 2] * s.inv, v[4 * i + 3] * s.inv);
+            w[i] = cvt4_fp8<FMT>(fmaxf(v[4 * i], nlim) * s.inv, fmaxf(v[4 * i + 1], nlim) * s.inv,
+                                 fmaxf(v[4 * i + 2], nlim) * s.inv, fmaxf(v[4 * i + 3], nlim) * s.inv);
     }
 }
 
@@ -620,7 +623,8 @@ __global__ void __launch_bounds__(256) mx_dequant_kernel(const uint8_t *__restri
             code = q[r * cols_stored + c];
         }
         const int sb = s[r * (cols_stored / 32) + c / 32];
-        const float sc = __uint_as_float(sb == 255 ? 0x7FC00000u : (sb == 0 ? 0x00400000u : (uint32_t) sb << 23));
+        // e8m0_to_scale of the reference (device/utils.cuh:124-126): byte << 23 reinterpreted; byte 0 is 0.0, byte 255 +inf
+        const float sc = __uint_as_float((uint32_t) sb << 23);
         const float val = decode_code(fmt, code) * sc;
         put_out(y + (transpose_out ? c * rows + r : i), val);
     }

@@ -73,11 +73,21 @@ class ColumnShardedLinear:
         return self._gemm(x)
 
     def gather(self, y_local: torch.Tensor) -> torch.Tensor:
-        """[M, n_local] on every rank -> [M, N] on every rank."""
+        """[M, n_local] on every rank -> [M, N] on every rank.
+
+        Equal shards (the usual case: N / world a multiple of 128) are gathered as rank-major blocks
+        [world, M, n_local] by one all_gather and returned as a permuted VIEW of that buffer ([M, world, n_local]
+        flattened to [M, N] is not contiguous; consumers that need contiguity call .contiguous() themselves).
+        Ragged shards go through a padded gather of the transposed shard."""
         if self.world == 1:
             return y_local
         M = y_local.shape[0]
         widths = [column_shard(self.n_total, self.world, r) for r in range(self.world)]
+        if len({h - l for l, h in widths}) == 1:
+            n_local = self.hi - self.lo
+            recv = y_local.new_empty((self.world * M, n_local))
+            dist.all_gather_into_tensor(recv, y_local.contiguous(), group=self.group)
+            return recv.view(self.world, M, n_local).permute(1, 0, 2).reshape(M, self.world * n_local)
         wmax = max(h - l for l, h in widths)
         # gather transposed so that each rank contributes a contiguous row block of y^T
         send = y_local.new_zeros((wmax, M))
@@ -87,6 +97,63 @@ class ColumnShardedLinear:
         parts = [recv[r * wmax: r * wmax + (h - l)] for r, (l, h) in enumerate(widths)]
         return torch.cat(parts, dim=0).t().contiguous()
 
+    def gather_buffer(self, M: int, dtype, device) -> torch.Tensor:
+        """Rank-major gather buffer [world, M, n_local] for equal shards; forward_into() lets the GEMM write this
+        rank's block in place, so the gather needs no send copy."""
+        return torch.empty((self.world, M, self.hi - self.lo), dtype=dtype, device=device)
+
+    def forward_into(self, x: torch.Tensor, buf: torch.Tensor) -> torch.Tensor:
+        """forward() whose result lands in this rank's block of a gather_buffer().  Without autograd and with the MX
+        recipe only the row-wise quantized copies are made (the transposed ones exist for backward) and the GEMM
+        writes the block itself; other recipes (and the `op` hook) run forward() and copy."""
+        slot = buf[self.rank]
+        from ..core.low_precision import ScalingGranularity, ScalingRecipe
+        cfg = self.config
+        if self._op is None and cfg is not None and cfg.granularity == ScalingGranularity.MX_BLOCKWISE and not torch.is_grad_enabled():
+            from ..kernels.gemm.gemm_fp8_impl import gemm_fp8_impl
+            from ..kernels.quantization.quantization_impl import quantize_mxfp8_impl
+            from ..ops.utils import _get_fp8_dtype
+            dt = _get_fp8_dtype(cfg.format, True)
+            two_d = ScalingRecipe(use_2d_block=True)
+            a_row, a_s = quantize_mxfp8_impl(x, dt, 1, cfg.block_size)
+            b_row, b_s = quantize_mxfp8_impl(self.weight, dt, 1, cfg.block_size, scaling_recipe=two_d)
+            gemm_fp8_impl(a_row, a_s, False, b_row, b_s, True, slot.dtype, False, cfg.granularity, out=slot)
+        else:
+            slot.copy_(self.forward(x))
+        return slot
+
+    def gather_in_place(self, buf: torch.Tensor) -> torch.Tensor:
+        """All-gathers `buf` ([world, M, n_local], this rank's block already written by the caller) in place."""
+        if self.world > 1:
+            dist.all_gather_into_tensor(buf.view(-1, buf.shape[-1]), buf[self.rank], group=self.group)
+        return buf
+
+    # ---- backward, each GEMM sharded along ITS OWN output columns so that no reduction is needed:
+    #   wgrad  dW[lo:hi]      = dY[:, lo:hi]^T . X        (the columns of dY this rank produced in forward; stays sharded)
+    #   dgrad  dX[:, k0:k1]   = dY . W[:, k0:k1]          (needs the full dY and a K-slice of the full weight)
+    def wgrad(self, x: torch.Tensor, dy_local: torch.Tensor, op: Optional[Callable] = None) -> torch.Tensor:
+        """[n_local, K] gradient of this rank's weight rows; `op(dy_local, x)` defaults to the FP8 operator's own
+        backward (autograd through forward())."""
+        if op is not None:
+            return op(dy_local, x)
+        w = self.weight.detach().requires_grad_(True)
+        from ..ops.gemm_fp8 import gemm_fp8
+        y = gemm_fp8(x, w, trans_b=True, config=self.config)
+        (gw,) = torch.autograd.grad(y, w, dy_local)
+        return gw
+
+    @staticmethod
+    def dgrad_shard(k_total: int, world: int, rank: int) -> Tuple[int, int]:
+        """[k0, k1) of input features whose gradient `rank` computes."""
+        return column_shard(k_total, world, rank)
+
+    def dgrad(self, dy_full: torch.Tensor, weight_kslice: torch.Tensor, op: Optional[Callable] = None) -> torch.Tensor:
+        """dX[:, k0:k1] = dY [M, N] . W[:, k0:k1] for this rank's K-slice of the FULL weight ([N, k1 - k0])."""
+        if op is not None:
+            return op(dy_full, weight_kslice)
+        from ..ops.gemm_fp8 import gemm_fp8
+        return gemm_fp8(dy_full, weight_kslice, trans_b=False, config=self.config)
+
 
 class ExpertShardedGroupedLinear:
     """Grouped GEMM with the experts sharded across ranks: rank r owns experts [g_lo, g_hi) and, because groups are
@@ -94,7 +161,8 @@ class ExpertShardedGroupedLinear:
     caller's business; forward() takes this rank's rows only.
     """
 
-    def __init__(self, num_experts: int, weight_shard: torch.Tensor, group=None, op: Optional[Callable] = None, config=None):
+    def __init__(self, num_experts: int, weight_shard: torch.Tensor, group=None, op: Optional[Callable] = None, config=None,
+                 cache_quantized_weight: bool = False):
         self.group = group
         self.world, self.rank = _world(group)
         self.num_experts = num_experts
@@ -103,12 +171,16 @@ class ExpertShardedGroupedLinear:
         self.weight = weight_shard
         self.config = config
         self._op = op
+        self._qcache = None
+        if cache_quantized_weight:
+            from ..modules._weight_cache import QuantizedWeightCache
+            self._qcache = QuantizedWeightCache()
 
     @classmethod
-    def from_full_weight(cls, weight: torch.Tensor, group=None, op=None, config=None):
+    def from_full_weight(cls, weight: torch.Tensor, group=None, op=None, config=None, cache_quantized_weight=False):
         world, rank = _world(group)
         lo, hi = expert_shard(weight.shape[0], world, rank)
-        return cls(weight.shape[0], weight[lo:hi].contiguous(), group, op, config)
+        return cls(weight.shape[0], weight[lo:hi].contiguous(), group, op, config, cache_quantized_weight)
 
     def local_rows(self, group_lens_all: List[int]) -> Tuple[int, int]:
         """Row range of the packed token matrix that belongs to this rank's experts."""
@@ -119,7 +191,12 @@ class ExpertShardedGroupedLinear:
         if self._op is not None:
             return self._op(x_local, self.weight, group_lens_local)
         from ..ops.grouped_gemm_fp8 import grouped_gemm_fp8
-        return grouped_gemm_fp8(x_local, self.weight, group_lens_local, trans_b=True, config=self.config)
+        w = self.weight
+        if self._qcache is not None:   # the experts' quantized copies are reused until the weight changes
+            from ..ops.utils import _get_fp8_dtype
+            w = self._qcache.get(self.weight, _get_fp8_dtype(self.config.format, True), self.config,
+                                 need_transpose=False)
+        return grouped_gemm_fp8(x_local, w, group_lens_local, trans_b=True, config=self.config)
 
     def gather(self, y_local: torch.Tensor, group_lens_all: List[int]) -> torch.Tensor:
         """Concatenates every rank's rows in expert order on every rank (padded all_gather)."""

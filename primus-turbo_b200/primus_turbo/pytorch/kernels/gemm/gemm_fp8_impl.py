@@ -103,7 +103,9 @@ def _launch(a_km, a_s, b_km, b_s, out, gran, beta, block_n=0):
     return out
 
 
-def _gemm(a, a_scale_inv, trans_a, b, b_scale_inv, trans_b, out_dtype, trans_c, granularity, out=None, block_n=0):
+def _gemm(a, a_scale_inv, trans_a, b, b_scale_inv, trans_b, out_dtype, trans_c, granularity, out=None, block_n=0,
+          accumulate=True):
+    """`out` given: accumulate into it (beta = 1), or overwrite it when accumulate is False."""
     nv.require_cuda(a, b, a_scale_inv, b_scale_inv)
     assert a.dim() == 2 and b.dim() == 2, "Only 2D tensors are supported"
     gran = _as_gran(granularity)
@@ -121,7 +123,8 @@ def _gemm(a, a_scale_inv, trans_a, b, b_scale_inv, trans_b, out_dtype, trans_c, 
             b_op = (_k_major(b, not trans_b), 0) + tuple(_k_major(b, not trans_b).shape)
         beta = 0.0
         if out is not None:
-            beta = 1.0
+            beta = 1.0 if accumulate else 0.0
+            assert out.is_contiguous() and tuple(out.shape) == ((N, M) if trans_c else (M, N))
         else:
             out = torch.empty((N, M) if trans_c else (M, N), dtype=out_dtype, device=a.device)
         if trans_c:
@@ -140,7 +143,7 @@ def _gemm(a, a_scale_inv, trans_a, b, b_scale_inv, trans_b, out_dtype, trans_c, 
     M, N = a_km.shape[0], b_km.shape[0]
     beta = 0.0
     if out is not None:
-        beta = 1.0
+        beta = 1.0 if accumulate else 0.0
         assert out.is_contiguous() and tuple(out.shape) == ((N, M) if trans_c else (M, N))
     else:
         out = torch.empty((N, M) if trans_c else (M, N), dtype=out_dtype, device=a.device)
@@ -150,9 +153,12 @@ def _gemm(a, a_scale_inv, trans_a, b, b_scale_inv, trans_b, out_dtype, trans_c, 
 
 
 def gemm_fp8_impl(a, a_scale_inv, trans_a, b, b_scale_inv, trans_b, out_dtype, trans_c, granularity,
-                  default_backend=0, block_n=0):
-    """C = op(A) . op(B) (optionally transposed). `default_backend` is accepted and ignored: there is one back end."""
-    return _gemm(a, a_scale_inv, trans_a, b, b_scale_inv, trans_b, out_dtype, trans_c, granularity, None, block_n)
+                  default_backend=0, block_n=0, out=None):
+    """C = op(A) . op(B) (optionally transposed). `default_backend` is accepted and ignored: there is one back end.
+    `out` (contiguous, result shape and dtype) is written instead of a fresh tensor: a caller that owns a larger buffer
+    (a gather buffer, a preallocated activation) passes the slot the result belongs in."""
+    return _gemm(a, a_scale_inv, trans_a, b, b_scale_inv, trans_b, out_dtype if out is None else out.dtype, trans_c,
+                 granularity, out, block_n, accumulate=False)
 
 
 def gemm_fp8_accum_impl(a, a_scale_inv, trans_a, b, b_scale_inv, trans_b, out, trans_c, granularity, default_backend=0):

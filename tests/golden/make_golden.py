@@ -25,6 +25,18 @@ scale can sit one ulp from the kernel's.  The fixture therefore also stores the 
 given that scale, while the scale itself is pinned to one ulp.  The Triton blockwise kernels
 divide truly and pin the scale formula bit for bit.
 
+* MX (mx.npz): three more pieces of the reference run here.  (1) `compute_tile_scale`
+  (csrc/kernels/quantization/quantization_mxfp8.cu:68-105, quantization_mxfp4.cu:149-181) and
+  `e8m0_to_scale` (csrc/include/primus_turbo/device/utils.cuh:124-126), compiled on the host by
+  oracle/build_ref.py: ue8m0 bytes and native scales for every non-negative bf16 bit pattern and
+  4096 float32 patterns as block amax, for e4m3 / e5m2 / e2m1, and the decode of all 256 scale
+  bytes.  (2) `_dequant_mxfp8` (tests/pytorch/modules/test_mega_moe_mxfp8.py:57-62), a torch
+  dequantizer, run on random code / scale bytes.  (3) `mxfp8_padded_ref` / `mxfp4_padded_ref`
+  (tests/pytorch/ops/test_quantization.py:288-340), which fix the zero-padded layouts of the row-wise,
+  column-wise and batched outputs.  The two test helpers are taken out of their files by name (the files
+  import the reference package, which cannot be imported without a GPU) and executed unchanged.
+  What stays unpinned is the final fp32 -> fp8 / fp4 rounding of an AMD convert instruction.
+
 The fixtures hold inputs (as uint16 bf16 bit patterns or float32) and the
 reference outputs (raw fp8 bytes, float32 scales) in one .npz per family.
 """
@@ -171,6 +183,66 @@ def blockwise(out):
     print("blockwise.npz", n, "cases")
 
 
+def _functions_from(path, names):
+    """Executes the named top-level functions of a reference test file (and nothing else of it) in a namespace that
+    provides torch; returns the namespace."""
+    import ast
+    src = open(path).read()
+    tree = ast.parse(src)
+    keep = [n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name in names]
+    assert len(keep) == len(names), f"{path}: expected functions {names}"
+    ns = {"torch": torch, "_MXFP8_BLOCK": 32}
+    exec(compile(ast.Module(body=keep, type_ignores=[]), path, "exec"), ns)
+    return ns
+
+
+def mx(out):
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from oracle import build_ref
+    build_ref.build(REF)
+    lib = build_ref.load()
+    flat = {}
+    # (1) scale rule: every non-negative bf16 pattern (incl. inf / NaN patterns) + float32 patterns with low bits set
+    rng = np.random.default_rng(44)
+    amax_bits = np.concatenate([np.arange(0x8000, dtype=np.uint32) << 16,
+                                rng.integers(0, 0x7F800000, size=4096, dtype=np.uint32)])
+    flat["scale_amax_bits"] = amax_bits
+    for fmt in ("e4m3", "e5m2", "e2m1"):
+        byte, native = build_ref.tile_scale(lib, fmt, amax_bits.view(np.float32))
+        flat[f"scale_byte_{fmt}"] = byte
+        flat[f"scale_native_bits_{fmt}"] = native.view(np.uint32)
+    dec = np.empty(256, dtype=np.float32)
+    allb = np.arange(256, dtype=np.uint8)
+    lib.ref_e8m0_to_scale(allb.ctypes.data, 256, dec.ctypes.data)
+    flat["e8m0_decode_bits"] = dec.view(np.uint32)
+    # (2) the reference's torch dequantizer on random codes and scale bytes (NaN codes excluded: NaN != NaN)
+    deq = _functions_from(os.path.join(REF, "tests/pytorch/modules/test_mega_moe_mxfp8.py"), ["_dequant_mxfp8"])["_dequant_mxfp8"]
+    for fmt, dt in (("e4m3", torch.float8_e4m3fn), ("e5m2", torch.float8_e5m2)):
+        codes = rng.integers(0, 256, size=(16, 256), dtype=np.uint8)
+        if fmt == "e4m3":
+            codes[(codes & 0x7F) == 0x7F] = 0x3A
+        else:
+            codes[(codes & 0x7C) == 0x7C] = 0x3A
+        sbytes = rng.integers(90, 160, size=(16, 8), dtype=np.uint8)
+        y = deq(torch.from_numpy(codes).view(dt), torch.from_numpy(sbytes))
+        flat[f"deq_codes_{fmt}"], flat[f"deq_scales_{fmt}"], flat[f"deq_out_{fmt}"] = codes, sbytes, y.numpy().copy()
+    # (3) padded layouts
+    pads = _functions_from(os.path.join(REF, "tests/pytorch/ops/test_quantization.py"), ["padding_size", "mxfp8_padded_ref", "mxfp4_padded_ref"])
+    gen = torch.Generator().manual_seed(45)
+    n = 0
+    for name in ("mxfp8_padded_ref", "mxfp4_padded_ref"):
+        for shape, axis in (((33, 64), 0), ((33, 64), 1), ((130, 96), 0), ((130, 96), 1), ((2, 40, 64), 1), ((2, 40, 64), 2)):
+            x = torch.randn(*shape, generator=gen).to(torch.bfloat16)
+            ref = pads[name](x, axis, 128, torch.bfloat16)
+            flat.update({f"pad{n}_fn": np.asarray(name), f"pad{n}_axis": np.asarray(axis), f"pad{n}_x_bf16": bf16_bits(x),
+                         f"pad{n}_ref_bf16": bf16_bits(ref.contiguous())})
+            n += 1
+    flat["n_pad"] = np.asarray(n)
+    np.savez_compressed(os.path.join(out, "mx.npz"), **flat)
+    print("mx.npz", n, "padded-layout cases,", amax_bits.size, "amax patterns x 3 formats")
+
+
 if __name__ == "__main__":
     tensor_row(HERE)
     blockwise(HERE)
+    mx(HERE)

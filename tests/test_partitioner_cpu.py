@@ -55,10 +55,58 @@ def _worker(rank, world, port):
         y_loc = ex.forward(xe[r0:r1], torch.tensor(lens[ex.g_lo:ex.g_hi]))
         y_all = ex.gather(y_loc, lens)
         assert torch.allclose(y_all, _grouped_ref(xe, we, torch.tensor(lens)), atol=1e-5), "expert gather differs"
-        # a rank that raises before the collective must not hang the others: checked on the host with a barrier timeout
+        # equal shards: the rank-major buffer is gathered in place and viewed as [M, N]
+        w2 = torch.randn(128 * world * 2, 64, generator=g)
+        lin2 = ColumnShardedLinear.from_full_weight(w2, op=lambda a, b: a @ b.t())
+        buf = lin2.gather_buffer(x.shape[0], x.dtype, x.device)
+        lin2.forward_into(x, buf)
+        full = lin2.gather_in_place(buf).permute(1, 0, 2).reshape(x.shape[0], -1)
+        assert torch.allclose(full, x @ w2.t(), atol=1e-5), "in-place gather differs"
+        assert torch.allclose(lin2.gather(lin2.forward(x)), x @ w2.t(), atol=1e-5), "equal-shard gather differs"
+        # backward shards: each GEMM is split along its own output columns, so no rank needs a reduction
+        dy = torch.randn(37, w2.shape[0], generator=g)
+        gw = lin2.wgrad(x, dy[:, lin2.lo:lin2.hi], op=lambda d, a: d.t() @ a)
+        assert torch.allclose(gw, (dy.t() @ x)[lin2.lo:lin2.hi], atol=1e-4), "sharded wgrad differs"
+        k0, k1 = lin2.dgrad_shard(64, world, dist.get_rank())
+        gx = lin2.dgrad(dy, w2[:, k0:k1], op=lambda d, ws: d @ ws)
+        assert torch.allclose(gx, (dy @ w2)[:, k0:k1], atol=1e-4), "sharded dgrad differs"
         dist.barrier()
     finally:
         dist.destroy_process_group()
+
+
+def _failing_worker(rank, world, port, out_dir):
+    """Rank 1 raises before the collective; rank 0 must get an error from its all_gather (not hang) and say so."""
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=10))
+    w = torch.randn(256, 16)
+    lin = ColumnShardedLinear.from_full_weight(w, op=lambda a, b: a @ b.t())
+    y = lin.forward(torch.randn(4, 16))
+    dist.barrier()
+    if rank == 1:
+        raise RuntimeError("injected failure before the gather")
+    try:
+        lin.gather(y)
+        outcome = "gather returned"
+    except Exception as exc:  # noqa: BLE001
+        outcome = "gather failed: " + type(exc).__name__
+    with open(os.path.join(out_dir, "rank0.txt"), "w") as f:
+        f.write(outcome)
+
+
+def test_rank_that_raises_before_the_collective(tmp_path):
+    """Host-side failure detection: the surviving rank's collective ends with an error within the group's timeout."""
+    ctx = mp.get_context("spawn")
+    port = 29900 + (os.getpid() % 90)
+    procs = [ctx.Process(target=_failing_worker, args=(r, 2, port, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=90)
+    assert all(not p.is_alive() for p in procs), "a rank hung after its peer failed"
+    assert procs[1].exitcode != 0
+    assert (tmp_path / "rank0.txt").read_text().startswith("gather failed"), (tmp_path / "rank0.txt").read_text()
 
 
 @pytest.mark.parametrize("world", [2, 3])

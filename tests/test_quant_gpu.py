@@ -215,28 +215,48 @@ def test_errors_are_reported(qi):
 
 
 @pytest.mark.parametrize("dtype", FP8)
-def test_nan_input_becomes_the_nan_code_and_leaves_the_rest_alone(qi, dtype):
-    """Documented difference from the reference: a NaN element does not take part in the amax (as there) and converts
-    to the format's NaN code (there: +qmax, through its fmin / fmax clamp); every other byte and every scale equals
-    the quantization of the same tensor with the NaN replaced by zero."""
+def test_nan_and_inf_inputs_follow_the_reference_clamp(qi, dtype):
+    """A NaN element takes no part in the amax and leaves through the reference's clamp: fmax(fmin(NaN, qmax), -qmax) =
+    +qmax for tensorwise / rowwise / blockwise (device/quant_utils.cuh:33-40), fmin(fmax(NaN, -lim), lim) = -qmax for MX
+    (quantization_mxfp8.cu:131-136); +-inf saturate to +-qmax.  Bytes and scales equal the oracle's, which applies the
+    same two clamps."""
+    fmt = fmt_of(dtype)
     x = make((256, 256), torch.bfloat16, 21, "normal")
     x[3, 5] = float("nan")
-    clean = x.clone()
-    clean[3, 5] = 0
-    pairs = [
-        (qi.quantize_fp8_tensorwise_impl(x, dtype), qi.quantize_fp8_tensorwise_impl(clean, dtype)),
-        (qi.quantize_fp8_rowwise_impl(x, dtype, -1), qi.quantize_fp8_rowwise_impl(clean, dtype, -1)),
-        (qi.quant_fp8_blockwise_impl(x, dtype, 1), qi.quant_fp8_blockwise_impl(clean, dtype, 1)),
-        (qi.quant_fp8_blockwise_impl(x, dtype, 0), qi.quant_fp8_blockwise_impl(clean, dtype, 0)),
-        (qi.quantize_mxfp8_impl(x, dtype, 1, 32), qi.quantize_mxfp8_impl(clean, dtype, 1, 32)),
-    ]
-    for (q, s), (qc, sc) in pairs:
-        assert torch.equal(s.reshape(-1).view(torch.uint8), sc.reshape(-1).view(torch.uint8))
-        assert bool(torch.isnan(q[3, 5].float()))
-        qb, qcb = q.view(torch.uint8).clone(), qc.view(torch.uint8).clone()
-        qb[3, 5] = 0
-        qcb[3, 5] = 0
-        assert torch.equal(qb, qcb)
+    x[200, 17] = float("nan")
+    xf = f32(x)
+    for name, got, want in [
+        ("tensorwise", qi.quantize_fp8_tensorwise_impl(x, dtype), oq.quantize_fp8_tensorwise(xf, fmt)),
+        ("rowwise", qi.quantize_fp8_rowwise_impl(x, dtype, -1), oq.quantize_fp8_rowwise(xf, fmt, -1)),
+        ("colwise", qi.quantize_fp8_rowwise_impl(x, dtype, -2), oq.quantize_fp8_rowwise(xf, fmt, -2)),
+        ("blockwise row", qi.quant_fp8_blockwise_impl(x, dtype, 1), oq.quantize_fp8_blockwise(xf, fmt, 1)),
+        ("blockwise col", qi.quant_fp8_blockwise_impl(x, dtype, 0), oq.quantize_fp8_blockwise(xf, fmt, 0)),
+        ("mx row", qi.quantize_mxfp8_impl(x, dtype, 1, 32), oq.quantize_mx(xf, fmt, 1)),
+        ("mx col", qi.quantize_mxfp8_impl(x, dtype, 0, 32), oq.quantize_mx(xf, fmt, 0)),
+    ]:
+        assert_bits_equal(u8(got[0]), want[0], name + " bytes")
+        if name.startswith("mx"):
+            assert_bits_equal(u8(got[1]), want[1], name + " scales")
+        else:
+            np.testing.assert_array_equal(f32(got[1]).reshape(-1), np.asarray(want[1], dtype=np.float32).reshape(-1), err_msg=name)
+    qmax_code = {"e4m3": 0x7E, "e5m2": 0x7B}[fmt]
+    assert int(u8(qi.quantize_fp8_rowwise_impl(x, dtype, -1)[0])[3, 5]) == qmax_code          # NaN -> +qmax
+    assert int(u8(qi.quantize_mxfp8_impl(x, dtype, 1, 32)[0])[3, 5]) == (qmax_code | 0x80)    # NaN -> -qmax (MX)
+    # dual outputs see the same NaN handling in both copies
+    qr, sr, qc, sc = qi.quantize_mxfp8_impl(x, dtype, None, 32, with_trans=True)
+    assert_bits_equal(u8(qr), oq.quantize_mx(xf, fmt, 1)[0], "mx dual row bytes")
+    assert_bits_equal(u8(qc), oq.quantize_mx(xf, fmt, 0)[0], "mx dual col bytes")
+    # +-inf: the block's amax is inf (scale byte from the exponent field 255), the elements saturate
+    y = make((128, 128), torch.bfloat16, 22, "normal")
+    y[1, 2] = float("inf")
+    y[70, 90] = float("-inf")
+    got = qi.quantize_fp8_rowwise_impl(y, dtype, -1)
+    want = oq.quantize_fp8_rowwise(f32(y), fmt, -1)
+    assert_bits_equal(u8(got[0]), want[0], "rowwise bytes with inf")
+    got = qi.quantize_mxfp8_impl(y, dtype, 1, 32)
+    want = oq.quantize_mx(f32(y), fmt, 1)
+    assert_bits_equal(u8(got[0]), want[0], "mx bytes with inf")
+    assert_bits_equal(u8(got[1]), want[1], "mx scales with inf")
 
 
 def test_mx_row_copy_at_a_16_byte_aligned_output(qi):
