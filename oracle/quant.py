@@ -15,6 +15,21 @@ from .codecs import (E2M1, E4M3, E5M2, FP8_MAX, decode, e8m0_decode, encode,
 F32 = np.float32
 
 
+def _amax(a: np.ndarray, axis=None, keepdims=False):
+    """max |a| as the kernels take it: fmaxf(fabsf(x), fabsf(y)) (device/reduce.cuh:119-125, quantization_mxfp8.cu amax
+    loops), which returns the other operand when one is NaN -- a NaN element takes no part in the maximum."""
+    a = np.abs(a)
+    if axis is None:
+        return np.fmax.reduce(a.reshape(-1), initial=F32(0)) if a.size else F32(0)
+    axes = (axis,) if isinstance(axis, int) else tuple(sorted((ax % a.ndim for ax in axis), reverse=True))
+    out = a
+    for ax in axes:
+        out = np.fmax.reduce(out, axis=ax, keepdims=True, initial=F32(0))
+    if not keepdims:
+        out = np.squeeze(out, axis=tuple(sorted(ax % a.ndim for ax in axes)))
+    return out
+
+
 def _ceil_to(x: int, a: int) -> int:
     return (x + a - 1) // a * a
 
@@ -40,7 +55,7 @@ def _scale_from_amax(amax, fmt: str, eps: float):
 def quantize_fp8_tensorwise(x: np.ndarray, fmt: str):
     """csrc/pytorch/quantization/quantization.cpp:44-90. Returns (q bytes, scale_inv 0-dim)."""
     x = np.asarray(x, dtype=F32)
-    amax = np.max(np.abs(x)) if x.size else F32(0)
+    amax = _amax(x)
     scale, scale_inv = _scale_from_amax(amax, fmt, 1e-12)
     return _quant_clamp_encode(x, scale, fmt), np.asarray(scale_inv, dtype=F32).reshape(())
 
@@ -50,7 +65,7 @@ def quantize_fp8_rowwise(x: np.ndarray, fmt: str, axis: int):
     Returns (q bytes same shape, scale_inv with `axis` reduced to 1)."""
     x = np.asarray(x, dtype=F32)
     axis = axis % x.ndim
-    amax = np.max(np.abs(x), axis=axis, keepdims=True)
+    amax = _amax(x, axis=axis, keepdims=True)
     scale, scale_inv = _scale_from_amax(amax, fmt, 1e-12)
     return _quant_clamp_encode(x, scale, fmt), scale_inv
 
@@ -71,7 +86,7 @@ def quantize_fp8_blockwise(x: np.ndarray, fmt: str, axis: int, block: int = 128)
         xp = np.zeros((M, nb * block), dtype=F32)
         xp[:, :N] = x
         blk = xp.reshape(M, nb, block)
-        amax = np.max(np.abs(blk), axis=2)
+        amax = _amax(blk, axis=2)
         scale, scale_inv = _scale_from_amax(amax, fmt, 1e-4)
         q = _quant_clamp_encode(blk, scale[:, :, None], fmt).reshape(M, nb * block)[:, :N]
         return np.ascontiguousarray(q), scale_inv
@@ -79,7 +94,7 @@ def quantize_fp8_blockwise(x: np.ndarray, fmt: str, axis: int, block: int = 128)
     xp = np.zeros((mb * block, N), dtype=F32)
     xp[:M] = x
     blk = xp.reshape(mb, block, N)
-    amax = np.max(np.abs(blk), axis=1)
+    amax = _amax(blk, axis=1)
     scale, scale_inv = _scale_from_amax(amax, fmt, 1e-4)
     q = _quant_clamp_encode(blk, scale[:, None, :], fmt).reshape(mb * block, N)[:M]
     return np.ascontiguousarray(q), scale_inv
@@ -104,7 +119,7 @@ def quantize_fp8_blockwise_weight(w: np.ndarray, fmt: str, block: int = 128):
     wp = np.zeros((B, mb * block, nb * block), dtype=F32)
     wp[:, :M, :N] = w
     t = wp.reshape(B, mb, block, nb, block)
-    amax = np.max(np.abs(t), axis=(2, 4))
+    amax = _amax(t, axis=(2, 4))
     scale, scale_inv = _scale_from_amax(amax, fmt, 1e-4)
     q = _quant_clamp_encode(t, scale[:, :, None, :, None], fmt).reshape(B, mb * block, nb * block)
     q = np.ascontiguousarray(q[:, :M, :N])
@@ -204,7 +219,7 @@ def _mx_quant_rows(xr: np.ndarray, fmt: str, tile_amax, zero_scale_byte: int, us
     blk = xr.reshape(R, C // 32, 32).astype(F32)
     if use_rht:
         blk = _rht16(blk)
-    amax = np.max(np.abs(blk), axis=2) if tile_amax is None else tile_amax
+    amax = _amax(blk, axis=2) if tile_amax is None else tile_amax
     byte, scale = mx_scale_from_amax(amax, fmt)
     if zero_scale_byte != 0:
         byte = np.where(amax == 0, np.uint8(zero_scale_byte), byte)
@@ -223,7 +238,7 @@ def _mx_quant_rows(xr: np.ndarray, fmt: str, tile_amax, zero_scale_byte: int, us
 def _tile_amax_2d(xp: np.ndarray) -> np.ndarray:
     """amax over 32x32 tiles of a [R32, C32] padded array -> [R32/32, C32/32]."""
     R, C = xp.shape
-    return np.max(np.abs(xp.reshape(R // 32, 32, C // 32, 32)), axis=(1, 3)).astype(F32)
+    return _amax(xp.reshape(R // 32, 32, C // 32, 32), axis=(1, 3)).astype(F32)
 
 
 def quantize_mx(x: np.ndarray, fmt: str, axis: int, use_2d_block: bool = False,

@@ -12,6 +12,7 @@
 //   fp8:  q = rne(clamp(v, +-qmax * scale) / scale)  (a NaN becomes -qmax)        fp4: q = rne_sat(v / scale)
 // A block whose scale byte is 0 (every |v| < 2^-118 or so) is written as zeros.
 #include <algorithm>
+#include <type_traits>
 
 #include "common.cuh"
 #include "gemm_common.cuh"
@@ -588,6 +589,385 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
     }
 }
 
+// ------------------------------------------------------------------------------------------------ warp-split form
+// The form used for bf16 inputs without the Hadamard option.  Same tiles and the same TMA input ring as
+// mx_quant_tma_kernel, but the eight consumer warps are split by output: four warps produce the row-wise copy (one
+// thread per tile row: two 32-element blocks read as eight 16-byte chunks), four produce the transposed copy (one
+// thread per column pair and 32-row band: a whole MX block of each of its two columns, so no value is exchanged between
+// threads and rows are read in order, every lane of a warp in the same tile row).  The transposed tile is assembled in
+// shared memory in the 128-byte (fp4: 64-byte) swizzled layout and written with one cp.async.bulk.tensor store per tile
+// from a double buffer, which frees the thread-to-element mapping from the shape of the global stores; the dense FP8
+// row copy leaves the same way, the grouped and the FP4 row copies with 32-byte stores per row.  Scaling is exact in
+// packed bf16 (the scale is a power of two), so one mul.bf16x2 scales two elements.  A block holding a NaN is found
+// with the NaN-propagating packed maximum and re-done on the slow path, which applies the reference's
+// fmax(v, -qmax * scale) to every element; all other blocks skip that clamp (the saturating convert covers it).
+constexpr int kSStages = 2;
+constexpr int kSCtasPerSm = 3;
+constexpr int kSGroupWarps = 4;                       // warps per output copy
+constexpr int kSGroupThreads = 32 * kSGroupWarps;
+constexpr int kSThreads = 32 * (1 + 2 * kSGroupWarps);
+constexpr int kSStageOutBytes = 8192;                 // one staged output tile (fp8: 128 x 64 bytes either way round)
+constexpr int kSSmemBytes = kSStages * kQTileBytes + 4 * kSStageOutBytes + 1024 + 1024;
+
+__device__ __forceinline__ uint32_t absmax2_nan_bf16(uint32_t m, uint32_t w) {
+    uint32_t r;
+    asm("max.NaN.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(m), "r"(w));
+    return r;
+}
+// either half of a packed bf16 |max| is a NaN
+__device__ __forceinline__ bool packed_bf16_has_nan(uint32_t pm) {
+    const uint32_t a = pm & 0x7FFF7FFFu;
+    return ((a & 0xFFFFu) > 0x7F80u) | ((a >> 16) > 0x7F80u);
+}
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t bf16_bits_x2(float lo, float hi) {
+    return (__float_as_uint(lo) >> 16) | (__float_as_uint(hi) & 0xFFFF0000u);
+}
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+// four floats -> four fp8 codes, a in the lowest byte
+template <int FMT> __device__ __forceinline__ uint32_t pack4_fp8(float a, float b, float c, float d) {
+    uint32_t r;
+    if constexpr (FMT == PT_E4M3)
+        asm("{ .reg .b16 x, y; cvt.rn.satfinite.e4m3x2.f32 x, %2, %1; cvt.rn.satfinite.e4m3x2.f32 y, %4, %3; mov.b32 %0, {x, y}; }"
+            : "=r"(r) : "f"(a), "f"(b), "f"(c), "f"(d));
+    else
+        asm("{ .reg .b16 x, y; cvt.rn.satfinite.e5m2x2.f32 x, %2, %1; cvt.rn.satfinite.e5m2x2.f32 y, %4, %3; mov.b32 %0, {x, y}; }"
+            : "=r"(r) : "f"(a), "f"(b), "f"(c), "f"(d));
+    return r;
+}
+// eight floats -> eight e2m1 codes, a in the lowest nibble
+__device__ __forceinline__ uint32_t pack8_e2m1(float a, float b, float c, float d, float e, float f, float g, float h) {
+    uint32_t r;
+    asm("{ .reg .b8 x, y, z, w; cvt.rn.satfinite.e2m1x2.f32 x, %2, %1; cvt.rn.satfinite.e2m1x2.f32 y, %4, %3;"
+        " cvt.rn.satfinite.e2m1x2.f32 z, %6, %5; cvt.rn.satfinite.e2m1x2.f32 w, %8, %7; mov.b32 %0, {x, y, z, w}; }"
+        : "=r"(r) : "f"(a), "f"(b), "f"(c), "f"(d), "f"(e), "f"(f), "f"(g), "f"(h));
+    return r;
+}
+// 3-D tiled store shared -> global (bulk-group completion), cf. tma_store_2d
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *m, const void *smem_src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(reinterpret_cast<uint64_t>(m)),
+                 "r"(sm100::smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+
+// ROWSTAGE: the row-wise copy is staged and written by TMA (dense FP8); otherwise by 32-byte stores from registers.
+template <int FMT, bool ROW, bool COL, bool ROW2D, bool COL2D, bool GROUPED, bool ROWSTAGE>
+__global__ void __launch_bounds__(kSThreads, kSCtasPerSm)
+    mx_quant_split_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_qrow,
+                          const __grid_constant__ CUtensorMap tmap_qcol, MxArgs a, int tiles_n, int tiles_m, int64_t total_tiles,
+                          int *status) {
+    using namespace sm100;
+    using T = __nv_bfloat16;
+    constexpr bool kFp4 = FMT == PT_E2M1;
+    constexpr int kColRowBytes = kFp4 ? 64 : 128;     // one column of the tile in the transposed copy: 128 rows
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *col_stage = smem + kSStages * kQTileBytes;            // 2 x 8 KiB
+    uint8_t *row_stage = col_stage + 2 * kSStageOutBytes;          // 2 x 8 KiB
+    uint64_t *full_bar = reinterpret_cast<uint64_t *>(row_stage + 2 * kSStageOutBytes);
+    uint64_t *empty_bar = full_bar + kSStages;
+    __shared__ __align__(4) uint8_t s_colscale[2][kTileN][4];      // [buffer][column][band]
+    __shared__ int s_abort;
+    volatile int *abort_flag = &s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < kSStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 2 * kSGroupWarps);
+        }
+        fence_barrier_init();
+        prefetch_tmap(&tmap);
+        if (COL) prefetch_tmap(&tmap_qcol);
+        if (ROW && ROWSTAGE) prefetch_tmap(&tmap_qrow);
+    }
+    __shared__ int s_gtab[GROUPED ? 3 * (kQMaxGroups + 1) : 1];
+    __syncthreads();
+    sm100::grid_dep_wait();    // the input may come from the previous kernel, and a GEMM before it may still read the outputs
+    sm100::grid_dep_launch();
+    if constexpr (GROUPED) {
+        for (int i = threadIdx.x; i <= a.num_groups; i += blockDim.x) {
+            s_gtab[i] = (int) a.poffs_col[i];
+            s_gtab[(kQMaxGroups + 1) + i] = (int) a.group_offs[i];
+            s_gtab[2 * (kQMaxGroups + 1) + i] = ROW ? (int) a.poffs_row[i] : 0;
+        }
+        __syncthreads();
+    }
+    bool ok = true;
+    auto locate_group = [&](int tm, int &in_row0, int &n_valid, int &row_out0) -> bool {
+        const int *pcol = s_gtab, *goffs = s_gtab + (kQMaxGroups + 1), *prow = s_gtab + 2 * (kQMaxGroups + 1);
+        const int m0 = tm * kTileM;
+        if (m0 >= pcol[a.num_groups]) return false;
+        int lo = 0, hi = a.num_groups - 1;  // last group whose padded start is <= m0 (empty groups are skipped)
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (pcol[mid] <= m0) lo = mid; else hi = mid - 1;
+        }
+        const int into = m0 - pcol[lo];
+        in_row0 = goffs[lo] + into;
+        n_valid = max(0, min(kTileM, min(goffs[lo + 1], (int) a.M) - in_row0));
+        row_out0 = prow[lo] + into;
+        return true;
+    };
+    const uint32_t per_g = (uint32_t) tiles_n * (uint32_t) tiles_m;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            for (uint32_t t = blockIdx.x; t < (uint32_t) total_tiles; t += gridDim.x) {
+                const uint32_t g = t / per_g, rem = t - g * per_g;
+                const int tm = (int) (rem / (uint32_t) tiles_n), tn = (int) (rem - (uint32_t) tm * tiles_n);
+                int in_row0 = tm * kTileM, row_out0 = 0, n_valid = kTileM;
+                if constexpr (GROUPED)
+                    if (!locate_group(tm, in_row0, n_valid, row_out0)) continue;
+                if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
+                mbar_arrive_expect_tx(&full_bar[stage], kQTileBytes);
+                sm100::tma_load_3d(smem + stage * kQTileBytes, &tmap, &full_bar[stage], tn * kTileN, in_row0, (int) g);
+                if (++stage == kSStages) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp <= kSGroupWarps) {
+        // ================================================================ row-wise copy: thread = tile row
+        const int row = threadIdx.x - 32;
+        uint32_t stage = 0, phase = 0, tile_i = 0;
+        for (uint32_t t = blockIdx.x; t < (uint32_t) total_tiles; t += gridDim.x) {
+            const uint32_t gq = t / per_g, rem = t - gq * per_g;
+            const int tm = (int) (rem / (uint32_t) tiles_n), tn = (int) (rem - (uint32_t) tm * tiles_n);
+            int in_row0 = tm * kTileM, row_out0 = tm * kTileM, n_valid = kTileM;
+            if constexpr (GROUPED)
+                if (!locate_group(tm, in_row0, n_valid, row_out0)) continue;
+            if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
+            uint32_t w[32];
+            if constexpr (ROW) {
+                const uint8_t *rp = smem + stage * kQTileBytes + row * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 q = *reinterpret_cast<const uint4 *>(rp + ((c ^ (row & 7)) << 4));
+                    w[4 * c] = q.x; w[4 * c + 1] = q.y; w[4 * c + 2] = q.z; w[4 * c + 3] = q.w;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[stage]);  // this warp no longer reads the stage
+            if (++stage == kSStages) { stage = 0; phase ^= 1; }
+            if constexpr (ROW) {
+                const int buf = tile_i & 1;
+                ++tile_i;
+                const int64_t g = gq;
+                const int64_t gm = (GROUPED ? row_out0 : tm * kTileM) + row;    // row of the row-wise copy
+                const bool live = GROUPED ? row < n_valid : gm < a.M;
+                const int64_t n0 = (int64_t) tn * kTileN;
+                uint8_t sbyte[2];
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    const uint32_t *x = &w[16 * b];
+                    uint32_t o[8];
+                    uint32_t pm = 0u;
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) pm = absmax2_nan_bf16(pm, x[k]);
+                    const bool has_nan = packed_bf16_has_nan(pm);
+                    if (has_nan) {  // a NaN element takes no part in the maximum
+                        pm = 0u;
+#pragma unroll
+                        for (int k = 0; k < 16; ++k) pm = absmax2<T>(pm, x[k]);
+                    }
+                    pm = absmax2_done(pm);
+                    float m = fmaxf(bf16_lo(pm), bf16_hi(pm));
+                    if constexpr (ROW2D) m = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(m)));  // 32 rows = this warp
+                    const MxScale sc = mx_scale<FMT>(m, GROUPED);
+                    sbyte[b] = sc.byte;
+                    if (sc.byte == 0) {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) o[k] = 0u;
+                    } else if (has_nan && !kFp4) {
+                        const float nlim = -MxParams<FMT>::qmax * sc.native;
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            o[k] = pack4_fp8<kFp4 ? PT_E4M3 : FMT>(fmaxf(bf16_lo(x[2 * k]), nlim) * sc.inv, fmaxf(bf16_hi(x[2 * k]), nlim) * sc.inv,
+                                                                    fmaxf(bf16_lo(x[2 * k + 1]), nlim) * sc.inv, fmaxf(bf16_hi(x[2 * k + 1]), nlim) * sc.inv);
+                    } else {
+                        const uint32_t inv2 = bf16_bits_x2(sc.inv, sc.inv);
+                        if constexpr (kFp4) {
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const uint32_t s0 = mul_bf16x2(x[4 * k], inv2), s1 = mul_bf16x2(x[4 * k + 1], inv2);
+                                const uint32_t s2 = mul_bf16x2(x[4 * k + 2], inv2), s3 = mul_bf16x2(x[4 * k + 3], inv2);
+                                o[k] = pack8_e2m1(bf16_lo(s0), bf16_hi(s0), bf16_lo(s1), bf16_hi(s1), bf16_lo(s2), bf16_hi(s2), bf16_lo(s3), bf16_hi(s3));
+                            }
+                        } else {
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) {
+                                const uint32_t s0 = mul_bf16x2(x[2 * k], inv2), s1 = mul_bf16x2(x[2 * k + 1], inv2);
+                                o[k] = pack4_fp8<kFp4 ? PT_E4M3 : FMT>(bf16_lo(s0), bf16_hi(s0), bf16_lo(s1), bf16_hi(s1));
+                            }
+                        }
+                    }
+                    if constexpr (ROWSTAGE) {
+                        // staged tile of 64-byte rows, 64-byte swizzle: chunk c of row r sits at chunk c ^ ((r >> 1) & 3)
+                        uint8_t *dst = row_stage + buf * kSStageOutBytes + row * 64;
+                        const int sw = (row >> 1) & 3;
+                        *reinterpret_cast<uint4 *>(dst + (((2 * b) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                        *reinterpret_cast<uint4 *>(dst + (((2 * b + 1) ^ sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+                    } else if (live) {
+                        uint8_t *qr = a.q_row + g * a.qrow_gstride;
+                        if constexpr (kFp4) {
+                            *reinterpret_cast<uint4 *>(qr + (gm * a.N_pad + n0) / 2 + 16 * b) = make_uint4(o[0], o[1], o[2], o[3]);
+                        } else {
+                            uint8_t *dst = qr + gm * a.N_pad + n0 + 32 * b;
+                            if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+                                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(o[0]), "r"(o[1]),
+                                             "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
+                            } else {
+                                reinterpret_cast<uint4 *>(dst)[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                                reinterpret_cast<uint4 *>(dst)[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                            }
+                        }
+                    }
+                }
+                if constexpr (ROWSTAGE) {
+                    fence_proxy_async_smem();
+                    if (row == 0) bulk_wait_read_all();   // the store of the previous tile has read the other buffer
+                    asm volatile("bar.sync 1, %0;" ::"n"(kSGroupThreads) : "memory");
+                    if (row == 0) {
+                        tma_store_3d(&tmap_qrow, row_stage + buf * kSStageOutBytes, (int) n0, tm * kTileM, (int) g);
+                        bulk_commit_group();
+                    }
+                }
+                if (live) {   // the two scale bytes of this row (an even offset: one 16-bit store)
+                    uint8_t *sp = a.s_row + g * a.srow_gstride + gm * (a.N_pad / 32) + n0 / 32;
+                    *reinterpret_cast<uint16_t *>(sp) = (uint16_t) (sbyte[0] | ((uint16_t) sbyte[1] << 8));
+                }
+            }
+        }
+        if (ROW && ROWSTAGE && row == 0) bulk_wait_read_all();
+    } else {
+        // ================================================================ transposed copy: thread = (32-row band, column pair)
+        const int ct = threadIdx.x - 32 - kSGroupThreads;
+        const int band = ct >> 5, pair = lane;
+        const int chunk = pair >> 2;
+        uint32_t stage = 0, phase = 0, tile_i = 0;
+        for (uint32_t t = blockIdx.x; t < (uint32_t) total_tiles; t += gridDim.x) {
+            const uint32_t gq = t / per_g, rem = t - gq * per_g;
+            const int tm = (int) (rem / (uint32_t) tiles_n), tn = (int) (rem - (uint32_t) tm * tiles_n);
+            int in_row0 = tm * kTileM, row_out0 = 0, n_valid = kTileM;
+            if constexpr (GROUPED)
+                if (!locate_group(tm, in_row0, n_valid, row_out0)) continue;
+            if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
+            uint32_t w[32];
+            if constexpr (COL) {
+                const uint8_t *cp = smem + stage * kQTileBytes + band * 32 * 128 + ((pair & 3) << 2);
+#pragma unroll
+                for (int r = 0; r < 32; ++r) {   // (32 band + r) % 8 == r % 8: every lane reads tile row r, no bank conflict
+                    const uint32_t v = *reinterpret_cast<const uint32_t *>(cp + r * 128 + ((chunk ^ (r & 7)) << 4));
+                    w[r] = (!GROUPED || band * 32 + r < n_valid) ? v : 0u;   // rows past the group's end count as zeros
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[stage]);
+            if (++stage == kSStages) { stage = 0; phase ^= 1; }
+            if constexpr (COL) {
+                const int buf = tile_i & 1;
+                ++tile_i;
+                uint32_t pm = 0u;
+#pragma unroll
+                for (int r = 0; r < 32; ++r) pm = absmax2_nan_bf16(pm, w[r]);
+                const bool has_nan = packed_bf16_has_nan(pm);
+                if (has_nan) {
+                    pm = 0u;
+#pragma unroll
+                    for (int r = 0; r < 32; ++r) pm = absmax2<T>(pm, w[r]);
+                }
+                pm = absmax2_done(pm);
+                float m0c = bf16_lo(pm), m1c = bf16_hi(pm);
+                if constexpr (COL2D) {   // 32 x 32 tile: the 16 column pairs of this half warp
+                    float m = fmaxf(m0c, m1c);
+                    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+                    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+                    m0c = m1c = m;
+                }
+                const MxScale s0 = mx_scale<FMT>(m0c, GROUPED), s1 = mx_scale<FMT>(m1c, GROUPED);
+                const float i0 = s0.inv, i1 = s1.inv;
+                uint32_t o0[8], o1[8];   // 32 codes of column 2 pair and of column 2 pair + 1
+                if (has_nan && !kFp4) {
+                    const float nl0 = -MxParams<FMT>::qmax * s0.native, nl1 = -MxParams<FMT>::qmax * s1.native;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        o0[k] = pack4_fp8<kFp4 ? PT_E4M3 : FMT>(fmaxf(bf16_lo(w[4 * k]), nl0) * i0, fmaxf(bf16_lo(w[4 * k + 1]), nl0) * i0,
+                                                                                    fmaxf(bf16_lo(w[4 * k + 2]), nl0) * i0, fmaxf(bf16_lo(w[4 * k + 3]), nl0) * i0);
+                        o1[k] = pack4_fp8<kFp4 ? PT_E4M3 : FMT>(fmaxf(bf16_hi(w[4 * k]), nl1) * i1, fmaxf(bf16_hi(w[4 * k + 1]), nl1) * i1,
+                                                                                    fmaxf(bf16_hi(w[4 * k + 2]), nl1) * i1, fmaxf(bf16_hi(w[4 * k + 3]), nl1) * i1);
+                    }
+                } else {
+                    const uint32_t inv2 = bf16_bits_x2(i0, i1);
+#pragma unroll
+                    for (int r = 0; r < 32; ++r) w[r] = mul_bf16x2(w[r], inv2);
+                    if constexpr (kFp4) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            o0[k] = pack8_e2m1(bf16_lo(w[8 * k]), bf16_lo(w[8 * k + 1]), bf16_lo(w[8 * k + 2]), bf16_lo(w[8 * k + 3]),
+                                               bf16_lo(w[8 * k + 4]), bf16_lo(w[8 * k + 5]), bf16_lo(w[8 * k + 6]), bf16_lo(w[8 * k + 7]));
+                            o1[k] = pack8_e2m1(bf16_hi(w[8 * k]), bf16_hi(w[8 * k + 1]), bf16_hi(w[8 * k + 2]), bf16_hi(w[8 * k + 3]),
+                                               bf16_hi(w[8 * k + 4]), bf16_hi(w[8 * k + 5]), bf16_hi(w[8 * k + 6]), bf16_hi(w[8 * k + 7]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            o0[k] = pack4_fp8<kFp4 ? PT_E4M3 : FMT>(bf16_lo(w[4 * k]), bf16_lo(w[4 * k + 1]), bf16_lo(w[4 * k + 2]), bf16_lo(w[4 * k + 3]));
+                            o1[k] = pack4_fp8<kFp4 ? PT_E4M3 : FMT>(bf16_hi(w[4 * k]), bf16_hi(w[4 * k + 1]), bf16_hi(w[4 * k + 2]), bf16_hi(w[4 * k + 3]));
+                        }
+                    }
+                }
+                if (s0.byte == 0) {   // such a column is written as (positive) zeros
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) o0[k] = 0u;
+                }
+                if (s1.byte == 0) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) o1[k] = 0u;
+                }
+                // staged transposed tile: row c = tile column c holds its 128 rows; this thread owns rows 32 band .. + 31
+                uint8_t *cs = col_stage + buf * kSStageOutBytes;
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    const int c = 2 * pair + cc;
+                    const uint32_t *o = cc ? o1 : o0;
+                    if constexpr (kFp4) {   // 64-byte rows, 64-byte swizzle; 16 bytes = chunk `band`
+                        *reinterpret_cast<uint4 *>(cs + c * 64 + ((band ^ ((c >> 1) & 3)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    } else {                // 128-byte rows, 128-byte swizzle; 32 bytes = chunks 2 band, 2 band + 1
+                        *reinterpret_cast<uint4 *>(cs + c * 128 + (((2 * band) ^ (c & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                        *reinterpret_cast<uint4 *>(cs + c * 128 + (((2 * band + 1) ^ (c & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+                    }
+                    s_colscale[buf][c][band] = cc ? s1.byte : s0.byte;
+                }
+                fence_proxy_async_smem();
+                if (ct == 0) bulk_wait_read_all();   // the store of the previous tile has read the other buffer
+                asm volatile("bar.sync 2, %0;" ::"n"(kSGroupThreads) : "memory");
+                const int64_t g = gq;
+                const int64_t m0 = (int64_t) tm * kTileM, n0 = (int64_t) tn * kTileN;
+                if (ct == 0) {
+                    tma_store_3d(&tmap_qcol, cs, (int) (kFp4 ? m0 / 2 : m0), (int) n0, (int) g);
+                    bulk_commit_group();
+                }
+                if (ct < kTileN && n0 + ct < a.N)   // the four band scales of column ct: one 32-bit store
+                    *reinterpret_cast<uint32_t *>(a.s_col + g * a.scol_gstride + (n0 + ct) * (a.M_pad / 32) + m0 / 32) =
+                        *reinterpret_cast<const uint32_t *>(&s_colscale[buf][ct][0]);
+            }
+        }
+        if (COL && ct == 0) bulk_wait_read_all();
+    }
+    if (!ok || *abort_flag) {
+        if (status && lane == 0) atomicExch(status, (int) PT_ERR_TIMEOUT);
+        __nanosleep(100000);  // let a copy still in flight land before the shared memory is released
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ dequantize
 template <typename T> __device__ __forceinline__ void put_out(T *p, float v);
 template <> __device__ __forceinline__ void put_out<float>(float *p, float v) { *p = v; }
@@ -645,8 +1025,75 @@ static int make_tmap_x(CUtensorMap *m, const void *base, int64_t G, int64_t M, i
     return PT_OK;
 }
 
+// 3-D byte tensor map [G, rows, row_bytes] for a staged output tile of box_bytes x box_rows (64- or 128-byte swizzle)
+static int make_tmap_out(CUtensorMap *m, const void *base, int64_t G, int64_t rows, int64_t row_bytes, int box_bytes, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return set_error(PT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[3] = {(cuuint64_t) row_bytes, (cuuint64_t) rows, (cuuint64_t) G};
+    cuuint64_t strides[2] = {(cuuint64_t) row_bytes, (cuuint64_t) rows * (cuuint64_t) row_bytes};
+    cuuint32_t box[3] = {(cuuint32_t) box_bytes, (cuuint32_t) box_rows, 1u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(PT_ERR_CUDA, "cuTensorMapEncodeTiled (quantize output) failed with code %d", (int) r);
+    return PT_OK;
+}
+
+// The warp-split kernel covers bf16 inputs, both copies requested, no Hadamard transform, 16-byte aligned outputs.
+// Returns PT_ERR_UNSUPPORTED (without setting an error message) when the call is outside that.
+template <int FMT, bool GROUPED>
+static int launch_mx_split(const MxArgs &a, int64_t G, int64_t m_tiles_rows, unsigned flags, cudaStream_t st) {
+    if (getenv("PT_MX_QUANT_NO_SPLIT") != nullptr) return PT_ERR_UNSUPPORTED;
+    const bool row = flags & PT_MX_ROW, col = flags & PT_MX_COL;
+    if (!row || !col || (flags & (PT_MX_ROW_RHT | PT_MX_COL_RHT))) return PT_ERR_UNSUPPORTED;
+    constexpr bool kFp4 = FMT == PT_E2M1;
+    if (!aligned(a.x, 16) || !aligned(a.q_row, 16) || !aligned(a.q_col, 16) || !aligned(a.s_row, 2) || !aligned(a.s_col, 4)) return PT_ERR_UNSUPPORTED;
+    if (a.M >= (1ll << 31) || m_tiles_rows >= (1ll << 31)) return PT_ERR_UNSUPPORTED;
+    if (GROUPED && a.num_groups > kQMaxGroups) return PT_ERR_UNSUPPORTED;
+    const int tiles_n = (int) (a.N_pad / kTileN), tiles_m = (int) (m_tiles_rows / kTileM);
+    const int64_t total_tiles = (int64_t) tiles_n * tiles_m * G;
+    PT_REQUIRE(total_tiles < (1ll << 31), "MX quantize: too many tiles");
+    CUtensorMap tx, trow, tcol;
+    int rc = make_tmap_x(&tx, a.x, G, a.M, a.N);
+    if (rc != PT_OK) return rc;
+    constexpr bool kRowStage = !GROUPED && !kFp4;
+    trow = tx;
+    if (kRowStage && (rc = make_tmap_out(&trow, a.q_row, G, a.M, a.N_pad, 64, kTileM)) != PT_OK) return rc;
+    if ((rc = make_tmap_out(&tcol, a.q_col, G, a.N, kFp4 ? a.M_pad / 2 : a.M_pad, kFp4 ? 64 : 128, kTileN)) != PT_OK) return rc;
+    const int grid = (int) std::min<int64_t>(total_tiles, (int64_t) sm_count() * kSCtasPerSm);
+    const bool r2d = flags & PT_MX_ROW_2D, c2d = flags & PT_MX_COL_2D;
+#define PT_MXS_CASE(R2, C2)                                                                                       \
+    if (r2d == R2 && c2d == C2) {                                                                                 \
+        auto kern = mx_quant_split_kernel<FMT, true, true, R2, C2, GROUPED, kRowStage>;                           \
+        static bool attr_set_dev[64] = {};                                                                        \
+        bool &attr_set = attr_set_dev[current_device_slot()];                                                     \
+        if (!attr_set) {                                                                                          \
+            PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSSmemBytes));     \
+            attr_set = true;                                                                                      \
+        }                                                                                                         \
+        PT_CUDA_OK(launch_overlapped(kern, dim3(grid), dim3(kSThreads), kSSmemBytes, st, tx, trow, tcol, a, tiles_n, tiles_m, total_tiles, (int *) nullptr)); \
+        PT_LAUNCH_OK();                                                                                           \
+        return PT_OK;                                                                                             \
+    }
+    PT_MXS_CASE(false, false)
+    if constexpr (!GROUPED) {
+        PT_MXS_CASE(true, true)
+        if constexpr (!kFp4) {
+            PT_MXS_CASE(true, false)
+            PT_MXS_CASE(false, true)
+        }
+    }
+#undef PT_MXS_CASE
+    return PT_ERR_UNSUPPORTED;
+}
+
 template <typename T, int FMT>
 static int launch_mx(const MxArgs &a, int64_t G, unsigned flags, cudaStream_t st) {
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        const int rc = launch_mx_split<FMT, false>(a, G, a.M_pad, flags, st);
+        if (rc != PT_ERR_UNSUPPORTED) return rc;
+    }
     dim3 grid((unsigned) (a.N_pad / kTileN), (unsigned) (a.M_pad / kTileM), (unsigned) G);
     // TMA needs a 16-byte row pitch; N % 32 == 0 guarantees it for 16-bit elements
     const bool use_tma = getenv("PT_MX_QUANT_NO_TMA") == nullptr;
@@ -708,6 +1155,10 @@ static int launch_mx(const MxArgs &a, int64_t G, unsigned flags, cudaStream_t st
 
 template <typename T, int FMT>
 static int launch_mx_grouped(const MxArgs &a, int64_t m_alloc, unsigned flags, cudaStream_t st) {
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        const int rc = launch_mx_split<FMT, true>(a, 1, m_alloc, flags, st);
+        if (rc != PT_ERR_UNSUPPORTED) return rc;
+    }
     dim3 grid((unsigned) (a.N_pad / kTileN), (unsigned) (m_alloc / kTileM), 1u);  // tiles past padded_offs_col[G] return at once
     const bool row = flags & PT_MX_ROW, col = flags & PT_MX_COL;
     const bool rrht = flags & PT_MX_ROW_RHT, crht = flags & PT_MX_COL_RHT;
