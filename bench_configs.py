@@ -12,6 +12,7 @@ The group-length generators are shared with tests/test_configs_gpu.py so that te
 ragged layouts.  Large operands are drawn with the device generator (seeded): 15 GB of weights do not fit a host
 generator's patience; the parity tests download the rows they compare.
 """
+import os
 import statistics
 
 import numpy as np
@@ -92,6 +93,11 @@ def time_cuda_rotating(fns, rounds=12, warmup=2):
             f()
     torch.cuda.synchronize()
     replay = None
+    # Captured launches of the persistent quantizers normally keep the static tile schedule (a replay could overlap
+    # another launch that holds the same counter slot); this graph is the only work on the device, so the dynamic
+    # schedule the eager launches of a training step get is allowed into it.
+    before = os.environ.get("PT_TILE_SCHED_IN_GRAPHS")
+    os.environ["PT_TILE_SCHED_IN_GRAPHS"] = "1"
     try:
         graph = torch.cuda.CUDAGraph()
         keep = []
@@ -101,7 +107,12 @@ def time_cuda_rotating(fns, rounds=12, warmup=2):
         replay = graph.replay
     except Exception:  # noqa: BLE001
         torch.cuda.synchronize()
-
+    finally:
+        if before is None:
+            os.environ.pop("PT_TILE_SCHED_IN_GRAPHS", None)
+        else:
+            os.environ["PT_TILE_SCHED_IN_GRAPHS"] = before
+    if replay is None:
         def replay():
             for f in fns:
                 f()

@@ -44,6 +44,20 @@ const char *pt_last_error(void);
 /* Library / device sanity: returns the number of SMs of the current device, or a negative status. */
 int pt_device_sm_count(void);
 
+/* Kernels wait on barriers (data arriving by TMA, tensor-core completion, peer CTAs) with a bound: a wait that outlasts
+ * it gives up, the kernel unwinds and reports PT_ERR_TIMEOUT in a device status word instead of hanging the GPU; the
+ * output of that launch is then invalid.  The GEMM entry points take the word as their `status` argument.  The
+ * quantizers have none: they report into the word registered here for the current device (null: none, the default).
+ * The word must stay allocated while registered.  A caller that never reads its status words gets unchecked results.
+ * (The reference has no counterpart: its kernels wait without a bound.) */
+int pt_set_default_status(int *status);
+
+/* Self-test of the bounded wait: launches one CTA whose first thread waits `limit_ns` nanoseconds (1 us .. 1 s) on a
+ * barrier that nothing completes; the wait gives up, the kernel returns, *status receives PT_ERR_TIMEOUT and
+ * *observers (optional device int, zeroed by the caller) the number of warps (4) that saw the abort flag.  Nothing
+ * faults and nothing waits without a bound.  (No counterpart in the reference.) */
+int pt_wait_probe(int64_t limit_ns, int *status, int *observers, void *stream);
+
 /* ------------------------------------------------------------------ tensorwise / rowwise FP8 */
 
 /* Bytes of scratch pt_quantize_fp8_tensorwise needs (holds the running amax). */

@@ -30,6 +30,7 @@ int set_error(int code, const char *fmt, ...);
 #define PT_LAUNCH_OK() PT_CUDA_OK(cudaGetLastError())
 
 int sm_count();  // cached multiprocessor count of the current device
+int *default_status();  // status word registered for the current device with pt_set_default_status, or null
 
 // Index of the current device for the small per-device caches below (function attributes and occupancy are
 // per-device state; a process may drive several GPUs).

@@ -549,7 +549,11 @@ static int launch_gemm(const void *a, int64_t a_rows, const void *b, int64_t b_r
     return PT_OK;
 }
 
-// CTA-pair launch (dense problems only): grid = 2 x min(tiles, co-resident clusters)
+// Devices on which a cluster launch was refused: the pair form is not tried again there.
+static bool g_pair_refused[64] = {};
+
+// CTA-pair launch: grid = 2 x min(tiles, co-resident clusters).  Returns PT_ERR_UNSUPPORTED (no message, CUDA's
+// last-error cleared) only when the cluster launch itself is refused; every other failure is reported as it is.
 template <int BLOCK_N, int MODE>
 static int launch_gemm_pair(const void *a, int64_t a_rows, const void *b, int64_t b_rows, GemmParams p, const MxScales &mx,
                             cudaStream_t st) {
@@ -590,7 +594,16 @@ static int launch_gemm_pair(const void *a, int64_t a_rows, const void *b, int64_
     }
     const int pairs = (int) std::min<int64_t>(tiles, max_clusters);
     if (pairs <= 0) return PT_OK;
-    PT_CUDA_OK(launch_overlapped(kern, dim3(2 * pairs), dim3(Cfg::kThreads), Cfg::kSmemBytes, st, ta, tb, tsf, p));
+    const cudaError_t le = launch_overlapped(kern, dim3(2 * pairs), dim3(Cfg::kThreads), Cfg::kSmemBytes, st, ta, tb, tsf, p);
+    if (le != cudaSuccess) {
+        cudaGetLastError();  // the refusal must not surface in a later, unrelated call
+        if (le == cudaErrorInvalidClusterSize || le == cudaErrorLaunchOutOfResources || le == cudaErrorInvalidConfiguration ||
+            le == cudaErrorNotSupported) {
+            g_pair_refused[current_device_slot()] = true;
+            return PT_ERR_UNSUPPORTED;
+        }
+        return set_error(PT_ERR_CUDA, "CTA-pair GEMM launch failed: %s", cudaGetErrorString(le));
+    }
     return PT_OK;
 }
 
@@ -612,17 +625,17 @@ static int dispatch_block_n(int block_n, const void *a, int64_t a_rows, const vo
         const int64_t rows_per_group = p.koffs ? p.M : p.M / p.G;
         const int64_t out_elems = (p.koffs ? (int64_t) p.G : 1) * p.M * (int64_t) p.N;
         const bool grouped = p.offs_write != nullptr && !p.koffs;
-        if (block_n == 0 && max_ctas <= 0 && pair_enabled() && rows_per_group >= 1024 && p.N >= 512 &&
+        if (block_n == 0 && max_ctas <= 0 && pair_enabled() && !g_pair_refused[current_device_slot()] && rows_per_group >= 1024 && p.N >= 512 &&
             out_elems >= (int64_t) 4096 * 4096 && (!mode_is_mx(MODE) || aligned(mx.workspace, 128))) {
             if constexpr (mode_is_mx(MODE)) {
                 constexpr int kSfP = MODE == GEMM_MXF4 ? 2 : 1;
                 if (mx.workspace_bytes >= mx_workspace_bytes(p.M, p.N, p.K, p.koffs ? 1 : p.G, grouped, 224) * kSfP) {
                     const int rc = launch_gemm_pair<224, MODE>(a, a_rows, b, b_rows, p, mx, st);
-                    if (rc != PT_ERR_CUDA) return rc;  // a device that cannot launch clusters falls through to single CTAs
+                    if (rc != PT_ERR_UNSUPPORTED) return rc;  // a device that cannot launch clusters falls through to single CTAs
                 }
             } else {
                 const int rc = launch_gemm_pair<256, MODE>(a, a_rows, b, b_rows, p, mx, st);
-                if (rc != PT_ERR_CUDA) return rc;
+                if (rc != PT_ERR_UNSUPPORTED) return rc;
             }
         }
     }

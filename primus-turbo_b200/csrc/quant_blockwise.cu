@@ -213,6 +213,7 @@ struct BqArgs {
     uint8_t *q_row, *q_col;
     float *s_row, *s_col;
     SegmentArgs seg;
+    int *status;               // receives PT_ERR_TIMEOUT if a bounded wait gives up (may be null)
 };
 
 template <typename T, int FMT, int MODE>
@@ -451,7 +452,10 @@ __global__ void __launch_bounds__(kBqThreads, kBqCtasPerSm)
             }
         }
     }
-    if (!ok || *abort_flag) __nanosleep(100000);  // let a copy still in flight land before the shared memory is released
+    if (!ok || *abort_flag) {
+        if (a.status && lane == 0) atomicExch(a.status, (int) PT_ERR_TIMEOUT);
+        __nanosleep(100000);  // let a copy still in flight land before the shared memory is released
+    }
 }
 
 // y = float(q) * s for the three block-scale layouts
@@ -657,7 +661,7 @@ static int launch_tile(const void *x, int x_dtype, int64_t B, int64_t m_tiles, i
         CUtensorMap tmap;
         int rc = make_tmap_u16_3d(&tmap, x, B, M, N, kBlk);
         if (rc != PT_OK) return rc;
-        BqArgs a{M, N, (int) tiles_n, (int) m_tiles, total_tiles, (uint8_t *) q_row, (uint8_t *) q_col, s_row, s_col, seg};
+        BqArgs a{M, N, (int) tiles_n, (int) m_tiles, total_tiles, (uint8_t *) q_row, (uint8_t *) q_col, s_row, s_col, seg, default_status()};
         const int tma_grid = (int) std::min<int64_t>(total_tiles, (int64_t) sm_count() * kBqCtasPerSm);
 #define PT_BQ_LAUNCH(T_)                                                                                           \
         PT_SWITCH_FP8(fmt, F, {                                                                                    \

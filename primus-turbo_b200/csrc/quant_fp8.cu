@@ -348,6 +348,8 @@ int pt_quantize_fp8_rowwise(const void *x, int x_dtype, int64_t B, int64_t M, in
         return PT_OK;
     }
     PT_REQUIRE(B <= 65535, "rowwise: batch too large");
+    // the column-scaled kernels put the 32-row blocks of M in grid.y
+    PT_REQUIRE(M <= 65535ll * 32, "rowwise: the scaled axis has %lld rows, at most %lld are supported", (long long) M, 65535ll * 32);
     unsigned *amax = (unsigned *) workspace;
     if (!scale_opt) {
         PT_REQUIRE(workspace && workspace_bytes >= (size_t) (B * N) * 4, "rowwise: workspace of B*N floats required");
@@ -396,6 +398,8 @@ int pt_quantize_fp8_colscale_noalloc(const void *x, int x_dtype, int64_t B, int6
     if (B * M * N == 0) return PT_OK;
     PT_REQUIRE(x && q, "no-alloc quantize: null pointer");
     PT_REQUIRE(B <= 65535, "no-alloc quantize: batch too large");
+    PT_REQUIRE(M <= 65535ll * 32, "no-alloc quantize: the scaled axis has %lld rows, at most %lld are supported", (long long) M,
+               65535ll * 32);
     unsigned *amax = nullptr;
     int rc = noalloc_scratch(&amax);  // first call on a device resolves the scratch address
     if (rc != PT_OK) return rc;

@@ -17,6 +17,7 @@
 #include "common.cuh"
 #include "gemm_common.cuh"
 #include "sm100_ptx.cuh"
+#include "tile_sched.cuh"
 
 namespace ptb {
 
@@ -590,17 +591,23 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
 }
 
 // ------------------------------------------------------------------------------------------------ warp-split form
-// The form used for bf16 inputs without the Hadamard option.  Same tiles and the same TMA input ring as
-// mx_quant_tma_kernel, but the eight consumer warps are split by output: four warps produce the row-wise copy (one
-// thread per tile row: two 32-element blocks read as eight 16-byte chunks), four produce the transposed copy (one
-// thread per column pair and 32-row band: a whole MX block of each of its two columns, so no value is exchanged between
-// threads and rows are read in order, every lane of a warp in the same tile row).  The transposed tile is assembled in
-// shared memory in the 128-byte (fp4: 64-byte) swizzled layout and written with one cp.async.bulk.tensor store per tile
-// from a double buffer, which frees the thread-to-element mapping from the shape of the global stores; the dense FP8
-// row copy leaves the same way, the grouped and the FP4 row copies with 32-byte stores per row.  Scaling is exact in
-// packed bf16 (the scale is a power of two), so one mul.bf16x2 scales two elements.  A block holding a NaN is found
-// with the NaN-propagating packed maximum and re-done on the slow path, which applies the reference's
-// fmax(v, -qmax * scale) to every element; all other blocks skip that clamp (the saturating convert covers it).
+// The form used for bf16 inputs, both copies, without the Hadamard option.  Same tiles and TMA input ring as
+// mx_quant_tma_kernel, but the eight consumer warps are split by output and never synchronise with one another:
+//   * four warps produce the row-wise copy, one thread per tile row (two 32-element blocks read as eight 16-byte
+//     chunks); the dense FP8 copy is staged as a 128 x 64-byte tile and written with one bulk tensor store per tile
+//     (grouped row copies, which need row masks, and fp4 use 32- / 16-byte stores from registers);
+//   * four warps produce the transposed copy, one thread per column pair and 32-row band: a whole MX block of each of
+//     its two columns, so rows are read in order, every lane of a warp in the same tile row (no bank conflict, no
+//     exchange between threads); the 64 x 128-byte (fp4: 64-byte) transposed tile is staged in the swizzled layout and
+//     written with one bulk tensor store, the four band scales of a column as one word.
+// The two groups synchronise only among their own four warps (one named barrier per tile, around the double-buffered
+// staging tile).  The producer thread also resolves each tile's coordinates (and, in the grouped form, its group) once
+// and hands them over in shared memory next to the data; outside stream capture it draws tiles from a device counter,
+// so CTAs that get ahead take more tiles and all SMs finish together.  (Per-warp stores of 32-byte wide pieces, which
+// need no barrier, measured slower: four times as many store transactions.)  Scaling is exact in packed bf16 (the scale is a power of two), so one
+// mul.bf16x2 scales two elements.  A block holding a NaN is found with the NaN-propagating packed maximum and patched
+// with max.bf16x2(v, -qmax * scale), which is the half of the reference's clamp that decides what a NaN becomes; all
+// other blocks skip the clamp (the saturating convert covers it).
 constexpr int kSStages = 2;
 constexpr int kSCtasPerSm = 3;
 constexpr int kSGroupWarps = 4;                       // warps per output copy
@@ -608,6 +615,11 @@ constexpr int kSGroupThreads = 32 * kSGroupWarps;
 constexpr int kSThreads = 32 * (1 + 2 * kSGroupWarps);
 constexpr int kSStageOutBytes = 8192;                 // one staged output tile (fp8: 128 x 64 bytes either way round)
 constexpr int kSSmemBytes = kSStages * kQTileBytes + 4 * kSStageOutBytes + 1024 + 1024;
+
+
+struct TileDesc {
+    int tn, tm, g, in_row0, n_valid, row_out0, pad0, pad1;   // tn < 0: no more tiles
+};
 
 __device__ __forceinline__ uint32_t absmax2_nan_bf16(uint32_t m, uint32_t w) {
     uint32_t r;
@@ -624,6 +636,12 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
     asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
     return r;
 }
+// max(a, b) per half; a NaN half yields the other operand
+__device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
 __device__ __forceinline__ uint32_t bf16_bits_x2(float lo, float hi) {
     return (__float_as_uint(lo) >> 16) | (__float_as_uint(hi) & 0xFFFF0000u);
 }
@@ -632,11 +650,11 @@ __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w 
 // four floats -> four fp8 codes, a in the lowest byte
 template <int FMT> __device__ __forceinline__ uint32_t pack4_fp8(float a, float b, float c, float d) {
     uint32_t r;
-    if constexpr (FMT == PT_E4M3)
-        asm("{ .reg .b16 x, y; cvt.rn.satfinite.e4m3x2.f32 x, %2, %1; cvt.rn.satfinite.e4m3x2.f32 y, %4, %3; mov.b32 %0, {x, y}; }"
+    if constexpr (FMT == PT_E5M2)
+        asm("{ .reg .b16 x, y; cvt.rn.satfinite.e5m2x2.f32 x, %2, %1; cvt.rn.satfinite.e5m2x2.f32 y, %4, %3; mov.b32 %0, {x, y}; }"
             : "=r"(r) : "f"(a), "f"(b), "f"(c), "f"(d));
     else
-        asm("{ .reg .b16 x, y; cvt.rn.satfinite.e5m2x2.f32 x, %2, %1; cvt.rn.satfinite.e5m2x2.f32 y, %4, %3; mov.b32 %0, {x, y}; }"
+        asm("{ .reg .b16 x, y; cvt.rn.satfinite.e4m3x2.f32 x, %2, %1; cvt.rn.satfinite.e4m3x2.f32 y, %4, %3; mov.b32 %0, {x, y}; }"
             : "=r"(r) : "f"(a), "f"(b), "f"(c), "f"(d));
     return r;
 }
@@ -655,22 +673,40 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap *m, const void *s
                  : "memory");
 }
 
+// 16 packed words (one 32-element block of a row) -> 8 words of fp8 codes or 4 words of e2m1 codes
+template <int FMT> __device__ __forceinline__ void encode_row_block(const uint32_t *x, uint32_t inv2, uint32_t *o) {
+    if constexpr (FMT == PT_E2M1) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t s0 = mul_bf16x2(x[4 * k], inv2), s1 = mul_bf16x2(x[4 * k + 1], inv2);
+            const uint32_t s2 = mul_bf16x2(x[4 * k + 2], inv2), s3 = mul_bf16x2(x[4 * k + 3], inv2);
+            o[k] = pack8_e2m1(bf16_lo(s0), bf16_hi(s0), bf16_lo(s1), bf16_hi(s1), bf16_lo(s2), bf16_hi(s2), bf16_lo(s3), bf16_hi(s3));
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t s0 = mul_bf16x2(x[2 * k], inv2), s1 = mul_bf16x2(x[2 * k + 1], inv2);
+            o[k] = pack4_fp8<FMT>(bf16_lo(s0), bf16_hi(s0), bf16_lo(s1), bf16_hi(s1));
+        }
+    }
+}
+
 // ROWSTAGE: the row-wise copy is staged and written by TMA (dense FP8); otherwise by 32-byte stores from registers.
-template <int FMT, bool ROW, bool COL, bool ROW2D, bool COL2D, bool GROUPED, bool ROWSTAGE>
+template <int FMT, bool ROW2D, bool COL2D, bool GROUPED, bool ROWSTAGE>
 __global__ void __launch_bounds__(kSThreads, kSCtasPerSm)
     mx_quant_split_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_qrow,
                           const __grid_constant__ CUtensorMap tmap_qcol, MxArgs a, int tiles_n, int tiles_m, int64_t total_tiles,
-                          int *status) {
+                          int sched_slot, int *status) {
     using namespace sm100;
     using T = __nv_bfloat16;
     constexpr bool kFp4 = FMT == PT_E2M1;
-    constexpr int kColRowBytes = kFp4 ? 64 : 128;     // one column of the tile in the transposed copy: 128 rows
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *col_stage = smem + kSStages * kQTileBytes;            // 2 x 8 KiB
     uint8_t *row_stage = col_stage + 2 * kSStageOutBytes;          // 2 x 8 KiB
     uint64_t *full_bar = reinterpret_cast<uint64_t *>(row_stage + 2 * kSStageOutBytes);
     uint64_t *empty_bar = full_bar + kSStages;
+    __shared__ __align__(16) TileDesc s_desc[kSStages];
     __shared__ __align__(4) uint8_t s_colscale[2][kTileN][4];      // [buffer][column][band]
     __shared__ int s_abort;
     volatile int *abort_flag = &s_abort;
@@ -684,10 +720,10 @@ __global__ void __launch_bounds__(kSThreads, kSCtasPerSm)
         }
         fence_barrier_init();
         prefetch_tmap(&tmap);
-        if (COL) prefetch_tmap(&tmap_qcol);
-        if (ROW && ROWSTAGE) prefetch_tmap(&tmap_qrow);
+        prefetch_tmap(&tmap_qcol);
+        if (ROWSTAGE) prefetch_tmap(&tmap_qrow);
     }
-    __shared__ int s_gtab[GROUPED ? 3 * (kQMaxGroups + 1) : 1];
+    __shared__ int s_gtab[GROUPED ? 3 * (kQMaxGroups + 1) : 1];   // grouped: the three offset tables, read by the producer
     __syncthreads();
     sm100::grid_dep_wait();    // the input may come from the previous kernel, and a GEMM before it may still read the outputs
     sm100::grid_dep_launch();
@@ -695,56 +731,62 @@ __global__ void __launch_bounds__(kSThreads, kSCtasPerSm)
         for (int i = threadIdx.x; i <= a.num_groups; i += blockDim.x) {
             s_gtab[i] = (int) a.poffs_col[i];
             s_gtab[(kQMaxGroups + 1) + i] = (int) a.group_offs[i];
-            s_gtab[2 * (kQMaxGroups + 1) + i] = ROW ? (int) a.poffs_row[i] : 0;
+            s_gtab[2 * (kQMaxGroups + 1) + i] = (int) a.poffs_row[i];
         }
         __syncthreads();
     }
     bool ok = true;
-    auto locate_group = [&](int tm, int &in_row0, int &n_valid, int &row_out0) -> bool {
-        const int *pcol = s_gtab, *goffs = s_gtab + (kQMaxGroups + 1), *prow = s_gtab + 2 * (kQMaxGroups + 1);
-        const int m0 = tm * kTileM;
-        if (m0 >= pcol[a.num_groups]) return false;
-        int lo = 0, hi = a.num_groups - 1;  // last group whose padded start is <= m0 (empty groups are skipped)
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (pcol[mid] <= m0) lo = mid; else hi = mid - 1;
-        }
-        const int into = m0 - pcol[lo];
-        in_row0 = goffs[lo] + into;
-        n_valid = max(0, min(kTileM, min(goffs[lo + 1], (int) a.M) - in_row0));
-        row_out0 = prow[lo] + into;
-        return true;
-    };
-    const uint32_t per_g = (uint32_t) tiles_n * (uint32_t) tiles_m;
 
     if (warp == 0) {
+        // ================================================================ producer: tile coordinates + TMA loads
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
-            for (uint32_t t = blockIdx.x; t < (uint32_t) total_tiles; t += gridDim.x) {
-                const uint32_t g = t / per_g, rem = t - g * per_g;
-                const int tm = (int) (rem / (uint32_t) tiles_n), tn = (int) (rem - (uint32_t) tm * tiles_n);
-                int in_row0 = tm * kTileM, row_out0 = 0, n_valid = kTileM;
-                if constexpr (GROUPED)
-                    if (!locate_group(tm, in_row0, n_valid, row_out0)) continue;
+            const uint32_t per_g = (uint32_t) tiles_n * (uint32_t) tiles_m;
+            int grp = 0;   // grouped: tiles arrive in ascending row order, so the group index only moves forward
+            // static schedule (sched_slot < 0): tiles blockIdx.x, + gridDim.x, ...; dynamic: the first tile is blockIdx.x,
+            // every further one comes from the slot's counter (tile_sched.cuh)
+            for (uint32_t t = blockIdx.x; t < (uint32_t) total_tiles; t = tile_sched_next(sched_slot, t)) {
+                TileDesc d;
+                d.g = (int) (t / per_g);
+                const uint32_t rem = t - (uint32_t) d.g * per_g;
+                d.tm = (int) (rem / (uint32_t) tiles_n);
+                d.tn = (int) (rem - (uint32_t) d.tm * tiles_n);
+                d.in_row0 = d.tm * kTileM; d.n_valid = kTileM; d.row_out0 = d.tm * kTileM; d.pad0 = d.pad1 = 0;
+                if constexpr (GROUPED) {
+                    const int *pcol = s_gtab, *goffs = s_gtab + (kQMaxGroups + 1), *prow = s_gtab + 2 * (kQMaxGroups + 1);
+                    const int m0 = d.tm * kTileM;
+                    if (m0 >= pcol[a.num_groups]) continue;   // past the padded end
+                    while (grp + 1 < a.num_groups && pcol[grp + 1] <= m0) ++grp;   // last group starting at or before m0
+                    const int into = m0 - pcol[grp];
+                    d.in_row0 = goffs[grp] + into;
+                    d.n_valid = max(0, min(kTileM, min(goffs[grp + 1], (int) a.M) - d.in_row0));
+                    d.row_out0 = prow[grp] + into;
+                }
                 if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
+                s_desc[stage] = d;
                 mbar_arrive_expect_tx(&full_bar[stage], kQTileBytes);
-                sm100::tma_load_3d(smem + stage * kQTileBytes, &tmap, &full_bar[stage], tn * kTileN, in_row0, (int) g);
+                sm100::tma_load_3d(smem + stage * kQTileBytes, &tmap, &full_bar[stage], d.tn * kTileN, d.in_row0, d.g);
                 if (++stage == kSStages) { stage = 0; phase ^= 1; }
             }
+            if (ok && (ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) {   // the terminal descriptor
+                s_desc[stage].tn = -1;
+                mbar_arrive(&full_bar[stage]);
+            }
+            tile_sched_done(sched_slot);
         }
     } else if (warp <= kSGroupWarps) {
         // ================================================================ row-wise copy: thread = tile row
         const int row = threadIdx.x - 32;
         uint32_t stage = 0, phase = 0, tile_i = 0;
-        for (uint32_t t = blockIdx.x; t < (uint32_t) total_tiles; t += gridDim.x) {
-            const uint32_t gq = t / per_g, rem = t - gq * per_g;
-            const int tm = (int) (rem / (uint32_t) tiles_n), tn = (int) (rem - (uint32_t) tm * tiles_n);
-            int in_row0 = tm * kTileM, row_out0 = tm * kTileM, n_valid = kTileM;
-            if constexpr (GROUPED)
-                if (!locate_group(tm, in_row0, n_valid, row_out0)) continue;
+        while (true) {
             if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
+            const int4 d0 = *reinterpret_cast<const int4 *>(&s_desc[stage]);
+            const int2 d1 = *reinterpret_cast<const int2 *>(&s_desc[stage].n_valid);
+            const int tn = d0.x, tm = d0.y, n_valid = d1.x, row_out0 = d1.y;
+            const int64_t g = d0.z;
+            if (tn < 0) break;
             uint32_t w[32];
-            if constexpr (ROW) {
+            {
                 const uint8_t *rp = smem + stage * kQTileBytes + row * 128;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
@@ -755,111 +797,93 @@ __global__ void __launch_bounds__(kSThreads, kSCtasPerSm)
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_bar[stage]);  // this warp no longer reads the stage
             if (++stage == kSStages) { stage = 0; phase ^= 1; }
-            if constexpr (ROW) {
-                const int buf = tile_i & 1;
-                ++tile_i;
-                const int64_t g = gq;
-                const int64_t gm = (GROUPED ? row_out0 : tm * kTileM) + row;    // row of the row-wise copy
-                const bool live = GROUPED ? row < n_valid : gm < a.M;
-                const int64_t n0 = (int64_t) tn * kTileN;
-                uint8_t sbyte[2];
+            const int buf = tile_i & 1;
+            ++tile_i;
+            const int64_t gm = (GROUPED ? row_out0 : tm * kTileM) + row;    // row of the row-wise copy
+            const bool live = GROUPED ? row < n_valid : gm < a.M;
+            const int64_t n0 = (int64_t) tn * kTileN;
+            uint8_t sbyte[2];
 #pragma unroll
-                for (int b = 0; b < 2; ++b) {
-                    const uint32_t *x = &w[16 * b];
-                    uint32_t o[8];
-                    uint32_t pm = 0u;
+            for (int b = 0; b < 2; ++b) {
+                uint32_t *x = &w[16 * b];
+                uint32_t o[8];
+                uint32_t pm = 0u;
 #pragma unroll
-                    for (int k = 0; k < 16; ++k) pm = absmax2_nan_bf16(pm, x[k]);
-                    const bool has_nan = packed_bf16_has_nan(pm);
-                    if (has_nan) {  // a NaN element takes no part in the maximum
-                        pm = 0u;
+                for (int k = 0; k < 16; ++k) pm = absmax2_nan_bf16(pm, x[k]);
+                const bool has_nan = packed_bf16_has_nan(pm);
+                if (has_nan) {  // a NaN element takes no part in the maximum
+                    pm = 0u;
 #pragma unroll
-                        for (int k = 0; k < 16; ++k) pm = absmax2<T>(pm, x[k]);
-                    }
-                    pm = absmax2_done(pm);
-                    float m = fmaxf(bf16_lo(pm), bf16_hi(pm));
-                    if constexpr (ROW2D) m = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(m)));  // 32 rows = this warp
-                    const MxScale sc = mx_scale<FMT>(m, GROUPED);
-                    sbyte[b] = sc.byte;
-                    if (sc.byte == 0) {
+                    for (int k = 0; k < 16; ++k) pm = absmax2<T>(pm, x[k]);
+                }
+                pm = absmax2_done(pm);
+                float m = fmaxf(bf16_lo(pm), bf16_hi(pm));
+                if constexpr (ROW2D) m = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(m)));  // 32 rows = this warp
+                const MxScale sc = mx_scale<FMT>(m, GROUPED);
+                sbyte[b] = sc.byte;
+                if (has_nan && !kFp4) {   // fmax(NaN, -qmax * scale) = -qmax * scale, exact in bf16 (1.75 * 2^k, or -inf)
+                    const float nlim = -MxParams<FMT>::qmax * sc.native;
+                    const uint32_t nlim2 = bf16_bits_x2(nlim, nlim);
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) o[k] = 0u;
-                    } else if (has_nan && !kFp4) {
-                        const float nlim = -MxParams<FMT>::qmax * sc.native;
+                    for (int k = 0; k < 16; ++k) x[k] = max_bf16x2(x[k], nlim2);
+                }
+                encode_row_block<FMT>(x, bf16_bits_x2(sc.inv, sc.inv), o);
+                if (sc.byte == 0) {       // such a block is written as (positive) zeros
 #pragma unroll
-                        for (int k = 0; k < 8; ++k)
-                            o[k] = pack4_fp8<kFp4 ? PT_E4M3 : FMT>(fmaxf(bf16_lo(x[2 * k]), nlim) * sc.inv, fmaxf(bf16_hi(x[2 * k]), nlim) * sc.inv,
-                                                                    fmaxf(bf16_lo(x[2 * k + 1]), nlim) * sc.inv, fmaxf(bf16_hi(x[2 * k + 1]), nlim) * sc.inv);
-                    } else {
-                        const uint32_t inv2 = bf16_bits_x2(sc.inv, sc.inv);
-                        if constexpr (kFp4) {
-#pragma unroll
-                            for (int k = 0; k < 4; ++k) {
-                                const uint32_t s0 = mul_bf16x2(x[4 * k], inv2), s1 = mul_bf16x2(x[4 * k + 1], inv2);
-                                const uint32_t s2 = mul_bf16x2(x[4 * k + 2], inv2), s3 = mul_bf16x2(x[4 * k + 3], inv2);
-                                o[k] = pack8_e2m1(bf16_lo(s0), bf16_hi(s0), bf16_lo(s1), bf16_hi(s1), bf16_lo(s2), bf16_hi(s2), bf16_lo(s3), bf16_hi(s3));
-                            }
-                        } else {
-#pragma unroll
-                            for (int k = 0; k < 8; ++k) {
-                                const uint32_t s0 = mul_bf16x2(x[2 * k], inv2), s1 = mul_bf16x2(x[2 * k + 1], inv2);
-                                o[k] = pack4_fp8<kFp4 ? PT_E4M3 : FMT>(bf16_lo(s0), bf16_hi(s0), bf16_lo(s1), bf16_hi(s1));
-                            }
-                        }
-                    }
-                    if constexpr (ROWSTAGE) {
-                        // staged tile of 64-byte rows, 64-byte swizzle: chunk c of row r sits at chunk c ^ ((r >> 1) & 3)
-                        uint8_t *dst = row_stage + buf * kSStageOutBytes + row * 64;
-                        const int sw = (row >> 1) & 3;
-                        *reinterpret_cast<uint4 *>(dst + (((2 * b) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-                        *reinterpret_cast<uint4 *>(dst + (((2 * b + 1) ^ sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
-                    } else if (live) {
-                        uint8_t *qr = a.q_row + g * a.qrow_gstride;
-                        if constexpr (kFp4) {
-                            *reinterpret_cast<uint4 *>(qr + (gm * a.N_pad + n0) / 2 + 16 * b) = make_uint4(o[0], o[1], o[2], o[3]);
-                        } else {
-                            uint8_t *dst = qr + gm * a.N_pad + n0 + 32 * b;
-                            if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
-                                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(o[0]), "r"(o[1]),
-                                             "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
-                            } else {
-                                reinterpret_cast<uint4 *>(dst)[0] = make_uint4(o[0], o[1], o[2], o[3]);
-                                reinterpret_cast<uint4 *>(dst)[1] = make_uint4(o[4], o[5], o[6], o[7]);
-                            }
-                        }
-                    }
+                    for (int k = 0; k < 8; ++k) o[k] = 0u;
                 }
                 if constexpr (ROWSTAGE) {
-                    fence_proxy_async_smem();
-                    if (row == 0) bulk_wait_read_all();   // the store of the previous tile has read the other buffer
-                    asm volatile("bar.sync 1, %0;" ::"n"(kSGroupThreads) : "memory");
-                    if (row == 0) {
-                        tma_store_3d(&tmap_qrow, row_stage + buf * kSStageOutBytes, (int) n0, tm * kTileM, (int) g);
-                        bulk_commit_group();
+                    // staged tile of 64-byte rows, 64-byte swizzle: chunk c of row r sits at chunk c ^ ((r >> 1) & 3)
+                    uint8_t *dst = row_stage + buf * kSStageOutBytes + row * 64;
+                    const int sw = (row >> 1) & 3;
+                    *reinterpret_cast<uint4 *>(dst + (((2 * b) ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<uint4 *>(dst + (((2 * b + 1) ^ sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+                } else if (live) {
+                    uint8_t *qr = a.q_row + g * a.qrow_gstride;
+                    if constexpr (kFp4) {
+                        *reinterpret_cast<uint4 *>(qr + (gm * a.N_pad + n0) / 2 + 16 * b) = make_uint4(o[0], o[1], o[2], o[3]);
+                    } else {
+                        uint8_t *dst = qr + gm * a.N_pad + n0 + 32 * b;
+                        if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+                            asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(o[0]), "r"(o[1]),
+                                         "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
+                        } else {
+                            reinterpret_cast<uint4 *>(dst)[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                            reinterpret_cast<uint4 *>(dst)[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                        }
                     }
                 }
-                if (live) {   // the two scale bytes of this row (an even offset: one 16-bit store)
-                    uint8_t *sp = a.s_row + g * a.srow_gstride + gm * (a.N_pad / 32) + n0 / 32;
-                    *reinterpret_cast<uint16_t *>(sp) = (uint16_t) (sbyte[0] | ((uint16_t) sbyte[1] << 8));
+            }
+            if constexpr (ROWSTAGE) {
+                fence_proxy_async_smem();
+                if (row == 0) bulk_wait_read_all();   // the store of the previous tile has read the other buffer
+                asm volatile("bar.sync 1, %0;" ::"n"(kSGroupThreads) : "memory");
+                if (row == 0) {
+                    tma_store_3d(&tmap_qrow, row_stage + buf * kSStageOutBytes, (int) n0, tm * kTileM, (int) g);
+                    bulk_commit_group();
                 }
             }
+            if (live) {   // the two scale bytes of this row (an even offset: one 16-bit store)
+                uint8_t *sp = a.s_row + g * a.srow_gstride + gm * (a.N_pad / 32) + n0 / 32;
+                *reinterpret_cast<uint16_t *>(sp) = (uint16_t) (sbyte[0] | ((uint16_t) sbyte[1] << 8));
+            }
         }
-        if (ROW && ROWSTAGE && row == 0) bulk_wait_read_all();
+        if (ROWSTAGE && row == 0) bulk_wait_read_all();
     } else {
         // ================================================================ transposed copy: thread = (32-row band, column pair)
         const int ct = threadIdx.x - 32 - kSGroupThreads;
         const int band = ct >> 5, pair = lane;
         const int chunk = pair >> 2;
         uint32_t stage = 0, phase = 0, tile_i = 0;
-        for (uint32_t t = blockIdx.x; t < (uint32_t) total_tiles; t += gridDim.x) {
-            const uint32_t gq = t / per_g, rem = t - gq * per_g;
-            const int tm = (int) (rem / (uint32_t) tiles_n), tn = (int) (rem - (uint32_t) tm * tiles_n);
-            int in_row0 = tm * kTileM, row_out0 = 0, n_valid = kTileM;
-            if constexpr (GROUPED)
-                if (!locate_group(tm, in_row0, n_valid, row_out0)) continue;
+        while (true) {
             if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
+            const int4 d0 = *reinterpret_cast<const int4 *>(&s_desc[stage]);
+            const int tn = d0.x, tm = d0.y;
+            const int64_t g = d0.z;
+            if (tn < 0) break;
+            const int n_valid = GROUPED ? s_desc[stage].n_valid : kTileM;
             uint32_t w[32];
-            if constexpr (COL) {
+            {
                 const uint8_t *cp = smem + stage * kQTileBytes + band * 32 * 128 + ((pair & 3) << 2);
 #pragma unroll
                 for (int r = 0; r < 32; ++r) {   // (32 band + r) % 8 == r % 8: every lane reads tile row r, no bank conflict
@@ -870,97 +894,86 @@ __global__ void __launch_bounds__(kSThreads, kSCtasPerSm)
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_bar[stage]);
             if (++stage == kSStages) { stage = 0; phase ^= 1; }
-            if constexpr (COL) {
-                const int buf = tile_i & 1;
-                ++tile_i;
-                uint32_t pm = 0u;
+            const int buf = tile_i & 1;
+            ++tile_i;
+            uint32_t pm = 0u;
 #pragma unroll
-                for (int r = 0; r < 32; ++r) pm = absmax2_nan_bf16(pm, w[r]);
-                const bool has_nan = packed_bf16_has_nan(pm);
-                if (has_nan) {
-                    pm = 0u;
+            for (int r = 0; r < 32; ++r) pm = absmax2_nan_bf16(pm, w[r]);
+            const bool has_nan = packed_bf16_has_nan(pm);
+            if (has_nan) {
+                pm = 0u;
 #pragma unroll
-                    for (int r = 0; r < 32; ++r) pm = absmax2<T>(pm, w[r]);
-                }
-                pm = absmax2_done(pm);
-                float m0c = bf16_lo(pm), m1c = bf16_hi(pm);
-                if constexpr (COL2D) {   // 32 x 32 tile: the 16 column pairs of this half warp
-                    float m = fmaxf(m0c, m1c);
-                    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-                    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-                    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
-                    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
-                    m0c = m1c = m;
-                }
-                const MxScale s0 = mx_scale<FMT>(m0c, GROUPED), s1 = mx_scale<FMT>(m1c, GROUPED);
-                const float i0 = s0.inv, i1 = s1.inv;
-                uint32_t o0[8], o1[8];   // 32 codes of column 2 pair and of column 2 pair + 1
-                if (has_nan && !kFp4) {
-                    const float nl0 = -MxParams<FMT>::qmax * s0.native, nl1 = -MxParams<FMT>::qmax * s1.native;
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        o0[k] = pack4_fp8<kFp4 ? PT_E4M3 : FMT>(fmaxf(bf16_lo(w[4 * k]), nl0) * i0, fmaxf(bf16_lo(w[4 * k + 1]), nl0) * i0,
-                                                                                    fmaxf(bf16_lo(w[4 * k + 2]), nl0) * i0, fmaxf(bf16_lo(w[4 * k + 3]), nl0) * i0);
-                        o1[k] = pack4_fp8<kFp4 ? PT_E4M3 : FMT>(fmaxf(bf16_hi(w[4 * k]), nl1) * i1, fmaxf(bf16_hi(w[4 * k + 1]), nl1) * i1,
-                                                                                    fmaxf(bf16_hi(w[4 * k + 2]), nl1) * i1, fmaxf(bf16_hi(w[4 * k + 3]), nl1) * i1);
-                    }
-                } else {
-                    const uint32_t inv2 = bf16_bits_x2(i0, i1);
-#pragma unroll
-                    for (int r = 0; r < 32; ++r) w[r] = mul_bf16x2(w[r], inv2);
-                    if constexpr (kFp4) {
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            o0[k] = pack8_e2m1(bf16_lo(w[8 * k]), bf16_lo(w[8 * k + 1]), bf16_lo(w[8 * k + 2]), bf16_lo(w[8 * k + 3]),
-                                               bf16_lo(w[8 * k + 4]), bf16_lo(w[8 * k + 5]), bf16_lo(w[8 * k + 6]), bf16_lo(w[8 * k + 7]));
-                            o1[k] = pack8_e2m1(bf16_hi(w[8 * k]), bf16_hi(w[8 * k + 1]), bf16_hi(w[8 * k + 2]), bf16_hi(w[8 * k + 3]),
-                                               bf16_hi(w[8 * k + 4]), bf16_hi(w[8 * k + 5]), bf16_hi(w[8 * k + 6]), bf16_hi(w[8 * k + 7]));
-                        }
-                    } else {
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-                            o0[k] = pack4_fp8<kFp4 ? PT_E4M3 : FMT>(bf16_lo(w[4 * k]), bf16_lo(w[4 * k + 1]), bf16_lo(w[4 * k + 2]), bf16_lo(w[4 * k + 3]));
-                            o1[k] = pack4_fp8<kFp4 ? PT_E4M3 : FMT>(bf16_hi(w[4 * k]), bf16_hi(w[4 * k + 1]), bf16_hi(w[4 * k + 2]), bf16_hi(w[4 * k + 3]));
-                        }
-                    }
-                }
-                if (s0.byte == 0) {   // such a column is written as (positive) zeros
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) o0[k] = 0u;
-                }
-                if (s1.byte == 0) {
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) o1[k] = 0u;
-                }
-                // staged transposed tile: row c = tile column c holds its 128 rows; this thread owns rows 32 band .. + 31
-                uint8_t *cs = col_stage + buf * kSStageOutBytes;
-#pragma unroll
-                for (int cc = 0; cc < 2; ++cc) {
-                    const int c = 2 * pair + cc;
-                    const uint32_t *o = cc ? o1 : o0;
-                    if constexpr (kFp4) {   // 64-byte rows, 64-byte swizzle; 16 bytes = chunk `band`
-                        *reinterpret_cast<uint4 *>(cs + c * 64 + ((band ^ ((c >> 1) & 3)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-                    } else {                // 128-byte rows, 128-byte swizzle; 32 bytes = chunks 2 band, 2 band + 1
-                        *reinterpret_cast<uint4 *>(cs + c * 128 + (((2 * band) ^ (c & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-                        *reinterpret_cast<uint4 *>(cs + c * 128 + (((2 * band + 1) ^ (c & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
-                    }
-                    s_colscale[buf][c][band] = cc ? s1.byte : s0.byte;
-                }
-                fence_proxy_async_smem();
-                if (ct == 0) bulk_wait_read_all();   // the store of the previous tile has read the other buffer
-                asm volatile("bar.sync 2, %0;" ::"n"(kSGroupThreads) : "memory");
-                const int64_t g = gq;
-                const int64_t m0 = (int64_t) tm * kTileM, n0 = (int64_t) tn * kTileN;
-                if (ct == 0) {
-                    tma_store_3d(&tmap_qcol, cs, (int) (kFp4 ? m0 / 2 : m0), (int) n0, (int) g);
-                    bulk_commit_group();
-                }
-                if (ct < kTileN && n0 + ct < a.N)   // the four band scales of column ct: one 32-bit store
-                    *reinterpret_cast<uint32_t *>(a.s_col + g * a.scol_gstride + (n0 + ct) * (a.M_pad / 32) + m0 / 32) =
-                        *reinterpret_cast<const uint32_t *>(&s_colscale[buf][ct][0]);
+                for (int r = 0; r < 32; ++r) pm = absmax2<T>(pm, w[r]);
             }
+            pm = absmax2_done(pm);
+            float m0c = bf16_lo(pm), m1c = bf16_hi(pm);
+            if constexpr (COL2D) {   // 32 x 32 tile: the 16 column pairs of this half warp
+                float m = fmaxf(m0c, m1c);
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+                m0c = m1c = m;
+            }
+            const MxScale s0 = mx_scale<FMT>(m0c, GROUPED), s1 = mx_scale<FMT>(m1c, GROUPED);
+            if (has_nan && !kFp4) {
+                const uint32_t nlim2 = bf16_bits_x2(-MxParams<FMT>::qmax * s0.native, -MxParams<FMT>::qmax * s1.native);
+#pragma unroll
+                for (int r = 0; r < 32; ++r) w[r] = max_bf16x2(w[r], nlim2);
+            }
+            const uint32_t inv2 = bf16_bits_x2(s0.inv, s1.inv);
+#pragma unroll
+            for (int r = 0; r < 32; ++r) w[r] = mul_bf16x2(w[r], inv2);
+            uint32_t o0[8], o1[8];   // 32 codes of column 2 pair and of column 2 pair + 1
+            if constexpr (kFp4) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    o0[k] = pack8_e2m1(bf16_lo(w[8 * k]), bf16_lo(w[8 * k + 1]), bf16_lo(w[8 * k + 2]), bf16_lo(w[8 * k + 3]),
+                                       bf16_lo(w[8 * k + 4]), bf16_lo(w[8 * k + 5]), bf16_lo(w[8 * k + 6]), bf16_lo(w[8 * k + 7]));
+                    o1[k] = pack8_e2m1(bf16_hi(w[8 * k]), bf16_hi(w[8 * k + 1]), bf16_hi(w[8 * k + 2]), bf16_hi(w[8 * k + 3]),
+                                       bf16_hi(w[8 * k + 4]), bf16_hi(w[8 * k + 5]), bf16_hi(w[8 * k + 6]), bf16_hi(w[8 * k + 7]));
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    o0[k] = pack4_fp8<FMT>(bf16_lo(w[4 * k]), bf16_lo(w[4 * k + 1]), bf16_lo(w[4 * k + 2]), bf16_lo(w[4 * k + 3]));
+                    o1[k] = pack4_fp8<FMT>(bf16_hi(w[4 * k]), bf16_hi(w[4 * k + 1]), bf16_hi(w[4 * k + 2]), bf16_hi(w[4 * k + 3]));
+                }
+            }
+            if (__any_sync(0xffffffffu, s0.byte == 0 || s1.byte == 0)) {   // such a column is written as (positive) zeros
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    if (s0.byte == 0) o0[k] = 0u;
+                    if (s1.byte == 0) o1[k] = 0u;
+                }
+            }
+            // staged transposed tile: row c = tile column c holds its 128 rows; this thread owns rows 32 band .. + 31
+            uint8_t *cs = col_stage + buf * kSStageOutBytes;
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+                const int c = 2 * pair + cc;
+                const uint32_t *o = cc ? o1 : o0;
+                if constexpr (kFp4) {   // 64-byte rows, 64-byte swizzle; 16 bytes = chunk `band`
+                    *reinterpret_cast<uint4 *>(cs + c * 64 + ((band ^ ((c >> 1) & 3)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                } else {                // 128-byte rows, 128-byte swizzle; 32 bytes = chunks 2 band, 2 band + 1
+                    *reinterpret_cast<uint4 *>(cs + c * 128 + (((2 * band) ^ (c & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<uint4 *>(cs + c * 128 + (((2 * band + 1) ^ (c & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+                }
+                s_colscale[buf][c][band] = cc ? s1.byte : s0.byte;
+            }
+            fence_proxy_async_smem();
+            if (ct == 0) bulk_wait_read_all();   // the store of the previous tile has read the other buffer
+            asm volatile("bar.sync 2, %0;" ::"n"(kSGroupThreads) : "memory");
+            const int64_t m0 = (int64_t) tm * kTileM, n0 = (int64_t) tn * kTileN;
+            if (ct == 0) {
+                tma_store_3d(&tmap_qcol, cs, (int) (kFp4 ? m0 / 2 : m0), (int) n0, (int) g);
+                bulk_commit_group();
+            }
+            if (ct < kTileN && n0 + ct < a.N)   // the four band scales of column ct: one 32-bit store
+                *reinterpret_cast<uint32_t *>(a.s_col + g * a.scol_gstride + (n0 + ct) * (a.M_pad / 32) + m0 / 32) =
+                    *reinterpret_cast<const uint32_t *>(&s_colscale[buf][ct][0]);
         }
-        if (COL && ct == 0) bulk_wait_read_all();
+        if (ct == 0) bulk_wait_read_all();
     }
     if (!ok || *abort_flag) {
         if (status && lane == 0) atomicExch(status, (int) PT_ERR_TIMEOUT);
@@ -1061,19 +1074,21 @@ static int launch_mx_split(const MxArgs &a, int64_t G, int64_t m_tiles_rows, uns
     trow = tx;
     if (kRowStage && (rc = make_tmap_out(&trow, a.q_row, G, a.M, a.N_pad, 64, kTileM)) != PT_OK) return rc;
     if ((rc = make_tmap_out(&tcol, a.q_col, G, a.N, kFp4 ? a.M_pad / 2 : a.M_pad, kFp4 ? 64 : 128, kTileN)) != PT_OK) return rc;
+    const int slot = tile_sched_acquire(st);
     const int grid = (int) std::min<int64_t>(total_tiles, (int64_t) sm_count() * kSCtasPerSm);
     const bool r2d = flags & PT_MX_ROW_2D, c2d = flags & PT_MX_COL_2D;
 #define PT_MXS_CASE(R2, C2)                                                                                       \
     if (r2d == R2 && c2d == C2) {                                                                                 \
-        auto kern = mx_quant_split_kernel<FMT, true, true, R2, C2, GROUPED, kRowStage>;                           \
+        auto kern = mx_quant_split_kernel<FMT, R2, C2, GROUPED, kRowStage>;                           \
         static bool attr_set_dev[64] = {};                                                                        \
         bool &attr_set = attr_set_dev[current_device_slot()];                                                     \
         if (!attr_set) {                                                                                          \
             PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSSmemBytes));     \
             attr_set = true;                                                                                      \
         }                                                                                                         \
-        PT_CUDA_OK(launch_overlapped(kern, dim3(grid), dim3(kSThreads), kSSmemBytes, st, tx, trow, tcol, a, tiles_n, tiles_m, total_tiles, (int *) nullptr)); \
+        PT_CUDA_OK(launch_overlapped(kern, dim3(grid), dim3(kSThreads), kSSmemBytes, st, tx, trow, tcol, a, tiles_n, tiles_m, total_tiles, slot, default_status())); \
         PT_LAUNCH_OK();                                                                                           \
+        tile_sched_release(slot, st);                                                                             \
         return PT_OK;                                                                                             \
     }
     PT_MXS_CASE(false, false)
@@ -1120,7 +1135,7 @@ static int launch_mx(const MxArgs &a, int64_t G, unsigned flags, cudaStream_t st
                 PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kQSmemBytes)); \
                 attr_set = true;                                                                           \
             }                                                                                              \
-            PT_CUDA_OK(launch_overlapped(kern, dim3(tma_grid), dim3(kQThreads), kQSmemBytes, st, tmap, a, tiles_n, tiles_m, total_tiles, (int *) nullptr)); \
+            PT_CUDA_OK(launch_overlapped(kern, dim3(tma_grid), dim3(kQThreads), kQSmemBytes, st, tmap, a, tiles_n, tiles_m, total_tiles, default_status())); \
         } else {                                                                                           \
             mx_quant_kernel<T, FMT, R, C, R2, C2, RR, CR><<<grid, kMxThreads, 0, st>>>(a);                 \
         }                                                                                                  \
@@ -1180,7 +1195,7 @@ static int launch_mx_grouped(const MxArgs &a, int64_t m_alloc, unsigned flags, c
         if (use_tma) {                                                                                \
             auto kern = mx_quant_tma_kernel<T, FMT, R, C, false, false, RR, CR, true>;               \
             PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kQSmemBytes)); \
-            PT_CUDA_OK(launch_overlapped(kern, dim3(tma_grid), dim3(kQThreads), kQSmemBytes, st, tmap, a, tiles_n, tiles_m, total_tiles, (int *) nullptr)); \
+            PT_CUDA_OK(launch_overlapped(kern, dim3(tma_grid), dim3(kQThreads), kQSmemBytes, st, tmap, a, tiles_n, tiles_m, total_tiles, default_status())); \
         } else {                                                                                      \
             mx_quant_kernel<T, FMT, R, C, false, false, RR, CR, true><<<grid, kMxThreads, 0, st>>>(a); \
         }                                                                                             \

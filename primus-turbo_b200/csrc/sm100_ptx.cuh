@@ -53,9 +53,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait in these kernels
 
-// Returns true when the phase completed; false when the limit passed or the CTA is aborting.
+// Returns true when the phase completed; false when `limit_ns` passed or the CTA is aborting.
 // On a timeout the caller's CTA-wide abort flag is raised so every other waiter unwinds at once.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+__device__ __forceinline__ bool mbar_wait_limited(uint64_t *bar, uint32_t parity, volatile int *abort_flag, uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     // The clock is first read after 64 failed polls (a read of %globaltimer costs far more than a poll, and most
     // waits end within a few polls); the limit counts from that first reading.
@@ -68,12 +68,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
             const uint64_t now = globaltimer_ns();
             if (t0 == 0) {
                 t0 = now;
-            } else if (now - t0 > kWaitLimitNs) {
+            } else if (now - t0 > limit_ns) {
                 *abort_flag = 1;
                 return false;
             }
         }
     }
+}
+// The production form: every wait of the GEMM and quantize kernels gives up after kWaitLimitNs.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+    return mbar_wait_limited(bar, parity, abort_flag, kWaitLimitNs);
 }
 
 // 3-D tiled load global -> this CTA's shared memory, completion counted in bytes on `bar`.

@@ -16,6 +16,8 @@ c_void_p, c_int, c_int64, c_float, c_size_t, c_uint = (ctypes.c_void_p, ctypes.c
 SIGNATURES = {
     "pt_last_error": (ctypes.c_char_p, []),
     "pt_device_sm_count": (c_int, []),
+    "pt_set_default_status": (c_int, [c_void_p]),
+    "pt_wait_probe": (c_int, [c_int64, c_void_p, c_void_p, c_void_p]),
     "pt_quantize_fp8_tensorwise_workspace_bytes": (c_size_t, []),
     "pt_quantize_fp8_tensorwise": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                            c_size_t, c_void_p]),

@@ -29,6 +29,7 @@ def _gemm_fp4(a, a_scale_inv, trans_a, b, b_scale_inv, trans_b, out_dtype, trans
     with nv.on_device(a.device):
         nv.check(lib.pt_gemm_fp4(nv.ptr(a), nv.ptr(a_s), nv.ptr(b), nv.ptr(b_s), nv.ptr(out), nv.src_code(out.dtype), M, N, K, beta, 0,
                                  nv.ptr(ws), ws_bytes, nv.ptr(st), nv.stream(a.device)), "gemm_fp4")
+    nv.poll_status(out.device)
     return out
 
 

@@ -85,6 +85,7 @@ def _launch_blockwise(a_op, a_desc, a_s, b_op, b_desc, b_s, out, beta, M, N, kc)
             nv.ptr(b_t), nv.fmt_code(b_t.dtype), b_mn, b_r, b_c, nv.ptr(b_s), *b_desc, 0,
             nv.ptr(out), nv.src_code(out.dtype), M, N, K, None, None, None, 1, float(beta), 0, nv.ptr(st),
             nv.stream(out.device)), "gemm_fp8_blockwise")
+    nv.poll_status(out.device)
     return out
 
 
@@ -100,6 +101,7 @@ def _launch(a_km, a_s, b_km, b_s, out, gran, beta, block_n=0):
                                        nv.fmt_code(b_km.dtype), nv.ptr(out), nv.src_code(out.dtype), _GRAN[gran], M, N, K,
                                        float(beta), block_n, nv.ptr(ws), ws_bytes, nv.ptr(st), nv.stream(out.device)),
                  "gemm_fp8")
+    nv.poll_status(out.device)
     return out
 
 

@@ -31,6 +31,7 @@ def _launch(a_km, b_km, out, beta):
     with nv.on_device(out.device):
         nv.check(nv.lib().pt_gemm(nv.ptr(a_km), nv.ptr(b_km), nv.src_code(a_km.dtype), nv.ptr(out), nv.src_code(out.dtype), M, N, K,
                                    float(beta), nv.ptr(st), nv.stream(out.device)), "gemm")
+    nv.poll_status(out.device)
     return out
 
 

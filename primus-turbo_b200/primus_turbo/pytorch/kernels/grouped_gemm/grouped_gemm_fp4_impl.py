@@ -33,6 +33,7 @@ def grouped_gemm_fp4_impl(a, b, a_scales, b_scales, group_lens, group_offs, tran
                                          nv.src_code(out_dtype), rows, rows, N, K, nv.ptr(offs_read), nv.ptr(offs_write), G, 0.0, 0,
                                          int(num_cu) if num_cu else 0, nv.ptr(ws), ws_bytes, nv.ptr(st), nv.stream(a.device)),
                  "grouped_gemm_fp4")
+    nv.poll_status(out.device)
     return out
 
 
@@ -57,6 +58,7 @@ def _variable_k(a, b, a_scales, b_scales, group_lens, group_offs, out_dtype, num
                                                     nv.ptr(out), nv.src_code(out.dtype), M, N, T, nv.ptr(k_offs), G, beta, 0,
                                                     int(num_cu) if num_cu else 0, nv.ptr(ws), ws_bytes, nv.ptr(st),
                                                     nv.stream(a.device)), "grouped_gemm_fp4_variable_k")
+    nv.poll_status(out.device)
     return out
 
 

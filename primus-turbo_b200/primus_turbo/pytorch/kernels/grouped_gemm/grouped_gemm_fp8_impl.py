@@ -70,6 +70,7 @@ def grouped_gemm_fp8_impl(a: torch.Tensor, b: torch.Tensor, a_scales: torch.Tens
                 nv.ptr(b), nv.fmt_code(b.dtype), b_mn, b_rows, b_cols, nv.ptr(b_s), *b_desc,
                 nv.ptr(out), nv.src_code(out_dtype), rows, N, K, nv.ptr(offs_read), nv.ptr(offs_write), None, G, 0.0,
                 max_ctas, nv.ptr(st), nv.stream(a.device)), "grouped_gemm_fp8_blockwise")
+            nv.poll_status(out.device)
             return out
         assert trans_b, "this granularity takes b as [G, N, K] (trans_b=True)"
         if gran in (ScalingGranularity.TENSORWISE, ScalingGranularity.ROWWISE):
@@ -82,6 +83,7 @@ def grouped_gemm_fp8_impl(a: torch.Tensor, b: torch.Tensor, a_scales: torch.Tens
                                          nv.fmt_code(b.dtype), nv.ptr(out), nv.src_code(out_dtype), _GRAN[gran], rows, rows, N, K,
                                          nv.ptr(offs_read), nv.ptr(offs_write), G, 0.0, 0, max_ctas, nv.ptr(ws), ws_bytes,
                                          nv.ptr(st), nv.stream(a.device)), "grouped_gemm_fp8")
+    nv.poll_status(out.device)
     return out
 
 
@@ -112,6 +114,7 @@ def _variable_k(a, b, a_scales, b_scales, group_lens, group_offs, trans_a, trans
                 nv.ptr(rhs), nv.fmt_code(rhs.dtype), 1, T, Nn, nv.ptr(rhs_s), 0, 1, Nn, 0,
                 nv.ptr(out), nv.src_code(out.dtype), R, Nn, T, None, None, nv.ptr(k_offs), G, beta, max_ctas, nv.ptr(st),
                 nv.stream(a.device)), "grouped_gemm_fp8_blockwise_variable_k")
+            nv.poll_status(out.device)
             return out
         # K-major operands sharing the padded token axis as contraction: a [Ra, T], b [Rb, T]; C[g] = a[:, seg] . b[:, seg]^T
         assert not trans_a and not trans_b, "variable-K takes [rows, tokens] operands (trans_a=False, trans_b=False)"
@@ -130,6 +133,7 @@ def _variable_k(a, b, a_scales, b_scales, group_lens, group_offs, trans_a, trans
                                                     nv.fmt_code(rhs.dtype), nv.ptr(out), nv.src_code(out.dtype), _GRAN[gran], R, Nn, T,
                                                     nv.ptr(k_offs), G, beta, 0, max_ctas, nv.ptr(ws), ws_bytes, nv.ptr(st),
                                                     nv.stream(a.device)), "grouped_gemm_fp8_variable_k")
+    nv.poll_status(out.device)
     return out
 
 

@@ -34,6 +34,7 @@ def grouped_gemm_impl(a: torch.Tensor, b: torch.Tensor, group_lens: torch.Tensor
         nv.check(nv.lib().pt_grouped_gemm(nv.ptr(a), nv.ptr(b_km), nv.src_code(a.dtype), nv.ptr(out), nv.src_code(out.dtype), rows, N, K,
                                            nv.ptr(offs), G, 0.0, int(num_cu) if num_cu else 0, nv.ptr(st), nv.stream(a.device)),
                  "grouped_gemm")
+    nv.poll_status(out.device)
     return out
 
 
@@ -60,6 +61,7 @@ def _variable_k(a, b, group_lens, group_offs, trans_a, trans_b, trans_c, num_cu,
                                                       nv.src_code(out.dtype), R, Nn, T, nv.ptr(poffs), G, beta,
                                                       int(num_cu) if num_cu else 0, nv.ptr(st), nv.stream(a.device)),
                  "grouped_gemm_variable_k")
+    nv.poll_status(out.device)
     return out
 
 
