@@ -146,6 +146,8 @@ int pt_compute_padded_group_offs(const int64_t *lens, int G, int64_t align, int6
 #define PT_MX_COL_2D 8u     /* col copy uses one scale per 32 x 32 tile */
 #define PT_MX_ROW_RHT 16u   /* e2m1 only: 16-point Hadamard along the quantized axis before amax */
 #define PT_MX_COL_RHT 32u
+#define PT_MX_ROW_SR 64u    /* e2m1 only: stochastic rounding of the row copy (a fresh seed per call; unbiased, not */
+#define PT_MX_COL_SR 128u   /*            reproducible -- quantization_mxfp4.cu:59-71,241-274 of the reference)     */
 
 /* x [G, M, N] (G = 1 for 2-D), bf16 / fp16, N % 32 == 0.  M_pad = ceil128(M), N_pad = ceil128(N).
  * fmt e4m3 / e5m2: q_row [G, M, N_pad], s_row [G, M, N_pad/32]; q_col [G, N, M_pad], s_col [G, N, M_pad/32].

@@ -64,9 +64,11 @@ inline int64_t ceil_to(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
 // ---------------------------------------------------------------- element access
 template <typename T> struct Src;
 template <> struct Src<__nv_bfloat16> {
+    static constexpr uint32_t kInfBits = 0x7F80u;
     static __device__ __forceinline__ float to_f32(uint16_t b) { return __uint_as_float((uint32_t) b << 16); }
 };
 template <> struct Src<__half> {
+    static constexpr uint32_t kInfBits = 0x7C00u;
     static __device__ __forceinline__ float to_f32(uint16_t b) { return __half2float(__ushort_as_half(b)); }
 };
 
@@ -107,6 +109,25 @@ template <> __device__ __forceinline__ uint32_t absmax2<__half>(uint32_t m, uint
     return r;
 }
 __device__ __forceinline__ uint32_t absmax2_done(uint32_t m) { return m & 0x7FFF7FFFu; }
+// The same with NaN propagation: a NaN half in any input leaves a NaN in that half of the running maximum, which is how
+// the quantizers find the (rare) blocks that hold a NaN without a test per element.
+template <typename T> __device__ __forceinline__ uint32_t absmax2_nan(uint32_t m, uint32_t w);
+template <> __device__ __forceinline__ uint32_t absmax2_nan<__nv_bfloat16>(uint32_t m, uint32_t w) {
+    uint32_t r;
+    asm("max.NaN.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(m), "r"(w));
+    return r;
+}
+template <> __device__ __forceinline__ uint32_t absmax2_nan<__half>(uint32_t m, uint32_t w) {
+    uint32_t r;
+    asm("max.NaN.xorsign.abs.f16x2 %0, %1, %2;" : "=r"(r) : "r"(m), "r"(w));
+    return r;
+}
+// either half of a packed running maximum is a NaN
+template <typename T> __device__ __forceinline__ bool packed_has_nan(uint32_t pm) {
+    const uint32_t a = pm & 0x7FFF7FFFu;
+    const uint32_t lim = Src<T>::kInfBits;
+    return ((a & 0xFFFFu) > lim) | ((a >> 16) > lim);
+}
 template <typename T> __device__ __forceinline__ float lo_f32(uint32_t w) { return Src<T>::to_f32((uint16_t) (w & 0xFFFF)); }
 template <typename T> __device__ __forceinline__ float hi_f32(uint32_t w) { return Src<T>::to_f32((uint16_t) (w >> 16)); }
 

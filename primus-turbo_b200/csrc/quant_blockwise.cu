@@ -11,6 +11,7 @@
 #include "common.cuh"
 #include "gemm_common.cuh"
 #include "sm100_ptx.cuh"
+#include "tile_sched.cuh"
 
 namespace ptb {
 
@@ -214,6 +215,12 @@ struct BqArgs {
     float *s_row, *s_col;
     SegmentArgs seg;
     int *status;               // receives PT_ERR_TIMEOUT if a bounded wait gives up (may be null)
+    int sched_slot;            // dynamic tile schedule: counter slot (tile_sched.cuh), or -1 for the static schedule
+};
+
+// what the producer hands over with each tile (col_blk < 0: no more tiles)
+struct BqTileDesc {
+    int batch, pid_m, col_blk, in_row0, n_valid, pad0, pad1, pad2;
 };
 
 template <typename T, int FMT, int MODE>
@@ -230,6 +237,7 @@ __global__ void __launch_bounds__(kBqThreads, kBqCtasPerSm)
     uint64_t *empty_bar = full_bar + kBqStages;
     __shared__ uint2 s_cmax[2][kBqConsumerWarps][32];  // packed column maxima of each 16-row band
     __shared__ float s_wmax[2][kBqConsumerWarps];
+    __shared__ __align__(16) BqTileDesc s_desc[kBqStages];
     __shared__ int s_abort;
     volatile int *abort_flag = &s_abort;
 
@@ -287,17 +295,25 @@ __global__ void __launch_bounds__(kBqThreads, kBqCtasPerSm)
     if (warp == 0) {
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
-            for (uint32_t t = blockIdx.x; t < (uint32_t) a.total_tiles; t += gridDim.x) {
+            // the producer resolves every tile once (coordinates, and in the segment form its group) and hands the result
+            // over in shared memory next to the data; tiles come from the dynamic schedule when a counter slot was given
+            for (uint32_t t = blockIdx.x; t < (uint32_t) a.total_tiles; t = tile_sched_next(a.sched_slot, t)) {
                 int64_t batch, pid_m, col_blk, in_row0;
                 int n_valid;
                 if (!locate(t, batch, pid_m, col_blk, in_row0, n_valid)) continue;
                 if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
+                s_desc[stage] = BqTileDesc{(int) batch, (int) pid_m, (int) col_blk, (int) in_row0, n_valid, 0, 0, 0};
                 mbar_arrive_expect_tx(&full_bar[stage], kBqTileBytes);
                 uint8_t *dst = smem + stage * kBqTileBytes;
                 tma_load_3d(dst, &tmap, &full_bar[stage], (int) (col_blk * kBlk), (int) in_row0, (int) batch);
                 tma_load_3d(dst + kBqTileBytes / 2, &tmap, &full_bar[stage], (int) (col_blk * kBlk + 64), (int) in_row0, (int) batch);
                 if (++stage == kBqStages) { stage = 0; phase ^= 1; }
             }
+            if (ok && (ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) {   // the terminal descriptor
+                s_desc[stage].col_blk = -1;
+                mbar_arrive(&full_bar[stage]);
+            }
+            tile_sched_done(a.sched_slot);
         }
     } else {
         const int cw = warp - 1;
@@ -308,11 +324,12 @@ __global__ void __launch_bounds__(kBqThreads, kBqCtasPerSm)
         // col pass: lane = column quad of the 128-wide tile row, warp = band of 16 rows
         const int c_box = lane >> 4, c_chunk = (lane & 15) >> 1, c_off = (lane & 1) << 3;
         uint32_t stage = 0, phase = 0, tile_count = 0;
-        for (uint32_t t = blockIdx.x; t < (uint32_t) a.total_tiles; t += gridDim.x) {
-            int64_t batch, pid_m, col_blk, in_row0;
-            int n_valid;
-            if (!locate(t, batch, pid_m, col_blk, in_row0, n_valid)) continue;
+        while (true) {
             if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
+            const int4 d0 = *reinterpret_cast<const int4 *>(&s_desc[stage]);
+            if (d0.z < 0) break;
+            const int64_t batch = d0.x, pid_m = d0.y, col_blk = d0.z, in_row0 = d0.w;
+            const int n_valid = s_desc[stage].n_valid;
             const uint8_t *tile = smem + stage * kBqTileBytes;
             const int buf = tile_count & 1;
             ++tile_count;
@@ -661,7 +678,7 @@ static int launch_tile(const void *x, int x_dtype, int64_t B, int64_t m_tiles, i
         CUtensorMap tmap;
         int rc = make_tmap_u16_3d(&tmap, x, B, M, N, kBlk);
         if (rc != PT_OK) return rc;
-        BqArgs a{M, N, (int) tiles_n, (int) m_tiles, total_tiles, (uint8_t *) q_row, (uint8_t *) q_col, s_row, s_col, seg, default_status()};
+        BqArgs a{M, N, (int) tiles_n, (int) m_tiles, total_tiles, (uint8_t *) q_row, (uint8_t *) q_col, s_row, s_col, seg, default_status(), tile_sched_acquire((cudaStream_t) stream)};
         const int tma_grid = (int) std::min<int64_t>(total_tiles, (int64_t) sm_count() * kBqCtasPerSm);
 #define PT_BQ_LAUNCH(T_)                                                                                           \
         PT_SWITCH_FP8(fmt, F, {                                                                                    \
@@ -672,6 +689,7 @@ static int launch_tile(const void *x, int x_dtype, int64_t B, int64_t m_tiles, i
         if (x_dtype == PT_BF16) { PT_BQ_LAUNCH(__nv_bfloat16); } else { PT_BQ_LAUNCH(__half); }
 #undef PT_BQ_LAUNCH
         PT_LAUNCH_OK();
+        tile_sched_release(a.sched_slot, (cudaStream_t) stream);
         return PT_OK;
     }
     PT_SWITCH_SRC(x_dtype, T, {

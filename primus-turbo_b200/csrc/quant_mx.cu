@@ -12,6 +12,7 @@
 //   fp8:  q = rne(clamp(v, +-qmax * scale) / scale)  (a NaN becomes -qmax)        fp4: q = rne_sat(v / scale)
 // A block whose scale byte is 0 (every |v| < 2^-118 or so) is written as zeros.
 #include <algorithm>
+#include <atomic>
 #include <type_traits>
 
 #include "common.cuh"
@@ -51,14 +52,48 @@ template <int FMT> __device__ __forceinline__ MxScale mx_scale(float amax, bool 
     return s;
 }
 
+// ---- stochastic rounding (e2m1 only).  The reference seeds every launch from a process-wide counter and hashes the
+// seed with the thread index (quantization_mxfp4.cu:59-71, :518); its results are "unbiased, not bit-exact" by its own
+// account.  Here: the same per-launch counter, a 32-bit mixer over (seed, position of the 4-element group), and the
+// hardware's stochastic convert, which takes four floats and 32 random bits.
+__device__ __forceinline__ uint32_t sr_mix(uint32_t x) {   // "lowbias32" integer hash
+    x ^= x >> 16; x *= 0x7feb352du;
+    x ^= x >> 15; x *= 0x846ca68bu;
+    x ^= x >> 16;
+    return x;
+}
+// four floats -> four e2m1 codes with stochastic rounding, a in the lowest nibble (the instruction puts its FIRST operand
+// in the highest nibble)
+__device__ __forceinline__ uint32_t cvt4_e2m1_sr(float a, float b, float c, float d, uint32_t rbits) {
+    uint16_t r;
+    asm("cvt.rs.satfinite.e2m1x4.f32 %0, {%1, %2, %3, %4}, %5;" : "=h"(r) : "f"(d), "f"(c), "f"(b), "f"(a), "r"(rbits));
+    return r;
+}
+static inline uint32_t sr_seed_from(uint32_t n) {   // host: launch number -> seed (never 0)
+    uint32_t x = n * 0x9e3779b9u + 0x85ebca6bu;
+    x ^= x >> 16; x *= 0x7feb352du;
+    x ^= x >> 15; x *= 0x846ca68bu;
+    x ^= x >> 16;
+    return x | 1u;
+}
+struct SrState {
+    uint32_t key;   // 0: round to nearest even; else seed-derived key, advanced once per 4-element group
+    __device__ __forceinline__ bool on() const { return key != 0u; }
+    __device__ __forceinline__ uint32_t next() { key = sr_mix(key + 0x9e3779b9u); return key; }
+};
+
 // 8 scaled values -> 8 codes packed into 8 bytes (fp8) or 4 bytes (fp4)
-template <int FMT> __device__ __forceinline__ uint2 mx_encode8(const float (&v)[8], const MxScale &s) {
+template <int FMT> __device__ __forceinline__ uint2 mx_encode8(const float (&v)[8], const MxScale &s, SrState *sr = nullptr) {
     uint2 o = make_uint2(0u, 0u);
     if (s.byte == 0) return o;
     float t[8];
     if constexpr (FMT == PT_E2M1) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) t[i] = v[i] * s.inv;
+        if (sr != nullptr && sr->on()) {
+            o.x = cvt4_e2m1_sr(t[0], t[1], t[2], t[3], sr->next()) | (cvt4_e2m1_sr(t[4], t[5], t[6], t[7], sr->next()) << 16);
+            return o;
+        }
         o.x = (uint32_t) cvt2_e2m1(t[0], t[1]) | ((uint32_t) cvt2_e2m1(t[2], t[3]) << 8) |
               ((uint32_t) cvt2_e2m1(t[4], t[5]) << 16) | ((uint32_t) cvt2_e2m1(t[6], t[7]) << 24);
     } else {
@@ -102,6 +137,8 @@ struct MxArgs {
     // grouped form: rows of x are split into groups; the tile grid runs over the 128-padded row space
     const int64_t *group_offs, *poffs_row, *poffs_col;
     int num_groups;
+    uint32_t sr_seed;        // stochastic rounding (e2m1): per-launch seed, never 0 when one of the two flags is set
+    int sr_row, sr_col;
 };
 
 // grid: (N_pad / 64, M_pad / 128, G); GROUPED: (N_pad / 64, (M + groups * 128) / 128, 1)
@@ -219,7 +256,8 @@ __global__ void __launch_bounds__(kMxThreads) mx_quant_kernel(MxArgs a) {
                 m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
             }
             const MxScale s = mx_scale<FMT>(m, GROUPED);
-            const uint2 o = mx_encode8<FMT>(t, s);
+            SrState sr{a.sr_row ? sr_mix(a.sr_seed ^ (uint32_t) ((gm * a.N_pad + gn) >> 2)) | 1u : 0u};
+            const uint2 o = mx_encode8<FMT>(t, s, &sr);
             if (gm < in_end && gn < a.N_pad) {
                 uint8_t *qr = a.q_row + g * a.qrow_gstride;
                 if constexpr (kFp4) *reinterpret_cast<uint32_t *>(qr + (go * a.N_pad + gn) / 2) = o.x;
@@ -251,12 +289,13 @@ __global__ void __launch_bounds__(kMxThreads) mx_quant_kernel(MxArgs a) {
             const int64_t gm = m0 + band * 32;
             uint8_t *qc = a.q_col + g * a.qcol_gstride;
             uint32_t w[8];
+            SrState sr{a.sr_col ? sr_mix(~a.sr_seed ^ (uint32_t) ((gc * a.M_pad + gm) >> 2)) | 1u : 0u};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 float t[8];
 #pragma unroll
                 for (int k = 0; k < 8; ++k) t[k] = c[8 * j + k];
-                const uint2 o = mx_encode8<FMT>(t, s);
+                const uint2 o = mx_encode8<FMT>(t, s, &sr);
                 if constexpr (kFp4) w[j] = o.x; else { w[2 * j] = o.x; w[2 * j + 1] = o.y; }
             }
             if constexpr (kFp4) {
@@ -288,13 +327,22 @@ constexpr int kQMaxGroups = 256;  // grouped form: offset tables of up to this m
 
 // 32 scaled values -> 32 fp8 codes (8 words) or 32 fp4 codes (4 words).  Of the reference's soft clamp to +-qmax*scale
 // only fmax(v, -lim) is kept (it sends a NaN to -qmax as the reference does); the saturating convert does the rest.
-template <int FMT> __device__ __forceinline__ void mx_encode32(const float (&v)[32], const MxScale &s, uint32_t (&w)[8]) {
+template <int FMT> __device__ __forceinline__ void mx_encode32(const float (&v)[32], const MxScale &s, uint32_t (&w)[8], SrState *sr = nullptr) {
     if (s.byte == 0) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) w[i] = 0u;
         return;
     }
     if constexpr (FMT == PT_E2M1) {
+        if (sr != nullptr && sr->on()) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float *t = &v[8 * i];
+                w[i] = cvt4_e2m1_sr(t[0] * s.inv, t[1] * s.inv, t[2] * s.inv, t[3] * s.inv, sr->next()) |
+                       (cvt4_e2m1_sr(t[4] * s.inv, t[5] * s.inv, t[6] * s.inv, t[7] * s.inv, sr->next()) << 16);
+            }
+            return;
+        }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float *t = &v[8 * i];
@@ -481,7 +529,8 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
                 const float m = ROW2D ? __uint_as_float(amax2d[r_row >> 5][r_blk]) : r_amax;
                 const MxScale sc = mx_scale<FMT>(m, GROUPED);
                 uint32_t w[8];
-                mx_encode32<FMT>(rv, sc, w);
+                SrState sr{a.sr_row ? sr_mix(a.sr_seed ^ (uint32_t) ((gm * a.N_pad + gn) >> 2)) | 1u : 0u};
+                mx_encode32<FMT>(rv, sc, w, &sr);
                 if ((GROUPED ? r_row < n_valid : gm < a.M) && gn < a.N_pad) {
                     uint8_t *qr = a.q_row + g * a.qrow_gstride;
                     if constexpr (kFp4) {
@@ -547,7 +596,8 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
                         float t0[8], t1[8];
 #pragma unroll
                         for (int k = 0; k < 8; ++k) { t0[k] = cv[k]; t1[k] = cv[8 + k]; }
-                        uint2 o0 = mx_encode8<FMT>(t0, sc), o1 = mx_encode8<FMT>(t1, sc);
+                        SrState sr{a.sr_col ? sr_mix(~a.sr_seed ^ (uint32_t) (((gc + cc) * a.M_pad + gm) >> 2)) | 1u : 0u};
+                        uint2 o0 = mx_encode8<FMT>(t0, sc, &sr), o1 = mx_encode8<FMT>(t1, sc, &sr);
                         if constexpr (kWide) {  // value r holds row r ^ k: undo the permutation on the codes
                             if constexpr (kFp4) {   // 8 codes per word: nibble r of o?.x
                                 if (c_k & 1) {
@@ -1059,7 +1109,7 @@ template <int FMT, bool GROUPED>
 static int launch_mx_split(const MxArgs &a, int64_t G, int64_t m_tiles_rows, unsigned flags, cudaStream_t st) {
     if (getenv("PT_MX_QUANT_NO_SPLIT") != nullptr) return PT_ERR_UNSUPPORTED;
     const bool row = flags & PT_MX_ROW, col = flags & PT_MX_COL;
-    if (!row || !col || (flags & (PT_MX_ROW_RHT | PT_MX_COL_RHT))) return PT_ERR_UNSUPPORTED;
+    if (!row || !col || (flags & (PT_MX_ROW_RHT | PT_MX_COL_RHT | PT_MX_ROW_SR | PT_MX_COL_SR))) return PT_ERR_UNSUPPORTED;
     constexpr bool kFp4 = FMT == PT_E2M1;
     if (!aligned(a.x, 16) || !aligned(a.q_row, 16) || !aligned(a.q_col, 16) || !aligned(a.s_row, 2) || !aligned(a.s_col, 4)) return PT_ERR_UNSUPPORTED;
     if (a.M >= (1ll << 31) || m_tiles_rows >= (1ll << 31)) return PT_ERR_UNSUPPORTED;
@@ -1215,6 +1265,15 @@ static int launch_mx_grouped(const MxArgs &a, int64_t m_alloc, unsigned flags, c
     return set_error(PT_ERR_UNSUPPORTED, "grouped MX quantize: flag combination 0x%x is not built", flags);
 }
 
+// Every launch that rounds stochastically takes a fresh seed from a process-wide counter (as the reference does,
+// quantization_mxfp4.cu:62,1141): two calls on the same input draw different bits.
+static void set_sr(MxArgs &a, unsigned flags) {
+    static std::atomic<uint32_t> counter{1};
+    a.sr_row = (flags & PT_MX_ROW_SR) != 0;
+    a.sr_col = (flags & PT_MX_COL_SR) != 0;
+    a.sr_seed = (a.sr_row || a.sr_col) ? sr_seed_from(counter.fetch_add(1, std::memory_order_relaxed)) : 0u;
+}
+
 }  // namespace ptb
 
 using namespace ptb;
@@ -1233,13 +1292,15 @@ int pt_grouped_quantize_mx(const void *x, int x_dtype, int64_t M, int64_t N, int
     PT_REQUIRE(!(flags & PT_MX_ROW) || (q_row && s_row && padded_offs_row), "grouped MX quantize: row outputs missing");
     PT_REQUIRE(!(flags & PT_MX_COL) || (q_col && s_col), "grouped MX quantize: col outputs missing");
     PT_REQUIRE(col_alloc % 128 == 0 && col_alloc >= M, "grouped MX quantize: col_alloc must be the 128-multiple width of the col-wise buffers");
-    PT_REQUIRE(fmt == PT_E2M1 || !(flags & (PT_MX_ROW_RHT | PT_MX_COL_RHT)), "grouped MX quantize: RHT is an e2m1 option");
+    PT_REQUIRE(fmt == PT_E2M1 || !(flags & (PT_MX_ROW_RHT | PT_MX_COL_RHT | PT_MX_ROW_SR | PT_MX_COL_SR)),
+               "grouped MX quantize: RHT and stochastic rounding are e2m1 options");
     if (N == 0) return PT_OK;
     PT_REQUIRE(x == nullptr ? M == 0 : aligned(x, 16), "grouped MX quantize: input must be 16-byte aligned");
     MxArgs a{};
     a.x = x; a.M = M; a.N = N; a.M_pad = col_alloc; a.N_pad = ceil_to(N, 128);
     a.q_row = (uint8_t *) q_row; a.s_row = s_row; a.q_col = (uint8_t *) q_col; a.s_col = s_col;
     a.group_offs = group_offs; a.poffs_row = padded_offs_row; a.poffs_col = padded_offs_col; a.num_groups = G;
+    set_sr(a, flags);
     const int64_t m_alloc = col_alloc;  // the padded row space never exceeds the width the caller allocated for it
     PT_REQUIRE(m_alloc / kTileM <= 65535, "grouped MX quantize: too many rows");
     cudaStream_t st = (cudaStream_t) stream;
@@ -1263,7 +1324,8 @@ int pt_quantize_mx(const void *x, int x_dtype, int64_t G, int64_t M, int64_t N, 
     PT_REQUIRE(flags & (PT_MX_ROW | PT_MX_COL), "MX quantize: no output requested");
     PT_REQUIRE(!(flags & PT_MX_ROW) || (q_row && s_row), "MX quantize: row outputs missing");
     PT_REQUIRE(!(flags & PT_MX_COL) || (q_col && s_col), "MX quantize: col outputs missing");
-    PT_REQUIRE(fmt == PT_E2M1 || !(flags & (PT_MX_ROW_RHT | PT_MX_COL_RHT)), "MX quantize: RHT is an e2m1 option");
+    PT_REQUIRE(fmt == PT_E2M1 || !(flags & (PT_MX_ROW_RHT | PT_MX_COL_RHT | PT_MX_ROW_SR | PT_MX_COL_SR)),
+               "MX quantize: RHT and stochastic rounding are e2m1 options");
     if (M == 0 || N == 0) return PT_OK;
     PT_REQUIRE(x && aligned(x, 16), "MX quantize: input must be 16-byte aligned");
     PT_REQUIRE(G <= 65535, "MX quantize: batch too large");
@@ -1275,6 +1337,7 @@ int pt_quantize_mx(const void *x, int x_dtype, int64_t G, int64_t M, int64_t N, 
     a.x_gstride = M * N;
     a.qrow_gstride = M * a.N_pad / div; a.srow_gstride = M * (a.N_pad / 32);
     a.qcol_gstride = N * a.M_pad / div; a.scol_gstride = N * (a.M_pad / 32);
+    set_sr(a, flags);
     cudaStream_t st = (cudaStream_t) stream;
     if (x_dtype == PT_BF16) {
         if (fmt == PT_E4M3) return launch_mx<__nv_bfloat16, PT_E4M3>(a, G, flags, st);

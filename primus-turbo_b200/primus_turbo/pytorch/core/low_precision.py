@@ -96,12 +96,12 @@ class Float4QuantConfig:
     strategy: ScalingStrategy = ScalingStrategy.DYNAMIC
     scale_dtype: ScaleDtype = ScaleDtype.E8M0
     block_size: Optional[int] = MXFP4_BLOCK_SIZE
-    use_gradient_sr: bool = False   # stochastic rounding of gradients: not provided on B200
+    use_gradient_sr: bool = False   # stochastic rounding when the output gradient is quantized (backward of the FP4 GEMMs)
     use_preshuffle: bool = False    # AITER pre-shuffled layouts: not provided on B200
 
     def __post_init__(self):
-        if self.use_gradient_sr or self.use_preshuffle:
-            raise NotImplementedError("use_gradient_sr / use_preshuffle are not provided by the B200 back end")
+        if self.use_preshuffle:
+            raise NotImplementedError("use_preshuffle (AITER pre-shuffled layouts) is not provided by the B200 back end")
         if self.format != Format.E2M1_X2:
             raise ValueError("Float4QuantConfig: format must be E2M1_X2")
         if self.granularity != ScalingGranularity.MX_BLOCKWISE:

@@ -11,6 +11,7 @@ PT_BF16, PT_F16, PT_F32 = 0, 1, 2
 PT_E4M3, PT_E5M2, PT_E2M1 = 0, 1, 2
 PT_TENSORWISE, PT_ROWWISE, PT_BLOCKWISE, PT_MX_BLOCKWISE = 0, 1, 2, 3
 PT_MX_ROW, PT_MX_COL, PT_MX_ROW_2D, PT_MX_COL_2D, PT_MX_ROW_RHT, PT_MX_COL_RHT = 1, 2, 4, 8, 16, 32
+PT_MX_ROW_SR, PT_MX_COL_SR = 64, 128
 
 _SRC = {torch.bfloat16: PT_BF16, torch.float16: PT_F16, torch.float32: PT_F32}
 _FMT = {torch.float8_e4m3fn: PT_E4M3, torch.float8_e5m2: PT_E5M2, torch.float4_e2m1fn_x2: PT_E2M1}

@@ -231,11 +231,12 @@ def _mx_quant(x, out_dtype, want_row, want_col, row_recipe, col_recipe):
     for r in (row_recipe, col_recipe):
         if r is not None and (r.shuffle_scale or r.shuffle_out):
             raise NotImplementedError("pre-shuffled (AITER) MX layouts are not provided on B200")
-        if r is not None and r.use_sr:
-            raise NotImplementedError("stochastic rounding is not provided on B200")
     x = x.contiguous()
     fmt = nv.fmt_code(out_dtype)
     fp4 = fmt == nv.PT_E2M1
+    for r in (row_recipe, col_recipe):
+        if r is not None and r.use_sr and not fp4:
+            raise ValueError("stochastic rounding is an MXFP4 option (ScalingRecipe.use_sr)")
     G = 1 if x.dim() == 2 else x.shape[0]
     M, N = x.shape[-2:]
     M_pad, N_pad = ceil_div(M, MX_ALIGN) * MX_ALIGN, ceil_div(N, MX_ALIGN) * MX_ALIGN
@@ -245,10 +246,12 @@ def _mx_quant(x, out_dtype, want_row, want_col, row_recipe, col_recipe):
     q_row = s_row = q_col = s_col = None
     if want_row:
         flags |= nv.PT_MX_ROW | (nv.PT_MX_ROW_2D if row_recipe.use_2d_block else 0) | (nv.PT_MX_ROW_RHT if row_recipe.use_rht else 0)
+        flags |= nv.PT_MX_ROW_SR if row_recipe.use_sr else 0
         q_row = torch.empty(lead + (M, N_pad // div), dtype=torch.uint8, device=x.device)
         s_row = torch.empty(lead + (M, N_pad // MX_BLOCK), dtype=torch.uint8, device=x.device)
     if want_col:
         flags |= nv.PT_MX_COL | (nv.PT_MX_COL_2D if col_recipe.use_2d_block else 0) | (nv.PT_MX_COL_RHT if col_recipe.use_rht else 0)
+        flags |= nv.PT_MX_COL_SR if col_recipe.use_sr else 0
         q_col = torch.empty(lead + (N, M_pad // div), dtype=torch.uint8, device=x.device)
         s_col = torch.empty(lead + (N, M_pad // MX_BLOCK), dtype=torch.uint8, device=x.device)
     with nv.on_device(x.device):
@@ -372,14 +375,17 @@ MX_GROUP_COL_ALIGN = 128  # col-wise copy: each group padded to 128 rows
 def _grouped_mx_quant(x, out_dtype, group_lens, group_offs, want_row, want_col, row_recipe, col_recipe):
     nv.require_cuda(x, group_lens, group_offs)
     for r in (row_recipe, col_recipe):
-        if r is not None and (r.shuffle_scale or r.shuffle_out or r.use_sr):
-            raise NotImplementedError("pre-shuffled layouts and stochastic rounding are not provided on B200")
+        if r is not None and (r.shuffle_scale or r.shuffle_out):
+            raise NotImplementedError("pre-shuffled (AITER) MX layouts are not provided on B200")
         if r is not None and r.use_2d_block:
             raise NotImplementedError("2-D block scales are a weight option; grouped activations use 1-D blocks")
     assert x.dim() == 2, "Input must be 2D"
     x = x.contiguous()
     fmt = nv.fmt_code(out_dtype)
     fp4 = fmt == nv.PT_E2M1
+    for r in (row_recipe, col_recipe):
+        if r is not None and r.use_sr and not fp4:
+            raise ValueError("stochastic rounding is an MXFP4 option (ScalingRecipe.use_sr)")
     M, N = x.shape
     G = group_lens.numel()
     lens = group_lens.to(torch.int64).contiguous()
@@ -400,11 +406,11 @@ def _grouped_mx_quant(x, out_dtype, group_lens, group_offs, want_row, want_col, 
     flags = 0
     q_row = s_row = q_col = s_col = None
     if want_row:
-        flags |= nv.PT_MX_ROW | (nv.PT_MX_ROW_RHT if row_recipe.use_rht else 0)
+        flags |= nv.PT_MX_ROW | (nv.PT_MX_ROW_RHT if row_recipe.use_rht else 0) | (nv.PT_MX_ROW_SR if row_recipe.use_sr else 0)
         q_row = torch.empty((rows_alloc, N_pad // div), dtype=torch.uint8, device=x.device)
         s_row = torch.empty((rows_alloc, N_pad // MX_BLOCK), dtype=torch.uint8, device=x.device)
     if want_col:
-        flags |= nv.PT_MX_COL | (nv.PT_MX_COL_RHT if col_recipe.use_rht else 0)
+        flags |= nv.PT_MX_COL | (nv.PT_MX_COL_RHT if col_recipe.use_rht else 0) | (nv.PT_MX_COL_SR if col_recipe.use_sr else 0)
         q_col = torch.empty((N, col_alloc // div), dtype=torch.uint8, device=x.device)
         s_col = torch.empty((N, col_alloc // MX_BLOCK), dtype=torch.uint8, device=x.device)
     with nv.on_device(x.device):

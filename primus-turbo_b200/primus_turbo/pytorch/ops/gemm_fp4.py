@@ -62,8 +62,9 @@ class FP4GemmMXFunction(torch.autograd.Function):
         dt = FP4GemmMXFunction.get_fp4_dtype(ctx.config.format)
         grad_out = grad_out.reshape(grad_out.shape[0], -1).contiguous()
         g_row, g_row_s, g_col, g_col_s = quantize_fp4_with_trans(grad_out, dt, ctx.config.granularity,
-                                                                 block_size=ctx.config.block_size, scaling_recipe=ScalingRecipe(),
-                                                                 scaling_recipe_for_trans=ScalingRecipe(use_rht=True))
+                                                                 block_size=ctx.config.block_size,
+                                                                 scaling_recipe=ScalingRecipe(use_sr=ctx.config.use_gradient_sr),
+                                                                 scaling_recipe_for_trans=ScalingRecipe(use_rht=True, use_sr=ctx.config.use_gradient_sr))
         grad_a = gemm_fp4_impl(g_row, g_row_s, False, b_col, b_col_s, True, ctx.out_dtype, False)
         if ctx.fuse:
             gemm_fp4_accum_impl(g_col, g_col_s, False, a_col, a_col_s, True, ctx.main_grad, False)

@@ -62,7 +62,8 @@ class FP4GroupedGemmMXFunc(torch.autograd.Function):
         grad_out = grad_out.contiguous()
         g_row, g_row_s, g_col, g_col_s, _, offs_row, lens_col, offs_col = grouped_quantize_mxfp4_impl(
             grad_out, float4_e2m1fn_x2, None, MXFP4_BLOCK_SIZE, group_lens, group_offs, with_trans=True,
-            scaling_recipe=ScalingRecipe(), scaling_recipe_for_trans=ScalingRecipe(use_rht=True))
+            scaling_recipe=ScalingRecipe(use_sr=ctx.config.use_gradient_sr),
+            scaling_recipe_for_trans=ScalingRecipe(use_rht=True, use_sr=ctx.config.use_gradient_sr))
         N, K = ctx.nk
         grad_a = grouped_gemm_fp4_impl(g_row, b_col, g_row_s, b_col_s, group_lens, offs_row, out_dtype=ctx.out_dtype, num_cu=ctx.num_cu,
                                        group_offs_out=group_offs)[:ctx.total_m]

@@ -158,3 +158,108 @@ def test_grouped_gemm_fp4_prequantized_operands(m):
     for g, n in enumerate(lens):
         if n >= 64:
             assert snr(b_q.grad[g], b_ref.grad[g]) > 6
+
+
+# ------------------------------------------------------------------------------------------------ stochastic rounding
+E2M1_GRID = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], dtype=np.float32)
+
+
+def _sr_input():
+    """[512, 256] bf16: every 32-block along either axis holds a 6.0 (so its scale is 1.0 and the codes are the values
+    themselves) and values that lie between two e2m1 codes."""
+    vals = torch.tensor([0.75, 2.25, -3.5, 5.0, 1.25, -0.25, 0.5, 4.0], dtype=torch.float32)
+    x = vals.repeat(512, 32)
+    x[:, ::32] = 6.0
+    x[::32, :] = 6.0
+    return x.to(torch.bfloat16).cuda()
+
+
+@pytest.mark.parametrize("axis", [1, 0])
+def test_mxfp4_sr_two_calls_differ_and_stay_between_neighbouring_codes(m, axis):
+    """The reference's own SR test (tests/pytorch/ops/test_quantization.py:766-797): two calls on one input differ.
+    Added: every result is one of the two codes that bracket the value, exactly representable values never move, and
+    the scales are those of round-to-nearest (rounding mode does not touch the scale)."""
+    qi, SR = m["qi"], m["SR"]
+    x = _sr_input()
+    q1, s1 = qi.quantize_mxfp4_impl(x, F4, axis, 32, scaling_recipe=SR(use_sr=True))
+    q2, s2 = qi.quantize_mxfp4_impl(x, F4, axis, 32, scaling_recipe=SR(use_sr=True))
+    q0, s0 = qi.quantize_mxfp4_impl(x, F4, axis, 32)
+    assert not torch.equal(q1.view(torch.uint8), q2.view(torch.uint8))
+    assert torch.equal(s1.view(torch.uint8), s0.view(torch.uint8)) and torch.equal(s2.view(torch.uint8), s0.view(torch.uint8))
+    xf = f32(x) if axis == 1 else f32(x).T
+    for q in (q1, q2):
+        d = oq.dequantize_mx(u8(q), u8(s0), "e2m1")[:, : xf.shape[1]]
+        lo = np.sign(xf) * E2M1_GRID[np.searchsorted(E2M1_GRID, np.abs(xf), side="right") - 1]
+        hi = np.sign(xf) * E2M1_GRID[np.minimum(np.searchsorted(E2M1_GRID, np.abs(xf), side="left"), 7)]
+        assert np.all((d == lo) | (d == hi)), "a stochastically rounded value left the two codes around it"
+        exact = np.isin(np.abs(xf), E2M1_GRID)
+        assert np.array_equal(d[exact], xf[exact])
+
+
+def test_mxfp4_sr_is_unbiased(m):
+    """Mean of the dequantized values over 16 x 512 x 28 draws per value: within 4 standard errors of the value."""
+    qi, SR = m["qi"], m["SR"]
+    x = _sr_input()
+    xf = f32(x)
+    acc = np.zeros_like(xf, dtype=np.float64)
+    n = 16
+    for _ in range(n):
+        q, s = qi.quantize_mxfp4_impl(x, F4, 1, 32, scaling_recipe=SR(use_sr=True))
+        acc += oq.dequantize_mx(u8(q), u8(s), "e2m1")
+    mean = acc / n
+    for v in (0.75, 2.25, -3.5, 5.0, 1.25, -0.25):
+        sel = xf == np.float32(v)
+        lo = E2M1_GRID[np.searchsorted(E2M1_GRID, abs(v), side="right") - 1]
+        hi = E2M1_GRID[np.searchsorted(E2M1_GRID, abs(v), side="left")]
+        p = (abs(v) - lo) / (hi - lo)
+        sigma = (hi - lo) * np.sqrt(p * (1 - p) / (n * sel.sum()))
+        assert abs(mean[sel].mean() - v) <= 4 * sigma + 1e-6, (v, mean[sel].mean(), sigma)
+
+
+def test_mxfp4_sr_dual_and_grouped_and_rht(m):
+    """SR through the dual, the Hadamard and the grouped paths: outputs differ between calls, scales do not; the
+    round-trip error stays within one code spacing of the (transformed) values."""
+    qi, SR = m["qi"], m["SR"]
+    x = make((384, 256), torch.bfloat16, 71, "normal")
+    sr, sr_rht = SR(use_sr=True), SR(use_sr=True, use_rht=True)
+    a = qi.quantize_mxfp4_impl(x, F4, None, 32, with_trans=True, scaling_recipe=sr, scaling_recipe_for_trans=sr_rht)
+    b = qi.quantize_mxfp4_impl(x, F4, None, 32, with_trans=True, scaling_recipe=sr, scaling_recipe_for_trans=sr_rht)
+    ref = qi.quantize_mxfp4_impl(x, F4, None, 32, with_trans=True, scaling_recipe=SR(), scaling_recipe_for_trans=SR(use_rht=True))
+    for i in (0, 2):
+        assert not torch.equal(a[i].view(torch.uint8), b[i].view(torch.uint8))
+        assert torch.equal(a[i + 1].view(torch.uint8), ref[i + 1].view(torch.uint8))
+    d = oq.dequantize_mx(u8(a[0]), u8(a[1]), "e2m1")[:, :256]
+    assert og.snr_db(d, f32(x)) > 8
+    lens = torch.tensor([100, 0, 156, 128], dtype=torch.int64, device="cuda")
+    offs = torch.zeros(5, dtype=torch.int64, device="cuda")
+    offs[1:] = torch.cumsum(lens, 0)
+    g1 = qi.grouped_quantize_mxfp4_impl(x, F4, None, 32, lens, offs, with_trans=True, scaling_recipe=sr, scaling_recipe_for_trans=sr_rht)
+    g2 = qi.grouped_quantize_mxfp4_impl(x, F4, None, 32, lens, offs, with_trans=True, scaling_recipe=sr, scaling_recipe_for_trans=sr_rht)
+    assert not torch.equal(g1[0].view(torch.uint8), g2[0].view(torch.uint8))
+    assert torch.equal(g1[1].view(torch.uint8), g2[1].view(torch.uint8))
+
+
+def test_gemm_fp4_with_gradient_sr_passes_the_snr_gate(m):
+    turbo = m["turbo"]
+    from primus_turbo.pytorch.core.low_precision import Float4QuantConfig
+    torch.manual_seed(6)
+    cfg = Float4QuantConfig(use_gradient_sr=True)
+    a = torch.randn(512, 1024, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    b = torch.randn(768, 1024, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    a_ref, b_ref = a.detach().clone().requires_grad_(), b.detach().clone().requires_grad_()
+    g = torch.randn(512, 768, device="cuda", dtype=torch.bfloat16)
+    out = turbo.ops.gemm_fp4(a, b, trans_b=True, config=cfg)
+    out.backward(g)
+    (a_ref @ b_ref.t()).backward(g)
+    ga1 = a.grad.clone()
+    assert snr(a.grad, a_ref.grad) > 8 and snr(b.grad, b_ref.grad) > 8
+    a.grad = b.grad = None
+    turbo.ops.gemm_fp4(a, b, trans_b=True, config=cfg).backward(g)
+    assert not torch.equal(a.grad, ga1), "gradients under stochastic rounding should differ between runs"
+    # grouped
+    lens = torch.tensor([200, 0, 312], dtype=torch.int64, device="cuda")
+    w = torch.randn(3, 256, 1024, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    x = torch.randn(512, 1024, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = turbo.ops.grouped_gemm_fp4(x, w, lens, trans_b=True, config=cfg)
+    y.backward(torch.randn_like(y))
+    assert torch.isfinite(x.grad.float()).all() and torch.isfinite(w.grad.float()).all()
