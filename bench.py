@@ -202,6 +202,7 @@ def _sub_records(args, dev, peaks, world, rank):
     else:
         import bench_sharded as bs
         attempt("expert_sharded_c4", lambda: bs.expert_sharded_c4(dev, peaks, world, rank))
+        attempt("expert_sharded_c4_row_balanced", lambda: bs.expert_sharded_c4(dev, peaks, world, rank, balance="rows"))
         attempt("n_sharded_c3", lambda: bs.n_sharded_c3(dev, peaks, world, rank))
     return sub
 

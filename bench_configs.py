@@ -284,16 +284,17 @@ def mx_c3(dev, peaks, n_lo=0, n_hi=None):
 
 
 # ---------------------------------------------------------------------------------------------- C4 (blockwise MoE)
-def grouped_blockwise_c4(dev, peaks, g_lo=0, g_hi=None, projections=("gate_up", "down"), iters=8):
+def grouped_blockwise_c4(dev, peaks, g_lo=0, g_hi=None, projections=("gate_up", "down"), iters=8, lens=None):
     """Blockwise-FP8 grouped forward / dgrad / wgrad over experts [g_lo, g_hi) of the 256 (all by default; one rank's
-    experts in the expert-sharded run) with the rows routed to them."""
+    experts in the expert-sharded run) with the rows routed to them (`lens`: this rank's share of each of them, when
+    popular experts are split between ranks)."""
     from primus_turbo.pytorch.core.low_precision import ScalingGranularity as SG
     from primus_turbo.pytorch.kernels.grouped_gemm import grouped_gemm_fp8_impl as ggi
     from primus_turbo.pytorch.kernels.quantization import quantization_impl as qi
     f8, f5 = torch.float8_e4m3fn, torch.float8_e5m2
     lens_all = zipf_group_lens(C4["G"], C4["rows"], seed=C4["seed"])
     g_hi = C4["G"] if g_hi is None else g_hi
-    lens = lens_all[g_lo:g_hi]
+    lens = lens_all[g_lo:g_hi] if lens is None else np.asarray(lens, dtype=np.int64)
     rows, G = int(lens.sum()), int(g_hi - g_lo)
     lens_t, offs = offsets_of(lens, dev)
     out = {"experts": [int(g_lo), int(g_hi)], "rows": rows, "empty_groups": int((lens == 0).sum()), "max_group": int(lens.max())}

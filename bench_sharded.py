@@ -23,40 +23,54 @@ def _max_over_ranks(values, dev):
     return [float(v) for v in t.tolist()]
 
 
+def _gather_ints(value, world, dev):
+    t = torch.zeros(world, dtype=torch.int64, device=dev)
+    t[dist.get_rank()] = int(value)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return [int(v) for v in t.tolist()]
+
+
 def _sum_over_ranks(values, dev):
     t = torch.tensor(values, dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.SUM)
     return [float(v) for v in t.tolist()]
 
 
-def expert_sharded_c4(dev, peaks, world, rank, projection="gate_up"):
+def expert_sharded_c4(dev, peaks, world, rank, projection="gate_up", balance="experts"):
+    """balance="experts": 256 / N consecutive experts per rank (the Zipf skew then decides the slowest rank);
+    balance="rows": the packed rows split evenly, popular experts shared between neighbouring ranks."""
+    import numpy as np
     from primus_turbo.pytorch.core.low_precision import Float8QuantConfig, Format, ScalingGranularity
-    from primus_turbo.pytorch.dist.partitioner import ExpertShardedGroupedLinear, expert_shard
+    from primus_turbo.pytorch.dist.partitioner import ExpertShardedGroupedLinear, expert_shard, row_balanced_expert_shard
     cfg = Float8QuantConfig(format=Format.E4M3, granularity=ScalingGranularity.BLOCKWISE, block_size=128)
     lens_all = bc.zipf_group_lens(bc.C4["G"], bc.C4["rows"], seed=bc.C4["seed"])
-    g_lo, g_hi = expert_shard(bc.C4["G"], world, rank)
+    if balance == "rows":
+        g_lo, g_hi, lens = row_balanced_expert_shard([int(v) for v in lens_all], world, rank)
+        lens = np.asarray(lens, dtype=np.int64)
+    else:
+        g_lo, g_hi = expert_shard(bc.C4["G"], world, rank)
+        lens = lens_all[g_lo:g_hi]
     N, K = (bc.C4["inter2"], bc.C4["hidden"]) if projection == "gate_up" else (bc.C4["hidden"], bc.C4["inter"])
-    lens = lens_all[g_lo:g_hi]
     rows = int(lens.sum())
     lens_t, _ = bc.offsets_of(lens, dev)
     w = bc.randn_bf16((g_hi - g_lo, N, K), 0.02, 83 + g_lo, dev)
     x = bc.randn_bf16((max(rows, 1), K), 1.0, 81 + g_lo, dev)[:rows]
-    ex = ExpertShardedGroupedLinear(bc.C4["G"], w, config=cfg, cache_quantized_weight=True)
-    lens_list = [int(v) for v in lens_all]
+    ex = ExpertShardedGroupedLinear(bc.C4["G"], w, config=cfg, cache_quantized_weight=True, experts=(g_lo, g_hi))
+    rows_all = _gather_ints(rows, world, dev)
     with torch.no_grad():
         fwd_ms = bc.time_cuda(lambda: ex.forward(x, lens_t), iters=8)
         dist.barrier()
-        gat_ms = bc.time_cuda(lambda: ex.gather(ex.forward(x, lens_t), lens_list), iters=6)
+        gat_ms = bc.time_cuda(lambda: ex.gather_rows(ex.forward(x, lens_t), rows_all), iters=6)
     del ex, w, x
     torch.cuda.empty_cache()
     # kernel-only forward / dgrad / wgrad of this rank's experts (same layouts, quantized operands prepared outside)
-    k = bc.grouped_blockwise_c4(dev, peaks, g_lo, g_hi, projections=(projection,), iters=6)[projection]
+    k = bc.grouped_blockwise_c4(dev, peaks, g_lo, g_hi, projections=(projection,), iters=6, lens=lens)[projection]
     ms = _max_over_ranks([fwd_ms, gat_ms, k["fwd"]["ms"], k["dgrad"]["ms"], k["wgrad"]["ms"]], dev)
     rows_max = _max_over_ranks([float(rows)], dev)[0]
     flops = 2.0 * bc.C4["rows"] * N * K
     tf = lambda m: flops / (m / 1e3) / 1e12
     recv_bytes = (bc.C4["rows"] - rows) * N * 2
-    return {"scaling": "strong", "projection": projection, "experts_per_rank": g_hi - g_lo, "rows_rank0": rows,
+    return {"scaling": "strong", "projection": projection, "balance": balance, "experts_on_rank0": g_hi - g_lo, "rows_rank0": rows,
             "load_imbalance_max_over_mean": rows_max / (bc.C4["rows"] / world),
             "operator_fwd": {"ms_max_rank": ms[0], "tflops_total": tf(ms[0]),
                              "what": "segment-M quantize of the local rows + grouped GEMM on cached quantized experts"},

@@ -308,6 +308,38 @@ int pt_grouped_gemm_fp8_blockwise(const void *a, int a_fmt, int a_mn, int64_t a_
                                   int64_t K, const int64_t *group_offs_read, const int64_t *group_offs_write,
                                   const int64_t *k_offs, int G, float beta, int max_ctas, int *status, void *stream);
 
+/* ------------------------------------------------------------------ MoE token permutation (mask-map form) */
+
+/* Scratch bytes of pt_moe_make_row_id_map. */
+size_t pt_moe_row_id_map_workspace_bytes(int64_t T, int E);
+
+/* routing_map [T, E] (bool / int32 / int64 elements, map_elem_bytes = 1 / 4 / 8; non-zero = token t goes to expert e) ->
+ * row_id_map int32 [T, 2E + 1]: per token the destination rows of its routed experts in ascending expert order (rows of
+ * expert 0 first, tokens in order inside an expert), at column E the expert ids in the same order, in the last column
+ * their number; unused slots hold -1.  tokens_per_expert int64 [E].
+ * Replaces make_row_id_map (primus_turbo/triton/moe/permutation.py:143-230 of the reference). */
+int pt_moe_make_row_id_map(const void *routing_map, int map_elem_bytes, int64_t T, int E, int *row_id_map, int64_t *tokens_per_expert,
+                           void *workspace, size_t workspace_bytes, void *stream);
+
+/* out[dst] = tokens[t] for every destination row of token t (rows of row_bytes bytes, a multiple of 16); with probs
+ * [T, E] (elements of probs_elem_bytes bytes) also out_probs[dst] = probs[t, e].  Destinations at or past num_out_tokens
+ * are dropped.  Replaces permute_with_mask_map (primus_turbo/triton/moe/permutation.py of the reference). */
+int pt_moe_permute(const void *tokens, int64_t T, int64_t row_bytes, int E, const int *row_id_map, const void *probs, int probs_elem_bytes,
+                   int64_t num_out_tokens, void *out, void *out_probs, void *stream);
+
+/* out[t] = sum over the routed experts of (merging_probs[t, e] *) permuted[dst], accumulated in fp32 in expert order
+ * (merging_probs optional).  With permuted_probs also unpermuted_probs[t, e] = permuted_probs[dst], zero where token t
+ * does not go to expert e; `out` may then be null.  dtype / probs_dtype: pt_dtype codes.
+ * Replaces unpermute_with_mask_map (primus_turbo/triton/moe/permutation.py of the reference). */
+int pt_moe_unpermute(const void *permuted, int dtype, int64_t T, int64_t H, int E, const int *row_id_map, const void *merging_probs,
+                     const void *permuted_probs, int probs_dtype, void *out, void *unpermuted_probs, void *stream);
+
+/* Backward of the weighted unpermute: act_grad[dst] = grad_out[t] * merging_probs[t, e];
+ * probs_grad[t, e] = <grad_out[t], fwd_in[dst]> (fp32 dot product), zero where token t does not go to expert e.
+ * Replaces unpermute_with_mask_map_bwd_with_merging_probs of the reference. */
+int pt_moe_unpermute_bwd_with_probs(const void *grad_out, const void *fwd_in, int dtype, int64_t T, int64_t H, int E, const int *row_id_map,
+                                    const void *merging_probs, int probs_dtype, void *act_grad, void *probs_grad, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -41,6 +41,12 @@ SIGNATURES = {
     "pt_grouped_quantize_mx": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int, c_uint,
                                        c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "pt_dequantize_mx": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_int, c_void_p]),
+    "pt_moe_row_id_map_workspace_bytes": (c_size_t, [c_int64, c_int]),
+    "pt_moe_make_row_id_map": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "pt_moe_permute": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
+    "pt_moe_unpermute": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "pt_moe_unpermute_bwd_with_probs": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p,
+                                                c_void_p, c_void_p]),
     "pt_transpose_2d": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "pt_transpose_batched": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "pt_grouped_transpose_pad": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p]),

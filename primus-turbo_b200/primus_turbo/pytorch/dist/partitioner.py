@@ -32,6 +32,54 @@ def expert_shard(num_experts: int, world: int, rank: int) -> Tuple[int, int]:
     return lo, lo + base + (1 if rank < extra else 0)
 
 
+def row_balanced_expert_shard(group_lens: List[int], world: int, rank: int, align: int = 128):
+    """Shard of `rank` when the packed token rows, not the experts, are split evenly: the rows [R * rank / world,
+    R * (rank + 1) / world) of the expert-major layout (cut points rounded to `align` rows inside an expert).  A popular
+    expert then straddles two or more ranks, each of which holds a copy of its weights and a slice of its rows, so one hot
+    expert (Zipf routing: a fifth of all rows on one of 256 experts) no longer decides the step time.
+
+    Returns (g_lo, g_hi, local_group_lens): the experts [g_lo, g_hi) this rank touches and how many rows of each."""
+    offs = [0]
+    for n in group_lens:
+        offs.append(offs[-1] + int(n))
+    total = offs[-1]
+
+    def cut(r):
+        if r <= 0:
+            return 0
+        if r >= world:
+            return total
+        c = total * r // world
+        g = max(0, min(len(group_lens) - 1, _last_leq(offs, c)))
+        inside = c - offs[g]
+        return min(offs[g] + (inside + align // 2) // align * align, offs[g + 1])
+
+    lo, hi = cut(rank), cut(rank + 1)
+    if hi <= lo:
+        return 0, 0, []
+    g_lo = _last_leq(offs, lo)
+    while g_lo < len(group_lens) and offs[g_lo + 1] <= lo:
+        g_lo += 1
+    g_hi = g_lo
+    lens = []
+    while g_hi < len(group_lens) and offs[g_hi] < hi:
+        lens.append(min(offs[g_hi + 1], hi) - max(offs[g_hi], lo))
+        g_hi += 1
+    return g_lo, g_hi, lens
+
+
+def _last_leq(offs: List[int], v: int) -> int:
+    """Largest g with offs[g] <= v (offs ascending, offs[0] = 0)."""
+    lo, hi = 0, len(offs) - 2
+    while lo < hi:
+        mid = (lo + hi + 1) // 2
+        if offs[mid] <= v:
+            lo = mid
+        else:
+            hi = mid - 1
+    return lo
+
+
 def _world(group) -> Tuple[int, int]:
     if not dist.is_available() or not dist.is_initialized():
         return 1, 0
@@ -162,11 +210,13 @@ class ExpertShardedGroupedLinear:
     """
 
     def __init__(self, num_experts: int, weight_shard: torch.Tensor, group=None, op: Optional[Callable] = None, config=None,
-                 cache_quantized_weight: bool = False):
+                 cache_quantized_weight: bool = False, experts: Optional[Tuple[int, int]] = None):
+        """`experts` = (g_lo, g_hi) overrides the even split by expert count, e.g. with the range
+        row_balanced_expert_shard() gives (then several ranks may hold the same popular expert and split its rows)."""
         self.group = group
         self.world, self.rank = _world(group)
         self.num_experts = num_experts
-        self.g_lo, self.g_hi = expert_shard(num_experts, self.world, self.rank)
+        self.g_lo, self.g_hi = expert_shard(num_experts, self.world, self.rank) if experts is None else experts
         assert weight_shard.shape[0] == self.g_hi - self.g_lo, "weight shard does not match this rank's experts"
         self.weight = weight_shard
         self.config = config
@@ -198,8 +248,20 @@ class ExpertShardedGroupedLinear:
                                  need_transpose=False)
         return grouped_gemm_fp8(x_local, w, group_lens_local, trans_b=True, config=self.config)
 
+    def gather_rows(self, y_local: torch.Tensor, rows: List[int]) -> torch.Tensor:
+        """Concatenates every rank's rows in rank order on every rank; rows[r] = row count of rank r (padded all_gather)."""
+        if self.world == 1:
+            return y_local
+        rmax = max(max(rows), 1)
+        send = y_local.new_zeros((rmax, y_local.shape[1]))
+        send[: y_local.shape[0]] = y_local
+        recv = y_local.new_empty((self.world * rmax, y_local.shape[1]))
+        dist.all_gather_into_tensor(recv, send, group=self.group)
+        return torch.cat([recv[r * rmax: r * rmax + n] for r, n in enumerate(rows)], dim=0)
+
     def gather(self, y_local: torch.Tensor, group_lens_all: List[int]) -> torch.Tensor:
-        """Concatenates every rank's rows in expert order on every rank (padded all_gather)."""
+        """Concatenates every rank's rows in expert order on every rank (padded all_gather); for the even split by
+        expert count."""
         if self.world == 1:
             return y_local
         rows = []

@@ -8,7 +8,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from primus_turbo.pytorch.dist.partitioner import (ColumnShardedLinear, ExpertShardedGroupedLinear, column_shard,
-                                                    expert_shard)
+                                                    expert_shard, row_balanced_expert_shard)
 
 
 def test_column_shard_bounds():
@@ -26,6 +26,29 @@ def test_expert_shard_bounds():
     assert [expert_shard(256, 8, r) for r in range(8)] == [(32 * r, 32 * r + 32) for r in range(8)]
     spans = [expert_shard(10, 4, r) for r in range(4)]
     assert spans == [(0, 3), (3, 6), (6, 8), (8, 10)]
+
+
+def test_row_balanced_expert_shard_covers_every_row_once():
+    import numpy as np
+    rng = np.random.default_rng(0)
+    for lens in ([27140, 0, 3, 500, 128, 0, 9000, 1], [5] * 7, [0, 0, 4096], list(rng.integers(0, 3000, size=64))):
+        lens = [int(v) for v in lens]
+        for world in (1, 2, 3, 4, 8):
+            cover = [0] * len(lens)
+            rows = []
+            prev_hi = 0
+            for r in range(world):
+                g_lo, g_hi, local = row_balanced_expert_shard(lens, world, r)
+                assert len(local) == g_hi - g_lo and all(n > 0 for n in local)
+                if local:
+                    assert g_lo >= max(prev_hi - 1, 0)      # ranks walk the experts in order; neighbours may share one
+                    prev_hi = g_hi
+                for i, n in enumerate(local):
+                    cover[g_lo + i] += n
+                rows.append(sum(local))
+            assert cover == lens
+            if sum(lens) >= 128 * world * 8:
+                assert max(rows) <= sum(lens) / world + 128  # balanced to within one alignment unit
 
 
 def _grouped_ref(x, w, lens):

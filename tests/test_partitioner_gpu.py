@@ -41,6 +41,22 @@ def _worker(rank, world, port, root):
             y_all = ex.gather(y_loc, lens)
             full = turbo.ops.grouped_gemm_fp8(xe, we, torch.tensor(lens, dtype=torch.int64, device="cuda"), trans_b=True, config=bcfg)
         assert torch.equal(y_all, full), "expert-sharded grouped GEMM differs from the unsharded one"
+        # FP8 all-to-all: unequal splits, forward + backward; the wire format costs at most the e4m3 / e5m2 rounding
+        from primus_turbo.pytorch.dist import FP8AllToAll
+        tcfg = Float8QuantConfig(format=Format.HYBRID, granularity=ScalingGranularity.TENSORWISE)
+        in_splits = [3, 5] if rank == 0 else [4, 2]
+        out_splits = [3, 4] if rank == 0 else [5, 2]
+        gen = torch.Generator().manual_seed(10 + rank)
+        t = torch.randn(sum(in_splits), 256, generator=gen).to(torch.bfloat16).cuda().requires_grad_()
+        got = FP8AllToAll.apply(dist.group.WORLD, t, out_splits, in_splits, True, True, tcfg)
+        want = torch.empty((sum(out_splits), 256), dtype=torch.bfloat16, device="cuda")
+        dist.all_to_all_single(want, t.detach(), output_split_sizes=out_splits, input_split_sizes=in_splits)
+        assert got.shape == want.shape
+        assert float((got.float() - want.float()).norm() / want.float().norm()) < 0.05
+        got.backward(torch.ones_like(got))
+        assert t.grad.shape == t.shape and torch.allclose(t.grad.float(), torch.ones_like(t.grad).float(), atol=0.07)
+        plain = FP8AllToAll.apply(dist.group.WORLD, t.detach(), out_splits, in_splits, False, False, tcfg)
+        assert torch.equal(plain, want)
         torch.cuda.synchronize()
         dist.barrier()
     finally:
