@@ -182,17 +182,17 @@ def quantize_records(dev, peaks, copies=4):
     run("mxfp8_row_act_8192x4096", [lambda x=x: qi.quantize_mxfp8_impl(x, f8, 1, 32) for x in acts], 3 * e + e // 32,
         "mx_quant_tma_kernel<row>")
     run("mxfp8_dual_act_8192x4096", [lambda x=x: qi.quantize_mxfp8_impl(x, f8, None, 32, True) for x in acts],
-        2 * e + 2 * (e + e // 32), "mx_quant_tma_kernel<row+col>")
+        2 * e + 2 * (e + e // 32), "mx_quant_split_kernel<e4m3>")
     run("mxfp8_dual_2d_weight_14336x4096", [lambda w=w: qi.quantize_mxfp8_impl(w, f8, None, 32, True, two_d, two_d) for w in wts],
-        2 * ew + 2 * (ew + ew // 32), "mx_quant_tma_kernel<row+col, 2-D>")
+        2 * ew + 2 * (ew + ew // 32), "mx_quant_split_kernel<e4m3, 2-D>")
     run("mxfp4_dual_act_8192x4096", [lambda x=x: qi.quantize_mxfp4_impl(x, f4, None, 32, True) for x in acts],
-        2 * e + 2 * (e // 2 + e // 32), "mx_quant_tma_kernel<e2m1, row+col>")
+        2 * e + 2 * (e // 2 + e // 32), "mx_quant_split_kernel<e2m1>")
     del wts
     # C3: dual MX quantization of the 16384 x 8192 activation (the transposed copy feeds the wgrad)
     a3 = [randn_bf16((C3["M"], C3["K"]), 1.0, 30 + i, dev) for i in range(2)]
     e3 = C3["M"] * C3["K"]
     run("mxfp8_dual_act_16384x8192", [lambda x=x: qi.quantize_mxfp8_impl(x, f8, None, 32, True) for x in a3],
-        2 * e3 + 2 * (e3 + e3 // 32), "mx_quant_tma_kernel<row+col>")
+        2 * e3 + 2 * (e3 + e3 // 32), "mx_quant_split_kernel<e4m3>")
     del a3
     # C4: segment-M row + column quantization of 32768 of the routed rows (hidden 7168), Zipf lengths of 64 experts
     lens = zipf_group_lens(64, 32768, seed=C4["seed"])
@@ -215,7 +215,27 @@ def quantize_records(dev, peaks, copies=4):
         2 * e5 + (e5 // 2 + e5 // 32) + (e5_pad // 2 + e5_pad // 32), "mx_quant_tma_kernel<e2m1, row+col, RHT, grouped>")
     run("grouped_mxfp8_dual_65536x4096_g8",
         [lambda x=x: qi.grouped_quantize_mxfp8_impl(x, f8, None, 32, lens5_t, offs5, with_trans=True) for x in x5],
-        2 * e5 + 2 * (e5 + e5 // 32), "mx_quant_tma_kernel<row+col, grouped>")
+        2 * e5 + 2 * (e5 + e5 // 32), "mx_quant_split_kernel<e4m3, grouped>")
+    del x5
+    # The step between the two grouped GEMMs of an expert MLP (C4: intermediate 2048, 32768 of the routed rows): SwiGLU with
+    # probabilities and the dual MX quantization of its result, as one kernel and as two.  Algorithmic bytes of the one-pass
+    # form: the [rows, 2 I] input + both copies with scales; the two-kernel form also writes and re-reads [rows, I] bf16.
+    rows, inter = 32768, C4["inter"]
+    xg = [randn_bf16((rows, 2 * inter), 1.0, 60 + i, dev) for i in range(3)]
+    probs = torch.rand(rows, device=dev, generator=torch.Generator(device=dev).manual_seed(61))
+    eo = rows * inter
+    for nm, od, ob in (("mxfp8", f8, 2 * (eo + eo // 32)), ("mxfp4", f4, 2 * (eo // 2 + eo // 32))):
+        run(f"swiglu_{nm}_dual_one_pass_{rows}x{inter}", [lambda x=x: qi.glu_quantize_mx_impl(x, probs, None, "silu", od, fused=True) for x in xg],
+            4 * eo + 4 * rows + ob, "mx_quant_split_kernel<SwiGLU prologue>")
+        run(f"swiglu_{nm}_dual_two_kernels_{rows}x{inter}", [lambda x=x: qi.glu_quantize_mx_impl(x, probs, None, "silu", od, fused=False) for x in xg],
+            4 * eo + 4 * rows + ob, "glu_fwd_kernel + mx_quant_split_kernel (same algorithmic bytes counted; moves 4 more bytes per element)")
+    del xg
+    # RMSNorm feeding an MX GEMM (C2's activation): statistics pass + normalising quantizer against rmsnorm + quantizer
+    gam = randn_bf16((K,), 1.0, 62, dev)
+    for fused, nm in ((True, "one_pass"), (False, "two_kernels")):
+        run(f"rmsnorm_mxfp8_dual_{nm}_8192x4096", [lambda x=x: qi.rmsnorm_quantize_mx_impl(x, gam, 1e-6, False, f8, fused=fused) for x in acts],
+            2 * e + 2 * (e + e // 32) + 4 * M, "rmsnorm_fwd_kernel<statistics> + mx_quant_split_kernel<RMSNorm prologue>" if fused
+            else "rmsnorm_fwd_kernel + mx_quant_split_kernel")
     return out
 
 

@@ -340,6 +340,58 @@ int pt_moe_unpermute(const void *permuted, int dtype, int64_t T, int64_t H, int 
 int pt_moe_unpermute_bwd_with_probs(const void *grad_out, const void *fwd_in, int dtype, int64_t T, int64_t H, int E, const int *row_id_map,
                                     const void *merging_probs, int probs_dtype, void *act_grad, void *probs_grad, void *stream);
 
+/* ---- gated activations and RMSNorm: the element-wise steps either side of the low-precision GEMMs -------------------- */
+
+/* out[r, :H] = act(x[r, :H]) * x[r, H:2H] * probs[r], computed in fp32 and rounded to dtype; act: 0 = SiLU (SwiGLU),
+ * 1 = GELU in its erf form (GeGLU).  row_mask (int64 [rows], optional): rows with a zero entry are not computed and
+ * come out as zeros.  Rows of x and out must be 16-byte multiples.
+ * Replaces swiglu_fwd_with_probs / geglu_fwd_with_probs (primus_turbo/pytorch/kernels/activation/{swiglu,geglu}_impl.py,
+ * kernels in primus_turbo/triton/activation/{swiglu,geglu}_kernel.py of the reference). */
+int pt_glu_fwd(const void *x, int dtype, const float *probs, const int64_t *row_mask, int64_t rows, int64_t H, int act, void *out, void *stream);
+
+/* grad_x[r, :H] = g * p * b * act'(a), grad_x[r, H:] = g * p * act(a), grad_probs[r] = sum_h g * act(a) * b (fp32).
+ * The GELU branch uses the derivative of the forward's erf form; the reference's GeGLU backward kernel multiplies the
+ * incoming gradient in twice (geglu_kernel.py, backward), which only agrees with autograd for a gradient of ones.
+ * Replaces swiglu_bwd_with_probs / geglu_bwd_with_probs of the reference. */
+int pt_glu_bwd(const void *grad_out, const void *x, int dtype, const float *probs, const int64_t *row_mask, int64_t rows, int64_t H, int act,
+               void *grad_x, float *grad_probs, void *stream);
+
+/* y[r] = (x[r] (+ residual[r])) * rstd[r] * g, rstd[r] = rsqrt(mean(x^2) + eps) in fp32, g = gamma or 1 + gamma
+ * (zero_centered).  With a residual the sum is rounded to dtype, written to x_plus_r and normalised from that rounded
+ * value.  y may be null: only rstd (and x_plus_r) are produced.
+ * Replaces rmsnorm_fwd_impl / rmsnorm_fwd_residual_impl (primus_turbo/pytorch/kernels/normalization/rmsnorm_impl.py,
+ * kernels in primus_turbo/triton/normalization/rmsnorm_kernel.py of the reference). */
+int pt_rmsnorm_fwd(const void *x, const void *residual, const void *gamma, int dtype, float eps, int zero_centered, int64_t rows, int64_t H, void *y,
+                   void *x_plus_r, float *rstd, void *stream);
+
+/* Number of partial dgamma rows pt_rmsnorm_bwd needs for this row count (dg_partial is fp32 [parts, H]). */
+int pt_rmsnorm_bwd_parts(int64_t rows);
+
+/* dx = (dy * g - x_hat * mean(dy * g * x_hat)) * rstd (+ dxpr), x_hat = x * rstd; dgamma[h] = sum_r dy * x_hat,
+ * accumulated in fp32 through dg_partial and rounded to dtype.  dxpr (optional) is the gradient that reached x_plus_r.
+ * Replaces rmsnorm_bwd_impl / rmsnorm_bwd_residual_impl of the reference. */
+int pt_rmsnorm_bwd(const void *dy, const void *dxpr, const void *x, const void *gamma, const float *rstd, int dtype, int zero_centered, int64_t rows,
+                   int64_t H, void *dx, void *dgamma, float *dg_partial, int parts, void *stream);
+
+/* MX quantization of a gated activation in one pass: what pt_glu_fwd followed by pt_quantize_mx (flags PT_MX_ROW |
+ * PT_MX_COL) writes, byte for byte, without the [rows, H] intermediate in memory.  x bf16 [rows, 2H]; H a multiple of 64;
+ * fmt PT_E4M3 or PT_E2M1; outputs laid out as pt_quantize_mx's.  PT_ERR_UNSUPPORTED outside that range (the caller then
+ * runs the two kernels).  Covers the SwiGLU -> quantize step between the two grouped GEMMs of an expert MLP
+ * (primus_turbo/pytorch/ops/activation.py:72-80 followed by quantize_fp8 in ops/grouped_gemm_fp8.py of the reference). */
+int pt_glu_quantize_mx(const void *x, int x_dtype, const float *probs, const int64_t *row_mask, int64_t rows, int64_t H, int act, int fmt,
+                       unsigned flags, void *q_row, uint8_t *s_row, void *q_col, uint8_t *s_col, void *stream);
+
+/* The same with the rows split into G groups: what pt_glu_fwd followed by pt_grouped_quantize_mx writes. */
+int pt_grouped_glu_quantize_mx(const void *x, int x_dtype, const float *probs, const int64_t *row_mask, int64_t rows, int64_t H, int act, int G,
+                               const int64_t *group_offs, const int64_t *padded_offs_row, const int64_t *padded_offs_col, int fmt, unsigned flags,
+                               void *q_row, uint8_t *s_row, void *q_col, uint8_t *s_col, int64_t col_alloc, void *stream);
+
+/* MX quantization of RMSNorm(x) given the row statistics (pt_rmsnorm_fwd with y = null): what pt_rmsnorm_fwd followed by
+ * pt_quantize_mx writes, byte for byte.  x, gamma bf16; H a multiple of 32.
+ * (primus_turbo/pytorch/ops/normalization.py rmsnorm followed by quantize_fp8 of the reference.) */
+int pt_rmsnorm_quantize_mx(const void *x, int x_dtype, const float *rstd, const void *gamma, int zero_centered, int64_t rows, int64_t H, int fmt,
+                           unsigned flags, void *q_row, uint8_t *s_row, void *q_col, uint8_t *s_col, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

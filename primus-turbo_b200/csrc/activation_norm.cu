@@ -1,0 +1,372 @@
+// Gated activations with routing probabilities (SwiGLU / GeGLU, forward and backward) and RMSNorm (forward with optional
+// residual add, row statistics alone, backward): the element-wise steps on either side of the low-precision GEMMs.
+//
+// HBM-bound streaming kernels: persistent CTAs walk the rows (grid = min(rows, CTAs that fit)), 16-byte loads and stores,
+// fp32 arithmetic (act_math.cuh), one block reduction per row where the operator needs one (the probability gradient,
+// the mean square).  The reference's forms: primus_turbo/pytorch/ops/activation.py:23-80 with
+// triton/activation/{swiglu,geglu}_kernel.py, and ops/normalization.py with triton/normalization/rmsnorm_kernel.py.
+#include <algorithm>
+
+#include "act_math.cuh"
+#include "common.cuh"
+
+namespace ptb {
+
+constexpr int kAnThreads = 256;
+
+template <typename T> __device__ __forceinline__ float an_to_f(T v);
+template <> __device__ __forceinline__ float an_to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float an_to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float an_to_f<__half>(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T an_from_f(float v);
+template <> __device__ __forceinline__ float an_from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 an_from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half an_from_f<__half>(float v) { return __float2half_rn(v); }
+
+__device__ __forceinline__ float block_sum(float v, float *s_red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();   // s_red may still be read from the previous use
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAnThreads / 32; ++w) t += s_red[w];
+    return t;
+}
+
+// ---------------------------------------------------------------------------------------------- gated activation
+// x [rows, 2H]: a = x[:, :H], b = x[:, H:]; out [rows, H] = act(a) * b * probs[row]; rows whose mask entry is 0 come out as zeros.
+template <typename T, int ACT>
+__global__ void __launch_bounds__(kAnThreads) glu_fwd_kernel(const T *__restrict__ x, const float *__restrict__ probs,
+                                                             const int64_t *__restrict__ row_mask, int64_t rows, int64_t H,
+                                                             T *__restrict__ out) {
+    constexpr int V = 16 / sizeof(T);
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        if (row_mask != nullptr && row_mask[r] == 0) {   // the reference leaves these rows unwritten; zeros keep the result deterministic
+            for (int64_t h = (int64_t) threadIdx.x * V; h < H; h += (int64_t) kAnThreads * V) *reinterpret_cast<uint4 *>(out + r * H + h) = make_uint4(0, 0, 0, 0);
+            continue;
+        }
+        const float p = probs[r];
+        const T *a = x + r * 2 * H, *b = a + H;
+        for (int64_t h = (int64_t) threadIdx.x * V; h < H; h += (int64_t) kAnThreads * V) {
+            const uint4 ar = __ldg(reinterpret_cast<const uint4 *>(a + h)), br = __ldg(reinterpret_cast<const uint4 *>(b + h));
+            const T *av = reinterpret_cast<const T *>(&ar), *bv = reinterpret_cast<const T *>(&br);
+            uint4 o;
+            T *ov = reinterpret_cast<T *>(&o);
+#pragma unroll
+            for (int i = 0; i < V; ++i) ov[i] = an_from_f<T>(glu_value<ACT>(an_to_f<T>(av[i]), an_to_f<T>(bv[i]), p));
+            *reinterpret_cast<uint4 *>(out + r * H + h) = o;
+        }
+    }
+}
+
+// grad_x[:, :H] = g * p * b * act'(a); grad_x[:, H:] = g * p * act(a); grad_probs[row] = sum_h g * act(a) * b
+template <typename T, int ACT>
+__global__ void __launch_bounds__(kAnThreads) glu_bwd_kernel(const T *__restrict__ grad_out, const T *__restrict__ x,
+                                                             const float *__restrict__ probs, const int64_t *__restrict__ row_mask,
+                                                             int64_t rows, int64_t H, T *__restrict__ grad_x, float *__restrict__ grad_probs) {
+    constexpr int V = 16 / sizeof(T);
+    __shared__ float s_red[kAnThreads / 32];
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        if (row_mask != nullptr && row_mask[r] == 0) {
+            for (int64_t h = (int64_t) threadIdx.x * V; h < 2 * H; h += (int64_t) kAnThreads * V)
+                *reinterpret_cast<uint4 *>(grad_x + r * 2 * H + h) = make_uint4(0, 0, 0, 0);
+            if (threadIdx.x == 0) grad_probs[r] = 0.f;
+            continue;
+        }
+        const float p = probs[r];
+        const T *a = x + r * 2 * H, *b = a + H, *g = grad_out + r * H;
+        float dot = 0.f;
+        for (int64_t h = (int64_t) threadIdx.x * V; h < H; h += (int64_t) kAnThreads * V) {
+            const uint4 ar = __ldg(reinterpret_cast<const uint4 *>(a + h)), br = __ldg(reinterpret_cast<const uint4 *>(b + h));
+            const uint4 gr = __ldg(reinterpret_cast<const uint4 *>(g + h));
+            const T *av = reinterpret_cast<const T *>(&ar), *bv = reinterpret_cast<const T *>(&br), *gv = reinterpret_cast<const T *>(&gr);
+            uint4 oa, ob;
+            T *oav = reinterpret_cast<T *>(&oa), *obv = reinterpret_cast<T *>(&ob);
+#pragma unroll
+            for (int i = 0; i < V; ++i) {
+                const float af = an_to_f<T>(av[i]), bf = an_to_f<T>(bv[i]), gf = an_to_f<T>(gv[i]);
+                const float act = act_value<ACT>(af);
+                dot += gf * act * bf;
+                const float gp = gf * p;
+                oav[i] = an_from_f<T>(gp * (bf * act_grad<ACT>(af)));
+                obv[i] = an_from_f<T>(gp * act);
+            }
+            *reinterpret_cast<uint4 *>(grad_x + r * 2 * H + h) = oa;
+            *reinterpret_cast<uint4 *>(grad_x + r * 2 * H + H + h) = ob;
+        }
+        const float total = block_sum(dot, s_red);
+        if (threadIdx.x == 0) grad_probs[r] = total;
+    }
+}
+
+// V elements of T moved as one access (V * sizeof(T) = 16 bytes on the aligned path, V = 1 for ragged or unaligned rows)
+template <typename T, int V> struct alignas(sizeof(T) * V) Vec { T e[V]; };
+template <typename T, int V> __device__ __forceinline__ Vec<T, V> ldv(const T *p) {
+    if constexpr (V * sizeof(T) == 16) {
+        const uint4 r = __ldg(reinterpret_cast<const uint4 *>(p));
+        return *reinterpret_cast<const Vec<T, V> *>(&r);
+    } else {
+        return *reinterpret_cast<const Vec<T, V> *>(p);
+    }
+}
+template <typename T, int V> __device__ __forceinline__ Vec<T, V> ldv_plain(const T *p) { return *reinterpret_cast<const Vec<T, V> *>(p); }
+template <typename T, int V> __device__ __forceinline__ void stv(T *p, const Vec<T, V> &v) { *reinterpret_cast<Vec<T, V> *>(p) = v; }
+
+// ---------------------------------------------------------------------------------------------- RMSNorm
+// y = (x [+ residual]) * rstd * g; rstd [rows] always written; x_plus_r written when a residual is given; y may be null
+// (statistics only).  The row is read once when it fits the registers (H <= 4 vectors x 256 threads), twice else.
+template <typename T, int V, bool RESIDUAL>
+__global__ void __launch_bounds__(kAnThreads) rmsnorm_fwd_kernel(const T *__restrict__ x, const T *__restrict__ residual,
+                                                                 const T *__restrict__ gamma, float eps, int zero_centered, int64_t rows,
+                                                                 int64_t H, T *__restrict__ y, T *__restrict__ x_plus_r,
+                                                                 float *__restrict__ rstd_out) {
+    constexpr int kKeep = 4;   // 16-byte vectors a thread keeps between the two passes
+    __shared__ float s_red[kAnThreads / 32];
+    const bool fits = H <= (int64_t) kAnThreads * V * kKeep;
+    auto load_sum = [&](int64_t r, int64_t h, float &ss) -> Vec<T, V> {   // x (+ residual) at [r, h .. h + V), its squares added to ss
+        Vec<T, V> v = ldv<T, V>(x + r * H + h);
+        T *e = v.e;
+        if constexpr (RESIDUAL) {
+            const Vec<T, V> rr = ldv<T, V>(residual + r * H + h);
+            const T *re = rr.e;
+#pragma unroll
+            for (int i = 0; i < V; ++i) e[i] = an_from_f<T>(an_to_f<T>(e[i]) + an_to_f<T>(re[i]));
+            stv<T, V>(x_plus_r + r * H + h, v);
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) { const float f = an_to_f<T>(e[i]); ss += f * f; }
+        return v;
+    };
+    auto scale_store = [&](int64_t r, int64_t h, const Vec<T, V> &v, float rstd) {
+        const Vec<T, V> gr = ldv<T, V>(gamma + h);
+        const T *e = v.e, *ge = gr.e;
+        Vec<T, V> o;
+        T *oe = o.e;
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+            oe[i] = an_from_f<T>(rmsnorm_value(an_to_f<T>(e[i]), rstd, an_to_f<T>(ge[i]) + (zero_centered ? 1.0f : 0.0f)));
+        stv<T, V>(y + r * H + h, o);
+    };
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        float ss = 0.f;
+        if (fits) {
+            Vec<T, V> keep[kKeep];
+#pragma unroll
+            for (int k = 0; k < kKeep; ++k) {
+                const int64_t h = ((int64_t) k * kAnThreads + threadIdx.x) * V;
+                if (h < H) keep[k] = load_sum(r, h, ss);
+            }
+            const float rstd = rsqrtf(block_sum(ss, s_red) / (float) H + eps);
+            if (threadIdx.x == 0) rstd_out[r] = rstd;
+            if (y == nullptr) continue;
+#pragma unroll
+            for (int k = 0; k < kKeep; ++k) {
+                const int64_t h = ((int64_t) k * kAnThreads + threadIdx.x) * V;
+                if (h < H) scale_store(r, h, keep[k], rstd);
+            }
+        } else {
+            for (int64_t h = (int64_t) threadIdx.x * V; h < H; h += (int64_t) kAnThreads * V) load_sum(r, h, ss);
+            const float rstd = rsqrtf(block_sum(ss, s_red) / (float) H + eps);
+            if (threadIdx.x == 0) rstd_out[r] = rstd;
+            if (y == nullptr) continue;
+            if (RESIDUAL) __syncthreads();   // x_plus_r written above is read back below (same thread, same addresses)
+            for (int64_t h = (int64_t) threadIdx.x * V; h < H; h += (int64_t) kAnThreads * V) {
+                const Vec<T, V> v = RESIDUAL ? ldv_plain<T, V>(x_plus_r + r * H + h) : ldv<T, V>(x + r * H + h);
+                scale_store(r, h, v, rstd);
+            }
+        }
+    }
+}
+
+// dx = (dy * g - x_hat * mean(dy * g * x_hat)) * rstd (+ grad of the x + residual sum when given);
+// dgamma partial of this CTA: sum over its rows of dy * x_hat, written to dg_partial[blockIdx.x, :] (fp32).
+template <typename T, int V>
+__global__ void __launch_bounds__(kAnThreads, 2) rmsnorm_bwd_kernel(const T *__restrict__ dy, const T *__restrict__ dxpr, const T *__restrict__ x,
+                                                                 const T *__restrict__ gamma, const float *__restrict__ rstd_in,
+                                                                 int zero_centered, int64_t rows, int64_t H, T *__restrict__ dx,
+                                                                 float *__restrict__ dg_partial) {
+    constexpr int kKeep = 4;   // vectors of columns per thread whose dgamma sums stay in registers
+    __shared__ float s_red[kAnThreads / 32];
+    float *dg = dg_partial + (int64_t) blockIdx.x * H;
+    const bool fits = H <= (int64_t) kAnThreads * V * kKeep;
+    float dgr[kKeep][V];
+#pragma unroll
+    for (int k = 0; k < kKeep; ++k)
+#pragma unroll
+        for (int i = 0; i < V; ++i) dgr[k][i] = 0.f;
+    if (!fits)
+        for (int64_t h = threadIdx.x; h < H; h += kAnThreads) dg[h] = 0.f;
+    __syncthreads();   // the zeros above are written by other threads than those that add to the same columns below
+    const float zc = zero_centered ? 1.0f : 0.0f;
+    // one row: its dot product sum_h dy * g * x_hat, then dx and the dgamma terms
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const float rstd = rstd_in[r];
+        float acc = 0.f;
+        if (fits) {   // the row (x and dy) stays in registers between the two steps
+            Vec<T, V> xk[kKeep], dk[kKeep];
+#pragma unroll
+            for (int k = 0; k < kKeep; ++k) {
+                const int64_t h = ((int64_t) k * kAnThreads + threadIdx.x) * V;
+                if (h < H) {
+                    xk[k] = ldv<T, V>(x + r * H + h);
+                    dk[k] = ldv<T, V>(dy + r * H + h);
+                    const Vec<T, V> gr = ldv<T, V>(gamma + h);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) acc += an_to_f<T>(dk[k].e[i]) * (an_to_f<T>(gr.e[i]) + zc) * (an_to_f<T>(xk[k].e[i]) * rstd);
+                }
+            }
+            const float m = block_sum(acc, s_red) / (float) H;
+#pragma unroll
+            for (int k = 0; k < kKeep; ++k) {
+                const int64_t h = ((int64_t) k * kAnThreads + threadIdx.x) * V;
+                if (h < H) {
+                    const Vec<T, V> gr = ldv<T, V>(gamma + h);
+                    Vec<T, V> pr = {};
+                    if (dxpr != nullptr) pr = ldv<T, V>(dxpr + r * H + h);
+                    Vec<T, V> o;
+#pragma unroll
+                    for (int i = 0; i < V; ++i) {
+                        const float x_hat = an_to_f<T>(xk[k].e[i]) * rstd, d = an_to_f<T>(dk[k].e[i]);
+                        float v = (d * (an_to_f<T>(gr.e[i]) + zc) - x_hat * m) * rstd;
+                        if (dxpr != nullptr) v += an_to_f<T>(pr.e[i]);
+                        o.e[i] = an_from_f<T>(v);
+                        dgr[k][i] += d * x_hat;
+                    }
+                    stv<T, V>(dx + r * H + h, o);
+                }
+            }
+            continue;
+        }
+        for (int64_t h = (int64_t) threadIdx.x * V; h < H; h += (int64_t) kAnThreads * V) {
+            const Vec<T, V> xr = ldv<T, V>(x + r * H + h), dr = ldv<T, V>(dy + r * H + h), gr = ldv<T, V>(gamma + h);
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc += an_to_f<T>(dr.e[i]) * (an_to_f<T>(gr.e[i]) + zc) * (an_to_f<T>(xr.e[i]) * rstd);
+        }
+        const float m = block_sum(acc, s_red) / (float) H;
+        for (int64_t h = (int64_t) threadIdx.x * V; h < H; h += (int64_t) kAnThreads * V) {
+            const Vec<T, V> xr = ldv<T, V>(x + r * H + h), dr = ldv<T, V>(dy + r * H + h), gr = ldv<T, V>(gamma + h);
+            Vec<T, V> pr = {};
+            if (dxpr != nullptr) pr = ldv<T, V>(dxpr + r * H + h);
+            Vec<T, V> o;
+#pragma unroll
+            for (int i = 0; i < V; ++i) {
+                const float x_hat = an_to_f<T>(xr.e[i]) * rstd, d = an_to_f<T>(dr.e[i]);
+                float v = (d * (an_to_f<T>(gr.e[i]) + zc) - x_hat * m) * rstd;
+                if (dxpr != nullptr) v += an_to_f<T>(pr.e[i]);
+                o.e[i] = an_from_f<T>(v);
+                dg[h + i] += d * x_hat;   // column h + i belongs to this thread alone in every row this CTA visits
+            }
+            stv<T, V>(dx + r * H + h, o);
+        }
+    }
+    if (fits) {
+#pragma unroll
+        for (int k = 0; k < kKeep; ++k) {
+            const int64_t h = ((int64_t) k * kAnThreads + threadIdx.x) * V;
+            if (h < H) {
+#pragma unroll
+                for (int i = 0; i < V; ++i) dg[h + i] = dgr[k][i];
+            }
+        }
+    }
+}
+
+// dgamma[h] = sum over parts of dg_partial[part, h]
+template <typename T>
+__global__ void __launch_bounds__(256) rmsnorm_dgamma_kernel(const float *__restrict__ dg_partial, int parts, int64_t H, T *__restrict__ dgamma) {
+    const int64_t h = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (h >= H) return;
+    float s = 0.f;
+    for (int p = 0; p < parts; ++p) s += dg_partial[(int64_t) p * H + h];
+    dgamma[h] = an_from_f<T>(s);
+}
+
+static int an_grid(int64_t rows) { return (int) std::min<int64_t>(rows, (int64_t) sm_count() * 8); }
+
+}  // namespace ptb
+
+using namespace ptb;
+
+extern "C" {
+
+int pt_glu_fwd(const void *x, int dtype, const float *probs, const int64_t *row_mask, int64_t rows, int64_t H, int act, void *out, void *stream) {
+    PT_REQUIRE(rows >= 0 && H >= 0 && (act == 0 || act == 1), "glu forward: bad arguments");
+    if (rows * H == 0) return PT_OK;
+    PT_REQUIRE(x && probs && out, "glu forward: null pointer");
+    PT_REQUIRE((H * (dtype == PT_F32 ? 4 : 2)) % 16 == 0 && aligned(x, 16) && aligned(out, 16), "glu forward: H must give 16-byte rows, 16-byte aligned");
+    PT_SWITCH_SRC(dtype, T, {
+        if (act == 0) glu_fwd_kernel<T, PT_ACT_SILU><<<an_grid(rows), kAnThreads, 0, (cudaStream_t) stream>>>((const T *) x, probs, row_mask, rows, H, (T *) out);
+        else glu_fwd_kernel<T, PT_ACT_GELU><<<an_grid(rows), kAnThreads, 0, (cudaStream_t) stream>>>((const T *) x, probs, row_mask, rows, H, (T *) out);
+    });
+    PT_LAUNCH_OK();
+    return PT_OK;
+}
+
+int pt_glu_bwd(const void *grad_out, const void *x, int dtype, const float *probs, const int64_t *row_mask, int64_t rows, int64_t H, int act,
+               void *grad_x, float *grad_probs, void *stream) {
+    PT_REQUIRE(rows >= 0 && H >= 0 && (act == 0 || act == 1), "glu backward: bad arguments");
+    if (rows * H == 0) return PT_OK;
+    PT_REQUIRE(grad_out && x && probs && grad_x && grad_probs, "glu backward: null pointer");
+    PT_REQUIRE((H * (dtype == PT_F32 ? 4 : 2)) % 16 == 0 && aligned(x, 16) && aligned(grad_out, 16) && aligned(grad_x, 16),
+               "glu backward: H must give 16-byte rows, 16-byte aligned");
+    PT_SWITCH_SRC(dtype, T, {
+        if (act == 0)
+            glu_bwd_kernel<T, PT_ACT_SILU><<<an_grid(rows), kAnThreads, 0, (cudaStream_t) stream>>>((const T *) grad_out, (const T *) x, probs, row_mask, rows,
+                                                                                                H, (T *) grad_x, grad_probs);
+        else
+            glu_bwd_kernel<T, PT_ACT_GELU><<<an_grid(rows), kAnThreads, 0, (cudaStream_t) stream>>>((const T *) grad_out, (const T *) x, probs, row_mask, rows,
+                                                                                                H, (T *) grad_x, grad_probs);
+    });
+    PT_LAUNCH_OK();
+    return PT_OK;
+}
+
+int pt_rmsnorm_fwd(const void *x, const void *residual, const void *gamma, int dtype, float eps, int zero_centered, int64_t rows, int64_t H, void *y,
+                   void *x_plus_r, float *rstd, void *stream) {
+    PT_REQUIRE(rows >= 0 && H >= 1, "rmsnorm forward: bad shape");
+    if (rows == 0) return PT_OK;
+    PT_REQUIRE(x && rstd && (y == nullptr || gamma), "rmsnorm forward: null pointer");
+    PT_REQUIRE((residual == nullptr) == (x_plus_r == nullptr), "rmsnorm forward: residual and x_plus_r go together");
+    const bool vec = (H * (dtype == PT_F32 ? 4 : 2)) % 16 == 0 && aligned(x, 16) && aligned(y, 16) && aligned(gamma, 16) && aligned(residual, 16) &&
+                     aligned(x_plus_r, 16);   // else element-wise accesses
+    cudaStream_t st = (cudaStream_t) stream;
+#define PT_RMS_FWD(V_, RES_) \
+    rmsnorm_fwd_kernel<T, V_, RES_><<<an_grid(rows), kAnThreads, 0, st>>>((const T *) x, (const T *) residual, (const T *) gamma, eps, zero_centered, rows, H, \
+                                                                          (T *) y, (T *) x_plus_r, rstd)
+    PT_SWITCH_SRC(dtype, T, {
+        constexpr int VW = 16 / sizeof(T);
+        if (vec) { if (residual) PT_RMS_FWD(VW, true); else PT_RMS_FWD(VW, false); }
+        else { if (residual) PT_RMS_FWD(1, true); else PT_RMS_FWD(1, false); }
+    });
+#undef PT_RMS_FWD
+    PT_LAUNCH_OK();
+    return PT_OK;
+}
+
+int pt_rmsnorm_bwd_parts(int64_t rows) { return (int) std::min<int64_t>(std::max<int64_t>(rows, 1), (int64_t) sm_count() * 2); }
+
+int pt_rmsnorm_bwd(const void *dy, const void *dxpr, const void *x, const void *gamma, const float *rstd, int dtype, int zero_centered, int64_t rows,
+                   int64_t H, void *dx, void *dgamma, float *dg_partial, int parts, void *stream) {
+    PT_REQUIRE(rows >= 0 && H >= 1, "rmsnorm backward: bad shape");
+    PT_REQUIRE(dgamma && dg_partial && parts == pt_rmsnorm_bwd_parts(rows), "rmsnorm backward: dgamma buffers / part count");
+    PT_REQUIRE(rows == 0 || (dy && x && gamma && rstd && dx), "rmsnorm backward: null pointer");
+    const bool vec = (H * (dtype == PT_F32 ? 4 : 2)) % 16 == 0 && aligned(x, 16) && aligned(dy, 16) && aligned(dx, 16) && aligned(gamma, 16) && aligned(dxpr, 16);
+    cudaStream_t st = (cudaStream_t) stream;
+    PT_SWITCH_SRC(dtype, T, {
+        constexpr int VW = 16 / sizeof(T);
+        if (vec)
+            rmsnorm_bwd_kernel<T, VW><<<parts, kAnThreads, 0, st>>>((const T *) dy, (const T *) dxpr, (const T *) x, (const T *) gamma, rstd, zero_centered, rows,
+                                                                    H, (T *) dx, dg_partial);
+        else
+            rmsnorm_bwd_kernel<T, 1><<<parts, kAnThreads, 0, st>>>((const T *) dy, (const T *) dxpr, (const T *) x, (const T *) gamma, rstd, zero_centered, rows, H,
+                                                                   (T *) dx, dg_partial);
+        PT_LAUNCH_OK();
+        rmsnorm_dgamma_kernel<T><<<(unsigned) ceil_div(H, 256), 256, 0, st>>>(dg_partial, parts, H, (T *) dgamma);
+    });
+    PT_LAUNCH_OK();
+    return PT_OK;
+}
+
+}  // extern "C"

@@ -18,6 +18,7 @@
 #include "common.cuh"
 #include "gemm_common.cuh"
 #include "sm100_ptx.cuh"
+#include "act_math.cuh"
 #include "tile_sched.cuh"
 
 namespace ptb {
@@ -139,6 +140,12 @@ struct MxArgs {
     int num_groups;
     uint32_t sr_seed;        // stochastic rounding (e2m1): per-launch seed, never 0 when one of the two flags is set
     int sr_row, sr_col;
+    // fused prologue of the warp-split kernel (PRO != 0): the quantized tensor is f(x), computed tile by tile in shared memory
+    int64_t x_cols;                 // row length of x when it differs from N (gated activations: 2 N), else 0
+    const float *pro_rowvec;        // per input row: the routing probability (gated activations) or rstd (RMSNorm)
+    const int64_t *pro_mask;        // gated activations, optional: rows with a zero entry quantize as zeros
+    const void *pro_gamma;          // RMSNorm: gain [N], the input's type
+    int pro_zero_centered;          // RMSNorm: gain is 1 + gamma
 };
 
 // grid: (N_pad / 64, M_pad / 128, G); GROUPED: (N_pad / 64, (M + groups * 128) / 128, 1)
@@ -664,7 +671,6 @@ constexpr int kSGroupWarps = 4;                       // warps per output copy
 constexpr int kSGroupThreads = 32 * kSGroupWarps;
 constexpr int kSThreads = 32 * (1 + 2 * kSGroupWarps);
 constexpr int kSStageOutBytes = 8192;                 // one staged output tile (fp8: 128 x 64 bytes either way round)
-constexpr int kSSmemBytes = kSStages * kQTileBytes + 4 * kSStageOutBytes + 1024 + 1024;
 
 
 struct TileDesc {
@@ -741,18 +747,76 @@ template <int FMT> __device__ __forceinline__ void encode_row_block(const uint32
     }
 }
 
+// Fused prologues: what is quantized is f(x), computed once per tile in shared memory by all eight consumer warps before
+// the two groups go their own ways.  The arithmetic is that of the stand-alone kernels (act_math.cuh), rounded to bf16
+// as they round, so "activation kernel, then quantizer" and the fused kernel write the same bytes.
+enum { PT_PRO_NONE = 0, PT_PRO_SWIGLU = 1, PT_PRO_GEGLU = 2, PT_PRO_RMSNORM = 3 };
+constexpr bool pro_is_glu(int pro) { return pro == PT_PRO_SWIGLU || pro == PT_PRO_GEGLU; }
+// a gated activation needs two input tiles per stage (the two halves of the row)
+constexpr int split_stage_bytes(int pro) { return pro_is_glu(pro) ? 2 * kQTileBytes : kQTileBytes; }
+constexpr int split_smem_bytes(int pro) { return kSStages * split_stage_bytes(pro) + 4 * kSStageOutBytes + 1024 + 1024; }
+constexpr int split_ctas_per_sm(int pro) { return pro_is_glu(pro) ? 2 : kSCtasPerSm; }
+
+// t: 0 .. 255 over the consumer threads; thread (row = t / 2, half = t % 2) transforms 32 elements of its row in place
+template <int PRO>
+__device__ __forceinline__ void split_prologue(uint8_t *tile, int t, int in_row0, int tn, const MxArgs &a) {
+    const int row = t >> 1, half = t & 1;
+    const int64_t grow = (int64_t) in_row0 + row;
+    const bool in = grow < a.M;
+    const float rv = in ? __ldg(a.pro_rowvec + grow) : 0.f;
+    bool masked = false;
+    if constexpr (pro_is_glu(PRO)) masked = in && a.pro_mask != nullptr && __ldg(a.pro_mask + grow) == 0;
+    uint8_t *rp = tile + row * 128;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        if (!in) break;   // zero-filled rows stay +0 (0 * rstd * negative gain would make them -0)
+        const int chunk = 4 * half + c;
+        uint8_t *pa = rp + ((chunk ^ (row & 7)) << 4);
+        const uint4 av = *reinterpret_cast<const uint4 *>(pa);
+        const uint32_t aw[4] = {av.x, av.y, av.z, av.w};
+        uint32_t ow[4];
+        if constexpr (pro_is_glu(PRO)) {
+            constexpr int ACT = PRO == PT_PRO_SWIGLU ? PT_ACT_SILU : PT_ACT_GELU;
+            const uint4 bv = *reinterpret_cast<const uint4 *>(pa + kQTileBytes);
+            const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float lo = glu_value<ACT>(bf16_lo(aw[k]), bf16_lo(bw[k]), rv), hi = glu_value<ACT>(bf16_hi(aw[k]), bf16_hi(bw[k]), rv);
+                const __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
+                ow[k] = masked ? 0u : *reinterpret_cast<const uint32_t *>(&r);
+            }
+        } else {
+            const int64_t n = (int64_t) tn * kTileN + chunk * 8;
+            uint4 gv = make_uint4(0u, 0u, 0u, 0u);
+            if (n < a.N) gv = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(a.pro_gamma) + n));
+            const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+            const float zc = a.pro_zero_centered ? 1.0f : 0.0f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float lo = rmsnorm_value(bf16_lo(aw[k]), rv, bf16_lo(gw[k]) + zc), hi = rmsnorm_value(bf16_hi(aw[k]), rv, bf16_hi(gw[k]) + zc);
+                const __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
+                ow[k] = *reinterpret_cast<const uint32_t *>(&r);
+            }
+        }
+        *reinterpret_cast<uint4 *>(pa) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+    sm100::fence_proxy_async_smem();   // the next bulk load into this stage must order after these writes
+    asm volatile("bar.sync 3, %0;" ::"n"(2 * kSGroupThreads) : "memory");
+}
+
 // ROWSTAGE: the row-wise copy is staged and written by TMA (dense FP8); otherwise by 32-byte stores from registers.
-template <int FMT, bool ROW2D, bool COL2D, bool GROUPED, bool ROWSTAGE>
-__global__ void __launch_bounds__(kSThreads, kSCtasPerSm)
+template <int FMT, bool ROW2D, bool COL2D, bool GROUPED, bool ROWSTAGE, int PRO = PT_PRO_NONE>
+__global__ void __launch_bounds__(kSThreads, split_ctas_per_sm(PRO))
     mx_quant_split_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_qrow,
                           const __grid_constant__ CUtensorMap tmap_qcol, MxArgs a, int tiles_n, int tiles_m, int64_t total_tiles,
                           int sched_slot, int *status) {
     using namespace sm100;
     using T = __nv_bfloat16;
     constexpr bool kFp4 = FMT == PT_E2M1;
+    constexpr int kStageBytes = split_stage_bytes(PRO);
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t *col_stage = smem + kSStages * kQTileBytes;            // 2 x 8 KiB
+    uint8_t *col_stage = smem + kSStages * kStageBytes;            // 2 x 8 KiB
     uint8_t *row_stage = col_stage + 2 * kSStageOutBytes;          // 2 x 8 KiB
     uint64_t *full_bar = reinterpret_cast<uint64_t *>(row_stage + 2 * kSStageOutBytes);
     uint64_t *empty_bar = full_bar + kSStages;
@@ -814,8 +878,10 @@ __global__ void __launch_bounds__(kSThreads, kSCtasPerSm)
                 }
                 if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
                 s_desc[stage] = d;
-                mbar_arrive_expect_tx(&full_bar[stage], kQTileBytes);
-                sm100::tma_load_3d(smem + stage * kQTileBytes, &tmap, &full_bar[stage], d.tn * kTileN, d.in_row0, d.g);
+                mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+                sm100::tma_load_3d(smem + stage * kStageBytes, &tmap, &full_bar[stage], d.tn * kTileN, d.in_row0, d.g);
+                if constexpr (pro_is_glu(PRO))   // the gate half of the same rows: columns N .. 2N of x
+                    sm100::tma_load_3d(smem + stage * kStageBytes + kQTileBytes, &tmap, &full_bar[stage], (int) a.N + d.tn * kTileN, d.in_row0, d.g);
                 if (++stage == kSStages) { stage = 0; phase ^= 1; }
             }
             if (ok && (ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) {   // the terminal descriptor
@@ -835,9 +901,10 @@ __global__ void __launch_bounds__(kSThreads, kSCtasPerSm)
             const int tn = d0.x, tm = d0.y, n_valid = d1.x, row_out0 = d1.y;
             const int64_t g = d0.z;
             if (tn < 0) break;
+            if constexpr (PRO != PT_PRO_NONE) split_prologue<PRO>(smem + stage * kStageBytes, threadIdx.x - 32, s_desc[stage].in_row0, tn, a);
             uint32_t w[32];
             {
-                const uint8_t *rp = smem + stage * kQTileBytes + row * 128;
+                const uint8_t *rp = smem + stage * kStageBytes + row * 128;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
                     const uint4 q = *reinterpret_cast<const uint4 *>(rp + ((c ^ (row & 7)) << 4));
@@ -931,10 +998,11 @@ __global__ void __launch_bounds__(kSThreads, kSCtasPerSm)
             const int tn = d0.x, tm = d0.y;
             const int64_t g = d0.z;
             if (tn < 0) break;
+            if constexpr (PRO != PT_PRO_NONE) split_prologue<PRO>(smem + stage * kStageBytes, threadIdx.x - 32, s_desc[stage].in_row0, tn, a);
             const int n_valid = GROUPED ? s_desc[stage].n_valid : kTileM;
             uint32_t w[32];
             {
-                const uint8_t *cp = smem + stage * kQTileBytes + band * 32 * 128 + ((pair & 3) << 2);
+                const uint8_t *cp = smem + stage * kStageBytes + band * 32 * 128 + ((pair & 3) << 2);
 #pragma unroll
                 for (int r = 0; r < 32; ++r) {   // (32 band + r) % 8 == r % 8: every lane reads tile row r, no bank conflict
                     const uint32_t v = *reinterpret_cast<const uint32_t *>(cp + r * 128 + ((chunk ^ (r & 7)) << 4));
@@ -1105,9 +1173,11 @@ static int make_tmap_out(CUtensorMap *m, const void *base, int64_t G, int64_t ro
 
 // The warp-split kernel covers bf16 inputs, both copies requested, no Hadamard transform, 16-byte aligned outputs.
 // Returns PT_ERR_UNSUPPORTED (without setting an error message) when the call is outside that.
-template <int FMT, bool GROUPED>
+template <int FMT, bool GROUPED, int PRO = PT_PRO_NONE>
 static int launch_mx_split(const MxArgs &a, int64_t G, int64_t m_tiles_rows, unsigned flags, cudaStream_t st) {
-    if (getenv("PT_MX_QUANT_NO_SPLIT") != nullptr) return PT_ERR_UNSUPPORTED;
+    if (PRO == PT_PRO_NONE && getenv("PT_MX_QUANT_NO_SPLIT") != nullptr) return PT_ERR_UNSUPPORTED;
+    if (PRO != PT_PRO_NONE && (flags & (PT_MX_ROW_2D | PT_MX_COL_2D))) return PT_ERR_UNSUPPORTED;
+    if (pro_is_glu(PRO) && a.N % kTileN != 0) return PT_ERR_UNSUPPORTED;   // the value tile's last columns would be gate columns
     const bool row = flags & PT_MX_ROW, col = flags & PT_MX_COL;
     if (!row || !col || (flags & (PT_MX_ROW_RHT | PT_MX_COL_RHT | PT_MX_ROW_SR | PT_MX_COL_SR))) return PT_ERR_UNSUPPORTED;
     constexpr bool kFp4 = FMT == PT_E2M1;
@@ -1118,31 +1188,32 @@ static int launch_mx_split(const MxArgs &a, int64_t G, int64_t m_tiles_rows, uns
     const int64_t total_tiles = (int64_t) tiles_n * tiles_m * G;
     PT_REQUIRE(total_tiles < (1ll << 31), "MX quantize: too many tiles");
     CUtensorMap tx, trow, tcol;
-    int rc = make_tmap_x(&tx, a.x, G, a.M, a.N);
+    int rc = make_tmap_x(&tx, a.x, G, a.M, a.x_cols ? a.x_cols : a.N);
     if (rc != PT_OK) return rc;
     constexpr bool kRowStage = !GROUPED && !kFp4;
     trow = tx;
     if (kRowStage && (rc = make_tmap_out(&trow, a.q_row, G, a.M, a.N_pad, 64, kTileM)) != PT_OK) return rc;
     if ((rc = make_tmap_out(&tcol, a.q_col, G, a.N, kFp4 ? a.M_pad / 2 : a.M_pad, kFp4 ? 64 : 128, kTileN)) != PT_OK) return rc;
     const int slot = tile_sched_acquire(st);
-    const int grid = (int) std::min<int64_t>(total_tiles, (int64_t) sm_count() * kSCtasPerSm);
+    const int grid = (int) std::min<int64_t>(total_tiles, (int64_t) sm_count() * split_ctas_per_sm(PRO));
+    constexpr int kSmem = split_smem_bytes(PRO);
     const bool r2d = flags & PT_MX_ROW_2D, c2d = flags & PT_MX_COL_2D;
 #define PT_MXS_CASE(R2, C2)                                                                                       \
     if (r2d == R2 && c2d == C2) {                                                                                 \
-        auto kern = mx_quant_split_kernel<FMT, R2, C2, GROUPED, kRowStage>;                           \
+        auto kern = mx_quant_split_kernel<FMT, R2, C2, GROUPED, kRowStage, PRO>;                                  \
         static bool attr_set_dev[64] = {};                                                                        \
         bool &attr_set = attr_set_dev[current_device_slot()];                                                     \
         if (!attr_set) {                                                                                          \
-            PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSSmemBytes));     \
+            PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));           \
             attr_set = true;                                                                                      \
         }                                                                                                         \
-        PT_CUDA_OK(launch_overlapped(kern, dim3(grid), dim3(kSThreads), kSSmemBytes, st, tx, trow, tcol, a, tiles_n, tiles_m, total_tiles, slot, default_status())); \
+        PT_CUDA_OK(launch_overlapped(kern, dim3(grid), dim3(kSThreads), kSmem, st, tx, trow, tcol, a, tiles_n, tiles_m, total_tiles, slot, default_status())); \
         PT_LAUNCH_OK();                                                                                           \
         tile_sched_release(slot, st);                                                                             \
         return PT_OK;                                                                                             \
     }
     PT_MXS_CASE(false, false)
-    if constexpr (!GROUPED) {
+    if constexpr (!GROUPED && PRO == PT_PRO_NONE) {
         PT_MXS_CASE(true, true)
         if constexpr (!kFp4) {
             PT_MXS_CASE(true, false)
@@ -1274,11 +1345,91 @@ static void set_sr(MxArgs &a, unsigned flags) {
     a.sr_seed = (a.sr_row || a.sr_col) ? sr_seed_from(counter.fetch_add(1, std::memory_order_relaxed)) : 0u;
 }
 
+
+// Shared argument checks and MxArgs set-up of the fused entry points (dense when group_offs is null).
+static int fused_args(MxArgs &a, const char *what, const void *x, int x_dtype, int64_t rows, int64_t H, int fmt, unsigned flags, void *q_row,
+                      uint8_t *s_row, void *q_col, uint8_t *s_col, int G, const int64_t *group_offs, const int64_t *poffs_row,
+                      const int64_t *poffs_col, int64_t col_alloc) {
+    PT_REQUIRE(rows >= 0 && H >= 0, "%s: bad shape", what);
+    PT_REQUIRE(x_dtype == PT_BF16, "%s: the fused kernels take bf16 input", what);
+    PT_REQUIRE(H % 32 == 0, "%s: the quantized width must be divisible by 32 (got %lld)", what, (long long) H);
+    PT_REQUIRE((flags & (PT_MX_ROW | PT_MX_COL)) == (PT_MX_ROW | PT_MX_COL) && !(flags & ~(unsigned) (PT_MX_ROW | PT_MX_COL)),
+               "%s: the fused kernels write both copies, with 1-D block scales and round-to-nearest (flags 0x%x)", what, flags);
+    PT_REQUIRE(fmt == PT_E4M3 || fmt == PT_E2M1, "%s: formats e4m3 and e2m1", what);
+    PT_REQUIRE(q_row && s_row && q_col && s_col, "%s: outputs missing", what);
+    a.x = x; a.M = rows; a.N = H; a.N_pad = ceil_to(H, 128);
+    a.q_row = (uint8_t *) q_row; a.s_row = s_row; a.q_col = (uint8_t *) q_col; a.s_col = s_col;
+    if (group_offs) {
+        PT_REQUIRE(G >= 1 && poffs_row && poffs_col, "%s: group offsets required", what);
+        PT_REQUIRE(col_alloc % 128 == 0 && col_alloc >= rows && col_alloc / kTileM <= 65535, "%s: col_alloc must be the 128-multiple width of the col-wise buffers", what);
+        a.M_pad = col_alloc; a.group_offs = group_offs; a.poffs_row = poffs_row; a.poffs_col = poffs_col; a.num_groups = G;
+    } else {
+        const int div = fmt == PT_E2M1 ? 2 : 1;
+        a.M_pad = ceil_to(rows, 128);
+        a.qrow_gstride = rows * a.N_pad / div; a.srow_gstride = rows * (a.N_pad / 32);
+        a.qcol_gstride = H * a.M_pad / div; a.scol_gstride = H * (a.M_pad / 32);
+    }
+    return PT_OK;
+}
+
+template <int PRO, bool GROUPED>
+static int launch_fused(const MxArgs &a, const char *what, int fmt, unsigned flags, cudaStream_t st) {
+    int rc = PT_ERR_UNSUPPORTED;
+    if (fmt == PT_E4M3) rc = launch_mx_split<PT_E4M3, GROUPED, PRO>(a, 1, a.M_pad, flags, st);
+    if (fmt == PT_E2M1) rc = launch_mx_split<PT_E2M1, GROUPED, PRO>(a, 1, a.M_pad, flags, st);
+    if (rc == PT_ERR_UNSUPPORTED)
+        return set_error(PT_ERR_UNSUPPORTED, "%s: outside the fused kernel's range (16-byte aligned buffers, fewer than 2^31 rows, at most %d groups, "
+                                             "width a multiple of 64 for the gated activations)", what, kQMaxGroups);
+    return rc;
+}
+
 }  // namespace ptb
 
 using namespace ptb;
 
 extern "C" {
+
+int pt_glu_quantize_mx(const void *x, int x_dtype, const float *probs, const int64_t *row_mask, int64_t rows, int64_t H, int act, int fmt,
+                       unsigned flags, void *q_row, uint8_t *s_row, void *q_col, uint8_t *s_col, void *stream) {
+    const char *what = "fused gated activation + MX quantize";
+    MxArgs a{};
+    int rc = fused_args(a, what, x, x_dtype, rows, H, fmt, flags, q_row, s_row, q_col, s_col, 0, nullptr, nullptr, nullptr, 0);
+    if (rc != PT_OK) return rc;
+    PT_REQUIRE(act == 0 || act == 1, "%s: act must be 0 (SiLU) or 1 (GELU)", what);
+    if (rows == 0 || H == 0) return PT_OK;
+    PT_REQUIRE(x && probs, "%s: null pointer", what);
+    a.x_cols = 2 * H; a.pro_rowvec = probs; a.pro_mask = row_mask;
+    return act == 0 ? launch_fused<PT_PRO_SWIGLU, false>(a, what, fmt, flags, (cudaStream_t) stream)
+                    : launch_fused<PT_PRO_GEGLU, false>(a, what, fmt, flags, (cudaStream_t) stream);
+}
+
+int pt_grouped_glu_quantize_mx(const void *x, int x_dtype, const float *probs, const int64_t *row_mask, int64_t rows, int64_t H, int act, int G,
+                               const int64_t *group_offs, const int64_t *padded_offs_row, const int64_t *padded_offs_col, int fmt, unsigned flags,
+                               void *q_row, uint8_t *s_row, void *q_col, uint8_t *s_col, int64_t col_alloc, void *stream) {
+    const char *what = "fused gated activation + grouped MX quantize";
+    PT_REQUIRE(group_offs, "%s: group offsets required", what);
+    MxArgs a{};
+    int rc = fused_args(a, what, x, x_dtype, rows, H, fmt, flags, q_row, s_row, q_col, s_col, G, group_offs, padded_offs_row, padded_offs_col, col_alloc);
+    if (rc != PT_OK) return rc;
+    PT_REQUIRE(act == 0 || act == 1, "%s: act must be 0 (SiLU) or 1 (GELU)", what);
+    if (H == 0) return PT_OK;
+    PT_REQUIRE(rows == 0 || (x && probs), "%s: null pointer", what);
+    a.x_cols = 2 * H; a.pro_rowvec = probs; a.pro_mask = row_mask;
+    return act == 0 ? launch_fused<PT_PRO_SWIGLU, true>(a, what, fmt, flags, (cudaStream_t) stream)
+                    : launch_fused<PT_PRO_GEGLU, true>(a, what, fmt, flags, (cudaStream_t) stream);
+}
+
+int pt_rmsnorm_quantize_mx(const void *x, int x_dtype, const float *rstd, const void *gamma, int zero_centered, int64_t rows, int64_t H, int fmt,
+                           unsigned flags, void *q_row, uint8_t *s_row, void *q_col, uint8_t *s_col, void *stream) {
+    const char *what = "fused RMSNorm + MX quantize";
+    MxArgs a{};
+    int rc = fused_args(a, what, x, x_dtype, rows, H, fmt, flags, q_row, s_row, q_col, s_col, 0, nullptr, nullptr, nullptr, 0);
+    if (rc != PT_OK) return rc;
+    if (rows == 0 || H == 0) return PT_OK;
+    PT_REQUIRE(x && rstd && gamma && aligned(gamma, 16), "%s: null or unaligned pointer", what);
+    a.pro_rowvec = rstd; a.pro_gamma = gamma; a.pro_zero_centered = zero_centered;
+    return launch_fused<PT_PRO_RMSNORM, false>(a, what, fmt, flags, (cudaStream_t) stream);
+}
 
 int pt_grouped_quantize_mx(const void *x, int x_dtype, int64_t M, int64_t N, int G, const int64_t *group_offs,
                            const int64_t *padded_offs_row, const int64_t *padded_offs_col, int fmt, unsigned flags, void *q_row,

@@ -47,6 +47,18 @@ SIGNATURES = {
     "pt_moe_unpermute": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "pt_moe_unpermute_bwd_with_probs": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p,
                                                 c_void_p, c_void_p]),
+    "pt_glu_fwd": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p]),
+    "pt_glu_bwd": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
+    "pt_rmsnorm_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "pt_rmsnorm_bwd_parts": (c_int, [c_int64]),
+    "pt_rmsnorm_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                               c_int, c_void_p]),
+    "pt_glu_quantize_mx": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_uint, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_void_p]),
+    "pt_grouped_glu_quantize_mx": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                           c_int, c_uint, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "pt_rmsnorm_quantize_mx": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_uint, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_void_p]),
     "pt_transpose_2d": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "pt_transpose_batched": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "pt_grouped_transpose_pad": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p]),

@@ -226,7 +226,35 @@ def dequant_fp8_blockwise_for_weight_impl(x: torch.Tensor, scales: torch.Tensor,
 
 
 # ------------------------------------------------------------------------------ MX
-def _mx_quant(x, out_dtype, want_row, want_col, row_recipe, col_recipe):
+def _launch_fused_mx(pro, x, M, N, fmt, flags, q_row, s_row, q_col, s_col, grouped=None):
+    """pro = ("glu", probs, row_mask, act_code) or ("rmsnorm", rstd, gamma, zero_centered): the quantizer applies the
+    operator to each tile of x as it loads it.  grouped = (G, offs, poffs_row, poffs_col, col_alloc) for the grouped form."""
+    lib, st = nv.lib(), nv.stream(x.device)
+    if pro[0] == "glu":
+        _, probs, row_mask, act = pro
+        if grouped is None:
+            nv.check(lib.pt_glu_quantize_mx(nv.ptr(x), nv.src_code(x.dtype), nv.ptr(probs), nv.ptr(row_mask), M, N, act, fmt, flags, nv.ptr(q_row),
+                                            nv.ptr(s_row), nv.ptr(q_col), nv.ptr(s_col), st), "glu_quantize_mx")
+        else:
+            G, offs, poffs_row, poffs_col, col_alloc = grouped
+            nv.check(lib.pt_grouped_glu_quantize_mx(nv.ptr(x), nv.src_code(x.dtype), nv.ptr(probs), nv.ptr(row_mask), M, N, act, G, nv.ptr(offs),
+                                                    nv.ptr(poffs_row), nv.ptr(poffs_col), fmt, flags, nv.ptr(q_row), nv.ptr(s_row), nv.ptr(q_col),
+                                                    nv.ptr(s_col), col_alloc, st), "grouped_glu_quantize_mx")
+    else:
+        _, rstd, gamma, zero_centered = pro
+        assert grouped is None
+        nv.check(lib.pt_rmsnorm_quantize_mx(nv.ptr(x), nv.src_code(x.dtype), nv.ptr(rstd), nv.ptr(gamma), int(bool(zero_centered)), M, N, fmt, flags,
+                                            nv.ptr(q_row), nv.ptr(s_row), nv.ptr(q_col), nv.ptr(s_col), st), "rmsnorm_quantize_mx")
+
+
+def fused_mx_supported(x: torch.Tensor, width: int, out_dtype, gated: bool) -> bool:
+    """Whether the one-pass kernels take this call: bf16 input, e4m3 or e2m1 codes, 16-byte aligned rows, and for the gated
+    activations a width that is a multiple of the 64-column tile.  Outside that the caller runs operator + quantizer."""
+    return (x.dtype == torch.bfloat16 and nv.fmt_code(out_dtype) in (nv.PT_E4M3, nv.PT_E2M1) and width % (64 if gated else 32) == 0
+            and x.data_ptr() % 16 == 0 and 0 < x.shape[0] < 2 ** 31)
+
+
+def _mx_quant(x, out_dtype, want_row, want_col, row_recipe, col_recipe, pro=None):
     nv.require_cuda(x)
     for r in (row_recipe, col_recipe):
         if r is not None and (r.shuffle_scale or r.shuffle_out):
@@ -239,6 +267,8 @@ def _mx_quant(x, out_dtype, want_row, want_col, row_recipe, col_recipe):
             raise ValueError("stochastic rounding is an MXFP4 option (ScalingRecipe.use_sr)")
     G = 1 if x.dim() == 2 else x.shape[0]
     M, N = x.shape[-2:]
+    if pro is not None and pro[0] == "glu":
+        N //= 2   # the quantized tensor is act(x[:, :N]) * x[:, N:] * probs
     M_pad, N_pad = ceil_div(M, MX_ALIGN) * MX_ALIGN, ceil_div(N, MX_ALIGN) * MX_ALIGN
     lead = () if x.dim() == 2 else (G,)
     div = 2 if fp4 else 1
@@ -255,8 +285,12 @@ def _mx_quant(x, out_dtype, want_row, want_col, row_recipe, col_recipe):
         q_col = torch.empty(lead + (N, M_pad // div), dtype=torch.uint8, device=x.device)
         s_col = torch.empty(lead + (N, M_pad // MX_BLOCK), dtype=torch.uint8, device=x.device)
     with nv.on_device(x.device):
-        nv.check(nv.lib().pt_quantize_mx(nv.ptr(x), nv.src_code(x.dtype), G, M, N, fmt, flags, nv.ptr(q_row), nv.ptr(s_row),
-                                          nv.ptr(q_col), nv.ptr(s_col), nv.stream(x.device)), "quantize_mx")
+        if pro is not None:
+            assert G == 1 and x.dim() == 2
+            _launch_fused_mx(pro, x, M, N, fmt, flags, q_row, s_row, q_col, s_col)
+        else:
+            nv.check(nv.lib().pt_quantize_mx(nv.ptr(x), nv.src_code(x.dtype), G, M, N, fmt, flags, nv.ptr(q_row), nv.ptr(s_row),
+                                              nv.ptr(q_col), nv.ptr(s_col), nv.stream(x.device)), "quantize_mx")
     view = lambda t: None if t is None else t.view(out_dtype)
     sview = lambda t: None if t is None else t.view(torch.float8_e8m0fnu)
     return view(q_row), sview(s_row), view(q_col), sview(s_col)
@@ -372,7 +406,7 @@ MX_GROUP_ROW_ALIGN = 32   # fp8 row-wise copy: each group padded to 32 rows (qua
 MX_GROUP_COL_ALIGN = 128  # col-wise copy: each group padded to 128 rows
 
 
-def _grouped_mx_quant(x, out_dtype, group_lens, group_offs, want_row, want_col, row_recipe, col_recipe):
+def _grouped_mx_quant(x, out_dtype, group_lens, group_offs, want_row, want_col, row_recipe, col_recipe, pro=None):
     nv.require_cuda(x, group_lens, group_offs)
     for r in (row_recipe, col_recipe):
         if r is not None and (r.shuffle_scale or r.shuffle_out):
@@ -387,6 +421,8 @@ def _grouped_mx_quant(x, out_dtype, group_lens, group_offs, want_row, want_col, 
         if r is not None and r.use_sr and not fp4:
             raise ValueError("stochastic rounding is an MXFP4 option (ScalingRecipe.use_sr)")
     M, N = x.shape
+    if pro is not None:
+        N //= 2
     G = group_lens.numel()
     lens = group_lens.to(torch.int64).contiguous()
     offs = group_offs.to(torch.int64).contiguous()
@@ -414,9 +450,12 @@ def _grouped_mx_quant(x, out_dtype, group_lens, group_offs, want_row, want_col, 
         q_col = torch.empty((N, col_alloc // div), dtype=torch.uint8, device=x.device)
         s_col = torch.empty((N, col_alloc // MX_BLOCK), dtype=torch.uint8, device=x.device)
     with nv.on_device(x.device):
-        nv.check(nv.lib().pt_grouped_quantize_mx(nv.ptr(x), nv.src_code(x.dtype), M, N, G, nv.ptr(offs), nv.ptr(poffs_row),
-                                                  nv.ptr(poffs_col), fmt, flags, nv.ptr(q_row), nv.ptr(s_row), nv.ptr(q_col),
-                                                  nv.ptr(s_col), col_alloc, nv.stream(x.device)), "grouped_quantize_mx")
+        if pro is not None:
+            _launch_fused_mx(pro, x, M, N, fmt, flags, q_row, s_row, q_col, s_col, grouped=(G, offs, poffs_row, poffs_col, col_alloc))
+        else:
+            nv.check(nv.lib().pt_grouped_quantize_mx(nv.ptr(x), nv.src_code(x.dtype), M, N, G, nv.ptr(offs), nv.ptr(poffs_row),
+                                                      nv.ptr(poffs_col), fmt, flags, nv.ptr(q_row), nv.ptr(s_row), nv.ptr(q_col),
+                                                      nv.ptr(s_col), col_alloc, nv.stream(x.device)), "grouped_quantize_mx")
     view = lambda t: None if t is None else t.view(out_dtype)
     sview = lambda t: None if t is None else t.view(torch.float8_e8m0fnu)
     return (view(q_row), sview(s_row), view(q_col), sview(s_col), plens_row, poffs_row, plens_col, poffs_col)
@@ -475,3 +514,47 @@ def grouped_dequantize_mxfp8_impl(x: torch.Tensor, out_dtype: torch.dtype, axis:
     padded = _dequantize_mx(x, out_dtype, axis, scale_inv)      # [M_pad, N(_pad)] in the original orientation
     idx = _tight_row_index(group_offs, group_offs_padded, total_M, x.device)
     return padded.index_select(0, idx)
+
+
+# ------------------------------------------------------------------------------ operator + MX quantizer in one pass
+def glu_quantize_mx_impl(x: torch.Tensor, probs: torch.Tensor, row_mask, act: str, out_dtype, fused=None):
+    """MX copies (row-wise and transposed) of act(x[:, :H]) * x[:, H:] * probs without the [tokens, H] intermediate:
+    (q_row, s_row, q_col, s_col), the bytes `glu_fwd_with_probs` followed by `quantize_mx*_impl(with_trans=True)` gives.
+    fused=None picks the one-pass kernel where it applies; False forces the two kernels (the comparison the tests make)."""
+    from ..activation.glu_impl import ACT_CODES, glu_fwd_with_probs
+    nv.require_cuda(x, probs, row_mask)
+    x, probs = x.contiguous(), probs.contiguous().view(-1)
+    H = x.shape[1] // 2
+    use = fused_mx_supported(x, H, out_dtype, True) if fused is None else fused
+    if not use:
+        return _mx_quant(glu_fwd_with_probs(x, probs, row_mask, act), out_dtype, True, True, ScalingRecipe(), ScalingRecipe())
+    return _mx_quant(x, out_dtype, True, True, ScalingRecipe(), ScalingRecipe(), pro=("glu", probs, row_mask, ACT_CODES[act]))
+
+
+def grouped_glu_quantize_mx_impl(x, probs, row_mask, act: str, out_dtype, group_lens, group_offs, fused=None):
+    """Grouped form (token segments per expert); returns what `grouped_quantize_mx*_impl(with_trans=True)` returns."""
+    from ..activation.glu_impl import ACT_CODES, glu_fwd_with_probs
+    nv.require_cuda(x, probs, row_mask)
+    x, probs = x.contiguous(), probs.contiguous().view(-1)
+    H = x.shape[1] // 2
+    use = (fused_mx_supported(x, H, out_dtype, True) and group_lens.numel() <= 256) if fused is None else fused
+    if not use:
+        return _grouped_mx_quant(glu_fwd_with_probs(x, probs, row_mask, act), out_dtype, group_lens, group_offs, True, True, ScalingRecipe(),
+                                 ScalingRecipe())
+    return _grouped_mx_quant(x, out_dtype, group_lens, group_offs, True, True, ScalingRecipe(), ScalingRecipe(),
+                             pro=("glu", probs, row_mask, ACT_CODES[act]))
+
+
+def rmsnorm_quantize_mx_impl(x: torch.Tensor, gamma: torch.Tensor, eps: float, zero_centered: bool, out_dtype, fused=None):
+    """MX copies of rmsnorm(x) and the row statistics: (q_row, s_row, q_col, s_col, rstd).  One statistics pass over x,
+    then the quantizer normalises each tile as it loads it; the normalised tensor is never written."""
+    from ..normalization.rmsnorm_impl import rmsnorm_fwd_impl, rmsnorm_stats_impl
+    nv.require_cuda(x, gamma)
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    gamma = gamma.contiguous()
+    use = (fused_mx_supported(x2, x2.shape[1], out_dtype, False) and gamma.dtype == x2.dtype) if fused is None else fused
+    if not use:
+        y, _, rstd = rmsnorm_fwd_impl(x2, gamma, eps, zero_centered)
+        return (*_mx_quant(y, out_dtype, True, True, ScalingRecipe(), ScalingRecipe()), rstd)
+    rstd = rmsnorm_stats_impl(x2, eps)
+    return (*_mx_quant(x2, out_dtype, True, True, ScalingRecipe(), ScalingRecipe(), pro=("rmsnorm", rstd, gamma, zero_centered)), rstd)
