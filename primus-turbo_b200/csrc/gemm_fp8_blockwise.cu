@@ -414,8 +414,13 @@ __global__ void __launch_bounds__(kBwThreads, 1)
                 auto add_chunk = [&](int c, const uint32_t(&r)[32]) {
                     if constexpr (sb_uniform) {
                         const float sc = sa_cur * sbu_cur;  // one scale for the whole 32 x 128 block of this warp
+                        uint64_t sc2;
+                        asm("mov.b64 %0, {%1, %1};" : "=l"(sc2) : "f"(sc));
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), sc, acc[c * 32 + i]);
+                        for (int i = 0; i < 16; ++i)   // two accumulators per instruction; each rounds like fmaf(r, sc, acc)
+                            asm("{\n\t.reg .b64 rr;\n\tmov.b64 rr, {%1, %2};\n\tfma.rn.f32x2 %0, rr, %3, %0;\n\t}"
+                                : "+l"(*reinterpret_cast<uint64_t *>(&acc[c * 32 + 2 * i]))
+                                : "r"(r[2 * i]), "r"(r[2 * i + 1]), "l"(sc2));
                     } else if constexpr (SBM == SB_SLAB) {
                         // the slab of this K step landed before the partial sum was announced (see the MMA issuer)
                         const float4 *sl =
