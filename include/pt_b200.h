@@ -221,6 +221,14 @@ int pt_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const void *b, co
                 int c_dtype, int granularity, int64_t M, int64_t N, int64_t K, float beta, int block_n, void *workspace,
                 size_t workspace_bytes, int *status, void *stream);
 
+/* pt_gemm_fp8 for PT_TENSORWISE / PT_ROWWISE with operands read in place whichever way they are stored: a_mn = 1 means
+ * `a` is stored [K, M] (contraction-major: the layout of an activation or gradient that a wgrad contracts over its tokens,
+ * or of a weight that a dgrad contracts over its output features), 0 means [M, K]; likewise b_mn for `b` ([K, N] / [N, K]).
+ * An MN-major operand needs a row count (M or N) that is a multiple of 16.  Removes the transposed copies the reference's
+ * NT-only back ends make first (primus_turbo/pytorch/ops/gemm_fp8.py:44-50 of the reference). */
+int pt_gemm_fp8_mn(const void *a, const void *a_scale, int a_fmt, int a_mn, const void *b, const void *b_scale, int b_fmt, int b_mn, void *c,
+                   int c_dtype, int granularity, int64_t M, int64_t N, int64_t K, float beta, int *status, void *stream);
+
 /* Scratch bytes pt_gemm_fp8 / pt_grouped_gemm_fp8 need: 0 except for PT_MX_BLOCKWISE, where the raw scales are
  * re-tiled into the block layout of the tensor core's scale copy before the GEMM (the reference's back ends also
  * pre-shuffle the raw scales right before their kernels, primus_turbo/pytorch/ops/gemm_fp8.py:577-579).

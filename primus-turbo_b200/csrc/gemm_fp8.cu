@@ -59,6 +59,8 @@ struct GemmParams {
     int *status;                // device int: set to a PT_ERR_* code on a bounded-wait expiry
     int raster_m;               // row blocks per raster band
     int64_t sfb_line0;          // CTA-pair MX kernel: first 128-byte line of the re-tiled B scales in the scale buffer
+    int a_mn, b_mn;             // tensorwise / rowwise, one group: the operand is stored [contraction, rows] (MN-major) and read in
+                                // place: 128-byte x 128-row boxes, described to the tensor core as in gemm_fp8_blockwise.cu
 };
 
 // F4: packed e2m1 operands.  A 128-byte stage row then holds 256 elements = two 128-element scale blocks, so every
@@ -364,8 +366,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 for (int kb = 0; kb < kb_count; ++kb) {
                     if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
                     mbar_arrive_expect_tx(&full_bar[stage], Cfg::kABytes + Cfg::kBBytes + Cfg::kSfBytes);
-                    tma_load_2d(smem_a + stage * Cfg::kABytes, &tmap_a, &full_bar[stage], (kb_begin + kb) * BLOCK_K, (int) a_row0);
-                    tma_load_2d(smem_b + stage * Cfg::kBBytes, &tmap_b, &full_bar[stage], (kb_begin + kb) * BLOCK_K, (int) b_row0);
+                    const int k0 = (kb_begin + kb) * BLOCK_K;
+                    if (!MX && p.a_mn) tma_load_2d(smem_a + stage * Cfg::kABytes, &tmap_a, &full_bar[stage], (int) a_row0, k0);
+                    else tma_load_2d(smem_a + stage * Cfg::kABytes, &tmap_a, &full_bar[stage], k0, (int) a_row0);
+                    if (!MX && p.b_mn) {   // one 128-wide box per 128 columns of the tile, 16 KiB apart
+#pragma unroll
+                        for (int j = 0; j < (BLOCK_N + 127) / 128; ++j)
+                            tma_load_2d(smem_b + stage * Cfg::kBBytes + j * 16384, &tmap_b, &full_bar[stage], (int) b_row0 + 128 * j, k0);
+                    } else {
+                        tma_load_2d(smem_b + stage * Cfg::kBBytes, &tmap_b, &full_bar[stage], k0, (int) b_row0);
+                    }
                     if constexpr (MX) {
                         // per stage: kSfP consecutive 512-byte blocks of A (one copy), and of each 128-row block of B
                         uint8_t *sf = smem_sf + stage * Cfg::kSfBytes;
@@ -384,9 +394,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (elect_one()) {
             constexpr uint32_t kIdescPlainShape = 0;
             (void) kIdescPlainShape;
+            const bool a_mn = !MX && MODE != GEMM_HP && p.a_mn, b_mn = !MX && MODE != GEMM_HP && p.b_mn;
             const uint32_t idesc = F4 ? idesc_block_scaled(1, 1, BLOCK_M, BLOCK_N)   // kind::mxf4: format code 1 = e2m1
                                    : MX ? idesc_block_scaled(p.a_fmt, p.b_fmt, BLOCK_M, BLOCK_N)
-                                        : idesc_f8(p.a_fmt, p.b_fmt, BLOCK_M, BLOCK_N);
+                                        : (idesc_f8(p.a_fmt, p.b_fmt, BLOCK_M, BLOCK_N) | ((uint32_t) a_mn << 15) | ((uint32_t) b_mn << 16));
+            // one instruction consumes 32 contraction indices: 32 bytes along a K-major row, or 32 rows of 128 bytes of an
+            // MN-major tile
+            const uint64_t a_kstep = a_mn ? (uint64_t) ((UMMA_K * 128) >> 4) : (uint64_t) (UMMA_K >> 4);
+            const uint64_t b_kstep = b_mn ? (uint64_t) ((UMMA_K * 128) >> 4) : (uint64_t) (UMMA_K >> 4);
             uint32_t stage = 0, phase = 0, acc_stage = 0, acc_phase = 0, sf_buf = 0;
             for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
                 int kb_begin, kb_count;
@@ -413,8 +428,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                         }
                         if constexpr (!F4) sf_buf ^= 1;
                     }
-                    const uint64_t a_desc = smem_desc_sw128(smem_u32(smem_a + stage * Cfg::kABytes));
-                    const uint64_t b_desc = smem_desc_sw128(smem_u32(smem_b + stage * Cfg::kBBytes));
+                    const uint32_t a_addr = smem_u32(smem_a + stage * Cfg::kABytes), b_addr = smem_u32(smem_b + stage * Cfg::kBBytes);
+                    const uint64_t a_desc = a_mn ? smem_desc_sw128_mn(a_addr, 16384) : smem_desc_sw128(a_addr);
+                    const uint64_t b_desc = b_mn ? smem_desc_sw128_mn(b_addr, 16384) : smem_desc_sw128(b_addr);
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
                         const uint64_t adv = (uint64_t) ((k * UMMA_K) >> 4);
@@ -427,7 +443,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                         else if constexpr (MODE == GEMM_HP)
                             mma_f16(d_tmem, a_desc + adv, b_desc + adv, idesc, accumulate);
                         else
-                            mma_f8(d_tmem, a_desc + adv, b_desc + adv, idesc, accumulate);
+                            mma_f8(d_tmem, a_desc + k * a_kstep, b_desc + k * b_kstep, idesc, accumulate);
                     }
                     tc_commit(&empty_bar[stage]);  // frees the ring slot once these MMAs have read it
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -533,8 +549,9 @@ static int launch_gemm(const void *a, int64_t a_rows, const void *b, int64_t b_r
     }
     CUtensorMap ta, tb;
     int rc;
-    if ((rc = make_tmap_bytes(&ta, a, a_rows, p.K, p.K, BLOCK_M)) != PT_OK) return rc;
-    if ((rc = make_tmap_bytes(&tb, b, b_rows, p.K, p.K, BLOCK_N)) != PT_OK) return rc;
+    // K-major: box = 128 contraction bytes x tile rows; MN-major: box = 128 row indices x 128 contraction rows
+    if ((rc = p.a_mn ? make_tmap_bytes(&ta, a, p.K, a_rows, a_rows, BLOCK_K) : make_tmap_bytes(&ta, a, a_rows, p.K, p.K, BLOCK_M)) != PT_OK) return rc;
+    if ((rc = p.b_mn ? make_tmap_bytes(&tb, b, p.K, b_rows, b_rows, BLOCK_K) : make_tmap_bytes(&tb, b, b_rows, p.K, p.K, BLOCK_N)) != PT_OK) return rc;
     auto kern = gemm_fp8_kernel<BLOCK_N, MODE>;
     static bool attr_set[64] = {};  // per instantiation and device
     const int dev = current_device_slot();
@@ -566,8 +583,8 @@ static int launch_gemm_pair(const void *a, int64_t a_rows, const void *b, int64_
         const int64_t lines = (int64_t) mx_workspace_bytes(p.M, p.N, p.K, p.koffs ? 1 : p.G, grouped, BLOCK_N) * Cfg::kSfPerStage / 128;
         if ((rc = make_tmap_lines(&tsf, p.sfa_tiled, lines, 4 * Cfg::kSfPerStage)) != PT_OK) return rc;
     }
-    if ((rc = make_tmap_bytes(&ta, a, a_rows, p.K, p.K, BLOCK_M)) != PT_OK) return rc;
-    if ((rc = make_tmap_bytes(&tb, b, b_rows, p.K, p.K, Cfg::kHalfN)) != PT_OK) return rc;
+    if ((rc = p.a_mn ? make_tmap_bytes(&ta, a, p.K, a_rows, a_rows, BLOCK_K) : make_tmap_bytes(&ta, a, a_rows, p.K, p.K, BLOCK_M)) != PT_OK) return rc;
+    if ((rc = p.b_mn ? make_tmap_bytes(&tb, b, p.K, b_rows, b_rows, BLOCK_K) : make_tmap_bytes(&tb, b, b_rows, p.K, p.K, Cfg::kHalfN)) != PT_OK) return rc;
     if constexpr (!mode_is_mx(MODE)) tsf = ta;
     auto kern = gemm_fp8_pair_kernel<BLOCK_N, MODE>;
     PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
@@ -652,10 +669,17 @@ static int dispatch_block_n(int block_n, const void *a, int64_t a_rows, const vo
 int gemm_fp8_host(const void *a, const void *a_scale, int a_fmt, const void *b, const void *b_scale, int b_fmt, void *c,
                   int c_dtype, int64_t ldc, int granularity, int64_t M, int64_t N, int64_t K, float beta,
                   const int64_t *offs_read, const int64_t *offs_write, const int64_t *k_offs, int G, int64_t a_rows_total,
-                  int block_n, int max_ctas, void *workspace, size_t workspace_bytes, int *status, void *stream) {
+                  int block_n, int max_ctas, void *workspace, size_t workspace_bytes, int *status, void *stream, int a_mn = 0,
+                  int b_mn = 0) {
     PT_REQUIRE(M >= 0 && N >= 0 && K >= 0 && G >= 1 && G <= kMaxGroups, "GEMM: bad shape (M=%lld N=%lld K=%lld G=%d)",
                (long long) M, (long long) N, (long long) K, G);
     const bool fp4 = a_fmt == PT_E2M1 || b_fmt == PT_E2M1;
+    if (a_mn || b_mn) {
+        PT_REQUIRE(G == 1 && !offs_read && !offs_write && !k_offs && (granularity == PT_TENSORWISE || granularity == PT_ROWWISE),
+                   "GEMM: MN-major operands are taken by the dense tensorwise / rowwise form");
+        PT_REQUIRE((!a_mn || M % 16 == 0) && (!b_mn || N % 16 == 0), "GEMM: an MN-major operand needs a row count that is a multiple of 16");
+        PT_REQUIRE(block_n == 0 || block_n == 128 || block_n == 256, "GEMM: MN-major operands take 128- or 256-column tiles");
+    }
     PT_REQUIRE(!fp4 || (a_fmt == PT_E2M1 && b_fmt == PT_E2M1 && granularity == PT_MX_BLOCKWISE),
                "GEMM: e2m1 operands go together and take MX_BLOCKWISE scales");
     PT_REQUIRE(fp4 || a_fmt == PT_E4M3 || a_fmt == PT_E5M2, "GEMM: A format must be e4m3, e5m2 or e2m1");
@@ -664,11 +688,12 @@ int gemm_fp8_host(const void *a, const void *a_scale, int a_fmt, const void *b, 
     PT_REQUIRE(beta == 0.f || beta == 1.f, "GEMM: beta must be 0 or 1");
     PT_REQUIRE((offs_read == nullptr) == (offs_write == nullptr) || offs_write, "GEMM: write offsets required with read offsets");
     if (M == 0 || N == 0) return PT_OK;
-    PT_REQUIRE(K > 0 && K % 16 == 0, "GEMM: K must be a positive multiple of 16 (got %lld)", (long long) K);
+    PT_REQUIRE(K > 0 && (K % 16 == 0 || (a_mn && b_mn)), "GEMM: K must be a positive multiple of 16 (got %lld)", (long long) K);
     PT_REQUIRE(a && b && c && a_scale && b_scale, "GEMM: null pointer");
     PT_REQUIRE(N < (1 << 30) && K < (1 << 30) && a_rows_total < (1ll << 31) && (int64_t) G * N < (1ll << 31),
                "GEMM: extent exceeds 32-bit tile coordinates");
     GemmParams p{};
+    p.a_mn = a_mn; p.b_mn = b_mn;
     p.M = M; p.N = (int) N; p.K = (int) K; p.C = c; p.ldc = ldc; p.c_dtype = c_dtype; p.beta = beta;
     const int esize = c_dtype == PT_F32 ? 4 : 2;
     p.vec_store_ok = aligned(c, 16) && (ldc * esize) % 16 == 0;
@@ -783,6 +808,12 @@ int pt_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const void *b, co
                 size_t workspace_bytes, int *status, void *stream) {
     return gemm_fp8_host(a, a_scale, a_fmt, b, b_scale, b_fmt, c, c_dtype, N, granularity, M, N, K, beta, nullptr, nullptr,
                          nullptr, 1, M, block_n, 0, workspace, workspace_bytes, status, stream);
+}
+
+int pt_gemm_fp8_mn(const void *a, const void *a_scale, int a_fmt, int a_mn, const void *b, const void *b_scale, int b_fmt, int b_mn, void *c,
+                   int c_dtype, int granularity, int64_t M, int64_t N, int64_t K, float beta, int *status, void *stream) {
+    return gemm_fp8_host(a, a_scale, a_fmt, b, b_scale, b_fmt, c, c_dtype, N, granularity, M, N, K, beta, nullptr, nullptr, nullptr, 1, M, 0, 0,
+                         nullptr, 0, status, stream, a_mn, b_mn);
 }
 
 int pt_grouped_gemm_fp8(const void *a, const void *a_scale, int a_fmt, const void *b, const void *b_scale, int b_fmt,

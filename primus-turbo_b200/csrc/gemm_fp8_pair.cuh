@@ -160,8 +160,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((PairCfg<BLOCK_N, mo
                     if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
                     const uint32_t full_leader = map_to_rank(&full_bar[stage], 0);
                     if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
-                    tma_load_2d_pair(smem_a + stage * Cfg::kABytes, &tmap_a, full_leader, (kb_begin + kb) * BLOCK_K, a_row0);
-                    tma_load_2d_pair(smem_b + stage * Cfg::kBBytes, &tmap_b, full_leader, (kb_begin + kb) * BLOCK_K, b_row0);
+                    const int k0 = (kb_begin + kb) * BLOCK_K;
+                    // MN-major operands (dense tensorwise / rowwise): 128 row indices x 128 contraction rows per CTA
+                    if (!MX && p.a_mn) tma_load_2d_pair(smem_a + stage * Cfg::kABytes, &tmap_a, full_leader, a_row0, k0);
+                    else tma_load_2d_pair(smem_a + stage * Cfg::kABytes, &tmap_a, full_leader, k0, a_row0);
+                    if (!MX && p.b_mn) tma_load_2d_pair(smem_b + stage * Cfg::kBBytes, &tmap_b, full_leader, b_row0, k0);
+                    else tma_load_2d_pair(smem_b + stage * Cfg::kBBytes, &tmap_b, full_leader, k0, b_row0);
                     if constexpr (MX) {
                         uint8_t *sf = smem_sf + stage * Cfg::kSfBytes;
                         tma_load_2d_pair(sf, &tmap_sf, full_leader, 0, (int) (sfa_line0 + 4 * kSfP * kb));
@@ -179,7 +183,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((PairCfg<BLOCK_N, mo
         if (rank == 0 && elect_one()) {
             const uint32_t idesc = F4 ? idesc_block_scaled(1, 1, kTileM, BLOCK_N)  // kind::mxf4: format code 1 = e2m1
                                    : MX ? idesc_block_scaled(p.a_fmt, p.b_fmt, kTileM, BLOCK_N)
-                                        : idesc_f8(p.a_fmt, p.b_fmt, kTileM, BLOCK_N);
+                                        : (idesc_f8(p.a_fmt, p.b_fmt, kTileM, BLOCK_N) | ((uint32_t) (p.a_mn != 0) << 15) | ((uint32_t) (p.b_mn != 0) << 16));
+            const bool a_mn = !MX && MODE != GEMM_HP && p.a_mn, b_mn = !MX && MODE != GEMM_HP && p.b_mn;
+            const uint64_t a_kstep = a_mn ? (uint64_t) ((UMMA_K * 128) >> 4) : (uint64_t) (UMMA_K >> 4);
+            const uint64_t b_kstep = b_mn ? (uint64_t) ((UMMA_K * 128) >> 4) : (uint64_t) (UMMA_K >> 4);
             uint32_t stage = 0, phase = 0, acc_stage = 0, acc_phase = 0, sf_buf = 0;
             for (int t = pair; ok && walk.locate(t, gi, m_blk, n_blk); t += num_pairs) {
                 int kb_begin, kb_count;
@@ -204,8 +211,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((PairCfg<BLOCK_N, mo
                         }
                         sf_buf ^= 1;
                     }
-                    const uint64_t a_desc = smem_desc_sw128(smem_u32(smem_a + stage * Cfg::kABytes));
-                    const uint64_t b_desc = smem_desc_sw128(smem_u32(smem_b + stage * Cfg::kBBytes));
+                    const uint32_t a_addr = smem_u32(smem_a + stage * Cfg::kABytes), b_addr = smem_u32(smem_b + stage * Cfg::kBBytes);
+                    const uint64_t a_desc = a_mn ? smem_desc_sw128_mn(a_addr, 16384) : smem_desc_sw128(a_addr);
+                    const uint64_t b_desc = b_mn ? smem_desc_sw128_mn(b_addr, 16384) : smem_desc_sw128(b_addr);
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
                         const uint64_t adv = (uint64_t) ((k * UMMA_K) >> 4);
@@ -215,7 +223,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((PairCfg<BLOCK_N, mo
                                           sfa_cur + (k >> 1) * Cfg::kSfColsHalf, sfb_cur + (k >> 1) * Cfg::kSfColsHalf, accumulate);
                         else if constexpr (MX) mma_mxf8_pair(d_tmem, a_desc + adv, b_desc + adv, idesc_sf_ids(idesc, k, k), sfa_cur, sfb_cur, accumulate);
                         else if constexpr (MODE == GEMM_HP) mma_f16_pair(d_tmem, a_desc + adv, b_desc + adv, idesc, accumulate);
-                        else mma_f8_pair(d_tmem, a_desc + adv, b_desc + adv, idesc, accumulate);
+                        else mma_f8_pair(d_tmem, a_desc + k * a_kstep, b_desc + k * b_kstep, idesc, accumulate);
                     }
                     tc_commit_pair(&empty_bar[stage], 3);  // frees the ring slot in both CTAs
                     if (++stage == kStages) { stage = 0; phase ^= 1; }

@@ -68,6 +68,8 @@ SIGNATURES = {
                                 c_int, c_void_p, c_void_p]),
     "pt_grouped_gemm_variable_k": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int,
                                            c_float, c_int, c_void_p, c_void_p]),
+    "pt_gemm_fp8_mn": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int64, c_int64,
+                               c_int64, c_float, c_void_p, c_void_p]),
     "pt_gemm_fp8": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int64,
                             c_int64, c_int64, c_float, c_int, c_void_p, c_size_t, c_void_p, c_void_p]),
     "pt_gemm_fp8_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int]),

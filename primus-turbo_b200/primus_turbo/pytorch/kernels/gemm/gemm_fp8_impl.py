@@ -105,6 +105,17 @@ def _launch(a_km, a_s, b_km, b_s, out, gran, beta, block_n=0):
     return out
 
 
+def _launch_mn(a_t, a_mn, a_s, b_t, b_mn, b_s, out, gran, beta, M, N, K):
+    """Tensorwise / rowwise with at least one operand read contraction-major in place."""
+    st = nv.status_word(out.device)
+    with nv.on_device(out.device):
+        nv.check(nv.lib().pt_gemm_fp8_mn(nv.ptr(a_t), nv.ptr(a_s), nv.fmt_code(a_t.dtype), a_mn, nv.ptr(b_t), nv.ptr(b_s),
+                                          nv.fmt_code(b_t.dtype), b_mn, nv.ptr(out), nv.src_code(out.dtype), _GRAN[gran], M, N, K,
+                                          float(beta), nv.ptr(st), nv.stream(out.device)), "gemm_fp8_mn")
+    nv.poll_status(out.device)
+    return out
+
+
 def _gemm(a, a_scale_inv, trans_a, b, b_scale_inv, trans_b, out_dtype, trans_c, granularity, out=None, block_n=0,
           accumulate=True):
     """`out` given: accumulate into it (beta = 1), or overwrite it when accumulate is False."""
@@ -134,10 +145,32 @@ def _gemm(a, a_scale_inv, trans_a, b, b_scale_inv, trans_b, out_dtype, trans_c, 
         return _launch_blockwise(a_op, a_desc, a_s, b_op, b_desc, b_s, out, beta, M, N, kc)
     if gran == ScalingGranularity.MX_BLOCKWISE:
         assert not trans_a and trans_b, "MX GEMM takes K-major operands only (trans_a=False, trans_b=True)"
-    a_km = _k_major(a, trans_a)            # [M, K]
-    b_km = _k_major(b, not trans_b)        # [N, K]
     a_s = a_scale_inv.contiguous()
     b_s = b_scale_inv.contiguous()
+    if gran in (ScalingGranularity.TENSORWISE, ScalingGranularity.ROWWISE) and block_n == 0 and (trans_a or not trans_b):
+        # an operand stored contraction-major ([K, rows]) is read in place (MN-major) when its row pitch allows; the
+        # transposed copy below remains for ragged shapes
+        M = a.shape[1] if trans_a else a.shape[0]
+        N = b.shape[0] if trans_b else b.shape[1]
+        kc = a.shape[0] if trans_a else a.shape[1]
+        a_mn, b_mn = int(trans_a), int(not trans_b)
+        ok = (not a_mn or M % 16 == 0) and (not b_mn or N % 16 == 0) and (kc % 16 == 0 or (a_mn and b_mn))
+        a_c, b_c = a.contiguous(), b.contiguous()
+        if ok and a_c.data_ptr() % 16 == 0 and b_c.data_ptr() % 16 == 0:
+            a_f, b_f = a_s.to(torch.float32).reshape(-1), b_s.to(torch.float32).reshape(-1)
+            if gran == ScalingGranularity.ROWWISE:
+                assert a_f.numel() == M and b_f.numel() == N, "rowwise scales must match M and N"
+            beta = 0.0
+            if out is not None:
+                beta = 1.0 if accumulate else 0.0
+                assert out.is_contiguous() and tuple(out.shape) == ((N, M) if trans_c else (M, N))
+            else:
+                out = torch.empty((N, M) if trans_c else (M, N), dtype=out_dtype, device=a.device)
+            if trans_c:
+                return _launch_mn(b_c, b_mn, b_f, a_c, a_mn, a_f, out, gran, beta, N, M, kc)
+            return _launch_mn(a_c, a_mn, a_f, b_c, b_mn, b_f, out, gran, beta, M, N, kc)
+    a_km = _k_major(a, trans_a)            # [M, K]
+    b_km = _k_major(b, not trans_b)        # [N, K]
     if gran in (ScalingGranularity.TENSORWISE, ScalingGranularity.ROWWISE):
         a_s, b_s = a_s.to(torch.float32).reshape(-1), b_s.to(torch.float32).reshape(-1)
         if gran == ScalingGranularity.ROWWISE:

@@ -74,6 +74,33 @@ def test_tensorwise_layouts(mods, trans_a, trans_b, trans_c):
     assert og.rel_frobenius(f32(c), ref) <= 1e-5
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 384, 512), (144, 272, 200), (1040, 528, 1000), (4096, 4096, 2048), (250, 384, 512)])
+@pytest.mark.parametrize("which", ["dgrad", "wgrad"])
+def test_rowwise_backward_layouts_read_in_place(mods, M, N, K, which):
+    """The two backward GEMMs of a rowwise linear with their operands as the forward stored them (MN-major in place when
+    the row counts are multiples of 16, the transposed-copy path for M = 250): dgrad = g [M, N] . w [N, K] contracts over
+    N, wgrad = g^T . x contracts over the tokens; scales run along the non-contracted index of each operand."""
+    qi, gi, nv, SG, _ = mods
+    x, w, g = make((M, K), torch.bfloat16, 41, "outlier"), make((N, K), torch.bfloat16, 42, "weight"), make((M, N), torch.bfloat16, 43)
+    if which == "dgrad":
+        qg, sg = qi.quantize_fp8_rowwise_impl(g, torch.float8_e5m2, -1)          # per token
+        qw, sw = qi.quantize_fp8_rowwise_impl(w, torch.float8_e4m3fn, -2)        # per input feature
+        c = gi.gemm_fp8_impl(qg, sg, False, qw, sw, False, torch.bfloat16, False, SG.ROWWISE)      # [M, K]
+        da = oq.dequantize_fp8(u8(qg), f32(sg).reshape(-1, 1), "e5m2")
+        db = oq.dequantize_fp8(u8(qw), f32(sw).reshape(1, -1), "e4m3")
+        ref, exact = da @ db, f32(g) @ f32(w)
+    else:
+        qx, sx = qi.quantize_fp8_rowwise_impl(x, torch.float8_e4m3fn, -2)        # per input feature
+        qg, sg = qi.quantize_fp8_rowwise_impl(g, torch.float8_e5m2, -2)          # per output feature
+        c = gi.gemm_fp8_impl(qx, sx, True, qg, sg, False, torch.bfloat16, True, SG.ROWWISE)        # [N, K]
+        da = oq.dequantize_fp8(u8(qx), f32(sx).reshape(1, -1), "e4m3")
+        db = oq.dequantize_fp8(u8(qg), f32(sg).reshape(1, -1), "e5m2")
+        ref, exact = db.T @ da, f32(g).T @ f32(x)
+    nv.check_status(c.device)
+    assert og.rel_frobenius(f32(c), ref) <= FP8_TOL
+    assert og.snr_db(f32(c), exact) > 20
+
+
 @pytest.mark.parametrize("M,N,K", [(256, 512, 256), (255, 520, 576), (512, 4096, 1024)])
 def test_rowwise_nt(mods, M, N, K):
     qi, gi, nv, SG, _ = mods
