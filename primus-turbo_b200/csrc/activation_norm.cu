@@ -180,6 +180,45 @@ __global__ void __launch_bounds__(kAnThreads) rmsnorm_fwd_kernel(const T *__rest
     }
 }
 
+// Row statistics alone (rstd), one warp per row, no block-wide barrier: the pass a normalising quantizer needs before it
+// streams the tensor a second time.  The sum of squares is formed in the order rmsnorm_fwd_kernel forms it (the partial
+// sums of its 256 threads, its eight warp reductions, then the eight warp sums in turn: lane l plays threads l, 32 + l,
+// ...), so both kernels give the same rstd bit for bit.
+template <typename T>
+__global__ void __launch_bounds__(kAnThreads) rmsnorm_stats_kernel(const T *__restrict__ x, float eps, int64_t rows, int64_t H,
+                                                                   float *__restrict__ rstd_out) {
+    constexpr int V = 16 / sizeof(T);
+    constexpr int kW = kAnThreads / 32;
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = (int64_t) gridDim.x * kW;
+    for (int64_t r = (int64_t) blockIdx.x * kW + (threadIdx.x >> 5); r < rows; r += warps) {
+        const T *row = x + r * H;
+        float ss[kW];
+#pragma unroll
+        for (int w = 0; w < kW; ++w) ss[w] = 0.f;
+        for (int64_t h0 = 0; h0 < H; h0 += (int64_t) kAnThreads * V) {
+#pragma unroll
+            for (int w = 0; w < kW; ++w) {
+                const int64_t h = h0 + (int64_t) (w * 32 + lane) * V;
+                if (h < H) {
+                    const Vec<T, V> v = ldv<T, V>(row + h);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) { const float f = an_to_f<T>(v.e[i]); ss[w] += f * f; }
+                }
+            }
+        }
+        float total = 0.f;
+#pragma unroll
+        for (int w = 0; w < kW; ++w) {
+            float v = ss[w];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            total += v;
+        }
+        if (lane == 0) rstd_out[r] = rsqrtf(total / (float) H + eps);
+    }
+}
+
 // dx = (dy * g - x_hat * mean(dy * g * x_hat)) * rstd (+ grad of the x + residual sum when given);
 // dgamma partial of this CTA: sum over its rows of dy * x_hat, written to dg_partial[blockIdx.x, :] (fp32).
 template <typename T, int V>
@@ -335,6 +374,12 @@ int pt_rmsnorm_fwd(const void *x, const void *residual, const void *gamma, int d
 #define PT_RMS_FWD(V_, RES_) \
     rmsnorm_fwd_kernel<T, V_, RES_><<<an_grid(rows), kAnThreads, 0, st>>>((const T *) x, (const T *) residual, (const T *) gamma, eps, zero_centered, rows, H, \
                                                                           (T *) y, (T *) x_plus_r, rstd)
+    if (y == nullptr && residual == nullptr && vec) {   // statistics only
+        const int grid = (int) std::min<int64_t>(ceil_div(rows, kAnThreads / 32), (int64_t) sm_count() * 8);
+        PT_SWITCH_SRC(dtype, T, { rmsnorm_stats_kernel<T><<<grid, kAnThreads, 0, st>>>((const T *) x, eps, rows, H, rstd); });
+        PT_LAUNCH_OK();
+        return PT_OK;
+    }
     PT_SWITCH_SRC(dtype, T, {
         constexpr int VW = 16 / sizeof(T);
         if (vec) { if (residual) PT_RMS_FWD(VW, true); else PT_RMS_FWD(VW, false); }
