@@ -179,6 +179,52 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+// Rows of 16-bit elements that fit the registers of one block (up to 4 x 16 bytes per thread = 8192 elements): the row
+// is read once, its |max| is formed on packed pairs, one block-wide exchange gives the scale, and the kept words are
+// scaled and converted.  Same arithmetic as rowwise_last_axis_kernel.
+template <typename T, int FMT>
+__global__ void __launch_bounds__(kThreads) rowwise_row_in_regs_kernel(const T *__restrict__ x, int64_t rows, int64_t len,
+                                                                     uint8_t *__restrict__ q, float *__restrict__ scale_inv) {
+    constexpr int kKeep = 4;
+    __shared__ float s[kThreads / 32];
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T *xr = x + row * len;
+        uint4 keep[kKeep];
+        uint32_t m2 = 0u;
+#pragma unroll
+        for (int k = 0; k < kKeep; ++k) {
+            const int64_t i = ((int64_t) k * kThreads + threadIdx.x) * 8;
+            if (i < len) {
+                keep[k] = __ldg(reinterpret_cast<const uint4 *>(xr + i));
+                m2 = absmax2<T>(absmax2<T>(absmax2<T>(absmax2<T>(m2, keep[k].x), keep[k].y), keep[k].z), keep[k].w);
+            }
+        }
+        m2 = absmax2_done(m2);
+        float m = warp_max(fmaxf(lo_f32<T>(m2), hi_f32<T>(m2)));
+        __syncthreads();   // s may still be read for the previous row
+        if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = m;
+        __syncthreads();
+        m = 0.f;
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) m = fmaxf(m, s[w]);
+        const float scale = scale_from_amax<FMT>(m, kEpsTensor);
+        if (threadIdx.x == 0) scale_inv[row] = __fdiv_rn(1.0f, scale);
+#pragma unroll
+        for (int k = 0; k < kKeep; ++k) {
+            const int64_t i = ((int64_t) k * kThreads + threadIdx.x) * 8;
+            if (i < len) {
+                const uint32_t w[4] = {keep[k].x, keep[k].y, keep[k].z, keep[k].w};
+                uint2 o;
+                o.x = cvt4_fp8<FMT>(mul_sat<FMT>(lo_f32<T>(w[0]), scale), mul_sat<FMT>(hi_f32<T>(w[0]), scale), mul_sat<FMT>(lo_f32<T>(w[1]), scale),
+                                    mul_sat<FMT>(hi_f32<T>(w[1]), scale));
+                o.y = cvt4_fp8<FMT>(mul_sat<FMT>(lo_f32<T>(w[2]), scale), mul_sat<FMT>(hi_f32<T>(w[2]), scale), mul_sat<FMT>(lo_f32<T>(w[3]), scale),
+                                    mul_sat<FMT>(hi_f32<T>(w[3]), scale));
+                *reinterpret_cast<uint2 *>(q + row * len + i) = o;
+            }
+        }
+    }
+}
+
 // Column amax of x [B, M, N]: each block owns a (b, 64-row, 256-column) tile and folds it into
 // amax_bits [B, N] with atomicMax.
 template <typename T>
@@ -340,6 +386,13 @@ int pt_quantize_fp8_rowwise(const void *x, int x_dtype, int64_t B, int64_t M, in
             const int vec_ok = aligned(x, 16) && aligned(q, 8) && (N % 8 == 0);
             const int blocks = (int) std::min<int64_t>(rows, (int64_t) sm_count() * 16);
             PT_SWITCH_FP8(fmt, F, {
+                if constexpr (sizeof(T) == 2) {
+                    if (vec_ok && !scale_opt && N <= (int64_t) kThreads * 8 * 4) {
+                        rowwise_row_in_regs_kernel<T, F><<<blocks, kThreads, 0, st>>>((const T *) x, rows, N, (uint8_t *) q, scale_inv);
+                        PT_LAUNCH_OK();
+                        return PT_OK;
+                    }
+                }
                 rowwise_last_axis_kernel<T, F><<<blocks, kThreads, 0, st>>>((const T *) x, rows, N, vec_ok, scale_opt,
                                                                             (uint8_t *) q, scale_inv);
             });
