@@ -176,7 +176,7 @@ def quantize_records(dev, peaks, copies=4):
     run("blockwise_row_act_8192x4096", [lambda x=x: qi.quant_fp8_blockwise_impl(x, f8, 1) for x in acts], 3 * e + 4 * e // 128,
         "blockwise_tma_kernel<ROW>")
     run("blockwise_dual_act_8192x4096", [lambda x=x: qi.quant_fp8_blockwise_dual_impl(x, f8) for x in acts], 4 * e + 8 * e // 128,
-        "blockwise_tma_kernel<DUAL>")
+        "blockwise_split_kernel")
     run("blockwise_weight_14336x4096", [lambda w=w: qi.quant_fp8_blockwise_for_weight_impl(w, f8) for w in wts],
         3 * ew + 4 * ew // 16384, "blockwise_tma_kernel<WEIGHT>")
     run("mxfp8_row_act_8192x4096", [lambda x=x: qi.quantize_mxfp8_impl(x, f8, 1, 32) for x in acts], 3 * e + e // 32,
@@ -201,7 +201,7 @@ def quantize_records(dev, peaks, copies=4):
     e4 = 32768 * C4["hidden"]
     e4_pad = int(((lens + 127) // 128 * 128).sum()) * C4["hidden"]
     run("blockwise_segment_m_32768x7168_g64", [lambda x=x: qi.quant_fp8_blockwise_segment_m_row_col_impl(x, f8, 128, lens_t, offs) for x in xs],
-        2 * e4 + e4 + e4_pad + 4 * e4 // 128 + 4 * e4_pad // 128, "blockwise_tma_kernel<SEGMENT>")
+        2 * e4 + e4 + e4_pad + 4 * e4 // 128 + 4 * e4_pad // 128, "blockwise_split_kernel<segment-M>")
     del xs
     # C5: grouped MXFP4 dual quantization (row copy plain, transposed copy with the 16-point Hadamard transform)
     lens5 = dirichlet_group_lens(C5["G"], C5["rows"], seed=C5["seed"])
@@ -385,3 +385,54 @@ def mxfp4_c5_sweep(dev, peaks, tokens_per_expert=(128, 512, 2048, 8192, 16384)):
         out[str(t)] = {"fwd_tflops": rec["fwd"]["tflops"], "dgrad_tflops": rec["dgrad"]["tflops"], "wgrad_tflops": rec["wgrad"]["tflops"]}
         torch.cuda.empty_cache()
     return out
+
+
+# ---------------------------------------------------------------------------------------------- small cases for profiling
+def _small_case(name, args):
+    """Runs one kernel a few times on a small input (larger than L2, a few hundred MB on the device): the command line an
+    ncu capture of that kernel wraps.  python bench_configs.py <case> [sizes...]"""
+    import primus_turbo.pytorch  # noqa: F401  (loads the library)
+    from primus_turbo.pytorch.core.low_precision import ScalingGranularity as SG
+    from primus_turbo.pytorch.kernels.grouped_gemm import grouped_gemm_fp8_impl as ggi
+    from primus_turbo.pytorch.kernels.quantization import quantization_impl as qi
+    dev = torch.device("cuda", 0)
+    f8, f5 = torch.float8_e4m3fn, torch.float8_e5m2
+    if name in ("mx_dual", "mxfp4_dual", "blockwise_dual", "swiglu_mx_dual"):
+        M, N = (int(args[0]), int(args[1])) if len(args) >= 2 else (8192, 4096)
+        xs = [randn_bf16((M, N * (2 if name == "swiglu_mx_dual" else 1)), 1.0, i, dev) for i in range(3)]
+        probs = torch.rand(M, device=dev)
+        for i in range(6):
+            x = xs[i % 3]
+            if name == "mx_dual":
+                qi.quantize_mxfp8_impl(x, f8, None, 32, True)
+            elif name == "mxfp4_dual":
+                qi.quantize_mxfp4_impl(x, torch.float4_e2m1fn_x2, None, 32, True)
+            elif name == "blockwise_dual":
+                qi.quant_fp8_blockwise_dual_impl(x, f8)
+            else:
+                qi.glu_quantize_mx_impl(x, probs, None, "silu", f8, fused=True)
+    elif name == "blockwise_grouped":   # forward + variable-K wgrad of G equal groups, C4 gate_up widths
+        G, per = (int(args[0]), int(args[1])) if len(args) >= 2 else (64, 512)
+        N, K = C4["inter2"], C4["hidden"]
+        lens = np.full(G, per, dtype=np.int64)
+        lens_t, offs = offsets_of(lens, dev)
+        x = randn_bf16((G * per, K), 1.0, 1, dev)
+        dy = randn_bf16((G * per, N), 1e-3, 2, dev)
+        w = randn_bf16((G, N, K), 0.02, 3, dev)
+        a_row, a_col, a_s_row, a_s_col, plens, poffs = qi.quant_fp8_blockwise_segment_m_row_col_impl(x, f8, 128, lens_t, offs)
+        g_row, g_col, g_s_row, g_s_col, _, _ = qi.quant_fp8_blockwise_segment_m_row_col_impl(dy, f5, 128, lens_t, offs)
+        w_q, w_s = qi.quant_fp8_blockwise_for_weight_impl(w, f8)
+        for _ in range(2):
+            ggi.grouped_gemm_fp8_impl(a_row, w_q, a_s_row, w_s, lens_t, offs, False, True, torch.bfloat16, SG.BLOCKWISE)
+            ggi.grouped_gemm_fp8_variable_k_impl(a_col, g_col, a_s_col, g_s_col, plens, poffs, True, False, True, torch.bfloat16, SG.BLOCKWISE)
+    else:
+        raise SystemExit(f"unknown case {name!r}: mx_dual, mxfp4_dual, blockwise_dual, swiglu_mx_dual [M N]; blockwise_grouped [G rows]")
+    torch.cuda.synchronize()
+    print("ok", name, *args)
+
+
+if __name__ == "__main__":
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "primus-turbo_b200"))
+    _small_case(sys.argv[1] if len(sys.argv) > 1 else "", sys.argv[2:])

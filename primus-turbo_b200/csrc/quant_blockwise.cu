@@ -475,6 +475,230 @@ __global__ void __launch_bounds__(kBqThreads, kBqCtasPerSm)
     }
 }
 
+// ------------------------------------------------------------------------------------------------ warp-split form
+// Dual (row-wise + column-wise) and segment-M quantization of 16-bit inputs.  Same tiles, TMA ring, tile descriptors and
+// dynamic schedule as blockwise_tma_kernel, but the eight consumer warps are split by output so that no shuffle and no
+// CTA-wide barrier is needed:
+//   * four warps produce the row-wise copy, one thread per tile row: the 128 elements of the row are read as sixteen
+//     16-byte chunks (conflict-free under the 128-byte swizzle), the row maximum is local to the thread, the 128 output
+//     bytes go to a swizzled staging tile that one bulk tensor store writes (whole tiles; a tile cut by a group's end
+//     is stored row by row);
+//   * four warps produce the column-wise copy, one thread per column pair and 64-row band: 64 rows x 2 columns in
+//     registers, the two bands of a column meet through 512 bytes of shared memory (one named barrier among these four
+//     warps), the output bytes are staged row-major and written by one bulk tensor store.
+// Arithmetic is that of blockwise_tile_kernel (same scale, clamp and convert), so all three forms write the same bytes.
+constexpr int kBsStages = 2;
+constexpr int kBsCtasPerSm = 2;
+constexpr int kBsGroupThreads = 128;
+constexpr int kBsThreads = 32 + 2 * kBsGroupThreads;
+constexpr int kBsStageOutBytes = kBlk * kBlk;   // one staged fp8 tile
+constexpr int kBsSmemBytes = kBsStages * kBqTileBytes + 2 * kBsStageOutBytes + 1024 + 256;
+
+template <typename T, int FMT, bool SEG>
+__global__ void __launch_bounds__(kBsThreads, kBsCtasPerSm)
+    blockwise_split_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_qrow,
+                           const __grid_constant__ CUtensorMap tmap_qcol, BqArgs a) {
+    using namespace sm100;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *row_stage = smem + kBsStages * kBqTileBytes;
+    uint8_t *col_stage = row_stage + kBsStageOutBytes;
+    uint64_t *full_bar = reinterpret_cast<uint64_t *>(col_stage + kBsStageOutBytes);
+    uint64_t *empty_bar = full_bar + kBsStages;
+    __shared__ uint32_t s_cmax[2][kBsGroupThreads];   // packed |max| of each (64-row band, column pair): index 64 band + pair
+    __shared__ __align__(16) BqTileDesc s_desc[kBsStages];
+    __shared__ int s_abort;
+    volatile int *abort_flag = &s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int st = 0; st < kBsStages; ++st) {
+            mbar_init(&full_bar[st], 1);
+            mbar_init(&empty_bar[st], 2 * kBsGroupThreads / 32);
+        }
+        fence_barrier_init();
+        prefetch_tmap(&tmap);
+        prefetch_tmap(&tmap_qrow);
+        prefetch_tmap(&tmap_qcol);
+    }
+    __shared__ int s_gtab[SEG ? 2 * (kBqMaxGroups + 1) : 1];
+    __syncthreads();
+    if constexpr (SEG) {
+        for (int i = threadIdx.x; i <= a.seg.num_groups; i += blockDim.x) {
+            s_gtab[i] = (int) a.seg.padded_offs[i];
+            s_gtab[(kBqMaxGroups + 1) + i] = (int) a.seg.group_offs[i];
+        }
+        __syncthreads();
+    }
+    bool ok = true;
+    const int64_t n_blocks = a.tiles_n;
+    const int64_t m_blocks = (a.M + kBlk - 1) / kBlk;
+
+    if (warp == 0) {
+        // ================================================================ producer: tile coordinates + TMA loads
+        if (lane == 0) {
+            const int64_t m_padded = SEG ? s_gtab[a.seg.num_groups] : 0;
+            uint32_t stage = 0, phase = 0;
+            for (uint32_t t = blockIdx.x; t < (uint32_t) a.total_tiles; t = tile_sched_next(a.sched_slot, t)) {
+                const uint32_t tm = t / (uint32_t) a.tiles_n;
+                BqTileDesc d{0, (int) tm, (int) (t - tm * (uint32_t) a.tiles_n), (int) tm * kBlk, kBlk, 0, 0, 0};
+                if constexpr (SEG) {
+                    const int64_t out_row0 = (int64_t) tm * kBlk;
+                    if (out_row0 >= m_padded) continue;
+                    const int *poffs = s_gtab, *goffs = s_gtab + (kBqMaxGroups + 1);
+                    int lo = 0, hi = a.seg.num_groups - 1;  // last group g with padded_offs[g] <= out_row0 (empty groups skipped)
+                    while (lo < hi) {
+                        const int mid = (lo + hi + 1) >> 1;
+                        if (poffs[mid] <= out_row0) lo = mid; else hi = mid - 1;
+                    }
+                    d.in_row0 = goffs[lo] + (int) (out_row0 - poffs[lo]);
+                    d.n_valid = (int) max((int64_t) 0, min((int64_t) kBlk, min((int64_t) goffs[lo + 1], a.M) - d.in_row0));
+                }
+                if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
+                s_desc[stage] = d;
+                mbar_arrive_expect_tx(&full_bar[stage], kBqTileBytes);
+                uint8_t *dst = smem + stage * kBqTileBytes;
+                tma_load_3d(dst, &tmap, &full_bar[stage], d.col_blk * kBlk, d.in_row0, 0);
+                tma_load_3d(dst + kBqTileBytes / 2, &tmap, &full_bar[stage], d.col_blk * kBlk + 64, d.in_row0, 0);
+                if (++stage == kBsStages) { stage = 0; phase ^= 1; }
+            }
+            if (ok && (ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) {   // the terminal descriptor
+                s_desc[stage].col_blk = -1;
+                mbar_arrive(&full_bar[stage]);
+            }
+            tile_sched_done(a.sched_slot);
+        }
+    } else if (warp <= kBsGroupThreads / 32) {
+        // ================================================================ row-wise copy: thread = tile row
+        const int row = threadIdx.x - 32;
+        uint32_t stage = 0, phase = 0;
+        while (true) {
+            if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
+            const int4 d0 = *reinterpret_cast<const int4 *>(&s_desc[stage]);
+            if (d0.z < 0) break;
+            const int pid_m = d0.y, col_blk = d0.z, in_row0 = d0.w;
+            const int n_valid = SEG ? s_desc[stage].n_valid : kBlk;
+            uint32_t w[64];
+            {
+                const uint8_t *rp = smem + stage * kBqTileBytes + row * 128;
+#pragma unroll
+                for (int b = 0; b < 2; ++b)
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const uint4 v = *reinterpret_cast<const uint4 *>(rp + b * (kBqTileBytes / 2) + ((c ^ (row & 7)) << 4));
+                        w[32 * b + 4 * c] = v.x; w[32 * b + 4 * c + 1] = v.y; w[32 * b + 4 * c + 2] = v.z; w[32 * b + 4 * c + 3] = v.w;
+                    }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[stage]);  // this warp no longer reads the stage
+            if (++stage == kBsStages) { stage = 0; phase ^= 1; }
+            uint32_t m2 = 0u;
+#pragma unroll
+            for (int k = 0; k < 64; ++k) m2 = absmax2<T>(m2, w[k]);
+            m2 = absmax2_done(m2);
+            const float scale = scale_from_amax<FMT>(fmaxf(lo_f32<T>(m2), hi_f32<T>(m2)), kEpsBlock);
+            const int64_t in_m = (int64_t) in_row0 + row;
+            const int64_t n0 = (int64_t) col_blk * kBlk;
+            const bool live = row < n_valid && in_m < a.M;
+            if (live) {
+                const float inv = __fdiv_rn(1.0f, scale);
+                if constexpr (SEG) a.s_row[(int64_t) col_blk * a.M + in_m] = inv;  // transposed [N blocks, M]
+                else a.s_row[in_m * n_blocks + col_blk] = inv;
+            }
+            // a whole tile leaves through the staging tile and one bulk store; one cut by the end of a group (the rows
+            // after it belong to other tiles) is stored row by row
+            const bool whole = !SEG || n_valid == kBlk;
+            if (whole) {
+                if (row == 0) bulk_wait_read_all();   // the previous tile's store has read the staging tile
+                asm volatile("bar.sync 1, %0;" ::"n"(kBsGroupThreads) : "memory");
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                uint32_t o[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint32_t x0 = w[8 * j + 2 * k], x1 = w[8 * j + 2 * k + 1];
+                    o[k] = cvt4_fp8<FMT>(mul_sat<FMT>(lo_f32<T>(x0), scale), mul_sat<FMT>(hi_f32<T>(x0), scale), mul_sat<FMT>(lo_f32<T>(x1), scale),
+                                         mul_sat<FMT>(hi_f32<T>(x1), scale));
+                }
+                if (whole) *reinterpret_cast<uint4 *>(row_stage + row * 128 + ((j ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                else if (live && n0 + 16 * j < a.N) *reinterpret_cast<uint4 *>(a.q_row + in_m * a.N + n0 + 16 * j) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+            if (whole) {
+                fence_proxy_async_smem();
+                asm volatile("bar.sync 1, %0;" ::"n"(kBsGroupThreads) : "memory");
+                if (row == 0) {
+                    tma_store_2d(&tmap_qrow, row_stage, (int) n0, in_row0);   // clipped at the matrix edges
+                    bulk_commit_group();
+                }
+            }
+        }
+        if (row == 0) bulk_wait_read_all();
+    } else {
+        // ================================================================ column-wise copy: thread = (64-row band, column pair)
+        const int ct = threadIdx.x - 32 - kBsGroupThreads;
+        const int band = ct >> 6, pair = ct & 63;
+        const int box = pair >> 5, chunk = (pair & 31) >> 2, sub = (pair & 3) << 2;
+        uint32_t stage = 0, phase = 0, tile_i = 0;
+        while (true) {
+            if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
+            const int4 d0 = *reinterpret_cast<const int4 *>(&s_desc[stage]);
+            if (d0.z < 0) break;
+            const int pid_m = d0.y, col_blk = d0.z;
+            const int n_valid = SEG ? s_desc[stage].n_valid : kBlk;
+            uint32_t w[64];
+            {
+                const uint8_t *cp = smem + stage * kBqTileBytes + box * (kBqTileBytes / 2) + band * 64 * 128 + sub;
+#pragma unroll
+                for (int r = 0; r < 64; ++r) {   // (64 band + r) % 8 == r % 8; a warp reads one 128-byte box row: no bank conflict
+                    const uint32_t v = *reinterpret_cast<const uint32_t *>(cp + r * 128 + ((chunk ^ (r & 7)) << 4));
+                    w[r] = (!SEG || band * 64 + r < n_valid) ? v : 0u;   // rows past the group's end count (and are written) as zeros
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[stage]);
+            if (++stage == kBsStages) { stage = 0; phase ^= 1; }
+            const int buf = tile_i & 1;
+            ++tile_i;
+            uint32_t m2 = 0u;
+#pragma unroll
+            for (int r = 0; r < 64; ++r) m2 = absmax2<T>(m2, w[r]);
+            s_cmax[buf][ct] = m2;   // [band][pair] flattened: ct = 64 band + pair
+            if (ct == 0) bulk_wait_read_all();   // the previous tile's store has read the staging tile
+            asm volatile("bar.sync 2, %0;" ::"n"(kBsGroupThreads) : "memory");
+            m2 = absmax2_done(absmax2<T>(m2, s_cmax[buf][ct ^ 64]));
+            const float sc0 = scale_from_amax<FMT>(lo_f32<T>(m2), kEpsBlock), sc1 = scale_from_amax<FMT>(hi_f32<T>(m2), kEpsBlock);
+            const int64_t n0 = (int64_t) col_blk * kBlk;
+            const int64_t gc = n0 + 2 * pair;
+            if (band == 0 && gc < a.N)
+                *reinterpret_cast<float2 *>(a.s_col + (int64_t) pid_m * a.N + gc) = make_float2(__fdiv_rn(1.0f, sc0), __fdiv_rn(1.0f, sc1));
+            // staged row-major: byte (row, column c) at row * 128 + swizzled chunk c / 16 + c % 16
+            {
+                const int c = 2 * pair;
+                uint8_t *sp = col_stage + band * 64 * 128 + (c & 15);
+                const int oc = c >> 4;
+#pragma unroll
+                for (int r = 0; r < 64; ++r) {
+                    const uint16_t o = cvt2_fp8<FMT>(mul_sat<FMT>(lo_f32<T>(w[r]), sc0), mul_sat<FMT>(hi_f32<T>(w[r]), sc1));
+                    *reinterpret_cast<uint16_t *>(sp + r * 128 + ((oc ^ (r & 7)) << 4)) = o;
+                }
+            }
+            fence_proxy_async_smem();
+            asm volatile("bar.sync 2, %0;" ::"n"(kBsGroupThreads) : "memory");
+            if (ct == 0) {
+                tma_store_2d(&tmap_qcol, col_stage, (int) n0, pid_m * kBlk);
+                bulk_commit_group();
+            }
+        }
+        if (ct == 0) bulk_wait_read_all();
+    }
+    if (!ok || *abort_flag) {
+        if (a.status && lane == 0) atomicExch(a.status, (int) PT_ERR_TIMEOUT);
+        __nanosleep(100000);  // let a copy still in flight land before the shared memory is released
+    }
+}
+
 // y = float(q) * s for the three block-scale layouts
 template <typename T, int FMT>
 __global__ void __launch_bounds__(256) dequant_blockwise_kernel(const uint8_t *__restrict__ q,
@@ -678,6 +902,29 @@ static int launch_tile(const void *x, int x_dtype, int64_t B, int64_t m_tiles, i
         CUtensorMap tmap;
         int rc = make_tmap_u16_3d(&tmap, x, B, M, N, kBlk);
         if (rc != PT_OK) return rc;
+        if constexpr (MODE == MODE_DUAL || MODE == MODE_SEGMENT) {
+            // both copies of a 16-bit input: the warp-split kernel (PT_BW_QUANT_NO_SPLIT=1 keeps the older form)
+            if (B == 1 && aligned(s_col, 8) && getenv("PT_BW_QUANT_NO_SPLIT") == nullptr) {
+                constexpr bool kSegK = MODE == MODE_SEGMENT;
+                CUtensorMap trow, tcol;
+                if ((rc = make_tmap_bytes(&trow, q_row, M, N, N, kBlk)) != PT_OK) return rc;
+                if ((rc = make_tmap_bytes(&tcol, q_col, kSegK ? m_tiles * kBlk : M, N, N, kBlk)) != PT_OK) return rc;
+                BqArgs a{M, N, (int) tiles_n, (int) m_tiles, total_tiles, (uint8_t *) q_row, (uint8_t *) q_col, s_row, s_col, seg, default_status(),
+                         tile_sched_acquire((cudaStream_t) stream)};
+                const int sgrid = (int) std::min<int64_t>(total_tiles, (int64_t) sm_count() * kBsCtasPerSm);
+#define PT_BS_LAUNCH(T_)                                                                                           \
+                PT_SWITCH_FP8(fmt, F, {                                                                            \
+                    auto kern = blockwise_split_kernel<T_, F, kSegK>;                                              \
+                    PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBsSmemBytes)); \
+                    kern<<<sgrid, kBsThreads, kBsSmemBytes, (cudaStream_t) stream>>>(tmap, trow, tcol, a);         \
+                })
+                if (x_dtype == PT_BF16) { PT_BS_LAUNCH(__nv_bfloat16); } else { PT_BS_LAUNCH(__half); }
+#undef PT_BS_LAUNCH
+                PT_LAUNCH_OK();
+                tile_sched_release(a.sched_slot, (cudaStream_t) stream);
+                return PT_OK;
+            }
+        }
         BqArgs a{M, N, (int) tiles_n, (int) m_tiles, total_tiles, (uint8_t *) q_row, (uint8_t *) q_col, s_row, s_col, seg, default_status(), tile_sched_acquire((cudaStream_t) stream)};
         const int tma_grid = (int) std::min<int64_t>(total_tiles, (int64_t) sm_count() * kBqCtasPerSm);
 #define PT_BQ_LAUNCH(T_)                                                                                           \
