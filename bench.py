@@ -199,6 +199,7 @@ def _sub_records(args, dev, peaks, world, rank):
         attempt("grouped_blockwise_c4", lambda: bc.grouped_blockwise_c4(dev, peaks))
         attempt("grouped_mxfp4_c5", lambda: bc.grouped_mxfp4_c5(dev, peaks))
         attempt("grouped_mxfp4_c5_sweep", lambda: bc.mxfp4_c5_sweep(dev, peaks))
+        attempt("streaming_f2_f4", lambda: bc.streaming_records(dev, peaks))
     else:
         import bench_sharded as bs
         attempt("expert_sharded_c4", lambda: bs.expert_sharded_c4(dev, peaks, world, rank))

@@ -387,6 +387,50 @@ def mxfp4_c5_sweep(dev, peaks, tokens_per_expert=(128, 512, 2048, 8192, 16384)):
     return out
 
 
+# ---------------------------------------------------------------------------------------------- rows around the GEMMs
+def streaming_records(dev, peaks):
+    """Gated activation, RMSNorm and MoE permutation kernels on C4-like tensors; GB/s of algorithmic bytes."""
+    from primus_turbo.pytorch.kernels.activation.glu_impl import glu_bwd_with_probs, glu_fwd_with_probs
+    from primus_turbo.pytorch.kernels.moe import permutation_impl as pm
+    from primus_turbo.pytorch.kernels.normalization import rmsnorm_impl as rn
+    out = {}
+
+    def run(name, fns, nbytes, kernel):
+        out[name] = _hbm_rec(nbytes, time_cuda_rotating(fns), peaks, kernel)
+
+    rows, inter = 32768, C4["inter"]
+    xs = [randn_bf16((rows, 2 * inter), 1.0, 90 + i, dev) for i in range(3)]
+    g = randn_bf16((rows, inter), 1.0, 93, dev)
+    probs = torch.rand(rows, device=dev, generator=torch.Generator(device=dev).manual_seed(94))
+    eo = rows * inter
+    run(f"swiglu_fwd_{rows}x{inter}", [lambda x=x: glu_fwd_with_probs(x, probs, None, "silu") for x in xs], 6 * eo + 4 * rows, "glu_fwd_kernel")
+    run(f"swiglu_bwd_{rows}x{inter}", [lambda x=x: glu_bwd_with_probs(g, x, probs, None, "silu") for x in xs], 10 * eo + 8 * rows, "glu_bwd_kernel")
+    del xs, g
+    tokens, hidden = 16384, C4["hidden"]
+    hs = [randn_bf16((tokens, hidden), 1.0, 95 + i, dev) for i in range(3)]
+    gamma = randn_bf16((hidden,), 1.0, 98, dev)
+    e = tokens * hidden
+    run(f"rmsnorm_fwd_{tokens}x{hidden}", [lambda x=x: rn.rmsnorm_fwd_impl(x, gamma, 1e-6) for x in hs], 4 * e + 4 * tokens, "rmsnorm_fwd_kernel")
+    y, x2, rstd = rn.rmsnorm_fwd_impl(hs[0], gamma, 1e-6)
+    run(f"rmsnorm_bwd_{tokens}x{hidden}", [lambda x=x: rn.rmsnorm_bwd_impl(y, x, gamma, rstd) for x in hs], 6 * e, "rmsnorm_bwd_kernel + rmsnorm_dgamma_kernel")
+    del y, x2
+    # top-8 routing of 16384 tokens over 256 experts (C4): 131072 permuted rows of 7168 bf16
+    E, topk = C4["G"], 8
+    gen = torch.Generator(device=dev).manual_seed(99)
+    scores = torch.rand(tokens, E, device=dev, generator=gen)
+    routing = torch.zeros(tokens, E, dtype=torch.bool, device=dev)
+    routing.scatter_(1, scores.topk(topk, dim=1).indices, True)
+    row_id_map, _ = pm.make_row_id_map(routing, tokens, E)
+    n_out = tokens * topk
+    run(f"moe_row_id_map_{tokens}x{E}", [lambda: pm.make_row_id_map(routing, tokens, E) for _ in range(2)], tokens * E * (1 + 8) + 4 * tokens, "moe_rank / offs / compact kernels")
+    run(f"moe_permute_{tokens}x{hidden}_top{topk}", [lambda x=x: pm.permute_with_mask_map(x, row_id_map, None, None, tokens, E, n_out, hidden) for x in hs],
+        2 * e + 2 * n_out * hidden, "moe_permute_kernel")
+    perm = pm.permute_with_mask_map(hs[0], row_id_map, None, None, tokens, E, n_out, hidden)[0]
+    run(f"moe_unpermute_{tokens}x{hidden}_top{topk}", [lambda: pm.unpermute_with_mask_map(perm, row_id_map, None, None, tokens, E, hidden) for _ in range(2)],
+        2 * n_out * hidden + 2 * e, "moe_unpermute_kernel")
+    return out
+
+
 # ---------------------------------------------------------------------------------------------- small cases for profiling
 def _small_case(name, args):
     """Runs one kernel a few times on a small input (larger than L2, a few hundred MB on the device): the command line an

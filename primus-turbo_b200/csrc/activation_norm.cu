@@ -6,9 +6,11 @@
 // the mean square).  The reference's forms: primus_turbo/pytorch/ops/activation.py:23-80 with
 // triton/activation/{swiglu,geglu}_kernel.py, and ops/normalization.py with triton/normalization/rmsnorm_kernel.py.
 #include <algorithm>
+#include <cstdlib>
 
 #include "act_math.cuh"
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace ptb {
 
@@ -312,6 +314,87 @@ __global__ void __launch_bounds__(kAnThreads, 2) rmsnorm_bwd_kernel(const T *__r
     }
 }
 
+// The same with the rows staged through shared memory: while a row is processed, the next one (x and dy) is already on
+// its way into the other half of a double buffer (16-byte cp.async; a thread reads back only what it copied itself, so
+// the buffers need no barrier).  For rows of up to 4 vectors per thread (8192 16-bit elements).  Element assignment and
+// summation order are those of rmsnorm_bwd_kernel: both give the same bits.
+template <typename T>
+__global__ void __launch_bounds__(kAnThreads, 3) rmsnorm_bwd_staged_kernel(const T *__restrict__ dy, const T *__restrict__ dxpr, const T *__restrict__ x,
+                                                                        const T *__restrict__ gamma, const float *__restrict__ rstd_in,
+                                                                        int zero_centered, int64_t rows, int64_t H, T *__restrict__ dx,
+                                                                        float *__restrict__ dg_partial) {
+    constexpr int V = 16 / sizeof(T);
+    constexpr int kKeep = 4;
+    extern __shared__ __align__(16) uint8_t an_smem[];   // [2][x row | dy row]
+    __shared__ float s_red[kAnThreads / 32];
+    const int64_t row_bytes = H * (int64_t) sizeof(T);
+    auto sx = [&](int b) { return reinterpret_cast<T *>(an_smem + (int64_t) b * 2 * row_bytes); };
+    auto sd = [&](int b) { return reinterpret_cast<T *>(an_smem + (int64_t) b * 2 * row_bytes + row_bytes); };
+    auto issue = [&](int64_t r, int b) {
+#pragma unroll
+        for (int k = 0; k < kKeep; ++k) {
+            const int64_t h = ((int64_t) k * kAnThreads + threadIdx.x) * V;
+            if (h < H) {
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sm100::smem_u32(sx(b) + h)), "l"(x + r * H + h) : "memory");
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sm100::smem_u32(sd(b) + h)), "l"(dy + r * H + h) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float dgr[kKeep][V];
+#pragma unroll
+    for (int k = 0; k < kKeep; ++k)
+#pragma unroll
+        for (int i = 0; i < V; ++i) dgr[k][i] = 0.f;
+    const float zc = zero_centered ? 1.0f : 0.0f;
+    int b = 0;
+    if ((int64_t) blockIdx.x < rows) issue(blockIdx.x, 0);
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x, b ^= 1) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (r + gridDim.x < rows) issue(r + gridDim.x, b ^ 1);
+        const float rstd = rstd_in[r];
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < kKeep; ++k) {
+            const int64_t h = ((int64_t) k * kAnThreads + threadIdx.x) * V;
+            if (h < H) {
+                const Vec<T, V> xv = ldv_plain<T, V>(sx(b) + h), dv = ldv_plain<T, V>(sd(b) + h), gr = ldv<T, V>(gamma + h);
+#pragma unroll
+                for (int i = 0; i < V; ++i) acc += an_to_f<T>(dv.e[i]) * (an_to_f<T>(gr.e[i]) + zc) * (an_to_f<T>(xv.e[i]) * rstd);
+            }
+        }
+        const float m = block_sum(acc, s_red) / (float) H;
+#pragma unroll
+        for (int k = 0; k < kKeep; ++k) {
+            const int64_t h = ((int64_t) k * kAnThreads + threadIdx.x) * V;
+            if (h < H) {
+                const Vec<T, V> xv = ldv_plain<T, V>(sx(b) + h), dv = ldv_plain<T, V>(sd(b) + h), gr = ldv<T, V>(gamma + h);
+                Vec<T, V> pr = {};
+                if (dxpr != nullptr) pr = ldv<T, V>(dxpr + r * H + h);
+                Vec<T, V> o;
+#pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    const float x_hat = an_to_f<T>(xv.e[i]) * rstd, d = an_to_f<T>(dv.e[i]);
+                    float v = (d * (an_to_f<T>(gr.e[i]) + zc) - x_hat * m) * rstd;
+                    if (dxpr != nullptr) v += an_to_f<T>(pr.e[i]);
+                    o.e[i] = an_from_f<T>(v);
+                    dgr[k][i] += d * x_hat;
+                }
+                stv<T, V>(dx + r * H + h, o);
+            }
+        }
+    }
+    float *dg = dg_partial + (int64_t) blockIdx.x * H;
+#pragma unroll
+    for (int k = 0; k < kKeep; ++k) {
+        const int64_t h = ((int64_t) k * kAnThreads + threadIdx.x) * V;
+        if (h < H) {
+#pragma unroll
+            for (int i = 0; i < V; ++i) dg[h + i] = dgr[k][i];
+        }
+    }
+}
+
 // dgamma[h] = sum over parts of dg_partial[part, h]
 template <typename T>
 __global__ void __launch_bounds__(256) rmsnorm_dgamma_kernel(const float *__restrict__ dg_partial, int parts, int64_t H, T *__restrict__ dgamma) {
@@ -390,7 +473,7 @@ int pt_rmsnorm_fwd(const void *x, const void *residual, const void *gamma, int d
     return PT_OK;
 }
 
-int pt_rmsnorm_bwd_parts(int64_t rows) { return (int) std::min<int64_t>(std::max<int64_t>(rows, 1), (int64_t) sm_count() * 2); }
+int pt_rmsnorm_bwd_parts(int64_t rows) { return (int) std::min<int64_t>(std::max<int64_t>(rows, 1), (int64_t) sm_count() * 3); }
 
 int pt_rmsnorm_bwd(const void *dy, const void *dxpr, const void *x, const void *gamma, const float *rstd, int dtype, int zero_centered, int64_t rows,
                    int64_t H, void *dx, void *dgamma, float *dg_partial, int parts, void *stream) {
@@ -401,7 +484,13 @@ int pt_rmsnorm_bwd(const void *dy, const void *dxpr, const void *x, const void *
     cudaStream_t st = (cudaStream_t) stream;
     PT_SWITCH_SRC(dtype, T, {
         constexpr int VW = 16 / sizeof(T);
-        if (vec)
+        if (vec && H <= (int64_t) kAnThreads * VW * 4 && getenv("PT_RMSNORM_BWD_NO_STAGE") == nullptr) {
+            const int smem = (int) (4 * H * (int64_t) sizeof(T));
+            auto kern = rmsnorm_bwd_staged_kernel<T>;
+            PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            kern<<<parts, kAnThreads, smem, st>>>((const T *) dy, (const T *) dxpr, (const T *) x, (const T *) gamma, rstd, zero_centered, rows, H, (T *) dx,
+                                                  dg_partial);
+        } else if (vec)
             rmsnorm_bwd_kernel<T, VW><<<parts, kAnThreads, 0, st>>>((const T *) dy, (const T *) dxpr, (const T *) x, (const T *) gamma, rstd, zero_centered, rows,
                                                                     H, (T *) dx, dg_partial);
         else
