@@ -94,6 +94,101 @@ __global__ void __launch_bounds__(256) moe_compact_kernel(const int *__restrict_
     if (lane == 0) row[2 * E] = n;
 }
 
+// ---- the same map built from row-major passes (E <= 1024): thread = expert, so every access to the [T, E] routing map and
+// every intermediate is contiguous across a warp.
+//   1. per block of 32 tokens, the number of tokens routed to each expert;
+//   2. per expert, the exclusive scan of those counts over the blocks (and the expert's total);
+//   3. per block again: ranks of its 32 tokens (expert offset + block offset + running count) into shared memory, then one
+//      warp per token compacts its routed experts into the row layout.
+constexpr int kMapTokens = 32;
+
+template <typename MapT>
+__global__ void __launch_bounds__(1024) moe_block_count_kernel(const MapT *__restrict__ routing_map, int T, int E, int *__restrict__ block_counts) {
+    const int e = threadIdx.x;
+    if (e >= E) return;
+    const int t0 = blockIdx.x * kMapTokens;
+    int c = 0;
+#pragma unroll 8
+    for (int i = 0; i < kMapTokens; ++i)
+        if (t0 + i < T) c += routing_map[(int64_t) (t0 + i) * E + e] != 0;
+    block_counts[(int64_t) blockIdx.x * E + e] = c;
+}
+
+// grid: groups of 32 experts; block: (32 experts, 32 segments of consecutive blocks)
+__global__ void __launch_bounds__(1024) moe_block_scan_kernel(int *__restrict__ block_counts, int nblocks, int E, int64_t *__restrict__ counts) {
+    __shared__ int s_seg[32][33];
+    const int e = blockIdx.x * 32 + threadIdx.x, seg = threadIdx.y;
+    const int per = (nblocks + 31) / 32, b0 = seg * per, b1 = min(nblocks, b0 + per);
+    int sum = 0;
+    if (e < E)
+        for (int b = b0; b < b1; ++b) sum += block_counts[(int64_t) b * E + e];
+    s_seg[seg][threadIdx.x] = sum;
+    __syncthreads();
+    int before = 0, total = 0;
+    for (int k = 0; k < 32; ++k) {
+        const int v = s_seg[k][threadIdx.x];
+        if (k < seg) before += v;
+        total += v;
+    }
+    if (e < E) {
+        int run = before;
+        for (int b = b0; b < b1; ++b) {
+            const int v = block_counts[(int64_t) b * E + e];
+            block_counts[(int64_t) b * E + e] = run;   // exclusive prefix over the blocks, in place
+            run += v;
+        }
+        if (seg == 0) counts[e] = total;
+    }
+}
+
+template <typename MapT>
+__global__ void __launch_bounds__(1024) moe_block_map_kernel(const MapT *__restrict__ routing_map, int T, int E, const int *__restrict__ block_offs,
+                                                             const int64_t *__restrict__ counts, int *__restrict__ row_id_map) {
+    extern __shared__ int s_rank[];   // [kMapTokens][E]
+    __shared__ int s_warp[32];
+    const int e = threadIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    // first destination row of every expert: exclusive scan of the totals over the experts
+    const int cnt = e < E ? (int) counts[e] : 0;
+    int incl = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    int base = 0;
+    for (int w = 0; w < warp; ++w) base += s_warp[w];
+    const int t0 = blockIdx.x * kMapTokens;
+    if (e < E) {
+        int run = base + incl - cnt + block_offs[(int64_t) blockIdx.x * E + e];
+#pragma unroll 8
+        for (int i = 0; i < kMapTokens; ++i) {
+            const bool v = t0 + i < T && routing_map[(int64_t) (t0 + i) * E + e] != 0;
+            s_rank[i * E + e] = v ? run : -1;
+            run += v;
+        }
+    }
+    __syncthreads();
+    for (int i = warp; i < kMapTokens && t0 + i < T; i += nwarps) {
+        int *row = row_id_map + (int64_t) (t0 + i) * (2 * E + 1);
+        int n = 0;
+        for (int eb = 0; eb < E; eb += 32) {
+            const int ee = eb + lane;
+            const int r = ee < E ? s_rank[i * E + ee] : -1;
+            const unsigned ballot = __ballot_sync(0xffffffffu, r >= 0);
+            if (r >= 0) {
+                const int pos = n + __popc(ballot & ((1u << lane) - 1u));
+                row[pos] = r;
+                row[E + pos] = ee;
+            }
+            n += __popc(ballot);
+        }
+        for (int k = n + lane; k < E; k += 32) { row[k] = -1; row[E + k] = -1; }   // unused slots, as moe_compact_kernel
+        if (lane == 0) row[2 * E] = n;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------- permute
 // One CTA per token: the row is read once (16-byte vectors) and written to each of its destinations.
 __global__ void __launch_bounds__(kPermThreads) moe_permute_kernel(const uint4 *__restrict__ tokens, int64_t row_vecs, int T, int E,
@@ -226,6 +321,27 @@ int pt_moe_make_row_id_map(const void *routing_map, int map_elem_bytes, int64_t 
     PT_REQUIRE(tokens_per_expert && (T == 0 || (routing_map && row_id_map)), "moe row_id_map: null pointer");
     PT_REQUIRE(workspace && workspace_bytes >= pt_moe_row_id_map_workspace_bytes(T, E), "moe row_id_map: workspace too small");
     cudaStream_t st = (cudaStream_t) stream;
+    if (E <= 1024 && T > 0) {   // row-major passes, thread = expert
+        int *block_counts = (int *) workspace;   // [ceil(T / 32), E] <= T * E ints
+        const int nblocks = (int) ceil_div(T, kMapTokens), threads = (int) ceil_to(E, 32);
+        const int smem = kMapTokens * E * (int) sizeof(int);
+#define PT_MOE_MAP(MapT_)                                                                                                             \
+        do {                                                                                                                          \
+            moe_block_count_kernel<MapT_><<<nblocks, threads, 0, st>>>((const MapT_ *) routing_map, (int) T, E, block_counts);            \
+            PT_LAUNCH_OK();                                                                                                           \
+            moe_block_scan_kernel<<<(unsigned) ceil_div(E, 32), dim3(32, 32), 0, st>>>(block_counts, nblocks, E, tokens_per_expert);     \
+            PT_LAUNCH_OK();                                                                                                           \
+            auto kern = moe_block_map_kernel<MapT_>;                                                                                  \
+            if (smem > 48 * 1024) PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));            \
+            kern<<<nblocks, threads, smem, st>>>((const MapT_ *) routing_map, (int) T, E, block_counts, tokens_per_expert, row_id_map);  \
+            PT_LAUNCH_OK();                                                                                                           \
+        } while (0)
+        if (map_elem_bytes == 1) PT_MOE_MAP(uint8_t);
+        else if (map_elem_bytes == 4) PT_MOE_MAP(int);
+        else PT_MOE_MAP(int64_t);
+#undef PT_MOE_MAP
+        return PT_OK;
+    }
     int *ranks = (int *) workspace, *offs = ranks + (int64_t) T * E;
     if (map_elem_bytes == 1) moe_rank_kernel<uint8_t><<<E, 1024, 0, st>>>((const uint8_t *) routing_map, (int) T, E, ranks, tokens_per_expert);
     else if (map_elem_bytes == 4) moe_rank_kernel<int><<<E, 1024, 0, st>>>((const int *) routing_map, (int) T, E, ranks, tokens_per_expert);

@@ -97,3 +97,31 @@ def test_permute_feeds_the_grouped_gemm():
         ref[sel] += (x[sel].float() @ w[e].float().t()) * probs[sel, e].unsqueeze(-1)
     err = (y.float() - ref).norm() / ref.norm()
     assert float(err) < 0.08
+
+
+@pytest.mark.parametrize("T,E,topk", [(1, 1, 1), (33, 5, 2), (1000, 40, 3), (16384, 256, 8), (2050, 1024, 4), (300, 1100, 2)])
+@pytest.mark.parametrize("map_dtype", [torch.bool, torch.int32, torch.int64])
+def test_row_id_map_layout(T, E, topk, map_dtype):
+    """row_id_map [T, 2E + 1] against its definition: per token the destination rows of its routed experts in ascending
+    expert order, the expert ids, and their number; destinations follow the expert-major order of the unfused reference.
+    E = 1100 takes the per-expert-column kernels, the others the row-major ones."""
+    from primus_turbo.pytorch.kernels.moe import permutation_impl as pm
+    rm, _ = _routing(T, E, topk, seed=7 * T + E, empty_expert=1 if E > 2 else None)
+    row_id_map, tpe = pm.make_row_id_map(rm.to(map_dtype), T, E)
+    rmt = rm.T.contiguous()
+    assert torch.equal(tpe.cpu(), rmt.sum(dim=1).cpu())
+    # destination of (e, t) in expert-major order = exclusive rank of the pair among the routed pairs
+    flat = rmt.reshape(-1).to(torch.int64)
+    dest = (flat.cumsum(0) - flat).reshape(E, T).T          # [T, E]
+    m = row_id_map.cpu()
+    n = m[:, 2 * E]
+    assert torch.equal(n, rm.sum(dim=1).cpu().to(m.dtype))
+    rm_c, dest_c = rm.cpu(), dest.cpu()
+    for t in (0, T // 2, T - 1):
+        es = torch.nonzero(rm_c[t]).flatten()
+        k = len(es)
+        assert torch.equal(m[t, E:E + k].long(), es) and torch.equal(m[t, :k].long(), dest_c[t, es])
+        assert (m[t, k:E] == -1).all() and (m[t, E + k:2 * E] == -1).all()
+    # every destination row is used exactly once
+    used = m[:, :E][m[:, :E] >= 0]
+    assert used.numel() == int(flat.sum()) and torch.equal(used.sort().values, torch.arange(used.numel(), dtype=used.dtype))
