@@ -241,6 +241,89 @@ __global__ void __launch_bounds__(kThreads)
     atomicMax(amax_bits + b * N + col, __float_as_uint(m));
 }
 
+// The same for 16-bit inputs with 16-byte aligned rows.  A CTA covers 128 rows x 256 columns: a warp reads 512 contiguous
+// bytes of a row (eight columns per lane, |max| on packed pairs), the eight warps take 16 rows each, their partial maxima
+// meet in shared memory and one atomic per column leaves the CTA.
+constexpr int kAmaxVecRows = 128, kAmaxVecCols = 256;
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    amax_cols_vec_kernel(const T *__restrict__ x, int64_t M, int64_t N, unsigned *__restrict__ amax_bits) {
+    __shared__ uint32_t s_m[kThreads / 32][32][4];
+    const int64_t b = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t c0 = (int64_t) blockIdx.x * kAmaxVecCols + lane * 8;
+    const int64_t r0 = (int64_t) blockIdx.y * kAmaxVecRows + warp * 16;
+    uint32_t m[4] = {0u, 0u, 0u, 0u};
+    if (c0 < N) {
+        const T *p = x + (b * M) * N + c0;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            if (r0 + i < M) {
+                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p + (r0 + i) * N));
+                m[0] = absmax2<T>(m[0], v.x); m[1] = absmax2<T>(m[1], v.y); m[2] = absmax2<T>(m[2], v.z); m[3] = absmax2<T>(m[3], v.w);
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) s_m[warp][lane][k] = m[k];
+    __syncthreads();
+    // thread t < 128 finishes column pair t of the CTA's 256 columns
+    if (threadIdx.x < 128) {
+        const int l = threadIdx.x >> 2, k = threadIdx.x & 3;
+        uint32_t w = 0u;
+#pragma unroll
+        for (int g = 0; g < kThreads / 32; ++g) w = absmax2<T>(w, s_m[g][l][k]);
+        w = absmax2_done(w);
+        const int64_t c = (int64_t) blockIdx.x * kAmaxVecCols + 2 * threadIdx.x;
+        if (c < N) {
+            atomicMax(amax_bits + b * N + c, __float_as_uint(lo_f32<T>(w)));
+            atomicMax(amax_bits + b * N + c + 1, __float_as_uint(hi_f32<T>(w)));
+        }
+    }
+}
+
+// The cast for 16-bit inputs with 16-byte aligned rows, on the tiling of amax_cols_vec_kernel: a lane owns eight columns
+// (their scales computed once), a warp 16 rows of them, all sixteen loads in flight.
+template <typename T, int FMT>
+__global__ void __launch_bounds__(kThreads)
+    cast_cols_vec_kernel(const T *__restrict__ x, int64_t M, int64_t N, const unsigned *__restrict__ amax_bits, uint8_t *__restrict__ q,
+                         float *__restrict__ scale_inv) {
+    const int64_t b = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t c0 = (int64_t) blockIdx.x * kAmaxVecCols + lane * 8;
+    if (c0 >= N) return;
+    const int64_t r0 = (int64_t) blockIdx.y * kAmaxVecRows + warp * 16;
+    float sc[8];
+    {
+        const uint4 a0 = *reinterpret_cast<const uint4 *>(amax_bits + b * N + c0), a1 = *reinterpret_cast<const uint4 *>(amax_bits + b * N + c0 + 4);
+        const uint32_t ab[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) sc[k] = scale_from_amax<FMT>(__uint_as_float(ab[k]), kEpsTensor);
+        if (blockIdx.y == 0 && warp == 0) {
+            float4 i0, i1;
+            i0.x = __fdiv_rn(1.0f, sc[0]); i0.y = __fdiv_rn(1.0f, sc[1]); i0.z = __fdiv_rn(1.0f, sc[2]); i0.w = __fdiv_rn(1.0f, sc[3]);
+            i1.x = __fdiv_rn(1.0f, sc[4]); i1.y = __fdiv_rn(1.0f, sc[5]); i1.z = __fdiv_rn(1.0f, sc[6]); i1.w = __fdiv_rn(1.0f, sc[7]);
+            *reinterpret_cast<float4 *>(scale_inv + b * N + c0) = i0;
+            *reinterpret_cast<float4 *>(scale_inv + b * N + c0 + 4) = i1;
+        }
+    }
+    uint4 v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+        if (r0 + i < M) v[i] = __ldg(reinterpret_cast<const uint4 *>(x + (b * M + r0 + i) * N + c0));
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        if (r0 + i < M) {
+            uint2 o;
+            o.x = cvt4_fp8<FMT>(mul_sat<FMT>(lo_f32<T>(v[i].x), sc[0]), mul_sat<FMT>(hi_f32<T>(v[i].x), sc[1]), mul_sat<FMT>(lo_f32<T>(v[i].y), sc[2]),
+                                mul_sat<FMT>(hi_f32<T>(v[i].y), sc[3]));
+            o.y = cvt4_fp8<FMT>(mul_sat<FMT>(lo_f32<T>(v[i].z), sc[4]), mul_sat<FMT>(hi_f32<T>(v[i].z), sc[5]), mul_sat<FMT>(lo_f32<T>(v[i].w), sc[6]),
+                                mul_sat<FMT>(hi_f32<T>(v[i].w), sc[7]));
+            *reinterpret_cast<uint2 *>(q + (b * M + r0 + i) * N + c0) = o;
+        }
+    }
+}
+
 // Cast of x [B, M, N] with one scale per (b, column). 8 columns per thread when aligned.
 template <typename T, int FMT>
 __global__ void __launch_bounds__(kThreads)
@@ -409,12 +492,30 @@ int pt_quantize_fp8_rowwise(const void *x, int x_dtype, int64_t B, int64_t M, in
         PT_CUDA_OK(cudaMemsetAsync(amax, 0, (size_t) (B * N) * 4, st));
     }
     PT_SWITCH_SRC(x_dtype, T, {
+        const int vec_ok = aligned(x, 16) && aligned(q, 8) && (N % 8 == 0);
         if (!scale_opt) {
-            dim3 grid((unsigned) ceil_div(N, kThreads), (unsigned) ceil_div(M, 64), (unsigned) B);
-            amax_cols_kernel<T><<<grid, kThreads, 0, st>>>((const T *) x, M, N, amax);
+            bool done = false;
+            if constexpr (sizeof(T) == 2) {
+                if (vec_ok) {
+                    dim3 grid((unsigned) ceil_div(N, kAmaxVecCols), (unsigned) ceil_div(M, kAmaxVecRows), (unsigned) B);
+                    amax_cols_vec_kernel<T><<<grid, kThreads, 0, st>>>((const T *) x, M, N, amax);
+                    done = true;
+                }
+            }
+            if (!done) {
+                dim3 grid((unsigned) ceil_div(N, kThreads), (unsigned) ceil_div(M, 64), (unsigned) B);
+                amax_cols_kernel<T><<<grid, kThreads, 0, st>>>((const T *) x, M, N, amax);
+            }
             PT_LAUNCH_OK();
         }
-        const int vec_ok = aligned(x, 16) && aligned(q, 8) && (N % 8 == 0);
+        if constexpr (sizeof(T) == 2) {
+            if (vec_ok && !scale_opt && aligned(amax, 16) && aligned(scale_inv, 16)) {
+                dim3 vgrid((unsigned) ceil_div(N, kAmaxVecCols), (unsigned) ceil_div(M, kAmaxVecRows), (unsigned) B);
+                PT_SWITCH_FP8(fmt, F, { cast_cols_vec_kernel<T, F><<<vgrid, kThreads, 0, st>>>((const T *) x, M, N, amax, (uint8_t *) q, scale_inv); });
+                PT_LAUNCH_OK();
+                return PT_OK;
+            }
+        }
         dim3 grid((unsigned) ceil_div(N, kThreads * (vec_ok ? 8 : 1)), (unsigned) ceil_div(M, 32), (unsigned) B);
         PT_SWITCH_FP8(fmt, F, {
             cast_cols_kernel<T, F><<<grid, kThreads, 0, st>>>((const T *) x, M, N, vec_ok, amax, scale_opt,
