@@ -13,8 +13,9 @@ Rank 0 prints one JSON line.  `value` is 2*M*N*K*R / step time summed over ranks
 `e2e` is the same metric through the public operator with pinned host buffers, host<->device copies inside the timed
 region; `roofline` describes the GEMM kernel (tensor bound); `cpu_baseline` is the torch-CPU port of the same pass.
 `sub` holds the other benchmark configurations (bench_configs.py): quantizer GB/s, dense backward, the MXFP8 70B
-FFN shape, the blockwise MoE grouped GEMMs and the MXFP4 grouped GEMMs, each with its own roofline record; with
-N > 1 also the expert-sharded and N-sharded runs through primus_turbo.pytorch.dist.partitioner.
+FFN shape, the blockwise MoE grouped GEMMs, the MXFP4 grouped GEMMs (and their tokens-per-expert sweep) and the
+streaming kernels around them (gated activation, RMSNorm, MoE permutation), each with its own roofline record; with
+N > 1 instead the expert-sharded and N-sharded runs through primus_turbo.pytorch.dist.partitioner.
 """
 import argparse
 import json
