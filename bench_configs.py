@@ -212,7 +212,7 @@ def quantize_records(dev, peaks, copies=4):
     run("grouped_mxfp4_dual_rht_65536x4096_g8",
         [lambda x=x: qi.grouped_quantize_mxfp4_impl(x, f4, None, 32, lens5_t, offs5, with_trans=True, scaling_recipe=SR(),
                                                     scaling_recipe_for_trans=SR(use_rht=True)) for x in x5],
-        2 * e5 + (e5 // 2 + e5 // 32) + (e5_pad // 2 + e5_pad // 32), "mx_quant_tma_kernel<e2m1, row+col, RHT, grouped>")
+        2 * e5 + (e5 // 2 + e5 // 32) + (e5_pad // 2 + e5_pad // 32), "mx_quant_split_kernel<e2m1, grouped, Hadamard columns>")
     run("grouped_mxfp8_dual_65536x4096_g8",
         [lambda x=x: qi.grouped_quantize_mxfp8_impl(x, f8, None, 32, lens5_t, offs5, with_trans=True) for x in x5],
         2 * e5 + 2 * (e5 + e5 // 32), "mx_quant_split_kernel<e4m3, grouped>")

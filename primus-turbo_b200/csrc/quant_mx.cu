@@ -805,8 +805,10 @@ __device__ __forceinline__ void split_prologue(uint8_t *tile, int t, int in_row0
 }
 
 // ROWSTAGE: the row-wise copy is staged and written by TMA (dense FP8); otherwise by 32-byte stores from registers.
-template <int FMT, bool ROW2D, bool COL2D, bool GROUPED, bool ROWSTAGE, int PRO = PT_PRO_NONE>
-__global__ void __launch_bounds__(kSThreads, split_ctas_per_sm(PRO))
+// COLRHT (e2m1): the transposed copy is taken of the 16-point Hadamard transform of each run of 16 rows, in fp32 and in the
+// operation order of mx_quant_tma_kernel's column pass (same bytes); the 64 fp32 values per thread cost a CTA per SM.
+template <int FMT, bool ROW2D, bool COL2D, bool GROUPED, bool ROWSTAGE, int PRO = PT_PRO_NONE, bool COLRHT = false>
+__global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO))
     mx_quant_split_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_qrow,
                           const __grid_constant__ CUtensorMap tmap_qcol, MxArgs a, int tiles_n, int tiles_m, int64_t total_tiles,
                           int sched_slot, int *status) {
@@ -1014,6 +1016,27 @@ __global__ void __launch_bounds__(kSThreads, split_ctas_per_sm(PRO))
             if (++stage == kSStages) { stage = 0; phase ^= 1; }
             const int buf = tile_i & 1;
             ++tile_i;
+            uint32_t o0[8], o1[8];   // 32 codes of column 2 pair and of column 2 pair + 1
+            MxScale s0, s1;
+            if constexpr (COLRHT) {
+                static_assert(!COLRHT || FMT == PT_E2M1, "the Hadamard option is an e2m1 one");
+                float c0[32], c1[32];
+#pragma unroll
+                for (int r = 0; r < 32; ++r) { c0[r] = bf16_lo(w[r]); c1[r] = bf16_hi(w[r]); }
+                rht16(c0); rht16(c0 + 16); rht16(c1); rht16(c1 + 16);
+                float m0c = 0.f, m1c = 0.f;
+#pragma unroll
+                for (int r = 0; r < 32; ++r) { m0c = fmaxf(m0c, fabsf(c0[r])); m1c = fmaxf(m1c, fabsf(c1[r])); }
+                s0 = mx_scale<FMT>(m0c, GROUPED);
+                s1 = mx_scale<FMT>(m1c, GROUPED);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    o0[k] = pack8_e2m1(c0[8 * k] * s0.inv, c0[8 * k + 1] * s0.inv, c0[8 * k + 2] * s0.inv, c0[8 * k + 3] * s0.inv, c0[8 * k + 4] * s0.inv,
+                                       c0[8 * k + 5] * s0.inv, c0[8 * k + 6] * s0.inv, c0[8 * k + 7] * s0.inv);
+                    o1[k] = pack8_e2m1(c1[8 * k] * s1.inv, c1[8 * k + 1] * s1.inv, c1[8 * k + 2] * s1.inv, c1[8 * k + 3] * s1.inv, c1[8 * k + 4] * s1.inv,
+                                       c1[8 * k + 5] * s1.inv, c1[8 * k + 6] * s1.inv, c1[8 * k + 7] * s1.inv);
+                }
+            } else {
             uint32_t pm = 0u;
 #pragma unroll
             for (int r = 0; r < 32; ++r) pm = absmax2_nan_bf16(pm, w[r]);
@@ -1033,7 +1056,8 @@ __global__ void __launch_bounds__(kSThreads, split_ctas_per_sm(PRO))
                 m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
                 m0c = m1c = m;
             }
-            const MxScale s0 = mx_scale<FMT>(m0c, GROUPED), s1 = mx_scale<FMT>(m1c, GROUPED);
+            s0 = mx_scale<FMT>(m0c, GROUPED);
+            s1 = mx_scale<FMT>(m1c, GROUPED);
             if (has_nan && !kFp4) {
                 const uint32_t nlim2 = bf16_bits_x2(-MxParams<FMT>::qmax * s0.native, -MxParams<FMT>::qmax * s1.native);
 #pragma unroll
@@ -1042,7 +1066,6 @@ __global__ void __launch_bounds__(kSThreads, split_ctas_per_sm(PRO))
             const uint32_t inv2 = bf16_bits_x2(s0.inv, s1.inv);
 #pragma unroll
             for (int r = 0; r < 32; ++r) w[r] = mul_bf16x2(w[r], inv2);
-            uint32_t o0[8], o1[8];   // 32 codes of column 2 pair and of column 2 pair + 1
             if constexpr (kFp4) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
@@ -1058,6 +1081,7 @@ __global__ void __launch_bounds__(kSThreads, split_ctas_per_sm(PRO))
                     o1[k] = pack4_fp8<FMT>(bf16_hi(w[4 * k]), bf16_hi(w[4 * k + 1]), bf16_hi(w[4 * k + 2]), bf16_hi(w[4 * k + 3]));
                 }
             }
+            }   // !COLRHT
             if (__any_sync(0xffffffffu, s0.byte == 0 || s1.byte == 0)) {   // such a column is written as (positive) zeros
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
@@ -1173,13 +1197,14 @@ static int make_tmap_out(CUtensorMap *m, const void *base, int64_t G, int64_t ro
 
 // The warp-split kernel covers bf16 inputs, both copies requested, no Hadamard transform, 16-byte aligned outputs.
 // Returns PT_ERR_UNSUPPORTED (without setting an error message) when the call is outside that.
-template <int FMT, bool GROUPED, int PRO = PT_PRO_NONE>
+template <int FMT, bool GROUPED, int PRO = PT_PRO_NONE, bool COLRHT = false>
 static int launch_mx_split(const MxArgs &a, int64_t G, int64_t m_tiles_rows, unsigned flags, cudaStream_t st) {
     if (PRO == PT_PRO_NONE && getenv("PT_MX_QUANT_NO_SPLIT") != nullptr) return PT_ERR_UNSUPPORTED;
     if (PRO != PT_PRO_NONE && (flags & (PT_MX_ROW_2D | PT_MX_COL_2D))) return PT_ERR_UNSUPPORTED;
     if (pro_is_glu(PRO) && a.N % kTileN != 0) return PT_ERR_UNSUPPORTED;   // the value tile's last columns would be gate columns
     const bool row = flags & PT_MX_ROW, col = flags & PT_MX_COL;
-    if (!row || !col || (flags & (PT_MX_ROW_RHT | PT_MX_COL_RHT | PT_MX_ROW_SR | PT_MX_COL_SR))) return PT_ERR_UNSUPPORTED;
+    if (!row || !col || (flags & (PT_MX_ROW_RHT | PT_MX_ROW_SR | PT_MX_COL_SR)) || ((flags & PT_MX_COL_RHT) != 0) != COLRHT) return PT_ERR_UNSUPPORTED;
+    if (COLRHT && (flags & (PT_MX_ROW_2D | PT_MX_COL_2D))) return PT_ERR_UNSUPPORTED;
     constexpr bool kFp4 = FMT == PT_E2M1;
     if (!aligned(a.x, 16) || !aligned(a.q_row, 16) || !aligned(a.q_col, 16) || !aligned(a.s_row, 2) || !aligned(a.s_col, 4)) return PT_ERR_UNSUPPORTED;
     if (a.M >= (1ll << 31) || m_tiles_rows >= (1ll << 31)) return PT_ERR_UNSUPPORTED;
@@ -1195,12 +1220,12 @@ static int launch_mx_split(const MxArgs &a, int64_t G, int64_t m_tiles_rows, uns
     if (kRowStage && (rc = make_tmap_out(&trow, a.q_row, G, a.M, a.N_pad, 64, kTileM)) != PT_OK) return rc;
     if ((rc = make_tmap_out(&tcol, a.q_col, G, a.N, kFp4 ? a.M_pad / 2 : a.M_pad, kFp4 ? 64 : 128, kTileN)) != PT_OK) return rc;
     const int slot = tile_sched_acquire(st);
-    const int grid = (int) std::min<int64_t>(total_tiles, (int64_t) sm_count() * split_ctas_per_sm(PRO));
+    const int grid = (int) std::min<int64_t>(total_tiles, (int64_t) sm_count() * (COLRHT ? 2 : split_ctas_per_sm(PRO)));
     constexpr int kSmem = split_smem_bytes(PRO);
     const bool r2d = flags & PT_MX_ROW_2D, c2d = flags & PT_MX_COL_2D;
 #define PT_MXS_CASE(R2, C2)                                                                                       \
     if (r2d == R2 && c2d == C2) {                                                                                 \
-        auto kern = mx_quant_split_kernel<FMT, R2, C2, GROUPED, kRowStage, PRO>;                                  \
+        auto kern = mx_quant_split_kernel<FMT, R2, C2, GROUPED, kRowStage, PRO, COLRHT>;                          \
         static bool attr_set_dev[64] = {};                                                                        \
         bool &attr_set = attr_set_dev[current_device_slot()];                                                     \
         if (!attr_set) {                                                                                          \
@@ -1213,7 +1238,7 @@ static int launch_mx_split(const MxArgs &a, int64_t G, int64_t m_tiles_rows, uns
         return PT_OK;                                                                                             \
     }
     PT_MXS_CASE(false, false)
-    if constexpr (!GROUPED && PRO == PT_PRO_NONE) {
+    if constexpr (!GROUPED && PRO == PT_PRO_NONE && !COLRHT) {
         PT_MXS_CASE(true, true)
         if constexpr (!kFp4) {
             PT_MXS_CASE(true, false)
@@ -1227,7 +1252,9 @@ static int launch_mx_split(const MxArgs &a, int64_t G, int64_t m_tiles_rows, uns
 template <typename T, int FMT>
 static int launch_mx(const MxArgs &a, int64_t G, unsigned flags, cudaStream_t st) {
     if constexpr (std::is_same<T, __nv_bfloat16>::value) {
-        const int rc = launch_mx_split<FMT, false>(a, G, a.M_pad, flags, st);
+        int rc = launch_mx_split<FMT, false>(a, G, a.M_pad, flags, st);
+        if constexpr (FMT == PT_E2M1)
+            if (rc == PT_ERR_UNSUPPORTED) rc = launch_mx_split<FMT, false, PT_PRO_NONE, true>(a, G, a.M_pad, flags, st);
         if (rc != PT_ERR_UNSUPPORTED) return rc;
     }
     dim3 grid((unsigned) (a.N_pad / kTileN), (unsigned) (a.M_pad / kTileM), (unsigned) G);
@@ -1292,7 +1319,9 @@ static int launch_mx(const MxArgs &a, int64_t G, unsigned flags, cudaStream_t st
 template <typename T, int FMT>
 static int launch_mx_grouped(const MxArgs &a, int64_t m_alloc, unsigned flags, cudaStream_t st) {
     if constexpr (std::is_same<T, __nv_bfloat16>::value) {
-        const int rc = launch_mx_split<FMT, true>(a, 1, m_alloc, flags, st);
+        int rc = launch_mx_split<FMT, true>(a, 1, m_alloc, flags, st);
+        if constexpr (FMT == PT_E2M1)
+            if (rc == PT_ERR_UNSUPPORTED) rc = launch_mx_split<FMT, true, PT_PRO_NONE, true>(a, 1, m_alloc, flags, st);
         if (rc != PT_ERR_UNSUPPORTED) return rc;
     }
     dim3 grid((unsigned) (a.N_pad / kTileN), (unsigned) (m_alloc / kTileM), 1u);  // tiles past padded_offs_col[G] return at once
