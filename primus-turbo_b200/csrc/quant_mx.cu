@@ -946,7 +946,22 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
 #pragma unroll
                     for (int k = 0; k < 16; ++k) x[k] = max_bf16x2(x[k], nlim2);
                 }
-                encode_row_block<FMT>(x, bf16_bits_x2(sc.inv, sc.inv), o);
+                bool sr_done = false;
+                if constexpr (kFp4) {
+                    if (a.sr_row) {   // stochastic rounding: 32 random bits per four elements from a hash of (seed, position)
+                        const uint32_t inv2 = bf16_bits_x2(sc.inv, sc.inv);
+                        SrState sr{sr_mix(a.sr_seed ^ (uint32_t) ((gm * a.N_pad + n0 + 32 * b) >> 2)) | 1u};
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const uint32_t v0 = mul_bf16x2(x[4 * k], inv2), v1 = mul_bf16x2(x[4 * k + 1], inv2);
+                            const uint32_t v2 = mul_bf16x2(x[4 * k + 2], inv2), v3 = mul_bf16x2(x[4 * k + 3], inv2);
+                            o[k] = cvt4_e2m1_sr(bf16_lo(v0), bf16_hi(v0), bf16_lo(v1), bf16_hi(v1), sr.next()) |
+                                   (cvt4_e2m1_sr(bf16_lo(v2), bf16_hi(v2), bf16_lo(v3), bf16_hi(v3), sr.next()) << 16);
+                        }
+                        sr_done = true;
+                    }
+                }
+                if (!sr_done) encode_row_block<FMT>(x, bf16_bits_x2(sc.inv, sc.inv), o);
                 if (sc.byte == 0) {       // such a block is written as (positive) zeros
 #pragma unroll
                     for (int k = 0; k < 8; ++k) o[k] = 0u;
@@ -1029,12 +1044,24 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
                 for (int r = 0; r < 32; ++r) { m0c = fmaxf(m0c, fabsf(c0[r])); m1c = fmaxf(m1c, fabsf(c1[r])); }
                 s0 = mx_scale<FMT>(m0c, GROUPED);
                 s1 = mx_scale<FMT>(m1c, GROUPED);
+                if (a.sr_col) {
+                    const uint32_t pos = (uint32_t) ((((int64_t) tn * kTileN + 2 * pair) * a.M_pad + (int64_t) tm * kTileM + 32 * band) >> 2);
+                    SrState r0{sr_mix(~a.sr_seed ^ pos) | 1u}, r1{sr_mix(~a.sr_seed ^ (pos + (uint32_t) (a.M_pad >> 2))) | 1u};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        o0[k] = cvt4_e2m1_sr(c0[8 * k] * s0.inv, c0[8 * k + 1] * s0.inv, c0[8 * k + 2] * s0.inv, c0[8 * k + 3] * s0.inv, r0.next()) |
+                                (cvt4_e2m1_sr(c0[8 * k + 4] * s0.inv, c0[8 * k + 5] * s0.inv, c0[8 * k + 6] * s0.inv, c0[8 * k + 7] * s0.inv, r0.next()) << 16);
+                        o1[k] = cvt4_e2m1_sr(c1[8 * k] * s1.inv, c1[8 * k + 1] * s1.inv, c1[8 * k + 2] * s1.inv, c1[8 * k + 3] * s1.inv, r1.next()) |
+                                (cvt4_e2m1_sr(c1[8 * k + 4] * s1.inv, c1[8 * k + 5] * s1.inv, c1[8 * k + 6] * s1.inv, c1[8 * k + 7] * s1.inv, r1.next()) << 16);
+                    }
+                } else {
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     o0[k] = pack8_e2m1(c0[8 * k] * s0.inv, c0[8 * k + 1] * s0.inv, c0[8 * k + 2] * s0.inv, c0[8 * k + 3] * s0.inv, c0[8 * k + 4] * s0.inv,
                                        c0[8 * k + 5] * s0.inv, c0[8 * k + 6] * s0.inv, c0[8 * k + 7] * s0.inv);
                     o1[k] = pack8_e2m1(c1[8 * k] * s1.inv, c1[8 * k + 1] * s1.inv, c1[8 * k + 2] * s1.inv, c1[8 * k + 3] * s1.inv, c1[8 * k + 4] * s1.inv,
                                        c1[8 * k + 5] * s1.inv, c1[8 * k + 6] * s1.inv, c1[8 * k + 7] * s1.inv);
+                }
                 }
             } else {
             uint32_t pm = 0u;
@@ -1066,7 +1093,17 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
             const uint32_t inv2 = bf16_bits_x2(s0.inv, s1.inv);
 #pragma unroll
             for (int r = 0; r < 32; ++r) w[r] = mul_bf16x2(w[r], inv2);
-            if constexpr (kFp4) {
+            if (kFp4 && a.sr_col) {
+                const uint32_t pos = (uint32_t) ((((int64_t) tn * kTileN + 2 * pair) * a.M_pad + (int64_t) tm * kTileM + 32 * band) >> 2);
+                SrState r0{sr_mix(~a.sr_seed ^ pos) | 1u}, r1{sr_mix(~a.sr_seed ^ (pos + (uint32_t) (a.M_pad >> 2))) | 1u};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    o0[k] = cvt4_e2m1_sr(bf16_lo(w[8 * k]), bf16_lo(w[8 * k + 1]), bf16_lo(w[8 * k + 2]), bf16_lo(w[8 * k + 3]), r0.next()) |
+                            (cvt4_e2m1_sr(bf16_lo(w[8 * k + 4]), bf16_lo(w[8 * k + 5]), bf16_lo(w[8 * k + 6]), bf16_lo(w[8 * k + 7]), r0.next()) << 16);
+                    o1[k] = cvt4_e2m1_sr(bf16_hi(w[8 * k]), bf16_hi(w[8 * k + 1]), bf16_hi(w[8 * k + 2]), bf16_hi(w[8 * k + 3]), r1.next()) |
+                            (cvt4_e2m1_sr(bf16_hi(w[8 * k + 4]), bf16_hi(w[8 * k + 5]), bf16_hi(w[8 * k + 6]), bf16_hi(w[8 * k + 7]), r1.next()) << 16);
+                }
+            } else if constexpr (kFp4) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     o0[k] = pack8_e2m1(bf16_lo(w[8 * k]), bf16_lo(w[8 * k + 1]), bf16_lo(w[8 * k + 2]), bf16_lo(w[8 * k + 3]),
@@ -1203,7 +1240,8 @@ static int launch_mx_split(const MxArgs &a, int64_t G, int64_t m_tiles_rows, uns
     if (PRO != PT_PRO_NONE && (flags & (PT_MX_ROW_2D | PT_MX_COL_2D))) return PT_ERR_UNSUPPORTED;
     if (pro_is_glu(PRO) && a.N % kTileN != 0) return PT_ERR_UNSUPPORTED;   // the value tile's last columns would be gate columns
     const bool row = flags & PT_MX_ROW, col = flags & PT_MX_COL;
-    if (!row || !col || (flags & (PT_MX_ROW_RHT | PT_MX_ROW_SR | PT_MX_COL_SR)) || ((flags & PT_MX_COL_RHT) != 0) != COLRHT) return PT_ERR_UNSUPPORTED;
+    if (!row || !col || (flags & PT_MX_ROW_RHT) || ((flags & PT_MX_COL_RHT) != 0) != COLRHT) return PT_ERR_UNSUPPORTED;
+    if ((flags & (PT_MX_ROW_SR | PT_MX_COL_SR)) && (FMT != PT_E2M1 || PRO != PT_PRO_NONE)) return PT_ERR_UNSUPPORTED;
     if (COLRHT && (flags & (PT_MX_ROW_2D | PT_MX_COL_2D))) return PT_ERR_UNSUPPORTED;
     constexpr bool kFp4 = FMT == PT_E2M1;
     if (!aligned(a.x, 16) || !aligned(a.q_row, 16) || !aligned(a.q_col, 16) || !aligned(a.s_row, 2) || !aligned(a.s_col, 4)) return PT_ERR_UNSUPPORTED;
