@@ -1420,8 +1420,9 @@ static int fused_args(MxArgs &a, const char *what, const void *x, int x_dtype, i
     PT_REQUIRE(rows >= 0 && H >= 0, "%s: bad shape", what);
     PT_REQUIRE(x_dtype == PT_BF16, "%s: the fused kernels take bf16 input", what);
     PT_REQUIRE(H % 32 == 0, "%s: the quantized width must be divisible by 32 (got %lld)", what, (long long) H);
-    PT_REQUIRE((flags & (PT_MX_ROW | PT_MX_COL)) == (PT_MX_ROW | PT_MX_COL) && !(flags & ~(unsigned) (PT_MX_ROW | PT_MX_COL)),
+    PT_REQUIRE((flags & (PT_MX_ROW | PT_MX_COL)) == (PT_MX_ROW | PT_MX_COL) && !(flags & ~(unsigned) (PT_MX_ROW | PT_MX_COL | PT_MX_COL_RHT)),
                "%s: the fused kernels write both copies, with 1-D block scales and round-to-nearest (flags 0x%x)", what, flags);
+    PT_REQUIRE(!(flags & PT_MX_COL_RHT) || fmt == PT_E2M1, "%s: the Hadamard transform of the transposed copy is an e2m1 option", what);
     PT_REQUIRE(fmt == PT_E4M3 || fmt == PT_E2M1, "%s: formats e4m3 and e2m1", what);
     PT_REQUIRE(q_row && s_row && q_col && s_col, "%s: outputs missing", what);
     a.x = x; a.M = rows; a.N = H; a.N_pad = ceil_to(H, 128);
@@ -1443,7 +1444,14 @@ template <int PRO, bool GROUPED>
 static int launch_fused(const MxArgs &a, const char *what, int fmt, unsigned flags, cudaStream_t st) {
     int rc = PT_ERR_UNSUPPORTED;
     if (fmt == PT_E4M3) rc = launch_mx_split<PT_E4M3, GROUPED, PRO>(a, 1, a.M_pad, flags, st);
-    if (fmt == PT_E2M1) rc = launch_mx_split<PT_E2M1, GROUPED, PRO>(a, 1, a.M_pad, flags, st);
+    if (fmt == PT_E2M1) {
+        if constexpr (pro_is_glu(PRO)) {
+            rc = (flags & PT_MX_COL_RHT) ? launch_mx_split<PT_E2M1, GROUPED, PRO, true>(a, 1, a.M_pad, flags, st)
+                                         : launch_mx_split<PT_E2M1, GROUPED, PRO>(a, 1, a.M_pad, flags, st);
+        } else {
+            rc = launch_mx_split<PT_E2M1, GROUPED, PRO>(a, 1, a.M_pad, flags, st);
+        }
+    }
     if (rc == PT_ERR_UNSUPPORTED)
         return set_error(PT_ERR_UNSUPPORTED, "%s: outside the fused kernel's range (16-byte aligned buffers, fewer than 2^31 rows, at most %d groups, "
                                              "width a multiple of 64 for the gated activations)", what, kQMaxGroups);

@@ -517,7 +517,13 @@ def grouped_dequantize_mxfp8_impl(x: torch.Tensor, out_dtype: torch.dtype, axis:
 
 
 # ------------------------------------------------------------------------------ operator + MX quantizer in one pass
-def glu_quantize_mx_impl(x: torch.Tensor, probs: torch.Tensor, row_mask, act: str, out_dtype, fused=None):
+def _glu_recipes(out_dtype, col_rht):
+    if col_rht:
+        assert nv.fmt_code(out_dtype) == nv.PT_E2M1, "the Hadamard transform of the transposed copy is an MXFP4 option"
+    return ScalingRecipe(), ScalingRecipe(use_rht=bool(col_rht))
+
+
+def glu_quantize_mx_impl(x: torch.Tensor, probs: torch.Tensor, row_mask, act: str, out_dtype, fused=None, col_rht=False):
     """MX copies (row-wise and transposed) of act(x[:, :H]) * x[:, H:] * probs without the [tokens, H] intermediate:
     (q_row, s_row, q_col, s_col), the bytes `glu_fwd_with_probs` followed by `quantize_mx*_impl(with_trans=True)` gives.
     fused=None picks the one-pass kernel where it applies; False forces the two kernels (the comparison the tests make)."""
@@ -526,23 +532,23 @@ def glu_quantize_mx_impl(x: torch.Tensor, probs: torch.Tensor, row_mask, act: st
     x, probs = x.contiguous(), probs.contiguous().view(-1)
     H = x.shape[1] // 2
     use = fused_mx_supported(x, H, out_dtype, True) if fused is None else fused
+    row_r, col_r = _glu_recipes(out_dtype, col_rht)
     if not use:
-        return _mx_quant(glu_fwd_with_probs(x, probs, row_mask, act), out_dtype, True, True, ScalingRecipe(), ScalingRecipe())
-    return _mx_quant(x, out_dtype, True, True, ScalingRecipe(), ScalingRecipe(), pro=("glu", probs, row_mask, ACT_CODES[act]))
+        return _mx_quant(glu_fwd_with_probs(x, probs, row_mask, act), out_dtype, True, True, row_r, col_r)
+    return _mx_quant(x, out_dtype, True, True, row_r, col_r, pro=("glu", probs, row_mask, ACT_CODES[act]))
 
 
-def grouped_glu_quantize_mx_impl(x, probs, row_mask, act: str, out_dtype, group_lens, group_offs, fused=None):
+def grouped_glu_quantize_mx_impl(x, probs, row_mask, act: str, out_dtype, group_lens, group_offs, fused=None, col_rht=False):
     """Grouped form (token segments per expert); returns what `grouped_quantize_mx*_impl(with_trans=True)` returns."""
     from ..activation.glu_impl import ACT_CODES, glu_fwd_with_probs
     nv.require_cuda(x, probs, row_mask)
     x, probs = x.contiguous(), probs.contiguous().view(-1)
     H = x.shape[1] // 2
     use = (fused_mx_supported(x, H, out_dtype, True) and group_lens.numel() <= 256) if fused is None else fused
+    row_r, col_r = _glu_recipes(out_dtype, col_rht)
     if not use:
-        return _grouped_mx_quant(glu_fwd_with_probs(x, probs, row_mask, act), out_dtype, group_lens, group_offs, True, True, ScalingRecipe(),
-                                 ScalingRecipe())
-    return _grouped_mx_quant(x, out_dtype, group_lens, group_offs, True, True, ScalingRecipe(), ScalingRecipe(),
-                             pro=("glu", probs, row_mask, ACT_CODES[act]))
+        return _grouped_mx_quant(glu_fwd_with_probs(x, probs, row_mask, act), out_dtype, group_lens, group_offs, True, True, row_r, col_r)
+    return _grouped_mx_quant(x, out_dtype, group_lens, group_offs, True, True, row_r, col_r, pro=("glu", probs, row_mask, ACT_CODES[act]))
 
 
 def rmsnorm_quantize_mx_impl(x: torch.Tensor, gamma: torch.Tensor, eps: float, zero_centered: bool, out_dtype, fused=None):

@@ -227,3 +227,29 @@ def test_fused_quantizer_refuses_what_it_does_not_cover():
         glu_quantize_mx_impl(x16, torch.rand(64, device="cuda"), None, "silu", torch.float8_e4m3fn, fused=True)
     out = glu_quantize_mx_impl(x16, torch.rand(64, device="cuda"), None, "silu", torch.float8_e4m3fn)   # two kernels
     assert out[0].shape == (64, 128)
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu"])
+def test_glu_quantize_mxfp4_with_hadamard_columns_fused_equals_two_kernels(act):
+    """The MXFP4 recipe's operand layout (row-wise copy plain, transposed copy after the 16-point Hadamard transform),
+    dense and grouped."""
+    from primus_turbo.pytorch.kernels.quantization.quantization_impl import glu_quantize_mx_impl, grouped_glu_quantize_mx_impl
+    F4 = torch.float4_e2m1fn_x2
+    g = torch.Generator(device="cuda").manual_seed(5)
+    rows, H = 1280, 1024
+    x = torch.randn(rows, 2 * H, device="cuda", dtype=torch.bfloat16, generator=g)
+    probs = torch.rand(rows, device="cuda", generator=g)
+    _same(glu_quantize_mx_impl(x, probs, None, act, F4, fused=True, col_rht=True), glu_quantize_mx_impl(x, probs, None, act, F4, fused=False, col_rht=True))
+    assert not torch.equal(glu_quantize_mx_impl(x, probs, None, act, F4, col_rht=True)[2].view(torch.uint8),
+                           glu_quantize_mx_impl(x, probs, None, act, F4)[2].view(torch.uint8))   # the transform is applied
+    lens = [256, 0, 512, 256, 256]
+    gl = torch.tensor(lens, device="cuda", dtype=torch.int64)
+    go = torch.cat([gl.new_zeros(1), gl.cumsum(0)])
+    f = grouped_glu_quantize_mx_impl(x, probs, None, act, F4, gl, go, fused=True, col_rht=True)
+    u = grouped_glu_quantize_mx_impl(x, probs, None, act, F4, gl, go, fused=False, col_rht=True)
+    ocol = f[7]
+    for i, n in enumerate(lens):
+        c0, c1 = int(ocol[i]), int(ocol[i + 1])
+        assert torch.equal(f[0].view(torch.uint8)[sum(lens[:i]):sum(lens[:i + 1])], u[0].view(torch.uint8)[sum(lens[:i]):sum(lens[:i + 1])])
+        assert torch.equal(f[2].view(torch.uint8)[:, c0 // 2:c1 // 2], u[2].view(torch.uint8)[:, c0 // 2:c1 // 2])
+        assert torch.equal(f[3].view(torch.uint8)[:, c0 // 32:c1 // 32], u[3].view(torch.uint8)[:, c0 // 32:c1 // 32])
