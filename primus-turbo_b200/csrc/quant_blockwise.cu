@@ -252,6 +252,8 @@ __global__ void __launch_bounds__(kBqThreads, kBqCtasPerSm)
         prefetch_tmap(&tmap);
     }
     __syncthreads();
+    grid_dep_wait();    // the input (and the group offsets) may come from the kernel launched just before
+    grid_dep_launch();
     bool ok = true;
     const uint32_t per_b = (uint32_t) a.tiles_n * (uint32_t) a.tiles_m;
     const int64_t m_blocks = (a.M + kBlk - 1) / kBlk;
@@ -524,6 +526,8 @@ __global__ void __launch_bounds__(kBsThreads, kBsCtasPerSm)
     }
     __shared__ int s_gtab[SEG ? 2 * (kBqMaxGroups + 1) : 1];
     __syncthreads();
+    grid_dep_wait();    // the input (and the group offsets) may come from the kernel launched just before
+    grid_dep_launch();
     if constexpr (SEG) {
         for (int i = threadIdx.x; i <= a.seg.num_groups; i += blockDim.x) {
             s_gtab[i] = (int) a.seg.padded_offs[i];
@@ -916,7 +920,7 @@ static int launch_tile(const void *x, int x_dtype, int64_t B, int64_t m_tiles, i
                 PT_SWITCH_FP8(fmt, F, {                                                                            \
                     auto kern = blockwise_split_kernel<T_, F, kSegK>;                                              \
                     PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBsSmemBytes)); \
-                    kern<<<sgrid, kBsThreads, kBsSmemBytes, (cudaStream_t) stream>>>(tmap, trow, tcol, a);         \
+                    PT_CUDA_OK(launch_overlapped(kern, dim3(sgrid), dim3(kBsThreads), kBsSmemBytes, (cudaStream_t) stream, tmap, trow, tcol, a)); \
                 })
                 if (x_dtype == PT_BF16) { PT_BS_LAUNCH(__nv_bfloat16); } else { PT_BS_LAUNCH(__half); }
 #undef PT_BS_LAUNCH
@@ -931,7 +935,7 @@ static int launch_tile(const void *x, int x_dtype, int64_t B, int64_t m_tiles, i
         PT_SWITCH_FP8(fmt, F, {                                                                                    \
             auto kern = blockwise_tma_kernel<T_, F, MODE>;                                                         \
             PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBqSmemBytes));     \
-            kern<<<tma_grid, kBqThreads, kBqSmemBytes, (cudaStream_t) stream>>>(tmap, a);                          \
+            PT_CUDA_OK(launch_overlapped(kern, dim3(tma_grid), dim3(kBqThreads), kBqSmemBytes, (cudaStream_t) stream, tmap, a)); \
         })
         if (x_dtype == PT_BF16) { PT_BQ_LAUNCH(__nv_bfloat16); } else { PT_BQ_LAUNCH(__half); }
 #undef PT_BQ_LAUNCH

@@ -41,10 +41,18 @@ constexpr float kEpsTensor = 1e-12f;
 
 // ------------------------------------------------------------------------------------------------
 // amax over a flat array: 8-element vectors, 4 in flight per thread, one atomicMax per block.
+// Entry of a kernel launched with launch_overlapped(): wait until every earlier kernel of the stream has completed (its
+// results are then visible), then let the next kernel of the stream begin its own launch.
+__device__ __forceinline__ void pdl_enter() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // Non-negative floats order like their bit patterns, so the running maximum is kept as uint32.
 template <typename T>
 __global__ void __launch_bounds__(kThreads) amax_flat_kernel(const T *__restrict__ x, int64_t n, int vec_ok,
                                                              unsigned *__restrict__ amax_bits) {
+    pdl_enter();
     float m = 0.f;
     const int64_t tid = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t nthreads = (int64_t) gridDim.x * blockDim.x;
@@ -87,6 +95,7 @@ template <typename T, int FMT>
 __global__ void __launch_bounds__(kThreads)
     cast_flat_kernel(const T *__restrict__ x, int64_t n, int vec_ok, const unsigned *__restrict__ amax_bits,
                      const float *__restrict__ scale_opt, uint8_t *__restrict__ q, float *__restrict__ scale_inv) {
+    pdl_enter();
     float scale;
     if (scale_opt != nullptr) scale = __ldg(scale_opt);
     else scale = scale_from_amax<FMT>(__uint_as_float(*amax_bits), kEpsTensor);
@@ -185,6 +194,7 @@ __global__ void __launch_bounds__(kThreads)
 template <typename T, int FMT>
 __global__ void __launch_bounds__(kThreads) rowwise_row_in_regs_kernel(const T *__restrict__ x, int64_t rows, int64_t len,
                                                                      uint8_t *__restrict__ q, float *__restrict__ scale_inv) {
+    pdl_enter();
     constexpr int kKeep = 4;
     __shared__ float s[kThreads / 32];
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -248,6 +258,7 @@ constexpr int kAmaxVecRows = 128, kAmaxVecCols = 256;
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
     amax_cols_vec_kernel(const T *__restrict__ x, int64_t M, int64_t N, unsigned *__restrict__ amax_bits) {
+    pdl_enter();
     __shared__ uint32_t s_m[kThreads / 32][32][4];
     const int64_t b = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -288,6 +299,7 @@ template <typename T, int FMT>
 __global__ void __launch_bounds__(kThreads)
     cast_cols_vec_kernel(const T *__restrict__ x, int64_t M, int64_t N, const unsigned *__restrict__ amax_bits, uint8_t *__restrict__ q,
                          float *__restrict__ scale_inv) {
+    pdl_enter();
     const int64_t b = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t c0 = (int64_t) blockIdx.x * kAmaxVecCols + lane * 8;
@@ -443,13 +455,12 @@ int pt_quantize_fp8_tensorwise(const void *x, int x_dtype, int64_t n, int fmt, v
         if (!scale_opt) {
             PT_CUDA_OK(cudaMemsetAsync(amax, 0, 4, st));
             const int blocks = (int) std::max<int64_t>(1, std::min(max_blocks, ceil_div(n, (int64_t) kThreads * 32)));
-            amax_flat_kernel<T><<<blocks, kThreads, 0, st>>>((const T *) x, n, vec_ok, amax);
-            PT_LAUNCH_OK();
+            PT_CUDA_OK(launch_overlapped(amax_flat_kernel<T>, dim3(blocks), dim3(kThreads), 0, st, (const T *) x, n, vec_ok, amax));
         }
         const int blocks = (int) std::max<int64_t>(1, std::min(max_blocks * 2, ceil_div(n, (int64_t) kThreads * 16)));
         PT_SWITCH_FP8(fmt, F, {
-            cast_flat_kernel<T, F><<<blocks, kThreads, 0, st>>>((const T *) x, n, vec_ok, amax, scale_opt,
-                                                                 (uint8_t *) q, scale_inv);
+            PT_CUDA_OK(launch_overlapped(cast_flat_kernel<T, F>, dim3(blocks), dim3(kThreads), 0, st, (const T *) x, n, vec_ok, (const unsigned *) amax,
+                                         scale_opt, (uint8_t *) q, scale_inv));
         });
         PT_LAUNCH_OK();
     });
@@ -471,8 +482,8 @@ int pt_quantize_fp8_rowwise(const void *x, int x_dtype, int64_t B, int64_t M, in
             PT_SWITCH_FP8(fmt, F, {
                 if constexpr (sizeof(T) == 2) {
                     if (vec_ok && !scale_opt && N <= (int64_t) kThreads * 8 * 4) {
-                        rowwise_row_in_regs_kernel<T, F><<<blocks, kThreads, 0, st>>>((const T *) x, rows, N, (uint8_t *) q, scale_inv);
-                        PT_LAUNCH_OK();
+                        PT_CUDA_OK(launch_overlapped(rowwise_row_in_regs_kernel<T, F>, dim3(blocks), dim3(kThreads), 0, st, (const T *) x, rows, N,
+                                                     (uint8_t *) q, scale_inv));
                         return PT_OK;
                     }
                 }
@@ -498,7 +509,7 @@ int pt_quantize_fp8_rowwise(const void *x, int x_dtype, int64_t B, int64_t M, in
             if constexpr (sizeof(T) == 2) {
                 if (vec_ok) {
                     dim3 grid((unsigned) ceil_div(N, kAmaxVecCols), (unsigned) ceil_div(M, kAmaxVecRows), (unsigned) B);
-                    amax_cols_vec_kernel<T><<<grid, kThreads, 0, st>>>((const T *) x, M, N, amax);
+                    PT_CUDA_OK(launch_overlapped(amax_cols_vec_kernel<T>, grid, dim3(kThreads), 0, st, (const T *) x, M, N, amax));
                     done = true;
                 }
             }
@@ -511,8 +522,10 @@ int pt_quantize_fp8_rowwise(const void *x, int x_dtype, int64_t B, int64_t M, in
         if constexpr (sizeof(T) == 2) {
             if (vec_ok && !scale_opt && aligned(amax, 16) && aligned(scale_inv, 16)) {
                 dim3 vgrid((unsigned) ceil_div(N, kAmaxVecCols), (unsigned) ceil_div(M, kAmaxVecRows), (unsigned) B);
-                PT_SWITCH_FP8(fmt, F, { cast_cols_vec_kernel<T, F><<<vgrid, kThreads, 0, st>>>((const T *) x, M, N, amax, (uint8_t *) q, scale_inv); });
-                PT_LAUNCH_OK();
+                PT_SWITCH_FP8(fmt, F, {
+                    PT_CUDA_OK(launch_overlapped(cast_cols_vec_kernel<T, F>, vgrid, dim3(kThreads), 0, st, (const T *) x, M, N, (const unsigned *) amax,
+                                                 (uint8_t *) q, scale_inv));
+                });
                 return PT_OK;
             }
         }

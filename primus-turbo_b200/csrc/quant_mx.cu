@@ -757,9 +757,61 @@ constexpr int split_stage_bytes(int pro) { return pro_is_glu(pro) ? 2 * kQTileBy
 constexpr int split_smem_bytes(int pro) { return kSStages * split_stage_bytes(pro) + 4 * kSStageOutBytes + 1024 + 1024; }
 constexpr int split_ctas_per_sm(int pro) { return pro_is_glu(pro) ? 2 : kSCtasPerSm; }
 
+// RMSNorm: thread t owns one 8-column chunk (its gains unpacked once) in rows t / 8 + {0, 32, 64, 96}; two packed fp32
+// multiplies per pair of elements, each rounding like the scalar x * rstd * g of the stand-alone kernel.  The gains and
+// the four row statistics of a tile travel in RmsAux: they are fetched one tile ahead, as soon as the producer has
+// published the next tile's descriptor, so that no consumer waits on a global load between a tile's arrival and its use.
+struct RmsAux {
+    uint4 gv;
+    float rv[4];
+};
+__device__ __forceinline__ void rms_aux_load(RmsAux &x, int t, int in_row0, int tn, const MxArgs &a) {
+    const int c = t & 7, r0 = t >> 3;
+    const int64_t n = (int64_t) tn * kTileN + c * 8;
+    x.gv = make_uint4(0u, 0u, 0u, 0u);
+    if (n < a.N) x.gv = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(a.pro_gamma) + n));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int64_t grow = (int64_t) in_row0 + r0 + 32 * j;
+        x.rv[j] = grow < a.M ? __ldg(a.pro_rowvec + grow) : 0.f;
+    }
+}
+__device__ __forceinline__ void split_prologue_rmsnorm(uint8_t *tile, int t, int in_row0, const RmsAux &x, const MxArgs &a) {
+    const int c = t & 7, r0 = t >> 3;
+    const uint32_t gw[4] = {x.gv.x, x.gv.y, x.gv.z, x.gv.w};
+    const float zc = a.pro_zero_centered ? 1.0f : 0.0f;
+    uint64_t g2[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) asm("mov.b64 %0, {%1, %2};" : "=l"(g2[k]) : "f"(bf16_lo(gw[k]) + zc), "f"(bf16_hi(gw[k]) + zc));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int row = r0 + 32 * j;
+        if ((int64_t) in_row0 + row >= a.M) continue;   // zero-filled rows stay +0 (0 * rstd * negative gain would make them -0)
+        uint8_t *pa = tile + row * 128 + ((c ^ (r0 & 7)) << 4);
+        const uint4 av = *reinterpret_cast<const uint4 *>(pa);
+        const uint32_t aw[4] = {av.x, av.y, av.z, av.w};
+        uint32_t ow[4];
+        uint64_t r2;
+        asm("mov.b64 %0, {%1, %1};" : "=l"(r2) : "f"(x.rv[j]));
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float lo, hi;
+            asm("{\n\t.reg .b64 xx;\n\tmov.b64 xx, {%2, %3};\n\tmul.rn.f32x2 xx, xx, %4;\n\tmul.rn.f32x2 xx, xx, %5;\n\tmov.b64 {%0, %1}, xx;\n\t}"
+                : "=f"(lo), "=f"(hi)
+                : "f"(bf16_lo(aw[k])), "f"(bf16_hi(aw[k])), "l"(r2), "l"(g2[k]));
+            const __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
+            ow[k] = *reinterpret_cast<const uint32_t *>(&r);
+        }
+        *reinterpret_cast<uint4 *>(pa) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+    sm100::fence_proxy_async_smem();   // the next bulk load into this stage must order after these writes
+    asm volatile("bar.sync 3, %0;" ::"n"(2 * kSGroupThreads) : "memory");
+}
+
 // t: 0 .. 255 over the consumer threads; thread (row = t / 2, half = t % 2) transforms 32 elements of its row in place
 template <int PRO>
 __device__ __forceinline__ void split_prologue(uint8_t *tile, int t, int in_row0, int tn, const MxArgs &a) {
+    static_assert(PRO != PT_PRO_RMSNORM, "the RMSNorm prologue is split_prologue_rmsnorm");
     const int row = t >> 1, half = t & 1;
     const int64_t grow = (int64_t) in_row0 + row;
     const bool in = grow < a.M;
@@ -822,6 +874,7 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
     uint8_t *row_stage = col_stage + 2 * kSStageOutBytes;          // 2 x 8 KiB
     uint64_t *full_bar = reinterpret_cast<uint64_t *>(row_stage + 2 * kSStageOutBytes);
     uint64_t *empty_bar = full_bar + kSStages;
+    uint64_t *desc_bar = empty_bar + kSStages;   // RMSNorm prologue: the stage's descriptor is written (its tile may still be in flight)
     __shared__ __align__(16) TileDesc s_desc[kSStages];
     __shared__ __align__(4) uint8_t s_colscale[2][kTileN][4];      // [buffer][column][band]
     __shared__ int s_abort;
@@ -833,6 +886,7 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
         for (int s = 0; s < kSStages; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 2 * kSGroupWarps);
+            mbar_init(&desc_bar[s], 1);
         }
         fence_barrier_init();
         prefetch_tmap(&tmap);
@@ -880,6 +934,7 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
                 }
                 if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
                 s_desc[stage] = d;
+                if constexpr (PRO == PT_PRO_RMSNORM) mbar_arrive(&desc_bar[stage]);
                 mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
                 sm100::tma_load_3d(smem + stage * kStageBytes, &tmap, &full_bar[stage], d.tn * kTileN, d.in_row0, d.g);
                 if constexpr (pro_is_glu(PRO))   // the gate half of the same rows: columns N .. 2N of x
@@ -888,6 +943,7 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
             }
             if (ok && (ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) {   // the terminal descriptor
                 s_desc[stage].tn = -1;
+                if constexpr (PRO == PT_PRO_RMSNORM) mbar_arrive(&desc_bar[stage]);
                 mbar_arrive(&full_bar[stage]);
             }
             tile_sched_done(sched_slot);
@@ -896,6 +952,9 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
         // ================================================================ row-wise copy: thread = tile row
         const int row = threadIdx.x - 32;
         uint32_t stage = 0, phase = 0, tile_i = 0;
+        static_assert(kSStages == 2, "the RMSNorm prefetch looks at the other stage");
+        [[maybe_unused]] RmsAux aux;
+        [[maybe_unused]] bool aux_ready = false;
         while (true) {
             if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
             const int4 d0 = *reinterpret_cast<const int4 *>(&s_desc[stage]);
@@ -903,7 +962,17 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
             const int tn = d0.x, tm = d0.y, n_valid = d1.x, row_out0 = d1.y;
             const int64_t g = d0.z;
             if (tn < 0) break;
-            if constexpr (PRO != PT_PRO_NONE) split_prologue<PRO>(smem + stage * kStageBytes, threadIdx.x - 32, s_desc[stage].in_row0, tn, a);
+            if constexpr (PRO == PT_PRO_RMSNORM) {
+                const int t = threadIdx.x - 32;
+                if (!aux_ready) rms_aux_load(aux, t, s_desc[stage].in_row0, tn, a);
+                split_prologue_rmsnorm(smem + stage * kStageBytes, t, s_desc[stage].in_row0, aux, a);
+                // the next tile's descriptor is normally published by now: fetch its gains and row statistics a tile early
+                const uint32_t ns = stage ^ 1u, np = stage == kSStages - 1 ? phase ^ 1u : phase;
+                aux_ready = mbar_test(&desc_bar[ns], np);
+                if (aux_ready && s_desc[ns].tn >= 0) rms_aux_load(aux, t, s_desc[ns].in_row0, s_desc[ns].tn, a);
+            } else if constexpr (PRO != PT_PRO_NONE) {
+                split_prologue<PRO>(smem + stage * kStageBytes, threadIdx.x - 32, s_desc[stage].in_row0, tn, a);
+            }
             uint32_t w[32];
             {
                 const uint8_t *rp = smem + stage * kStageBytes + row * 128;
@@ -1009,13 +1078,26 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
         const int band = ct >> 5, pair = lane;
         const int chunk = pair >> 2;
         uint32_t stage = 0, phase = 0, tile_i = 0;
+        static_assert(kSStages == 2, "the RMSNorm prefetch looks at the other stage");
+        [[maybe_unused]] RmsAux aux;
+        [[maybe_unused]] bool aux_ready = false;
         while (true) {
             if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
             const int4 d0 = *reinterpret_cast<const int4 *>(&s_desc[stage]);
             const int tn = d0.x, tm = d0.y;
             const int64_t g = d0.z;
             if (tn < 0) break;
-            if constexpr (PRO != PT_PRO_NONE) split_prologue<PRO>(smem + stage * kStageBytes, threadIdx.x - 32, s_desc[stage].in_row0, tn, a);
+            if constexpr (PRO == PT_PRO_RMSNORM) {
+                const int t = threadIdx.x - 32;
+                if (!aux_ready) rms_aux_load(aux, t, s_desc[stage].in_row0, tn, a);
+                split_prologue_rmsnorm(smem + stage * kStageBytes, t, s_desc[stage].in_row0, aux, a);
+                // the next tile's descriptor is normally published by now: fetch its gains and row statistics a tile early
+                const uint32_t ns = stage ^ 1u, np = stage == kSStages - 1 ? phase ^ 1u : phase;
+                aux_ready = mbar_test(&desc_bar[ns], np);
+                if (aux_ready && s_desc[ns].tn >= 0) rms_aux_load(aux, t, s_desc[ns].in_row0, s_desc[ns].tn, a);
+            } else if constexpr (PRO != PT_PRO_NONE) {
+                split_prologue<PRO>(smem + stage * kStageBytes, threadIdx.x - 32, s_desc[stage].in_row0, tn, a);
+            }
             const int n_valid = GROUPED ? s_desc[stage].n_valid : kTileM;
             uint32_t w[32];
             {
