@@ -191,8 +191,6 @@ __global__ void __launch_bounds__(kAnThreads) rmsnorm_stats_kernel(const T *__re
                                                                    float *__restrict__ rstd_out) {
     constexpr int V = 16 / sizeof(T);
     constexpr int kW = kAnThreads / 32;
-    // the quantizer that consumes rstd is launched to overlap this kernel's tail; it waits for this grid before it reads
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int lane = threadIdx.x & 31;
     const int64_t warps = (int64_t) gridDim.x * kW;
     for (int64_t r = (int64_t) blockIdx.x * kW + (threadIdx.x >> 5); r < rows; r += warps) {

@@ -758,15 +758,16 @@ constexpr int split_smem_bytes(int pro) { return kSStages * split_stage_bytes(pr
 constexpr int split_ctas_per_sm(int pro) { return pro_is_glu(pro) ? 2 : kSCtasPerSm; }
 
 // RMSNorm: thread t owns one 8-column chunk (its gains unpacked once) in rows t / 8 + {0, 32, 64, 96}; two packed fp32
-// multiplies per pair of elements, each rounding like the scalar x * rstd * g of the stand-alone kernel.  The gains and
-// the four row statistics of a tile travel in RmsAux: they are fetched one tile ahead, as soon as the producer has
-// published the next tile's descriptor, so that no consumer waits on a global load between a tile's arrival and its use.
+// multiplies per pair of elements, each rounding like the scalar x * rstd * g of the stand-alone kernel.  (Fetching the
+// gains and row statistics one tile ahead, off a barrier on the published descriptor, did not change the time: the
+// prologue is bound by its instructions, not by these loads.)
 struct RmsAux {
     uint4 gv;
     float rv[4];
 };
-__device__ __forceinline__ void rms_aux_load(RmsAux &x, int t, int in_row0, int tn, const MxArgs &a) {
+__device__ __forceinline__ void split_prologue_rmsnorm(uint8_t *tile, int t, int in_row0, int tn, const MxArgs &a) {
     const int c = t & 7, r0 = t >> 3;
+    RmsAux x;
     const int64_t n = (int64_t) tn * kTileN + c * 8;
     x.gv = make_uint4(0u, 0u, 0u, 0u);
     if (n < a.N) x.gv = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(a.pro_gamma) + n));
@@ -775,9 +776,6 @@ __device__ __forceinline__ void rms_aux_load(RmsAux &x, int t, int in_row0, int 
         const int64_t grow = (int64_t) in_row0 + r0 + 32 * j;
         x.rv[j] = grow < a.M ? __ldg(a.pro_rowvec + grow) : 0.f;
     }
-}
-__device__ __forceinline__ void split_prologue_rmsnorm(uint8_t *tile, int t, int in_row0, const RmsAux &x, const MxArgs &a) {
-    const int c = t & 7, r0 = t >> 3;
     const uint32_t gw[4] = {x.gv.x, x.gv.y, x.gv.z, x.gv.w};
     const float zc = a.pro_zero_centered ? 1.0f : 0.0f;
     uint64_t g2[4];
@@ -874,7 +872,6 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
     uint8_t *row_stage = col_stage + 2 * kSStageOutBytes;          // 2 x 8 KiB
     uint64_t *full_bar = reinterpret_cast<uint64_t *>(row_stage + 2 * kSStageOutBytes);
     uint64_t *empty_bar = full_bar + kSStages;
-    uint64_t *desc_bar = empty_bar + kSStages;   // RMSNorm prologue: the stage's descriptor is written (its tile may still be in flight)
     __shared__ __align__(16) TileDesc s_desc[kSStages];
     __shared__ __align__(4) uint8_t s_colscale[2][kTileN][4];      // [buffer][column][band]
     __shared__ int s_abort;
@@ -886,7 +883,6 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
         for (int s = 0; s < kSStages; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 2 * kSGroupWarps);
-            mbar_init(&desc_bar[s], 1);
         }
         fence_barrier_init();
         prefetch_tmap(&tmap);
@@ -934,7 +930,6 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
                 }
                 if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
                 s_desc[stage] = d;
-                if constexpr (PRO == PT_PRO_RMSNORM) mbar_arrive(&desc_bar[stage]);
                 mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
                 sm100::tma_load_3d(smem + stage * kStageBytes, &tmap, &full_bar[stage], d.tn * kTileN, d.in_row0, d.g);
                 if constexpr (pro_is_glu(PRO))   // the gate half of the same rows: columns N .. 2N of x
@@ -943,7 +938,6 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
             }
             if (ok && (ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) {   // the terminal descriptor
                 s_desc[stage].tn = -1;
-                if constexpr (PRO == PT_PRO_RMSNORM) mbar_arrive(&desc_bar[stage]);
                 mbar_arrive(&full_bar[stage]);
             }
             tile_sched_done(sched_slot);
@@ -952,9 +946,6 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
         // ================================================================ row-wise copy: thread = tile row
         const int row = threadIdx.x - 32;
         uint32_t stage = 0, phase = 0, tile_i = 0;
-        static_assert(kSStages == 2, "the RMSNorm prefetch looks at the other stage");
-        [[maybe_unused]] RmsAux aux;
-        [[maybe_unused]] bool aux_ready = false;
         while (true) {
             if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
             const int4 d0 = *reinterpret_cast<const int4 *>(&s_desc[stage]);
@@ -963,13 +954,7 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
             const int64_t g = d0.z;
             if (tn < 0) break;
             if constexpr (PRO == PT_PRO_RMSNORM) {
-                const int t = threadIdx.x - 32;
-                if (!aux_ready) rms_aux_load(aux, t, s_desc[stage].in_row0, tn, a);
-                split_prologue_rmsnorm(smem + stage * kStageBytes, t, s_desc[stage].in_row0, aux, a);
-                // the next tile's descriptor is normally published by now: fetch its gains and row statistics a tile early
-                const uint32_t ns = stage ^ 1u, np = stage == kSStages - 1 ? phase ^ 1u : phase;
-                aux_ready = mbar_test(&desc_bar[ns], np);
-                if (aux_ready && s_desc[ns].tn >= 0) rms_aux_load(aux, t, s_desc[ns].in_row0, s_desc[ns].tn, a);
+                split_prologue_rmsnorm(smem + stage * kStageBytes, threadIdx.x - 32, s_desc[stage].in_row0, tn, a);
             } else if constexpr (PRO != PT_PRO_NONE) {
                 split_prologue<PRO>(smem + stage * kStageBytes, threadIdx.x - 32, s_desc[stage].in_row0, tn, a);
             }
@@ -1078,9 +1063,6 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
         const int band = ct >> 5, pair = lane;
         const int chunk = pair >> 2;
         uint32_t stage = 0, phase = 0, tile_i = 0;
-        static_assert(kSStages == 2, "the RMSNorm prefetch looks at the other stage");
-        [[maybe_unused]] RmsAux aux;
-        [[maybe_unused]] bool aux_ready = false;
         while (true) {
             if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
             const int4 d0 = *reinterpret_cast<const int4 *>(&s_desc[stage]);
@@ -1088,13 +1070,7 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
             const int64_t g = d0.z;
             if (tn < 0) break;
             if constexpr (PRO == PT_PRO_RMSNORM) {
-                const int t = threadIdx.x - 32;
-                if (!aux_ready) rms_aux_load(aux, t, s_desc[stage].in_row0, tn, a);
-                split_prologue_rmsnorm(smem + stage * kStageBytes, t, s_desc[stage].in_row0, aux, a);
-                // the next tile's descriptor is normally published by now: fetch its gains and row statistics a tile early
-                const uint32_t ns = stage ^ 1u, np = stage == kSStages - 1 ? phase ^ 1u : phase;
-                aux_ready = mbar_test(&desc_bar[ns], np);
-                if (aux_ready && s_desc[ns].tn >= 0) rms_aux_load(aux, t, s_desc[ns].in_row0, s_desc[ns].tn, a);
+                split_prologue_rmsnorm(smem + stage * kStageBytes, threadIdx.x - 32, s_desc[stage].in_row0, tn, a);
             } else if constexpr (PRO != PT_PRO_NONE) {
                 split_prologue<PRO>(smem + stage * kStageBytes, threadIdx.x - 32, s_desc[stage].in_row0, tn, a);
             }
