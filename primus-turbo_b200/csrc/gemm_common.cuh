@@ -62,6 +62,10 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) 
 }
 
 inline int raster_rows(int64_t a_rows, int64_t k_bytes) {
+    if (const char *e = getenv("PT_GEMM_RASTER_M")) {   // row blocks (of 128 rows) per band, for experiments
+        const int v = atoi(e);
+        if (v > 0) return v;
+    }
     return a_rows * k_bytes <= (int64_t) 48 * 1024 * 1024 ? (1 << 20) : 16;
 }
 
