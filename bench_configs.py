@@ -469,8 +469,24 @@ def _small_case(name, args):
         for _ in range(2):
             ggi.grouped_gemm_fp8_impl(a_row, w_q, a_s_row, w_s, lens_t, offs, False, True, torch.bfloat16, SG.BLOCKWISE)
             ggi.grouped_gemm_fp8_variable_k_impl(a_col, g_col, a_s_col, g_s_col, plens, poffs, True, False, True, torch.bfloat16, SG.BLOCKWISE)
+    elif name in ("rowwise_other_axis", "rmsnorm_bwd", "rmsnorm_mx_dual"):
+        from primus_turbo.pytorch.kernels.normalization import rmsnorm_impl as ri
+        M, N = (int(args[0]), int(args[1])) if len(args) >= 2 else (8192, 4096)
+        xs = [randn_bf16((M, N), 1.0, i, dev) for i in range(3)]
+        gamma = randn_bf16((N,), 1.0, 7, dev)
+        dy = randn_bf16((M, N), 1e-2, 8, dev)
+        rstd = ri.rmsnorm_stats_impl(xs[0], 1e-6)
+        for i in range(6):
+            x = xs[i % 3]
+            if name == "rowwise_other_axis":
+                qi.quantize_fp8_rowwise_impl(x, f8, -2)
+            elif name == "rmsnorm_bwd":
+                ri.rmsnorm_bwd_impl(dy, x, gamma, rstd)
+            else:
+                qi.rmsnorm_quantize_mx_impl(x, gamma, 1e-6, False, f8, fused=True)
     else:
-        raise SystemExit(f"unknown case {name!r}: mx_dual, mxfp4_dual, blockwise_dual, swiglu_mx_dual [M N]; blockwise_grouped [G rows]")
+        raise SystemExit(f"unknown case {name!r}: mx_dual, mxfp4_dual, blockwise_dual, swiglu_mx_dual, rowwise_other_axis, "
+                         "rmsnorm_bwd, rmsnorm_mx_dual [M N]; blockwise_grouped [G rows]")
     torch.cuda.synchronize()
     print("ok", name, *args)
 
