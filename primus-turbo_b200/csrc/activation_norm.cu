@@ -318,14 +318,14 @@ __global__ void __launch_bounds__(kAnThreads, 2) rmsnorm_bwd_kernel(const T *__r
 // its way into the other half of a double buffer (16-byte cp.async; a thread reads back only what it copied itself, so
 // the buffers need no barrier).  For rows of up to 4 vectors per thread (8192 16-bit elements).  Element assignment and
 // summation order are those of rmsnorm_bwd_kernel: both give the same bits.
-template <typename T>
+template <typename T, int KEEP>
 __global__ void __launch_bounds__(kAnThreads, 3) rmsnorm_bwd_staged_kernel(const T *__restrict__ dy, const T *__restrict__ dxpr, const T *__restrict__ x,
                                                                         const T *__restrict__ gamma, const float *__restrict__ rstd_in,
                                                                         int zero_centered, int64_t rows, int64_t H, T *__restrict__ dx,
-                                                                        float *__restrict__ dg_partial) {
+                                                                        float *__restrict__ dg_partial, int stages) {
     constexpr int V = 16 / sizeof(T);
-    constexpr int kKeep = 4;
-    extern __shared__ __align__(16) uint8_t an_smem[];   // [2][x row | dy row]
+    constexpr int kKeep = KEEP;   // vectors per thread and row: 2 (rows of up to 512 vectors) or 4
+    extern __shared__ __align__(16) uint8_t an_smem[];   // [stages][x row | dy row]
     __shared__ float s_red[kAnThreads / 32];
     const int64_t row_bytes = H * (int64_t) sizeof(T);
     auto sx = [&](int b) { return reinterpret_cast<T *>(an_smem + (int64_t) b * 2 * row_bytes); };
@@ -334,12 +334,24 @@ __global__ void __launch_bounds__(kAnThreads, 3) rmsnorm_bwd_staged_kernel(const
 #pragma unroll
         for (int k = 0; k < kKeep; ++k) {
             const int64_t h = ((int64_t) k * kAnThreads + threadIdx.x) * V;
-            if (h < H) {
+            if (h < H && r < rows) {
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sm100::smem_u32(sx(b) + h)), "l"(x + r * H + h) : "memory");
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sm100::smem_u32(sd(b) + h)), "l"(dy + r * H + h) : "memory");
             }
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");   // one group per row slot, empty past the last row
+    };
+    // all but the newest stages - 2 groups have landed (the row about to be used is the oldest one in flight)
+    auto wait_oldest = [&]() {
+        switch (stages) {
+            case 2: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+            case 3: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+            case 4: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+            case 5: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+            case 6: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+            case 7: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+            default: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+        }
     };
     float dgr[kKeep][V];
 #pragma unroll
@@ -347,20 +359,76 @@ __global__ void __launch_bounds__(kAnThreads, 3) rmsnorm_bwd_staged_kernel(const
 #pragma unroll
         for (int i = 0; i < V; ++i) dgr[k][i] = 0.f;
     const float zc = zero_centered ? 1.0f : 0.0f;
+    // Two vectors per thread: the thread's gains (the same for every row) are converted once, and a row's normalised values
+    // stay in registers between its dot product and its write-out.  Four vectors per thread would spill: that form reads
+    // them from shared memory twice.
+    constexpr bool kInRegs = KEEP == 2;
+    [[maybe_unused]] float gp[kInRegs ? kKeep : 1][V];
+    if constexpr (kInRegs) {
+#pragma unroll
+        for (int k = 0; k < kKeep; ++k) {
+            const int64_t h = ((int64_t) k * kAnThreads + threadIdx.x) * V;
+            Vec<T, V> gr = {};
+            if (h < H) gr = ldv<T, V>(gamma + h);
+#pragma unroll
+            for (int i = 0; i < V; ++i) gp[k][i] = an_to_f<T>(gr.e[i]) + zc;
+        }
+    }
+    // Ring of `stages` row slots: stages - 1 rows are on their way while one is processed (a CTA keeps
+    // (stages - 1) x 2 rows of bytes in flight; with one row ahead, three CTAs per SM of 4096-element rows asked for 48 KB
+    // at a time and the kernel ran at the memory latency, not the bandwidth).
     int b = 0;
-    if ((int64_t) blockIdx.x < rows) issue(blockIdx.x, 0);
-    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x, b ^= 1) {
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        if (r + gridDim.x < rows) issue(r + gridDim.x, b ^ 1);
+    for (int s0 = 0; s0 < stages - 1; ++s0) issue((int64_t) blockIdx.x + (int64_t) s0 * gridDim.x, s0);
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x, b = b + 1 == stages ? 0 : b + 1) {
+        wait_oldest();
+        issue(r + (int64_t) (stages - 1) * gridDim.x, b == 0 ? stages - 1 : b - 1);   // the slot this thread read one row ago
         const float rstd = rstd_in[r];
         float acc = 0.f;
+        if constexpr (!kInRegs) {
+#pragma unroll
+            for (int k = 0; k < kKeep; ++k) {
+                const int64_t h = ((int64_t) k * kAnThreads + threadIdx.x) * V;
+                if (h < H) {
+                    const Vec<T, V> xv = ldv_plain<T, V>(sx(b) + h), dv = ldv_plain<T, V>(sd(b) + h), gr = ldv<T, V>(gamma + h);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) acc += an_to_f<T>(dv.e[i]) * (an_to_f<T>(gr.e[i]) + zc) * (an_to_f<T>(xv.e[i]) * rstd);
+                }
+            }
+            const float m = block_sum(acc, s_red) / (float) H;
+#pragma unroll
+            for (int k = 0; k < kKeep; ++k) {
+                const int64_t h = ((int64_t) k * kAnThreads + threadIdx.x) * V;
+                if (h < H) {
+                    const Vec<T, V> xv = ldv_plain<T, V>(sx(b) + h), dv = ldv_plain<T, V>(sd(b) + h), gr = ldv<T, V>(gamma + h);
+                    Vec<T, V> pr = {};
+                    if (dxpr != nullptr) pr = ldv<T, V>(dxpr + r * H + h);
+                    Vec<T, V> o;
+#pragma unroll
+                    for (int i = 0; i < V; ++i) {
+                        const float x_hat = an_to_f<T>(xv.e[i]) * rstd, d = an_to_f<T>(dv.e[i]);
+                        float v = (d * (an_to_f<T>(gr.e[i]) + zc) - x_hat * m) * rstd;
+                        if (dxpr != nullptr) v += an_to_f<T>(pr.e[i]);
+                        o.e[i] = an_from_f<T>(v);
+                        dgr[k][i] += d * x_hat;
+                    }
+                    stv<T, V>(dx + r * H + h, o);
+                }
+            }
+            continue;
+        }
+        float xh[kInRegs ? kKeep : 1][V];
+        Vec<T, V> dvk[kInRegs ? kKeep : 1];
 #pragma unroll
         for (int k = 0; k < kKeep; ++k) {
             const int64_t h = ((int64_t) k * kAnThreads + threadIdx.x) * V;
             if (h < H) {
-                const Vec<T, V> xv = ldv_plain<T, V>(sx(b) + h), dv = ldv_plain<T, V>(sd(b) + h), gr = ldv<T, V>(gamma + h);
+                const Vec<T, V> xv = ldv_plain<T, V>(sx(b) + h);
+                dvk[k] = ldv_plain<T, V>(sd(b) + h);
 #pragma unroll
-                for (int i = 0; i < V; ++i) acc += an_to_f<T>(dv.e[i]) * (an_to_f<T>(gr.e[i]) + zc) * (an_to_f<T>(xv.e[i]) * rstd);
+                for (int i = 0; i < V; ++i) {
+                    xh[k][i] = an_to_f<T>(xv.e[i]) * rstd;
+                    acc += an_to_f<T>(dvk[k].e[i]) * gp[k][i] * xh[k][i];
+                }
             }
         }
         const float m = block_sum(acc, s_red) / (float) H;
@@ -368,14 +436,13 @@ __global__ void __launch_bounds__(kAnThreads, 3) rmsnorm_bwd_staged_kernel(const
         for (int k = 0; k < kKeep; ++k) {
             const int64_t h = ((int64_t) k * kAnThreads + threadIdx.x) * V;
             if (h < H) {
-                const Vec<T, V> xv = ldv_plain<T, V>(sx(b) + h), dv = ldv_plain<T, V>(sd(b) + h), gr = ldv<T, V>(gamma + h);
                 Vec<T, V> pr = {};
                 if (dxpr != nullptr) pr = ldv<T, V>(dxpr + r * H + h);
                 Vec<T, V> o;
 #pragma unroll
                 for (int i = 0; i < V; ++i) {
-                    const float x_hat = an_to_f<T>(xv.e[i]) * rstd, d = an_to_f<T>(dv.e[i]);
-                    float v = (d * (an_to_f<T>(gr.e[i]) + zc) - x_hat * m) * rstd;
+                    const float x_hat = xh[k][i], d = an_to_f<T>(dvk[k].e[i]);
+                    float v = (d * gp[k][i] - x_hat * m) * rstd;
                     if (dxpr != nullptr) v += an_to_f<T>(pr.e[i]);
                     o.e[i] = an_from_f<T>(v);
                     dgr[k][i] += d * x_hat;
@@ -396,13 +463,29 @@ __global__ void __launch_bounds__(kAnThreads, 3) rmsnorm_bwd_staged_kernel(const
 }
 
 // dgamma[h] = sum over parts of dg_partial[part, h]
+// A CTA owns 32 columns; its 16 warps take every 16th part (128-byte coalesced reads, four in flight) and their sums meet
+// in shared memory in a fixed order.  (One thread per column over all parts left 8-16 CTAs walking 444 dependent rows of
+// the partial array: tens of microseconds behind every backward.)
+constexpr int kDgLanes = 16;
 template <typename T>
-__global__ void __launch_bounds__(256) rmsnorm_dgamma_kernel(const float *__restrict__ dg_partial, int parts, int64_t H, T *__restrict__ dgamma) {
-    const int64_t h = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
-    if (h >= H) return;
-    float s = 0.f;
-    for (int p = 0; p < parts; ++p) s += dg_partial[(int64_t) p * H + h];
-    dgamma[h] = an_from_f<T>(s);
+__global__ void __launch_bounds__(32 * kDgLanes) rmsnorm_dgamma_kernel(const float *__restrict__ dg_partial, int parts, int64_t H,
+                                                                      T *__restrict__ dgamma) {
+    __shared__ float s_part[kDgLanes][33];
+    const int c = threadIdx.x & 31, pl = threadIdx.x >> 5;
+    const int64_t h = (int64_t) blockIdx.x * 32 + c;
+    float acc = 0.f;
+    if (h < H) {
+#pragma unroll 4
+        for (int p = pl; p < parts; p += kDgLanes) acc += dg_partial[(int64_t) p * H + h];
+    }
+    s_part[pl][c] = acc;
+    __syncthreads();
+    if (pl == 0 && h < H) {
+        float t = 0.f;
+#pragma unroll
+        for (int i = 0; i < kDgLanes; ++i) t += s_part[i][c];
+        dgamma[h] = an_from_f<T>(t);
+    }
 }
 
 static int an_grid(int64_t rows) { return (int) std::min<int64_t>(rows, (int64_t) sm_count() * 8); }
@@ -485,11 +568,14 @@ int pt_rmsnorm_bwd(const void *dy, const void *dxpr, const void *x, const void *
     PT_SWITCH_SRC(dtype, T, {
         constexpr int VW = 16 / sizeof(T);
         if (vec && H <= (int64_t) kAnThreads * VW * 4 && getenv("PT_RMSNORM_BWD_NO_STAGE") == nullptr) {
-            const int smem = (int) (4 * H * (int64_t) sizeof(T));
-            auto kern = rmsnorm_bwd_staged_kernel<T>;
+            // as many row slots as fit 72 KiB (three CTAs per SM), between 2 and 8
+            const int64_t slot_bytes = 2 * H * (int64_t) sizeof(T);
+            const int stages = (int) std::max<int64_t>(2, std::min<int64_t>(8, (72 * 1024) / slot_bytes));
+            const int smem = (int) (stages * slot_bytes);
+            auto kern = H <= (int64_t) kAnThreads * VW * 2 ? rmsnorm_bwd_staged_kernel<T, 2> : rmsnorm_bwd_staged_kernel<T, 4>;
             PT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
             kern<<<parts, kAnThreads, smem, st>>>((const T *) dy, (const T *) dxpr, (const T *) x, (const T *) gamma, rstd, zero_centered, rows, H, (T *) dx,
-                                                  dg_partial);
+                                                  dg_partial, stages);
         } else if (vec)
             rmsnorm_bwd_kernel<T, VW><<<parts, kAnThreads, 0, st>>>((const T *) dy, (const T *) dxpr, (const T *) x, (const T *) gamma, rstd, zero_centered, rows,
                                                                     H, (T *) dx, dg_partial);
@@ -497,7 +583,7 @@ int pt_rmsnorm_bwd(const void *dy, const void *dxpr, const void *x, const void *
             rmsnorm_bwd_kernel<T, 1><<<parts, kAnThreads, 0, st>>>((const T *) dy, (const T *) dxpr, (const T *) x, (const T *) gamma, rstd, zero_centered, rows, H,
                                                                    (T *) dx, dg_partial);
         PT_LAUNCH_OK();
-        rmsnorm_dgamma_kernel<T><<<(unsigned) ceil_div(H, 256), 256, 0, st>>>(dg_partial, parts, H, (T *) dgamma);
+        rmsnorm_dgamma_kernel<T><<<(unsigned) ceil_div(H, 32), 32 * kDgLanes, 0, st>>>(dg_partial, parts, H, (T *) dgamma);
     });
     PT_LAUNCH_OK();
     return PT_OK;

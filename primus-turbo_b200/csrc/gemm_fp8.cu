@@ -153,7 +153,7 @@ __global__ void __launch_bounds__(128) sf_retile_kernel(RetileArgs args_a, Retil
             const int64_t row = row_start + r;
             uint32_t w = 0;
             if (r < rows_in_block && row < a.src_rows && lane < nkb && (kb0 + lane) * 4 < a.sf_ld)
-                w = __ldg(reinterpret_cast<const uint32_t *>(a.src + row * a.sf_ld) + kb0 + lane);
+                w = __ldcg(reinterpret_cast<const uint32_t *>(a.src + row * a.sf_ld) + kb0 + lane);   // written by the kernel before: not the read-only path
             s_words[r][lane] = w;
         }
         __syncthreads();
@@ -180,8 +180,8 @@ __device__ __forceinline__ void epilogue_store_block(const GemmParams &p, uint32
     const int lanes_per_row = (32 * esize) / 16;      // 4 (16-bit) or 8 (fp32)
     const int rows_per_pass = 32 / lanes_per_row;     // 8 or 4
     float row_scale = 1.f;
-    if (MODE == GEMM_TENSOR) row_scale = __ldg(p.sa) * __ldg(p.sb);
-    if (MODE == GEMM_ROW) row_scale = (tile_row0 + lane < c_row_end) ? __ldg(p.sa + tile_row0 + lane) : 0.f;
+    if (MODE == GEMM_TENSOR) row_scale = __ldcg(p.sa) * __ldcg(p.sb);   // scales may come from the kernel launched just before: no read-only path
+    if (MODE == GEMM_ROW) row_scale = (tile_row0 + lane < c_row_end) ? __ldcg(p.sa + tile_row0 + lane) : 0.f;
     const int n_end = min(p.N, n0 + BLOCK_N);  // a last partial chunk reads past the tile; masked below
 #pragma unroll 1
     for (int c = c_begin; c < c_end; ++c) {
@@ -205,7 +205,7 @@ __device__ __forceinline__ void epilogue_store_block(const GemmParams &p, uint32
         for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]) * row_scale;
         if (MODE == GEMM_ROW) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) f[i] *= (col0 + i < n_end) ? __ldg(p.sb + (int64_t) gi * p.b_group_rows + col0 + i) : 0.f;
+            for (int i = 0; i < 32; ++i) f[i] *= (col0 + i < n_end) ? __ldcg(p.sb + (int64_t) gi * p.b_group_rows + col0 + i) : 0.f;
         }
         // stage this thread's row
         uint8_t *my = stg + lane * pitch;
@@ -466,7 +466,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             const bool have_acc = kb_count > 0;
             const int64_t tile_row0 = c_row_base + (int64_t) m_blk * BLOCK_M + q * 32;
             const int n0 = n_blk * BLOCK_N;
-            if (have_acc && !(ok = mbar_wait(&tmem_full_bar[acc_stage], acc_phase, abort_flag))) break;
+            if (have_acc && !(ok = mbar_wait_warp(&tmem_full_bar[acc_stage], acc_phase, abort_flag))) break;
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t) (q * 32) << 16) + acc_stage * BLOCK_N;
             epilogue_store_block<BLOCK_N, MODE>(p, taddr, have_acc, tile_row0, c_row_end, n0, gi, stg, lane, 0, (BLOCK_N + 31) / 32,

@@ -154,7 +154,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kBwThreads, 1)
             const float *srcb = p.sb.base + (int64_t) gi * p.sb.group_stride + (int64_t) kb_begin * p.sb.kb_stride + (int64_t) nb * p.sb.row_stride;
             for (int kb = 0; kb < kb_count; ++kb, ++step) {
                 const uint32_t slot = step % kBwSlabRing;
-                if (!(ok = mbar_wait(&scale_empty_bar[slot], ((step / kBwSlabRing) & 1u) ^ 1u, abort_flag))) break;
+                if (!(ok = mbar_wait_warp(&scale_empty_bar[slot], ((step / kBwSlabRing) & 1u) ^ 1u, abort_flag))) break;
                 float *slot_ptr = smem_scale + slot * kBwScaleSlot;
                 cp_async_4(slot_ptr + lt, src0 + (int64_t) kb * p.sa.kb_stride);
                 cp_async_4(slot_ptr + lt + 64, src1 + (int64_t) kb * p.sa.kb_stride);
@@ -225,10 +225,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kBwThreads, 1)
 
             for (int kb = 0; kb < kb_count; ++kb, ++step) {
                 // scales (and the B slab) of this K step, staged by this CTA's loader warps / producer
-                if (!(ok = mbar_wait(&scale_full_bar[step % kBwSlabRing], (step / kBwSlabRing) & 1u, abort_flag))) break;
+                if (!(ok = mbar_wait_warp(&scale_full_bar[step % kBwSlabRing], (step / kBwSlabRing) & 1u, abort_flag))) break;
                 if constexpr (SBM == SB_SLAB)
-                    if (!(ok = mbar_wait(&slab_full_bar[step % kBwSlabRing], (step / kBwSlabRing) & 1u, abort_flag))) break;
-                if (!(ok = mbar_wait(&part_full_bar[pb], pphase, abort_flag))) break;
+                    if (!(ok = mbar_wait_warp(&slab_full_bar[step % kBwSlabRing], (step / kBwSlabRing) & 1u, abort_flag))) break;
+                if (!(ok = mbar_wait_warp(&part_full_bar[pb], pphase, abort_flag))) break;
                 tc_fence_after_sync();
                 const uint32_t taddr = tmem_base + ((uint32_t) (q * 32) << 16) + pb * BW_BLOCK_N + half * 128;
                 // TMEM reads are issued one chunk ahead of the FMAs that consume them

@@ -250,7 +250,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((PairCfg<BLOCK_N, mo
             const bool have_acc = kb_count > 0;
             const int64_t tile_row0 = c_row_base + (int64_t) m_blk * kTileM + (int64_t) rank * BLOCK_M + q * 32;
             const int n0 = n_blk * BLOCK_N;
-            if (have_acc && !(ok = mbar_wait(&tmem_full_bar[acc_stage], acc_phase, abort_flag))) break;
+            if (have_acc && !(ok = mbar_wait_warp(&tmem_full_bar[acc_stage], acc_phase, abort_flag))) break;
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t) (q * 32) << 16) + acc_stage * BLOCK_N;
             const uint32_t release_addr = map_to_rank(&tmem_empty_bar[acc_stage], 0);

@@ -327,7 +327,7 @@ __global__ void __launch_bounds__(kBqThreads, kBqCtasPerSm)
         const int c_box = lane >> 4, c_chunk = (lane & 15) >> 1, c_off = (lane & 1) << 3;
         uint32_t stage = 0, phase = 0, tile_count = 0;
         while (true) {
-            if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
+            if (!(ok = mbar_wait_warp(&full_bar[stage], phase, abort_flag))) break;
             const int4 d0 = *reinterpret_cast<const int4 *>(&s_desc[stage]);
             if (d0.z < 0) break;
             const int64_t batch = d0.x, pid_m = d0.y, col_blk = d0.z, in_row0 = d0.w;
@@ -390,7 +390,7 @@ __global__ void __launch_bounds__(kBqThreads, kBqCtasPerSm)
                 w_amax = warp_max(fmaxf(lo_f32<T>(m), hi_f32<T>(m)));
                 if (lane == 0) s_wmax[buf][cw] = w_amax;
             }
-            if constexpr (kCol || kWeight) asm volatile("bar.sync 1, %0;" ::"n"(kBqConsumerWarps * 32) : "memory");
+            if constexpr (kCol || kWeight) sm100::named_barrier<1, kBqConsumerWarps * 32>();
 
             // ---- row pass
             if constexpr (kRow || kWeight) {
@@ -578,7 +578,7 @@ __global__ void __launch_bounds__(kBsThreads, kBsCtasPerSm)
         const int row = threadIdx.x - 32;
         uint32_t stage = 0, phase = 0;
         while (true) {
-            if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
+            if (!(ok = mbar_wait_warp(&full_bar[stage], phase, abort_flag))) break;
             const int4 d0 = *reinterpret_cast<const int4 *>(&s_desc[stage]);
             if (d0.z < 0) break;
             const int pid_m = d0.y, col_blk = d0.z, in_row0 = d0.w;
@@ -615,7 +615,7 @@ __global__ void __launch_bounds__(kBsThreads, kBsCtasPerSm)
             const bool whole = !SEG || n_valid == kBlk;
             if (whole) {
                 if (row == 0) bulk_wait_read_all();   // the previous tile's store has read the staging tile
-                asm volatile("bar.sync 1, %0;" ::"n"(kBsGroupThreads) : "memory");
+                sm100::named_barrier<1, kBsGroupThreads>();
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -631,7 +631,7 @@ __global__ void __launch_bounds__(kBsThreads, kBsCtasPerSm)
             }
             if (whole) {
                 fence_proxy_async_smem();
-                asm volatile("bar.sync 1, %0;" ::"n"(kBsGroupThreads) : "memory");
+                sm100::named_barrier<1, kBsGroupThreads>();
                 if (row == 0) {
                     tma_store_2d(&tmap_qrow, row_stage, (int) n0, in_row0);   // clipped at the matrix edges
                     bulk_commit_group();
@@ -646,7 +646,7 @@ __global__ void __launch_bounds__(kBsThreads, kBsCtasPerSm)
         const int box = pair >> 5, chunk = (pair & 31) >> 2, sub = (pair & 3) << 2;
         uint32_t stage = 0, phase = 0, tile_i = 0;
         while (true) {
-            if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
+            if (!(ok = mbar_wait_warp(&full_bar[stage], phase, abort_flag))) break;
             const int4 d0 = *reinterpret_cast<const int4 *>(&s_desc[stage]);
             if (d0.z < 0) break;
             const int pid_m = d0.y, col_blk = d0.z;
@@ -670,7 +670,7 @@ __global__ void __launch_bounds__(kBsThreads, kBsCtasPerSm)
             for (int r = 0; r < 64; ++r) m2 = absmax2<T>(m2, w[r]);
             s_cmax[buf][ct] = m2;   // [band][pair] flattened: ct = 64 band + pair
             if (ct == 0) bulk_wait_read_all();   // the previous tile's store has read the staging tile
-            asm volatile("bar.sync 2, %0;" ::"n"(kBsGroupThreads) : "memory");
+            sm100::named_barrier<2, kBsGroupThreads>();
             m2 = absmax2_done(absmax2<T>(m2, s_cmax[buf][ct ^ 64]));
             const float sc0 = scale_from_amax<FMT>(lo_f32<T>(m2), kEpsBlock), sc1 = scale_from_amax<FMT>(hi_f32<T>(m2), kEpsBlock);
             const int64_t n0 = (int64_t) col_blk * kBlk;
@@ -689,7 +689,7 @@ __global__ void __launch_bounds__(kBsThreads, kBsCtasPerSm)
                 }
             }
             fence_proxy_async_smem();
-            asm volatile("bar.sync 2, %0;" ::"n"(kBsGroupThreads) : "memory");
+            sm100::named_barrier<2, kBsGroupThreads>();
             if (ct == 0) {
                 tma_store_2d(&tmap_qcol, col_stage, (int) n0, pid_m * kBlk);
                 bulk_commit_group();

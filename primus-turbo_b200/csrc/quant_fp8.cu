@@ -42,7 +42,9 @@ constexpr float kEpsTensor = 1e-12f;
 // ------------------------------------------------------------------------------------------------
 // amax over a flat array: 8-element vectors, 4 in flight per thread, one atomicMax per block.
 // Entry of a kernel launched with launch_overlapped(): wait until every earlier kernel of the stream has completed (its
-// results are then visible), then let the next kernel of the stream begin its own launch.
+// results are then visible), then let the next kernel of the stream begin its own launch.  Only the second kernel of a
+// quantizer is launched that way: its grid exists before the first one has finished, so what the first one wrote (the
+// amax words) is read with __ldcg, never through the read-only path; x was complete before the first kernel started.
 __device__ __forceinline__ void pdl_enter() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -98,7 +100,7 @@ __global__ void __launch_bounds__(kThreads)
     pdl_enter();
     float scale;
     if (scale_opt != nullptr) scale = __ldg(scale_opt);
-    else scale = scale_from_amax<FMT>(__uint_as_float(*amax_bits), kEpsTensor);
+    else scale = scale_from_amax<FMT>(__uint_as_float(__ldcg(amax_bits)), kEpsTensor);   // from the kernel before: not the read-only path
     const int64_t tid = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t nthreads = (int64_t) gridDim.x * blockDim.x;
     if (tid == 0) *scale_inv = __fdiv_rn(1.0f, scale);
@@ -315,7 +317,8 @@ __global__ void __launch_bounds__(kThreads)
     const int64_t r0 = (int64_t) blockIdx.y * kAmaxVecRows + warp * 16;
     float sc[8];
     {
-        const uint4 a0 = *reinterpret_cast<const uint4 *>(amax_bits + b * N + c0), a1 = *reinterpret_cast<const uint4 *>(amax_bits + b * N + c0 + 4);
+        // written by the amax kernel this launch overlaps: not the read-only path
+        const uint4 a0 = __ldcg(reinterpret_cast<const uint4 *>(amax_bits + b * N + c0)), a1 = __ldcg(reinterpret_cast<const uint4 *>(amax_bits + b * N + c0 + 4));
         const uint32_t ab[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
 #pragma unroll
         for (int k = 0; k < 8; ++k) sc[k] = scale_from_amax<FMT>(__uint_as_float(ab[k]), kEpsTensor);
@@ -463,7 +466,8 @@ int pt_quantize_fp8_tensorwise(const void *x, int x_dtype, int64_t n, int fmt, v
         if (!scale_opt) {
             PT_CUDA_OK(cudaMemsetAsync(amax, 0, 4, st));
             const int blocks = (int) std::max<int64_t>(1, std::min(max_blocks, ceil_div(n, (int64_t) kThreads * 32)));
-            PT_CUDA_OK(launch_overlapped(amax_flat_kernel<T>, dim3(blocks), dim3(kThreads), 0, st, (const T *) x, n, vec_ok, amax));
+            amax_flat_kernel<T><<<blocks, kThreads, 0, st>>>((const T *) x, n, vec_ok, amax);   // reads x through the read-only path: an ordinary launch
+            PT_LAUNCH_OK();
         }
         const int blocks = (int) std::max<int64_t>(1, std::min(max_blocks * 2, ceil_div(n, (int64_t) kThreads * 16)));
         PT_SWITCH_FP8(fmt, F, {
@@ -490,8 +494,8 @@ int pt_quantize_fp8_rowwise(const void *x, int x_dtype, int64_t B, int64_t M, in
             PT_SWITCH_FP8(fmt, F, {
                 if constexpr (sizeof(T) == 2) {
                     if (vec_ok && !scale_opt && N <= (int64_t) kThreads * 8 * 4) {
-                        PT_CUDA_OK(launch_overlapped(rowwise_row_in_regs_kernel<T, F>, dim3(blocks), dim3(kThreads), 0, st, (const T *) x, rows, N,
-                                                     (uint8_t *) q, scale_inv));
+                        rowwise_row_in_regs_kernel<T, F><<<blocks, kThreads, 0, st>>>((const T *) x, rows, N, (uint8_t *) q, scale_inv);
+                        PT_LAUNCH_OK();
                         return PT_OK;
                     }
                 }
@@ -517,7 +521,7 @@ int pt_quantize_fp8_rowwise(const void *x, int x_dtype, int64_t B, int64_t M, in
             if constexpr (sizeof(T) == 2) {
                 if (vec_ok) {
                     dim3 grid((unsigned) ceil_div(N, kAmaxVecCols), (unsigned) ceil_div(M, kAmaxCtaRows), (unsigned) B);
-                    PT_CUDA_OK(launch_overlapped(amax_cols_vec_kernel<T>, grid, dim3(kThreads), 0, st, (const T *) x, M, N, amax));
+                    amax_cols_vec_kernel<T><<<grid, kThreads, 0, st>>>((const T *) x, M, N, amax);   // reads x through the read-only path: an ordinary launch
                     done = true;
                 }
             }

@@ -488,7 +488,7 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
             if constexpr (GROUPED)
                 if (!locate_group(tm, in_row0, n_valid, row_out0)) continue;
             ++tile_count;
-            if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
+            if (!(ok = mbar_wait_warp(&full_bar[stage], phase, abort_flag))) break;
             const SwizzledTile<T> tile{smem + stage * kQTileBytes};
             unsigned(*amax2d)[2] = s_amax2d[tile_count % 3];
 
@@ -527,7 +527,7 @@ __global__ void __launch_bounds__(kQThreads, kQCtasPerSm)
                 m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
                 m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
                 if (lane < 2) atomicMax(&amax2d[r_row >> 5][r_blk], __float_as_uint(m));
-                asm volatile("bar.sync 1, %0;" ::"n"(kQConsumerWarps * 32));
+                sm100::named_barrier<1, kQConsumerWarps * 32>();
             }
 
             if constexpr (ROW) {
@@ -747,6 +747,11 @@ template <int FMT> __device__ __forceinline__ void encode_row_block(const uint32
     }
 }
 
+// Loads in kernels that are launched to overlap their predecessor (launch_overlapped) and read what it wrote: the grid
+// exists before that data does, and the read-only path (ld.global.nc, __ldg, const __restrict__ kernel parameters) is
+// defined for data that does not change during the grid's lifetime.  These kernels therefore read such data (row
+// statistics, probabilities, gains, scales) with __ldcg.
+//
 // Fused prologues: what is quantized is f(x), computed once per tile in shared memory by all eight consumer warps before
 // the two groups go their own ways.  The arithmetic is that of the stand-alone kernels (act_math.cuh), rounded to bf16
 // as they round, so "activation kernel, then quantizer" and the fused kernel write the same bytes.
@@ -770,11 +775,11 @@ __device__ __forceinline__ void split_prologue_rmsnorm(uint8_t *tile, int t, int
     RmsAux x;
     const int64_t n = (int64_t) tn * kTileN + c * 8;
     x.gv = make_uint4(0u, 0u, 0u, 0u);
-    if (n < a.N) x.gv = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(a.pro_gamma) + n));
+    if (n < a.N) x.gv = __ldcg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(a.pro_gamma) + n));
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const int64_t grow = (int64_t) in_row0 + r0 + 32 * j;
-        x.rv[j] = grow < a.M ? __ldg(a.pro_rowvec + grow) : 0.f;
+        x.rv[j] = grow < a.M ? __ldcg(a.pro_rowvec + grow) : 0.f;
     }
     const uint32_t gw[4] = {x.gv.x, x.gv.y, x.gv.z, x.gv.w};
     const float zc = a.pro_zero_centered ? 1.0f : 0.0f;
@@ -803,7 +808,7 @@ __device__ __forceinline__ void split_prologue_rmsnorm(uint8_t *tile, int t, int
         *reinterpret_cast<uint4 *>(pa) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
     sm100::fence_proxy_async_smem();   // the next bulk load into this stage must order after these writes
-    asm volatile("bar.sync 3, %0;" ::"n"(2 * kSGroupThreads) : "memory");
+    sm100::named_barrier<3, 2 * kSGroupThreads>();
 }
 
 // t: 0 .. 255 over the consumer threads; thread (row = t / 2, half = t % 2) transforms 32 elements of its row in place
@@ -813,9 +818,9 @@ __device__ __forceinline__ void split_prologue(uint8_t *tile, int t, int in_row0
     const int row = t >> 1, half = t & 1;
     const int64_t grow = (int64_t) in_row0 + row;
     const bool in = grow < a.M;
-    const float rv = in ? __ldg(a.pro_rowvec + grow) : 0.f;
+    const float rv = in ? __ldcg(a.pro_rowvec + grow) : 0.f;
     bool masked = false;
-    if constexpr (pro_is_glu(PRO)) masked = in && a.pro_mask != nullptr && __ldg(a.pro_mask + grow) == 0;
+    if constexpr (pro_is_glu(PRO)) masked = in && a.pro_mask != nullptr && __ldcg(a.pro_mask + grow) == 0;
     uint8_t *rp = tile + row * 128;
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
@@ -838,7 +843,7 @@ __device__ __forceinline__ void split_prologue(uint8_t *tile, int t, int in_row0
         } else {
             const int64_t n = (int64_t) tn * kTileN + chunk * 8;
             uint4 gv = make_uint4(0u, 0u, 0u, 0u);
-            if (n < a.N) gv = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(a.pro_gamma) + n));
+            if (n < a.N) gv = __ldcg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(a.pro_gamma) + n));
             const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
             const float zc = a.pro_zero_centered ? 1.0f : 0.0f;
 #pragma unroll
@@ -851,7 +856,7 @@ __device__ __forceinline__ void split_prologue(uint8_t *tile, int t, int in_row0
         *reinterpret_cast<uint4 *>(pa) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
     sm100::fence_proxy_async_smem();   // the next bulk load into this stage must order after these writes
-    asm volatile("bar.sync 3, %0;" ::"n"(2 * kSGroupThreads) : "memory");
+    sm100::named_barrier<3, 2 * kSGroupThreads>();
 }
 
 // ROWSTAGE: the row-wise copy is staged and written by TMA (dense FP8); otherwise by 32-byte stores from registers.
@@ -947,7 +952,7 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
         const int row = threadIdx.x - 32;
         uint32_t stage = 0, phase = 0, tile_i = 0;
         while (true) {
-            if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
+            if (!(ok = mbar_wait_warp(&full_bar[stage], phase, abort_flag))) break;
             const int4 d0 = *reinterpret_cast<const int4 *>(&s_desc[stage]);
             const int2 d1 = *reinterpret_cast<const int2 *>(&s_desc[stage].n_valid);
             const int tn = d0.x, tm = d0.y, n_valid = d1.x, row_out0 = d1.y;
@@ -1045,7 +1050,7 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
             if constexpr (ROWSTAGE) {
                 fence_proxy_async_smem();
                 if (row == 0) bulk_wait_read_all();   // the store of the previous tile has read the other buffer
-                asm volatile("bar.sync 1, %0;" ::"n"(kSGroupThreads) : "memory");
+                sm100::named_barrier<1, kSGroupThreads>();
                 if (row == 0) {
                     tma_store_3d(&tmap_qrow, row_stage + buf * kSStageOutBytes, (int) n0, tm * kTileM, (int) g);
                     bulk_commit_group();
@@ -1064,7 +1069,7 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
         const int chunk = pair >> 2;
         uint32_t stage = 0, phase = 0, tile_i = 0;
         while (true) {
-            if (!(ok = mbar_wait(&full_bar[stage], phase, abort_flag))) break;
+            if (!(ok = mbar_wait_warp(&full_bar[stage], phase, abort_flag))) break;
             const int4 d0 = *reinterpret_cast<const int4 *>(&s_desc[stage]);
             const int tn = d0.x, tm = d0.y;
             const int64_t g = d0.z;
@@ -1200,7 +1205,7 @@ __global__ void __launch_bounds__(kSThreads, COLRHT ? 2 : split_ctas_per_sm(PRO)
             }
             fence_proxy_async_smem();
             if (ct == 0) bulk_wait_read_all();   // the store of the previous tile has read the other buffer
-            asm volatile("bar.sync 2, %0;" ::"n"(kSGroupThreads) : "memory");
+            sm100::named_barrier<2, kSGroupThreads>();
             const int64_t m0 = (int64_t) tm * kTileM, n0 = (int64_t) tn * kTileN;
             if (ct == 0) {
                 tma_store_3d(&tmap_qcol, cs, (int) (kFp4 ? m0 / 2 : m0), (int) n0, (int) g);

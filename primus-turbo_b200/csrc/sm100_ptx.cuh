@@ -80,6 +80,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     return mbar_wait_limited(bar, parity, abort_flag, kWaitLimitNs);
 }
 
+// The wait of a whole warp (all 32 lanes call it): every lane polls, then one vote makes the outcome the same in all lanes
+// and brings the warp back together, so that what follows (named barriers, .sync.aligned tensor-memory instructions, an
+// early exit on a timeout) is executed by the warp as one.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)) != 0;
+}
+
 // 3-D tiled load global -> this CTA's shared memory, completion counted in bytes on `bar`.
 __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *m, uint64_t *bar, int c0, int c1, int c2) {
     asm volatile(
@@ -119,6 +126,15 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t *bar) {
 }
 
 // ------------------------------------------------------------------ proxies / fences
+// Named barrier among COUNT threads (whole warps).  Lanes leave the polling loops of mbar_wait one by one and nothing
+// obliges the compiler to bring them together again before a barrier written in inline assembly; a warp that executes the
+// aligned form (bar.sync) in two parts is counted twice, which completed a 256-thread barrier one warp early (B200, three
+// CTAs per SM: a few times in a hundred launches another warp then read a tile that warp was still rewriting).  So the
+// warp is reconverged first and the barrier is the unaligned form, which counts threads.
+template <int ID, int COUNT> __device__ __forceinline__ void named_barrier() {
+    __syncwarp();
+    asm volatile("barrier.sync %0, %1;" ::"n"(ID), "n"(COUNT) : "memory");
+}
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
