@@ -194,13 +194,14 @@ def _sub_records(args, dev, peaks, world, rank):
         torch.cuda.empty_cache()
 
     if world == 1:
+        # the bandwidth-bound records first, before the GEMM records have pushed the GPU into its power cap
         attempt("quantize", lambda: bc.quantize_records(dev, peaks))
+        attempt("streaming_f2_f4", lambda: bc.streaming_records(dev, peaks))
         attempt("dense_bwd_c2", lambda: bc.dense_bwd_c2(dev, peaks))
         attempt("mx_c3", lambda: bc.mx_c3(dev, peaks))
         attempt("grouped_blockwise_c4", lambda: bc.grouped_blockwise_c4(dev, peaks))
         attempt("grouped_mxfp4_c5", lambda: bc.grouped_mxfp4_c5(dev, peaks))
         attempt("grouped_mxfp4_c5_sweep", lambda: bc.mxfp4_c5_sweep(dev, peaks))
-        attempt("streaming_f2_f4", lambda: bc.streaming_records(dev, peaks))
     else:
         import bench_sharded as bs
         attempt("expert_sharded_c4", lambda: bs.expert_sharded_c4(dev, peaks, world, rank))

@@ -253,3 +253,18 @@ def test_glu_quantize_mxfp4_with_hadamard_columns_fused_equals_two_kernels(act):
         assert torch.equal(f[0].view(torch.uint8)[sum(lens[:i]):sum(lens[:i + 1])], u[0].view(torch.uint8)[sum(lens[:i]):sum(lens[:i + 1])])
         assert torch.equal(f[2].view(torch.uint8)[:, c0 // 2:c1 // 2], u[2].view(torch.uint8)[:, c0 // 2:c1 // 2])
         assert torch.equal(f[3].view(torch.uint8)[:, c0 // 32:c1 // 32], u[3].view(torch.uint8)[:, c0 // 32:c1 // 32])
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float8_e4m3fn, torch.float4_e2m1fn_x2])
+def test_fused_rmsnorm_quantizer_gives_the_same_bytes_every_launch(out_dtype):
+    """Thirty launches on an input of 3584 tiles (three CTAs per SM, every warp role busy) must all write the bytes of the
+    two-kernel path: a barrier between the in-place normalisation and the row / column passes that lets one warp through
+    early shows up here as a handful of blocks quantized from half-normalised data in a few launches of a hundred."""
+    from primus_turbo.pytorch.kernels.quantization.quantization_impl import rmsnorm_quantize_mx_impl
+    rows, H = 4096, 7168
+    g = torch.Generator(device="cuda").manual_seed(rows + H)
+    x = torch.randn(rows, H, device="cuda", dtype=torch.bfloat16, generator=g) * 2
+    gamma = torch.randn(H, device="cuda", dtype=torch.bfloat16, generator=g)
+    plain = rmsnorm_quantize_mx_impl(x, gamma, 1e-6, False, out_dtype, fused=False)
+    for _ in range(30):
+        _same(rmsnorm_quantize_mx_impl(x, gamma, 1e-6, False, out_dtype, fused=True), plain)
