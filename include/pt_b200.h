@@ -383,8 +383,9 @@ int pt_rmsnorm_bwd(const void *dy, const void *dxpr, const void *x, const void *
 
 /* MX quantization of a gated activation in one pass: what pt_glu_fwd followed by pt_quantize_mx (flags PT_MX_ROW |
  * PT_MX_COL) writes, byte for byte, without the [rows, H] intermediate in memory.  x bf16 [rows, 2H]; H a multiple of 64;
- * fmt PT_E4M3 or PT_E2M1; outputs laid out as pt_quantize_mx's.  PT_ERR_UNSUPPORTED outside that range (the caller then
- * runs the two kernels).  Covers the SwiGLU -> quantize step between the two grouped GEMMs of an expert MLP
+ * fmt PT_E4M3 or PT_E2M1; outputs laid out as pt_quantize_mx's.  With fmt PT_E2M1 the flags may add PT_MX_COL_RHT (the
+ * transposed copy is taken of the 16-point Hadamard transform, as the MXFP4 recipe lays out its wgrad operand); no other
+ * option flags.  PT_ERR_UNSUPPORTED outside that range (the caller then runs the two kernels).  Covers the SwiGLU -> quantize step between the two grouped GEMMs of an expert MLP
  * (primus_turbo/pytorch/ops/activation.py:72-80 followed by quantize_fp8 in ops/grouped_gemm_fp8.py of the reference). */
 int pt_glu_quantize_mx(const void *x, int x_dtype, const float *probs, const int64_t *row_mask, int64_t rows, int64_t H, int act, int fmt,
                        unsigned flags, void *q_row, uint8_t *s_row, void *q_col, uint8_t *s_col, void *stream);
