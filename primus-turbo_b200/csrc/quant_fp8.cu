@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(kThreads)
                      const float *__restrict__ scale_opt, uint8_t *__restrict__ q, float *__restrict__ scale_inv) {
     pdl_enter();
     float scale;
-    if (scale_opt != nullptr) scale = __ldg(scale_opt);
+    if (scale_opt != nullptr) scale = __ldcg(scale_opt);
     else scale = scale_from_amax<FMT>(__uint_as_float(__ldcg(amax_bits)), kEpsTensor);   // from the kernel before: not the read-only path
     const int64_t tid = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t nthreads = (int64_t) gridDim.x * blockDim.x;
@@ -193,11 +193,11 @@ __global__ void __launch_bounds__(kThreads)
 // Rows of 16-bit elements that fit the registers of one block (up to 4 x 16 bytes per thread = 8192 elements): the row
 // is read once, its |max| is formed on packed pairs, one block-wide exchange gives the scale, and the kept words are
 // scaled and converted.  Same arithmetic as rowwise_last_axis_kernel.
-template <typename T, int FMT>
-__global__ void __launch_bounds__(kThreads) rowwise_row_in_regs_kernel(const T *__restrict__ x, int64_t rows, int64_t len,
-                                                                     uint8_t *__restrict__ q, float *__restrict__ scale_inv) {
+template <typename T, int FMT, int KEEP>
+__global__ void __launch_bounds__(kThreads, KEEP == 2 ? 8 : 4) rowwise_row_in_regs_kernel(const T *__restrict__ x, int64_t rows, int64_t len,
+                                                                                        uint8_t *__restrict__ q, float *__restrict__ scale_inv) {
     pdl_enter();
-    constexpr int kKeep = 4;
+    constexpr int kKeep = KEEP;   // 16-byte words per thread: 2 (rows of up to 4096 elements, eight CTAs per SM) or 4
     __shared__ float s[kThreads / 32];
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const T *xr = x + row * len;
@@ -439,6 +439,23 @@ static int noalloc_scratch(unsigned **out) {
 
 }  // namespace ptb
 
+namespace ptb {
+// Grid for a grid-stride loop over `items` units of work: no more CTAs than are resident at once, and every CTA the same
+// number of units give or take one.  (A fixed "SMs x 16" grid gave the 8192-row rowwise quantizer 3.2 waves of CTAs of
+// 3 or 4 rows each: the last wave ran a third full.)
+template <typename Kernel> static int balanced_grid(Kernel kern, int threads, int64_t items) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, 0) != cudaSuccess || per_sm <= 0) {
+        cudaGetLastError();
+        per_sm = 4;
+    }
+    const int64_t resident = (int64_t) sm_count() * per_sm;
+    const int64_t per_cta = std::max<int64_t>(1, ceil_div(items, resident));
+    return (int) std::max<int64_t>(1, ceil_div(items, per_cta));
+}
+
+}  // namespace ptb
+
 using namespace ptb;
 
 extern "C" {
@@ -465,12 +482,14 @@ int pt_quantize_fp8_tensorwise(const void *x, int x_dtype, int64_t n, int fmt, v
         const int vec_ok = aligned(x, sizeof(T) == 4 ? 16 : 16) && aligned(q, 16);
         if (!scale_opt) {
             PT_CUDA_OK(cudaMemsetAsync(amax, 0, 4, st));
-            const int blocks = (int) std::max<int64_t>(1, std::min(max_blocks, ceil_div(n, (int64_t) kThreads * 32)));
+            const int blocks = vec_ok ? balanced_grid(amax_flat_kernel<T>, kThreads, ceil_div(n, (int64_t) kThreads * 8))
+                                      : (int) std::max<int64_t>(1, std::min(max_blocks, ceil_div(n, (int64_t) kThreads * 32)));
             amax_flat_kernel<T><<<blocks, kThreads, 0, st>>>((const T *) x, n, vec_ok, amax);   // reads x through the read-only path: an ordinary launch
             PT_LAUNCH_OK();
         }
-        const int blocks = (int) std::max<int64_t>(1, std::min(max_blocks * 2, ceil_div(n, (int64_t) kThreads * 16)));
         PT_SWITCH_FP8(fmt, F, {
+            const int blocks = vec_ok ? balanced_grid(cast_flat_kernel<T, F>, kThreads, ceil_div(n, (int64_t) kThreads * 16))
+                                      : (int) std::max<int64_t>(1, std::min(max_blocks * 2, ceil_div(n, (int64_t) kThreads * 16)));
             PT_CUDA_OK(launch_overlapped(cast_flat_kernel<T, F>, dim3(blocks), dim3(kThreads), 0, st, (const T *) x, n, vec_ok, (const unsigned *) amax,
                                          scale_opt, (uint8_t *) q, scale_inv));
         });
@@ -494,7 +513,13 @@ int pt_quantize_fp8_rowwise(const void *x, int x_dtype, int64_t B, int64_t M, in
             PT_SWITCH_FP8(fmt, F, {
                 if constexpr (sizeof(T) == 2) {
                     if (vec_ok && !scale_opt && N <= (int64_t) kThreads * 8 * 4) {
-                        rowwise_row_in_regs_kernel<T, F><<<blocks, kThreads, 0, st>>>((const T *) x, rows, N, (uint8_t *) q, scale_inv);
+                        if (N <= (int64_t) kThreads * 8 * 2) {
+                            const int rblocks = balanced_grid(rowwise_row_in_regs_kernel<T, F, 2>, kThreads, rows);
+                            rowwise_row_in_regs_kernel<T, F, 2><<<rblocks, kThreads, 0, st>>>((const T *) x, rows, N, (uint8_t *) q, scale_inv);
+                        } else {
+                            const int rblocks = balanced_grid(rowwise_row_in_regs_kernel<T, F, 4>, kThreads, rows);
+                            rowwise_row_in_regs_kernel<T, F, 4><<<rblocks, kThreads, 0, st>>>((const T *) x, rows, N, (uint8_t *) q, scale_inv);
+                        }
                         PT_LAUNCH_OK();
                         return PT_OK;
                     }
