@@ -401,6 +401,20 @@ int pt_grouped_glu_quantize_mx(const void *x, int x_dtype, const float *probs, c
 int pt_rmsnorm_quantize_mx(const void *x, int x_dtype, const float *rstd, const void *gamma, int zero_centered, int64_t rows, int64_t H, int fmt,
                            unsigned flags, void *q_row, uint8_t *s_row, void *q_col, uint8_t *s_col, void *stream);
 
+/* ---- pre-shuffled MX layouts (the tile orders the reference hands to its pre-shuffled GEMM back ends) ----------------
+ * Replaces torch.ops.primus_turbo_cpp_extension.shuffle_scale / shuffle_weight of the reference
+ * (csrc/pytorch/shuffle/shuffle.cpp:16-92, csrc/kernels/shuffle/shuffle.cu:33-118, index rules
+ * csrc/include/primus_turbo/device/shuffle.cuh:39-80) and the shuffle_scale / shuffle_out options of its MX quantizers
+ * (csrc/pytorch/quantization/quantization.cpp:795-830), which write the same bytes.
+ *
+ * pt_shuffle_e8m0_scale: scale ue8m0 [M, N] -> out [ceil(M, 256), ceil(N, 8)] bytes, padding 0; element (row, col) at
+ *   ((row / 32) * (N_pad / 8) + col / 8) * 256 + (col % 4) * 64 + (row % 16) * 4 + ((col % 8) / 4) * 2 + (row % 32) / 16.
+ * pt_shuffle_mx_codes: codes [M, row_bytes] (packed e2m1 pairs or fp8 bytes), M % 16 == 0, row_bytes % 32 == 0 -> out of
+ *   the same size; byte (row, col) at (row / 16) * (row_bytes * 16) + (col / 32) * 512 + ((col % 32) / 16) * 256 +
+ *   (row % 16) * 16 + col % 16.  Both pointers 16-byte aligned; out must not overlap the input. */
+int pt_shuffle_e8m0_scale(const uint8_t *scale, int64_t M, int64_t N, uint8_t *out, void *stream);
+int pt_shuffle_mx_codes(const void *codes, int64_t M, int64_t row_bytes, void *out, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

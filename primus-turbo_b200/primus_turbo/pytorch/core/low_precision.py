@@ -54,7 +54,9 @@ class ScalingStrategy(Enum):
 
 class ScalingRecipe(NamedTuple):
     """Per-operand options of the MX quantizers (low_precision.py:145-162 of the reference).
-    The shuffle_* layouts are AITER-specific pre-shuffles and are not provided here."""
+    shuffle_scale / shuffle_out: the dense quantizers return the scales / codes in the reference's pre-shuffled tile order
+    (what shuffle_scale / shuffle_weight make of the plain outputs).  That order is an export format for the reference's
+    pre-shuffled GEMM back ends: the GEMMs of this library read the plain layout only."""
     use_2d_block: bool = False
     use_sr: bool = False
     use_rht: bool = False

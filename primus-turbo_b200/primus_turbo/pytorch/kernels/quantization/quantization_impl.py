@@ -254,11 +254,52 @@ def fused_mx_supported(x: torch.Tensor, width: int, out_dtype, gated: bool) -> b
             and x.data_ptr() % 16 == 0 and 0 < x.shape[0] < 2 ** 31)
 
 
+def shuffle_scale_impl(scale: torch.Tensor, layout=(16, 16)) -> torch.Tensor:
+    """ue8m0 scale [M, N] -> [ceil(M, 256), ceil(N, 8)] in the pre-shuffled tile order (zero padding).  Mirrors
+    torch.ops.primus_turbo_cpp_extension.shuffle_scale of the reference (csrc/pytorch/shuffle/shuffle.cpp:16-50)."""
+    nv.require_cuda(scale)
+    assert tuple(layout) == (16, 16), "Unsupported shuffle layout."
+    assert scale.dim() == 2, "Scale must be 2D"
+    assert scale.dtype in (torch.float8_e8m0fnu, torch.uint8), "Scale must be Float8_e8m0fnu."
+    src = scale.contiguous().view(torch.uint8)
+    M, N = src.shape
+    out = torch.empty(ceil_div(M, 256) * 256, ceil_div(N, 8) * 8, dtype=torch.uint8, device=scale.device)
+    with nv.on_device(scale.device):
+        nv.check(nv.lib().pt_shuffle_e8m0_scale(nv.ptr(src), M, N, nv.ptr(out), nv.stream(scale.device)), "shuffle_scale")
+    return out.view(torch.float8_e8m0fnu)
+
+
+def shuffle_weight_impl(weight: torch.Tensor, layout=(16, 16)) -> torch.Tensor:
+    """MXFP4 (packed pairs) or MXFP8 codes [M, K] -> the same shape in the pre-shuffled (16 rows x 32 bytes) tile order.
+    Mirrors torch.ops.primus_turbo_cpp_extension.shuffle_weight of the reference (csrc/pytorch/shuffle/shuffle.cpp:52-92),
+    which takes MXFP4; the MX quantizers' shuffle_out option uses the same order for FP8 codes."""
+    nv.require_cuda(weight)
+    assert tuple(layout) == (16, 16), "Unsupported shuffle layout."
+    assert weight.dim() == 2, "Weight must be 2D"
+    assert weight.is_contiguous(), "Weight must be contiguous"
+    src = weight.view(torch.uint8)
+    M, K = src.shape
+    assert M % 16 == 0, f"M must be divisible by 16 for shuffled codes. But got M={M}"
+    assert K % 32 == 0, f"N must be divisible by 32 for shuffled codes. But got N={K}"
+    out = torch.empty_like(src)
+    with nv.on_device(weight.device):
+        nv.check(nv.lib().pt_shuffle_mx_codes(nv.ptr(src), M, K, nv.ptr(out), nv.stream(weight.device)), "shuffle_weight")
+    return out.view(weight.dtype)
+
+
+def _shuffled(q, s, recipe):
+    """The shuffle_scale / shuffle_out options of a ScalingRecipe, applied to one copy (2-D, or batched group by group)."""
+    if q is None or recipe is None or not (recipe.shuffle_scale or recipe.shuffle_out):
+        return q, s
+    if recipe.shuffle_scale:
+        s = shuffle_scale_impl(s) if s.dim() == 2 else torch.stack([shuffle_scale_impl(t) for t in s])
+    if recipe.shuffle_out:
+        q = shuffle_weight_impl(q) if q.dim() == 2 else torch.stack([shuffle_weight_impl(t.contiguous()) for t in q])
+    return q, s
+
+
 def _mx_quant(x, out_dtype, want_row, want_col, row_recipe, col_recipe, pro=None):
     nv.require_cuda(x)
-    for r in (row_recipe, col_recipe):
-        if r is not None and (r.shuffle_scale or r.shuffle_out):
-            raise NotImplementedError("pre-shuffled (AITER) MX layouts are not provided on B200")
     x = x.contiguous()
     fmt = nv.fmt_code(out_dtype)
     fp4 = fmt == nv.PT_E2M1
@@ -293,7 +334,9 @@ def _mx_quant(x, out_dtype, want_row, want_col, row_recipe, col_recipe, pro=None
                                               nv.ptr(q_col), nv.ptr(s_col), nv.stream(x.device)), "quantize_mx")
     view = lambda t: None if t is None else t.view(out_dtype)
     sview = lambda t: None if t is None else t.view(torch.float8_e8m0fnu)
-    return view(q_row), sview(s_row), view(q_col), sview(s_col)
+    q_row, s_row = _shuffled(view(q_row), sview(s_row), row_recipe if want_row else None)
+    q_col, s_col = _shuffled(view(q_col), sview(s_col), col_recipe if want_col else None)
+    return q_row, s_row, q_col, s_col
 
 
 def _quantize_mx_impl(x, out_dtype, axis, block_size, with_trans, scaling_recipe, scaling_recipe_for_trans):
@@ -410,7 +453,7 @@ def _grouped_mx_quant(x, out_dtype, group_lens, group_offs, want_row, want_col, 
     nv.require_cuda(x, group_lens, group_offs)
     for r in (row_recipe, col_recipe):
         if r is not None and (r.shuffle_scale or r.shuffle_out):
-            raise NotImplementedError("pre-shuffled (AITER) MX layouts are not provided on B200")
+            raise NotImplementedError("pre-shuffled MX layouts are provided for the dense quantizers only")
         if r is not None and r.use_2d_block:
             raise NotImplementedError("2-D block scales are a weight option; grouped activations use 1-D blocks")
     assert x.dim() == 2, "Input must be 2D"

@@ -19,11 +19,23 @@ from ..kernels.quantization.quantization_impl import (dequant_fp8_blockwise_for_
                                                       quant_fp8_blockwise_dual_impl, quant_fp8_blockwise_for_weight_impl,
                                                       quant_fp8_blockwise_impl, quantize_fp8_rowwise_impl,
                                                       quantize_fp8_tensorwise_impl, quantize_mxfp4_impl,
-                                                      quantize_mxfp8_impl)
+                                                      quantize_mxfp8_impl, shuffle_scale_impl, shuffle_weight_impl)
 
 __all__ = ["quantize_fp8", "quantize_fp8_with_trans", "dequantize_fp8", "quantize_fp4", "quantize_fp4_with_trans",
            "dequantize_fp4", "grouped_quantize_fp8", "grouped_quantize_fp8_with_trans", "grouped_dequantize_fp8",
-           "grouped_quantize_fp4", "grouped_quantize_fp4_with_trans", "grouped_dequantize_fp4"]
+           "grouped_quantize_fp4", "grouped_quantize_fp4_with_trans", "grouped_dequantize_fp4", "shuffle_scale", "shuffle_weight"]
+
+
+def shuffle_scale(scale: torch.Tensor, layout=(16, 16)) -> torch.Tensor:
+    """ue8m0 scales [M, N] in the pre-shuffled tile order, [ceil(M, 256), ceil(N, 8)], padding 0
+    (torch.ops.primus_turbo_cpp_extension.shuffle_scale of the reference)."""
+    return shuffle_scale_impl(scale, layout)
+
+
+def shuffle_weight(weight: torch.Tensor, layout=(16, 16)) -> torch.Tensor:
+    """MX codes [M, K] (M % 16 == 0, K % 32 == 0 bytes) in the pre-shuffled tile order, same shape
+    (torch.ops.primus_turbo_cpp_extension.shuffle_weight of the reference)."""
+    return shuffle_weight_impl(weight, layout)
 
 
 def _mx_axis(x, axis):
