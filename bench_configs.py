@@ -469,6 +469,19 @@ def _small_case(name, args):
         for _ in range(2):
             ggi.grouped_gemm_fp8_impl(a_row, w_q, a_s_row, w_s, lens_t, offs, False, True, torch.bfloat16, SG.BLOCKWISE)
             ggi.grouped_gemm_fp8_variable_k_impl(a_col, g_col, a_s_col, g_s_col, plens, poffs, True, False, True, torch.bfloat16, SG.BLOCKWISE)
+    elif name == "mx_c3":   # forward and wgrad GEMM of the C3 linear (or of M N K given), one launch each after the quantizers
+        from primus_turbo.pytorch.kernels.gemm.gemm_fp8_impl import gemm_fp8_impl
+        M, N, K = (int(args[0]), int(args[1]), int(args[2])) if len(args) >= 3 else (C3["M"], C3["N"], C3["K"])
+        x = randn_bf16((M, K), 1.0, 71, dev)
+        w = randn_bf16((N, K), 0.01, 72, dev)
+        dy = randn_bf16((M, N), 1e-3, 73, dev)
+        a_row, a_row_s, a_col, a_col_s = qi.quantize_mxfp8_impl(x, f8, None, 32, True)
+        b_row, b_row_s, _, _ = qi.quantize_mxfp8_impl(w, f8, None, 32, True)
+        _, _, g_col, g_col_s = qi.quantize_mxfp8_impl(dy, f5, None, 32, True)
+        del x, w, dy
+        for _ in range(2):
+            gemm_fp8_impl(a_row, a_row_s, False, b_row, b_row_s, True, torch.bfloat16, False, SG.MX_BLOCKWISE)
+            gemm_fp8_impl(g_col, g_col_s, False, a_col, a_col_s, True, torch.bfloat16, False, SG.MX_BLOCKWISE)
     elif name in ("rowwise_other_axis", "rmsnorm_bwd", "rmsnorm_mx_dual"):
         from primus_turbo.pytorch.kernels.normalization import rmsnorm_impl as ri
         M, N = (int(args[0]), int(args[1])) if len(args) >= 2 else (8192, 4096)
@@ -486,7 +499,7 @@ def _small_case(name, args):
                 qi.rmsnorm_quantize_mx_impl(x, gamma, 1e-6, False, f8, fused=True)
     else:
         raise SystemExit(f"unknown case {name!r}: mx_dual, mxfp4_dual, blockwise_dual, swiglu_mx_dual, rowwise_other_axis, "
-                         "rmsnorm_bwd, rmsnorm_mx_dual [M N]; blockwise_grouped [G rows]")
+                         "rmsnorm_bwd, rmsnorm_mx_dual [M N]; blockwise_grouped [G rows]; mx_c3 [M N K]")
     torch.cuda.synchronize()
     print("ok", name, *args)
 

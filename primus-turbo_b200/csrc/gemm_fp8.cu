@@ -241,7 +241,9 @@ __device__ __forceinline__ void epilogue_store_block(const GemmParams &p, uint32
                 const uint4 val = *reinterpret_cast<const uint4 *>(stg + rr * pitch + (sub ^ rsw) * 16);
                 uint8_t *dst = reinterpret_cast<uint8_t *>(p.C) + (grow * p.ldc + gcol) * esize;
                 if (p.vec_store_ok && gcol + elems16 <= n_end && p.beta == 0.f) {
-                    *reinterpret_cast<uint4 *>(dst) = val;
+                    // written once and not read by this kernel: streaming store, so that C leaves L2 before the operand
+                    // panels that other CTAs are about to re-read
+                    __stcs(reinterpret_cast<uint4 *>(dst), val);
                 } else {
                     const uint8_t *src = reinterpret_cast<const uint8_t *>(&val);
                     for (int e = 0; e < elems16 && gcol + e < n_end; ++e) {
@@ -350,6 +352,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // ================================================================ TMA producer
         if (elect_one()) {
             uint32_t stage = 0, phase = 0;
+            const uint64_t keep = l2_policy_evict_last();
             for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
                 const int64_t a_row0 = ((p.offs_read && !p.koffs) ? p.offs_read[gi] : 0) + (int64_t) m_blk * BLOCK_M;
                 const int64_t b_row0 = (p.koffs ? 0 : (int64_t) gi * p.b_group_rows) + (int64_t) n_blk * BLOCK_N;
@@ -367,14 +370,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag))) break;
                     mbar_arrive_expect_tx(&full_bar[stage], Cfg::kABytes + Cfg::kBBytes + Cfg::kSfBytes);
                     const int k0 = (kb_begin + kb) * BLOCK_K;
-                    if (!MX && p.a_mn) tma_load_2d(smem_a + stage * Cfg::kABytes, &tmap_a, &full_bar[stage], (int) a_row0, k0);
-                    else tma_load_2d(smem_a + stage * Cfg::kABytes, &tmap_a, &full_bar[stage], k0, (int) a_row0);
+                    if (!MX && p.a_mn) tma_load_2d_hint(smem_a + stage * Cfg::kABytes, &tmap_a, &full_bar[stage], (int) a_row0, k0, keep);
+                    else tma_load_2d_hint(smem_a + stage * Cfg::kABytes, &tmap_a, &full_bar[stage], k0, (int) a_row0, keep);
                     if (!MX && p.b_mn) {   // one 128-wide box per 128 columns of the tile, 16 KiB apart
 #pragma unroll
                         for (int j = 0; j < (BLOCK_N + 127) / 128; ++j)
-                            tma_load_2d(smem_b + stage * Cfg::kBBytes + j * 16384, &tmap_b, &full_bar[stage], (int) b_row0 + 128 * j, k0);
+                            tma_load_2d_hint(smem_b + stage * Cfg::kBBytes + j * 16384, &tmap_b, &full_bar[stage], (int) b_row0 + 128 * j, k0, keep);
                     } else {
-                        tma_load_2d(smem_b + stage * Cfg::kBBytes, &tmap_b, &full_bar[stage], k0, (int) b_row0);
+                        tma_load_2d_hint(smem_b + stage * Cfg::kBBytes, &tmap_b, &full_bar[stage], k0, (int) b_row0, keep);
                     }
                     if constexpr (MX) {
                         // per stage: kSfP consecutive 512-byte blocks of A (one copy), and of each 128-row block of B

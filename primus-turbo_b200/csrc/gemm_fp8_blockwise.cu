@@ -169,10 +169,11 @@ __device__ __forceinline__ void bw_store_tile_bulk(const float (&acc)[128], uint
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
+            const uint64_t leave = l2_policy_evict_first();   // the output is not read again by this kernel
 #pragma unroll
             for (int b = 0; b < 2; ++b)
                 if (n0 + (rd * 2 + b) * box_cols < N)  // boxes that start past the last column are dropped
-                    tma_store_2d(tmap_c, stg + b * 4096, (n0 + (rd * 2 + b) * box_cols) * esize, (int) tile_row0);
+                    tma_store_2d_hint(tmap_c, stg + b * 4096, (n0 + (rd * 2 + b) * box_cols) * esize, (int) tile_row0, leave);
             bulk_commit_group();
         }
     }
@@ -270,6 +271,7 @@ __global__ void __launch_bounds__(kBwThreads, 1)
         // ================================================================ TMA producer
         if (elect_one()) {
             uint32_t stage = 0, phase = 0, step = 0;
+            const uint64_t keep = l2_policy_evict_last();
             for (int t = blockIdx.x; ok && walk.locate(t, gi, m_blk, n_blk); t += gridDim.x) {
                 const int64_t a_row0 = (p.koffs ? 0 : (p.offs_read ? p.offs_read[gi] : 0)) + (int64_t) m_blk * BLOCK_M;
                 const int64_t b_row0 = (p.koffs ? 0 : (int64_t) gi * p.b_group_rows) + (int64_t) n_blk * BW_BLOCK_N;
@@ -282,15 +284,15 @@ __global__ void __launch_bounds__(kBwThreads, 1)
                     mbar_arrive_expect_tx(&full_bar[stage], kBwABytes + kBwBBytes);
                     const int k0 = (kb_begin + kb) * BLOCK_K;
                     uint8_t *sa = smem_a + stage * kBwABytes, *sb = smem_b + stage * kBwBBytes;
-                    if (p.a_mn) tma_load_2d(sa, &tmap_a, &full_bar[stage], (int) a_row0, k0);
-                    else tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, (int) a_row0);
+                    if (p.a_mn) tma_load_2d_hint(sa, &tmap_a, &full_bar[stage], (int) a_row0, k0, keep);
+                    else tma_load_2d_hint(sa, &tmap_a, &full_bar[stage], k0, (int) a_row0, keep);
                     if (p.b_mn) {
                         // two 128-wide boxes; contraction rows of group g start at g * b_group_kstride
                         const int kr = (int) ((p.koffs ? 0 : (int64_t) gi * p.b_group_kstride) + k0);
-                        tma_load_2d(sb, &tmap_b, &full_bar[stage], n0, kr);
-                        tma_load_2d(sb + kBwBBytes / 2, &tmap_b, &full_bar[stage], n0 + 128, kr);
+                        tma_load_2d_hint(sb, &tmap_b, &full_bar[stage], n0, kr, keep);
+                        tma_load_2d_hint(sb + kBwBBytes / 2, &tmap_b, &full_bar[stage], n0 + 128, kr, keep);
                     } else {
-                        tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, (int) b_row0);
+                        tma_load_2d_hint(sb, &tmap_b, &full_bar[stage], k0, (int) b_row0, keep);
                     }
                     if constexpr (SBM == SB_SLAB) {
                         // per-column B scales of this K step: one contiguous run of `slab_cols` floats.  Ring slot

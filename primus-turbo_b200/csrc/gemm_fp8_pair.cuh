@@ -143,6 +143,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((PairCfg<BLOCK_N, mo
         // ================================================================ TMA producer (both CTAs)
         if (elect_one()) {
             uint32_t stage = 0, phase = 0;
+            const uint64_t keep = l2_policy_evict_last();
             for (int t = pair; ok && walk.locate(t, gi, m_blk, n_blk); t += num_pairs) {
                 const int a_row0 = (int) (((p.offs_read && !p.koffs) ? p.offs_read[gi] : 0) + (int64_t) m_blk * kTileM) + (int) rank * BLOCK_M;
                 const int b_row0 = (int) ((p.koffs ? 0 : (int64_t) gi * p.b_group_rows) + (int64_t) n_blk * BLOCK_N) + (int) rank * Cfg::kHalfN;
@@ -162,10 +163,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((PairCfg<BLOCK_N, mo
                     if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
                     const int k0 = (kb_begin + kb) * BLOCK_K;
                     // MN-major operands (dense tensorwise / rowwise): 128 row indices x 128 contraction rows per CTA
-                    if (!MX && p.a_mn) tma_load_2d_pair(smem_a + stage * Cfg::kABytes, &tmap_a, full_leader, a_row0, k0);
-                    else tma_load_2d_pair(smem_a + stage * Cfg::kABytes, &tmap_a, full_leader, k0, a_row0);
-                    if (!MX && p.b_mn) tma_load_2d_pair(smem_b + stage * Cfg::kBBytes, &tmap_b, full_leader, b_row0, k0);
-                    else tma_load_2d_pair(smem_b + stage * Cfg::kBBytes, &tmap_b, full_leader, k0, b_row0);
+                    if (!MX && p.a_mn) tma_load_2d_pair_hint(smem_a + stage * Cfg::kABytes, &tmap_a, full_leader, a_row0, k0, keep);
+                    else tma_load_2d_pair_hint(smem_a + stage * Cfg::kABytes, &tmap_a, full_leader, k0, a_row0, keep);
+                    if (!MX && p.b_mn) tma_load_2d_pair_hint(smem_b + stage * Cfg::kBBytes, &tmap_b, full_leader, b_row0, k0, keep);
+                    else tma_load_2d_pair_hint(smem_b + stage * Cfg::kBBytes, &tmap_b, full_leader, k0, b_row0, keep);
                     if constexpr (MX) {
                         uint8_t *sf = smem_sf + stage * Cfg::kSfBytes;
                         tma_load_2d_pair(sf, &tmap_sf, full_leader, 0, (int) (sfa_line0 + 4 * kSfP * kb));
