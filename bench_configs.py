@@ -236,6 +236,10 @@ def quantize_records(dev, peaks, copies=4):
         run(f"rmsnorm_mxfp8_dual_{nm}_8192x4096", [lambda x=x: qi.rmsnorm_quantize_mx_impl(x, gam, 1e-6, False, f8, fused=fused) for x in acts],
             2 * e + 2 * (e + e // 32) + 4 * M, "rmsnorm_fwd_kernel<statistics> + mx_quant_split_kernel<RMSNorm prologue>" if fused
             else "rmsnorm_fwd_kernel + mx_quant_split_kernel")
+    # the forward-only form: RMSNorm and the row-wise MX copy alone
+    for fused, nm in ((True, "one_pass"), (False, "two_kernels")):
+        run(f"rmsnorm_mxfp8_row_{nm}_8192x4096", [lambda x=x: qi.rmsnorm_quantize_mx_row_impl(x, gam, 1e-6, False, f8, fused=fused) for x in acts],
+            2 * e + (e + e // 32) + 4 * M, "rmsnorm_mx_row_kernel" if fused else "rmsnorm_fwd_kernel + mx_quant_tma_kernel (same algorithmic bytes counted)")
     return out
 
 

@@ -401,6 +401,14 @@ int pt_grouped_glu_quantize_mx(const void *x, int x_dtype, const float *probs, c
 int pt_rmsnorm_quantize_mx(const void *x, int x_dtype, const float *rstd, const void *gamma, int zero_centered, int64_t rows, int64_t H, int fmt,
                            unsigned flags, void *q_row, uint8_t *s_row, void *q_col, uint8_t *s_col, void *stream);
 
+/* RMSNorm and the row-wise MX copy in one pass over x (forward-only callers need no transposed copy): writes rstd [rows]
+ * and what pt_rmsnorm_fwd followed by pt_quantize_mx (flags PT_MX_ROW) writes, byte for byte, without y in memory.
+ * x, gamma bf16; fmt PT_E4M3, PT_E5M2 or PT_E2M1; q_row [rows, ceil(H, 128)] codes (half the bytes for e2m1), s_row
+ * [rows, ceil(H, 128) / 32].  PT_ERR_UNSUPPORTED when H is not a multiple of 32 or exceeds 8192 (the caller then runs
+ * the two kernels).  (primus_turbo/pytorch/ops/normalization.py rmsnorm followed by quantize_fp8 of the reference.) */
+int pt_rmsnorm_quantize_mx_row(const void *x, int x_dtype, const void *gamma, float eps, int zero_centered, int64_t rows, int64_t H,
+                               int fmt, void *q_row, uint8_t *s_row, float *rstd, void *stream);
+
 /* ---- pre-shuffled MX layouts (the tile orders the reference hands to its pre-shuffled GEMM back ends) ----------------
  * Replaces torch.ops.primus_turbo_cpp_extension.shuffle_scale / shuffle_weight of the reference
  * (csrc/pytorch/shuffle/shuffle.cpp:16-92, csrc/kernels/shuffle/shuffle.cu:33-118, index rules

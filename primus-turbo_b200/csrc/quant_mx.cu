@@ -859,6 +859,119 @@ __device__ __forceinline__ void split_prologue(uint8_t *tile, int t, int in_row0
     sm100::named_barrier<3, 2 * kSGroupThreads>();
 }
 
+// RMSNorm and the row-wise MX copy in one pass over x (the forward-only / inference form: no transposed copy): a block
+// reads a row into registers, forms rstd in the order of the stand-alone RMSNorm kernel (activation_norm.cu: per-thread
+// sums over its vectors in turn, eight warp reductions, then the eight warp sums in turn), normalises with its
+// arithmetic and rounding, and quantizes each 32-element block, which sits in four neighbouring threads (eight elements
+// each): two shuffles give the block |max|.  The bytes are those of the RMSNorm kernel followed by the row-wise quantizer.
+// ncu on 8192 x 4096: 24 thread instructions per element, issue slots 80 % busy: the kernel is bound by instruction issue
+// (33.7 us; a one-warp-per-row form with sixteen loads in flight per lane was slower, 46 us).
+constexpr int kRnThreads = 256, kRnKeep = 4;
+// KEEP: 16-byte words per thread and row (2 for rows of up to 4096 elements: fewer registers, more CTAs per SM).  The next
+// row of the block is requested before the current one is reduced, so its latency overlaps the two block-wide exchanges.
+template <int FMT, int KEEP>
+__global__ void __launch_bounds__(kRnThreads, KEEP == 2 ? 6 : 4) rmsnorm_mx_row_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ gamma,
+                                                                    float eps, int zero_centered, int64_t rows, int64_t H, int64_t n_pad,
+                                                                    uint8_t *__restrict__ q_row, uint8_t *__restrict__ s_row,
+                                                                    float *__restrict__ rstd_out) {
+    using T = __nv_bfloat16;
+    constexpr bool kFp4 = FMT == PT_E2M1;
+    __shared__ float s_red[kRnThreads / 32];
+    const float zc = zero_centered ? 1.0f : 0.0f;
+    auto fetch = [&](int64_t r, uint4(&v)[KEEP]) {
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) {
+            const int64_t h = ((int64_t) k * kRnThreads + threadIdx.x) * 8;
+            v[k] = (h < H && r < rows) ? __ldg(reinterpret_cast<const uint4 *>(x + r * H + h)) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+    uint4 keep[KEEP], next[KEEP];
+    fetch(blockIdx.x, keep);
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        fetch(r + gridDim.x, next);
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) {
+            const int64_t h = ((int64_t) k * kRnThreads + threadIdx.x) * 8;
+            if (h < H) {
+                const uint32_t w[4] = {keep[k].x, keep[k].y, keep[k].z, keep[k].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float lo = bf16_lo(w[i]), hi = bf16_hi(w[i]);
+                    ss += lo * lo;
+                    ss += hi * hi;
+                }
+            }
+        }
+        float v = ss;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        __syncthreads();   // s_red may still be read for the previous row
+        if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = v;
+        __syncthreads();
+        float total = 0.f;
+#pragma unroll
+        for (int w = 0; w < kRnThreads / 32; ++w) total += s_red[w];
+        const float rstd = rsqrtf(total / (float) H + eps);
+        if (threadIdx.x == 0) rstd_out[r] = rstd;
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) {
+            const int64_t h = ((int64_t) k * kRnThreads + threadIdx.x) * 8;
+            const bool live = h < n_pad;   // every lane takes part in the shuffles below; only the stores are conditional
+            uint32_t y[4] = {0u, 0u, 0u, 0u};
+            if (h < H) {
+                const uint4 gv = __ldg(reinterpret_cast<const uint4 *>(gamma + h));
+                const uint32_t xw[4] = {keep[k].x, keep[k].y, keep[k].z, keep[k].w}, gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const __nv_bfloat162 t = __floats2bfloat162_rn(rmsnorm_value(bf16_lo(xw[i]), rstd, bf16_lo(gw[i]) + zc),
+                                                                   rmsnorm_value(bf16_hi(xw[i]), rstd, bf16_hi(gw[i]) + zc));
+                    y[i] = *reinterpret_cast<const uint32_t *>(&t);
+                }
+            }
+            // |max| of the 32-element block: this thread's four words, then the three neighbours
+            uint32_t pm = 0u;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pm = absmax2_nan_bf16(pm, y[i]);
+            pm = absmax2_nan_bf16(pm, __shfl_xor_sync(0xffffffffu, pm, 1));
+            pm = absmax2_nan_bf16(pm, __shfl_xor_sync(0xffffffffu, pm, 2));
+            const bool has_nan = packed_bf16_has_nan(pm);
+            if (__any_sync(0xffffffffu, has_nan)) {   // a NaN element takes no part in the maximum (rare: the whole warp redoes it)
+                uint32_t pq = 0u;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) pq = absmax2<T>(pq, y[i]);
+                pq = absmax2<T>(pq, __shfl_xor_sync(0xffffffffu, pq, 1));
+                pq = absmax2<T>(pq, __shfl_xor_sync(0xffffffffu, pq, 2));
+                if (has_nan) pm = pq;
+            }
+            pm = absmax2_done(pm);
+            const float m = fmaxf(bf16_lo(pm), bf16_hi(pm));
+            const MxScale sc = mx_scale<FMT>(m, false);
+            if (has_nan && !kFp4) {
+                const float nlim = -MxParams<FMT>::qmax * sc.native;
+                const uint32_t nlim2 = bf16_bits_x2(nlim, nlim);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) y[i] = max_bf16x2(y[i], nlim2);
+            }
+            const uint32_t inv2 = bf16_bits_x2(sc.inv, sc.inv);
+            const uint32_t s0 = mul_bf16x2(y[0], inv2), s1 = mul_bf16x2(y[1], inv2), s2 = mul_bf16x2(y[2], inv2), s3 = mul_bf16x2(y[3], inv2);
+            if constexpr (kFp4) {
+                uint32_t o = pack8_e2m1(bf16_lo(s0), bf16_hi(s0), bf16_lo(s1), bf16_hi(s1), bf16_lo(s2), bf16_hi(s2), bf16_lo(s3), bf16_hi(s3));
+                if (sc.byte == 0) o = 0u;
+                if (live) *reinterpret_cast<uint32_t *>(q_row + (r * n_pad + h) / 2) = o;
+            } else {
+                uint2 o = make_uint2(pack4_fp8<FMT>(bf16_lo(s0), bf16_hi(s0), bf16_lo(s1), bf16_hi(s1)),
+                                     pack4_fp8<FMT>(bf16_lo(s2), bf16_hi(s2), bf16_lo(s3), bf16_hi(s3)));
+                if (sc.byte == 0) o = make_uint2(0u, 0u);
+                if (live) *reinterpret_cast<uint2 *>(q_row + r * n_pad + h) = o;
+            }
+            if (live && (threadIdx.x & 3) == 0) s_row[r * (n_pad / 32) + h / 32] = sc.byte;
+        }
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) keep[k] = next[k];
+    }
+}
+
 // ROWSTAGE: the row-wise copy is staged and written by TMA (dense FP8); otherwise by 32-byte stores from registers.
 // COLRHT (e2m1): the transposed copy is taken of the 16-point Hadamard transform of each run of 16 rows, in fp32 and in the
 // operation order of mx_quant_tma_kernel's column pass (same bytes); the 64 fp32 values per thread cost a CTA per SM.
@@ -1567,6 +1680,45 @@ int pt_rmsnorm_quantize_mx(const void *x, int x_dtype, const float *rstd, const 
     PT_REQUIRE(x && rstd && gamma && aligned(gamma, 16), "%s: null or unaligned pointer", what);
     a.pro_rowvec = rstd; a.pro_gamma = gamma; a.pro_zero_centered = zero_centered;
     return launch_fused<PT_PRO_RMSNORM, false>(a, what, fmt, flags, (cudaStream_t) stream);
+}
+
+int pt_rmsnorm_quantize_mx_row(const void *x, int x_dtype, const void *gamma, float eps, int zero_centered, int64_t rows, int64_t H,
+                               int fmt, void *q_row, uint8_t *s_row, float *rstd, void *stream) {
+    const char *what = "RMSNorm + row-wise MX quantize";
+    PT_REQUIRE(rows >= 0 && H >= 0, "%s: bad shape", what);
+    PT_REQUIRE(x_dtype == PT_BF16, "%s: bf16 input", what);
+    PT_REQUIRE(fmt == PT_E4M3 || fmt == PT_E5M2 || fmt == PT_E2M1, "%s: formats e4m3, e5m2, e2m1", what);
+    if (H % 32 != 0 || ceil_to(H, 128) > (int64_t) kRnThreads * 8 * kRnKeep) return PT_ERR_UNSUPPORTED;   // the caller runs the two kernels
+    if (rows == 0 || H == 0) return PT_OK;
+    PT_REQUIRE(x && gamma && q_row && s_row && rstd && aligned(x, 16) && aligned(gamma, 16) && aligned(q_row, 8) && aligned(s_row, 4),
+               "%s: null or unaligned pointer", what);
+    cudaStream_t st = (cudaStream_t) stream;
+    const int64_t n_pad = ceil_to(H, 128);
+#define PT_RN_LAUNCH_K(F_, K_)                                                                                      \
+    do {                                                                                                            \
+        auto kern = rmsnorm_mx_row_kernel<F_, K_>;                                                                  \
+        int per_sm = 0;                                                                                             \
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kRnThreads, 0) != cudaSuccess || per_sm <= 0) { \
+            cudaGetLastError();                                                                                     \
+            per_sm = 2;                                                                                             \
+        }                                                                                                           \
+        const int64_t per_cta = std::max<int64_t>(1, ceil_div(rows, (int64_t) sm_count() * per_sm));               \
+        const int grid = (int) ceil_div(rows, per_cta);                                                             \
+        kern<<<grid, kRnThreads, 0, st>>>((const __nv_bfloat16 *) x, (const __nv_bfloat16 *) gamma, eps, zero_centered, rows, H, n_pad, \
+                                          (uint8_t *) q_row, s_row, rstd);                                          \
+    } while (0)
+#define PT_RN_LAUNCH(F_)                                                                                            \
+    do {                                                                                                            \
+        if (n_pad <= (int64_t) kRnThreads * 8 * 2) PT_RN_LAUNCH_K(F_, 2);                                           \
+        else PT_RN_LAUNCH_K(F_, 4);                                                                                 \
+    } while (0)
+    if (fmt == PT_E4M3) PT_RN_LAUNCH(PT_E4M3);
+    else if (fmt == PT_E5M2) PT_RN_LAUNCH(PT_E5M2);
+    else PT_RN_LAUNCH(PT_E2M1);
+#undef PT_RN_LAUNCH_K
+#undef PT_RN_LAUNCH
+    PT_LAUNCH_OK();
+    return PT_OK;
 }
 
 int pt_grouped_quantize_mx(const void *x, int x_dtype, int64_t M, int64_t N, int G, const int64_t *group_offs,

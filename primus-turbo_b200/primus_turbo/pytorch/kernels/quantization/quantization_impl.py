@@ -594,6 +594,33 @@ def grouped_glu_quantize_mx_impl(x, probs, row_mask, act: str, out_dtype, group_
     return _grouped_mx_quant(x, out_dtype, group_lens, group_offs, True, True, row_r, col_r, pro=("glu", probs, row_mask, ACT_CODES[act]))
 
 
+def rmsnorm_quantize_mx_row_impl(x: torch.Tensor, gamma: torch.Tensor, eps: float, zero_centered: bool, out_dtype, fused=None):
+    """Row-wise MX copy of rmsnorm(x) and the row statistics, (q_row, s_row, rstd), in one pass over x: what a forward-only
+    caller feeds the first GEMM.  Falls back to RMSNorm kernel + row-wise quantizer outside the one-pass kernel's range
+    (bf16, H a multiple of 32, at most 8192); both write the same bytes."""
+    from ..normalization.rmsnorm_impl import rmsnorm_fwd_impl
+    nv.require_cuda(x, gamma)
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    gamma = gamma.contiguous()
+    rows, H = x2.shape
+    ok = x2.dtype == torch.bfloat16 and gamma.dtype == torch.bfloat16 and H % MX_BLOCK == 0 and H <= 8192
+    use = ok if fused is None else fused
+    if use:
+        fmt = nv.fmt_code(out_dtype)
+        n_pad = ceil_div(H, MX_ALIGN) * MX_ALIGN
+        q = torch.empty(rows, n_pad // (2 if fmt == nv.PT_E2M1 else 1), dtype=torch.uint8, device=x.device)
+        s = torch.empty(rows, n_pad // MX_BLOCK, dtype=torch.uint8, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        with nv.on_device(x.device):
+            nv.check(nv.lib().pt_rmsnorm_quantize_mx_row(nv.ptr(x2), nv.src_code(x2.dtype), nv.ptr(gamma), float(eps), int(bool(zero_centered)),
+                                                          rows, H, fmt, nv.ptr(q), nv.ptr(s), nv.ptr(rstd), nv.stream(x.device)),
+                     "rmsnorm_quantize_mx_row")
+        return q.view(out_dtype), s.view(torch.float8_e8m0fnu), rstd
+    y, _, rstd = rmsnorm_fwd_impl(x2, gamma, eps, zero_centered)
+    q, s, _, _ = _mx_quant(y, out_dtype, True, False, ScalingRecipe(), ScalingRecipe())
+    return q, s, rstd
+
+
 def rmsnorm_quantize_mx_impl(x: torch.Tensor, gamma: torch.Tensor, eps: float, zero_centered: bool, out_dtype, fused=None):
     """MX copies of rmsnorm(x) and the row statistics: (q_row, s_row, q_col, s_col, rstd).  One statistics pass over x,
     then the quantizer normalises each tile as it loads it; the normalised tensor is never written."""

@@ -268,3 +268,26 @@ def test_fused_rmsnorm_quantizer_gives_the_same_bytes_every_launch(out_dtype):
     plain = rmsnorm_quantize_mx_impl(x, gamma, 1e-6, False, out_dtype, fused=False)
     for _ in range(30):
         _same(rmsnorm_quantize_mx_impl(x, gamma, 1e-6, False, out_dtype, fused=True), plain)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float8_e4m3fn, torch.float8_e5m2, torch.float4_e2m1fn_x2])
+@pytest.mark.parametrize("rows,H,zc", [(1, 32, False), (128, 128, False), (1000, 4096, True), (333, 7168, False), (64, 8192, False), (50, 160, True)])
+def test_rmsnorm_row_quantizer_one_pass_equals_two_kernels(out_dtype, rows, H, zc):
+    """Forward-only form: RMSNorm and the row-wise MX copy in one pass write the bytes of RMSNorm kernel + quantizer, and
+    the same rstd; a NaN and an all-zero row included."""
+    from primus_turbo.pytorch.kernels.quantization.quantization_impl import rmsnorm_quantize_mx_row_impl
+    g = torch.Generator(device="cuda").manual_seed(rows * 7 + H)
+    x = torch.randn(rows, H, device="cuda", dtype=torch.bfloat16, generator=g) * 3
+    if rows > 2:
+        x[1] = 0
+        x[2, H // 2] = float("nan")
+    if rows > 4:
+        x[3, 5] = float("inf")          # rstd = 0: one NaN (inf * 0) in a row of zeros, so a single block holds a NaN
+    gamma = torch.randn(H, device="cuda", dtype=torch.bfloat16, generator=g)
+    if H > 64:
+        gamma[40] = float("nan")        # a NaN gain: one NaN per row, in one block only
+    one = rmsnorm_quantize_mx_row_impl(x, gamma, 1e-6, zc, out_dtype, fused=True)
+    two = rmsnorm_quantize_mx_row_impl(x, gamma, 1e-6, zc, out_dtype, fused=False)
+    assert torch.equal(one[0].view(torch.uint8), two[0].view(torch.uint8))
+    assert torch.equal(one[1].view(torch.uint8), two[1].view(torch.uint8))
+    assert torch.equal(one[2].view(torch.int32), two[2].view(torch.int32))
