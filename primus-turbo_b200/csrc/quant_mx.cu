@@ -870,7 +870,7 @@ constexpr int kRnThreads = 256, kRnKeep = 4;
 // KEEP: 16-byte words per thread and row (2 for rows of up to 4096 elements: fewer registers, more CTAs per SM).  The next
 // row of the block is requested before the current one is reduced, so its latency overlaps the two block-wide exchanges.
 template <int FMT, int KEEP>
-__global__ void __launch_bounds__(kRnThreads, KEEP == 2 ? 6 : 4) rmsnorm_mx_row_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ gamma,
+__global__ void __launch_bounds__(kRnThreads, KEEP == 2 ? 5 : 4) rmsnorm_mx_row_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ gamma,
                                                                     float eps, int zero_centered, int64_t rows, int64_t H, int64_t n_pad,
                                                                     uint8_t *__restrict__ q_row, uint8_t *__restrict__ s_row,
                                                                     float *__restrict__ rstd_out) {
@@ -885,6 +885,20 @@ __global__ void __launch_bounds__(kRnThreads, KEEP == 2 ? 6 : 4) rmsnorm_mx_row_
             v[k] = (h < H && r < rows) ? __ldg(reinterpret_cast<const uint4 *>(x + r * H + h)) : make_uint4(0u, 0u, 0u, 0u);
         }
     };
+    // this thread's gains are the same for every row: converted once when they fit the registers (KEEP == 2)
+    constexpr bool kGainsInRegs = KEEP == 2;
+    [[maybe_unused]] float gp[kGainsInRegs ? KEEP : 1][8];
+    if constexpr (kGainsInRegs) {
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) {
+            const int64_t h = ((int64_t) k * kRnThreads + threadIdx.x) * 8;
+            uint4 gv = make_uint4(0u, 0u, 0u, 0u);
+            if (h < H) gv = __ldg(reinterpret_cast<const uint4 *>(gamma + h));
+            const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { gp[k][2 * i] = bf16_lo(gw[i]) + zc; gp[k][2 * i + 1] = bf16_hi(gw[i]) + zc; }
+        }
+    }
     uint4 keep[KEEP], next[KEEP];
     fetch(blockIdx.x, keep);
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -920,13 +934,23 @@ __global__ void __launch_bounds__(kRnThreads, KEEP == 2 ? 6 : 4) rmsnorm_mx_row_
             const bool live = h < n_pad;   // every lane takes part in the shuffles below; only the stores are conditional
             uint32_t y[4] = {0u, 0u, 0u, 0u};
             if (h < H) {
-                const uint4 gv = __ldg(reinterpret_cast<const uint4 *>(gamma + h));
-                const uint32_t xw[4] = {keep[k].x, keep[k].y, keep[k].z, keep[k].w}, gw[4] = {gv.x, gv.y, gv.z, gv.w};
+                const uint32_t xw[4] = {keep[k].x, keep[k].y, keep[k].z, keep[k].w};
+                if constexpr (kGainsInRegs) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const __nv_bfloat162 t = __floats2bfloat162_rn(rmsnorm_value(bf16_lo(xw[i]), rstd, bf16_lo(gw[i]) + zc),
-                                                                   rmsnorm_value(bf16_hi(xw[i]), rstd, bf16_hi(gw[i]) + zc));
-                    y[i] = *reinterpret_cast<const uint32_t *>(&t);
+                    for (int i = 0; i < 4; ++i) {
+                        const __nv_bfloat162 t = __floats2bfloat162_rn(rmsnorm_value(bf16_lo(xw[i]), rstd, gp[k][2 * i]),
+                                                                       rmsnorm_value(bf16_hi(xw[i]), rstd, gp[k][2 * i + 1]));
+                        y[i] = *reinterpret_cast<const uint32_t *>(&t);
+                    }
+                } else {
+                    const uint4 gv = __ldg(reinterpret_cast<const uint4 *>(gamma + h));
+                    const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const __nv_bfloat162 t = __floats2bfloat162_rn(rmsnorm_value(bf16_lo(xw[i]), rstd, bf16_lo(gw[i]) + zc),
+                                                                       rmsnorm_value(bf16_hi(xw[i]), rstd, bf16_hi(gw[i]) + zc));
+                        y[i] = *reinterpret_cast<const uint32_t *>(&t);
+                    }
                 }
             }
             // |max| of the 32-element block: this thread's four words, then the three neighbours
