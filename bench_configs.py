@@ -229,6 +229,9 @@ def quantize_records(dev, peaks, copies=4):
             4 * eo + 4 * rows + ob, "mx_quant_split_kernel<SwiGLU prologue>")
         run(f"swiglu_{nm}_dual_two_kernels_{rows}x{inter}", [lambda x=x: qi.glu_quantize_mx_impl(x, probs, None, "silu", od, fused=False) for x in xg],
             4 * eo + 4 * rows + ob, "glu_fwd_kernel + mx_quant_split_kernel (same algorithmic bytes counted; moves 4 more bytes per element)")
+    for fused, nm in ((True, "one_pass"), (False, "two_kernels")):   # the forward-only form: row-wise copy alone
+        run(f"swiglu_mxfp8_row_{nm}_{rows}x{inter}", [lambda x=x: qi.glu_quantize_mx_row_impl(x, probs, None, "silu", f8, fused=fused) for x in xg],
+            4 * eo + 4 * rows + eo + eo // 32, "glu_mx_row_kernel" if fused else "glu_fwd_kernel + mx_quant_tma_kernel (same algorithmic bytes counted)")
     del xg
     # RMSNorm feeding an MX GEMM (C2's activation): statistics pass + normalising quantizer against rmsnorm + quantizer
     gam = randn_bf16((K,), 1.0, 62, dev)

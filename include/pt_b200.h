@@ -401,6 +401,13 @@ int pt_grouped_glu_quantize_mx(const void *x, int x_dtype, const float *probs, c
 int pt_rmsnorm_quantize_mx(const void *x, int x_dtype, const float *rstd, const void *gamma, int zero_centered, int64_t rows, int64_t H, int fmt,
                            unsigned flags, void *q_row, uint8_t *s_row, void *q_col, uint8_t *s_col, void *stream);
 
+/* Gated activation and the row-wise MX copy in one pass (forward-only callers: no transposed copy): what pt_glu_fwd followed
+ * by pt_quantize_mx (flags PT_MX_ROW) writes, byte for byte.  x bf16 [rows, 2H]; H a multiple of 32 (else
+ * PT_ERR_UNSUPPORTED); fmt PT_E4M3, PT_E5M2 or PT_E2M1; q_row [rows, ceil(H, 128)] codes, s_row [rows, ceil(H, 128) / 32].
+ * (primus_turbo/pytorch/ops/activation.py:72-80 followed by quantize_fp8 of the reference.) */
+int pt_glu_quantize_mx_row(const void *x, int x_dtype, const float *probs, const int64_t *row_mask, int64_t rows, int64_t H, int act, int fmt,
+                           void *q_row, uint8_t *s_row, void *stream);
+
 /* RMSNorm and the row-wise MX copy in one pass over x (forward-only callers need no transposed copy): writes rstd [rows]
  * and what pt_rmsnorm_fwd followed by pt_quantize_mx (flags PT_MX_ROW) writes, byte for byte, without y in memory.
  * x, gamma bf16; fmt PT_E4M3, PT_E5M2 or PT_E2M1; q_row [rows, ceil(H, 128)] codes (half the bytes for e2m1), s_row

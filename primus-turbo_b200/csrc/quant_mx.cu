@@ -859,6 +859,48 @@ __device__ __forceinline__ void split_prologue(uint8_t *tile, int t, int in_row0
     sm100::named_barrier<3, 2 * kSGroupThreads>();
 }
 
+// The quantization of one 32-element block held by four neighbouring lanes, eight bf16 values (four packed words) each:
+// |max| over the four lanes (NaN ignored), ue8m0 scale, codes.  Every lane of the warp must call it.  Returns the scale
+// byte; `out` receives 8 fp8 codes (two words) or 8 e2m1 codes (one word).
+template <int FMT>
+__device__ __forceinline__ uint8_t mx_block_of_four_lanes(uint32_t (&y)[4], uint32_t (&out)[2]) {
+    using T = __nv_bfloat16;
+    constexpr bool kFp4 = FMT == PT_E2M1;
+    uint32_t pm = 0u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pm = absmax2_nan_bf16(pm, y[i]);
+    pm = absmax2_nan_bf16(pm, __shfl_xor_sync(0xffffffffu, pm, 1));
+    pm = absmax2_nan_bf16(pm, __shfl_xor_sync(0xffffffffu, pm, 2));
+    const bool has_nan = packed_bf16_has_nan(pm);
+    if (__any_sync(0xffffffffu, has_nan)) {   // a NaN element takes no part in the maximum (rare: the whole warp redoes it)
+        uint32_t pq = 0u;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) pq = absmax2<T>(pq, y[i]);
+        pq = absmax2<T>(pq, __shfl_xor_sync(0xffffffffu, pq, 1));
+        pq = absmax2<T>(pq, __shfl_xor_sync(0xffffffffu, pq, 2));
+        if (has_nan) pm = pq;
+    }
+    pm = absmax2_done(pm);
+    const MxScale sc = mx_scale<FMT>(fmaxf(bf16_lo(pm), bf16_hi(pm)), false);
+    if (has_nan && !kFp4) {
+        const float nlim = -MxParams<FMT>::qmax * sc.native;
+        const uint32_t nlim2 = bf16_bits_x2(nlim, nlim);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) y[i] = max_bf16x2(y[i], nlim2);
+    }
+    const uint32_t inv2 = bf16_bits_x2(sc.inv, sc.inv);
+    const uint32_t s0 = mul_bf16x2(y[0], inv2), s1 = mul_bf16x2(y[1], inv2), s2 = mul_bf16x2(y[2], inv2), s3 = mul_bf16x2(y[3], inv2);
+    if constexpr (kFp4) {
+        out[0] = pack8_e2m1(bf16_lo(s0), bf16_hi(s0), bf16_lo(s1), bf16_hi(s1), bf16_lo(s2), bf16_hi(s2), bf16_lo(s3), bf16_hi(s3));
+        out[1] = 0u;
+    } else {
+        out[0] = pack4_fp8<FMT>(bf16_lo(s0), bf16_hi(s0), bf16_lo(s1), bf16_hi(s1));
+        out[1] = pack4_fp8<FMT>(bf16_lo(s2), bf16_hi(s2), bf16_lo(s3), bf16_hi(s3));
+    }
+    if (sc.byte == 0) out[0] = out[1] = 0u;
+    return sc.byte;
+}
+
 // RMSNorm and the row-wise MX copy in one pass over x (the forward-only / inference form: no transposed copy): a block
 // reads a row into registers, forms rstd in the order of the stand-alone RMSNorm kernel (activation_norm.cu: per-thread
 // sums over its vectors in turn, eight warp reductions, then the eight warp sums in turn), normalises with its
@@ -953,46 +995,54 @@ __global__ void __launch_bounds__(kRnThreads, KEEP == 2 ? 5 : 4) rmsnorm_mx_row_
                     }
                 }
             }
-            // |max| of the 32-element block: this thread's four words, then the three neighbours
-            uint32_t pm = 0u;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) pm = absmax2_nan_bf16(pm, y[i]);
-            pm = absmax2_nan_bf16(pm, __shfl_xor_sync(0xffffffffu, pm, 1));
-            pm = absmax2_nan_bf16(pm, __shfl_xor_sync(0xffffffffu, pm, 2));
-            const bool has_nan = packed_bf16_has_nan(pm);
-            if (__any_sync(0xffffffffu, has_nan)) {   // a NaN element takes no part in the maximum (rare: the whole warp redoes it)
-                uint32_t pq = 0u;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) pq = absmax2<T>(pq, y[i]);
-                pq = absmax2<T>(pq, __shfl_xor_sync(0xffffffffu, pq, 1));
-                pq = absmax2<T>(pq, __shfl_xor_sync(0xffffffffu, pq, 2));
-                if (has_nan) pm = pq;
+            uint32_t o[2];
+            const uint8_t sbyte = mx_block_of_four_lanes<FMT>(y, o);   // every lane takes part
+            if (live) {
+                if constexpr (kFp4) *reinterpret_cast<uint32_t *>(q_row + (r * n_pad + h) / 2) = o[0];
+                else *reinterpret_cast<uint2 *>(q_row + r * n_pad + h) = make_uint2(o[0], o[1]);
             }
-            pm = absmax2_done(pm);
-            const float m = fmaxf(bf16_lo(pm), bf16_hi(pm));
-            const MxScale sc = mx_scale<FMT>(m, false);
-            if (has_nan && !kFp4) {
-                const float nlim = -MxParams<FMT>::qmax * sc.native;
-                const uint32_t nlim2 = bf16_bits_x2(nlim, nlim);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) y[i] = max_bf16x2(y[i], nlim2);
-            }
-            const uint32_t inv2 = bf16_bits_x2(sc.inv, sc.inv);
-            const uint32_t s0 = mul_bf16x2(y[0], inv2), s1 = mul_bf16x2(y[1], inv2), s2 = mul_bf16x2(y[2], inv2), s3 = mul_bf16x2(y[3], inv2);
-            if constexpr (kFp4) {
-                uint32_t o = pack8_e2m1(bf16_lo(s0), bf16_hi(s0), bf16_lo(s1), bf16_hi(s1), bf16_lo(s2), bf16_hi(s2), bf16_lo(s3), bf16_hi(s3));
-                if (sc.byte == 0) o = 0u;
-                if (live) *reinterpret_cast<uint32_t *>(q_row + (r * n_pad + h) / 2) = o;
-            } else {
-                uint2 o = make_uint2(pack4_fp8<FMT>(bf16_lo(s0), bf16_hi(s0), bf16_lo(s1), bf16_hi(s1)),
-                                     pack4_fp8<FMT>(bf16_lo(s2), bf16_hi(s2), bf16_lo(s3), bf16_hi(s3)));
-                if (sc.byte == 0) o = make_uint2(0u, 0u);
-                if (live) *reinterpret_cast<uint2 *>(q_row + r * n_pad + h) = o;
-            }
-            if (live && (threadIdx.x & 3) == 0) s_row[r * (n_pad / 32) + h / 32] = sc.byte;
+            if (live && (threadIdx.x & 3) == 0) s_row[r * (n_pad / 32) + h / 32] = sbyte;
         }
 #pragma unroll
         for (int k = 0; k < KEEP; ++k) keep[k] = next[k];
+    }
+}
+
+// Gated activation and the row-wise MX copy in one pass (forward-only callers): out = act(x[:, :H]) * x[:, H:] * probs[row]
+// with the stand-alone kernel's arithmetic and rounding (activation_norm.cu, act_math.cuh), quantized as the row-wise
+// quantizer does; masked rows are zeros.  A block walks a row in steps of 2048 columns.  (Requesting the next step's inputs
+// ahead made it slower, 4200 -> 3900 GB/s on 32768 x 2048: it is bound by its arithmetic, not by the loads.)
+template <int FMT, int ACT>
+__global__ void __launch_bounds__(kRnThreads) glu_mx_row_kernel(const __nv_bfloat16 *__restrict__ x, const float *__restrict__ probs,
+                                                                const int64_t *__restrict__ row_mask, int64_t rows, int64_t H, int64_t n_pad,
+                                                                uint8_t *__restrict__ q_row, uint8_t *__restrict__ s_row) {
+    constexpr bool kFp4 = FMT == PT_E2M1;
+    const int64_t steps = (n_pad + kRnThreads * 8 - 1) / (kRnThreads * 8);
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const bool masked = row_mask != nullptr && row_mask[r] == 0;
+        const float p = probs[r];
+        const __nv_bfloat16 *a = x + r * 2 * H, *b = a + H;
+        for (int64_t it = 0; it < steps; ++it) {
+            const int64_t h = (it * kRnThreads + threadIdx.x) * 8;
+            uint32_t y[4] = {0u, 0u, 0u, 0u};
+            if (h < H && !masked) {
+                const uint4 ar = __ldg(reinterpret_cast<const uint4 *>(a + h)), br = __ldg(reinterpret_cast<const uint4 *>(b + h));
+                const uint32_t aw[4] = {ar.x, ar.y, ar.z, ar.w}, bw[4] = {br.x, br.y, br.z, br.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const __nv_bfloat162 t = __floats2bfloat162_rn(glu_value<ACT>(bf16_lo(aw[i]), bf16_lo(bw[i]), p),
+                                                                   glu_value<ACT>(bf16_hi(aw[i]), bf16_hi(bw[i]), p));
+                    y[i] = *reinterpret_cast<const uint32_t *>(&t);
+                }
+            }
+            uint32_t o[2];
+            const uint8_t sbyte = mx_block_of_four_lanes<FMT>(y, o);   // every lane takes part
+            if (h < n_pad) {
+                if constexpr (kFp4) *reinterpret_cast<uint32_t *>(q_row + (r * n_pad + h) / 2) = o[0];
+                else *reinterpret_cast<uint2 *>(q_row + r * n_pad + h) = make_uint2(o[0], o[1]);
+                if ((threadIdx.x & 3) == 0) s_row[r * (n_pad / 32) + h / 32] = sbyte;
+            }
+        }
     }
 }
 
@@ -1704,6 +1754,43 @@ int pt_rmsnorm_quantize_mx(const void *x, int x_dtype, const float *rstd, const 
     PT_REQUIRE(x && rstd && gamma && aligned(gamma, 16), "%s: null or unaligned pointer", what);
     a.pro_rowvec = rstd; a.pro_gamma = gamma; a.pro_zero_centered = zero_centered;
     return launch_fused<PT_PRO_RMSNORM, false>(a, what, fmt, flags, (cudaStream_t) stream);
+}
+
+int pt_glu_quantize_mx_row(const void *x, int x_dtype, const float *probs, const int64_t *row_mask, int64_t rows, int64_t H, int act, int fmt,
+                           void *q_row, uint8_t *s_row, void *stream) {
+    const char *what = "gated activation + row-wise MX quantize";
+    PT_REQUIRE(rows >= 0 && H >= 0 && (act == 0 || act == 1), "%s: bad arguments", what);
+    PT_REQUIRE(x_dtype == PT_BF16, "%s: bf16 input", what);
+    PT_REQUIRE(fmt == PT_E4M3 || fmt == PT_E5M2 || fmt == PT_E2M1, "%s: formats e4m3, e5m2, e2m1", what);
+    if (H % 32 != 0) return PT_ERR_UNSUPPORTED;   // the caller runs the two kernels
+    if (rows == 0 || H == 0) return PT_OK;
+    PT_REQUIRE(x && probs && q_row && s_row && aligned(x, 16) && aligned(q_row, 8), "%s: null or unaligned pointer", what);
+    const int64_t n_pad = ceil_to(H, 128);
+    cudaStream_t st = (cudaStream_t) stream;
+#define PT_GR_LAUNCH(F_, A_)                                                                                        \
+    do {                                                                                                            \
+        auto kern = glu_mx_row_kernel<F_, A_>;                                                                      \
+        int per_sm = 0;                                                                                             \
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kRnThreads, 0) != cudaSuccess || per_sm <= 0) { \
+            cudaGetLastError();                                                                                     \
+            per_sm = 2;                                                                                             \
+        }                                                                                                           \
+        const int64_t per_cta = std::max<int64_t>(1, ceil_div(rows, (int64_t) sm_count() * per_sm));               \
+        kern<<<(int) ceil_div(rows, per_cta), kRnThreads, 0, st>>>((const __nv_bfloat16 *) x, probs, row_mask, rows, H, n_pad, \
+                                                                   (uint8_t *) q_row, s_row);                      \
+    } while (0)
+#define PT_GR_FMT(A_)                                                                                               \
+    do {                                                                                                            \
+        if (fmt == PT_E4M3) PT_GR_LAUNCH(PT_E4M3, A_);                                                              \
+        else if (fmt == PT_E5M2) PT_GR_LAUNCH(PT_E5M2, A_);                                                         \
+        else PT_GR_LAUNCH(PT_E2M1, A_);                                                                             \
+    } while (0)
+    if (act == 0) PT_GR_FMT(PT_ACT_SILU);
+    else PT_GR_FMT(PT_ACT_GELU);
+#undef PT_GR_FMT
+#undef PT_GR_LAUNCH
+    PT_LAUNCH_OK();
+    return PT_OK;
 }
 
 int pt_rmsnorm_quantize_mx_row(const void *x, int x_dtype, const void *gamma, float eps, int zero_centered, int64_t rows, int64_t H,

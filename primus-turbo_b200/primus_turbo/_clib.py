@@ -47,6 +47,7 @@ SIGNATURES = {
     "pt_moe_unpermute": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "pt_moe_unpermute_bwd_with_probs": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p,
                                                 c_void_p, c_void_p]),
+    "pt_glu_quantize_mx_row": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "pt_rmsnorm_quantize_mx_row": (c_int, [c_void_p, c_int, c_void_p, c_float, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p,
                                            c_void_p]),
     "pt_shuffle_e8m0_scale": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),

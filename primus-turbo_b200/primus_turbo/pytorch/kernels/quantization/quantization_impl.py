@@ -594,6 +594,30 @@ def grouped_glu_quantize_mx_impl(x, probs, row_mask, act: str, out_dtype, group_
     return _grouped_mx_quant(x, out_dtype, group_lens, group_offs, True, True, row_r, col_r, pro=("glu", probs, row_mask, ACT_CODES[act]))
 
 
+def glu_quantize_mx_row_impl(x: torch.Tensor, probs: torch.Tensor, row_mask, act: str, out_dtype, fused=None):
+    """Row-wise MX copy of act(x[:, :H]) * x[:, H:] * probs, (q_row, s_row), in one pass over x: what a forward-only caller
+    feeds the down projection.  Falls back to activation kernel + row-wise quantizer outside the one-pass kernel's range
+    (bf16, H a multiple of 32); both write the same bytes."""
+    from ..activation.glu_impl import ACT_CODES, glu_fwd_with_probs
+    nv.require_cuda(x, probs, row_mask)
+    rows, h2 = x.shape
+    H = h2 // 2
+    ok = x.dtype == torch.bfloat16 and H % MX_BLOCK == 0
+    use = ok if fused is None else fused
+    if use:
+        x, probs = x.contiguous(), probs.contiguous().view(-1)
+        fmt = nv.fmt_code(out_dtype)
+        n_pad = ceil_div(H, MX_ALIGN) * MX_ALIGN
+        q = torch.empty(rows, n_pad // (2 if fmt == nv.PT_E2M1 else 1), dtype=torch.uint8, device=x.device)
+        s = torch.empty(rows, n_pad // MX_BLOCK, dtype=torch.uint8, device=x.device)
+        with nv.on_device(x.device):
+            nv.check(nv.lib().pt_glu_quantize_mx_row(nv.ptr(x), nv.src_code(x.dtype), nv.ptr(probs), nv.ptr(row_mask), rows, H, ACT_CODES[act], fmt,
+                                                      nv.ptr(q), nv.ptr(s), nv.stream(x.device)), "glu_quantize_mx_row")
+        return q.view(out_dtype), s.view(torch.float8_e8m0fnu)
+    q, s, _, _ = _mx_quant(glu_fwd_with_probs(x, probs, row_mask, act), out_dtype, True, False, ScalingRecipe(), ScalingRecipe())
+    return q, s
+
+
 def rmsnorm_quantize_mx_row_impl(x: torch.Tensor, gamma: torch.Tensor, eps: float, zero_centered: bool, out_dtype, fused=None):
     """Row-wise MX copy of rmsnorm(x) and the row statistics, (q_row, s_row, rstd), in one pass over x: what a forward-only
     caller feeds the first GEMM.  Falls back to RMSNorm kernel + row-wise quantizer outside the one-pass kernel's range

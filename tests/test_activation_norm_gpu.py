@@ -291,3 +291,23 @@ def test_rmsnorm_row_quantizer_one_pass_equals_two_kernels(out_dtype, rows, H, z
     assert torch.equal(one[0].view(torch.uint8), two[0].view(torch.uint8))
     assert torch.equal(one[1].view(torch.uint8), two[1].view(torch.uint8))
     assert torch.equal(one[2].view(torch.int32), two[2].view(torch.int32))
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu"])
+@pytest.mark.parametrize("out_dtype", [torch.float8_e4m3fn, torch.float8_e5m2, torch.float4_e2m1fn_x2])
+@pytest.mark.parametrize("rows,H,masked", [(1, 32, False), (128, 64, False), (1000, 1408, True), (300, 2048, False), (77, 7168, False), (50, 2080, True)])
+def test_glu_row_quantizer_one_pass_equals_two_kernels(act, out_dtype, rows, H, masked):
+    """Forward-only form: gated activation and the row-wise MX copy in one pass write the bytes of activation kernel +
+    quantizer; masked rows, a NaN and an inf included."""
+    from primus_turbo.pytorch.kernels.quantization.quantization_impl import glu_quantize_mx_row_impl
+    g = torch.Generator(device="cuda").manual_seed(rows * 3 + H)
+    x = torch.randn(rows, 2 * H, device="cuda", dtype=torch.bfloat16, generator=g) * 2
+    if rows > 2:
+        x[1, 3] = float("nan")
+        x[2, H + 7] = float("inf")
+    probs = torch.rand(rows, device="cuda", generator=g)
+    mask = (torch.rand(rows, device="cuda", generator=g) > 0.3).to(torch.int64) if masked else None
+    one = glu_quantize_mx_row_impl(x, probs, mask, act, out_dtype, fused=True)
+    two = glu_quantize_mx_row_impl(x, probs, mask, act, out_dtype, fused=False)
+    assert torch.equal(one[0].view(torch.uint8), two[0].view(torch.uint8))
+    assert torch.equal(one[1].view(torch.uint8), two[1].view(torch.uint8))
