@@ -11,7 +11,7 @@ functions of the `*_impl` modules, which call the C ABI.
 The autograd Functions of `primus_turbo.pytorch.ops` call those functions directly (one Python frame less per launch);
 code that was written against `torch.ops.primus_turbo.<name>` or traces through the ops finds them here.
 """
-from typing import Optional, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 
@@ -333,6 +333,29 @@ def _(x, dtype, block_size, group_lens, group_offs, gemm_other_dim=None):
             e((m_alloc // block_size, N), torch.float32), e((G,), torch.int64), e((G + 1,), torch.int64))
 
 
+# ------------------------------------------------------------------------------------------------ pre-shuffled layouts
+# (torch.ops.primus_turbo_cpp_extension.shuffle_scale / shuffle_weight of the reference: csrc/pytorch/bindings_pytorch.cpp)
+@_op("primus_turbo::shuffle_scale", mutates_args=(), device_types="cuda")
+def shuffle_scale(scale: torch.Tensor, layout: List[int]) -> torch.Tensor:
+    return _q.shuffle_scale_impl(scale, tuple(layout))
+
+
+@shuffle_scale.register_fake
+def _(scale, layout):
+    M, N = scale.shape
+    return torch.empty((_ceil_div(M, 256) * 256, _ceil_div(N, 8) * 8), dtype=scale.dtype, device=scale.device)
+
+
+@_op("primus_turbo::shuffle_weight", mutates_args=(), device_types="cuda")
+def shuffle_weight(weight: torch.Tensor, layout: List[int]) -> torch.Tensor:
+    return _q.shuffle_weight_impl(weight, tuple(layout))
+
+
+@shuffle_weight.register_fake
+def _(weight, layout):
+    return torch.empty_like(weight)
+
+
 REGISTERED = [
     "gemm_fp8_impl", "gemm_fp8_accum_impl", "gemm_fp4_impl", "gemm_fp4_accum_impl", "gemm_impl", "gemm_accum_impl",
     "grouped_gemm_fp8_impl", "grouped_gemm_fp8_variable_k_impl", "grouped_gemm_fp8_variable_k_accum_impl",
@@ -340,4 +363,5 @@ REGISTERED = [
     "grouped_gemm_impl", "grouped_gemm_variable_k_impl", "grouped_gemm_variable_k_accum_impl",
     "quant_fp8_blockwise_impl", "dequant_fp8_blockwise_impl", "dequant_fp8_blockwise_for_weight_impl",
     "quant_fp8_blockwise_dual_impl", "quant_fp8_blockwise_for_weight_impl", "quant_fp8_blockwise_segment_m_row_col_impl",
+    "shuffle_scale", "shuffle_weight",
 ]

@@ -98,6 +98,9 @@ def test_custom_ops_are_registered_with_fake_impls():
         assert tuple(s.shape) == (3, 520)
         qr, sr, qc, sc = torch.ops.primus_turbo.quant_fp8_blockwise_dual_impl(e((256, 384)), f8)
         assert tuple(sr.shape) == (256, 3) and tuple(sc.shape) == (2, 384)
+        sh = torch.ops.primus_turbo.shuffle_scale(e((100, 9), torch.float8_e8m0fnu), [16, 16])
+        assert tuple(sh.shape) == (256, 16) and sh.dtype == torch.float8_e8m0fnu
+        assert tuple(torch.ops.primus_turbo.shuffle_weight(e((32, 64), torch.uint8), [16, 16]).shape) == (32, 64)
         qw, sw = torch.ops.primus_turbo.quant_fp8_blockwise_for_weight_impl(e((4, 256, 384)), f8)
         assert tuple(sw.shape) == (4, 2, 3)
         lens, offs = e((4,), torch.int64), e((5,), torch.int64)
