@@ -600,7 +600,9 @@ def glu_quantize_mx_row_impl(x: torch.Tensor, probs: torch.Tensor, row_mask, act
     (bf16, H a multiple of 32); both write the same bytes."""
     from ..activation.glu_impl import ACT_CODES, glu_fwd_with_probs
     nv.require_cuda(x, probs, row_mask)
+    x = x.reshape(-1, x.shape[-1])
     rows, h2 = x.shape
+    assert h2 % 2 == 0
     H = h2 // 2
     ok = x.dtype == torch.bfloat16 and H % MX_BLOCK == 0
     use = ok if fused is None else fused
