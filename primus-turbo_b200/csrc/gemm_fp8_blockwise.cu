@@ -542,9 +542,9 @@ static int bw_launch_pair(Kernel kernel, int64_t tiles, cudaStream_t stream, con
     return PT_OK;
 }
 
-// The CTA-pair form is correct but not faster than the single-CTA kernel yet (B200: 1965-2009 against 2077-2115
-// TFLOP/s on 8192 x 14336 x 4096 and 8192^3): it relieves shared memory, but the promotion warps set the pace in both
-// forms and the pair adds a cross-CTA hand-over of the partial-sum buffer per K step.  It therefore runs only when
+// The CTA-pair form is correct but slower than the single-CTA kernel (B200, 8192 x 14336 x 4096: 1730-1800 against
+// 2157-2162 TFLOP/s; 8192^3: 1600-1640 against 2020-2070): it halves the operand traffic per SM, but the promotion warps set
+// the pace in both forms and the pair adds a cross-CTA hand-over of the partial-sum buffer per K step.  It therefore runs only when
 // PT_BW_GEMM_PAIR=1 (read per call); PT_GEMM_PAIR=0 switches it off together with the other pair kernels.
 static bool bw_pair_enabled() {
     const char *on = getenv("PT_BW_GEMM_PAIR");
