@@ -276,3 +276,30 @@ def test_mx_row_copy_at_a_16_byte_aligned_output(qi):
     assert torch.equal(q_view.view(M, N), q_ref.view(torch.uint8))
     assert torch.equal(s_row, s_ref.view(torch.uint8))
     assert int(raw[:16].max()) == 0 and int(raw[16 + M * N:].max()) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("which", ["mxfp8_dual", "mxfp4_dual", "mxfp8_dual_2d", "blockwise_dual", "rowwise", "tensorwise"])
+def test_quantizers_give_the_same_bytes_every_launch(which):
+    """Twenty launches on an input that fills every SM several times over must agree byte for byte with the first: the
+    warp-specialised quantizers synchronise their warp groups with mbarriers and named barriers, and a lost or early
+    hand-over shows up as a few blocks that differ in a few launches of a hundred, not as a wrong result every time."""
+    import primus_turbo.pytorch as turbo
+    from primus_turbo.pytorch.core.low_precision import ScalingGranularity as SG, ScalingRecipe
+    from primus_turbo.pytorch.kernels.quantization import quantization_impl as qi
+    g = torch.Generator(device="cuda").manual_seed(77)
+    x = torch.randn(4096, 7168, device="cuda", dtype=torch.bfloat16, generator=g)
+    f8, f4 = torch.float8_e4m3fn, torch.float4_e2m1fn_x2
+    run = {
+        "mxfp8_dual": lambda: qi.quantize_mxfp8_impl(x, f8, None, 32, True),
+        "mxfp4_dual": lambda: qi.quantize_mxfp4_impl(x, f4, None, 32, True),
+        "mxfp8_dual_2d": lambda: qi.quantize_mxfp8_impl(x, f8, None, 32, True, ScalingRecipe(use_2d_block=True), ScalingRecipe(use_2d_block=True)),
+        "blockwise_dual": lambda: qi.quant_fp8_blockwise_dual_impl(x, f8),
+        "rowwise": lambda: qi.quantize_fp8_rowwise_impl(x, f8, -1) + qi.quantize_fp8_rowwise_impl(x, f8, -2),
+        "tensorwise": lambda: qi.quantize_fp8_tensorwise_impl(x, f8),
+    }[which]
+    bits = lambda t: t.view(torch.uint8) if t.element_size() == 1 else t.view(torch.int32)
+    first = [bits(t).clone() for t in run()]
+    for _ in range(20):
+        for a, b in zip(run(), first):
+            assert torch.equal(bits(a), b)
