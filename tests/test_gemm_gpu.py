@@ -146,6 +146,32 @@ def test_mx_deterministic(mods):
     nv.check_status(first.device)
 
 
+def test_large_gemms_repeat_bit_identically(mods):
+    """Sizes that keep every SM busy for many tiles (CTA pairs for MX, the promotion warps of the blockwise kernel in all
+    three directions): ten launches each must agree bit for bit, so that a hand-over between warp roles that is lost now
+    and then does not hide behind a tolerance."""
+    qi, gi, nv, SG, _ = mods
+    f8, f5 = torch.float8_e4m3fn, torch.float8_e5m2
+    M, N, K = 4096, 3584, 2048
+    x, w, dy = make((M, K), torch.bfloat16, 41), make((N, K), torch.bfloat16, 42), make((M, N), torch.bfloat16, 43)
+    qa, sa = qi.quantize_mxfp8_impl(x, f8, 1, 32)
+    qb, sb = qi.quantize_mxfp8_impl(w, f8, 1, 32)
+    a_row, a_row_s, a_col, a_col_s = qi.quant_fp8_blockwise_dual_impl(x, f8)
+    w_q, w_s = qi.quant_fp8_blockwise_for_weight_impl(w, f8)
+    g_row, g_row_s, g_col, g_col_s = qi.quant_fp8_blockwise_dual_impl(dy, f5)
+    runs = [
+        lambda: gi.gemm_fp8_impl(qa, sa, False, qb, sb, True, torch.bfloat16, False, SG.MX_BLOCKWISE),
+        lambda: gi.gemm_fp8_impl(a_row, a_row_s, False, w_q, w_s, True, torch.bfloat16, False, SG.BLOCKWISE),
+        lambda: gi.gemm_fp8_impl(g_row, g_row_s, False, w_q, w_s, False, torch.bfloat16, False, SG.BLOCKWISE),
+        lambda: gi.gemm_fp8_impl(a_col, a_col_s, True, g_col, g_col_s, False, torch.bfloat16, True, SG.BLOCKWISE),
+    ]
+    for run in runs:
+        first = run()
+        for _ in range(9):
+            assert torch.equal(first, run())
+    nv.check_status(x.device)
+
+
 def test_accumulate_into_out(mods):
     qi, gi, nv, SG, _ = mods
     a, b = make((256, 256), torch.bfloat16, 33), make((384, 256), torch.bfloat16, 34)
