@@ -489,6 +489,16 @@ def _small_case(name, args):
         for _ in range(2):
             gemm_fp8_impl(a_row, a_row_s, False, b_row, b_row_s, True, torch.bfloat16, False, SG.MX_BLOCKWISE)
             gemm_fp8_impl(g_col, g_col_s, False, a_col, a_col_s, True, torch.bfloat16, False, SG.MX_BLOCKWISE)
+    elif name in ("rmsnorm_mx_row", "glu_mx_row"):   # the one-pass forward-only forms
+        M, N = (int(args[0]), int(args[1])) if len(args) >= 2 else (8192, 4096)
+        xs = [randn_bf16((M, N * (2 if name == "glu_mx_row" else 1)), 1.0, i, dev) for i in range(3)]
+        gamma = randn_bf16((N,), 1.0, 7, dev)
+        probs = torch.rand(M, device=dev)
+        for i in range(6):
+            if name == "rmsnorm_mx_row":
+                qi.rmsnorm_quantize_mx_row_impl(xs[i % 3], gamma, 1e-6, False, f8, fused=True)
+            else:
+                qi.glu_quantize_mx_row_impl(xs[i % 3], probs, None, "silu", f8, fused=True)
     elif name in ("rowwise_other_axis", "rmsnorm_bwd", "rmsnorm_mx_dual"):
         from primus_turbo.pytorch.kernels.normalization import rmsnorm_impl as ri
         M, N = (int(args[0]), int(args[1])) if len(args) >= 2 else (8192, 4096)
@@ -506,7 +516,7 @@ def _small_case(name, args):
                 qi.rmsnorm_quantize_mx_impl(x, gamma, 1e-6, False, f8, fused=True)
     else:
         raise SystemExit(f"unknown case {name!r}: mx_dual, mxfp4_dual, blockwise_dual, swiglu_mx_dual, rowwise_other_axis, "
-                         "rmsnorm_bwd, rmsnorm_mx_dual [M N]; blockwise_grouped [G rows]; mx_c3 [M N K]")
+                         "rmsnorm_bwd, rmsnorm_mx_dual, rmsnorm_mx_row, glu_mx_row [M N]; blockwise_grouped [G rows]; mx_c3 [M N K]")
     torch.cuda.synchronize()
     print("ok", name, *args)
 
