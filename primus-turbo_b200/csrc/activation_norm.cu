@@ -488,7 +488,17 @@ __global__ void __launch_bounds__(32 * kDgLanes) rmsnorm_dgamma_kernel(const flo
     }
 }
 
-static int an_grid(int64_t rows) { return (int) std::min<int64_t>(rows, (int64_t) sm_count() * 8); }
+// Grid of a block-per-row kernel: no more CTAs than are resident at once, and the same number of rows for each, give or
+// take one (a fixed "SMs x 8" grid left the last of its 1.6 waves 60 % full on kernels that fit five CTAs per SM).
+template <typename Kernel> static int an_grid(Kernel kern, int64_t rows) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kAnThreads, 0) != cudaSuccess || per_sm <= 0) {
+        cudaGetLastError();
+        per_sm = 4;
+    }
+    const int64_t per_cta = std::max<int64_t>(1, ceil_div(rows, (int64_t) sm_count() * per_sm));
+    return (int) std::max<int64_t>(1, ceil_div(rows, per_cta));
+}
 
 }  // namespace ptb
 
@@ -502,8 +512,8 @@ int pt_glu_fwd(const void *x, int dtype, const float *probs, const int64_t *row_
     PT_REQUIRE(x && probs && out, "glu forward: null pointer");
     PT_REQUIRE((H * (dtype == PT_F32 ? 4 : 2)) % 16 == 0 && aligned(x, 16) && aligned(out, 16), "glu forward: H must give 16-byte rows, 16-byte aligned");
     PT_SWITCH_SRC(dtype, T, {
-        if (act == 0) glu_fwd_kernel<T, PT_ACT_SILU><<<an_grid(rows), kAnThreads, 0, (cudaStream_t) stream>>>((const T *) x, probs, row_mask, rows, H, (T *) out);
-        else glu_fwd_kernel<T, PT_ACT_GELU><<<an_grid(rows), kAnThreads, 0, (cudaStream_t) stream>>>((const T *) x, probs, row_mask, rows, H, (T *) out);
+        if (act == 0) glu_fwd_kernel<T, PT_ACT_SILU><<<an_grid(glu_fwd_kernel<T, PT_ACT_SILU>, rows), kAnThreads, 0, (cudaStream_t) stream>>>((const T *) x, probs, row_mask, rows, H, (T *) out);
+        else glu_fwd_kernel<T, PT_ACT_GELU><<<an_grid(glu_fwd_kernel<T, PT_ACT_GELU>, rows), kAnThreads, 0, (cudaStream_t) stream>>>((const T *) x, probs, row_mask, rows, H, (T *) out);
     });
     PT_LAUNCH_OK();
     return PT_OK;
@@ -518,10 +528,10 @@ int pt_glu_bwd(const void *grad_out, const void *x, int dtype, const float *prob
                "glu backward: H must give 16-byte rows, 16-byte aligned");
     PT_SWITCH_SRC(dtype, T, {
         if (act == 0)
-            glu_bwd_kernel<T, PT_ACT_SILU><<<an_grid(rows), kAnThreads, 0, (cudaStream_t) stream>>>((const T *) grad_out, (const T *) x, probs, row_mask, rows,
+            glu_bwd_kernel<T, PT_ACT_SILU><<<an_grid(glu_bwd_kernel<T, PT_ACT_SILU>, rows), kAnThreads, 0, (cudaStream_t) stream>>>((const T *) grad_out, (const T *) x, probs, row_mask, rows,
                                                                                                 H, (T *) grad_x, grad_probs);
         else
-            glu_bwd_kernel<T, PT_ACT_GELU><<<an_grid(rows), kAnThreads, 0, (cudaStream_t) stream>>>((const T *) grad_out, (const T *) x, probs, row_mask, rows,
+            glu_bwd_kernel<T, PT_ACT_GELU><<<an_grid(glu_bwd_kernel<T, PT_ACT_GELU>, rows), kAnThreads, 0, (cudaStream_t) stream>>>((const T *) grad_out, (const T *) x, probs, row_mask, rows,
                                                                                                 H, (T *) grad_x, grad_probs);
     });
     PT_LAUNCH_OK();
@@ -538,7 +548,7 @@ int pt_rmsnorm_fwd(const void *x, const void *residual, const void *gamma, int d
                      aligned(x_plus_r, 16);   // else element-wise accesses
     cudaStream_t st = (cudaStream_t) stream;
 #define PT_RMS_FWD(V_, RES_) \
-    rmsnorm_fwd_kernel<T, V_, RES_><<<an_grid(rows), kAnThreads, 0, st>>>((const T *) x, (const T *) residual, (const T *) gamma, eps, zero_centered, rows, H, \
+    rmsnorm_fwd_kernel<T, V_, RES_><<<an_grid(rmsnorm_fwd_kernel<T, V_, RES_>, rows), kAnThreads, 0, st>>>((const T *) x, (const T *) residual, (const T *) gamma, eps, zero_centered, rows, H, \
                                                                           (T *) y, (T *) x_plus_r, rstd)
     if (y == nullptr && residual == nullptr && vec) {   // statistics only
         const int grid = (int) std::min<int64_t>(ceil_div(rows, kAnThreads / 32), (int64_t) sm_count() * 8);
