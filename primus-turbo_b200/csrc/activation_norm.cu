@@ -551,8 +551,10 @@ int pt_rmsnorm_fwd(const void *x, const void *residual, const void *gamma, int d
     rmsnorm_fwd_kernel<T, V_, RES_><<<an_grid(rmsnorm_fwd_kernel<T, V_, RES_>, rows), kAnThreads, 0, st>>>((const T *) x, (const T *) residual, (const T *) gamma, eps, zero_centered, rows, H, \
                                                                           (T *) y, (T *) x_plus_r, rstd)
     if (y == nullptr && residual == nullptr && vec) {   // statistics only
-        const int grid = (int) std::min<int64_t>(ceil_div(rows, kAnThreads / 32), (int64_t) sm_count() * 8);
-        PT_SWITCH_SRC(dtype, T, { rmsnorm_stats_kernel<T><<<grid, kAnThreads, 0, st>>>((const T *) x, eps, rows, H, rstd); });
+        PT_SWITCH_SRC(dtype, T, {
+            const int grid = an_grid(rmsnorm_stats_kernel<T>, ceil_div(rows, kAnThreads / 32));   // a warp per row: groups of eight rows
+            rmsnorm_stats_kernel<T><<<grid, kAnThreads, 0, st>>>((const T *) x, eps, rows, H, rstd);
+        });
         PT_LAUNCH_OK();
         return PT_OK;
     }
